@@ -1,0 +1,31 @@
+// Internal interface of the tcgen05 GEMM (see gemm_tc.cu).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace eisen {
+
+enum GemmOutMode : int {
+  GEMM_OUT_BF16 = 0,        // C(bf16)  = alpha * acc
+  GEMM_OUT_BF16_ACC = 1,    // C(bf16) += alpha * acc
+  GEMM_OUT_F32 = 2,         // C(f32)   = alpha * acc
+  GEMM_OUT_F32_ACC = 3,     // C(f32)  += alpha * acc   (read-modify-write, one writer per element)
+  GEMM_OUT_F32_ATOMIC = 4,  // C(f32)  += alpha * acc   (red.global.add, any number of writers)
+};
+
+// a_mn / b_mn: 0 = K-major operand ([rows][K]), 1 = MN-major operand ([K][rows]).
+// Returns 0 on success; *err points at a static message otherwise.  Asynchronous on `stream`.
+int gemm_bf16_tc(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int K, const void* A,
+                 long long lda, const void* B, long long ldb, void* C, long long ldc, int out_mode,
+                 int split_k, float alpha, int* status, const char** err);
+
+// split factor that fills the machine when M*N alone gives fewer tiles than SMs
+int gemm_tc_auto_split_k(int M, int N, int K);
+
+int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
+                      uint64_t row_stride_elems, uint32_t box_inner, uint32_t box_outer);
+int make_tmap_bf16_nd(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                      const uint64_t* strides_elems, const uint32_t* box);
+
+}  // namespace eisen

@@ -1,0 +1,877 @@
+// TEST INFRASTRUCTURE — NOT PRODUCT CODE.
+//
+// CPU restatement of the `Device::Cpu` arms of philsupertramp/eisen's autograd ops, its tape
+// walk, its Llama-style modules and its AdamW, in plain single-precision C++ with the same loop
+// nests and the same accumulation order.  It is the parity oracle of the CUDA path and the timed
+// CPU baseline; only tests, the smoke check and the benchmark's CPU-baseline leg may use it.
+//
+// Parity status: the Rust reference cannot be compiled in this environment (no cargo/rustc), so
+// the oracle is pinned against the literal input/output vectors of the reference's own tests
+// (transcribed in tests/golden/reference_vectors.json) and cross-checked against an independent
+// PyTorch-autograd model.  Whole-model gradients, GQA with repeats > 1, masked cross-entropy and
+// AdamW values are not pinned by any reference vector: for those, parity is pinned by restatement
+// only.
+//
+// Each function cites the reference file:line it follows (paths relative to the reference root).
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <functional>
+#include <limits>
+#include <vector>
+
+#include <thread>
+
+namespace {
+
+struct OTensor {
+  std::vector<size_t> shape;
+  std::vector<float> data;
+  std::vector<float> grad;
+};
+
+struct OGraph;
+struct ONode {
+  std::vector<size_t> inputs;
+  size_t output;
+  std::function<void(OGraph&)> bwd;
+};
+
+// src/graph/mod.rs:56-78 (tensor arena + tape), CPU device only
+struct OGraph {
+  std::vector<OTensor> tensors;
+  std::vector<ONode> tape;
+  bool no_grad = false;
+  size_t num_params = 0;
+};
+
+int g_threads = 1;  // 1 = the reference's schedule (single thread)
+
+// Optional row-parallel schedule for the timed CPU baseline: the outer loop of an op is cut into
+// g_threads contiguous ranges.  Every output element is still produced by the same sequential
+// inner loops, so results do not depend on the thread count.
+template <class F>
+void parallel_for(long long n, F f) {
+  const int T = (g_threads > 1 && n > 1) ? (int)std::min<long long>(g_threads, n) : 1;
+  if (T == 1) { for (long long i = 0; i < n; ++i) f(i); return; }
+  std::vector<std::thread> th;
+  for (int t = 0; t < T; ++t) {
+    long long lo = n * t / T, hi = n * (t + 1) / T;
+    th.emplace_back([=] { for (long long i = lo; i < hi; ++i) f(i); });
+  }
+  for (auto& x : th) x.join();
+}
+#define PFOR(var, n) parallel_for((long long)(n), [&](long long var)
+
+size_t numel(const std::vector<size_t>& s) {
+  size_t n = 1;
+  for (size_t d : s) n *= d;
+  return n;
+}
+
+// src/graph/mod.rs `alloc`: CPU tensors carry a zero grad of the same size
+size_t g_alloc(OGraph& g, std::vector<size_t> shape, std::vector<float> data) {
+  OTensor t;
+  t.shape = std::move(shape);
+  t.grad.assign(data.size(), 0.0f);
+  t.data = std::move(data);
+  g.tensors.push_back(std::move(t));
+  return g.tensors.size() - 1;
+}
+
+void push(OGraph& g, std::vector<size_t> in, size_t out, std::function<void(OGraph&)> f) {
+  if (!g.no_grad) g.tape.push_back(ONode{std::move(in), out, std::move(f)});
+}
+
+// ---------------------------------------------------------------- elementwise
+// src/graph/ops/elementwise.rs:146-184 (broadcast-aware add; both grads accumulate)
+size_t op_add(OGraph& g, size_t a, size_t b) {
+  const auto as = g.tensors[a].shape, bs = g.tensors[b].shape;
+  const size_t nd = std::max(as.size(), bs.size());
+  std::vector<size_t> os(nd), ap(nd, 1), bp(nd, 1);
+  for (size_t i = 0; i < as.size(); ++i) ap[nd - as.size() + i] = as[i];
+  for (size_t i = 0; i < bs.size(); ++i) bp[nd - bs.size() + i] = bs[i];
+  for (size_t i = 0; i < nd; ++i) os[i] = std::max(ap[i], bp[i]);
+  auto bstrides = [&](const std::vector<size_t>& p) {
+    std::vector<size_t> st(nd, 0);
+    size_t acc = 1;
+    for (size_t i = nd; i-- > 0;) {
+      st[i] = (p[i] == 1 && os[i] != 1) ? 0 : acc;
+      acc *= p[i];
+    }
+    return st;
+  };
+  const auto ast = bstrides(ap), bst = bstrides(bp);
+  const size_t n = numel(os);
+  std::vector<size_t> ia(n), ib(n);
+  for (size_t i = 0; i < n; ++i) {
+    size_t rem = i, fa = 0, fb = 0;
+    for (size_t d = nd; d-- > 0;) {
+      size_t c = rem % os[d];
+      rem /= os[d];
+      fa += c * ast[d];
+      fb += c * bst[d];
+    }
+    ia[i] = fa;
+    ib[i] = fb;
+  }
+  std::vector<float> out(n);
+  for (size_t i = 0; i < n; ++i) out[i] = g.tensors[a].data[ia[i]] + g.tensors[b].data[ib[i]];
+  size_t o = g_alloc(g, os, std::move(out));
+  push(g, {a, b}, o, [=](OGraph& gg) {
+    const std::vector<float> og = gg.tensors[o].grad;
+    for (size_t i = 0; i < n; ++i) {
+      gg.tensors[a].grad[ia[i]] += og[i];
+      gg.tensors[b].grad[ib[i]] += og[i];
+    }
+  });
+  return o;
+}
+
+// src/graph/ops/elementwise.rs:294-331 (no broadcast)
+size_t op_mul(OGraph& g, size_t a, size_t b) {
+  const std::vector<float> ad = g.tensors[a].data, bd = g.tensors[b].data;
+  const size_t n = ad.size();
+  std::vector<float> out(n);
+  for (size_t i = 0; i < n; ++i) out[i] = ad[i] * bd[i];
+  size_t o = g_alloc(g, g.tensors[a].shape, std::move(out));
+  push(g, {a, b}, o, [=](OGraph& gg) {
+    const std::vector<float> og = gg.tensors[o].grad;
+    for (size_t i = 0; i < n; ++i) {
+      gg.tensors[a].grad[i] += og[i] * bd[i];
+      gg.tensors[b].grad[i] += og[i] * ad[i];
+    }
+  });
+  return o;
+}
+
+// src/graph/ops/elementwise.rs:439-465
+size_t op_silu(OGraph& g, size_t a) {
+  const std::vector<float> ad = g.tensors[a].data;
+  const size_t n = ad.size();
+  std::vector<float> out(n);
+  for (size_t i = 0; i < n; ++i) {
+    float x = ad[i];
+    out[i] = x * (1.0f / (1.0f + std::exp(-x)));
+  }
+  size_t o = g_alloc(g, g.tensors[a].shape, std::move(out));
+  push(g, {a}, o, [=](OGraph& gg) {
+    const std::vector<float> og = gg.tensors[o].grad;
+    for (size_t i = 0; i < n; ++i) {
+      float x = ad[i];
+      float sig = 1.0f / (1.0f + std::exp(-x));
+      float silu = x * sig;
+      gg.tensors[a].grad[i] += og[i] * (silu + sig * (1.0f - silu));
+    }
+  });
+  return o;
+}
+
+// ---------------------------------------------------------------- matmul family
+// src/graph/ops/linear.rs:250-297 (C[m,n] = A[m,k] B[k,n]; lhs may have rank > 2, out is [m,n])
+size_t op_matmul(OGraph& g, size_t a, size_t b) {
+  const auto& as = g.tensors[a].shape;
+  const size_t k = as.back();
+  const size_t m = numel(as) / k;
+  const size_t n = g.tensors[b].shape[1];
+  const std::vector<float> af = g.tensors[a].data, bf = g.tensors[b].data;
+  std::vector<float> out(m * n);
+  PFOR(r, m) {
+    for (size_t c = 0; c < n; ++c) {
+      float sum = 0.0f;
+      for (size_t i = 0; i < k; ++i) sum += af[r * k + i] * bf[i * n + c];
+      out[r * n + c] = sum;
+    }
+  });
+  size_t o = g_alloc(g, {m, n}, std::move(out));
+  push(g, {a, b}, o, [=](OGraph& gg) {
+    const std::vector<float> og = gg.tensors[o].grad;
+    float* ag = gg.tensors[a].grad.data();
+    PFOR(r, m) {
+      for (size_t i = 0; i < k; ++i) {
+        float sum = 0.0f;
+        for (size_t c = 0; c < n; ++c) sum += og[r * n + c] * bf[i * n + c];
+        ag[r * k + i] += sum;
+      }
+    });
+    float* bg = gg.tensors[b].grad.data();
+    PFOR(i, k) {
+      for (size_t c = 0; c < n; ++c) {
+        float sum = 0.0f;
+        for (size_t r = 0; r < m; ++r) sum += af[r * k + i] * og[r * n + c];
+        bg[i * n + c] += sum;
+      }
+    });
+  });
+  return o;
+}
+
+// The CPU arm is `unimplemented!` (src/graph/ops/linear.rs:519-521); restated from the GPU
+// kernels matmul_trans_b_f32 / matmul_backward_a (dA += dC B) / matmul_trans_a_f32
+// (kernels/ops_f32.cu:842-882): C[m,n] = A[m,k] B[n,k]^T.
+size_t op_matmul_trans_b(OGraph& g, size_t a, size_t b) {
+  const auto& as = g.tensors[a].shape;
+  const size_t k = as.back();
+  const size_t m = numel(as) / k;
+  const size_t n = g.tensors[b].shape[0];
+  const std::vector<float> af = g.tensors[a].data, bf = g.tensors[b].data;
+  std::vector<float> out(m * n);
+  PFOR(r, m) {
+    for (size_t c = 0; c < n; ++c) {
+      float sum = 0.0f;
+      for (size_t i = 0; i < k; ++i) sum += af[r * k + i] * bf[c * k + i];
+      out[r * n + c] = sum;
+    }
+  });
+  size_t o = g_alloc(g, {m, n}, std::move(out));
+  push(g, {a, b}, o, [=](OGraph& gg) {
+    const std::vector<float> og = gg.tensors[o].grad;
+    float* ag = gg.tensors[a].grad.data();
+    PFOR(r, m) {
+      for (size_t i = 0; i < k; ++i) {
+        float sum = 0.0f;
+        for (size_t c = 0; c < n; ++c) sum += og[r * n + c] * bf[c * k + i];
+        ag[r * k + i] += sum;
+      }
+    });
+    float* bg = gg.tensors[b].grad.data();
+    PFOR(c, n) {
+      for (size_t i = 0; i < k; ++i) {
+        float sum = 0.0f;
+        for (size_t r = 0; r < m; ++r) sum += og[r * n + c] * af[r * k + i];
+        bg[c * k + i] += sum;
+      }
+    });
+  });
+  return o;
+}
+
+// src/graph/ops/linear.rs:1425-1510 (CPU arm accumulates into both grads)
+size_t op_bmm(OGraph& g, size_t a, size_t b, bool trans_b) {
+  const auto as = g.tensors[a].shape, bs = g.tensors[b].shape;
+  const size_t batch = as[0], m = as[1], k = as[2];
+  const size_t n = trans_b ? bs[1] : bs[2];
+  const std::vector<float> ad = g.tensors[a].data, bd = g.tensors[b].data;
+  std::vector<float> out(batch * m * n);
+  PFOR(bb, batch) {
+    for (size_t i = 0; i < m; ++i)
+      for (size_t j = 0; j < n; ++j) {
+        float acc = 0.0f;
+        for (size_t kk = 0; kk < k; ++kk) {
+          size_t ai = (bb * m + i) * k + kk;
+          size_t bi = trans_b ? (bb * n + j) * k + kk : (bb * k + kk) * n + j;
+          acc += ad[ai] * bd[bi];
+        }
+        out[(bb * m + i) * n + j] = acc;
+      }
+  });
+  size_t o = g_alloc(g, {batch, m, n}, std::move(out));
+  push(g, {a, b}, o, [=](OGraph& gg) {
+    const std::vector<float> og = gg.tensors[o].grad;
+    float* ag = gg.tensors[a].grad.data();
+    float* bg = gg.tensors[b].grad.data();
+    PFOR(bb, batch) {
+      for (size_t i = 0; i < m; ++i)
+        for (size_t j = 0; j < n; ++j) {
+          float go = og[(bb * m + i) * n + j];
+          for (size_t kk = 0; kk < k; ++kk) {
+            size_t ai = (bb * m + i) * k + kk;
+            size_t bi = trans_b ? (bb * n + j) * k + kk : (bb * k + kk) * n + j;
+            ag[ai] += go * bd[bi];
+            bg[bi] += go * ad[ai];
+          }
+        }
+    });
+  });
+  return o;
+}
+
+// ---------------------------------------------------------------- row ops
+// src/graph/ops/reduction.rs:476-524
+size_t op_softmax(OGraph& g, size_t a) {
+  const std::vector<float> ad = g.tensors[a].data;
+  const size_t n = g.tensors[a].shape.back();
+  const size_t rows = ad.size() / n;
+  std::vector<float> out(ad.size());
+  PFOR(row, rows) {
+    const size_t off = row * n;
+    float mx = -std::numeric_limits<float>::infinity();
+    for (size_t j = 0; j < n; ++j) mx = std::max(mx, ad[off + j]);
+    float sum = 0.0f;
+    for (size_t j = 0; j < n; ++j) {
+      float e = std::exp(ad[off + j] - mx);
+      out[off + j] = e;
+      sum += e;
+    }
+    for (size_t j = 0; j < n; ++j) out[off + j] /= sum;
+  });
+  const std::vector<float> of = out;
+  size_t o = g_alloc(g, g.tensors[a].shape, std::move(out));
+  push(g, {a}, o, [=](OGraph& gg) {
+    const std::vector<float> og = gg.tensors[o].grad;
+    float* ag = gg.tensors[a].grad.data();
+    PFOR(row, rows) {
+      const size_t off = row * n;
+      float dot = 0.0f;
+      for (size_t j = 0; j < n; ++j) dot += og[off + j] * of[off + j];
+      for (size_t j = 0; j < n; ++j) ag[off + j] += of[off + j] * (og[off + j] - dot);
+    });
+  });
+  return o;
+}
+
+constexpr int64_t ORC_IGNORE = -1;  // stands for IGNORE_INDEX = usize::MAX (src/data/fim.rs:173)
+
+// src/graph/ops/reduction.rs:668-717 (plain) and 888-942 (masked: rows with IGNORE_INDEX are
+// skipped, normaliser 1/valid_count).  The 1e-8 inside the log is not differentiated.
+size_t ce_impl(OGraph& g, size_t logits, const std::vector<int64_t>& targets, bool masked, float normalizer) {
+  const size_t B = g.tensors[logits].shape[0], C = g.tensors[logits].shape[1];
+  const std::vector<float>& ld = g.tensors[logits].data;
+  std::vector<float> probs(B * C, 0.0f);
+  float loss = 0.0f;
+  for (size_t b = 0; b < B; ++b) {
+    if (masked && targets[b] == ORC_IGNORE) continue;
+    float mx = -std::numeric_limits<float>::infinity();
+    for (size_t c = 0; c < C; ++c) mx = std::max(mx, ld[b * C + c]);
+    float sum = 0.0f;
+    for (size_t c = 0; c < C; ++c) {
+      float e = std::exp(ld[b * C + c] - mx);
+      probs[b * C + c] = e;
+      sum += e;
+    }
+    for (size_t c = 0; c < C; ++c) probs[b * C + c] /= sum;
+    float p = probs[b * C + (size_t)targets[b]];
+    if (masked) loss += -std::log(p + 1e-8f) * normalizer;
+    else loss += -std::log(p + 1e-8f);
+  }
+  if (!masked) loss = loss / (float)B;
+  size_t o = g_alloc(g, {}, {loss});
+  push(g, {logits}, o, [=](OGraph& gg) {
+    const float ograd = gg.tensors[o].grad[0];
+    float* lg = gg.tensors[logits].grad.data();
+    for (size_t b = 0; b < B; ++b) {
+      if (masked && targets[b] == ORC_IGNORE) continue;
+      for (size_t c = 0; c < C; ++c) {
+        float gr = probs[b * C + c];
+        if ((int64_t)c == targets[b]) gr -= 1.0f;
+        if (masked) lg[b * C + c] += gr * normalizer * ograd;
+        else lg[b * C + c] += (gr / (float)B) * ograd;
+      }
+    }
+  });
+  return o;
+}
+
+size_t op_cross_entropy(OGraph& g, size_t logits, const std::vector<int64_t>& t) {
+  return ce_impl(g, logits, t, false, 0.0f);
+}
+
+// src/graph/ops/reduction.rs:724-737 (dispatch of the masked variant)
+size_t op_cross_entropy_masked(OGraph& g, size_t logits, const std::vector<int64_t>& t) {
+  size_t valid = 0;
+  for (int64_t x : t) valid += (x != ORC_IGNORE);
+  if (valid == t.size()) return op_cross_entropy(g, logits, t);
+  if (valid == 0) return g_alloc(g, {}, {0.0f});
+  return ce_impl(g, logits, t, true, 1.0f / (float)valid);
+}
+
+// src/graph/ops/normalization.rs:132-181
+size_t op_rms_norm(OGraph& g, size_t x, size_t w, float eps) {
+  const std::vector<float> xf = g.tensors[x].data, wf = g.tensors[w].data;
+  const size_t dim = g.tensors[x].shape.back();
+  const size_t nv = xf.size() / dim;
+  std::vector<float> out(xf.size()), rr(nv);
+  for (size_t n = 0; n < nv; ++n) {
+    const size_t off = n * dim;
+    float ss = 0.0f;
+    for (size_t d = 0; d < dim; ++d) ss += xf[off + d] * xf[off + d];
+    float rrms = 1.0f / std::sqrt(ss / (float)dim + eps);
+    rr[n] = rrms;
+    for (size_t d = 0; d < dim; ++d) out[off + d] = xf[off + d] * rrms * wf[d];
+  }
+  size_t o = g_alloc(g, g.tensors[x].shape, std::move(out));
+  push(g, {x, w}, o, [=](OGraph& gg) {
+    const std::vector<float> og = gg.tensors[o].grad;
+    for (size_t n = 0; n < nv; ++n) {
+      const size_t off = n * dim;
+      const float rrms = rr[n];
+      float gdxw = 0.0f;
+      for (size_t d = 0; d < dim; ++d) gdxw += og[off + d] * xf[off + d] * wf[d];
+      const float rrc_d = (rrms * rrms * rrms) / (float)dim;
+      for (size_t d = 0; d < dim; ++d) {
+        float dx = rrms * (og[off + d] * wf[d]) - xf[off + d] * rrc_d * gdxw;
+        gg.tensors[x].grad[off + d] += dx;
+        gg.tensors[w].grad[d] += og[off + d] * xf[off + d] * rrms;
+      }
+    }
+  });
+  return o;
+}
+
+// src/graph/ops/transform.rs:541-610: interleaved pairs inside each head of [B,S,hidden]
+size_t op_rope(OGraph& g, size_t a, size_t head_dim) {
+  const auto shape = g.tensors[a].shape;
+  const size_t batch = shape[0], S = shape[1], H = shape[2];
+  const std::vector<float> ad = g.tensors[a].data;
+  std::vector<float> out = ad;
+  auto each = [=](const std::function<void(size_t, size_t, float, float)>& f) {
+    for (size_t bb = 0; bb < batch; ++bb)
+      for (size_t pos = 0; pos < S; ++pos)
+        for (size_t base = 0; base < H; base += head_dim)
+          for (size_t pair = 0; pair < head_dim / 2; ++pair) {
+            size_t even = base + 2 * pair, odd = even + 1;
+            if (odd >= base + head_dim || odd >= H) continue;
+            size_t i0 = (bb * S + pos) * H + even, i1 = (bb * S + pos) * H + odd;
+            float theta = (float)pos / std::pow(10000.0f, (2.0f * (float)pair) / (float)head_dim);
+            f(i0, i1, std::sin(theta), std::cos(theta));
+          }
+  };
+  each([&](size_t i0, size_t i1, float s, float c) {
+    float x0 = ad[i0], x1 = ad[i1];
+    out[i0] = x0 * c - x1 * s;
+    out[i1] = x0 * s + x1 * c;
+  });
+  size_t o = g_alloc(g, shape, std::move(out));
+  push(g, {a}, o, [=](OGraph& gg) {
+    const std::vector<float> og = gg.tensors[o].grad;
+    float* ag = gg.tensors[a].grad.data();
+    each([&](size_t i0, size_t i1, float s, float c) {
+      float g0 = og[i0], g1 = og[i1];
+      ag[i0] += g0 * c + g1 * s;
+      ag[i1] += -g0 * s + g1 * c;
+    });
+  });
+  return o;
+}
+
+// src/graph/ops/transform.rs:287-324 (indices are stored as f32 and cast to usize)
+size_t op_gather(OGraph& g, size_t w, size_t idx) {
+  const size_t hd = g.tensors[w].shape[1];
+  const size_t n = g.tensors[idx].data.size();
+  std::vector<size_t> id(n);
+  for (size_t i = 0; i < n; ++i) id[i] = (size_t)g.tensors[idx].data[i];
+  std::vector<float> out(n * hd);
+  for (size_t i = 0; i < n; ++i)
+    for (size_t d = 0; d < hd; ++d) out[i * hd + d] = g.tensors[w].data[id[i] * hd + d];
+  auto os = g.tensors[idx].shape;
+  os.push_back(hd);
+  size_t o = g_alloc(g, os, std::move(out));
+  push(g, {w, idx}, o, [=](OGraph& gg) {
+    const std::vector<float> og = gg.tensors[o].grad;
+    float* wg = gg.tensors[w].grad.data();
+    for (size_t i = 0; i < n; ++i)
+      for (size_t d = 0; d < hd; ++d) wg[id[i] * hd + d] += og[i * hd + d];
+  });
+  return o;
+}
+
+// src/graph/ops/transform.rs:389-407 (physical copy; bwd accumulates)
+size_t op_reshape(OGraph& g, size_t a, std::vector<size_t> shape) {
+  const size_t n = g.tensors[a].data.size();
+  size_t o = g_alloc(g, std::move(shape), g.tensors[a].data);
+  push(g, {a}, o, [=](OGraph& gg) {
+    for (size_t i = 0; i < n; ++i) gg.tensors[a].grad[i] += gg.tensors[o].grad[i];
+  });
+  return o;
+}
+
+// src/graph/ops/transform.rs:83-127: [B,S,H,D] -> [B,H,S,D]
+size_t op_transpose_0213(OGraph& g, size_t a) {
+  const auto s = g.tensors[a].shape;
+  const size_t B = s[0], S = s[1], H = s[2], D = s[3];
+  std::vector<float> out(g.tensors[a].data.size());
+  auto src = [=](size_t b, size_t h, size_t ss, size_t d) { return ((b * S + ss) * H + h) * D + d; };
+  auto dst = [=](size_t b, size_t h, size_t ss, size_t d) { return ((b * H + h) * S + ss) * D + d; };
+  for (size_t b = 0; b < B; ++b)
+    for (size_t ss = 0; ss < S; ++ss)
+      for (size_t h = 0; h < H; ++h)
+        for (size_t d = 0; d < D; ++d) out[dst(b, h, ss, d)] = g.tensors[a].data[src(b, h, ss, d)];
+  size_t o = g_alloc(g, {B, H, S, D}, std::move(out));
+  push(g, {a}, o, [=](OGraph& gg) {
+    for (size_t b = 0; b < B; ++b)
+      for (size_t ss = 0; ss < S; ++ss)
+        for (size_t h = 0; h < H; ++h)
+          for (size_t d = 0; d < D; ++d)
+            gg.tensors[a].grad[src(b, h, ss, d)] += gg.tensors[o].grad[dst(b, h, ss, d)];
+  });
+  return o;
+}
+
+// src/graph/ops/gqa.rs:13-23 (identity for repeats == 1) and 146-194
+size_t op_repeat_kv(OGraph& g, size_t x, size_t repeats) {
+  if (repeats == 1) return x;
+  const auto s = g.tensors[x].shape;
+  const size_t B = s[0], KV = s[1], S = s[2], D = s[3], Q = KV * repeats;
+  std::vector<float> out(B * Q * S * D);
+  for (size_t b = 0; b < B; ++b)
+    for (size_t qh = 0; qh < Q; ++qh) {
+      size_t kvh = qh / repeats;
+      for (size_t ss = 0; ss < S; ++ss)
+        for (size_t d = 0; d < D; ++d)
+          out[((b * Q + qh) * S + ss) * D + d] = g.tensors[x].data[((b * KV + kvh) * S + ss) * D + d];
+    }
+  size_t o = g_alloc(g, {B, Q, S, D}, std::move(out));
+  push(g, {x}, o, [=](OGraph& gg) {
+    for (size_t b = 0; b < B; ++b)
+      for (size_t kvh = 0; kvh < KV; ++kvh)
+        for (size_t r = 0; r < repeats; ++r) {
+          size_t qh = kvh * repeats + r;
+          for (size_t ss = 0; ss < S; ++ss)
+            for (size_t d = 0; d < D; ++d)
+              gg.tensors[x].grad[((b * KV + kvh) * S + ss) * D + d] +=
+                  gg.tensors[o].grad[((b * Q + qh) * S + ss) * D + d];
+        }
+  });
+  return o;
+}
+
+// src/graph/ops/attention.rs:145-192 (forward only; the reference asserts no_grad)
+size_t op_flash_attention(OGraph& g, size_t q, size_t k, size_t v, float scale, bool causal) {
+  const auto qs = g.tensors[q].shape, ks = g.tensors[k].shape;
+  const size_t batch = qs[0], m = qs[1], d = qs[2], n = ks[1];
+  const auto& qd = g.tensors[q].data;
+  const auto& kd = g.tensors[k].data;
+  const auto& vd = g.tensors[v].data;
+  std::vector<float> out(batch * m * d), scores(n), probs(n);
+  for (size_t bb = 0; bb < batch; ++bb)
+    for (size_t i = 0; i < m; ++i) {
+      for (size_t j = 0; j < n; ++j) {
+        if (causal && j > i) { scores[j] = -std::numeric_limits<float>::infinity(); continue; }
+        float dot = 0.0f;
+        for (size_t dd = 0; dd < d; ++dd) dot += qd[(bb * m + i) * d + dd] * kd[(bb * n + j) * d + dd];
+        scores[j] = dot * scale;
+      }
+      float mx = -std::numeric_limits<float>::infinity();
+      for (size_t j = 0; j < n; ++j) mx = std::max(mx, scores[j]);
+      float den = 0.0f;
+      for (size_t j = 0; j < n; ++j) { probs[j] = std::exp(scores[j] - mx); den += probs[j]; }
+      for (size_t j = 0; j < n; ++j) probs[j] /= den;
+      for (size_t dd = 0; dd < d; ++dd) {
+        float acc = 0.0f;
+        for (size_t j = 0; j < n; ++j) acc += probs[j] * vd[(bb * n + j) * d + dd];
+        out[(bb * m + i) * d + dd] = acc;
+      }
+    }
+  return g_alloc(g, {batch, m, d}, std::move(out));
+}
+
+// ---------------------------------------------------------------- tape walk
+// src/graph/mod.rs:670-796, CPU parts: seed every element of the loss grad with 1, walk the
+// tape in reverse, keep the nodes.
+void g_backward(OGraph& g, size_t loss) {
+  if (g.no_grad) return;
+  for (float& x : g.tensors[loss].grad) x = 1.0f;
+  for (size_t i = g.tape.size(); i-- > 0;) g.tape[i].bwd(g);
+}
+
+// src/graph/mod.rs:336-365 / 432-435
+void g_restore(OGraph& g, size_t sp) {
+  while (g.tensors.size() > sp) g.tensors.pop_back();
+}
+void g_clear_activations(OGraph& g) {
+  g.tape.clear();
+  g_restore(g, g.num_params);
+}
+
+// ---------------------------------------------------------------- modules
+// src/nn/linear.rs:10-49: LCG + Box-Muller, std 0.02, the seed restarts at 42 for every layer
+std::vector<float> linear_init(size_t n) {
+  std::vector<float> w(n);
+  uint32_t seed = 42;
+  const float umax = (float)UINT32_MAX;
+  for (size_t i = 0; i < n; ++i) {
+    float u1 = std::min((float)seed / umax + 1e-7f, 1.0f - 1e-7f);
+    seed = seed * 1664525u + 1013904223u;
+    float u2 = std::min(std::max((float)seed / umax, 1e-7f), 1.0f - 1e-7f);
+    seed = seed * 1664525u + 1013904223u;
+    float mag = std::sqrt(-2.0f * std::log(u1));
+    float z0 = mag * std::cos(2.0f * 3.14159265358979323846f * u2);
+    w[i] = z0 * 0.02f;
+  }
+  return w;
+}
+// src/nn/embedding.rs:9-32: uniform in +-0.02 from an LCG seeded with 84
+std::vector<float> embedding_init(size_t n) {
+  std::vector<float> w(n);
+  uint32_t seed = 84;
+  const float umax = (float)UINT32_MAX;
+  for (size_t i = 0; i < n; ++i) {
+    seed = seed * 1664525u + 1013904223u;
+    float r = ((float)seed / umax) * 2.0f - 1.0f;
+    w[i] = r * 0.02f;
+  }
+  return w;
+}
+
+struct OBlock {
+  size_t norm1, q, k, v, o, norm2, gate, up, down;
+};
+// src/nn/transformer.rs:69-122 (creation order fixes the tensor ids) and 198-210 (params order)
+struct OLM {
+  size_t vocab, hidden, heads, kv_heads, ffn, layers;
+  bool tie;
+  size_t emb, norm_f, head;
+  std::vector<OBlock> blocks;
+};
+
+size_t linear_new(OGraph& g, size_t in, size_t out) { return g_alloc(g, {in, out}, linear_init(in * out)); }
+size_t norm_new(OGraph& g, size_t d) { return g_alloc(g, {d}, std::vector<float>(d, 1.0f)); }
+
+// src/nn/linear.rs:53-95 (no bias on this path): matmul, then the 3-D shape is restored by
+// reinterpretation
+size_t linear_fwd(OGraph& g, size_t x, size_t w) {
+  const auto xs = g.tensors[x].shape;
+  size_t o = op_matmul(g, x, w);
+  if (xs.size() == 3) g.tensors[o].shape = {xs[0], xs[1], g.tensors[w].shape[1]};
+  return o;
+}
+
+// src/nn/attention.rs:289-388
+size_t gqa_fwd(OGraph& g, const OLM& lm, const OBlock& b, size_t x, bool causal) {
+  const auto xs = g.tensors[x].shape;
+  const size_t B = xs[0], S = xs[1];
+  const size_t hd = lm.hidden / lm.heads;
+  size_t q = linear_fwd(g, x, b.q), k = linear_fwd(g, x, b.k), v = linear_fwd(g, x, b.v);
+  size_t qr = op_rope(g, q, hd), kr = op_rope(g, k, hd);
+  size_t q4 = op_reshape(g, qr, {B, S, lm.heads, hd});
+  size_t k4 = op_reshape(g, kr, {B, S, lm.kv_heads, hd});
+  size_t v4 = op_reshape(g, v, {B, S, lm.kv_heads, hd});
+  size_t qt = op_transpose_0213(g, q4), kt = op_transpose_0213(g, k4), vt = op_transpose_0213(g, v4);
+  const size_t rep = lm.heads / lm.kv_heads;
+  size_t krep = op_repeat_kv(g, kt, rep), vrep = op_repeat_kv(g, vt, rep);
+  const size_t bh = B * lm.heads;
+  g.tensors[qt].shape = {bh, S, hd};
+  g.tensors[krep].shape = {bh, S, hd};
+  g.tensors[vrep].shape = {bh, S, hd};
+  const float scale = 1.0f / std::sqrt((float)hd);
+  size_t ctx;
+  if (g.no_grad) {
+    ctx = op_flash_attention(g, qt, krep, vrep, scale, causal);
+  } else {
+    size_t scores = op_bmm(g, qt, krep, true);
+    size_t sc = g_alloc(g, {bh, S, S}, std::vector<float>(bh * S * S, scale));
+    size_t scaled = op_mul(g, scores, sc);
+    size_t masked = scaled;
+    if (causal) {
+      std::vector<float> md(S * S, 0.0f);
+      for (size_t r = 0; r < S; ++r)
+        for (size_t c = 0; c < S; ++c)
+          if (c > r) md[r * S + c] = -1e20f;
+      size_t mask = g_alloc(g, {1, S, S}, std::move(md));
+      masked = op_add(g, scaled, mask);
+    }
+    size_t probs = op_softmax(g, masked);
+    ctx = op_bmm(g, probs, vrep, false);
+  }
+  g.tensors[ctx].shape = {B, lm.heads, S, hd};
+  size_t ct = op_transpose_0213(g, ctx);
+  size_t c2 = op_reshape(g, ct, {B, S, lm.hidden});
+  return linear_fwd(g, c2, b.o);
+}
+
+// src/nn/transformer.rs:32-49
+size_t block_fwd(OGraph& g, const OLM& lm, const OBlock& b, size_t x) {
+  size_t n1 = op_rms_norm(g, x, b.norm1, 1e-5f);
+  size_t at = gqa_fwd(g, lm, b, n1, true);
+  size_t r1 = op_add(g, x, at);
+  size_t n2 = op_rms_norm(g, r1, b.norm2, 1e-5f);
+  size_t go = linear_fwd(g, n2, b.gate);
+  size_t gt = op_silu(g, go);
+  size_t up = linear_fwd(g, n2, b.up);
+  size_t gd = op_mul(g, gt, up);
+  size_t f2 = linear_fwd(g, gd, b.down);
+  return op_add(g, r1, f2);
+}
+
+// src/nn/transformer.rs:184-196
+size_t lm_fwd(OGraph& g, const OLM& lm, size_t x) {
+  size_t h = op_gather(g, lm.emb, x);
+  for (const OBlock& b : lm.blocks) h = block_fwd(g, lm, b, h);
+  h = op_rms_norm(g, h, lm.norm_f, 1e-5f);
+  if (lm.tie) return op_matmul_trans_b(g, h, lm.emb);
+  return linear_fwd(g, h, lm.head);
+}
+
+// src/nn/optim.rs:32-46 (defaults), 250-289 (clip), 334-338 + 523-543 (CPU step)
+struct OAdamW {
+  std::vector<size_t> params;
+  float lr, beta1 = 0.9f, beta2 = 0.999f, eps = 1e-8f, wd = 0.01f;
+  size_t t = 0;
+  std::vector<std::vector<float>> m, v;
+};
+
+}  // namespace
+
+// =====================================================================================
+// C interface (ctypes)
+// =====================================================================================
+extern "C" {
+
+void orc_set_threads(int n) { g_threads = n < 1 ? 1 : n; }
+int orc_max_threads() {
+  unsigned n = std::thread::hardware_concurrency();
+  return n ? (int)n : 1;
+}
+
+void* orc_graph_new() { return new OGraph(); }
+void orc_graph_free(void* g) { delete static_cast<OGraph*>(g); }
+#define G (*static_cast<OGraph*>(g))
+
+long long orc_alloc(void* g, const long long* shape, int ndim, const float* data) {
+  std::vector<size_t> s(shape, shape + ndim);
+  size_t n = numel(s);
+  return (long long)g_alloc(G, s, std::vector<float>(data, data + n));
+}
+long long orc_numel(void* g, long long id) { return (long long)G.tensors[id].data.size(); }
+int orc_shape(void* g, long long id, long long* out) {
+  const auto& s = G.tensors[id].shape;
+  for (size_t i = 0; i < s.size(); ++i) out[i] = (long long)s[i];
+  return (int)s.size();
+}
+void orc_get_data(void* g, long long id, float* out) {
+  std::memcpy(out, G.tensors[id].data.data(), G.tensors[id].data.size() * 4);
+}
+void orc_get_grad(void* g, long long id, float* out) {
+  std::memcpy(out, G.tensors[id].grad.data(), G.tensors[id].grad.size() * 4);
+}
+void orc_set_data(void* g, long long id, const float* in) {
+  std::memcpy(G.tensors[id].data.data(), in, G.tensors[id].data.size() * 4);
+}
+void orc_set_no_grad(void* g, int f) { G.no_grad = f != 0; }
+long long orc_num_tensors(void* g) { return (long long)G.tensors.size(); }
+long long orc_tape_len(void* g) { return (long long)G.tape.size(); }
+void orc_tape_clear(void* g) { G.tape.clear(); }
+void orc_mark_params(void* g) { G.num_params = G.tensors.size(); }
+long long orc_mark_save_point(void* g) { return (long long)G.tensors.size(); }
+void orc_restore_save_point(void* g, long long sp) { g_restore(G, (size_t)sp); }
+void orc_clear_activations(void* g) { g_clear_activations(G); }
+void orc_reinterpret_shape(void* g, long long id, const long long* shape, int ndim) {
+  G.tensors[id].shape.assign(shape, shape + ndim);
+}
+void orc_zero_grad_tensor(void* g, long long id) {
+  std::fill(G.tensors[id].grad.begin(), G.tensors[id].grad.end(), 0.0f);
+}
+
+long long orc_add(void* g, long long a, long long b) { return (long long)op_add(G, a, b); }
+long long orc_mul(void* g, long long a, long long b) { return (long long)op_mul(G, a, b); }
+long long orc_silu(void* g, long long a) { return (long long)op_silu(G, a); }
+long long orc_matmul(void* g, long long a, long long b) { return (long long)op_matmul(G, a, b); }
+long long orc_matmul_trans_b(void* g, long long a, long long b) { return (long long)op_matmul_trans_b(G, a, b); }
+long long orc_bmm(void* g, long long a, long long b, int tb) { return (long long)op_bmm(G, a, b, tb != 0); }
+long long orc_softmax(void* g, long long a) { return (long long)op_softmax(G, a); }
+long long orc_cross_entropy(void* g, long long l, const long long* t, long long n) {
+  return (long long)op_cross_entropy(G, l, std::vector<int64_t>(t, t + n));
+}
+long long orc_cross_entropy_masked(void* g, long long l, const long long* t, long long n) {
+  return (long long)op_cross_entropy_masked(G, l, std::vector<int64_t>(t, t + n));
+}
+long long orc_rms_norm(void* g, long long x, long long w, float eps) { return (long long)op_rms_norm(G, x, w, eps); }
+long long orc_rope(void* g, long long a, long long hd) { return (long long)op_rope(G, a, (size_t)hd); }
+long long orc_gather(void* g, long long w, long long idx) { return (long long)op_gather(G, w, idx); }
+long long orc_reshape(void* g, long long a, const long long* shape, int ndim) {
+  return (long long)op_reshape(G, a, std::vector<size_t>(shape, shape + ndim));
+}
+long long orc_transpose_0213(void* g, long long a) { return (long long)op_transpose_0213(G, a); }
+long long orc_repeat_kv(void* g, long long a, long long r) { return (long long)op_repeat_kv(G, a, (size_t)r); }
+long long orc_flash_attention(void* g, long long q, long long k, long long v, float scale, int causal) {
+  return (long long)op_flash_attention(G, q, k, v, scale, causal != 0);
+}
+void orc_backward(void* g, long long loss) { g_backward(G, (size_t)loss); }
+
+// ---- TransformerLM
+void* orc_lm_new(void* g, long long vocab, long long hidden, long long heads, long long kv_heads,
+                 long long ffn, long long layers, int tie) {
+  OLM* lm = new OLM();
+  lm->vocab = vocab; lm->hidden = hidden; lm->heads = heads; lm->kv_heads = kv_heads;
+  lm->ffn = ffn; lm->layers = layers; lm->tie = tie != 0;
+  const size_t hd = hidden / heads, kvd = kv_heads * hd;
+  lm->emb = g_alloc(G, {(size_t)vocab, (size_t)hidden}, embedding_init(vocab * hidden));
+  for (long long l = 0; l < layers; ++l) {
+    OBlock b;
+    b.norm1 = norm_new(G, hidden);
+    b.q = linear_new(G, hidden, hidden);
+    b.k = linear_new(G, hidden, kvd);
+    b.v = linear_new(G, hidden, kvd);
+    b.o = linear_new(G, hidden, hidden);
+    b.norm2 = norm_new(G, hidden);
+    b.gate = linear_new(G, hidden, ffn);
+    b.up = linear_new(G, hidden, ffn);
+    b.down = linear_new(G, ffn, hidden);
+    lm->blocks.push_back(b);
+  }
+  lm->norm_f = norm_new(G, hidden);
+  lm->head = lm->tie ? lm->emb : linear_new(G, hidden, vocab);
+  return lm;
+}
+void orc_lm_free(void* lm) { delete static_cast<OLM*>(lm); }
+long long orc_lm_forward(void* lm, void* g, long long x) { return (long long)lm_fwd(G, *static_cast<OLM*>(lm), (size_t)x); }
+// params() order of src/nn/transformer.rs:198-210 and 57-66
+int orc_lm_params(void* lmv, long long* out) {
+  OLM& lm = *static_cast<OLM*>(lmv);
+  int n = 0;
+  out[n++] = lm.emb;
+  for (const OBlock& b : lm.blocks) {
+    out[n++] = b.norm1; out[n++] = b.q; out[n++] = b.k; out[n++] = b.v; out[n++] = b.o;
+    out[n++] = b.norm2; out[n++] = b.up; out[n++] = b.down; out[n++] = b.gate;
+  }
+  out[n++] = lm.norm_f;
+  if (!lm.tie) out[n++] = lm.head;
+  return n;
+}
+
+// ---- AdamW
+void* orc_adamw_new(const long long* params, int n, float lr) {
+  OAdamW* o = new OAdamW();
+  o->params.assign(params, params + n);
+  o->lr = lr;
+  o->m.resize(n);
+  o->v.resize(n);
+  return o;
+}
+void orc_adamw_free(void* o) { delete static_cast<OAdamW*>(o); }
+void orc_adamw_config(void* ov, float lr, float b1, float b2, float eps, float wd) {
+  OAdamW& o = *static_cast<OAdamW*>(ov);
+  o.lr = lr; o.beta1 = b1; o.beta2 = b2; o.eps = eps; o.wd = wd;
+}
+void orc_adamw_zero_grad(void* ov, void* g) {
+  for (size_t p : static_cast<OAdamW*>(ov)->params)
+    std::fill(G.tensors[p].grad.begin(), G.tensors[p].grad.end(), 0.0f);
+}
+// src/nn/optim.rs:250-289: f64 sum of squares, coef = min(1, max/(norm+1e-6)); returns the norm
+float orc_adamw_clip_grad_norm(void* ov, void* g, float max_norm, float* coef_out) {
+  OAdamW& o = *static_cast<OAdamW*>(ov);
+  double ss = 0.0;
+  for (size_t p : o.params)
+    for (float x : G.tensors[p].grad) ss += (double)x * (double)x;
+  float norm = (float)std::sqrt(ss);
+  float coef = norm > 0.0f ? std::min(max_norm / (norm + 1e-6f), 1.0f) : 1.0f;
+  if (coef < 1.0f)
+    for (size_t p : o.params)
+      for (float& x : G.tensors[p].grad) x *= coef;
+  if (coef_out) *coef_out = coef;
+  return norm;
+}
+// src/nn/optim.rs:334-338 and 523-543
+void orc_adamw_step(void* ov, void* g) {
+  OAdamW& o = *static_cast<OAdamW*>(ov);
+  o.t += 1;
+  const float bc1 = 1.0f / (1.0f - __builtin_powif(o.beta1, (int)o.t));  // powi
+  const float bc2 = 1.0f / (1.0f - __builtin_powif(o.beta2, (int)o.t));
+  for (size_t pi = 0; pi < o.params.size(); ++pi) {
+    OTensor& t = G.tensors[o.params[pi]];
+    const size_t n = t.data.size();
+    if (o.m[pi].empty()) { o.m[pi].assign(n, 0.0f); o.v[pi].assign(n, 0.0f); }
+    float* m = o.m[pi].data();
+    float* v = o.v[pi].data();
+    for (size_t i = 0; i < n; ++i) {
+      const float grad = t.grad[i], w = t.data[i];
+      const float decayed = w * (1.0f - o.lr * o.wd);
+      m[i] = o.beta1 * m[i] + (1.0f - o.beta1) * grad;
+      v[i] = o.beta2 * v[i] + (1.0f - o.beta2) * grad * grad;
+      const float mh = m[i] * bc1, vh = v[i] * bc2;
+      t.data[i] = decayed - o.lr * mh / (std::sqrt(vh) + o.eps);
+    }
+  }
+}
+
+}  // extern "C"
