@@ -1,0 +1,730 @@
+// Flash attention forward and backward with grouped-query heads on tcgen05 tensor cores.
+//
+// Tensors are [B, S, H, D] views with element strides (D contiguous), D in {64, 128}, bf16.
+// Query head h uses KV head h / (Hq / Hkv); nothing is replicated or transposed in memory.
+// All tiles are 128 x 128 (queries x keys); operands reach shared memory by TMA with 128-byte
+// swizzle and are consumed by tcgen05.mma either K-major or MN-major, so one resident tile serves
+// both A*B^T and A^T*B style products; accumulators live in TMEM.
+//
+// Forward (per CTA: one 128-query tile of one head), warps 0-3 softmax (thread = query row),
+// warp 4 TMA, warp 5 MMA:
+//   S = Q K^T  ->  TMEM (two buffers)         p = exp2((s - m) * scale*log2e), online max / sum
+//   P (bf16)   ->  shared memory (two buffers)
+//   PV         ->  TMEM (two buffers), folded into an f32 register accumulator with the rescale
+// Backward (per CTA: one 128-key tile of one KV head, looping over the query heads of its group
+// and over query tiles), warps 0-7 compute, warp 8 TMA, warp 9 MMA:
+//   S = Q K^T, dP = dO V^T            -> TMEM
+//   P = exp2(S*c - lse), dS = P*(dP - delta)*scale   -> shared memory (bf16)
+//   dV += P^T dO, dK += dS^T Q        -> TMEM, kept across the whole loop (this is the GQA reduce)
+//   dQ  = dS K                        -> TMEM -> f32 red.global.add into a workspace
+// It replaces the reference's materialised chain bmm -> mul(scale) -> add(mask) -> softmax -> bmm
+// and its gradient kernels (src/nn/attention.rs:339-375; kernels/ops_f32.cu:342-511, 625-646,
+// 787-840); the reference has no fused backward (src/graph/ops/attention.rs:15-18).
+#include "ptx.cuh"
+#include "common.cuh"
+#include "errors.h"
+#include "gemm_tc.h"
+#include "../../include/eisen_b200.h"
+
+namespace eisen {
+namespace {
+
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct AttnParams {
+  int B, S, Hq, Hkv, D;
+  int causal;
+  float scale;
+  // outputs / side inputs (element strides)
+  void* o; long long o_bs, o_ss, o_hs;
+  float* lse;        // [B, Hq, S]
+  const float* delta;  // [B, Hq, S]
+  float* dq_acc;     // [B, S, Hq, D] f32
+  void* dk; void* dv; long long kv_bs, kv_ss, kv_hs;
+  int* status;
+};
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// writes 32 consecutive bf16 of row `row` starting at column `col0` (multiple of 32) into a
+// [128 x 128] bf16 tile stored as two 128B-swizzled [128 x 64] halves, 16 KB apart
+__device__ __forceinline__ void store_row_chunk32(uint32_t tile_base, int row, int col0, const uint32_t (&pk)[16]) {
+  const uint32_t half = tile_base + (col0 >> 6) * 16384u;
+  const int chunk0 = (col0 & 63) >> 3;  // first 16-byte chunk inside the 128-byte row
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    st_shared_v4(half + swz128(row, chunk0 + j), pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+}
+
+// =====================================================================================
+// forward
+// =====================================================================================
+template <int D>
+struct FwdCfg {
+  static constexpr int TILE = 128 * D * 2;  // bytes of a [128 x D] bf16 tile
+  static constexpr int P_TILE = 128 * 128 * 2;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = TILE;
+  static constexpr int OFF_V = OFF_K + 2 * TILE;
+  static constexpr int OFF_P = OFF_V + 2 * TILE;
+  static constexpr int OFF_BAR = OFF_P + 2 * P_TILE;
+  static constexpr int SMEM = OFF_BAR + 256 + 1024;
+  static constexpr int TMEM_COLS = 512;
+};
+
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+  using Cfg = FwdCfg<D>;
+  constexpr int ATOMS = D / 64;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+  uint64_t* q_full = bars;          // 1
+  uint64_t* k_full = bars + 1;      // 2
+  uint64_t* k_empty = bars + 3;     // 2
+  uint64_t* v_full = bars + 5;      // 2
+  uint64_t* v_empty = bars + 7;     // 2
+  uint64_t* s_full = bars + 9;      // 2
+  uint64_t* s_empty = bars + 11;    // 2 (128 arrivals)
+  uint64_t* p_ready = bars + 13;    // 2 (128 arrivals)
+  uint64_t* o_full = bars + 15;     // 2
+  uint64_t* o_empty = bars + 17;    // 2 (128 arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qt = gridDim.x;
+  const int qt = n_qt - 1 - blockIdx.x;  // heavy (late) causal tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / (p.Hq / p.Hkv);
+  const int n_kv_all = (p.S + 127) / 128;
+  const int n_kv = p.causal ? min(qt + 1, n_kv_all) : n_kv_all;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 128);
+      mbar_init(&p_ready[i], 128);
+      mbar_init(&o_full[i], 1); mbar_init(&o_empty[i], 128);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+  }
+  if (warp == 5) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tm_S = tmem_base;            // 2 x 128 columns
+  const uint32_t tm_O = tmem_base + 256;      // 2 x D columns
+
+  if (warp == 4) {
+    // ---------------- TMA ----------------
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, Cfg::TILE);
+#pragma unroll
+      for (int a = 0; a < ATOMS; ++a)
+        tma_load_4d(smem + Cfg::OFF_Q + a * 16384, &tmQ, q_full, a * 64, h, qt * 128, b);
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
+        mbar_arrive_expect_tx(&k_full[st], Cfg::TILE);
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a)
+          tma_load_4d(smem + Cfg::OFF_K + st * Cfg::TILE + a * 16384, &tmK, &k_full[st], a * 64, kvh, j * 128, b);
+        mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
+        mbar_arrive_expect_tx(&v_full[st], Cfg::TILE);
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a)
+          tma_load_4d(smem + Cfg::OFF_V + st * Cfg::TILE + a * 16384, &tmV, &v_full[st], a * 64, kvh, j * 128, b);
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------- MMA ----------------
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_pv = make_idesc_bf16(128, D, 0, 1);
+      const uint32_t sQ = smem_u32(smem + Cfg::OFF_Q);
+      mbar_wait(q_full, 0, abort_flag, p.status, FAULT_WAIT_ATTN);
+      for (int j = 0; j <= n_kv; ++j) {
+        if (j < n_kv) {
+          const int st = j & 1;
+          const uint32_t ph = (j >> 1) & 1;
+          mbar_wait(&k_full[st], ph, abort_flag, p.status, FAULT_WAIT_ATTN);
+          mbar_wait(&s_empty[st], ph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
+          tc_fence_after_sync();
+          const uint32_t sK = smem_u32(smem + Cfg::OFF_K + st * Cfg::TILE);
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t off = (k >> 2) * 16384u + (k & 3) * 32u;
+            umma_bf16_ss(tm_S + st * 128, make_smem_desc(sQ + off, 16, 1024), make_smem_desc(sK + off, 16, 1024),
+                         idesc_s, k > 0);
+          }
+          umma_commit(&s_full[st]);
+          umma_commit(&k_empty[st]);
+        }
+        if (j > 0) {
+          const int jj = j - 1;
+          const int st = jj & 1;
+          const uint32_t ph = (jj >> 1) & 1;
+          mbar_wait(&p_ready[st], ph, abort_flag, p.status, FAULT_WAIT_ATTN);
+          mbar_wait(&v_full[st], ph, abort_flag, p.status, FAULT_WAIT_ATTN);
+          mbar_wait(&o_empty[st], ph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
+          tc_fence_after_sync();
+          const uint32_t sP = smem_u32(smem + Cfg::OFF_P + st * Cfg::P_TILE);
+          const uint32_t sV = smem_u32(smem + Cfg::OFF_V + st * Cfg::TILE);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {  // 128 keys in steps of 16
+            const uint64_t da = make_smem_desc(sP + (k >> 2) * 16384u + (k & 3) * 32u, 16, 1024);
+            const uint64_t db = make_smem_desc(sV + k * 2048u, 16384, 1024);  // V is MN-major: [key][d]
+            umma_bf16_ss(tm_O + st * D, da, db, idesc_pv, k > 0);
+          }
+          umma_commit(&o_full[st]);
+          umma_commit(&v_empty[st]);
+        }
+      }
+    }
+  } else {
+    // ---------------- softmax + output (warps 0-3, thread = query row) ----------------
+    const int row = warp * 32 + lane;
+    const int qrow = qt * 128 + row;
+    const uint32_t lane_off = uint32_t(warp * 32) << 16;
+    const float sl2 = p.scale * LOG2E;
+    float m = -INFINITY, l = 0.0f, alpha_pending = 1.0f;
+    float acc[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) acc[i] = 0.0f;
+
+    auto fold_tile = [&](int jj, float alpha) {
+      const int st = jj & 1;
+      const uint32_t ph = (jj >> 1) & 1;
+      mbar_wait(&o_full[st], ph, abort_flag, p.status, FAULT_WAIT_ATTN);
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tm_O + st * D + c * 32 + lane_off, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[c * 32 + i] = acc[c * 32 + i] * alpha + __uint_as_float(r[i]);
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&o_empty[st]);
+    };
+
+    for (int j = 0; j < n_kv; ++j) {
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      const bool need_mask = (p.causal && j == qt) || ((j + 1) * 128 > p.S);
+      mbar_wait(&s_full[st], ph, abort_flag, p.status, FAULT_WAIT_ATTN);
+      tc_fence_after_sync();
+      const uint32_t tS = tm_S + st * 128 + lane_off;
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tS + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(r[i]);
+          if (need_mask) {
+            const int kc = j * 128 + c * 32 + i;
+            if (kc >= p.S || (p.causal && kc > qrow)) s = -INFINITY;
+          }
+          mx = fmaxf(mx, s);
+        }
+      }
+      const float m_new = fmaxf(m, mx);
+      const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;  // a fully masked row keeps p = 0
+      const float alpha = exp2f((m - m_use) * sl2);
+      // pass 2: probabilities -> shared memory (bf16), row sum
+      float rs = 0.0f;
+      const uint32_t sP = smem_u32(smem + Cfg::OFF_P + st * Cfg::P_TILE);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tS + c * 32, r);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float s0 = __uint_as_float(r[i]), s1 = __uint_as_float(r[i + 1]);
+          float p0 = exp2f((s0 - m_use) * sl2), p1 = exp2f((s1 - m_use) * sl2);
+          if (need_mask) {
+            const int kc = j * 128 + c * 32 + i;
+            if (kc >= p.S || (p.causal && kc > qrow)) p0 = 0.0f;
+            if (kc + 1 >= p.S || (p.causal && kc + 1 > qrow)) p1 = 0.0f;
+          }
+          // the row sum uses the bf16-rounded values that the MMA will see
+          __nv_bfloat162 hb = __floats2bfloat162_rn(p0, p1);
+          float2 fb = __bfloat1622float2(hb);
+          rs += fb.x + fb.y;
+          pk[i >> 1] = *reinterpret_cast<uint32_t*>(&hb);
+        }
+        store_row_chunk32(sP, row, c * 32, pk);
+      }
+      l = l * alpha + rs;
+      m = m_new;
+      tc_fence_before_sync();
+      mbar_arrive(&s_empty[st]);
+      fence_proxy_async_smem();
+      mbar_arrive(&p_ready[st]);
+      // fold the previous tile's PV while the tensor core works on this one
+      if (j > 0) fold_tile(j - 1, alpha_pending);
+      alpha_pending = alpha;
+    }
+    if (n_kv > 0) fold_tile(n_kv - 1, alpha_pending);
+
+    if (qrow < p.S) {
+      const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + (long long)b * p.o_bs + (long long)qrow * p.o_ss +
+                            (long long)h * p.o_hs;
+#pragma unroll
+      for (int c = 0; c < D / 8; ++c) {
+        uint4 o;
+        o.x = pack_bf16x2(acc[c * 8 + 0] * inv, acc[c * 8 + 1] * inv);
+        o.y = pack_bf16x2(acc[c * 8 + 2] * inv, acc[c * 8 + 3] * inv);
+        o.z = pack_bf16x2(acc[c * 8 + 4] * inv, acc[c * 8 + 5] * inv);
+        o.w = pack_bf16x2(acc[c * 8 + 6] * inv, acc[c * 8 + 7] * inv);
+        reinterpret_cast<uint4*>(orow)[c] = o;
+      }
+      if (p.lse) p.lse[((long long)b * p.Hq + h) * p.S + qrow] = (l > 0.0f) ? m * p.scale + logf(l) : -INFINITY;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// =====================================================================================
+// backward
+// =====================================================================================
+template <int D>
+struct BwdCfg {
+  static constexpr int TILE = 128 * D * 2;
+  static constexpr int P_TILE = 128 * 128 * 2;
+  static constexpr int NS = (D == 64) ? 2 : 1;  // Q / dO stages
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = TILE;
+  static constexpr int OFF_Q = 2 * TILE;               // NS stages
+  static constexpr int OFF_DO = OFF_Q + NS * TILE;     // NS stages
+  static constexpr int OFF_P = OFF_DO + NS * TILE;
+  static constexpr int OFF_DS = OFF_P + P_TILE;
+  static constexpr int OFF_BAR = OFF_DS + P_TILE;
+  static constexpr int SMEM = OFF_BAR + 256 + 1024;
+  static constexpr int TMEM_COLS = 512;
+  // TMEM columns: S / dQ at 0 (dQ reuses S once P and dS are in shared memory), dP at 128,
+  // dV at 256, dK at 256 + D
+  static constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + D, COL_DQ = 0;
+};
+
+template <int D>
+__global__ void __launch_bounds__(320, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                const AttnParams p) {
+  using Cfg = BwdCfg<D>;
+  constexpr int ATOMS = D / 64;
+  constexpr int NS = Cfg::NS;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+  uint64_t* kv_full = bars;        // 1
+  uint64_t* qdo_full = bars + 1;   // NS (<= 2)
+  uint64_t* qdo_empty = bars + 3;  // NS
+  uint64_t* sdp_full = bars + 5;   // 1
+  uint64_t* pds_ready = bars + 6;  // 1 (256 arrivals)
+  uint64_t* dq_full = bars + 7;    // 1
+  uint64_t* dq_read = bars + 8;    // 1 (256 arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int jt = blockIdx.x;  // key tile; tile 0 has the most work under the causal mask
+  const int kvh = blockIdx.y, b = blockIdx.z;
+  const int rep = p.Hq / p.Hkv;
+  const int n_qt = (p.S + 127) / 128;
+  const int i0 = p.causal ? jt : 0;
+  const int per_head = n_qt - i0;
+  const int iters = per_head * rep;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < NS; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_ready, 256);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_read, 256);
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO);
+  }
+  if (warp == 9) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 8) {
+    // ---------------- TMA ----------------
+    if (lane == 0) {
+      mbar_arrive_expect_tx(kv_full, 2 * Cfg::TILE);
+#pragma unroll
+      for (int a = 0; a < ATOMS; ++a) {
+        tma_load_4d(smem + Cfg::OFF_K + a * 16384, &tmK, kv_full, a * 64, kvh, jt * 128, b);
+        tma_load_4d(smem + Cfg::OFF_V + a * 16384, &tmV, kv_full, a * 64, kvh, jt * 128, b);
+      }
+      for (int it = 0; it < iters; ++it) {
+        const int st = it % NS;
+        const uint32_t ph = (it / NS) & 1;
+        const int h = kvh * rep + it / per_head;
+        const int qi = i0 + it % per_head;
+        mbar_wait(&qdo_empty[st], ph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
+        mbar_arrive_expect_tx(&qdo_full[st], 2 * Cfg::TILE);
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a) {
+          tma_load_4d(smem + Cfg::OFF_Q + st * Cfg::TILE + a * 16384, &tmQ, &qdo_full[st], a * 64, h, qi * 128, b);
+          tma_load_4d(smem + Cfg::OFF_DO + st * Cfg::TILE + a * 16384, &tmdO, &qdo_full[st], a * 64, h, qi * 128, b);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ---------------- MMA ----------------
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);   // Q K^T, dO V^T
+      const uint32_t idesc_t = make_idesc_bf16(128, D, 1, 1);     // P^T dO, dS^T Q
+      const uint32_t idesc_q = make_idesc_bf16(128, D, 0, 1);     // dS K
+      const uint32_t sK = smem_u32(smem + Cfg::OFF_K), sV = smem_u32(smem + Cfg::OFF_V);
+      const uint32_t sP = smem_u32(smem + Cfg::OFF_P), sDS = smem_u32(smem + Cfg::OFF_DS);
+      mbar_wait(kv_full, 0, abort_flag, p.status, FAULT_WAIT_ATTN);
+      for (int it = 0; it < iters; ++it) {
+        const int st = it % NS;
+        const uint32_t ph = (it / NS) & 1;
+        const uint32_t iph = it & 1;
+        const uint32_t sQ = smem_u32(smem + Cfg::OFF_Q + st * Cfg::TILE);
+        const uint32_t sDO = smem_u32(smem + Cfg::OFF_DO + st * Cfg::TILE);
+        mbar_wait(&qdo_full[st], ph, abort_flag, p.status, FAULT_WAIT_ATTN);
+        if (it > 0) mbar_wait(dq_read, iph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);  // dQ of it-1 drained
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384u + (k & 3) * 32u;
+          umma_bf16_ss(tmem_base + Cfg::COL_S, make_smem_desc(sQ + off, 16, 1024), make_smem_desc(sK + off, 16, 1024),
+                       idesc_s, k > 0);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384u + (k & 3) * 32u;
+          umma_bf16_ss(tmem_base + Cfg::COL_DP, make_smem_desc(sDO + off, 16, 1024),
+                       make_smem_desc(sV + off, 16, 1024), idesc_s, k > 0);
+        }
+        umma_commit(sdp_full);
+        mbar_wait(pds_ready, iph, abort_flag, p.status, FAULT_WAIT_ATTN);
+        tc_fence_after_sync();
+        // K dimension of the next three products = the 128 query rows (dV, dK) or 128 keys (dQ)
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // dV += P^T dO
+          umma_bf16_ss(tmem_base + Cfg::COL_DV, make_smem_desc(sP + k * 2048u, 16384, 1024),
+                       make_smem_desc(sDO + k * 2048u, 16384, 1024), idesc_t, (it > 0 || k > 0));
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // dK += dS^T Q
+          umma_bf16_ss(tmem_base + Cfg::COL_DK, make_smem_desc(sDS + k * 2048u, 16384, 1024),
+                       make_smem_desc(sQ + k * 2048u, 16384, 1024), idesc_t, (it > 0 || k > 0));
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // dQ = dS K
+          umma_bf16_ss(tmem_base + Cfg::COL_DQ, make_smem_desc(sDS + (k >> 2) * 16384u + (k & 3) * 32u, 16, 1024),
+                       make_smem_desc(sK + k * 2048u, 16384, 1024), idesc_q, k > 0);
+        umma_commit(dq_full);
+        umma_commit(&qdo_empty[st]);
+      }
+    }
+  } else {
+    // ---------------- compute warps 0-7 ----------------
+    const int q4 = warp & 3;        // TMEM lane quarter
+    const int ch = warp >> 2;       // column half
+    const int row = q4 * 32 + lane;
+    const uint32_t lane_off = uint32_t(q4 * 32) << 16;
+    const float sl2 = p.scale * LOG2E;
+    const uint32_t sP = smem_u32(smem + Cfg::OFF_P), sDS = smem_u32(smem + Cfg::OFF_DS);
+    for (int it = 0; it < iters; ++it) {
+      const uint32_t iph = it & 1;
+      const int h = kvh * rep + it / per_head;
+      const int qi = i0 + it % per_head;
+      const int qrow = qi * 128 + row;
+      const bool row_ok = qrow < p.S;
+      const long long stat_idx = ((long long)b * p.Hq + h) * p.S + qrow;
+      const float lse2 = row_ok ? p.lse[stat_idx] * LOG2E : INFINITY;  // +inf -> p = 0
+      const float dlt = row_ok ? p.delta[stat_idx] : 0.0f;
+      const bool need_mask = (p.causal && qi == jt) || ((jt + 1) * 128 > p.S);
+      mbar_wait(sdp_full, iph, abort_flag, p.status, FAULT_WAIT_ATTN);
+      tc_fence_after_sync();
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        const int col0 = ch * 64 + c * 32;
+        uint32_t rs[32], rd[32];
+        tmem_ld_32x32b_x32(tmem_base + Cfg::COL_S + col0 + lane_off, rs);
+        tmem_ld_32x32b_x32(tmem_base + Cfg::COL_DP + col0 + lane_off, rd);
+        tmem_ld_wait();
+        uint32_t pk[16], dk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = exp2f(__uint_as_float(rs[i]) * sl2 - lse2);
+          float p1 = exp2f(__uint_as_float(rs[i + 1]) * sl2 - lse2);
+          if (need_mask) {
+            const int kc = jt * 128 + col0 + i;
+            if (kc >= p.S || (p.causal && kc > qrow)) p0 = 0.0f;
+            if (kc + 1 >= p.S || (p.causal && kc + 1 > qrow)) p1 = 0.0f;
+          }
+          const float d0 = p0 * (__uint_as_float(rd[i]) - dlt) * p.scale;
+          const float d1 = p1 * (__uint_as_float(rd[i + 1]) - dlt) * p.scale;
+          pk[i >> 1] = pack_bf16x2(p0, p1);
+          dk[i >> 1] = pack_bf16x2(d0, d1);
+        }
+        store_row_chunk32(sP, row, col0, pk);
+        store_row_chunk32(sDS, row, col0, dk);
+      }
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+      mbar_arrive(pds_ready);
+      // dQ tile -> f32 accumulation buffer
+      mbar_wait(dq_full, iph, abort_flag, p.status, FAULT_WAIT_ATTN);
+      tc_fence_after_sync();
+      float* dq_row = p.dq_acc + (((long long)b * p.S + qrow) * p.Hq + h) * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 64; ++c) {
+        const int col0 = ch * (D / 2) + c * 32;
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_base + Cfg::COL_DQ + col0 + lane_off, r);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + col0 + i),
+                         "f"(__uint_as_float(r[i])), "f"(__uint_as_float(r[i + 1])),
+                         "f"(__uint_as_float(r[i + 2])), "f"(__uint_as_float(r[i + 3]))
+                         : "memory");
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(dq_read);
+    }
+    // dK / dV of this key tile: TMEM -> bf16 -> global (the last dq_full wait covers them)
+    if (iters > 0) {
+      tc_fence_after_sync();
+      const int krow = jt * 128 + row;
+      const long long base = (long long)b * p.kv_bs + (long long)krow * p.kv_ss + (long long)kvh * p.kv_hs;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(which ? p.dk : p.dv) + base;
+        const int colbase = which ? Cfg::COL_DK : Cfg::COL_DV;
+#pragma unroll 1
+        for (int c = 0; c < D / 64; ++c) {
+          const int col0 = ch * (D / 2) + c * 32;
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_base + colbase + col0 + lane_off, r);
+          tmem_ld_wait();
+          if (krow < p.S) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+              o.y = pack_bf16x2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+              o.z = pack_bf16x2(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+              o.w = pack_bf16x2(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
+              *reinterpret_cast<uint4*>(dst + col0 + i) = o;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  if (warp == 9) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// delta[b,h,s] = sum_d o[b,s,h,d] * do[b,s,h,d]; one warp per (b,s,h)
+__global__ void __launch_bounds__(256)
+attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
+                  int B, int S, int H, int D, long long bs, long long ss, long long hs) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const long long total = (long long)B * S * H;
+  for (long long w = warp0; w < total; w += (long long)gridDim.x * 8) {
+    const int h = (int)(w % H);
+    const int s = (int)((w / H) % S);
+    const int b = (int)(w / ((long long)H * S));
+    const long long off = (long long)b * bs + (long long)s * ss + (long long)h * hs;
+    float acc = 0.0f;
+    for (int c = lane * 8; c < D; c += 256) {
+      float x[8], y[8];
+      ld16(o + off + c, x);
+      ld16(d_o + off + c, y);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc += x[k] * y[k];
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) delta[((long long)b * H + h) * S + s] = acc;
+  }
+}
+
+// dq (bf16, strided [B,S,H,D]) = dq_acc (f32, contiguous [B,S,H,D])
+__global__ void __launch_bounds__(256)
+attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long rows /*B*S*H*/,
+                       int S, int H, int D, long long bs, long long ss, long long hs) {
+  const int per_row = D / 8;
+  const long long total = rows * per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / per_row;
+    const int c = (int)(i % per_row) * 8;
+    const int h = (int)(r % H);
+    const int s = (int)((r / H) % S);
+    const long long b = r / ((long long)H * S);
+    float lo[4], hi[4];
+    ld16(acc + r * D + c, lo);
+    ld16(acc + r * D + c + 4, hi);
+    float v[8] = {lo[0], lo[1], lo[2], lo[3], hi[0], hi[1], hi[2], hi[3]};
+    st16(dq + b * bs + (long long)s * ss + (long long)h * hs + c, v);
+  }
+}
+
+int make_qkv_tmap(CUtensorMap* tm, const void* base, int B, int S, int H, int D, long long bs, long long ss,
+                  long long hs) {
+  const uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)S, (uint64_t)B};
+  const uint64_t strides[3] = {(uint64_t)hs, (uint64_t)ss, (uint64_t)bs};
+  const uint32_t box[4] = {64, 1, 128, 1};
+  return make_tmap_bf16_nd(tm, base, 4, dims, strides, box);
+}
+
+int check_args(long long B, long long S, long long Hq, long long Hkv, long long D, const long long* strides, int n) {
+  if (D != 64 && D != 128) return fail(EISEN_ERR_INVALID, "attention: head_dim must be 64 or 128");
+  if (B <= 0 || S <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return fail(EISEN_ERR_INVALID, "attention: bad B/S/H (Hq % Hkv must be 0)");
+  if (B > 65535 || Hq > 65535) return fail(EISEN_ERR_LIMIT, "attention: B and Hq must be <= 65535");
+  for (int i = 0; i < n; ++i)
+    if (strides[i] % 8) return fail(EISEN_ERR_INVALID, "attention: strides must be multiples of 8 elements");
+  return 0;
+}
+
+}  // namespace
+}  // namespace eisen
+
+using namespace eisen;
+
+extern "C" {
+
+int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, void* o, float* lse, long long B,
+                   long long S, long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss,
+                   long long q_hs, long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs,
+                   long long o_ss, long long o_hs, float scale, int causal, int* status) {
+  const long long st[9] = {q_bs, q_ss, q_hs, kv_bs, kv_ss, kv_hs, o_bs, o_ss, o_hs};
+  int rc = check_args(B, S, Hq, Hkv, D, st, 9);
+  if (rc) return rc;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return fail(EISEN_ERR_INVALID, "attn_fwd: unaligned pointer");
+  CUtensorMap tq, tk, tv;
+  if (make_qkv_tmap(&tq, q, (int)B, (int)S, (int)Hq, (int)D, q_bs, q_ss, q_hs) ||
+      make_qkv_tmap(&tk, k, (int)B, (int)S, (int)Hkv, (int)D, kv_bs, kv_ss, kv_hs) ||
+      make_qkv_tmap(&tv, v, (int)B, (int)S, (int)Hkv, (int)D, kv_bs, kv_ss, kv_hs))
+    return fail(EISEN_ERR_CUDA, "attn_fwd: cuTensorMapEncodeTiled failed");
+  AttnParams p{};
+  p.B = (int)B; p.S = (int)S; p.Hq = (int)Hq; p.Hkv = (int)Hkv; p.D = (int)D;
+  p.causal = causal; p.scale = scale;
+  p.o = o; p.o_bs = o_bs; p.o_ss = o_ss; p.o_hs = o_hs;
+  p.lse = lse; p.status = status;
+  dim3 grid((unsigned)((S + 127) / 128), (unsigned)Hq, (unsigned)B);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (D == 64) {
+    static bool set64 = false;
+    if (!set64) { if (cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<64>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute"); set64 = true; }
+    attn_fwd_kernel<64><<<grid, 192, FwdCfg<64>::SMEM, s>>>(tq, tk, tv, p);
+  } else {
+    static bool set128 = false;
+    if (!set128) { if (cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<128>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute"); set128 = true; }
+    attn_fwd_kernel<128><<<grid, 192, FwdCfg<128>::SMEM, s>>>(tq, tk, tv, p);
+  }
+  return check_launch("attn_fwd");
+}
+
+// workspace layout: dq_acc f32 [B,S,Hq,D] | delta f32 [B,Hq,S]
+long long eisen_attn_bwd_workspace_bytes(long long B, long long S, long long Hq, long long Hkv, long long D) {
+  (void)Hkv;
+  return B * S * Hq * D * 4 + B * Hq * S * 4 + 256;
+}
+
+int eisen_attn_bwd(void* stream, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                   const void* d_o, void* dq, void* dk, void* dv, void* workspace, long long B, long long S,
+                   long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss, long long q_hs,
+                   long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs, long long o_ss,
+                   long long o_hs, float scale, int causal, int* status) {
+  const long long st[9] = {q_bs, q_ss, q_hs, kv_bs, kv_ss, kv_hs, o_bs, o_ss, o_hs};
+  int rc = check_args(B, S, Hq, Hkv, D, st, 9);
+  if (rc) return rc;
+  if (!workspace) return fail(EISEN_ERR_INVALID, "attn_bwd: workspace is null");
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(d_o) || !aligned16(dq) ||
+      !aligned16(dk) || !aligned16(dv) || !aligned16(workspace))
+    return fail(EISEN_ERR_INVALID, "attn_bwd: unaligned pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  float* dq_acc = (float*)workspace;
+  float* delta = dq_acc + B * S * Hq * D;
+  if (cudaMemsetAsync(dq_acc, 0, (size_t)(B * S * Hq * D) * 4, s) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_bwd: memset failed");
+  attn_delta_kernel<<<grid_for(B * S * Hq, 8, 8), 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta,
+                                                                (int)B, (int)S, (int)Hq, (int)D, o_bs, o_ss, o_hs);
+  rc = check_launch("attn_delta");
+  if (rc) return rc;
+  CUtensorMap tq, tk, tv, tdo;
+  // dO uses the strides of O
+  if (make_qkv_tmap(&tq, q, (int)B, (int)S, (int)Hq, (int)D, q_bs, q_ss, q_hs) ||
+      make_qkv_tmap(&tk, k, (int)B, (int)S, (int)Hkv, (int)D, kv_bs, kv_ss, kv_hs) ||
+      make_qkv_tmap(&tv, v, (int)B, (int)S, (int)Hkv, (int)D, kv_bs, kv_ss, kv_hs) ||
+      make_qkv_tmap(&tdo, d_o, (int)B, (int)S, (int)Hq, (int)D, o_bs, o_ss, o_hs))
+    return fail(EISEN_ERR_CUDA, "attn_bwd: cuTensorMapEncodeTiled failed");
+  AttnParams p{};
+  p.B = (int)B; p.S = (int)S; p.Hq = (int)Hq; p.Hkv = (int)Hkv; p.D = (int)D;
+  p.causal = causal; p.scale = scale;
+  p.lse = const_cast<float*>(lse); p.delta = delta; p.dq_acc = dq_acc;
+  p.dk = dk; p.dv = dv; p.kv_bs = kv_bs; p.kv_ss = kv_ss; p.kv_hs = kv_hs;
+  p.status = status;
+  dim3 grid((unsigned)((S + 127) / 128), (unsigned)Hkv, (unsigned)B);
+  if (D == 64) {
+    static bool set64 = false;
+    if (!set64) { if (cudaFuncSetAttribute(attn_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<64>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_bwd: smem attribute"); set64 = true; }
+    attn_bwd_kernel<64><<<grid, 320, BwdCfg<64>::SMEM, s>>>(tq, tk, tv, tdo, p);
+  } else {
+    static bool set128 = false;
+    if (!set128) { if (cudaFuncSetAttribute(attn_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<128>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_bwd: smem attribute"); set128 = true; }
+    attn_bwd_kernel<128><<<grid, 320, BwdCfg<128>::SMEM, s>>>(tq, tk, tv, tdo, p);
+  }
+  rc = check_launch("attn_bwd");
+  if (rc) return rc;
+  attn_dq_convert_kernel<<<grid_for(B * S * Hq * D / 8, 256, 8), 256, 0, s>>>(dq_acc, (__nv_bfloat16*)dq, B * S * Hq, (int)S,
+                                                                              (int)Hq, (int)D, q_bs, q_ss, q_hs);
+  return check_launch("attn_dq_convert");
+}
+
+}  // extern "C"

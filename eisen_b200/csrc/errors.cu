@@ -1,0 +1,52 @@
+// Error bookkeeping of the C ABI and the C entry point of the tcgen05 GEMM.
+#include "errors.h"
+#include "gemm_tc.h"
+#include "../../include/eisen_b200.h"
+
+#include <cstdio>
+#include <cstring>
+
+namespace eisen {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* msg) {
+  std::snprintf(g_err, sizeof(g_err), "%s", msg ? msg : "");
+}
+int fail(int code, const char* msg) {
+  set_error(msg);
+  return code;
+}
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) return 0;
+  char buf[400];
+  std::snprintf(buf, sizeof(buf), "%s: %s", what, cudaGetErrorString(e));
+  set_error(buf);
+  return EISEN_ERR_CUDA;
+}
+
+}  // namespace eisen
+
+extern "C" {
+
+const char* eisen_last_error(void) { return eisen::g_err; }
+const char* eisen_version(void) { return "eisen_b200 0.1 (sm_100a)"; }
+
+int eisen_gemm_bf16(void* stream, int a_mn, int b_mn, long long M, long long N, long long K, const void* A,
+                    long long lda, const void* B, long long ldb, void* C, long long ldc, int out_mode,
+                    int split_k, float alpha, int* status) {
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL)
+    return eisen::fail(EISEN_ERR_LIMIT, "gemm_bf16: a dimension exceeds 2^31-1");
+  if (out_mode < 0 || out_mode > 4) return eisen::fail(EISEN_ERR_INVALID, "gemm_bf16: bad out_mode");
+  if (split_k == 0) {
+    split_k = (out_mode == eisen::GEMM_OUT_F32_ATOMIC) ? eisen::gemm_tc_auto_split_k((int)M, (int)N, (int)K) : 1;
+  }
+  const char* err = nullptr;
+  int rc = eisen::gemm_bf16_tc((cudaStream_t)stream, a_mn, b_mn, (int)M, (int)N, (int)K, A, lda, B, ldb, C, ldc,
+                               out_mode, split_k, alpha, status, &err);
+  if (rc) return eisen::fail(rc == 1 ? EISEN_ERR_INVALID : EISEN_ERR_CUDA, err ? err : "gemm_bf16 failed");
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,203 @@
+/*
+ * eisen_b200 — C ABI of the B200-native (sm_100a) training-step hot path of philsupertramp/eisen.
+ *
+ * Two layers are exported from libeisen_b200.so:
+ *
+ *  (1) Kernel level (this first half): one entry point per device operation.  These replace the
+ *      `stream.launch_builder(&f).arg(..).launch(cfg)` calls in the `Device::Gpu` arms of the
+ *      reference's `impl Graph` ops (src/graph/ops/*.rs) and of `AdamW` (src/nn/optim.rs).
+ *      Plain pointers and sizes only; every call is asynchronous on the given CUDA stream
+ *      (`void* stream` is a `cudaStream_t`), performs no allocation and no synchronisation, and
+ *      keeps no pointer after it returns.  Scratch memory is passed in by the caller and sized by
+ *      the matching `*_workspace_bytes` query.
+ *
+ *  (2) Graph level (second half): the host-side mirror of the reference's `Graph` / tape / nn
+ *      modules / AdamW, driven through opaque handles, for callers that want the whole engine
+ *      behaviour (tensor ids, Wengert-list backward, pooled activations, save points).
+ *
+ * Conventions
+ *   - return value: 0 = success, otherwise an `EISEN_ERR_*` code; eisen_last_error() gives the
+ *     message of the last failure on the calling thread.  Nothing aborts.
+ *   - dtype arguments: EISEN_F32 or EISEN_BF16.  Gradient ("d*") outputs take an `accumulate`
+ *     flag: 0 writes, 1 adds to what is there (the reference's kernels always add,
+ *     kernels/ops_f32.cu, except bmm_backward_* which overwrite).
+ *   - all tensors are row-major and contiguous unless strides are passed.
+ */
+#ifndef EISEN_B200_H
+#define EISEN_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EISEN_F32 0
+#define EISEN_BF16 1
+
+#define EISEN_OK 0
+#define EISEN_ERR_INVALID 1
+#define EISEN_ERR_CUDA 2
+#define EISEN_ERR_KERNEL 3
+#define EISEN_ERR_OOM 4
+#define EISEN_ERR_LIMIT 5
+
+/* message of the last failed call on this thread ("" if none) */
+const char* eisen_last_error(void);
+/* version string of the library */
+const char* eisen_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Dense contractions
+ * ------------------------------------------------------------------------------------------ */
+
+/* bf16 x bf16 -> f32-accumulated GEMM on tcgen05 tensor cores (TMA-fed, TMEM accumulators).
+ *   C[M,N] (op)= alpha * sum_k A(m,k) * B(n,k)
+ * a_mn / b_mn = 0: operand stored [rows][K] (K contiguous); 1: stored [K][rows].
+ * out_mode: 0 bf16 store, 1 bf16 accumulate, 2 f32 store, 3 f32 accumulate, 4 f32 atomic
+ * accumulate (required for split_k > 1; split_k = 0 lets the library choose).
+ * status (device int, may be null) receives a non-zero code if a bounded wait inside the kernel
+ * ran out.  Leading dimensions of A and B must be multiples of 8 elements, bases 16-byte aligned.
+ * Replaces matmul_f32 / matmul_backward_a_f32 / matmul_backward_b_f32 (kernels/ops_f32.cu:158-259),
+ * matmul_trans_b_f32 / matmul_trans_a_f32 (842-882) and the bf16-operand variants
+ * (kernels/ops_bf16.cu:26-223) launched from src/graph/ops/linear.rs:136-213, 402-481, 615-730. */
+int eisen_gemm_bf16(void* stream, int a_mn, int b_mn, long long M, long long N, long long K, const void* A,
+                    long long lda, const void* B, long long ldb, void* C, long long ldc, int out_mode,
+                    int split_k, float alpha, int* status);
+
+/* f32 SIMT GEMM with element strides and a batch dimension (f32 parity path):
+ *   C[b,m,n] (+)= sum_k A[b*a_bs + m*a_ms + k*a_ks] * B[b*b_bs + k*b_ks + n*b_ns]
+ * Replaces the same reference kernels for f32 tensors plus bmm_f32 and bmm_backward_*
+ * (kernels/ops_f32.cu:342-511; src/graph/ops/linear.rs:1302-1386). */
+int eisen_gemm_f32_strided(void* stream, const float* A, const float* B, float* C, long long batch, long long M,
+                           long long N, long long K, long long a_bs, long long a_ms, long long a_ks,
+                           long long b_bs, long long b_ks, long long b_ns, long long c_bs, long long ldc,
+                           int accumulate);
+
+/* ------------------------------------------------------------------------------------------
+ * Flash attention with grouped-query heads (bf16, tcgen05).  Layout of all tensors: [B, S, H, D]
+ * with explicit element strides for batch, sequence and head (D contiguous), so the projections'
+ * [B,S,hidden] outputs are consumed in place: no reshape / transpose_0213 / repeat_kv copies
+ * (src/nn/attention.rs:305-331, 379-384).  Query head h reads KV head h / (Hq/Hkv).
+ * Forward replaces flash_attention_f32 (kernels/ops_f32.cu:648-692, inference only in the
+ * reference, src/graph/ops/attention.rs:15-18) and the training chain bmm -> mul -> add(mask)
+ * -> softmax -> bmm (src/nn/attention.rs:339-375); backward replaces that chain's gradient
+ * kernels (bmm_backward_*, softmax_backward_f32, mul/add backward, repeat_kv_backward).
+ * lse: [B, Hq, S] f32 log-sum-exp of the scaled, masked scores (natural log).
+ * ------------------------------------------------------------------------------------------ */
+int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, void* o, float* lse, long long B,
+                   long long S, long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss,
+                   long long q_hs, long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs,
+                   long long o_ss, long long o_hs, float scale, int causal, int* status);
+long long eisen_attn_bwd_workspace_bytes(long long B, long long S, long long Hq, long long Hkv, long long D);
+/* dq, dk, dv are written (not accumulated); they use the strides of q and k/v respectively. */
+int eisen_attn_bwd(void* stream, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                   const void* d_o, void* dq, void* dk, void* dv, void* workspace, long long B, long long S,
+                   long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss, long long q_hs,
+                   long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs, long long o_ss,
+                   long long o_hs, float scale, int causal, int* status);
+
+/* ------------------------------------------------------------------------------------------
+ * Row-wise ops
+ * ------------------------------------------------------------------------------------------ */
+
+/* RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w; w is f32 [dim]; rrms_out (f32 [rows]) may be null.
+ * Replaces rmsnorm_f32 / rmsnorm_bf16 (kernels/ops_f32.cu:539-551, ops_bf16.cu:660-681;
+ * src/graph/ops/normalization.rs:88). */
+int eisen_rmsnorm_fwd(void* stream, const void* x, const float* w, void* y, float* rrms_out, long long rows,
+                      long long dim, float eps, int dtype);
+long long eisen_rmsnorm_bwd_workspace_bytes(long long rows, long long dim);
+/* dx (op)= ..., dw (f32) += ...  Replaces rmsnorm_backward_f32 and its bf16 variants
+ * (kernels/ops_f32.cu:553-578; src/graph/ops/normalization.rs:122). */
+int eisen_rmsnorm_bwd(void* stream, const void* x, const float* w, const void* dy, void* dx, float* dw,
+                      void* workspace, long long rows, long long dim, float eps, int dtype, int accumulate_dx);
+
+/* softmax over the last dimension and its backward (kernels/ops_f32.cu:625-646). */
+int eisen_softmax_fwd(void* stream, const void* x, void* y, long long rows, long long n, int dtype);
+int eisen_softmax_bwd(void* stream, const void* y, const void* dy, void* dx, long long rows, long long n,
+                      int dtype, int accumulate);
+
+/* Fused softmax-cross-entropy.  Row loss = -ln(softmax(x)[t] + 1e-8) * normalizer; rows whose
+ * target equals ignore_index contribute nothing.  Outputs: *loss (device f32), row_loss [rows],
+ * lse [rows].  Replaces cross_entropy_f32 / cross_entropy_masked_f32 (kernels/ops_f32.cu:580-598,
+ * 5-30; src/graph/ops/reduction.rs:610, 823).  Targets are int32 (the reference passes f32). */
+int eisen_ce_fwd(void* stream, const void* logits, const int* targets, float* loss, float* row_loss, float* lse,
+                 long long rows, long long vocab, int ignore_index, float normalizer, int dtype);
+/* dlogits (op)= (softmax(x) - onehot) * normalizer * (*grad_out); dlogits may alias logits.
+ * Replaces cross_entropy_backward_f32 / cross_entropy_masked_backward_f32 (600-623, 32-64). */
+int eisen_ce_bwd(void* stream, const void* logits, const int* targets, const float* lse, void* dlogits,
+                 const float* grad_out, long long rows, long long vocab, int ignore_index, float normalizer,
+                 int dtype, int accumulate);
+
+/* ------------------------------------------------------------------------------------------
+ * Elementwise / layout ops
+ * ------------------------------------------------------------------------------------------ */
+int eisen_fill_f32(void* stream, float* p, float value, long long n);                  /* fill_f32, ops_f32.cu:101 */
+int eisen_scale_f32(void* stream, float* p, float s, long long n);                     /* scale_f32, ops_f32.cu:107 */
+int eisen_cast(void* stream, const void* src, int src_dtype, void* dst, int dst_dtype, long long n); /* cast_*, ops_bf16.cu:4-24 */
+/* out[i] = a[i] + b[i % b_numel]  (add_f32, ops_f32.cu:66-82) */
+int eisen_add(void* stream, const void* a, const void* b, void* out, long long n, long long b_numel, int dtype);
+/* dst[i] (op)= src[i], mixed dtypes allowed  (accumulate_f32, ops_f32.cu:84-99) */
+int eisen_accumulate(void* stream, void* dst, int dst_dtype, const void* src, int src_dtype, long long n,
+                     int accumulate);
+/* dst[j] (op)= sum_{i % m == j} src[i]  (broadcast-operand gradient of accumulate_f32) */
+int eisen_reduce_leading(void* stream, const void* src, int src_dtype, float* dst, long long n, long long m,
+                         int accumulate);
+int eisen_mul_fwd(void* stream, const void* a, const void* b, void* out, long long n, int dtype);  /* mul_f32, ops_f32.cu:113 */
+int eisen_mul_bwd(void* stream, const void* a, const void* b, const void* dout, void* da, void* db, long long n,
+                  int dtype, int accumulate_a, int accumulate_b);                      /* mul_backward_f32, ops_f32.cu:119 */
+int eisen_silu_fwd(void* stream, const void* x, void* y, long long n, int dtype);      /* silu_f32, ops_f32.cu:135 */
+int eisen_silu_bwd(void* stream, const void* x, const void* dy, void* dx, long long n, int dtype, int accumulate); /* :142 */
+/* fused SwiGLU: out = silu(gate) * up and its one-pass backward (replaces silu + mul and their
+ * backward kernels on the path src/nn/transformer.rs:41-44) */
+int eisen_swiglu_fwd(void* stream, const void* gate, const void* up, void* out, long long n, int dtype);
+int eisen_swiglu_bwd(void* stream, const void* gate, const void* up, const void* dh, void* dgate, void* dup,
+                     long long n, int dtype, int accumulate);
+/* RoPE on interleaved pairs (rope_f32 / rope_backward_f32, ops_f32.cu:724-760;
+ * src/graph/ops/transform.rs:517-531).  table_cos_sin: [seq_len, head_dim/2] pairs of f32. */
+int eisen_rope_table(void* stream, float* table_cos_sin, long long seq_len, long long head_dim, float base);
+int eisen_rope(void* stream, const void* x, void* y, const float* table_cos_sin, long long B, long long S,
+               long long hidden, long long head_dim, int dtype, int inverse, int accumulate);
+/* y[B,H,S,D] (op)= x[B,S,H,D]  (transpose_0213_f32 and its backward, ops_f32.cu:694-722) */
+int eisen_transpose_0213(void* stream, const void* x, void* y, long long B, long long S, long long H, long long D,
+                         int dtype, int accumulate);
+/* GQA head replication and its backward (repeat_kv_f32 / repeat_kv_backward_f32, ops_f32.cu:787-840) */
+int eisen_repeat_kv_fwd(void* stream, const void* x, void* y, long long B, long long KV, long long S, long long D,
+                        long long repeats, int dtype);
+int eisen_repeat_kv_bwd(void* stream, const void* dy, void* dx, long long B, long long KV, long long S,
+                        long long D, long long repeats, int dtype, int accumulate);
+
+/* ------------------------------------------------------------------------------------------
+ * Embedding
+ * ------------------------------------------------------------------------------------------ */
+/* out[i,:] = W[ids[i],:]  (gather_f32 / gather_bf16_*, ops_f32.cu:513-524, ops_bf16.cu:225, 716;
+ * src/graph/ops/transform.rs:203-227).  ids are int32.  bad_id_flag (device int, may be null) is
+ * set when an id is outside [0, vocab); such rows read row 0 (the reference does not check). */
+int eisen_embedding_fwd(void* stream, const void* w, int w_dtype, const int* ids, void* out, int out_dtype,
+                        long long n_ids, long long dim, long long vocab, int* bad_id_flag);
+long long eisen_embedding_bwd_workspace_bytes(long long n_ids, long long vocab);
+/* dW[ids[i],:] += g[i,:], deterministic, no floating-point atomics
+ * (gather_backward_f32, ops_f32.cu:526-537; src/graph/ops/transform.rs:259). */
+int eisen_embedding_bwd(void* stream, const void* g, int g_dtype, const int* ids, float* dw, void* workspace,
+                        long long n_ids, long long dim, long long vocab);
+/* integer bookkeeping of the last eisen_embedding_bwd on `workspace` (device int32 outputs, any
+ * may be null): count[vocab], offset[vocab] (exclusive prefix), perm[n_ids] (positions grouped
+ * by id in position order) */
+int eisen_embedding_bwd_bookkeeping(void* stream, const void* workspace, long long n_ids, long long vocab,
+                                    int* count_out, int* offset_out, int* perm_out);
+
+/* ------------------------------------------------------------------------------------------
+ * Optimizer
+ * ------------------------------------------------------------------------------------------ */
+/* Fused AdamW over a flat f32 buffer (adamw_step_f32, ops_f32.cu:762-784; src/nn/optim.rs:415-481,
+ * one launch per tensor there).  See optim.cu for the exact update. */
+int eisen_adamw_step(void* stream, float* w, void* w_bf16, const float* g, float* m, float* v, long long n,
+                     float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2,
+                     float grad_scale, const double* sumsq, float max_norm);
+long long eisen_sumsq_workspace_bytes(long long n);
+/* *out (device f64) (op)= sum x^2 — the device-side half of AdamW::clip_grad_norm
+ * (src/nn/optim.rs:250-281 copies every gradient to the host instead). */
+int eisen_sumsq(void* stream, const float* x, long long n, void* workspace, double* out, int accumulate);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EISEN_B200_H */

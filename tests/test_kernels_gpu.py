@@ -1,0 +1,497 @@
+"""Kernel-level parity tests through the C ABI (run on a B200 with `-m gpu`).
+
+Byte/index work (embedding bookkeeping) is checked bit-exactly; f32 kernels against the CPU oracle
+at 1e-5 relative L2; bf16 tensor-core kernels against an f32 evaluation of the same bf16 inputs.
+"""
+import math
+
+import numpy as np
+import pytest
+
+from conftest import rel_l2
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+import eisen_b200 as eb  # noqa: E402
+from oracle_binding import IGNORE_INDEX, OracleAdamW, OracleGraph  # noqa: E402
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def P(t):
+    return t.data_ptr() if t is not None else None
+
+
+def status_word():
+    return torch.zeros(1, dtype=torch.int32, device=dev())
+
+
+DT = {torch.float32: eb.F32, torch.bfloat16: eb.BF16}
+
+
+# --------------------------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 768, 1088), (200, 136, 72), (1024, 2048, 512)])
+def test_gemm_bf16_majors(a_mn, b_mn, M, N, K):
+    g = torch.Generator(device="cpu").manual_seed(M * 7 + N * 3 + K + a_mn * 2 + b_mn)
+    A = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    B = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    ref = A.float() @ B.float().t()
+    Ad = (A.t().contiguous() if a_mn else A).to(dev())
+    Bd = (B.t().contiguous() if b_mn else B).to(dev())
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+    st = status_word()
+    eb.call("eisen_gemm_bf16", stream(), a_mn, b_mn, M, N, K, P(Ad), Ad.stride(0), P(Bd), Bd.stride(0), P(C), N, 0, 1, 1.0, P(st))
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    out = C.float().cpu()
+    assert torch.isfinite(out).all()
+    assert rel_l2(out.numpy(), ref.numpy()) < 4e-3  # bf16 output rounding
+
+
+@pytest.mark.parametrize("mode", [2, 3, 4])
+def test_gemm_f32_out_modes(mode):
+    M, N, K = 256, 384, 2048
+    g = torch.Generator(device="cpu").manual_seed(mode)
+    A = torch.randn(K, M, generator=g).to(torch.bfloat16)  # MN-major A: dW = X^T dY
+    B = torch.randn(K, N, generator=g).to(torch.bfloat16)
+    C0 = torch.randn(M, N, generator=g)
+    ref = A.float().t() @ B.float()
+    if mode != 2:
+        ref = ref + C0
+    Ad, Bd, C = A.to(dev()), B.to(dev()), C0.clone().to(dev())
+    st = status_word()
+    split = 4 if mode == 4 else 1
+    eb.call("eisen_gemm_bf16", stream(), 1, 1, M, N, K, P(Ad), M, P(Bd), N, P(C), N, mode, split, 1.0, P(st))
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert rel_l2(C.cpu().numpy(), ref.numpy()) < 1e-5
+
+
+def test_gemm_bf16_accumulate_and_alpha():
+    M, N, K = 128, 256, 128
+    g = torch.Generator(device="cpu").manual_seed(5)
+    A = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    B = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    C0 = torch.randn(M, N, generator=g).to(torch.bfloat16)
+    ref = C0.float() + 0.5 * (A.float() @ B.float().t())
+    Ad, Bd, C = A.to(dev()), B.to(dev()), C0.clone().to(dev())
+    eb.call("eisen_gemm_bf16", stream(), 0, 0, M, N, K, P(Ad), K, P(Bd), K, P(C), N, 1, 1, 0.5, None)
+    torch.cuda.synchronize()
+    assert rel_l2(C.float().cpu().numpy(), ref.numpy()) < 4e-3
+
+
+def test_gemm_rejects_unaligned_ld():
+    A = torch.zeros(8, 12, dtype=torch.bfloat16, device=dev())
+    C = torch.zeros(8, 8, dtype=torch.bfloat16, device=dev())
+    rc = eb.lib().eisen_gemm_bf16(stream(), 0, 0, 8, 8, 12, P(A), 12, P(A), 12, P(C), 8, 0, 1, 1.0, None)
+    assert rc == 1 and b"16-byte" in eb.lib().eisen_last_error()
+
+
+def test_gemm_f32_strided_matches_oracle():
+    rng = np.random.default_rng(0)
+    A = rng.standard_normal((37, 53)).astype(np.float32)
+    B = rng.standard_normal((53, 29)).astype(np.float32)
+    og = OracleGraph()
+    oa, ob = og.alloc([37, 53], A), og.alloc([53, 29], B)
+    oc = og.matmul(oa, ob)
+    og.backward(oc)
+    Ad, Bd = torch.from_numpy(A).to(dev()), torch.from_numpy(B).to(dev())
+    C = torch.empty(37, 29, device=dev())
+    eb.call("eisen_gemm_f32_strided", stream(), P(Ad), P(Bd), P(C), 1, 37, 29, 53, 0, 53, 1, 0, 29, 1, 0, 29, 0)
+    assert rel_l2(C.cpu().numpy(), og.data(oc)) < 1e-6
+    # dA = dC B^T, dB = A^T dC with dC = 1
+    dC = torch.ones(37, 29, device=dev())
+    dA = torch.zeros(37, 53, device=dev())
+    dB = torch.zeros(53, 29, device=dev())
+    eb.call("eisen_gemm_f32_strided", stream(), P(dC), P(Bd), P(dA), 1, 37, 53, 29, 0, 29, 1, 0, 1, 29, 0, 53, 1)
+    eb.call("eisen_gemm_f32_strided", stream(), P(Ad), P(dC), P(dB), 1, 53, 29, 37, 0, 1, 53, 0, 29, 1, 0, 29, 1)
+    assert rel_l2(dA.cpu().numpy(), og.grad(oa)) < 1e-6
+    assert rel_l2(dB.cpu().numpy(), og.grad(ob)) < 1e-6
+
+
+# --------------------------------------------------------------------------------- attention
+def _attn_reference(q, k, v, d_o, scale, causal):
+    """Materialised chain of src/nn/attention.rs:339-375 in f32 on the bf16 inputs, [B,S,H,D]."""
+    B, S, Hq, D = q.shape
+    Hkv = k.shape[2]
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    kr = kf.repeat_interleave(Hq // Hkv, dim=2)
+    vr = vf.repeat_interleave(Hq // Hkv, dim=2)
+    s = torch.einsum("bqhd,bkhd->bhqk", qf, kr) * scale
+    if causal:
+        mask = torch.triu(torch.full((S, S), -1e20), diagonal=1)
+        s = s + mask
+    p = torch.softmax(s, dim=-1)
+    o = torch.einsum("bhqk,bkhd->bqhd", p, vr)
+    lse = torch.logsumexp(s, dim=-1)
+    o.backward(d_o.float())
+    return o.detach(), lse.detach(), qf.grad, kf.grad, vf.grad
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv,D,causal", [
+    (1, 128, 1, 1, 64, False),
+    (1, 128, 1, 1, 64, True),
+    (2, 256, 4, 2, 64, True),
+    (1, 384, 2, 1, 128, True),
+    (1, 200, 2, 2, 64, True),     # ragged sequence (not a multiple of the 128 tile)
+    (2, 512, 8, 2, 128, True),
+    (1, 320, 2, 2, 128, False),
+])
+def test_flash_attention_fwd_bwd(B, S, Hq, Hkv, D, causal):
+    g = torch.Generator(device="cpu").manual_seed(B * 1000 + S + Hq * 7 + D)
+    # fused projection layout: q is a view into [B,S,Hq*D], k/v views into one [B,S,2*Hkv*D] buffer
+    q = torch.randn(B, S, Hq, D, generator=g).to(torch.bfloat16)
+    kv = torch.randn(B, S, 2, Hkv, D, generator=g).to(torch.bfloat16)
+    d_o = torch.randn(B, S, Hq, D, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    o_ref, lse_ref, dq_ref, dk_ref, dv_ref = _attn_reference(q, kv[:, :, 0], kv[:, :, 1], d_o, scale, causal)
+    qd, kvd, dod = q.to(dev()), kv.to(dev()), d_o.to(dev())
+    kd, vd = kvd[:, :, 0], kvd[:, :, 1]
+    o = torch.full((B, S, Hq, D), float("nan"), dtype=torch.bfloat16, device=dev())
+    lse = torch.empty(B, Hq, S, dtype=torch.float32, device=dev())
+    st = status_word()
+    eb.call("eisen_attn_fwd", stream(), P(qd), P(kd), P(vd), P(o), P(lse), B, S, Hq, Hkv, D,
+            qd.stride(0), qd.stride(1), qd.stride(2), kd.stride(0), kd.stride(1), kd.stride(2),
+            o.stride(0), o.stride(1), o.stride(2), scale, int(causal), P(st))
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert rel_l2(o.float().cpu().numpy(), o_ref.numpy()) < 1e-2
+    assert np.abs(lse.cpu().numpy() - lse_ref.numpy()).max() < 2e-2
+    dq = torch.full_like(qd, float("nan"))
+    dkv = torch.full_like(kvd, float("nan"))
+    dk, dv = dkv[:, :, 0], dkv[:, :, 1]
+    ws = torch.empty(eb.lib().eisen_attn_bwd_workspace_bytes(B, S, Hq, Hkv, D), dtype=torch.uint8, device=dev())
+    eb.call("eisen_attn_bwd", stream(), P(qd), P(kd), P(vd), P(o), P(lse), P(dod), P(dq), P(dk), P(dv), P(ws),
+            B, S, Hq, Hkv, D, qd.stride(0), qd.stride(1), qd.stride(2), kd.stride(0), kd.stride(1), kd.stride(2),
+            o.stride(0), o.stride(1), o.stride(2), scale, int(causal), P(st))
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert rel_l2(dq.float().cpu().numpy(), dq_ref.numpy()) < 2e-2
+    assert rel_l2(dk.float().cpu().numpy(), dk_ref.numpy()) < 2e-2
+    assert rel_l2(dv.float().cpu().numpy(), dv_ref.numpy()) < 2e-2
+
+
+def test_attention_rejects_bad_head_dim():
+    t = torch.zeros(1, 128, 1, 32, dtype=torch.bfloat16, device=dev())
+    lse = torch.zeros(1, 1, 128, device=dev())
+    rc = eb.lib().eisen_attn_fwd(stream(), P(t), P(t), P(t), P(t), P(lse), 1, 128, 1, 1, 32, 4096, 32, 32, 4096, 32, 32,
+                                 4096, 32, 32, 1.0, 1, None)
+    assert rc == 1
+
+
+# --------------------------------------------------------------------------------- row ops
+@pytest.mark.parametrize("rows,dim", [(2, 4), (33, 128), (64, 2048), (7, 100)])
+def test_rmsnorm_f32_vs_oracle(rows, dim):
+    rng = np.random.default_rng(rows + dim)
+    X = rng.standard_normal((rows, dim)).astype(np.float32)
+    W = (1.0 + 0.1 * rng.standard_normal(dim)).astype(np.float32)
+    DY = rng.standard_normal((rows, dim)).astype(np.float32)
+    og = OracleGraph()
+    ox, ow = og.alloc([rows, dim], X), og.alloc([dim], W)
+    oy = og.rms_norm(ox, ow, 1e-5)
+    # backward with an arbitrary upstream gradient: loss = sum(y * DY)
+    ody = og.alloc([rows, dim], DY)
+    og.backward(og.mul(oy, ody))
+    x, w, dy = (torch.from_numpy(a).to(dev()) for a in (X, W, DY))
+    y = torch.empty_like(x)
+    eb.call("eisen_rmsnorm_fwd", stream(), P(x), P(w), P(y), None, rows, dim, 1e-5, eb.F32)
+    assert rel_l2(y.cpu().numpy(), og.data(oy)) < 1e-6
+    dx = torch.full_like(x, float("nan"))
+    dw = torch.zeros(dim, device=dev())
+    ws = torch.empty(eb.lib().eisen_rmsnorm_bwd_workspace_bytes(rows, dim), dtype=torch.uint8, device=dev())
+    eb.call("eisen_rmsnorm_bwd", stream(), P(x), P(w), P(dy), P(dx), P(dw), P(ws), rows, dim, 1e-5, eb.F32, 0)
+    assert rel_l2(dx.cpu().numpy(), og.grad(ox)) < 1e-5
+    assert rel_l2(dw.cpu().numpy(), og.grad(ow)) < 1e-5
+    # accumulate into dx and dw a second time
+    eb.call("eisen_rmsnorm_bwd", stream(), P(x), P(w), P(dy), P(dx), P(dw), P(ws), rows, dim, 1e-5, eb.F32, 1)
+    assert rel_l2(dx.cpu().numpy(), 2 * og.grad(ox)) < 1e-5
+    assert rel_l2(dw.cpu().numpy(), 2 * og.grad(ow)) < 1e-5
+
+
+def test_rmsnorm_bf16():
+    rows, dim = 300, 2048
+    g = torch.Generator(device="cpu").manual_seed(9)
+    x = torch.randn(rows, dim, generator=g).to(torch.bfloat16)
+    dy = torch.randn(rows, dim, generator=g).to(torch.bfloat16)
+    w = 1.0 + 0.1 * torch.randn(dim, generator=g)
+    xf = x.float().requires_grad_(True)
+    wf = w.clone().requires_grad_(True)
+    yf = xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + 1e-5) * wf
+    yf.backward(dy.float())
+    xd, dyd, wd = x.to(dev()), dy.to(dev()), w.to(dev())
+    y = torch.empty_like(xd)
+    eb.call("eisen_rmsnorm_fwd", stream(), P(xd), P(wd), P(y), None, rows, dim, 1e-5, eb.BF16)
+    assert rel_l2(y.float().cpu().numpy(), yf.detach().numpy()) < 5e-3
+    dx = torch.empty_like(xd)
+    dw = torch.zeros(dim, device=dev())
+    ws = torch.empty(eb.lib().eisen_rmsnorm_bwd_workspace_bytes(rows, dim), dtype=torch.uint8, device=dev())
+    eb.call("eisen_rmsnorm_bwd", stream(), P(xd), P(wd), P(dyd), P(dx), P(dw), P(ws), rows, dim, 1e-5, eb.BF16, 0)
+    assert rel_l2(dx.float().cpu().numpy(), xf.grad.numpy()) < 5e-3
+    assert rel_l2(dw.cpu().numpy(), wf.grad.numpy()) < 1e-4
+
+
+@pytest.mark.parametrize("rows,vocab,masked", [(2, 3, False), (64, 512, False), (40, 1000, True), (16, 32000, True)])
+def test_cross_entropy_f32_vs_oracle(rows, vocab, masked):
+    rng = np.random.default_rng(rows * vocab)
+    L = (3.0 * rng.standard_normal((rows, vocab))).astype(np.float32)
+    T = rng.integers(0, vocab, rows)
+    if masked:
+        T[rng.random(rows) < 0.3] = IGNORE_INDEX
+        T[0] = 1  # at least one valid row
+        T[1] = IGNORE_INDEX
+    og = OracleGraph()
+    ol = og.alloc([rows, vocab], L)
+    oloss = og.cross_entropy_masked(ol, T.tolist())
+    og.backward(oloss)
+    valid = int((T != IGNORE_INDEX).sum())
+    norm = 1.0 / valid if masked else 1.0 / rows
+    l = torch.from_numpy(L).to(dev())
+    t = torch.from_numpy(T.astype(np.int32)).to(dev())
+    loss = torch.zeros(1, device=dev())
+    row_loss = torch.empty(rows, device=dev())
+    lse = torch.empty(rows, device=dev())
+    eb.call("eisen_ce_fwd", stream(), P(l), P(t), P(loss), P(row_loss), P(lse), rows, vocab, IGNORE_INDEX, norm, eb.F32)
+    assert abs(loss.item() - og.data(oloss)[0]) < 1e-5 * max(1.0, abs(og.data(oloss)[0]))
+    dl = torch.full_like(l, float("nan"))
+    one = torch.ones(1, device=dev())
+    eb.call("eisen_ce_bwd", stream(), P(l), P(t), P(lse), P(dl), P(one), rows, vocab, IGNORE_INDEX, norm, eb.F32, 0)
+    assert rel_l2(dl.cpu().numpy(), og.grad(ol)) < 1e-5
+    if masked:
+        assert (dl.cpu().numpy().reshape(rows, vocab)[T == IGNORE_INDEX] == 0).all()
+    # in place
+    eb.call("eisen_ce_bwd", stream(), P(l), P(t), P(lse), P(l), P(one), rows, vocab, IGNORE_INDEX, norm, eb.F32, 0)
+    assert rel_l2(l.cpu().numpy(), og.grad(ol)) < 1e-5
+
+
+def test_cross_entropy_bf16():
+    rows, vocab = 128, 8192
+    g = torch.Generator(device="cpu").manual_seed(4)
+    l = (2.0 * torch.randn(rows, vocab, generator=g)).to(torch.bfloat16)
+    t = torch.randint(0, vocab, (rows,), generator=g)
+    lf = l.float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(lf, t)
+    ref.backward()
+    ld, td = l.to(dev()), t.to(torch.int32).to(dev())
+    loss = torch.zeros(1, device=dev())
+    row_loss = torch.empty(rows, device=dev())
+    lse = torch.empty(rows, device=dev())
+    eb.call("eisen_ce_fwd", stream(), P(ld), P(td), P(loss), P(row_loss), P(lse), rows, vocab, -1, 1.0 / rows, eb.BF16)
+    assert abs(loss.item() - ref.item()) < 1e-3
+    eb.call("eisen_ce_bwd", stream(), P(ld), P(td), P(lse), P(ld), None, rows, vocab, -1, 1.0 / rows, eb.BF16, 0)
+    assert rel_l2(ld.float().cpu().numpy(), lf.grad.numpy()) < 1e-2
+
+
+def test_softmax_vs_oracle():
+    rng = np.random.default_rng(3)
+    X = rng.standard_normal((10, 77)).astype(np.float32)
+    DY = rng.standard_normal((10, 77)).astype(np.float32)
+    og = OracleGraph()
+    ox = og.alloc([10, 77], X)
+    oy = og.softmax(ox)
+    og.backward(og.mul(oy, og.alloc([10, 77], DY)))
+    x, dy = torch.from_numpy(X).to(dev()), torch.from_numpy(DY).to(dev())
+    y, dx = torch.empty_like(x), torch.empty_like(x)
+    eb.call("eisen_softmax_fwd", stream(), P(x), P(y), 10, 77, eb.F32)
+    eb.call("eisen_softmax_bwd", stream(), P(y), P(dy), P(dx), 10, 77, eb.F32, 0)
+    assert rel_l2(y.cpu().numpy(), og.data(oy)) < 1e-6
+    assert rel_l2(dx.cpu().numpy(), og.grad(ox)) < 1e-5
+
+
+# --------------------------------------------------------------------------------- elementwise
+@pytest.mark.parametrize("B,S,hidden,hd", [(1, 2, 4, 4), (2, 64, 128, 32), (2, 100, 256, 64), (1, 5, 12, 6)])
+def test_rope_f32_vs_oracle(B, S, hidden, hd):
+    rng = np.random.default_rng(hidden)
+    X = rng.standard_normal((B, S, hidden)).astype(np.float32)
+    DY = rng.standard_normal((B, S, hidden)).astype(np.float32)
+    og = OracleGraph()
+    ox = og.alloc([B, S, hidden], X)
+    oy = og.rope(ox, hd)
+    og.backward(og.mul(oy, og.alloc([B, S, hidden], DY)))
+    tab = torch.empty(S, hd // 2, 2, device=dev())
+    eb.call("eisen_rope_table", stream(), P(tab), S, hd, 10000.0)
+    x, dy = torch.from_numpy(X).to(dev()), torch.from_numpy(DY).to(dev())
+    y, dx = torch.empty_like(x), torch.empty_like(x)
+    eb.call("eisen_rope", stream(), P(x), P(y), P(tab), B, S, hidden, hd, eb.F32, 0, 0)
+    eb.call("eisen_rope", stream(), P(dy), P(dx), P(tab), B, S, hidden, hd, eb.F32, 1, 0)
+    assert rel_l2(y.cpu().numpy(), og.data(oy)) < 2e-6
+    assert rel_l2(dx.cpu().numpy(), og.grad(ox)) < 2e-6
+
+
+def test_swiglu_matches_silu_mul_chain():
+    rng = np.random.default_rng(8)
+    n = 1000
+    G, U, DH = (rng.standard_normal(n).astype(np.float32) for _ in range(3))
+    og = OracleGraph()
+    o_g, o_u = og.alloc([n], G), og.alloc([n], U)
+    oh = og.mul(og.silu(o_g), o_u)
+    og.backward(og.mul(oh, og.alloc([n], DH)))
+    gt, ut, dh = (torch.from_numpy(a).to(dev()) for a in (G, U, DH))
+    h, dg, du = torch.empty_like(gt), torch.empty_like(gt), torch.empty_like(gt)
+    eb.call("eisen_swiglu_fwd", stream(), P(gt), P(ut), P(h), n, eb.F32)
+    eb.call("eisen_swiglu_bwd", stream(), P(gt), P(ut), P(dh), P(dg), P(du), n, eb.F32, 0)
+    assert rel_l2(h.cpu().numpy(), og.data(oh)) < 1e-6
+    assert rel_l2(dg.cpu().numpy(), og.grad(o_g)) < 1e-5
+    assert rel_l2(du.cpu().numpy(), og.grad(o_u)) < 1e-6
+
+
+def test_layout_ops_vs_oracle():
+    rng = np.random.default_rng(12)
+    X = rng.standard_normal((2, 5, 3, 8)).astype(np.float32)
+    og = OracleGraph()
+    ox = og.alloc([2, 5, 3, 8], X)
+    ot = og.transpose_0213(ox)
+    x = torch.from_numpy(X).to(dev())
+    y = torch.empty(2, 3, 5, 8, device=dev())
+    eb.call("eisen_transpose_0213", stream(), P(x), P(y), 2, 5, 3, 8, eb.F32, 0)
+    assert (y.cpu().numpy().reshape(-1) == og.data(ot)).all()
+    K = rng.standard_normal((2, 2, 5, 8)).astype(np.float32)
+    ok = og.alloc([2, 2, 5, 8], K)
+    orp = og.repeat_kv(ok, 3)
+    og.backward(orp)
+    k = torch.from_numpy(K).to(dev())
+    r = torch.empty(2, 6, 5, 8, device=dev())
+    eb.call("eisen_repeat_kv_fwd", stream(), P(k), P(r), 2, 2, 5, 8, 3, eb.F32)
+    assert (r.cpu().numpy().reshape(-1) == og.data(orp)).all()
+    dk = torch.empty_like(k)
+    ones = torch.ones_like(r)
+    eb.call("eisen_repeat_kv_bwd", stream(), P(ones), P(dk), 2, 2, 5, 8, 3, eb.F32, 0)
+    assert (dk.cpu().numpy().reshape(-1) == og.grad(ok)).all()
+
+
+def test_add_broadcast_and_accumulate():
+    x = torch.arange(8, dtype=torch.float32, device=dev())
+    m = torch.tensor([0.0, -1.0, 0.0, 0.0], device=dev())
+    o = torch.empty_like(x)
+    eb.call("eisen_add", stream(), P(x), P(m), P(o), 8, 4, eb.F32)
+    assert o.cpu().tolist() == [0, 0, 2, 3, 4, 4, 6, 7]
+    dm = torch.zeros(4, device=dev())
+    eb.call("eisen_reduce_leading", stream(), P(torch.ones(8, device=dev())), eb.F32, P(dm), 8, 4, 1)
+    assert dm.cpu().tolist() == [2, 2, 2, 2]
+    a = torch.ones(10, device=dev())
+    b = torch.full((10,), 0.5, dtype=torch.bfloat16, device=dev())
+    eb.call("eisen_accumulate", stream(), P(a), eb.F32, P(b), eb.BF16, 10, 1)
+    assert a.cpu().tolist() == [1.5] * 10
+
+
+# --------------------------------------------------------------------------------- embedding
+@pytest.mark.parametrize("n,vocab,dim,skew", [(4, 3, 2, False), (1000, 64, 48, False), (16384, 32000, 128, False), (4096, 17, 64, True)])
+def test_embedding_gather_scatter_bit_exact(n, vocab, dim, skew):
+    rng = np.random.default_rng(n + vocab)
+    ids = rng.integers(0, vocab, n).astype(np.int32)
+    if skew:
+        ids[: n // 2] = 5  # one id with thousands of occurrences
+    W = rng.standard_normal((vocab, dim)).astype(np.float32)
+    # integer-valued gradients: sums are exact in f32, so the scatter must match bit for bit
+    Gr = rng.integers(-8, 9, (n, dim)).astype(np.float32)
+    w, idt, gr = torch.from_numpy(W).to(dev()), torch.from_numpy(ids).to(dev()), torch.from_numpy(Gr).to(dev())
+    out = torch.empty(n, dim, device=dev())
+    bad = torch.zeros(1, dtype=torch.int32, device=dev())
+    eb.call("eisen_embedding_fwd", stream(), P(w), eb.F32, P(idt), P(out), eb.F32, n, dim, vocab, P(bad))
+    assert (out.cpu().numpy() == W[ids]).all() and bad.item() == 0
+    dw = torch.zeros(vocab, dim, device=dev())
+    ws = torch.empty(eb.lib().eisen_embedding_bwd_workspace_bytes(n, vocab), dtype=torch.uint8, device=dev())
+    eb.call("eisen_embedding_bwd", stream(), P(gr), eb.F32, P(idt), P(dw), P(ws), n, dim, vocab)
+    ref = np.zeros((vocab, dim), np.float32)
+    np.add.at(ref, ids, Gr)
+    assert (dw.cpu().numpy() == ref).all()
+    # bookkeeping: positions grouped by id in position order == stable argsort of the ids
+    cnt = torch.empty(vocab, dtype=torch.int32, device=dev())
+    off = torch.empty(vocab, dtype=torch.int32, device=dev())
+    perm = torch.empty(n, dtype=torch.int32, device=dev())
+    eb.call("eisen_embedding_bwd_bookkeeping", stream(), P(ws), n, vocab, P(cnt), P(off), P(perm))
+    assert (cnt.cpu().numpy() == np.bincount(ids, minlength=vocab)).all()
+    assert (off.cpu().numpy() == np.concatenate([[0], np.cumsum(np.bincount(ids, minlength=vocab))[:-1]])).all()
+    assert (perm.cpu().numpy() == np.argsort(ids, kind="stable")).all()
+
+
+def test_embedding_reference_golden():
+    # tests/gpu_kernels.rs:155-207: the repeated id collects a gradient of exactly 2
+    w = torch.tensor([[0.1, 0.2], [0.3, 0.4], [0.5, 0.6]], device=dev())
+    ids = torch.tensor([2, 0, 2, 1], dtype=torch.int32, device=dev())
+    out = torch.empty(4, 2, device=dev())
+    eb.call("eisen_embedding_fwd", stream(), P(w), eb.F32, P(ids), P(out), eb.F32, 4, 2, 3, None)
+    assert np.allclose(out.cpu().numpy().reshape(-1), [0.5, 0.6, 0.1, 0.2, 0.5, 0.6, 0.3, 0.4])
+    dw = torch.zeros(3, 2, device=dev())
+    ws = torch.empty(eb.lib().eisen_embedding_bwd_workspace_bytes(4, 3), dtype=torch.uint8, device=dev())
+    eb.call("eisen_embedding_bwd", stream(), P(torch.ones(4, 2, device=dev())), eb.F32, P(ids), P(dw), P(ws), 4, 2, 3)
+    assert dw.cpu().numpy().reshape(-1).tolist() == [1, 1, 1, 1, 2, 2]
+
+
+def test_embedding_flags_out_of_range_id():
+    w = torch.zeros(3, 4, device=dev())
+    ids = torch.tensor([1, 7], dtype=torch.int32, device=dev())
+    out = torch.empty(2, 4, device=dev())
+    bad = torch.zeros(1, dtype=torch.int32, device=dev())
+    eb.call("eisen_embedding_fwd", stream(), P(w), eb.F32, P(ids), P(out), eb.F32, 2, 4, 3, P(bad))
+    assert bad.item() == 1
+
+
+# --------------------------------------------------------------------------------- optimizer
+def test_adamw_vs_oracle_three_steps():
+    rng = np.random.default_rng(21)
+    n = 10007
+    W = (0.02 * rng.standard_normal(n)).astype(np.float32)
+    og = OracleGraph()
+    ow = og.alloc([n], W)
+    opt = OracleAdamW(og, [ow], 3e-4)
+    opt.config(3e-4, 0.9, 0.95, 1e-8, 0.1)
+    w = torch.from_numpy(W).to(dev())
+    m, v = torch.zeros_like(w), torch.zeros_like(w)
+    wb = torch.empty(n, dtype=torch.bfloat16, device=dev())
+    for t in range(1, 4):
+        Gr = (1e-3 * rng.standard_normal(n)).astype(np.float32)
+        # oracle: load the gradient by a mul-backward trick is overkill; set it through a graph op
+        og.zero_grad_tensor(ow)
+        gsrc = og.alloc([n], Gr)
+        og.backward(og.mul(ow, gsrc))  # d(w*g)/dw = g
+        og.tape_clear()
+        opt.step()
+        bc1 = np.float32(1.0) / (np.float32(1.0) - np.float32(0.9) ** t)
+        bc2 = np.float32(1.0) / (np.float32(1.0) - np.float32(0.95) ** t)
+        gt = torch.from_numpy(Gr).to(dev())
+        eb.call("eisen_adamw_step", stream(), P(w), P(wb), P(gt), P(m), P(v), n, 3e-4, 0.9, 0.95, 1e-8, 0.1,
+                float(bc1), float(bc2), 1.0, None, 0.0)
+        assert rel_l2(w.cpu().numpy(), og.data(ow)) < 1e-6
+    assert rel_l2(wb.float().cpu().numpy(), og.data(ow)) < 4e-3
+
+
+def test_sumsq_and_fused_clip():
+    rng = np.random.default_rng(22)
+    n = 100003
+    Gr = rng.standard_normal(n).astype(np.float32)
+    g = torch.from_numpy(Gr).to(dev())
+    ws = torch.empty(eb.lib().eisen_sumsq_workspace_bytes(n), dtype=torch.uint8, device=dev())
+    ss = torch.zeros(1, dtype=torch.float64, device=dev())
+    eb.call("eisen_sumsq", stream(), P(g), n, P(ws), P(ss), 0)
+    ref = float((Gr.astype(np.float64) ** 2).sum())
+    assert abs(ss.item() - ref) / ref < 1e-12
+    # fused clip == explicit clip (src/nn/optim.rs:283-287) followed by the plain step
+    W = (0.02 * rng.standard_normal(n)).astype(np.float32)
+    norm = np.float32(math.sqrt(ref))
+    coef = min(np.float32(1.0) / (norm + np.float32(1e-6)), np.float32(1.0))
+    w1, w2 = torch.from_numpy(W).to(dev()), torch.from_numpy(W).to(dev())
+    m1, v1, m2, v2 = (torch.zeros(n, device=dev()) for _ in range(4))
+    eb.call("eisen_adamw_step", stream(), P(w1), None, P(g), P(m1), P(v1), n, 1e-3, 0.9, 0.95, 1e-8, 0.1, 10.0, 20.0, 1.0, P(ss), 1.0)
+    g2 = g * float(coef)
+    eb.call("eisen_adamw_step", stream(), P(w2), None, P(g2), P(m2), P(v2), n, 1e-3, 0.9, 0.95, 1e-8, 0.1, 10.0, 20.0, 1.0, None, 0.0)
+    assert rel_l2(w1.cpu().numpy(), w2.cpu().numpy()) < 1e-6
+
+
+def test_fill_scale_cast():
+    x = torch.empty(1001, device=dev())
+    eb.call("eisen_fill_f32", stream(), P(x), 2.5, 1001)
+    eb.call("eisen_scale_f32", stream(), P(x), 2.0, 1001)
+    assert (x.cpu().numpy() == 5.0).all()
+    b = torch.empty(1001, dtype=torch.bfloat16, device=dev())
+    eb.call("eisen_cast", stream(), P(x), eb.F32, P(b), eb.BF16, 1001)
+    y = torch.empty(1001, device=dev())
+    eb.call("eisen_cast", stream(), P(b), eb.BF16, P(y), eb.F32, 1001)
+    assert (y.cpu().numpy() == 5.0).all()
