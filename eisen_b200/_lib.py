@@ -29,9 +29,8 @@ _CTYPES = {
     "int": C.c_int,
     "float": C.c_float,
     "double": C.c_double,
-    "eisen_graph_t": C.c_void_p,
-    "eisen_lm_t": C.c_void_p,
-    "eisen_adamw_t": C.c_void_p,
+    "void**": C.c_void_p,
+    "eisen_block_cb": C.c_void_p,
 }
 
 _DECL = re.compile(r"^\s*(const char\*|int|long long|void|eisen_\w+_t)\s+(eisen_\w+)\s*\(([^;{]*?)\)\s*;", re.M | re.S)

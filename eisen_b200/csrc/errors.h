@@ -4,16 +4,10 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include "../../include/eisen_b200.h"  // EISEN_OK / EISEN_ERR_* codes
+
 namespace eisen {
 
-enum Status : int {
-  EISEN_OK = 0,
-  EISEN_ERR_INVALID = 1,   // bad argument (shape, alignment, dtype)
-  EISEN_ERR_CUDA = 2,      // a CUDA runtime / driver call failed
-  EISEN_ERR_KERNEL = 3,    // a kernel recorded a fault in its status word (a bounded wait ran out)
-  EISEN_ERR_OOM = 4,       // device allocation failed
-  EISEN_ERR_LIMIT = 5,     // a stated size limit of an entry point was exceeded
-};
 
 void set_error(const char* msg);
 int fail(int code, const char* msg);

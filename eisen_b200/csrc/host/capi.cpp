@@ -1,0 +1,248 @@
+// Graph-level C ABI: opaque handles over Graph / TransformerLM / AdamW (graph.h).  Exceptions
+// never cross the boundary: they become status codes plus eisen_last_error().
+#include <cstring>
+
+#include "../../../include/eisen_b200.h"
+#include "../errors.h"
+#include "graph.h"
+
+using namespace eisen;
+
+namespace {
+
+template <class F>
+int guarded(F f) {
+  try {
+    f();
+    return 0;
+  } catch (const EisenException& e) {
+    set_error(e.what());
+    return e.code ? e.code : EISEN_ERR_INVALID;
+  } catch (const std::out_of_range&) {
+    set_error("tensor id out of range");
+    return EISEN_ERR_INVALID;
+  } catch (const std::bad_alloc&) {
+    set_error("host allocation failed");
+    return EISEN_ERR_OOM;
+  } catch (const std::exception& e) {
+    set_error(e.what());
+    return EISEN_ERR_INVALID;
+  }
+}
+
+inline Graph& G(void* g) {
+  if (!g) throw EisenException(EISEN_ERR_INVALID, "null graph handle");
+  return *static_cast<Graph*>(g);
+}
+inline std::vector<int64_t> shp(const long long* s, int n) { return std::vector<int64_t>(s, s + n); }
+
+}  // namespace
+
+extern "C" {
+
+int eisen_graph_create(int precision, void* stream, void** out) {
+  return guarded([&] {
+    if (precision != 0 && precision != 1) throw EisenException(EISEN_ERR_INVALID, "precision must be 0 (Fp32) or 1 (Bf16Mixed)");
+    *out = new Graph(precision ? Precision::Bf16Mixed : Precision::Fp32, (cudaStream_t)stream);
+  });
+}
+int eisen_graph_destroy(void* g) {
+  return guarded([&] { delete static_cast<Graph*>(g); });
+}
+int eisen_graph_alloc(void* g, const long long* shape, int ndim, const float* host_data, long long* id_out) {
+  return guarded([&] { *id_out = G(g).alloc(shp(shape, ndim), host_data); });
+}
+int eisen_graph_alloc_ids(void* g, const long long* shape, int ndim, const int* host_ids, long long* id_out) {
+  return guarded([&] { *id_out = G(g).alloc_ids(shp(shape, ndim), host_ids, true); });
+}
+int eisen_graph_alloc_pooled(void* g, const long long* shape, int ndim, long long* id_out) {
+  return guarded([&] { *id_out = G(g).alloc_pooled(shp(shape, ndim)); });
+}
+int eisen_graph_load_tensor_data(void* g, long long id, const float* host, long long n) {
+  return guarded([&] { G(g).load_tensor_data(id, host, n); });
+}
+int eisen_graph_sync_to_cpu(void* g, long long id, float* out) {
+  return guarded([&] { G(g).sync_to_cpu(id, out); });
+}
+int eisen_graph_sync_grad_to_cpu(void* g, long long id, float* out) {
+  return guarded([&] { G(g).sync_grad_to_cpu(id, out); });
+}
+int eisen_graph_shape(void* g, long long id, long long* shape_out, int* ndim_out) {
+  return guarded([&] {
+    const HTensor& t = G(g).tensors.at(id);
+    for (size_t i = 0; i < t.shape.size(); ++i) shape_out[i] = t.shape[i];
+    *ndim_out = (int)t.shape.size();
+  });
+}
+int eisen_graph_tensor_ptrs(void* g, long long id, void** data, void** grad, int* dtype, int* grad_dtype) {
+  return guarded([&] {
+    const HTensor& t = G(g).tensors.at(id);
+    if (data) *data = t.data;
+    if (grad) *grad = t.grad;
+    if (dtype) *dtype = t.dtype;
+    if (grad_dtype) *grad_dtype = t.grad_dtype;
+  });
+}
+int eisen_graph_set_no_grad(void* g, int flag) {
+  return guarded([&] { G(g).no_grad = flag != 0; });
+}
+int eisen_graph_mark_params(void* g) {
+  return guarded([&] { G(g).mark_params(); });
+}
+int eisen_graph_mark_save_point(void* g, long long* out) {
+  return guarded([&] { *out = G(g).mark_save_point(); });
+}
+int eisen_graph_restore_save_point(void* g, long long sp) {
+  return guarded([&] { G(g).restore_save_point(sp); });
+}
+int eisen_graph_clear_activations(void* g) {
+  return guarded([&] { G(g).clear_activations(); });
+}
+int eisen_graph_tape_clear(void* g) {
+  return guarded([&] { G(g).tape.clear(); });
+}
+int eisen_graph_reinterpret_shape(void* g, long long id, const long long* shape, int ndim) {
+  return guarded([&] { G(g).reinterpret_shape(id, shp(shape, ndim)); });
+}
+int eisen_graph_zero_grad(void* g, long long id) {
+  return guarded([&] { G(g).zero_grad(id); });
+}
+int eisen_graph_backward(void* g, long long loss_id) {
+  return guarded([&] { G(g).backward(loss_id); });
+}
+int eisen_graph_synchronize(void* g) {
+  return guarded([&] { G(g).synchronize(); });
+}
+int eisen_graph_counts(void* g, long long* num_tensors, long long* tape_len, long long* num_params) {
+  return guarded([&] {
+    Graph& gg = G(g);
+    if (num_tensors) *num_tensors = (long long)gg.tensors.size();
+    if (tape_len) *tape_len = (long long)gg.tape.size();
+    if (num_params) *num_params = gg.num_params;
+  });
+}
+int eisen_graph_pool_stats(void* g, long long* out5) {
+  return guarded([&] {
+    Graph& gg = G(g);
+    out5[0] = (long long)gg.pool_bytes_live;
+    out5[1] = (long long)gg.pool_bytes_cached;
+    out5[2] = (long long)gg.device_bytes_allocated;
+    out5[3] = gg.pool_hits;
+    out5[4] = gg.pool_misses;
+  });
+}
+int eisen_graph_param_arena(void* g, void** weights, void** shadow, void** grads, long long* elems) {
+  return guarded([&] {
+    Graph& gg = G(g);
+    if (weights) *weights = gg.arena_w;
+    if (shadow) *shadow = gg.arena_shadow;
+    if (grads) *grads = gg.arena_g;
+    if (elems) *elems = gg.arena_used;
+  });
+}
+
+#define OP2(name, call) \
+  int eisen_graph_##name(void* g, long long a, long long b, long long* out) { return guarded([&] { *out = G(g).call(a, b); }); }
+#define OP1(name, call) \
+  int eisen_graph_##name(void* g, long long a, long long* out) { return guarded([&] { *out = G(g).call(a); }); }
+OP2(add, add)
+OP2(mul, mul)
+OP1(silu, silu)
+OP2(swiglu, swiglu)
+OP2(matmul, matmul)
+OP2(matmul_trans_b, matmul_trans_b)
+OP1(softmax, softmax)
+OP2(gather, gather)
+OP1(transpose_0213, transpose_0213)
+OP2(repeat_kv, repeat_kv)
+OP2(rope, rope)
+
+int eisen_graph_bmm(void* g, long long a, long long b, int trans_b, long long* out) {
+  return guarded([&] { *out = G(g).bmm(a, b, trans_b != 0); });
+}
+int eisen_graph_cross_entropy(void* g, long long logits, const long long* targets, long long n, long long* out) {
+  return guarded([&] { *out = G(g).cross_entropy(logits, (const int64_t*)targets, n); });
+}
+int eisen_graph_cross_entropy_masked(void* g, long long logits, const long long* targets, long long n, long long* out) {
+  return guarded([&] { *out = G(g).cross_entropy_masked(logits, (const int64_t*)targets, n); });
+}
+int eisen_graph_rms_norm(void* g, long long x, long long w, float eps, long long* out) {
+  return guarded([&] { *out = G(g).rms_norm(x, w, eps); });
+}
+int eisen_graph_reshape(void* g, long long a, const long long* shape, int ndim, long long* out) {
+  return guarded([&] { *out = G(g).reshape(a, shp(shape, ndim)); });
+}
+int eisen_graph_flash_attention(void* g, long long q, long long k, long long v, float scale, int causal, long long* out) {
+  return guarded([&] { *out = G(g).flash_attention(q, k, v, scale, causal != 0); });
+}
+int eisen_graph_attention(void* g, long long q, long long k, long long v, long long num_heads, long long num_kv_heads,
+                          int causal, long long* out) {
+  return guarded([&] { *out = G(g).attention(q, k, v, num_heads, num_kv_heads, causal != 0); });
+}
+
+// ---- TransformerLM
+int eisen_lm_create(void* g, long long vocab, long long hidden, long long heads, long long kv_heads, long long ffn,
+                    long long layers, int tie, void** out) {
+  return guarded([&] { *out = new TransformerLM(G(g), vocab, hidden, heads, kv_heads, ffn, layers, tie != 0); });
+}
+int eisen_lm_destroy(void* lm) {
+  return guarded([&] { delete static_cast<TransformerLM*>(lm); });
+}
+int eisen_lm_set_fused(void* lm, int fused) {
+  return guarded([&] { static_cast<TransformerLM*>(lm)->fused = fused != 0; });
+}
+int eisen_lm_forward(void* lm, void* g, long long x, long long* out) {
+  return guarded([&] { *out = static_cast<TransformerLM*>(lm)->forward(G(g), x); });
+}
+int eisen_lm_params(void* lm, long long* out, int* n) {
+  return guarded([&] {
+    auto p = static_cast<TransformerLM*>(lm)->params();
+    for (size_t i = 0; i < p.size(); ++i) out[i] = p[i];
+    *n = (int)p.size();
+  });
+}
+int eisen_lm_train_micro_step(void* lm, void* g, long long x_ids, const long long* targets, long long n_targets,
+                              int checkpoint, eisen_block_cb after_block, void* user, long long* loss_id) {
+  return guarded([&] {
+    std::function<void(int64_t)> cb;
+    if (after_block) cb = [after_block, user](int64_t l) { after_block((long long)l, user); };
+    *loss_id = static_cast<TransformerLM*>(lm)->train_micro_step(G(g), x_ids, (const int64_t*)targets, n_targets,
+                                                                 checkpoint != 0, cb);
+  });
+}
+
+// ---- AdamW
+int eisen_optim_create(void* g, const long long* params, int n, float lr, void** out) {
+  return guarded([&] { *out = new AdamW(G(g), std::vector<int64_t>(params, params + n), lr); });
+}
+int eisen_optim_destroy(void* opt) {
+  return guarded([&] { delete static_cast<AdamW*>(opt); });
+}
+int eisen_optim_config(void* opt, float lr, float beta1, float beta2, float eps, float weight_decay) {
+  return guarded([&] {
+    AdamW& o = *static_cast<AdamW*>(opt);
+    o.lr = lr; o.beta1 = beta1; o.beta2 = beta2; o.eps = eps; o.weight_decay = weight_decay;
+  });
+}
+int eisen_optim_zero_grad(void* opt) {
+  return guarded([&] { static_cast<AdamW*>(opt)->zero_grad(); });
+}
+int eisen_optim_clip_grad_norm(void* opt, float max_norm, float* norm_out, float* coef_out) {
+  return guarded([&] {
+    float coef = 1.0f;
+    float n = static_cast<AdamW*>(opt)->clip_grad_norm(max_norm, &coef);
+    if (norm_out) *norm_out = n;
+    if (coef_out) *coef_out = coef;
+  });
+}
+int eisen_optim_step(void* opt) {
+  return guarded([&] { static_cast<AdamW*>(opt)->step(); });
+}
+int eisen_optim_step_fused(void* opt, float max_norm, float grad_scale) {
+  return guarded([&] { static_cast<AdamW*>(opt)->step_fused(max_norm, grad_scale); });
+}
+int eisen_optim_is_flat(void* opt, int* flat) {
+  return guarded([&] { *flat = static_cast<AdamW*>(opt)->flat ? 1 : 0; });
+}
+
+}  // extern "C"

@@ -1,0 +1,891 @@
+// Graph / tape host logic: see graph.h.  Every op follows the shape rules of its reference
+// counterpart (cited per op) and launches kernels of this library on the graph's stream; there
+// is no host synchronisation inside an op and no per-op cudaMalloc once the pool is warm.
+#include "graph.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+#include "../../../include/eisen_b200.h"
+
+namespace eisen {
+
+namespace {
+
+inline size_t dsize(int dt) { return dt == 1 ? 2 : 4; }
+inline int64_t numel_of(const std::vector<int64_t>& s) {
+  int64_t n = 1;
+  for (int64_t d : s) n *= d;
+  return n;
+}
+inline size_t round256(size_t b) { return (b + 255) & ~size_t(255); }
+
+void ck(int rc, const char* what) {
+  if (rc != 0) throw EisenException(rc, std::string(what) + ": " + eisen_last_error());
+}
+void cuck(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) throw EisenException(EISEN_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+[[noreturn]] void invalid(const std::string& m) { throw EisenException(EISEN_ERR_INVALID, m); }
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------- storage
+Graph::Graph(Precision prec, cudaStream_t s) : precision(prec), stream(s) {
+  cuck(cudaMalloc(&status_dev, 256), "cudaMalloc(status)");
+  cuck(cudaMemsetAsync(status_dev, 0, 256, stream), "memset(status)");
+  bad_id_dev = status_dev + 16;
+}
+
+Graph::~Graph() {
+  cudaStreamSynchronize(stream);
+  for (HTensor& t : tensors) free_tensor(t);
+  for (auto& kv : pool_)
+    for (void* p : kv.second) cudaFree(p);
+  for (auto& kv : rope_tables_) cudaFree(kv.second);
+  if (scratch_) cudaFree(scratch_);
+  if (arena_w) cudaFree(arena_w);
+  if (arena_shadow) cudaFree(arena_shadow);
+  if (arena_g) cudaFree(arena_g);
+  if (status_dev) cudaFree(status_dev);
+}
+
+// exact-size free lists, as the reference's vram_pool keyed by element count
+// (src/graph/mod.rs:62-64, 437-556)
+void* Graph::pool_get(size_t bytes) {
+  bytes = round256(std::max<size_t>(bytes, 4));
+  auto it = pool_.find(bytes);
+  if (it != pool_.end() && !it->second.empty()) {
+    void* p = it->second.back();
+    it->second.pop_back();
+    pool_bytes_cached -= bytes;
+    pool_bytes_live += bytes;
+    ++pool_hits;
+    return p;
+  }
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) {
+    // drop the cache and retry once (src/graph/memory.rs:189-266: alloc -> drop pool -> retry)
+    cudaGetLastError();
+    cudaStreamSynchronize(stream);
+    for (auto& kv : pool_) {
+      for (void* q : kv.second) cudaFree(q);
+      kv.second.clear();
+    }
+    device_bytes_allocated -= pool_bytes_cached;
+    pool_bytes_cached = 0;
+    e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) throw EisenException(EISEN_ERR_OOM, "out of device memory in the activation pool");
+  }
+  device_bytes_allocated += bytes;
+  pool_bytes_live += bytes;
+  ++pool_misses;
+  return p;
+}
+
+void Graph::pool_put(void* p, size_t bytes) {
+  if (!p) return;
+  bytes = round256(std::max<size_t>(bytes, 4));
+  pool_[bytes].push_back(p);
+  pool_bytes_cached += bytes;
+  pool_bytes_live -= bytes;
+}
+
+void* Graph::scratch(size_t bytes) {
+  if (bytes > scratch_bytes_) {
+    // the old buffer may still be in use by queued kernels: hand it to the pool instead of freeing
+    if (scratch_) { pool_bytes_live += round256(scratch_bytes_); pool_put(scratch_, scratch_bytes_); }
+    scratch_bytes_ = round256(bytes + bytes / 4);
+    cuck(cudaMalloc(&scratch_, scratch_bytes_), "cudaMalloc(scratch)");
+    device_bytes_allocated += scratch_bytes_;
+  }
+  return scratch_;
+}
+
+int64_t Graph::new_tensor(HTensor&& t) {
+  tensors.push_back(std::move(t));
+  return (int64_t)tensors.size() - 1;
+}
+
+void Graph::free_tensor(HTensor& t) {
+  if (t.is_pooled) {
+    pool_put(t.data, (size_t)t.numel * dsize(t.dtype == DT_I32 ? 0 : t.dtype));
+    pool_put(t.grad, (size_t)t.numel * dsize(t.grad_dtype));
+  } else {
+    if (t.owns_data && t.data) cudaFree(t.data);
+    if (t.owns_data && t.shadow) cudaFree(t.shadow);
+    if (t.owns_grad && t.grad) cudaFree(t.grad);
+  }
+  t.data = t.shadow = t.grad = nullptr;
+}
+
+void Graph::reserve_param_arena(int64_t total_elems) {
+  if (arena_w) invalid("reserve_param_arena: arena already reserved");
+  arena_cap = (total_elems + 63) / 64 * 64;
+  cuck(cudaMalloc(&arena_w, (size_t)arena_cap * 4), "cudaMalloc(param arena)");
+  cuck(cudaMalloc(&arena_g, (size_t)arena_cap * 4), "cudaMalloc(grad arena)");
+  cuck(cudaMemsetAsync(arena_w, 0, (size_t)arena_cap * 4, stream), "memset");
+  cuck(cudaMemsetAsync(arena_g, 0, (size_t)arena_cap * 4, stream), "memset");
+  if (precision == Precision::Bf16Mixed) {
+    cuck(cudaMalloc(&arena_shadow, (size_t)arena_cap * 2), "cudaMalloc(shadow arena)");
+    cuck(cudaMemsetAsync(arena_shadow, 0, (size_t)arena_cap * 2, stream), "memset");
+  }
+  device_bytes_allocated += (size_t)arena_cap * (precision == Precision::Bf16Mixed ? 10 : 8);
+}
+
+// src/graph/mod.rs `alloc`: a leaf with host data and a zero gradient.  Leaves created before
+// mark_params() are parameters (f32 master data, f32 gradient, bf16 shadow in Bf16Mixed);
+// later leaves are inputs (their gradient has the activation dtype).
+int64_t Graph::alloc(const std::vector<int64_t>& shape, const float* host) {
+  HTensor t;
+  t.shape = shape;
+  t.numel = numel_of(shape);
+  t.dtype = 0;
+  const bool param = (num_params == 0);
+  t.is_param = param;
+  const size_t n = (size_t)std::max<int64_t>(t.numel, 1);
+  const int64_t padded = (t.numel + 63) / 64 * 64;
+  const bool in_arena = param && arena_w && arena_used + padded <= arena_cap;
+  if (in_arena) {
+    t.data = arena_w + arena_used;
+    t.grad = arena_g + arena_used;
+    t.grad_dtype = 0;
+    if (arena_shadow) t.shadow = static_cast<uint16_t*>(arena_shadow) + arena_used;
+    arena_used += padded;
+  } else {
+    cuck(cudaMalloc(&t.data, round256(n * 4)), "cudaMalloc(leaf)");
+    t.owns_data = true;
+    t.grad_dtype = param ? 0 : act_dtype();
+    cuck(cudaMalloc(&t.grad, round256(n * dsize(t.grad_dtype))), "cudaMalloc(leaf grad)");
+    t.owns_grad = true;
+    cuck(cudaMemsetAsync(t.grad, 0, n * dsize(t.grad_dtype), stream), "memset(leaf grad)");
+    if (precision == Precision::Bf16Mixed) cuck(cudaMalloc(&t.shadow, round256(n * 2)), "cudaMalloc(leaf shadow)");
+    device_bytes_allocated += round256(n * 4) * 2;
+  }
+  t.grad_init = true;  // zero-initialised: every writer accumulates
+  int64_t id = new_tensor(std::move(t));
+  if (host) load_tensor_data(id, host, tensors[id].numel);
+  return id;
+}
+
+// token ids as device int32 (the reference keeps them in an f32 tensor, tests/phase2_embedding.rs:16-17)
+int64_t Graph::alloc_ids(const std::vector<int64_t>& shape, const int32_t* host_ids, bool async_pinned) {
+  HTensor t;
+  t.shape = shape;
+  t.numel = numel_of(shape);
+  t.dtype = DT_I32;
+  t.constant = true;
+  t.is_pooled = true;
+  t.data = pool_get((size_t)t.numel * 4);
+  // stream-ordered copy; for pageable memory the runtime stages the source before returning, so
+  // the caller's buffer may be reused at once either way
+  (void)async_pinned;
+  cuck(cudaMemcpyAsync(t.data, host_ids, (size_t)t.numel * 4, cudaMemcpyHostToDevice, stream), "H2D(ids)");
+  return new_tensor(std::move(t));
+}
+
+int64_t Graph::alloc_pooled_dtype(const std::vector<int64_t>& shape, int dtype) {
+  HTensor t;
+  t.shape = shape;
+  t.numel = numel_of(shape);
+  t.dtype = dtype;
+  t.grad_dtype = dtype;
+  t.is_pooled = true;
+  t.data = pool_get((size_t)std::max<int64_t>(t.numel, 1) * dsize(dtype));
+  return new_tensor(std::move(t));
+}
+int64_t Graph::alloc_pooled(const std::vector<int64_t>& shape) { return alloc_pooled_dtype(shape, act_dtype()); }
+
+// src/graph/mod.rs:368-430.  bf16 copies are rounded to nearest (the reference truncates on the
+// host, src/tensor.rs:7-9; not reproduced).
+void Graph::load_tensor_data(int64_t id, const float* host, int64_t n) {
+  HTensor& t = tensors.at(id);
+  if (n != t.numel) invalid("load_tensor_data: element count does not match the tensor shape");
+  if (t.dtype == 0) {
+    cuck(cudaMemcpyAsync(t.data, host, (size_t)n * 4, cudaMemcpyHostToDevice, stream), "H2D");
+    if (t.shadow) ck(eisen_cast(stream, t.data, 0, t.shadow, 1, n), "cast(shadow)");
+    cuck(cudaStreamSynchronize(stream), "sync");
+  } else if (t.dtype == 1) {
+    float* tmp = static_cast<float*>(pool_get((size_t)n * 4));
+    cuck(cudaMemcpyAsync(tmp, host, (size_t)n * 4, cudaMemcpyHostToDevice, stream), "H2D");
+    ck(eisen_cast(stream, tmp, 0, t.data, 1, n), "cast");
+    cuck(cudaStreamSynchronize(stream), "sync");
+    pool_put(tmp, (size_t)n * 4);
+  } else {
+    invalid("load_tensor_data: id tensors are loaded with alloc_ids");
+  }
+}
+
+static void read_back(Graph& g, const void* dev, int dt, int64_t n, float* out) {
+  if (dt == 0) {
+    cuck(cudaMemcpyAsync(out, dev, (size_t)n * 4, cudaMemcpyDeviceToHost, g.stream), "D2H");
+    cuck(cudaStreamSynchronize(g.stream), "sync");
+  } else {
+    float* tmp = static_cast<float*>(g.pool_get((size_t)n * 4));
+    ck(eisen_cast(g.stream, dev, 1, tmp, 0, n), "cast");
+    cuck(cudaMemcpyAsync(out, tmp, (size_t)n * 4, cudaMemcpyDeviceToHost, g.stream), "D2H");
+    cuck(cudaStreamSynchronize(g.stream), "sync");
+    g.pool_put(tmp, (size_t)n * 4);
+  }
+  g.check_status();
+}
+
+void Graph::sync_to_cpu(int64_t id, float* out) {
+  HTensor& t = tensors.at(id);
+  if (t.dtype == DT_I32) invalid("sync_to_cpu: id tensor");
+  read_back(*this, t.data, t.dtype, t.numel, out);
+}
+void Graph::sync_grad_to_cpu(int64_t id, float* out) {
+  HTensor& t = tensors.at(id);
+  if (!t.grad || !t.grad_init) {
+    std::fill(out, out + t.numel, 0.0f);
+    return;
+  }
+  read_back(*this, t.grad, t.grad_dtype, t.numel, out);
+}
+
+void Graph::synchronize() {
+  cuck(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+  check_status();
+}
+
+void Graph::check_status() {
+  int h[32] = {0};
+  cuck(cudaMemcpy(h, status_dev, sizeof(h), cudaMemcpyDeviceToHost), "read status");
+  if (h[0] != 0) {
+    cudaMemset(status_dev, 0, 4);
+    throw EisenException(EISEN_ERR_KERNEL, "a tensor-core kernel gave up on a bounded wait (fault code " + std::to_string(h[0]) + ")");
+  }
+  if (h[16] != 0) {
+    cudaMemset(bad_id_dev, 0, 4);
+    throw EisenException(EISEN_ERR_INVALID, "gather: a token id is outside [0, vocab)");
+  }
+}
+
+void Graph::restore_save_point(int64_t sp) {
+  while ((int64_t)tensors.size() > sp) {
+    free_tensor(tensors.back());
+    tensors.pop_back();
+  }
+}
+void Graph::clear_activations() {
+  tape.clear();
+  restore_save_point(num_params);
+}
+void Graph::reinterpret_shape(int64_t id, const std::vector<int64_t>& shape) {
+  HTensor& t = tensors.at(id);
+  if (numel_of(shape) != t.numel) invalid("reinterpret_shape: element count changes");
+  t.shape = shape;
+}
+void Graph::zero_grad(int64_t id) {
+  HTensor& t = tensors.at(id);
+  if (t.grad) {
+    cuck(cudaMemsetAsync(t.grad, 0, (size_t)t.numel * dsize(t.grad_dtype), stream), "memset(grad)");
+    t.grad_init = true;
+  }
+}
+
+void Graph::ensure_grad(int64_t id) {
+  HTensor& t = tensors.at(id);
+  if (t.grad) return;
+  if (t.constant) invalid("ensure_grad: constant tensor");
+  t.grad = pool_get((size_t)std::max<int64_t>(t.numel, 1) * dsize(t.grad_dtype));
+  t.grad_init = false;
+  if (!t.is_pooled) t.owns_grad = false;  // returned through the pool only for pooled tensors
+}
+
+void Graph::seed_grad_ones(int64_t id) {
+  ensure_grad(id);
+  HTensor& t = tensors.at(id);
+  if (t.grad_dtype == 0) {
+    ck(eisen_fill_f32(stream, static_cast<float*>(t.grad), 1.0f, t.numel), "fill");
+  } else {
+    float* tmp = static_cast<float*>(pool_get((size_t)t.numel * 4));
+    ck(eisen_fill_f32(stream, tmp, 1.0f, t.numel), "fill");
+    ck(eisen_cast(stream, tmp, 0, t.grad, 1, t.numel), "cast");
+    pool_put(tmp, (size_t)t.numel * 4);  // stream-ordered reuse
+  }
+  t.grad_init = true;
+}
+
+// src/graph/mod.rs:670-796: seed with ones, walk the tape in reverse, keep the nodes
+void Graph::backward(int64_t loss_id) {
+  if (no_grad) return;
+  seed_grad_ones(loss_id);
+  backward_from(0);
+}
+void Graph::backward_from(int64_t begin) {
+  for (int64_t i = (int64_t)tape.size(); i-- > begin;) tape[i].backward();
+}
+
+const void* Graph::operand(const HTensor& t) const {
+  if (precision == Precision::Bf16Mixed && t.dtype == 0) {
+    if (!t.shadow) throw EisenException(EISEN_ERR_INVALID, "f32 tensor without a bf16 shadow used in Bf16Mixed mode");
+    return t.shadow;
+  }
+  return t.data;
+}
+
+const float* Graph::rope_table(int64_t S, int64_t hd) {
+  const int64_t key = S * 100000 + hd;
+  auto it = rope_tables_.find(key);
+  if (it != rope_tables_.end()) return it->second;
+  float* tab = nullptr;
+  cuck(cudaMalloc(&tab, (size_t)S * (hd / 2) * 8), "cudaMalloc(rope table)");
+  ck(eisen_rope_table(stream, tab, S, hd, 10000.0f), "rope_table");
+  rope_tables_[key] = tab;
+  return tab;
+}
+
+// helper: true if the output carries a gradient worth propagating
+#define OUT_GRAD_OR_RETURN(o)                         \
+  HTensor& to = tensors[o];                           \
+  if (!to.grad || !to.grad_init) return;
+
+// ------------------------------------------------------------------------------------- elementwise
+// src/graph/ops/elementwise.rs:7-186 — b may broadcast over leading dims (bias, [1,S,S] mask)
+int64_t Graph::add(int64_t a, int64_t b) {
+  const HTensor& ta = tensors.at(a);
+  const HTensor& tb = tensors.at(b);
+  if (tb.numel == 0 || ta.numel % tb.numel) invalid("add: rhs must match or broadcast over leading dims");
+  const int dt = act_dtype();
+  const int64_t n = ta.numel, bn = tb.numel;
+  int64_t o = alloc_pooled(ta.shape);
+  ck(eisen_add(stream, operand(tensors[a]), operand(tensors[b]), tensors[o].data, n, bn, dt), "add");
+  if (!no_grad) {
+    tape.push_back({{a, b}, o, [this, a, b, o, n, bn]() {
+      OUT_GRAD_OR_RETURN(o);
+      HTensor& ga = tensors[a];
+      if (!ga.constant) {
+        ensure_grad(a);
+        ck(eisen_accumulate(stream, ga.grad, ga.grad_dtype, to.grad, to.grad_dtype, n, ga.grad_init), "add.bwd(a)");
+        ga.grad_init = true;
+      }
+      HTensor& gb = tensors[b];
+      if (!gb.constant) {
+        ensure_grad(b);
+        if (bn == n) {
+          ck(eisen_accumulate(stream, gb.grad, gb.grad_dtype, to.grad, to.grad_dtype, n, gb.grad_init), "add.bwd(b)");
+        } else {
+          if (gb.grad_dtype != 0) invalid("add: broadcast operand needs an f32 gradient");
+          ck(eisen_reduce_leading(stream, to.grad, to.grad_dtype, static_cast<float*>(gb.grad), n, bn, gb.grad_init), "add.bwd(b)");
+        }
+        gb.grad_init = true;
+      }
+    }});
+  }
+  return o;
+}
+
+// src/graph/ops/elementwise.rs:188-334 (no broadcast)
+int64_t Graph::mul(int64_t a, int64_t b) {
+  const HTensor& ta = tensors.at(a);
+  if (ta.numel != tensors.at(b).numel) invalid("mul: shapes differ");
+  const int dt = act_dtype();
+  const int64_t n = ta.numel;
+  int64_t o = alloc_pooled(ta.shape);
+  ck(eisen_mul_fwd(stream, operand(tensors[a]), operand(tensors[b]), tensors[o].data, n, dt), "mul");
+  if (!no_grad) {
+    tape.push_back({{a, b}, o, [this, a, b, o, n, dt]() {
+      OUT_GRAD_OR_RETURN(o);
+      HTensor& ga = tensors[a];
+      HTensor& gb = tensors[b];
+      void* da = nullptr;
+      void* db = nullptr;
+      if (!ga.constant) { ensure_grad(a); da = ga.grad; }
+      if (!gb.constant) { ensure_grad(b); db = gb.grad; }
+      if ((da && ga.grad_dtype != dt) || (db && gb.grad_dtype != dt)) invalid("mul: gradient dtype differs from the activation dtype");
+      ck(eisen_mul_bwd(stream, operand(ga), operand(gb), to.grad, da, db, n, dt, ga.grad_init, gb.grad_init), "mul.bwd");
+      if (da) ga.grad_init = true;
+      if (db) gb.grad_init = true;
+    }});
+  }
+  return o;
+}
+
+// src/graph/ops/elementwise.rs:337-467
+int64_t Graph::silu(int64_t a) {
+  const int dt = act_dtype();
+  const int64_t n = tensors.at(a).numel;
+  int64_t o = alloc_pooled(tensors[a].shape);
+  ck(eisen_silu_fwd(stream, operand(tensors[a]), tensors[o].data, n, dt), "silu");
+  if (!no_grad) {
+    tape.push_back({{a}, o, [this, a, o, n, dt]() {
+      OUT_GRAD_OR_RETURN(o);
+      HTensor& ga = tensors[a];
+      ensure_grad(a);
+      ck(eisen_silu_bwd(stream, operand(ga), to.grad, ga.grad, n, dt, ga.grad_init), "silu.bwd");
+      ga.grad_init = true;
+    }});
+  }
+  return o;
+}
+
+// silu(gate) * up in one pass each way (src/nn/transformer.rs:41-44 uses silu + mul)
+int64_t Graph::swiglu(int64_t gate, int64_t up) {
+  const int dt = act_dtype();
+  const int64_t n = tensors.at(gate).numel;
+  if (tensors.at(up).numel != n) invalid("swiglu: shapes differ");
+  int64_t o = alloc_pooled(tensors[gate].shape);
+  ck(eisen_swiglu_fwd(stream, operand(tensors[gate]), operand(tensors[up]), tensors[o].data, n, dt), "swiglu");
+  if (!no_grad) {
+    tape.push_back({{gate, up}, o, [this, gate, up, o, n, dt]() {
+      OUT_GRAD_OR_RETURN(o);
+      HTensor& gg = tensors[gate];
+      HTensor& gu = tensors[up];
+      ensure_grad(gate);
+      ensure_grad(up);
+      if (gg.grad_init != gu.grad_init) invalid("swiglu: gate and up gradients must both be fresh or both initialised");
+      ck(eisen_swiglu_bwd(stream, operand(gg), operand(gu), to.grad, gg.grad, gu.grad, n, dt, gg.grad_init), "swiglu.bwd");
+      gg.grad_init = gu.grad_init = true;
+    }});
+  }
+  return o;
+}
+
+// ------------------------------------------------------------------------------------- contractions
+namespace {
+// C[m,n] (op)= A(m,k) B(n,k) with per-operand major, dispatched on the graph precision.
+// a_mn / b_mn as in eisen_gemm_bf16; strides are the row lengths of the stored matrices.
+void gemm(Graph& g, bool a_mn, bool b_mn, int64_t M, int64_t N, int64_t K, const void* A, const void* B, void* C,
+          int c_dtype, bool accumulate) {
+  if (g.precision == Precision::Fp32) {
+    const int64_t a_ms = a_mn ? 1 : K, a_ks = a_mn ? M : 1;
+    const int64_t b_ns = b_mn ? 1 : K, b_ks = b_mn ? N : 1;
+    ck(eisen_gemm_f32_strided(g.stream, (const float*)A, (const float*)B, (float*)C, 1, M, N, K, 0, a_ms, a_ks, 0,
+                              b_ks, b_ns, 0, N, accumulate),
+       "gemm_f32");
+    return;
+  }
+  const int64_t lda = a_mn ? M : K, ldb = b_mn ? N : K;
+  int mode;
+  if (c_dtype == 1) mode = accumulate ? 1 : 0;
+  else mode = accumulate ? 4 : 2;  // f32 accumulation goes through red.global.add with automatic split-K
+  ck(eisen_gemm_bf16(g.stream, a_mn, b_mn, M, N, K, A, lda, B, ldb, C, N, mode, mode == 4 ? 0 : 1, 1.0f, g.status_dev),
+     "gemm_bf16");
+}
+}  // namespace
+
+// src/graph/ops/linear.rs:35-299 (f32) and 526-770 (bf16 operands): C[m,n] = A[m,k] B[k,n]
+int64_t Graph::matmul(int64_t a, int64_t b) {
+  const HTensor& ta = tensors.at(a);
+  const HTensor& tb = tensors.at(b);
+  if (ta.shape.size() < 2) invalid("matmul: lhs must have rank >= 2");
+  if (tb.shape.size() != 2) invalid("matmul: rhs must have rank 2 [k, n]");
+  const int64_t k = ta.shape.back(), m = ta.numel / k, n = tb.shape[1];
+  if (tb.shape[0] != k) invalid("matmul: lhs last dim must equal rhs first dim");
+  int64_t o = alloc_pooled({m, n});
+  gemm(*this, false, true, m, n, k, operand(tensors[a]), operand(tensors[b]), tensors[o].data, act_dtype(), false);
+  if (!no_grad) {
+    tape.push_back({{a, b}, o, [this, a, b, o, m, n, k]() {
+      OUT_GRAD_OR_RETURN(o);
+      HTensor& ga = tensors[a];
+      HTensor& gb = tensors[b];
+      if (!ga.constant) {  // dA[m,k] (+)= dC[m,n] B[k,n]^T
+        ensure_grad(a);
+        gemm(*this, false, false, m, k, n, to.grad, operand(gb), ga.grad, ga.grad_dtype, ga.grad_init);
+        ga.grad_init = true;
+      }
+      if (!gb.constant) {  // dB[k,n] (+)= A[m,k]^T dC[m,n]
+        ensure_grad(b);
+        gemm(*this, true, true, k, n, m, operand(ga), to.grad, gb.grad, gb.grad_dtype, gb.grad_init);
+        gb.grad_init = true;
+      }
+    }});
+  }
+  return o;
+}
+
+// src/graph/ops/linear.rs:301-523 (tied LM head): C[m,n] = A[m,k] B[n,k]^T
+int64_t Graph::matmul_trans_b(int64_t a, int64_t b) {
+  const HTensor& ta = tensors.at(a);
+  const HTensor& tb = tensors.at(b);
+  if (tb.shape.size() != 2) invalid("matmul_trans_b: rhs must have rank 2 [n, k]");
+  const int64_t k = ta.shape.back(), m = ta.numel / k, n = tb.shape[0];
+  if (tb.shape[1] != k) invalid("matmul_trans_b: inner dims differ");
+  int64_t o = alloc_pooled({m, n});
+  gemm(*this, false, false, m, n, k, operand(tensors[a]), operand(tensors[b]), tensors[o].data, act_dtype(), false);
+  if (!no_grad) {
+    tape.push_back({{a, b}, o, [this, a, b, o, m, n, k]() {
+      OUT_GRAD_OR_RETURN(o);
+      HTensor& ga = tensors[a];
+      HTensor& gb = tensors[b];
+      if (!ga.constant) {  // dA[m,k] (+)= dC[m,n] B[n,k]
+        ensure_grad(a);
+        gemm(*this, false, true, m, k, n, to.grad, operand(gb), ga.grad, ga.grad_dtype, ga.grad_init);
+        ga.grad_init = true;
+      }
+      if (!gb.constant) {  // dB[n,k] (+)= dC[m,n]^T A[m,k]
+        ensure_grad(b);
+        gemm(*this, true, true, n, k, m, to.grad, operand(ga), gb.grad, gb.grad_dtype, gb.grad_init);
+        gb.grad_init = true;
+      }
+    }});
+  }
+  return o;
+}
+
+// src/graph/ops/linear.rs:1198-1512; f32 only (the bf16 path uses the fused attention op)
+int64_t Graph::bmm(int64_t a, int64_t b, bool trans_b) {
+  if (precision != Precision::Fp32) invalid("bmm: only the Fp32 graph materialises attention scores; use attention()");
+  const HTensor& ta = tensors.at(a);
+  const HTensor& tb = tensors.at(b);
+  if (ta.shape.size() != 3 || tb.shape.size() != 3) invalid("bmm: operands must be [batch, m, k]");
+  const int64_t batch = ta.shape[0], m = ta.shape[1], k = ta.shape[2];
+  const int64_t n = trans_b ? tb.shape[1] : tb.shape[2];
+  if (tb.shape[0] != batch || (trans_b ? tb.shape[2] : tb.shape[1]) != k) invalid("bmm: shape mismatch");
+  int64_t o = alloc_pooled({batch, m, n});
+  const int64_t b_ks = trans_b ? 1 : n, b_ns = trans_b ? k : 1;
+  ck(eisen_gemm_f32_strided(stream, (const float*)tensors[a].data, (const float*)tensors[b].data, (float*)tensors[o].data,
+                            batch, m, n, k, m * k, k, 1, k * n, b_ks, b_ns, m * n, n, 0),
+     "bmm");
+  if (!no_grad) {
+    tape.push_back({{a, b}, o, [this, a, b, o, batch, m, n, k, trans_b, b_ks, b_ns]() {
+      OUT_GRAD_OR_RETURN(o);
+      HTensor& ga = tensors[a];
+      HTensor& gb = tensors[b];
+      const float* dC = (const float*)to.grad;
+      if (!ga.constant) {  // dA[b,m,k] (+)= sum_n dC[b,m,n] B(b,k,n)
+        ensure_grad(a);
+        ck(eisen_gemm_f32_strided(stream, dC, (const float*)gb.data, (float*)ga.grad, batch, m, k, n, m * n, n, 1, k * n,
+                                  b_ns, b_ks, m * k, k, ga.grad_init),
+           "bmm.bwd(a)");
+        ga.grad_init = true;
+      }
+      if (!gb.constant) {
+        ensure_grad(b);
+        if (trans_b) {  // dB[b,n,k] (+)= sum_m dC[b,m,n] A[b,m,k]
+          ck(eisen_gemm_f32_strided(stream, dC, (const float*)ga.data, (float*)gb.grad, batch, n, k, m, m * n, 1, n, m * k,
+                                    k, 1, n * k, k, gb.grad_init),
+             "bmm.bwd(b)");
+        } else {        // dB[b,k,n] (+)= sum_m A[b,m,k] dC[b,m,n]
+          ck(eisen_gemm_f32_strided(stream, (const float*)ga.data, dC, (float*)gb.grad, batch, k, n, m, m * k, 1, k, m * n,
+                                    n, 1, k * n, n, gb.grad_init),
+             "bmm.bwd(b)");
+        }
+        gb.grad_init = true;
+      }
+    }});
+  }
+  return o;
+}
+
+// ------------------------------------------------------------------------------------- row ops
+// src/graph/ops/reduction.rs:397-526
+int64_t Graph::softmax(int64_t a) {
+  const HTensor& ta = tensors.at(a);
+  const int dt = act_dtype();
+  const int64_t n = ta.shape.back(), rows = ta.numel / n;
+  int64_t o = alloc_pooled(ta.shape);
+  ck(eisen_softmax_fwd(stream, operand(tensors[a]), tensors[o].data, rows, n, dt), "softmax");
+  if (!no_grad) {
+    tape.push_back({{a}, o, [this, a, o, rows, n, dt]() {
+      OUT_GRAD_OR_RETURN(o);
+      HTensor& ga = tensors[a];
+      ensure_grad(a);
+      ck(eisen_softmax_bwd(stream, to.data, to.grad, ga.grad, rows, n, dt, ga.grad_init), "softmax.bwd");
+      ga.grad_init = true;
+    }});
+  }
+  return o;
+}
+
+int64_t Graph::ce_impl(int64_t logits, const int64_t* targets, int64_t n, bool masked, float normalizer) {
+  const HTensor& tl = tensors.at(logits);
+  if (tl.shape.size() != 2 || tl.shape[0] != n) invalid("cross_entropy: logits must be [rows, classes] with one target per row");
+  const int64_t rows = tl.shape[0], vocab = tl.shape[1];
+  const int dt = act_dtype();
+  // targets -> device int32; IGNORE_INDEX (usize::MAX in the reference, any negative value here) -> -1
+  std::vector<int32_t> h((size_t)rows);
+  for (int64_t i = 0; i < rows; ++i) {
+    if (targets[i] < 0) h[i] = -1;
+    else if (targets[i] >= vocab) invalid("cross_entropy: target out of range");
+    else h[i] = (int32_t)targets[i];
+  }
+  int64_t tid = alloc_ids({rows}, h.data(), false);
+  int64_t lse = alloc_pooled_dtype({rows}, 0);
+  int64_t row_loss = alloc_pooled_dtype({rows}, 0);
+  int64_t o = alloc_pooled_dtype({}, 0);
+  tensors[lse].constant = tensors[row_loss].constant = true;
+  ck(eisen_ce_fwd(stream, operand(tensors[logits]), (const int*)tensors[tid].data, (float*)tensors[o].data,
+                  (float*)tensors[row_loss].data, (float*)tensors[lse].data, rows, vocab, -1, normalizer, dt),
+     "cross_entropy");
+  (void)masked;
+  if (!no_grad) {
+    tape.push_back({{logits}, o, [this, logits, tid, lse, o, rows, vocab, normalizer, dt]() {
+      OUT_GRAD_OR_RETURN(o);
+      HTensor& gl = tensors[logits];
+      ensure_grad(logits);
+      ck(eisen_ce_bwd(stream, operand(gl), (const int*)tensors[tid].data, (const float*)tensors[lse].data, gl.grad,
+                      (const float*)to.grad, rows, vocab, -1, normalizer, dt, gl.grad_init),
+         "cross_entropy.bwd");
+      gl.grad_init = true;
+    }});
+  }
+  return o;
+}
+
+// src/graph/ops/reduction.rs:529-719: mean over rows of -ln(p_target + 1e-8)
+int64_t Graph::cross_entropy(int64_t logits, const int64_t* targets, int64_t n) {
+  for (int64_t i = 0; i < n; ++i)
+    if (targets[i] < 0) invalid("cross_entropy: negative target (use cross_entropy_masked for ignored rows)");
+  return ce_impl(logits, targets, n, false, 1.0f / (float)n);
+}
+
+// src/graph/ops/reduction.rs:724-737: plain CE when nothing is masked, constant 0 when all is
+int64_t Graph::cross_entropy_masked(int64_t logits, const int64_t* targets, int64_t n) {
+  int64_t valid = 0;
+  for (int64_t i = 0; i < n; ++i) valid += (targets[i] >= 0);
+  if (valid == n) return cross_entropy(logits, targets, n);
+  if (valid == 0) {
+    int64_t o = alloc_pooled_dtype({}, 0);
+    cuck(cudaMemsetAsync(tensors[o].data, 0, 4, stream), "memset");
+    return o;
+  }
+  return ce_impl(logits, targets, n, true, 1.0f / (float)valid);
+}
+
+// src/graph/ops/normalization.rs:8-183
+int64_t Graph::rms_norm(int64_t x, int64_t w, float eps) {
+  const HTensor& tx = tensors.at(x);
+  const HTensor& tw = tensors.at(w);
+  const int64_t dim = tx.shape.back(), rows = tx.numel / dim;
+  if (tw.numel != dim || tw.dtype != 0) invalid("rms_norm: weight must be an f32 vector of the last dimension");
+  const int dt = act_dtype();
+  int64_t o = alloc_pooled(tx.shape);
+  ck(eisen_rmsnorm_fwd(stream, operand(tensors[x]), (const float*)tw.data, tensors[o].data, nullptr, rows, dim, eps, dt),
+     "rms_norm");
+  if (!no_grad) {
+    tape.push_back({{x, w}, o, [this, x, w, o, rows, dim, eps, dt]() {
+      OUT_GRAD_OR_RETURN(o);
+      HTensor& gx = tensors[x];
+      HTensor& gw = tensors[w];
+      ensure_grad(x);
+      ensure_grad(w);
+      if (!gw.grad_init) { cuck(cudaMemsetAsync(gw.grad, 0, (size_t)dim * 4, stream), "memset"); gw.grad_init = true; }
+      void* ws = scratch((size_t)eisen_rmsnorm_bwd_workspace_bytes(rows, dim));
+      ck(eisen_rmsnorm_bwd(stream, operand(gx), (const float*)gw.data, to.grad, gx.grad, (float*)gw.grad, ws, rows, dim,
+                           eps, dt, gx.grad_init),
+         "rms_norm.bwd");
+      gx.grad_init = true;
+    }});
+  }
+  return o;
+}
+
+// src/graph/ops/transform.rs:467-612
+int64_t Graph::rope(int64_t a, int64_t head_dim) {
+  const HTensor& ta = tensors.at(a);
+  if (ta.shape.size() != 3) invalid("rope: expects [batch, seq, hidden]");
+  const int64_t B = ta.shape[0], S = ta.shape[1], H = ta.shape[2];
+  const int dt = act_dtype();
+  const float* tab = rope_table(S, head_dim);
+  int64_t o = alloc_pooled(ta.shape);
+  ck(eisen_rope(stream, operand(tensors[a]), tensors[o].data, tab, B, S, H, head_dim, dt, 0, 0), "rope");
+  if (!no_grad) {
+    tape.push_back({{a}, o, [this, a, o, B, S, H, head_dim, dt, tab]() {
+      OUT_GRAD_OR_RETURN(o);
+      HTensor& ga = tensors[a];
+      ensure_grad(a);
+      ck(eisen_rope(stream, to.grad, ga.grad, tab, B, S, H, head_dim, dt, 1, ga.grad_init), "rope.bwd");
+      ga.grad_init = true;
+    }});
+  }
+  return o;
+}
+
+// src/graph/ops/transform.rs:132-326.  idx is an id tensor (alloc_ids) or, as in the reference,
+// an f32 tensor of integral values (converted exactly on the host; not a hot path).
+int64_t Graph::gather(int64_t w, int64_t idx) {
+  const HTensor& tw = tensors.at(w);
+  if (tw.shape.size() != 2) invalid("gather: weights must be [vocab, dim]");
+  const int64_t vocab = tw.shape[0], dim = tw.shape[1];
+  int64_t ids = idx;
+  if (tensors.at(idx).dtype != DT_I32) {
+    const HTensor& ti = tensors[idx];
+    std::vector<float> hf((size_t)ti.numel);
+    cuck(cudaMemcpyAsync(hf.data(), ti.data, (size_t)ti.numel * 4, cudaMemcpyDeviceToHost, stream), "D2H(ids)");
+    cuck(cudaStreamSynchronize(stream), "sync");
+    std::vector<int32_t> hi((size_t)ti.numel);
+    for (size_t i = 0; i < hi.size(); ++i) hi[i] = (int32_t)hf[i];
+    const std::vector<int64_t> shp = ti.shape;
+    ids = alloc_ids(shp, hi.data(), false);
+  }
+  const int64_t n = tensors[ids].numel;
+  std::vector<int64_t> os = tensors[ids].shape;
+  os.push_back(dim);
+  const int dt = act_dtype();
+  int64_t o = alloc_pooled(os);
+  ck(eisen_embedding_fwd(stream, operand(tensors[w]), dt, (const int*)tensors[ids].data, tensors[o].data, dt, n, dim,
+                         vocab, bad_id_dev),
+     "gather");
+  if (!no_grad) {
+    tape.push_back({{w, idx}, o, [this, w, ids, o, n, dim, vocab]() {
+      OUT_GRAD_OR_RETURN(o);
+      HTensor& gw = tensors[w];
+      ensure_grad(w);
+      if (gw.grad_dtype != 0) invalid("gather: the table gradient must be f32");
+      if (!gw.grad_init) { cuck(cudaMemsetAsync(gw.grad, 0, (size_t)gw.numel * 4, stream), "memset"); gw.grad_init = true; }
+      void* ws = scratch((size_t)eisen_embedding_bwd_workspace_bytes(n, vocab));
+      ck(eisen_embedding_bwd(stream, to.grad, to.grad_dtype, (const int*)tensors[ids].data, (float*)gw.grad, ws, n, dim, vocab),
+         "gather.bwd");
+    }});
+  }
+  return o;
+}
+
+// src/graph/ops/transform.rs:329-409: a physical copy whose backward accumulates
+int64_t Graph::reshape(int64_t a, const std::vector<int64_t>& shape) {
+  const HTensor& ta = tensors.at(a);
+  if (numel_of(shape) != ta.numel) invalid("reshape: element count changes");
+  const int dt = act_dtype();
+  const int64_t n = ta.numel;
+  int64_t o = alloc_pooled(shape);
+  ck(eisen_cast(stream, operand(tensors[a]), dt, tensors[o].data, dt, n), "reshape");
+  if (!no_grad) {
+    tape.push_back({{a}, o, [this, a, o, n]() {
+      OUT_GRAD_OR_RETURN(o);
+      HTensor& ga = tensors[a];
+      ensure_grad(a);
+      ck(eisen_accumulate(stream, ga.grad, ga.grad_dtype, to.grad, to.grad_dtype, n, ga.grad_init), "reshape.bwd");
+      ga.grad_init = true;
+    }});
+  }
+  return o;
+}
+
+// src/graph/ops/transform.rs:7-129
+int64_t Graph::transpose_0213(int64_t a) {
+  const HTensor& ta = tensors.at(a);
+  if (ta.shape.size() != 4) invalid("transpose_0213: expects a rank-4 tensor");
+  const int64_t B = ta.shape[0], S = ta.shape[1], H = ta.shape[2], D = ta.shape[3];
+  const int dt = act_dtype();
+  int64_t o = alloc_pooled({B, H, S, D});
+  ck(eisen_transpose_0213(stream, operand(tensors[a]), tensors[o].data, B, S, H, D, dt, 0), "transpose_0213");
+  if (!no_grad) {
+    tape.push_back({{a}, o, [this, a, o, B, S, H, D, dt]() {
+      OUT_GRAD_OR_RETURN(o);
+      HTensor& ga = tensors[a];
+      ensure_grad(a);
+      // the inverse permutation is the same kernel with S and H exchanged
+      ck(eisen_transpose_0213(stream, to.grad, ga.grad, B, H, S, D, dt, ga.grad_init), "transpose_0213.bwd");
+      ga.grad_init = true;
+    }});
+  }
+  return o;
+}
+
+// src/graph/ops/gqa.rs:13-196
+int64_t Graph::repeat_kv(int64_t a, int64_t repeats) {
+  if (repeats == 1) return a;  // gqa.rs:21-23
+  const HTensor& ta = tensors.at(a);
+  if (ta.shape.size() != 4) invalid("repeat_kv: expects [B, KV, S, D]");
+  const int64_t B = ta.shape[0], KV = ta.shape[1], S = ta.shape[2], D = ta.shape[3];
+  const int dt = act_dtype();
+  int64_t o = alloc_pooled({B, KV * repeats, S, D});
+  ck(eisen_repeat_kv_fwd(stream, operand(tensors[a]), tensors[o].data, B, KV, S, D, repeats, dt), "repeat_kv");
+  if (!no_grad) {
+    tape.push_back({{a}, o, [this, a, o, B, KV, S, D, repeats, dt]() {
+      OUT_GRAD_OR_RETURN(o);
+      HTensor& ga = tensors[a];
+      ensure_grad(a);
+      ck(eisen_repeat_kv_bwd(stream, to.grad, ga.grad, B, KV, S, D, repeats, dt, ga.grad_init), "repeat_kv.bwd");
+      ga.grad_init = true;
+    }});
+  }
+  return o;
+}
+
+// src/graph/ops/attention.rs:7-194: q [BH,M,D], k/v [BH,N,D], forward only (asserts no_grad)
+int64_t Graph::flash_attention(int64_t q, int64_t k, int64_t v, float scale, bool causal) {
+  if (!no_grad) invalid("flash_attention: forward only, set no_grad (as the reference asserts); training uses attention()");
+  const HTensor& tq = tensors.at(q);
+  const HTensor& tk = tensors.at(k);
+  if (tq.shape.size() != 3 || tk.shape.size() != 3) invalid("flash_attention: expects [batch*heads, seq, head_dim]");
+  const int64_t BH = tq.shape[0], S = tq.shape[1], D = tq.shape[2];
+  if (tk.shape[1] != S) invalid("flash_attention: query and key lengths must match");
+  int64_t o = alloc_pooled({BH, S, D});
+  if (precision == Precision::Bf16Mixed) {
+    // [BH,S,D] is the [B,S,H,D] layout with H = 1
+    ck(eisen_attn_fwd(stream, operand(tensors[q]), operand(tensors[k]), operand(tensors[v]), tensors[o].data, nullptr,
+                      BH, S, 1, 1, D, S * D, D, D, S * D, D, D, S * D, D, D, scale, causal, status_dev),
+       "flash_attention");
+    return o;
+  }
+  // Fp32: scores -> softmax -> PV with the f32 kernels (exactly the materialised chain)
+  float* sc = static_cast<float*>(pool_get((size_t)BH * S * S * 4));
+  float* pr = static_cast<float*>(pool_get((size_t)BH * S * S * 4));
+  ck(eisen_gemm_f32_strided(stream, (const float*)tensors[q].data, (const float*)tensors[k].data, sc, BH, S, S, D, S * D, D,
+                            1, S * D, 1, D, S * S, S, 0),
+     "flash.scores");
+  ck(eisen_scale_f32(stream, sc, scale, BH * S * S), "flash.scale");
+  if (causal) {
+    std::vector<float> m((size_t)S * S, 0.0f);
+    for (int64_t r = 0; r < S; ++r)
+      for (int64_t c = r + 1; c < S; ++c) m[r * S + c] = -1e20f;
+    float* md = static_cast<float*>(pool_get((size_t)S * S * 4));
+    cuck(cudaMemcpyAsync(md, m.data(), (size_t)S * S * 4, cudaMemcpyHostToDevice, stream), "H2D(mask)");
+    ck(eisen_add(stream, sc, md, sc, BH * S * S, S * S, 0), "flash.mask");
+    cuck(cudaStreamSynchronize(stream), "sync");
+    pool_put(md, (size_t)S * S * 4);
+  }
+  ck(eisen_softmax_fwd(stream, sc, pr, BH * S, S, 0), "flash.softmax");
+  ck(eisen_gemm_f32_strided(stream, pr, (const float*)tensors[v].data, (float*)tensors[o].data, BH, S, D, S, S * S, S, 1,
+                            S * D, D, 1, S * D, D, 0),
+     "flash.pv");
+  pool_put(sc, (size_t)BH * S * S * 4);
+  pool_put(pr, (size_t)BH * S * S * 4);
+  return o;
+}
+
+// Fused causal GQA attention on [B,S,H*D] projections (Bf16Mixed, D in {64,128}); replaces
+// reshape/transpose_0213/repeat_kv/bmm/mul/add/softmax/bmm/transpose/reshape of
+// src/nn/attention.rs:305-384 and their backward nodes.
+int64_t Graph::attention(int64_t q, int64_t k, int64_t v, int64_t Hq, int64_t Hkv, bool causal) {
+  if (precision != Precision::Bf16Mixed) invalid("attention: fused attention runs in Bf16Mixed mode");
+  const HTensor& tq = tensors.at(q);
+  const HTensor& tk = tensors.at(k);
+  if (tq.shape.size() != 3) invalid("attention: expects [B, S, heads*head_dim]");
+  const int64_t B = tq.shape[0], S = tq.shape[1], D = tq.shape[2] / Hq;
+  if (tk.shape[2] != Hkv * D) invalid("attention: k/v width must be kv_heads*head_dim");
+  const float scale = 1.0f / std::sqrt((float)D);
+  int64_t o = alloc_pooled(tq.shape);
+  int64_t lse = alloc_pooled_dtype({B, Hq, S}, 0);
+  tensors[lse].constant = true;
+  const int64_t qb = S * Hq * D, qs = Hq * D, kb = S * Hkv * D, ks = Hkv * D;
+  ck(eisen_attn_fwd(stream, operand(tensors[q]), operand(tensors[k]), operand(tensors[v]), tensors[o].data,
+                    (float*)tensors[lse].data, B, S, Hq, Hkv, D, qb, qs, D, kb, ks, D, qb, qs, D, scale, causal, status_dev),
+     "attention");
+  if (!no_grad) {
+    tape.push_back({{q, k, v}, o, [this, q, k, v, o, lse, B, S, Hq, Hkv, D, qb, qs, kb, ks, scale, causal]() {
+      OUT_GRAD_OR_RETURN(o);
+      HTensor* gt[3] = {&tensors[q], &tensors[k], &tensors[v]};
+      void* dst[3];
+      void* tmp[3] = {nullptr, nullptr, nullptr};
+      const int64_t ids[3] = {q, k, v};
+      for (int i = 0; i < 3; ++i) {
+        ensure_grad(ids[i]);
+        if (gt[i]->grad_dtype != 1) invalid("attention: gradients of q/k/v must be bf16");
+        if (gt[i]->grad_init) { tmp[i] = pool_get((size_t)gt[i]->numel * 2); dst[i] = tmp[i]; }
+        else dst[i] = gt[i]->grad;
+      }
+      void* ws = scratch((size_t)eisen_attn_bwd_workspace_bytes(B, S, Hq, Hkv, D));
+      ck(eisen_attn_bwd(stream, operand(*gt[0]), operand(*gt[1]), operand(*gt[2]), to.data, (const float*)tensors[lse].data,
+                        to.grad, dst[0], dst[1], dst[2], ws, B, S, Hq, Hkv, D, qb, qs, D, kb, ks, D, qb, qs, D, scale,
+                        causal, status_dev),
+         "attention.bwd");
+      for (int i = 0; i < 3; ++i) {
+        if (tmp[i]) {
+          ck(eisen_accumulate(stream, gt[i]->grad, 1, tmp[i], 1, gt[i]->numel, 1), "attention.bwd(acc)");
+          pool_put(tmp[i], (size_t)gt[i]->numel * 2);
+        }
+        gt[i]->grad_init = true;
+      }
+    }});
+  }
+  return o;
+}
+
+}  // namespace eisen

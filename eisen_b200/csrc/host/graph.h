@@ -1,0 +1,192 @@
+// Host-side mirror of the reference's Graph / Tape / Tensor (src/graph/mod.rs:56-78,
+// src/tape.rs:3-12, src/tensor.rs:19-44) with the `Device::Gpu` arms of its ops rebuilt on the
+// kernels of this library.  Tensor ids are indices into `tensors`, ops run the forward at once
+// and push a tape node (unless no_grad), `backward` walks the tape in reverse.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <functional>
+#include <stdexcept>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+namespace eisen {
+
+enum class Precision : int { Fp32 = 0, Bf16Mixed = 1 };  // src/graph/mod.rs PrecisionMode
+constexpr int DT_I32 = 2;                                 // token-id tensors (device int32)
+
+struct EisenException : std::runtime_error {
+  int code;
+  EisenException(int c, const std::string& m) : std::runtime_error(m), code(c) {}
+};
+
+struct HTensor {
+  std::vector<int64_t> shape;
+  int64_t numel = 0;
+  int dtype = 0;           // DT_F32 / DT_BF16 / DT_I32 of `data`
+  void* data = nullptr;
+  void* shadow = nullptr;  // bf16 copy of an f32 parameter (Bf16Mixed), refreshed by AdamW
+  void* grad = nullptr;
+  int grad_dtype = 0;
+  bool grad_init = false;  // false: grad holds garbage and stands for zero; first writer overwrites
+  bool is_pooled = false;  // activation: buffers return to the pool on restore_save_point
+  bool owns_data = false;  // free with cudaFree on destruction (non-pooled, non-arena)
+  bool owns_grad = false;
+  bool is_param = false;
+  bool constant = false;   // no gradient is ever formed (masks, scale tensors, ids)
+  std::string name;
+};
+
+struct HNode {
+  std::vector<int64_t> inputs;
+  int64_t output;
+  std::function<void()> backward;
+};
+
+class Graph {
+ public:
+  Graph(Precision prec, cudaStream_t stream);
+  ~Graph();
+
+  // ---- storage (src/graph/mod.rs: alloc, alloc_pooled 437-556, load_tensor_data 368-430)
+  int64_t alloc(const std::vector<int64_t>& shape, const float* host_data);  // f32 leaf / parameter
+  int64_t alloc_ids(const std::vector<int64_t>& shape, const int32_t* host_ids, bool host_is_pinned_async);
+  int64_t alloc_pooled(const std::vector<int64_t>& shape);                   // activation dtype
+  int64_t alloc_pooled_dtype(const std::vector<int64_t>& shape, int dtype);
+  void load_tensor_data(int64_t id, const float* host, int64_t n);
+  void sync_to_cpu(int64_t id, float* out);       // Tensor::sync_to_cpu
+  void sync_grad_to_cpu(int64_t id, float* out);  // Graph::sync_grad_to_cpu
+  void reserve_param_arena(int64_t total_elems);  // parameters allocated afterwards share flat buffers
+  void name_tensor(int64_t id, const std::string& n) { tensors.at(id).name = n; }
+
+  // ---- graph state (src/graph/mod.rs:328-365, 432-435)
+  void mark_params() { num_params = (int64_t)tensors.size(); }
+  int64_t mark_save_point() const { return (int64_t)tensors.size(); }
+  void restore_save_point(int64_t sp);
+  void clear_activations();
+  void reinterpret_shape(int64_t id, const std::vector<int64_t>& shape);
+  void zero_grad(int64_t id);
+  void backward(int64_t loss_id);
+  void backward_from(int64_t tape_begin);  // walks nodes [tape_begin, end) in reverse, no seeding
+  void seed_grad_ones(int64_t id);
+  void synchronize();
+  void check_status();                      // raises if a kernel recorded a fault
+
+  // ---- ops (src/graph/ops/*.rs)
+  int64_t add(int64_t a, int64_t b);
+  int64_t mul(int64_t a, int64_t b);
+  int64_t silu(int64_t a);
+  int64_t swiglu(int64_t gate, int64_t up);
+  int64_t matmul(int64_t a, int64_t b);
+  int64_t matmul_trans_b(int64_t a, int64_t b);
+  int64_t bmm(int64_t a, int64_t b, bool trans_b);
+  int64_t softmax(int64_t a);
+  int64_t cross_entropy(int64_t logits, const int64_t* targets, int64_t n);
+  int64_t cross_entropy_masked(int64_t logits, const int64_t* targets, int64_t n);
+  int64_t rms_norm(int64_t x, int64_t w, float eps);
+  int64_t rope(int64_t a, int64_t head_dim);
+  int64_t gather(int64_t w, int64_t idx);
+  int64_t reshape(int64_t a, const std::vector<int64_t>& shape);
+  int64_t transpose_0213(int64_t a);
+  int64_t repeat_kv(int64_t a, int64_t repeats);
+  int64_t flash_attention(int64_t q, int64_t k, int64_t v, float scale, bool causal);  // [BH,S,D], forward only
+  // fused GQA attention on the projections' [B,S,H*D] outputs, with backward
+  int64_t attention(int64_t q, int64_t k, int64_t v, int64_t num_heads, int64_t num_kv_heads, bool causal);
+
+  // ---- helpers used by modules / optimizer
+  int act_dtype() const { return precision == Precision::Bf16Mixed ? 1 : 0; }
+  void* pool_get(size_t bytes);
+  void pool_put(void* p, size_t bytes);
+  void* scratch(size_t bytes);  // grow-only scratch buffer valid until the next scratch() call
+  void ensure_grad(int64_t id);
+  const float* rope_table(int64_t seq_len, int64_t head_dim);
+  int64_t ce_impl(int64_t logits, const int64_t* targets, int64_t n, bool masked, float normalizer);
+  const void* operand(const HTensor& t) const;  // bf16 shadow of an f32 parameter in Bf16Mixed
+
+  std::vector<HTensor> tensors;
+  std::vector<HNode> tape;
+  bool no_grad = false;
+  int64_t num_params = 0;
+  Precision precision;
+  cudaStream_t stream;
+  int* status_dev = nullptr;  // fault word of the tensor-core kernels
+  int* bad_id_dev = nullptr;
+
+  // flat parameter arena (f32 weights | bf16 shadow | f32 grads), element offsets
+  float* arena_w = nullptr;
+  void* arena_shadow = nullptr;
+  float* arena_g = nullptr;
+  int64_t arena_cap = 0, arena_used = 0;
+
+  size_t pool_bytes_cached = 0, pool_bytes_live = 0, device_bytes_allocated = 0;
+  int64_t pool_hits = 0, pool_misses = 0;
+
+ private:
+  std::unordered_map<size_t, std::vector<void*>> pool_;
+  void* scratch_ = nullptr;
+  size_t scratch_bytes_ = 0;
+  std::unordered_map<int64_t, float*> rope_tables_;
+  int64_t new_tensor(HTensor&& t);
+  void free_tensor(HTensor& t);
+};
+
+// ---------------------------------------------------------------------------------------
+// modules (src/nn/*.rs)
+// ---------------------------------------------------------------------------------------
+struct BlockParams {
+  int64_t norm1, q, k, v, o, norm2, gate, up, down;
+};
+
+class TransformerLM {
+ public:
+  // src/nn/transformer.rs:81-122
+  TransformerLM(Graph& g, int64_t vocab, int64_t hidden, int64_t heads, int64_t kv_heads, int64_t ffn,
+                int64_t layers, bool tie);
+  int64_t forward(Graph& g, int64_t x_ids);                       // :184-196
+  int64_t block_forward(Graph& g, const BlockParams& b, int64_t x);  // :32-49
+  int64_t gqa_forward(Graph& g, const BlockParams& b, int64_t x, bool causal);  // attention.rs:289-388
+  std::vector<int64_t> params() const;                            // :198-210
+  // One micro-step: forward, loss (masked cross-entropy over [B*S] targets), backward.
+  // checkpoint = true keeps only block inputs in the forward and re-runs each block under a
+  // save point during the backward (the primitives of src/graph/mod.rs:332-365).
+  // after_block(l) is called when the gradients of block l (and, with l == layers, of the
+  // final norm / head; with l == -1, of the embedding) are complete.
+  int64_t train_micro_step(Graph& g, int64_t x_ids, const int64_t* targets, int64_t n_targets, bool checkpoint,
+                           const std::function<void(int64_t)>& after_block);
+  int64_t vocab, hidden, heads, kv_heads, ffn, layers;
+  bool tie;
+  bool fused = true;  // fused attention / SwiGLU ops (always the reference chain in Fp32 mode when false)
+  int64_t emb, norm_f, head;
+  std::vector<BlockParams> blocks;
+};
+
+// src/nn/optim.rs
+class AdamW {
+ public:
+  AdamW(Graph& g, std::vector<int64_t> params, float lr);
+  ~AdamW();
+  void zero_grad();                                    // :207-245
+  float clip_grad_norm(float max_norm, float* coef);   // :250-321 (host-visible norm, one 8-byte read-back)
+  void step();                                         // :334-481
+  // no host synchronisation: norm and clip coefficient stay on the device; grad_scale folds the
+  // data-parallel 1/world factor
+  void step_fused(float max_norm, float grad_scale);
+  float lr, beta1 = 0.9f, beta2 = 0.999f, eps = 1e-8f, weight_decay = 0.01f;
+  int64_t t = 0;
+  Graph& g;
+  std::vector<int64_t> params;
+  bool flat = false;  // parameters cover the arena: one launch
+  float* m = nullptr;
+  float* v = nullptr;
+  std::vector<int64_t> offsets;  // per-parameter offsets into m / v when not flat
+  int64_t total = 0;
+  double* sumsq_dev = nullptr;
+  void* sumsq_ws = nullptr;
+
+ private:
+  void launch(float grad_scale, const double* sumsq, float max_norm);
+};
+
+}  // namespace eisen

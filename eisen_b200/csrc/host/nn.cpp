@@ -1,0 +1,371 @@
+// Modules and optimizer of the training step: TransformerLM (src/nn/transformer.rs),
+// GroupedQueryAttention (src/nn/attention.rs:251-404), Linear / Embedding / RMSNorm
+// (src/nn/linear.rs, embedding.rs, rmsnorm.rs) and AdamW (src/nn/optim.rs), on the Graph of
+// graph.h.  Parameter ids, creation order and params() order follow the reference.
+#include <cmath>
+#include <cstring>
+
+#include "../../../include/eisen_b200.h"
+#include "graph.h"
+
+namespace eisen {
+
+namespace {
+
+void ck(int rc, const char* what) {
+  if (rc != 0) throw EisenException(rc, std::string(what) + ": " + eisen_last_error());
+}
+void cuck(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) throw EisenException(EISEN_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+// src/nn/linear.rs:10-49: LCG + Box-Muller, std 0.02; the seed restarts at 42 for every layer
+std::vector<float> linear_init(size_t n) {
+  std::vector<float> w(n);
+  uint32_t seed = 42;
+  const float umax = (float)UINT32_MAX;
+  for (size_t i = 0; i < n; ++i) {
+    float u1 = std::min((float)seed / umax + 1e-7f, 1.0f - 1e-7f);
+    seed = seed * 1664525u + 1013904223u;
+    float u2 = std::min(std::max((float)seed / umax, 1e-7f), 1.0f - 1e-7f);
+    seed = seed * 1664525u + 1013904223u;
+    float mag = std::sqrt(-2.0f * std::log(u1));
+    w[i] = mag * std::cos(2.0f * 3.14159265358979323846f * u2) * 0.02f;
+  }
+  return w;
+}
+// src/nn/embedding.rs:9-32
+std::vector<float> embedding_init(size_t n) {
+  std::vector<float> w(n);
+  uint32_t seed = 84;
+  const float umax = (float)UINT32_MAX;
+  for (size_t i = 0; i < n; ++i) {
+    seed = seed * 1664525u + 1013904223u;
+    w[i] = (((float)seed / umax) * 2.0f - 1.0f) * 0.02f;
+  }
+  return w;
+}
+
+int64_t pad64(int64_t n) { return (n + 63) / 64 * 64; }
+
+int64_t linear_new(Graph& g, int64_t in, int64_t out, std::vector<float>& cache) {
+  const size_t n = (size_t)in * out;
+  if (cache.size() < n) cache = linear_init(n);  // every layer draws the same stream: a prefix is enough
+  return g.alloc({in, out}, cache.data());
+}
+int64_t norm_new(Graph& g, int64_t d) {
+  std::vector<float> ones((size_t)d, 1.0f);
+  return g.alloc({d}, ones.data());
+}
+
+// src/nn/linear.rs:53-95 (no bias on this path)
+int64_t linear_fwd(Graph& g, int64_t x, int64_t w) {
+  const std::vector<int64_t> xs = g.tensors.at(x).shape;
+  int64_t o = g.matmul(x, w);
+  if (xs.size() == 3) g.reinterpret_shape(o, {xs[0], xs[1], g.tensors[w].shape[1]});
+  return o;
+}
+
+}  // namespace
+
+TransformerLM::TransformerLM(Graph& g, int64_t vocab_, int64_t hidden_, int64_t heads_, int64_t kv_heads_,
+                             int64_t ffn_, int64_t layers_, bool tie_)
+    : vocab(vocab_), hidden(hidden_), heads(heads_), kv_heads(kv_heads_), ffn(ffn_), layers(layers_), tie(tie_) {
+  if (hidden % heads) throw EisenException(EISEN_ERR_INVALID, "hidden_dim must be cleanly divisible by num_heads");
+  if (heads % kv_heads) throw EisenException(EISEN_ERR_INVALID, "num_heads must be divisible by num_kv_heads");
+  const int64_t hd = hidden / heads, kvd = kv_heads * hd;
+  if (!g.arena_w && g.num_params == 0) {
+    int64_t total = pad64(vocab * hidden) + pad64(hidden) + (tie ? 0 : pad64(hidden * vocab));
+    total += layers * (2 * pad64(hidden) + 2 * pad64(hidden * hidden) + 2 * pad64(hidden * kvd) + 3 * pad64(hidden * ffn));
+    g.reserve_param_arena(total);
+  }
+  std::vector<float> cache;
+  {
+    std::vector<float> e = embedding_init((size_t)vocab * hidden);
+    emb = g.alloc({vocab, hidden}, e.data());
+  }
+  // creation order of TransformerBlock::new (src/nn/transformer.rs:19-29)
+  for (int64_t l = 0; l < layers; ++l) {
+    BlockParams b;
+    b.norm1 = norm_new(g, hidden);
+    b.q = linear_new(g, hidden, hidden, cache);
+    b.k = linear_new(g, hidden, kvd, cache);
+    b.v = linear_new(g, hidden, kvd, cache);
+    b.o = linear_new(g, hidden, hidden, cache);
+    b.norm2 = norm_new(g, hidden);
+    b.gate = linear_new(g, hidden, ffn, cache);
+    b.up = linear_new(g, hidden, ffn, cache);
+    b.down = linear_new(g, ffn, hidden, cache);
+    blocks.push_back(b);
+  }
+  norm_f = norm_new(g, hidden);
+  head = tie ? emb : linear_new(g, hidden, vocab, cache);
+  fused = (g.precision == Precision::Bf16Mixed) && (hd == 64 || hd == 128);
+}
+
+std::vector<int64_t> TransformerLM::params() const {
+  std::vector<int64_t> p{emb};
+  for (const BlockParams& b : blocks) {
+    p.insert(p.end(), {b.norm1, b.q, b.k, b.v, b.o, b.norm2, b.up, b.down, b.gate});
+  }
+  p.push_back(norm_f);
+  if (!tie) p.push_back(head);
+  return p;
+}
+
+int64_t TransformerLM::gqa_forward(Graph& g, const BlockParams& b, int64_t x, bool causal) {
+  const std::vector<int64_t> xs = g.tensors.at(x).shape;
+  if (xs.size() != 3) throw EisenException(EISEN_ERR_INVALID, "GQA requires [Batch, Seq, Dim]");
+  const int64_t B = xs[0], S = xs[1], hd = hidden / heads;
+  int64_t q = linear_fwd(g, x, b.q), k = linear_fwd(g, x, b.k), v = linear_fwd(g, x, b.v);
+  int64_t qr = g.rope(q, hd), kr = g.rope(k, hd);
+  int64_t ctx2;
+  if (fused) {
+    ctx2 = g.attention(qr, kr, v, heads, kv_heads, causal);
+  } else {
+    // the reference chain, op for op (src/nn/attention.rs:305-384)
+    int64_t q4 = g.reshape(qr, {B, S, heads, hd});
+    int64_t k4 = g.reshape(kr, {B, S, kv_heads, hd});
+    int64_t v4 = g.reshape(v, {B, S, kv_heads, hd});
+    int64_t qt = g.transpose_0213(q4), kt = g.transpose_0213(k4), vt = g.transpose_0213(v4);
+    const int64_t rep = heads / kv_heads;
+    int64_t krep = g.repeat_kv(kt, rep), vrep = g.repeat_kv(vt, rep);
+    const int64_t bh = B * heads;
+    g.reinterpret_shape(qt, {bh, S, hd});
+    g.reinterpret_shape(krep, {bh, S, hd});
+    g.reinterpret_shape(vrep, {bh, S, hd});
+    const float scale = 1.0f / std::sqrt((float)hd);
+    int64_t ctx;
+    if (g.no_grad) {
+      ctx = g.flash_attention(qt, krep, vrep, scale, causal);
+    } else {
+      int64_t scores = g.bmm(qt, krep, true);
+      int64_t sc = g.alloc_pooled({bh, S, S});
+      g.tensors[sc].constant = true;
+      ck(eisen_fill_f32(g.stream, (float*)g.tensors[sc].data, scale, bh * S * S), "fill(scale)");
+      int64_t scaled = g.mul(scores, sc);
+      int64_t masked = scaled;
+      if (causal) {
+        std::vector<float> md((size_t)S * S, 0.0f);
+        for (int64_t r = 0; r < S; ++r)
+          for (int64_t c = r + 1; c < S; ++c) md[r * S + c] = -1e20f;
+        int64_t mask = g.alloc_pooled({1, S, S});
+        g.tensors[mask].constant = true;
+        g.load_tensor_data(mask, md.data(), S * S);
+        masked = g.add(scaled, mask);
+      }
+      int64_t probs = g.softmax(masked);
+      ctx = g.bmm(probs, vrep, false);
+    }
+    g.reinterpret_shape(ctx, {B, heads, S, hd});
+    int64_t ct = g.transpose_0213(ctx);
+    ctx2 = g.reshape(ct, {B, S, hidden});
+  }
+  return linear_fwd(g, ctx2, b.o);
+}
+
+int64_t TransformerLM::block_forward(Graph& g, const BlockParams& b, int64_t x) {
+  int64_t n1 = g.rms_norm(x, b.norm1, 1e-5f);
+  int64_t at = gqa_forward(g, b, n1, true);
+  int64_t r1 = g.add(x, at);
+  int64_t n2 = g.rms_norm(r1, b.norm2, 1e-5f);
+  int64_t go = linear_fwd(g, n2, b.gate);
+  int64_t up, gd;
+  if (fused) {
+    up = linear_fwd(g, n2, b.up);
+    gd = g.swiglu(go, up);
+  } else {
+    int64_t gt = g.silu(go);
+    up = linear_fwd(g, n2, b.up);
+    gd = g.mul(gt, up);
+  }
+  int64_t f2 = linear_fwd(g, gd, b.down);
+  return g.add(r1, f2);
+}
+
+int64_t TransformerLM::forward(Graph& g, int64_t x) {
+  int64_t h = g.gather(emb, x);
+  for (const BlockParams& b : blocks) h = block_forward(g, b, h);
+  h = g.rms_norm(h, norm_f, 1e-5f);
+  if (tie) return g.matmul_trans_b(h, emb);
+  return linear_fwd(g, h, head);
+}
+
+int64_t TransformerLM::train_micro_step(Graph& g, int64_t x, const int64_t* targets, int64_t n_targets, bool checkpoint,
+                                        const std::function<void(int64_t)>& after_block) {
+  if (g.no_grad) throw EisenException(EISEN_ERR_INVALID, "train_micro_step: graph is in no_grad mode");
+  const int64_t tape0 = (int64_t)g.tape.size();
+  int64_t h = g.gather(emb, x);
+  const int64_t tape_after_emb = (int64_t)g.tape.size();
+  std::vector<int64_t> block_in((size_t)layers);
+  std::vector<int64_t> block_tape((size_t)layers + 1);
+  for (int64_t l = 0; l < layers; ++l) {
+    block_in[l] = h;
+    block_tape[l] = (int64_t)g.tape.size();
+    if (checkpoint) {
+      // keep only the block output: run the block without a tape under a save point and move
+      // its result into a holder allocated before the save point
+      int64_t holder = g.alloc_pooled(g.tensors[h].shape);
+      const int64_t sp = g.mark_save_point();
+      g.no_grad = true;
+      int64_t r = block_forward(g, blocks[l], h);
+      g.no_grad = false;
+      std::swap(g.tensors[holder].data, g.tensors[r].data);
+      g.restore_save_point(sp);
+      h = holder;
+    } else {
+      h = block_forward(g, blocks[l], h);
+    }
+  }
+  block_tape[layers] = (int64_t)g.tape.size();
+  int64_t hn = g.rms_norm(h, norm_f, 1e-5f);
+  int64_t logits = tie ? g.matmul_trans_b(hn, emb) : linear_fwd(g, hn, head);
+  g.reinterpret_shape(logits, {n_targets, vocab});
+  int64_t loss = g.cross_entropy_masked(logits, targets, n_targets);
+
+  // ---- backward
+  g.seed_grad_ones(loss);
+  g.backward_from(block_tape[layers]);  // loss, head, final norm
+  if (after_block) after_block(layers);
+  if (checkpoint) {
+    int64_t out = h;  // holder of the last block's output; its grad is complete now
+    for (int64_t l = layers - 1; l >= 0; --l) {
+      const int64_t sp = g.mark_save_point();
+      const int64_t t0 = (int64_t)g.tape.size();
+      int64_t y = block_forward(g, blocks[l], block_in[l]);
+      // hand the output gradient to the recomputed output
+      HTensor& ty = g.tensors[y];
+      HTensor& to = g.tensors[out];
+      ty.grad = to.grad;
+      ty.grad_dtype = to.grad_dtype;
+      ty.grad_init = to.grad_init;
+      to.grad = nullptr;
+      to.grad_init = false;
+      g.backward_from(t0);
+      g.tape.resize((size_t)t0);
+      g.restore_save_point(sp);
+      out = block_in[l];
+      if (after_block) after_block(l);
+    }
+  } else {
+    for (int64_t l = layers - 1; l >= 0; --l) {
+      for (int64_t i = block_tape[l + 1]; i-- > block_tape[l];) g.tape[i].backward();
+      if (after_block) after_block(l);
+    }
+  }
+  for (int64_t i = tape_after_emb; i-- > tape0;) g.tape[i].backward();  // embedding scatter
+  if (after_block) after_block(-1);
+  return loss;
+}
+
+// ------------------------------------------------------------------------------------- AdamW
+AdamW::AdamW(Graph& g_, std::vector<int64_t> params_, float lr_) : lr(lr_), g(g_), params(std::move(params_)) {
+  // one launch over the arena when the parameter list is exactly the arena's content
+  int64_t in_arena = 0, arena_elems = 0;
+  for (int64_t p : params) {
+    const HTensor& t = g.tensors.at(p);
+    if (g.arena_w && t.data >= (void*)g.arena_w && t.data < (void*)(g.arena_w + g.arena_cap)) {
+      ++in_arena;
+      arena_elems += (t.numel + 63) / 64 * 64;
+    }
+  }
+  flat = g.arena_w && in_arena == (int64_t)params.size() && arena_elems == g.arena_used;
+  if (flat) {
+    total = g.arena_used;
+  } else {
+    for (int64_t p : params) {
+      offsets.push_back(total);
+      total += (g.tensors.at(p).numel + 63) / 64 * 64;
+    }
+  }
+  const size_t bytes = (size_t)std::max<int64_t>(total, 64) * 4;
+  cuck(cudaMalloc(&m, bytes), "cudaMalloc(adam m)");
+  cuck(cudaMalloc(&v, bytes), "cudaMalloc(adam v)");
+  cuck(cudaMemsetAsync(m, 0, bytes, g.stream), "memset");
+  cuck(cudaMemsetAsync(v, 0, bytes, g.stream), "memset");
+  cuck(cudaMalloc(&sumsq_dev, 64), "cudaMalloc(sumsq)");
+  cuck(cudaMalloc(&sumsq_ws, (size_t)eisen_sumsq_workspace_bytes(std::max<int64_t>(total, 64))), "cudaMalloc(sumsq ws)");
+  g.device_bytes_allocated += 2 * bytes;
+}
+
+AdamW::~AdamW() {
+  cudaStreamSynchronize(g.stream);
+  cudaFree(m);
+  cudaFree(v);
+  cudaFree(sumsq_dev);
+  cudaFree(sumsq_ws);
+}
+
+void AdamW::zero_grad() {
+  if (flat) {
+    cuck(cudaMemsetAsync(g.arena_g, 0, (size_t)total * 4, g.stream), "memset(grads)");
+    return;
+  }
+  for (int64_t p : params) g.zero_grad(p);
+}
+
+// squared norm of all parameter gradients into sumsq_dev (f64, device)
+static void grad_sumsq(AdamW& o) {
+  Graph& g = o.g;
+  if (o.flat) {
+    ck(eisen_sumsq(g.stream, g.arena_g, o.total, o.sumsq_ws, o.sumsq_dev, 0), "sumsq");
+    return;
+  }
+  bool first = true;
+  for (int64_t p : o.params) {
+    const HTensor& t = g.tensors[p];
+    ck(eisen_sumsq(g.stream, (const float*)t.grad, t.numel, o.sumsq_ws, o.sumsq_dev, first ? 0 : 1), "sumsq");
+    first = false;
+  }
+}
+
+float AdamW::clip_grad_norm(float max_norm, float* coef_out) {
+  grad_sumsq(*this);
+  double ss = 0.0;
+  cuck(cudaMemcpyAsync(&ss, sumsq_dev, 8, cudaMemcpyDeviceToHost, g.stream), "D2H(sumsq)");
+  cuck(cudaStreamSynchronize(g.stream), "sync");
+  const float norm = (float)std::sqrt(ss);
+  const float coef = norm > 0.0f ? std::min(max_norm / (norm + 1e-6f), 1.0f) : 1.0f;
+  if (coef < 1.0f) {
+    if (flat) {
+      ck(eisen_scale_f32(g.stream, g.arena_g, coef, total), "scale");
+    } else {
+      for (int64_t p : params) ck(eisen_scale_f32(g.stream, (float*)g.tensors[p].grad, coef, g.tensors[p].numel), "scale");
+    }
+  }
+  if (coef_out) *coef_out = coef;
+  return norm;
+}
+
+void AdamW::launch(float grad_scale, const double* sumsq, float max_norm) {
+  t += 1;
+  // src/nn/optim.rs:336-338: reciprocal bias corrections from powi
+  float p1 = 1.0f, p2 = 1.0f;
+  for (int64_t i = 0; i < t; ++i) { p1 *= beta1; p2 *= beta2; }
+  const float bc1 = 1.0f / (1.0f - p1), bc2 = 1.0f / (1.0f - p2);
+  if (flat) {
+    ck(eisen_adamw_step(g.stream, g.arena_w, g.arena_shadow, g.arena_g, m, v, total, lr, beta1, beta2, eps, weight_decay,
+                        bc1, bc2, grad_scale, sumsq, max_norm),
+       "adamw_step");
+    return;
+  }
+  for (size_t i = 0; i < params.size(); ++i) {
+    HTensor& tt = g.tensors[params[i]];
+    ck(eisen_adamw_step(g.stream, (float*)tt.data, tt.shadow, (const float*)tt.grad, m + offsets[i], v + offsets[i],
+                        tt.numel, lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale, sumsq, max_norm),
+       "adamw_step");
+  }
+}
+
+void AdamW::step() { launch(1.0f, nullptr, 0.0f); }
+
+void AdamW::step_fused(float max_norm, float grad_scale) {
+  if (max_norm > 0.0f) {
+    grad_sumsq(*this);
+    launch(grad_scale, sumsq_dev, max_norm);
+  } else {
+    launch(grad_scale, nullptr, 0.0f);
+  }
+}
+
+}  // namespace eisen

@@ -197,6 +197,97 @@ long long eisen_sumsq_workspace_bytes(long long n);
  * (src/nn/optim.rs:250-281 copies every gradient to the host instead). */
 int eisen_sumsq(void* stream, const float* x, long long n, void* workspace, double* out, int accumulate);
 
+/* ==========================================================================================
+ * Graph level: host-side mirror of the reference's Graph / tape / modules / AdamW.
+ *
+ * A graph owns its tensors; ids are indices into its tensor list and stay valid until
+ * eisen_graph_restore_save_point / eisen_graph_clear_activations pops them (src/graph/mod.rs:
+ * 336-365, 432-435).  Each op runs its forward at once on the graph's stream and, unless no_grad
+ * is set, pushes a tape node; eisen_graph_backward seeds the loss gradient with ones and walks
+ * the tape in reverse (src/graph/mod.rs:670-796).  precision: 0 = Fp32, 1 = Bf16Mixed (bf16
+ * activations and activation gradients, f32 master parameters with a bf16 shadow, f32 parameter
+ * gradients).  Leaves allocated before eisen_graph_mark_params are parameters.
+ * All handles are `void*`; out-parameters are written only on success.
+ * ========================================================================================== */
+typedef void (*eisen_block_cb)(long long layer, void* user);
+
+int eisen_graph_create(int precision, void* stream, void** out);                       /* Graph::new, src/graph/mod.rs:152-307 */
+int eisen_graph_destroy(void* g);
+int eisen_graph_alloc(void* g, const long long* shape, int ndim, const float* host_data, long long* id_out); /* Graph::alloc */
+int eisen_graph_alloc_ids(void* g, const long long* shape, int ndim, const int* host_ids, long long* id_out); /* int32 token ids */
+int eisen_graph_alloc_pooled(void* g, const long long* shape, int ndim, long long* id_out);  /* Graph::alloc_pooled, :437-556 */
+int eisen_graph_load_tensor_data(void* g, long long id, const float* host, long long n);     /* :368-430 */
+int eisen_graph_sync_to_cpu(void* g, long long id, float* out);                        /* Tensor::sync_to_cpu */
+int eisen_graph_sync_grad_to_cpu(void* g, long long id, float* out);                   /* Graph::sync_grad_to_cpu */
+int eisen_graph_shape(void* g, long long id, long long* shape_out, int* ndim_out);
+int eisen_graph_tensor_ptrs(void* g, long long id, void** data, void** grad, int* dtype, int* grad_dtype);
+int eisen_graph_set_no_grad(void* g, int flag);                                        /* Graph.no_grad */
+int eisen_graph_mark_params(void* g);                                                  /* :328-330 */
+int eisen_graph_mark_save_point(void* g, long long* out);                              /* :332-334 */
+int eisen_graph_restore_save_point(void* g, long long save_point);                     /* :336-365 */
+int eisen_graph_clear_activations(void* g);                                            /* :432-435 */
+int eisen_graph_tape_clear(void* g);                                                   /* g.tape.nodes.clear() */
+int eisen_graph_reinterpret_shape(void* g, long long id, const long long* shape, int ndim); /* ops/transform.rs:413-426 */
+int eisen_graph_zero_grad(void* g, long long id);
+int eisen_graph_backward(void* g, long long loss_id);                                  /* :670-796 */
+int eisen_graph_synchronize(void* g);   /* waits for the stream and raises recorded kernel faults */
+int eisen_graph_counts(void* g, long long* num_tensors, long long* tape_len, long long* num_params);
+/* out5: pool bytes in use, pool bytes cached, device bytes allocated, pool hits, pool misses */
+int eisen_graph_pool_stats(void* g, long long* out5);
+/* flat parameter buffers (f32 weights, bf16 shadow or null, f32 gradients) and their length */
+int eisen_graph_param_arena(void* g, void** weights, void** shadow, void** grads, long long* elems);
+
+/* ops: src/graph/ops/elementwise.rs (add 7, mul 188, silu 337), linear.rs (matmul 35/526,
+ * matmul_trans_b 301, bmm 1198), reduction.rs (softmax 397, cross_entropy 529, masked 724),
+ * normalization.rs (rms_norm 8), transform.rs (transpose_0213 7, gather 132, reshape 329,
+ * rope 467), gqa.rs (repeat_kv 13), attention.rs (flash_attention 7).  Targets < 0 stand for
+ * IGNORE_INDEX (usize::MAX, src/data/fim.rs:173). */
+int eisen_graph_add(void* g, long long a, long long b, long long* out);
+int eisen_graph_mul(void* g, long long a, long long b, long long* out);
+int eisen_graph_silu(void* g, long long a, long long* out);
+int eisen_graph_swiglu(void* g, long long gate, long long up, long long* out);          /* fused silu(gate)*up */
+int eisen_graph_matmul(void* g, long long a, long long b, long long* out);
+int eisen_graph_matmul_trans_b(void* g, long long a, long long b, long long* out);
+int eisen_graph_bmm(void* g, long long a, long long b, int trans_b, long long* out);
+int eisen_graph_softmax(void* g, long long a, long long* out);
+int eisen_graph_cross_entropy(void* g, long long logits, const long long* targets, long long n, long long* out);
+int eisen_graph_cross_entropy_masked(void* g, long long logits, const long long* targets, long long n, long long* out);
+int eisen_graph_rms_norm(void* g, long long x, long long w, float eps, long long* out);
+int eisen_graph_rope(void* g, long long a, long long head_dim, long long* out);
+int eisen_graph_gather(void* g, long long weights, long long indices, long long* out);
+int eisen_graph_reshape(void* g, long long a, const long long* shape, int ndim, long long* out);
+int eisen_graph_transpose_0213(void* g, long long a, long long* out);
+int eisen_graph_repeat_kv(void* g, long long a, long long repeats, long long* out);
+int eisen_graph_flash_attention(void* g, long long q, long long k, long long v, float scale, int causal, long long* out);
+/* fused causal GQA attention with backward on [B,S,heads*head_dim] projections (Bf16Mixed) */
+int eisen_graph_attention(void* g, long long q, long long k, long long v, long long num_heads,
+                          long long num_kv_heads, int causal, long long* out);
+
+/* TransformerLM (src/nn/transformer.rs:69-211) */
+int eisen_lm_create(void* g, long long vocab, long long hidden, long long heads, long long kv_heads, long long ffn,
+                    long long layers, int tie_weights, void** out);
+int eisen_lm_destroy(void* lm);
+int eisen_lm_set_fused(void* lm, int fused);   /* 0: the reference's op-by-op attention / MLP chain */
+int eisen_lm_forward(void* lm, void* g, long long x_ids, long long* logits_out);       /* Module::forward, :184-196 */
+int eisen_lm_params(void* lm, long long* ids_out, int* n_out);                         /* Module::params, :198-210 */
+/* one micro-step: forward, masked cross-entropy over n_targets rows, backward; with checkpoint
+ * != 0 each block is re-run under a save point during the backward (src/graph/mod.rs:332-365).
+ * after_block(l, user) fires when the gradients of block l are final (l == layers: final norm
+ * and head, l == -1: embedding); it may enqueue work on other streams. */
+int eisen_lm_train_micro_step(void* lm, void* g, long long x_ids, const long long* targets, long long n_targets,
+                              int checkpoint, eisen_block_cb after_block, void* user, long long* loss_id);
+
+/* AdamW (src/nn/optim.rs): zero_grad 207, clip_grad_norm 250, step 334 */
+int eisen_optim_create(void* g, const long long* params, int n, float lr, void** out);
+int eisen_optim_destroy(void* opt);
+int eisen_optim_config(void* opt, float lr, float beta1, float beta2, float eps, float weight_decay);
+int eisen_optim_zero_grad(void* opt);
+int eisen_optim_clip_grad_norm(void* opt, float max_norm, float* norm_out, float* coef_out);
+int eisen_optim_step(void* opt);
+/* clip (max_norm > 0) and step without a host round trip; the gradient is read as g * grad_scale */
+int eisen_optim_step_fused(void* opt, float max_norm, float grad_scale);
+int eisen_optim_is_flat(void* opt, int* flat);
+
 #ifdef __cplusplus
 }
 #endif

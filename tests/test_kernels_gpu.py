@@ -277,8 +277,10 @@ def test_cross_entropy_bf16():
     l = (2.0 * torch.randn(rows, vocab, generator=g)).to(torch.bfloat16)
     t = torch.randint(0, vocab, (rows,), generator=g)
     lf = l.float().requires_grad_(True)
-    ref = torch.nn.functional.cross_entropy(lf, t)
-    ref.backward()
+    # the reference's loss is -ln(p + 1e-8) (src/graph/ops/reduction.rs:690); its gradient ignores the 1e-8
+    pt = torch.softmax(lf, dim=-1).gather(1, t[:, None]).squeeze(1)
+    ref = (-(pt + 1e-8).log()).mean().detach()
+    torch.nn.functional.cross_entropy(lf, t).backward()
     ld, td = l.to(dev()), t.to(torch.int32).to(dev())
     loss = torch.zeros(1, device=dev())
     row_loss = torch.empty(rows, device=dev())
