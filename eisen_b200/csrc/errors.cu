@@ -3,12 +3,16 @@
 #include "gemm_tc.h"
 #include "../../include/eisen_b200.h"
 
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 
 namespace eisen {
 
 static thread_local char g_err[512] = "";
+static std::atomic<long long> g_launches{0};
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 void set_error(const char* msg) {
   std::snprintf(g_err, sizeof(g_err), "%s", msg ? msg : "");
@@ -18,6 +22,7 @@ int fail(int code, const char* msg) {
   return code;
 }
 int check_launch(const char* what) {
+  count_launch();
   cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess) return 0;
   char buf[400];
@@ -32,6 +37,7 @@ extern "C" {
 
 const char* eisen_last_error(void) { return eisen::g_err; }
 const char* eisen_version(void) { return "eisen_b200 0.1 (sm_100a)"; }
+long long eisen_launch_count(void) { return eisen::g_launches.load(); }
 
 int eisen_gemm_bf16(void* stream, int a_mn, int b_mn, long long M, long long N, long long K, const void* A,
                     long long lda, const void* B, long long ldb, void* C, long long ldc, int out_mode,
@@ -46,6 +52,7 @@ int eisen_gemm_bf16(void* stream, int a_mn, int b_mn, long long M, long long N, 
   int rc = eisen::gemm_bf16_tc((cudaStream_t)stream, a_mn, b_mn, (int)M, (int)N, (int)K, A, lda, B, ldb, C, ldc,
                                out_mode, split_k, alpha, status, &err);
   if (rc) return eisen::fail(rc == 1 ? EISEN_ERR_INVALID : EISEN_ERR_CUDA, err ? err : "gemm_bf16 failed");
+  if (M > 0 && N > 0 && K > 0) eisen::count_launch();
   return 0;
 }
 

@@ -11,6 +11,7 @@ namespace eisen {
 
 void set_error(const char* msg);
 int fail(int code, const char* msg);
-int check_launch(const char* what);
+int check_launch(const char* what);  // also counts the launch
+void count_launch();
 
 }  // namespace eisen

@@ -211,6 +211,21 @@ int eisen_lm_train_micro_step(void* lm, void* g, long long x_ids, const long lon
   });
 }
 
+int eisen_lm_train_micro_step_dev(void* lm, void* g, long long x_ids, long long target_ids, long long n_valid,
+                                  int checkpoint, eisen_block_cb after_block, void* user, long long* loss_id) {
+  return guarded([&] {
+    std::function<void(int64_t)> cb;
+    if (after_block) cb = [after_block, user](int64_t l) { after_block((long long)l, user); };
+    *loss_id = static_cast<TransformerLM*>(lm)->train_micro_step_dev(G(g), x_ids, target_ids, n_valid, checkpoint != 0, cb);
+  });
+}
+int eisen_graph_prof_enable(void* g, int on) {
+  return guarded([&] { G(g).prof_on = on != 0; });
+}
+int eisen_graph_prof_read(void* g, double* out9) {
+  return guarded([&] { G(g).prof_read(out9); });
+}
+
 // ---- AdamW
 int eisen_optim_create(void* g, const long long* params, int n, float lr, void** out) {
   return guarded([&] { *out = new AdamW(G(g), std::vector<int64_t>(params, params + n), lr); });

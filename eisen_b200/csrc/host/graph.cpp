@@ -339,6 +339,41 @@ const float* Graph::rope_table(int64_t S, int64_t hd) {
   return tab;
 }
 
+void Graph::prof_begin(int cls, double flops) {
+  if (!prof_on) return;
+  ProfRec r;
+  auto get = [this]() {
+    cudaEvent_t e;
+    if (!prof_free.empty()) { e = prof_free.back(); prof_free.pop_back(); }
+    else cuck(cudaEventCreate(&e), "cudaEventCreate");
+    return e;
+  };
+  r.a = get();
+  r.b = get();
+  r.flops = flops;
+  r.cls = cls;
+  cuck(cudaEventRecord(r.a, stream), "cudaEventRecord");
+  prof_recs.push_back(r);
+}
+void Graph::prof_end() {
+  if (!prof_on || prof_recs.empty()) return;
+  cuck(cudaEventRecord(prof_recs.back().b, stream), "cudaEventRecord");
+}
+void Graph::prof_read(double* out9) {
+  for (int i = 0; i < 9; ++i) out9[i] = 0.0;
+  cuck(cudaStreamSynchronize(stream), "sync");
+  for (ProfRec& r : prof_recs) {
+    float ms = 0.0f;
+    cuck(cudaEventElapsedTime(&ms, r.a, r.b), "cudaEventElapsedTime");
+    out9[r.cls * 3 + 0] += ms;
+    out9[r.cls * 3 + 1] += r.flops;
+    out9[r.cls * 3 + 2] += 1.0;
+    prof_free.push_back(r.a);
+    prof_free.push_back(r.b);
+  }
+  prof_recs.clear();
+}
+
 // helper: true if the output carries a gradient worth propagating
 #define OUT_GRAD_OR_RETURN(o)                         \
   HTensor& to = tensors[o];                           \
@@ -463,8 +498,10 @@ void gemm(Graph& g, bool a_mn, bool b_mn, int64_t M, int64_t N, int64_t K, const
   int mode;
   if (c_dtype == 1) mode = accumulate ? 1 : 0;
   else mode = accumulate ? 4 : 2;  // f32 accumulation goes through red.global.add with automatic split-K
+  g.prof_begin(0, 2.0 * (double)M * (double)N * (double)K);
   ck(eisen_gemm_bf16(g.stream, a_mn, b_mn, M, N, K, A, lda, B, ldb, C, N, mode, mode == 4 ? 0 : 1, 1.0f, g.status_dev),
      "gemm_bf16");
+  g.prof_end();
 }
 }  // namespace
 
@@ -596,7 +633,6 @@ int64_t Graph::ce_impl(int64_t logits, const int64_t* targets, int64_t n, bool m
   const HTensor& tl = tensors.at(logits);
   if (tl.shape.size() != 2 || tl.shape[0] != n) invalid("cross_entropy: logits must be [rows, classes] with one target per row");
   const int64_t rows = tl.shape[0], vocab = tl.shape[1];
-  const int dt = act_dtype();
   // targets -> device int32; IGNORE_INDEX (usize::MAX in the reference, any negative value here) -> -1
   std::vector<int32_t> h((size_t)rows);
   for (int64_t i = 0; i < rows; ++i) {
@@ -604,7 +640,17 @@ int64_t Graph::ce_impl(int64_t logits, const int64_t* targets, int64_t n, bool m
     else if (targets[i] >= vocab) invalid("cross_entropy: target out of range");
     else h[i] = (int32_t)targets[i];
   }
+  (void)masked;
   int64_t tid = alloc_ids({rows}, h.data(), false);
+  return ce_device(logits, tid, normalizer);
+}
+
+int64_t Graph::ce_device(int64_t logits, int64_t tid, float normalizer) {
+  const HTensor& tl = tensors.at(logits);
+  if (tl.shape.size() != 2) invalid("cross_entropy: logits must be [rows, classes]");
+  const int64_t rows = tl.shape[0], vocab = tl.shape[1];
+  if (tensors.at(tid).dtype != DT_I32 || tensors[tid].numel != rows) invalid("cross_entropy: one int32 target per row expected");
+  const int dt = act_dtype();
   int64_t lse = alloc_pooled_dtype({rows}, 0);
   int64_t row_loss = alloc_pooled_dtype({rows}, 0);
   int64_t o = alloc_pooled_dtype({}, 0);
@@ -612,7 +658,6 @@ int64_t Graph::ce_impl(int64_t logits, const int64_t* targets, int64_t n, bool m
   ck(eisen_ce_fwd(stream, operand(tensors[logits]), (const int*)tensors[tid].data, (float*)tensors[o].data,
                   (float*)tensors[row_loss].data, (float*)tensors[lse].data, rows, vocab, -1, normalizer, dt),
      "cross_entropy");
-  (void)masked;
   if (!no_grad) {
     tape.push_back({{logits}, o, [this, logits, tid, lse, o, rows, vocab, normalizer, dt]() {
       OUT_GRAD_OR_RETURN(o);
@@ -855,11 +900,15 @@ int64_t Graph::attention(int64_t q, int64_t k, int64_t v, int64_t Hq, int64_t Hk
   int64_t lse = alloc_pooled_dtype({B, Hq, S}, 0);
   tensors[lse].constant = true;
   const int64_t qb = S * Hq * D, qs = Hq * D, kb = S * Hkv * D, ks = Hkv * D;
+  // flash convention: 4*B*H*S^2*D forward FLOPs, halved under the causal mask; backward 2.5x
+  const double attn_flops = 4.0 * (double)B * (double)Hq * (double)S * (double)S * (double)D * (causal ? 0.5 : 1.0);
+  prof_begin(1, attn_flops);
   ck(eisen_attn_fwd(stream, operand(tensors[q]), operand(tensors[k]), operand(tensors[v]), tensors[o].data,
                     (float*)tensors[lse].data, B, S, Hq, Hkv, D, qb, qs, D, kb, ks, D, qb, qs, D, scale, causal, status_dev),
      "attention");
+  prof_end();
   if (!no_grad) {
-    tape.push_back({{q, k, v}, o, [this, q, k, v, o, lse, B, S, Hq, Hkv, D, qb, qs, kb, ks, scale, causal]() {
+    tape.push_back({{q, k, v}, o, [this, q, k, v, o, lse, B, S, Hq, Hkv, D, qb, qs, kb, ks, scale, causal, attn_flops]() {
       OUT_GRAD_OR_RETURN(o);
       HTensor* gt[3] = {&tensors[q], &tensors[k], &tensors[v]};
       void* dst[3];
@@ -872,10 +921,12 @@ int64_t Graph::attention(int64_t q, int64_t k, int64_t v, int64_t Hq, int64_t Hk
         else dst[i] = gt[i]->grad;
       }
       void* ws = scratch((size_t)eisen_attn_bwd_workspace_bytes(B, S, Hq, Hkv, D));
+      prof_begin(2, 2.5 * attn_flops);
       ck(eisen_attn_bwd(stream, operand(*gt[0]), operand(*gt[1]), operand(*gt[2]), to.data, (const float*)tensors[lse].data,
                         to.grad, dst[0], dst[1], dst[2], ws, B, S, Hq, Hkv, D, qb, qs, D, kb, ks, D, qb, qs, D, scale,
                         causal, status_dev),
          "attention.bwd");
+      prof_end();
       for (int i = 0; i < 3; ++i) {
         if (tmp[i]) {
           ck(eisen_accumulate(stream, gt[i]->grad, 1, tmp[i], 1, gt[i]->numel, 1), "attention.bwd(acc)");

@@ -103,6 +103,16 @@ class Graph {
   void ensure_grad(int64_t id);
   const float* rope_table(int64_t seq_len, int64_t head_dim);
   int64_t ce_impl(int64_t logits, const int64_t* targets, int64_t n, bool masked, float normalizer);
+  int64_t ce_device(int64_t logits, int64_t target_ids, float normalizer);  // targets already on the device
+
+  // event-based timing of the tensor-core kernels (class 0 GEMM, 1 attention fwd, 2 attention bwd)
+  bool prof_on = false;
+  struct ProfRec { cudaEvent_t a, b; double flops; int cls; };
+  std::vector<ProfRec> prof_recs;
+  std::vector<cudaEvent_t> prof_free;
+  void prof_begin(int cls, double flops);
+  void prof_end();
+  void prof_read(double* out9);
   const void* operand(const HTensor& t) const;  // bf16 shadow of an f32 parameter in Bf16Mixed
 
   std::vector<HTensor> tensors;
@@ -155,6 +165,8 @@ class TransformerLM {
   // final norm / head; with l == -1, of the embedding) are complete.
   int64_t train_micro_step(Graph& g, int64_t x_ids, const int64_t* targets, int64_t n_targets, bool checkpoint,
                            const std::function<void(int64_t)>& after_block);
+  int64_t train_micro_step_dev(Graph& g, int64_t x_ids, int64_t target_ids, int64_t n_valid, bool checkpoint,
+                               const std::function<void(int64_t)>& after_block);
   int64_t vocab, hidden, heads, kv_heads, ffn, layers;
   bool tie;
   bool fused = true;  // fused attention / SwiGLU ops (always the reference chain in Fp32 mode when false)

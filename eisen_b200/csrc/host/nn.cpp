@@ -193,7 +193,21 @@ int64_t TransformerLM::forward(Graph& g, int64_t x) {
 
 int64_t TransformerLM::train_micro_step(Graph& g, int64_t x, const int64_t* targets, int64_t n_targets, bool checkpoint,
                                         const std::function<void(int64_t)>& after_block) {
+  std::vector<int32_t> h((size_t)n_targets);
+  int64_t valid = 0;
+  for (int64_t i = 0; i < n_targets; ++i) {
+    if (targets[i] >= vocab) throw EisenException(EISEN_ERR_INVALID, "train_micro_step: target out of range");
+    h[i] = targets[i] < 0 ? -1 : (int32_t)targets[i];
+    valid += targets[i] >= 0;
+  }
+  int64_t tid = g.alloc_ids({n_targets}, h.data(), false);
+  return train_micro_step_dev(g, x, tid, valid, checkpoint, after_block);
+}
+
+int64_t TransformerLM::train_micro_step_dev(Graph& g, int64_t x, int64_t target_ids, int64_t n_valid, bool checkpoint,
+                                            const std::function<void(int64_t)>& after_block) {
   if (g.no_grad) throw EisenException(EISEN_ERR_INVALID, "train_micro_step: graph is in no_grad mode");
+  const int64_t n_targets = g.tensors.at(target_ids).numel;
   const int64_t tape0 = (int64_t)g.tape.size();
   int64_t h = g.gather(emb, x);
   const int64_t tape_after_emb = (int64_t)g.tape.size();
@@ -221,7 +235,8 @@ int64_t TransformerLM::train_micro_step(Graph& g, int64_t x, const int64_t* targ
   int64_t hn = g.rms_norm(h, norm_f, 1e-5f);
   int64_t logits = tie ? g.matmul_trans_b(hn, emb) : linear_fwd(g, hn, head);
   g.reinterpret_shape(logits, {n_targets, vocab});
-  int64_t loss = g.cross_entropy_masked(logits, targets, n_targets);
+  // src/graph/ops/reduction.rs:724-737: mean over the valid rows; all rows masked -> loss 0, no gradient
+  int64_t loss = g.ce_device(logits, target_ids, n_valid > 0 ? 1.0f / (float)n_valid : 0.0f);
 
   // ---- backward
   g.seed_grad_ones(loss);

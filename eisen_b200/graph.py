@@ -151,6 +151,15 @@ class Graph:
         call("eisen_graph_pool_stats", self._h, buf)
         return dict(zip(("live_bytes", "cached_bytes", "device_bytes", "hits", "misses"), list(buf)))
 
+    def prof_enable(self, on=True):
+        call("eisen_graph_prof_enable", self._h, 1 if on else 0)
+
+    def prof_read(self):
+        """{class: (ms, flops, launches)} of the tensor-core kernels timed since the last read."""
+        buf = (C.c_double * 9)()
+        call("eisen_graph_prof_read", self._h, buf)
+        return {n: (buf[3 * i], buf[3 * i + 1], int(buf[3 * i + 2])) for i, n in enumerate(("gemm", "attn_fwd", "attn_bwd"))}
+
     # ---- ops
     def add(self, a, b):
         return self._op("add", a, b)
@@ -242,6 +251,15 @@ class TransformerLM:
         cb = BLOCK_CB(lambda layer, user: after_block(layer)) if after_block else None
         out = C.c_longlong()
         call("eisen_lm_train_micro_step", self._h, self.g._h, x_id, t, len(t), 1 if checkpoint else 0,
+             C.cast(cb, C.c_void_p) if cb else None, None, C.byref(out))
+        return out.value
+
+
+    def train_micro_step_dev(self, x_id, target_ids_id, n_valid, checkpoint=False, after_block=None):
+        """As train_micro_step with the targets already on the device (alloc_ids, -1 = ignored)."""
+        cb = BLOCK_CB(lambda layer, user: after_block(layer)) if after_block else None
+        out = C.c_longlong()
+        call("eisen_lm_train_micro_step_dev", self._h, self.g._h, x_id, target_ids_id, n_valid, 1 if checkpoint else 0,
              C.cast(cb, C.c_void_p) if cb else None, None, C.byref(out))
         return out.value
 

@@ -44,6 +44,8 @@ extern "C" {
 const char* eisen_last_error(void);
 /* version string of the library */
 const char* eisen_version(void);
+/* number of kernels this library has launched in the process so far */
+long long eisen_launch_count(void);
 
 /* ------------------------------------------------------------------------------------------
  * Dense contractions
@@ -276,6 +278,18 @@ int eisen_lm_params(void* lm, long long* ids_out, int* n_out);                  
  * and head, l == -1: embedding); it may enqueue work on other streams. */
 int eisen_lm_train_micro_step(void* lm, void* g, long long x_ids, const long long* targets, long long n_targets,
                               int checkpoint, eisen_block_cb after_block, void* user, long long* loss_id);
+
+/* same, with the targets already on the device (an id tensor from eisen_graph_alloc_ids holding
+ * -1 for ignored rows) and their number of valid rows */
+int eisen_lm_train_micro_step_dev(void* lm, void* g, long long x_ids, long long target_ids, long long n_valid,
+                                  int checkpoint, eisen_block_cb after_block, void* user, long long* loss_id);
+
+/* Per-class device timing of the tensor-core kernels of a graph, taken with CUDA events on the
+ * graph's stream around each launch while enabled.  eisen_graph_prof_read synchronises the
+ * stream, sums the intervals and resets them.  out[class][0..2] = milliseconds, algorithmic
+ * FLOPs, launches for class 0 = GEMM, 1 = attention forward, 2 = attention backward. */
+int eisen_graph_prof_enable(void* g, int on);
+int eisen_graph_prof_read(void* g, double* out9);
 
 /* AdamW (src/nn/optim.rs): zero_grad 207, clip_grad_norm 250, step 334 */
 int eisen_optim_create(void* g, const long long* params, int n, float lr, void** out);

@@ -614,7 +614,12 @@ struct OLM {
   std::vector<OBlock> blocks;
 };
 
-size_t linear_new(OGraph& g, size_t in, size_t out) { return g_alloc(g, {in, out}, linear_init(in * out)); }
+// every Linear restarts the same LCG stream, so a longest-so-far prefix serves all layers
+size_t linear_new(OGraph& g, size_t in, size_t out) {
+  static std::vector<float> cache;
+  if (cache.size() < in * out) cache = linear_init(in * out);
+  return g_alloc(g, {in, out}, std::vector<float>(cache.begin(), cache.begin() + in * out));
+}
 size_t norm_new(OGraph& g, size_t d) { return g_alloc(g, {d}, std::vector<float>(d, 1.0f)); }
 
 // src/nn/linear.rs:53-95 (no bias on this path): matmul, then the 3-D shape is restored by
@@ -863,14 +868,18 @@ void orc_adamw_step(void* ov, void* g) {
     if (o.m[pi].empty()) { o.m[pi].assign(n, 0.0f); o.v[pi].assign(n, 0.0f); }
     float* m = o.m[pi].data();
     float* v = o.v[pi].data();
-    for (size_t i = 0; i < n; ++i) {
-      const float grad = t.grad[i], w = t.data[i];
-      const float decayed = w * (1.0f - o.lr * o.wd);
-      m[i] = o.beta1 * m[i] + (1.0f - o.beta1) * grad;
-      v[i] = o.beta2 * v[i] + (1.0f - o.beta2) * grad * grad;
-      const float mh = m[i] * bc1, vh = v[i] * bc2;
-      t.data[i] = decayed - o.lr * mh / (std::sqrt(vh) + o.eps);
-    }
+    const size_t chunk = 1 << 16;
+    PFOR(c, (n + chunk - 1) / chunk) {
+      const size_t hi = std::min(n, (size_t)(c + 1) * chunk);
+      for (size_t i = (size_t)c * chunk; i < hi; ++i) {
+        const float grad = t.grad[i], w = t.data[i];
+        const float decayed = w * (1.0f - o.lr * o.wd);
+        m[i] = o.beta1 * m[i] + (1.0f - o.beta1) * grad;
+        v[i] = o.beta2 * v[i] + (1.0f - o.beta2) * grad * grad;
+        const float mh = m[i] * bc1, vh = v[i] * bc2;
+        t.data[i] = decayed - o.lr * mh / (std::sqrt(vh) + o.eps);
+      }
+    });
   }
 }
 
