@@ -59,27 +59,38 @@ __device__ __forceinline__ void store_row_chunk32(uint32_t tile_base, int row, i
 }
 
 // =====================================================================================
-// forward
+// forward: two 128-query tiles of one head per CTA.  Warps 0-3 run the softmax of tile A,
+// warps 4-7 that of tile B (thread = query row), warp 8 issues TMA, warp 9 issues MMAs.  K and V
+// tiles are loaded once and used by both query tiles; while one tile's softmax runs on the SIMT
+// side the tensor core works on the other tile's S = Q K^T and PV products.
 // =====================================================================================
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int D>
 struct FwdCfg {
   static constexpr int TILE = 128 * D * 2;  // bytes of a [128 x D] bf16 tile
   static constexpr int P_TILE = 128 * 128 * 2;
-  static constexpr int OFF_Q = 0;
-  static constexpr int OFF_K = TILE;
-  static constexpr int OFF_V = OFF_K + 2 * TILE;
-  static constexpr int OFF_P = OFF_V + 2 * TILE;
+  static constexpr int NSV = (D == 64) ? 2 : 1;  // V stages (shared memory is the limit at D = 128)
+  static constexpr int OFF_Q = 0;                 // 2 tiles
+  static constexpr int OFF_K = 2 * TILE;          // 2 stages
+  static constexpr int OFF_V = OFF_K + 2 * TILE;  // NSV stages
+  static constexpr int OFF_P = OFF_V + NSV * TILE;  // 2 tiles
   static constexpr int OFF_BAR = OFF_P + 2 * P_TILE;
   static constexpr int SMEM = OFF_BAR + 256 + 1024;
   static constexpr int TMEM_COLS = 512;
 };
 
 template <int D>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
   using Cfg = FwdCfg<D>;
   constexpr int ATOMS = D / 64;
+  constexpr int NSV = Cfg::NSV;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -89,50 +100,53 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* k_empty = bars + 3;     // 2
   uint64_t* v_full = bars + 5;      // 2
   uint64_t* v_empty = bars + 7;     // 2
-  uint64_t* s_full = bars + 9;      // 2
-  uint64_t* s_empty = bars + 11;    // 2 (128 arrivals)
-  uint64_t* p_ready = bars + 13;    // 2 (128 arrivals)
-  uint64_t* o_full = bars + 15;     // 2
-  uint64_t* o_empty = bars + 17;    // 2 (128 arrivals)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
+  uint64_t* s_full = bars + 9;      // per query tile
+  uint64_t* p_ready = bars + 11;    // per query tile (128 arrivals)
+  uint64_t* o_full = bars + 13;     // per query tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_qt = gridDim.x;
-  const int qt = n_qt - 1 - blockIdx.x;  // heavy (late) causal tiles first
+  const int n_qt = (p.S + 127) / 128;
+  const int pair = (int)gridDim.x - 1 - (int)blockIdx.x;  // heavy (late) causal tiles first
+  const int qtA = 2 * pair, qtB = 2 * pair + 1;
+  const bool b_valid = qtB < n_qt;
   const int h = blockIdx.y, b = blockIdx.z;
   const int kvh = h / (p.Hq / p.Hkv);
-  const int n_kv_all = (p.S + 127) / 128;
-  const int n_kv = p.causal ? min(qt + 1, n_kv_all) : n_kv_all;
+  const int nA = p.causal ? min(qtA + 1, n_qt) : n_qt;                 // key tiles of query tile A
+  const int nB = b_valid ? (p.causal ? min(qtB + 1, n_qt) : n_qt) : 0;  // key tiles of query tile B
+  const int n_kv = max(nA, nB);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 128);
+      mbar_init(&s_full[i], 1);
       mbar_init(&p_ready[i], 128);
-      mbar_init(&o_full[i], 1); mbar_init(&o_empty[i], 128);
+      mbar_init(&o_full[i], 1);
     }
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
   }
-  if (warp == 5) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
+  if (warp == 9) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tm_S = tmem_base;            // 2 x 128 columns
-  const uint32_t tm_O = tmem_base + 256;      // 2 x D columns
+  const uint32_t tm_S = tmem_base;        // S of tile A at +0, of tile B at +128
+  const uint32_t tm_O = tmem_base + 256;  // PV of tile A at +0, of tile B at +D
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ---------------- TMA ----------------
     if (lane == 0) {
-      mbar_arrive_expect_tx(q_full, Cfg::TILE);
+      mbar_arrive_expect_tx(q_full, (b_valid ? 2 : 1) * Cfg::TILE);
 #pragma unroll
-      for (int a = 0; a < ATOMS; ++a)
-        tma_load_4d(smem + Cfg::OFF_Q + a * 16384, &tmQ, q_full, a * 64, h, qt * 128, b);
+      for (int a = 0; a < ATOMS; ++a) {
+        tma_load_4d(smem + Cfg::OFF_Q + a * 16384, &tmQ, q_full, a * 64, h, qtA * 128, b);
+        if (b_valid) tma_load_4d(smem + Cfg::OFF_Q + Cfg::TILE + a * 16384, &tmQ, q_full, a * 64, h, qtB * 128, b);
+      }
       for (int j = 0; j < n_kv; ++j) {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
@@ -141,93 +155,115 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int a = 0; a < ATOMS; ++a)
           tma_load_4d(smem + Cfg::OFF_K + st * Cfg::TILE + a * 16384, &tmK, &k_full[st], a * 64, kvh, j * 128, b);
-        mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
-        mbar_arrive_expect_tx(&v_full[st], Cfg::TILE);
+        const int sv = j % NSV;
+        const uint32_t phv = (j / NSV) & 1;
+        mbar_wait(&v_empty[sv], phv ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
+        mbar_arrive_expect_tx(&v_full[sv], Cfg::TILE);
 #pragma unroll
         for (int a = 0; a < ATOMS; ++a)
-          tma_load_4d(smem + Cfg::OFF_V + st * Cfg::TILE + a * 16384, &tmV, &v_full[st], a * 64, kvh, j * 128, b);
+          tma_load_4d(smem + Cfg::OFF_V + sv * Cfg::TILE + a * 16384, &tmV, &v_full[sv], a * 64, kvh, j * 128, b);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ---------------- MMA ----------------
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
       const uint32_t idesc_pv = make_idesc_bf16(128, D, 0, 1);
       const uint32_t sQ = smem_u32(smem + Cfg::OFF_Q);
+      auto issue_s = [&](int t, int j) {  // S_t = Q_t K_j^T
+        const uint32_t sK = smem_u32(smem + Cfg::OFF_K + (j & 1) * Cfg::TILE);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384u + (k & 3) * 32u;
+          umma_bf16_ss(tm_S + t * 128, make_smem_desc(sQ + t * Cfg::TILE + off, 16, 1024),
+                       make_smem_desc(sK + off, 16, 1024), idesc_s, k > 0);
+        }
+        umma_commit(&s_full[t]);
+      };
+      auto issue_pv = [&](int t, int j) {  // O_t = P_t V_j (fresh accumulator, folded by the softmax warps)
+        const uint32_t sP = smem_u32(smem + Cfg::OFF_P + t * Cfg::P_TILE);
+        const uint32_t sV = smem_u32(smem + Cfg::OFF_V + (j % NSV) * Cfg::TILE);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {  // 128 keys in steps of 16
+          const uint64_t da = make_smem_desc(sP + (k >> 2) * 16384u + (k & 3) * 32u, 16, 1024);
+          const uint64_t db = make_smem_desc(sV + k * 2048u, 16384, 1024);  // V is MN-major: [key][d]
+          umma_bf16_ss(tm_O + t * D, da, db, idesc_pv, k > 0);
+        }
+        umma_commit(&o_full[t]);
+      };
       mbar_wait(q_full, 0, abort_flag, p.status, FAULT_WAIT_ATTN);
-      for (int j = 0; j <= n_kv; ++j) {
-        if (j < n_kv) {
-          const int st = j & 1;
-          const uint32_t ph = (j >> 1) & 1;
-          mbar_wait(&k_full[st], ph, abort_flag, p.status, FAULT_WAIT_ATTN);
-          mbar_wait(&s_empty[st], ph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
+      mbar_wait(&k_full[0], 0, abort_flag, p.status, FAULT_WAIT_ATTN);
+      tc_fence_after_sync();
+      issue_s(0, 0);
+      if (b_valid) issue_s(1, 0);
+      umma_commit(&k_empty[0]);
+      for (int j = 0; j < n_kv; ++j) {
+        const uint32_t jph = j & 1;
+        const uint32_t phv = (j / NSV) & 1;
+        const bool more = j + 1 < n_kv;
+        const uint32_t kph1 = ((j + 1) >> 1) & 1;
+        if (j < nA) {
+          mbar_wait(&p_ready[0], jph, abort_flag, p.status, FAULT_WAIT_ATTN);
+          mbar_wait(&v_full[j % NSV], phv, abort_flag, p.status, FAULT_WAIT_ATTN);
           tc_fence_after_sync();
-          const uint32_t sK = smem_u32(smem + Cfg::OFF_K + st * Cfg::TILE);
-#pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t off = (k >> 2) * 16384u + (k & 3) * 32u;
-            umma_bf16_ss(tm_S + st * 128, make_smem_desc(sQ + off, 16, 1024), make_smem_desc(sK + off, 16, 1024),
-                         idesc_s, k > 0);
+          issue_pv(0, j);
+          if (j + 1 < nA) {
+            mbar_wait(&k_full[(j + 1) & 1], kph1, abort_flag, p.status, FAULT_WAIT_ATTN);
+            tc_fence_after_sync();
+            issue_s(0, j + 1);
           }
-          umma_commit(&s_full[st]);
-          umma_commit(&k_empty[st]);
         }
-        if (j > 0) {
-          const int jj = j - 1;
-          const int st = jj & 1;
-          const uint32_t ph = (jj >> 1) & 1;
-          mbar_wait(&p_ready[st], ph, abort_flag, p.status, FAULT_WAIT_ATTN);
-          mbar_wait(&v_full[st], ph, abort_flag, p.status, FAULT_WAIT_ATTN);
-          mbar_wait(&o_empty[st], ph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
+        if (j < nB) {
+          mbar_wait(&p_ready[1], jph, abort_flag, p.status, FAULT_WAIT_ATTN);
+          mbar_wait(&v_full[j % NSV], phv, abort_flag, p.status, FAULT_WAIT_ATTN);
           tc_fence_after_sync();
-          const uint32_t sP = smem_u32(smem + Cfg::OFF_P + st * Cfg::P_TILE);
-          const uint32_t sV = smem_u32(smem + Cfg::OFF_V + st * Cfg::TILE);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {  // 128 keys in steps of 16
-            const uint64_t da = make_smem_desc(sP + (k >> 2) * 16384u + (k & 3) * 32u, 16, 1024);
-            const uint64_t db = make_smem_desc(sV + k * 2048u, 16384, 1024);  // V is MN-major: [key][d]
-            umma_bf16_ss(tm_O + st * D, da, db, idesc_pv, k > 0);
+          issue_pv(1, j);
+          if (j + 1 < nB) {
+            mbar_wait(&k_full[(j + 1) & 1], kph1, abort_flag, p.status, FAULT_WAIT_ATTN);
+            tc_fence_after_sync();
+            issue_s(1, j + 1);
           }
-          umma_commit(&o_full[st]);
-          umma_commit(&v_empty[st]);
         }
+        umma_commit(&v_empty[j % NSV]);
+        if (more) umma_commit(&k_empty[(j + 1) & 1]);
       }
     }
   } else {
-    // ---------------- softmax + output (warps 0-3, thread = query row) ----------------
-    const int row = warp * 32 + lane;
+    // ---------------- softmax + output (warps 0-3: tile A, warps 4-7: tile B; thread = query row) -------------
+    const int t = warp >> 2;
+    const int n_mine = t ? nB : nA;
+    const int qt = t ? qtB : qtA;
+    const int row = (warp & 3) * 32 + lane;
     const int qrow = qt * 128 + row;
-    const uint32_t lane_off = uint32_t(warp * 32) << 16;
+    const uint32_t lane_off = uint32_t((warp & 3) * 32) << 16;
     const float sl2 = p.scale * LOG2E;
-    float m = -INFINITY, l = 0.0f, alpha_pending = 1.0f;
+    const uint32_t tS = tm_S + t * 128 + lane_off;
+    const uint32_t tO = tm_O + t * D + lane_off;
+    const uint32_t sP = smem_u32(smem + Cfg::OFF_P + t * Cfg::P_TILE);
+    float m = -INFINITY, l = 0.0f, alpha_prev = 1.0f;
     float acc[D];
 #pragma unroll
     for (int i = 0; i < D; ++i) acc[i] = 0.0f;
 
-    auto fold_tile = [&](int jj, float alpha) {
-      const int st = jj & 1;
-      const uint32_t ph = (jj >> 1) & 1;
-      mbar_wait(&o_full[st], ph, abort_flag, p.status, FAULT_WAIT_ATTN);
+    auto fold = [&](uint32_t ph, float alpha) {  // acc = acc * alpha + (P V of the finished tile)
+      mbar_wait(&o_full[t], ph, abort_flag, p.status, FAULT_WAIT_ATTN);
       tc_fence_after_sync();
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32b_x32(tm_O + st * D + c * 32 + lane_off, r);
+        tmem_ld_32x32b_x32(tO + c * 32, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[c * 32 + i] = acc[c * 32 + i] * alpha + __uint_as_float(r[i]);
+        for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, __uint_as_float(r[i]));
       }
       tc_fence_before_sync();
-      mbar_arrive(&o_empty[st]);
     };
 
-    for (int j = 0; j < n_kv; ++j) {
-      const int st = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
+    for (int j = 0; j < n_mine; ++j) {
+      const uint32_t jph = j & 1;
       const bool need_mask = (p.causal && j == qt) || ((j + 1) * 128 > p.S);
-      mbar_wait(&s_full[st], ph, abort_flag, p.status, FAULT_WAIT_ATTN);
+      mbar_wait(&s_full[t], jph, abort_flag, p.status, FAULT_WAIT_ATTN);
       tc_fence_after_sync();
-      const uint32_t tS = tm_S + st * 128 + lane_off;
       // pass 1: row maximum
       float mx = -INFINITY;
 #pragma unroll 1
@@ -235,22 +271,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         uint32_t r[32];
         tmem_ld_32x32b_x32(tS + c * 32, r);
         tmem_ld_wait();
+        if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(r[i]);
-          if (need_mask) {
+          for (int i = 0; i < 32; ++i) {
             const int kc = j * 128 + c * 32 + i;
-            if (kc >= p.S || (p.causal && kc > qrow)) s = -INFINITY;
+            if (!(kc >= p.S || (p.causal && kc > qrow))) mx = fmaxf(mx, __uint_as_float(r[i]));
           }
-          mx = fmaxf(mx, s);
+        } else {
+          float m0 = __uint_as_float(r[0]), m1 = __uint_as_float(r[1]), m2 = __uint_as_float(r[2]), m3 = __uint_as_float(r[3]);
+#pragma unroll
+          for (int i = 4; i < 32; i += 4) {
+            m0 = fmaxf(m0, __uint_as_float(r[i]));
+            m1 = fmaxf(m1, __uint_as_float(r[i + 1]));
+            m2 = fmaxf(m2, __uint_as_float(r[i + 2]));
+            m3 = fmaxf(m3, __uint_as_float(r[i + 3]));
+          }
+          mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
         }
       }
       const float m_new = fmaxf(m, mx);
       const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;  // a fully masked row keeps p = 0
-      const float alpha = exp2f((m - m_use) * sl2);
+      const float alpha = ex2_approx((m - m_use) * sl2);
+      const float msl2 = m_use * sl2;
+      // the previous tile's P V is complete by now (the tensor core ran it before this S)
+      if (j > 0) fold(jph ^ 1, alpha_prev);
       // pass 2: probabilities -> shared memory (bf16), row sum
-      float rs = 0.0f;
-      const uint32_t sP = smem_u32(smem + Cfg::OFF_P + st * Cfg::P_TILE);
+      float rs0 = 0.0f, rs1 = 0.0f;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t r[32];
@@ -259,47 +305,45 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float s0 = __uint_as_float(r[i]), s1 = __uint_as_float(r[i + 1]);
-          float p0 = exp2f((s0 - m_use) * sl2), p1 = exp2f((s1 - m_use) * sl2);
+          float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), sl2, -msl2));
+          float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), sl2, -msl2));
           if (need_mask) {
             const int kc = j * 128 + c * 32 + i;
             if (kc >= p.S || (p.causal && kc > qrow)) p0 = 0.0f;
             if (kc + 1 >= p.S || (p.causal && kc + 1 > qrow)) p1 = 0.0f;
           }
-          // the row sum uses the bf16-rounded values that the MMA will see
-          __nv_bfloat162 hb = __floats2bfloat162_rn(p0, p1);
-          float2 fb = __bfloat1622float2(hb);
-          rs += fb.x + fb.y;
-          pk[i >> 1] = *reinterpret_cast<uint32_t*>(&hb);
+          rs0 += p0;
+          rs1 += p1;
+          pk[i >> 1] = pack_bf16x2(p0, p1);
         }
         store_row_chunk32(sP, row, c * 32, pk);
       }
-      l = l * alpha + rs;
+      l = fmaf(l, alpha, rs0 + rs1);
       m = m_new;
+      alpha_prev = alpha;
       tc_fence_before_sync();
-      mbar_arrive(&s_empty[st]);
       fence_proxy_async_smem();
-      mbar_arrive(&p_ready[st]);
-      // fold the previous tile's PV while the tensor core works on this one
-      if (j > 0) fold_tile(j - 1, alpha_pending);
-      alpha_pending = alpha;
+      mbar_arrive(&p_ready[t]);
     }
-    if (n_kv > 0) fold_tile(n_kv - 1, alpha_pending);
-
-    if (qrow < p.S) {
-      const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
-      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + (long long)b * p.o_bs + (long long)qrow * p.o_ss +
-                            (long long)h * p.o_hs;
+    if (n_mine > 0) {
+      // the last fold needs no rescale beyond the one already folded into l: acc is scaled to the
+      // running maximum of the tile before, so apply the last alpha
+      fold((n_mine - 1) & 1, alpha_prev);
+      if (qrow < p.S) {
+        const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
+        __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + (long long)b * p.o_bs + (long long)qrow * p.o_ss +
+                              (long long)h * p.o_hs;
 #pragma unroll
-      for (int c = 0; c < D / 8; ++c) {
-        uint4 o;
-        o.x = pack_bf16x2(acc[c * 8 + 0] * inv, acc[c * 8 + 1] * inv);
-        o.y = pack_bf16x2(acc[c * 8 + 2] * inv, acc[c * 8 + 3] * inv);
-        o.z = pack_bf16x2(acc[c * 8 + 4] * inv, acc[c * 8 + 5] * inv);
-        o.w = pack_bf16x2(acc[c * 8 + 6] * inv, acc[c * 8 + 7] * inv);
-        reinterpret_cast<uint4*>(orow)[c] = o;
+        for (int c = 0; c < D / 8; ++c) {
+          uint4 o;
+          o.x = pack_bf16x2(acc[c * 8 + 0] * inv, acc[c * 8 + 1] * inv);
+          o.y = pack_bf16x2(acc[c * 8 + 2] * inv, acc[c * 8 + 3] * inv);
+          o.z = pack_bf16x2(acc[c * 8 + 4] * inv, acc[c * 8 + 5] * inv);
+          o.w = pack_bf16x2(acc[c * 8 + 6] * inv, acc[c * 8 + 7] * inv);
+          reinterpret_cast<uint4*>(orow)[c] = o;
+        }
+        if (p.lse) p.lse[((long long)b * p.Hq + h) * p.S + qrow] = (l > 0.0f) ? m * p.scale + logf(l) : -INFINITY;
       }
-      if (p.lse) p.lse[((long long)b * p.Hq + h) * p.S + qrow] = (l > 0.0f) ? m * p.scale + logf(l) : -INFINITY;
     }
   }
 
@@ -308,12 +352,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (*abort_flag) {
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
 }
-
 // =====================================================================================
 // backward
 // =====================================================================================
@@ -657,16 +700,16 @@ int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, vo
   p.causal = causal; p.scale = scale;
   p.o = o; p.o_bs = o_bs; p.o_ss = o_ss; p.o_hs = o_hs;
   p.lse = lse; p.status = status;
-  dim3 grid((unsigned)((S + 127) / 128), (unsigned)Hq, (unsigned)B);
+  dim3 grid((unsigned)(((S + 127) / 128 + 1) / 2), (unsigned)Hq, (unsigned)B);  // two query tiles per CTA
   cudaStream_t s = (cudaStream_t)stream;
   if (D == 64) {
     static bool set64 = false;
     if (!set64) { if (cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<64>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute"); set64 = true; }
-    attn_fwd_kernel<64><<<grid, 192, FwdCfg<64>::SMEM, s>>>(tq, tk, tv, p);
+    attn_fwd_kernel<64><<<grid, 320, FwdCfg<64>::SMEM, s>>>(tq, tk, tv, p);
   } else {
     static bool set128 = false;
     if (!set128) { if (cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<128>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute"); set128 = true; }
-    attn_fwd_kernel<128><<<grid, 192, FwdCfg<128>::SMEM, s>>>(tq, tk, tv, p);
+    attn_fwd_kernel<128><<<grid, 320, FwdCfg<128>::SMEM, s>>>(tq, tk, tv, p);
   }
   return check_launch("attn_fwd");
 }
