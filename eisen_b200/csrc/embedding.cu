@@ -232,3 +232,58 @@ int eisen_embedding_bwd_bookkeeping(void* stream, const void* workspace, long lo
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// Embedding backward without any allocation by the caller or by this library.
+//
+// Some hosts of this library own every byte of device memory themselves and cannot hand out a
+// workspace on demand: an engine that runs under a fixed VRAM budget and accounts each buffer
+// in its own pool (the way the reference's Graph does with EISEN_VRAM_BUDGET_MB), or a training
+// loop that must not call cudaMalloc in the middle of a step because the call synchronises the
+// device.  For them the integer bookkeeping of the scatter (count, offset, rank, perm) lives in
+// a fixed array inside the library image instead of a caller-provided workspace.
+//
+// The array is part of the module: every GPU that loads the library holds
+// (2 * 131072 + 2 * 65536) * 4 bytes = 1.5 MB of it until the process exits.
+// ---------------------------------------------------------------------------------------
+namespace {
+constexpr long long kStaticMaxIds = 65536;     // token positions per call
+constexpr long long kStaticMaxVocab = 131072;  // rows of the embedding table
+static __device__ __align__(256) int g_embedding_static_scratch[2 * kStaticMaxVocab + 2 * kStaticMaxIds];
+
+// Device address of the array, looked up once per device.  In host code the array's name is only
+// a handle for the runtime, not an address a kernel could use, so it goes through
+// cudaGetSymbolAddress with the target device current.
+int* static_scratch_for_current_device(const char** err) {
+  static int* ptrs[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    *err = "embedding_bwd_static: cannot identify the current device";
+    return nullptr;
+  }
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_embedding_static_scratch);
+    if (e != cudaSuccess || !p) {
+      *err = "embedding_bwd_static: cudaGetSymbolAddress failed for the scratch array";
+      return nullptr;
+    }
+    ptrs[dev] = static_cast<int*>(p);
+  }
+  return ptrs[dev];
+}
+}  // namespace
+
+extern "C" int eisen_embedding_bwd_static(void* stream, const void* g, int g_dt, const int* ids, float* dw,
+                                          long long n_ids, long long dim, long long vocab) {
+  if (n_ids > kStaticMaxIds || vocab > kStaticMaxVocab)
+    return fail(EISEN_ERR_LIMIT,
+                "embedding_bwd_static: at most 65536 ids and 131072 table rows fit the built-in scratch; "
+                "use eisen_embedding_bwd with a workspace for larger sizes");
+  const char* err = nullptr;
+  int* scratch = static_scratch_for_current_device(&err);
+  if (!scratch) return fail(EISEN_ERR_CUDA, err);
+  // same kernels as eisen_embedding_bwd; its first step clears count[0..vocab), the only part of
+  // the scratch that has to start at zero (offset, rank and perm are fully rewritten)
+  return eisen_embedding_bwd(stream, g, g_dt, ids, dw, scratch, n_ids, dim, vocab);
+}

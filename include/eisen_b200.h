@@ -186,6 +186,19 @@ int eisen_embedding_bwd(void* stream, const void* g, int g_dtype, const int* ids
 int eisen_embedding_bwd_bookkeeping(void* stream, const void* workspace, long long n_ids, long long vocab,
                                     int* count_out, int* offset_out, int* perm_out);
 
+/* Embedding backward for callers that cannot allocate device memory (no counterpart in the
+ * reference).  Same result as eisen_embedding_bwd, but the integer scratch (count, offset, rank,
+ * perm) is a fixed 1.5 MB array inside the library instead of a caller-provided workspace: meant
+ * for hosts that own all device memory under a fixed budget, or that must not call cudaMalloc
+ * inside a training step.  Limits: n_ids <= 65536 and vocab <= 131072, larger sizes return
+ * EISEN_ERR_LIMIT.  The call allocates nothing.  The first call on each device looks up the
+ * array's device address (cudaGetSymbolAddress, with that device current); make that first call
+ * before any stream capture.  All calls on a device share the one array and it keeps the last
+ * call's contents (each call clears the part that must start at zero), so two calls that overlap
+ * on the GPU, e.g. on different streams, race: keep them on one stream or otherwise ordered. */
+int eisen_embedding_bwd_static(void* stream, const void* g, int g_dtype, const int* ids, float* dw,
+                               long long n_ids, long long dim, long long vocab);
+
 /* ------------------------------------------------------------------------------------------
  * Optimizer
  * ------------------------------------------------------------------------------------------ */
