@@ -47,6 +47,7 @@ def main():
     ap.add_argument("--b-mn", type=int, default=1)
     ap.add_argument("--out-mode", type=int, default=0)
     ap.add_argument("--split-k", type=int, default=0)
+    ap.add_argument("--gemm-mode", type=int, default=-1, help="eisen_gemm_set_mode value (default: leave as is)")
     ap.add_argument("--batch", type=int, default=2)
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=8)
@@ -62,6 +63,8 @@ def main():
     s = torch.cuda.current_stream().cuda_stream
     st = torch.zeros(1, dtype=torch.int32, device=dev)
     out = {"case": a.case}
+    if a.gemm_mode >= 0:
+        eb.call("eisen_gemm_set_mode", a.gemm_mode)
     if a.case == "gemm":
         M, N, K = a.m, a.n, a.k
         A = torch.randn((K, M) if a.a_mn else (M, K), device=dev).to(torch.bfloat16)

@@ -612,28 +612,36 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
-// delta[b,h,s] = sum_d o[b,s,h,d] * do[b,s,h,d]; one warp per (b,s,h)
+// delta[b,h,s] = sum_d o[b,s,h,d] * do[b,s,h,d]; D/8 lanes per (b,s,h) row, 16 bytes per lane
+template <int D>
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
-                  int B, int S, int H, int D, long long bs, long long ss, long long hs) {
-  const int lane = threadIdx.x & 31;
-  const long long warp0 = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+                  int B, int S, int H, long long bs, long long ss, long long hs) {
+  constexpr int LPR = D / 8;  // lanes per row (8 or 16)
   const long long total = (long long)B * S * H;
-  for (long long w = warp0; w < total; w += (long long)gridDim.x * 8) {
+  const int lane = threadIdx.x & 31;
+  // the loop runs on warp bases so that every lane of a warp takes part in each shuffle
+  for (long long tb = blockIdx.x * (long long)blockDim.x + (threadIdx.x - lane); tb < total * LPR;
+       tb += (long long)gridDim.x * blockDim.x) {
+    const long long t = tb + lane;
+    const bool valid = t < total * LPR;
+    const long long w = valid ? t / LPR : 0;
+    const int c = (int)(t % LPR) * 8;
     const int h = (int)(w % H);
     const int s = (int)((w / H) % S);
     const int b = (int)(w / ((long long)H * S));
-    const long long off = (long long)b * bs + (long long)s * ss + (long long)h * hs;
+    const long long off = (long long)b * bs + (long long)s * ss + (long long)h * hs + c;
     float acc = 0.0f;
-    for (int c = lane * 8; c < D; c += 256) {
+    if (valid) {
       float x[8], y[8];
-      ld16(o + off + c, x);
-      ld16(d_o + off + c, y);
+      ld16(o + off, x);
+      ld16(d_o + off, y);
 #pragma unroll
       for (int k = 0; k < 8; ++k) acc += x[k] * y[k];
     }
-    acc = warp_sum(acc);
-    if (lane == 0) delta[((long long)b * H + h) * S + s] = acc;
+#pragma unroll
+    for (int m = LPR / 2; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+    if (valid && (t % LPR) == 0) delta[((long long)b * H + h) * S + s] = acc;
   }
 }
 
@@ -736,8 +744,13 @@ int eisen_attn_bwd(void* stream, const void* q, const void* k, const void* v, co
   float* dq_acc = (float*)workspace;
   float* delta = dq_acc + B * S * Hq * D;
   if (cudaMemsetAsync(dq_acc, 0, (size_t)(B * S * Hq * D) * 4, s) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_bwd: memset failed");
-  attn_delta_kernel<<<grid_for(B * S * Hq, 8, 8), 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta,
-                                                                (int)B, (int)S, (int)Hq, (int)D, o_bs, o_ss, o_hs);
+  // total threads is a multiple of 32 (S*H*D/8 with D/8 in {8,16}), so every shuffle group is complete
+  if (D == 64)
+    attn_delta_kernel<64><<<grid_for(B * S * Hq * 8, 256, 8), 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o,
+                                                                          delta, (int)B, (int)S, (int)Hq, o_bs, o_ss, o_hs);
+  else
+    attn_delta_kernel<128><<<grid_for(B * S * Hq * 16, 256, 8), 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o,
+                                                                            delta, (int)B, (int)S, (int)Hq, o_bs, o_ss, o_hs);
   rc = check_launch("attn_delta");
   if (rc) return rc;
   CUtensorMap tq, tk, tv, tdo;

@@ -11,6 +11,7 @@ namespace eisen {
 
 static thread_local char g_err[512] = "";
 static std::atomic<long long> g_launches{0};
+std::atomic<int> g_gemm_mode{0};  // 0 = choose per shape, 1 = single-CTA tiles only, 2 = paired-CTA tiles only
 
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
@@ -38,6 +39,11 @@ extern "C" {
 const char* eisen_last_error(void) { return eisen::g_err; }
 const char* eisen_version(void) { return "eisen_b200 0.1 (sm_100a)"; }
 long long eisen_launch_count(void) { return eisen::g_launches.load(); }
+int eisen_gemm_set_mode(int mode) {
+  if (mode < 0 || mode > 2) return eisen::fail(EISEN_ERR_INVALID, "gemm_set_mode: mode must be 0, 1 or 2");
+  eisen::g_gemm_mode.store(mode);
+  return 0;
+}
 
 int eisen_gemm_bf16(void* stream, int a_mn, int b_mn, long long M, long long N, long long K, const void* A,
                     long long lda, const void* B, long long ldb, void* C, long long ldc, int out_mode,
@@ -45,12 +51,19 @@ int eisen_gemm_bf16(void* stream, int a_mn, int b_mn, long long M, long long N, 
   if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL)
     return eisen::fail(EISEN_ERR_LIMIT, "gemm_bf16: a dimension exceeds 2^31-1");
   if (out_mode < 0 || out_mode > 4) return eisen::fail(EISEN_ERR_INVALID, "gemm_bf16: bad out_mode");
+  // tile shape: the paired-CTA kernel (256 x 256 per cluster) when the problem has at least one
+  // full pair tile in each dimension, else the single-CTA kernel (128 x 256)
+  const int mode = eisen::g_gemm_mode.load();
+  const bool pair = mode == 2 || (mode == 0 && M >= 256 && N >= 128);
   if (split_k == 0) {
-    split_k = (out_mode == eisen::GEMM_OUT_F32_ATOMIC) ? eisen::gemm_tc_auto_split_k((int)M, (int)N, (int)K) : 1;
+    if (out_mode != eisen::GEMM_OUT_F32_ATOMIC) split_k = 1;
+    else split_k = pair ? eisen::gemm_pair_auto_split_k((int)M, (int)N, (int)K) : eisen::gemm_tc_auto_split_k((int)M, (int)N, (int)K);
   }
   const char* err = nullptr;
-  int rc = eisen::gemm_bf16_tc((cudaStream_t)stream, a_mn, b_mn, (int)M, (int)N, (int)K, A, lda, B, ldb, C, ldc,
-                               out_mode, split_k, alpha, status, &err);
+  int rc = pair ? eisen::gemm_bf16_tc_pair((cudaStream_t)stream, a_mn, b_mn, (int)M, (int)N, (int)K, A, lda, B, ldb, C, ldc,
+                                           out_mode, split_k, alpha, status, &err)
+                : eisen::gemm_bf16_tc((cudaStream_t)stream, a_mn, b_mn, (int)M, (int)N, (int)K, A, lda, B, ldb, C, ldc,
+                                      out_mode, split_k, alpha, status, &err);
   if (rc) return eisen::fail(rc == 1 ? EISEN_ERR_INVALID : EISEN_ERR_CUDA, err ? err : "gemm_bf16 failed");
   if (M > 0 && N > 0 && K > 0) eisen::count_launch();
   return 0;

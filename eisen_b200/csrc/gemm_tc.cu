@@ -16,6 +16,7 @@
 // accumulators, so the epilogue of tile i overlaps the main loop of tile i+1).
 #include "ptx.cuh"
 #include "gemm_tc.h"
+#include "gemm_epilogue.cuh"
 
 #include <cuda.h>
 #include <cstdio>
@@ -202,70 +203,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         float v[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-        const bool full = (col0 + 32 <= p.N);
-        if (p.out_mode == GEMM_OUT_BF16 || p.out_mode == GEMM_OUT_BF16_ACC) {
-          __nv_bfloat16* c_row = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
-          const bool vec = full && ((reinterpret_cast<uintptr_t>(c_row) & 15) == 0);
-          if (vec) {
-            uint4* dst = reinterpret_cast<uint4*>(c_row);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (p.out_mode == GEMM_OUT_BF16_ACC) {
-                uint4 old = dst[j];
-                const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&old);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  float2 f = __bfloat1622float2(o2[e]);
-                  v[j * 8 + 2 * e] += f.x;
-                  v[j * 8 + 2 * e + 1] += f.y;
-                }
-              }
-              uint4 o;
-              o.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
-              o.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
-              o.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
-              o.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
-              dst[j] = o;
-            }
-          } else {
-            for (int i = 0; i < 32 && col0 + i < p.N; ++i) {
-              float x = v[i];
-              if (p.out_mode == GEMM_OUT_BF16_ACC) x += __bfloat162float(c_row[i]);
-              c_row[i] = __float2bfloat16(x);
-            }
-          }
-        } else {
-          float* c_row = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
-          const bool vec = full && ((reinterpret_cast<uintptr_t>(c_row) & 15) == 0);
-          if (p.out_mode == GEMM_OUT_F32_ATOMIC) {
-            if (vec) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(c_row + 4 * j),
-                             "f"(v[4 * j]), "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
-                             : "memory");
-            } else {
-              for (int i = 0; i < 32 && col0 + i < p.N; ++i) atomicAdd(c_row + i, v[i]);
-            }
-          } else if (vec) {
-            float4* dst = reinterpret_cast<float4*>(c_row);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-              if (p.out_mode == GEMM_OUT_F32_ACC) {
-                float4 old = dst[j];
-                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-              }
-              dst[j] = o;
-            }
-          } else {
-            for (int i = 0; i < 32 && col0 + i < p.N; ++i) {
-              float x = v[i];
-              if (p.out_mode == GEMM_OUT_F32_ACC) x += c_row[i];
-              c_row[i] = x;
-            }
-          }
-        }
+        gemm_store_chunk32(p.C, p.ldc, p.out_mode, row, col0, p.N, v);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -399,6 +337,8 @@ int gemm_bf16_tc(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int K, c
   if (e != cudaSuccess) { if (err) *err = cudaGetErrorString(e); return 3; }
   return 0;
 }
+
+int gemm_num_sms() { return num_sms(); }
 
 int gemm_tc_auto_split_k(int M, int N, int K) {
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);

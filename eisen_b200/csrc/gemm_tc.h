@@ -20,6 +20,13 @@ int gemm_bf16_tc(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int K, c
                  long long lda, const void* B, long long ldb, void* C, long long ldc, int out_mode,
                  int split_k, float alpha, int* status, const char** err);
 
+// paired-CTA (cta_group::2) variant: 256 x 256 tile per cluster of two CTAs (gemm_tc2.cu)
+int gemm_bf16_tc_pair(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int K, const void* A, long long lda,
+                      const void* B, long long ldb, void* C, long long ldc, int out_mode, int split_k, float alpha,
+                      int* status, const char** err);
+int gemm_pair_auto_split_k(int M, int N, int K);
+int gemm_num_sms();
+
 // split factor that fills the machine when M*N alone gives fewer tiles than SMs
 int gemm_tc_auto_split_k(int M, int N, int K);
 

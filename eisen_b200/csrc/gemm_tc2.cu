@@ -1,0 +1,313 @@
+// Paired-CTA variant of the bf16 tcgen05 GEMM (see gemm_tc.cu for the operand conventions).
+//
+// Two CTAs of a cluster work on one 256 x 256 output tile: each CTA stages its own 128 rows of A
+// and its own 128 columns of B (32 KB per k-block instead of 48 KB for a 128 x 256 tile), the
+// leader CTA issues tcgen05.mma.cta_group::2 with M = 256, and each CTA's TMEM receives its
+// 128 x 256 half of the accumulator.  The 128 x 256 single-CTA tile is limited by the ~64 B/clk
+// at which an SM can take in operands (48 KB per 512 tensor-core clocks); the pair needs 32 KB
+// per 512 clocks.  No load is broadcast between the CTAs: each issues its own TMA loads, which
+// report their bytes to the leader's barrier.
+#include "ptx.cuh"
+#include "gemm_tc.h"
+#include "gemm_epilogue.cuh"
+
+#include <cuda.h>
+#include <cstdio>
+#include <cstdlib>
+
+namespace eisen {
+namespace {
+
+constexpr int PM = 128;   // rows per CTA (256 per pair)
+constexpr int PN = 256;   // columns per pair (128 staged per CTA)
+constexpr int BK = 64;
+constexpr int PSTAGES = 6;
+constexpr int PA_BYTES = PM * BK * 2;        // 16 KB
+constexpr int PB_BYTES = (PN / 2) * BK * 2;  // 16 KB
+constexpr int PSTAGE_BYTES = PA_BYTES + PB_BYTES;
+constexpr int P_THREADS = 192;
+constexpr int P_ACC_COLS = PN;
+constexpr int P_SMEM = PSTAGES * PSTAGE_BYTES + 1024 + 256;
+
+struct PairParams {
+  int M, N, K;
+  int a_mn, b_mn;
+  void* C;
+  long long ldc;
+  int out_mode;
+  int split_k, kblocks_per_split, kblocks_total;
+  int m_tiles, n_tiles, total_tiles;  // m_tiles counts 256-row pair tiles
+  float alpha;
+  int* status;
+};
+
+__global__ void __launch_bounds__(P_THREADS, 1)
+gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const PairParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + PSTAGES * PA_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PSTAGES * PSTAGE_BYTES);
+  uint64_t* full_bar = bars;                       // [PSTAGES]  used in the leader (2 arrivals + bytes of both CTAs)
+  uint64_t* empty_bar = bars + PSTAGES;            // [PSTAGES]  one per CTA, signalled by the leader's commits
+  uint64_t* tmem_full_bar = bars + 2 * PSTAGES;    // [2]        one per CTA, signalled by the leader's commits
+  uint64_t* tmem_empty_bar = bars + 2 * PSTAGES + 2;  // [2]     used in the leader (8 arrivals: 4 warps per CTA)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * PSTAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const uint32_t peer = rank ^ 1u;
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PSTAGES; ++s) {
+      mbar_init(&full_bar[s], 2);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full_bar[a], 1);
+      mbar_init(&tmem_empty_bar[a], 8);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 2 * P_ACC_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised before anyone signals across the pair
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_mn = p.m_tiles * p.n_tiles;
+  const int cluster_id = blockIdx.x >> 1;
+  const int n_clusters = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (each CTA loads its own slices) ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = cluster_id; t < p.total_tiles; t += n_clusters) {
+        const int ks = t / tiles_mn;
+        const int mn = t - ks * tiles_mn;
+        const int mt = mn % p.m_tiles;
+        const int nt = mn / p.m_tiles;
+        const int m0 = mt * (2 * PM) + (int)rank * PM;
+        const int n0 = nt * PN + (int)rank * (PN / 2);
+        const int kb0 = ks * p.kblocks_per_split;
+        const int kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, FAULT_WAIT_EMPTY);
+          const uint32_t full_leader = mapa_cluster(smem_u32(&full_bar[stage]), 0);
+          mbar_arrive_expect_tx_cluster(full_leader, PSTAGE_BYTES);
+          uint8_t* sa = smem_a + stage * PA_BYTES;
+          uint8_t* sb = smem_b + stage * PB_BYTES;
+          const int k0 = kb * BK;
+          if (!p.a_mn) {
+            tma_load_2d_pair(sa, &tmA, full_leader, k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < PM / 64; ++j) tma_load_2d_pair(sa + j * (64 * BK * 2), &tmA, full_leader, m0 + 64 * j, k0);
+          }
+          if (!p.b_mn) {
+            tma_load_2d_pair(sb, &tmB, full_leader, k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < (PN / 2) / 64; ++j)
+              tma_load_2d_pair(sb + j * (64 * BK * 2), &tmB, full_leader, n0 + 64 * j, k0);
+          }
+          if (++stage == PSTAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (leader && lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(2 * PM, PN, p.a_mn, p.b_mn);
+      const uint32_t a_lbo = p.a_mn ? 64 * BK * 2 : 16, a_sbo = 1024;
+      const uint32_t b_lbo = p.b_mn ? 64 * BK * 2 : 16, b_sbo = 1024;
+      const uint32_t a_kstep = p.a_mn ? 16 * 128 : 32;
+      const uint32_t b_kstep = p.b_mn ? 16 * 128 : 32;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int t = cluster_id; t < p.total_tiles; t += n_clusters) {
+        const int ks = t / tiles_mn;
+        const int kb0 = ks * p.kblocks_per_split;
+        const int kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
+        mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag, p.status, FAULT_WAIT_TMEM_EMPTY);
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * P_ACC_COLS;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          mbar_wait(&full_bar[stage], phase, abort_flag, p.status, FAULT_WAIT_FULL);
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem_a + stage * PA_BYTES);
+          const uint32_t sb = smem_u32(smem_b + stage * PB_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = make_smem_desc(sa + k * a_kstep, a_lbo, a_sbo);
+            const uint64_t db = make_smem_desc(sb + k * b_kstep, b_lbo, b_sbo);
+            umma_bf16_ss_pair(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          // release the stage in both CTAs once these MMAs have read it
+          const uint32_t e_local = smem_u32(&empty_bar[stage]);
+          umma_commit_pair(mapa_cluster(e_local, 0));
+          umma_commit_pair(mapa_cluster(e_local, 1));
+          if (++stage == PSTAGES) { stage = 0; phase ^= 1; }
+        }
+        const uint32_t f_local = smem_u32(&tmem_full_bar[acc]);
+        umma_commit_pair(mapa_cluster(f_local, 0));
+        umma_commit_pair(mapa_cluster(f_local, 1));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ---------------- epilogue: this CTA's 128 x 256 half, TMEM -> registers -> global ----------------
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = cluster_id; t < p.total_tiles; t += n_clusters) {
+      const int ks = t / tiles_mn;
+      const int mn = t - ks * tiles_mn;
+      const int mt = mn % p.m_tiles;
+      const int nt = mn / p.m_tiles;
+      const int row = mt * (2 * PM) + (int)rank * PM + q * 32 + lane;
+      const int n0 = nt * PN;
+      const int kb0 = ks * p.kblocks_per_split;
+      const bool has_k = kb0 < p.kblocks_total;
+      mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag, p.status, FAULT_WAIT_TMEM_FULL);
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + acc * P_ACC_COLS + (uint32_t(q * 32) << 16);
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = 0; c < PN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (!row_ok || col0 >= p.N || !has_k) continue;
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+        gemm_store_chunk32(p.C, p.ldc, p.out_mode, row, col0, p.N, v);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&tmem_empty_bar[acc]), 0));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  cluster_sync_all();  // neither CTA leaves while the other may still signal it or read its operands
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, 2 * P_ACC_COLS);
+  }
+  (void)peer;
+}
+
+}  // namespace
+
+int gemm_bf16_tc_pair(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int K, const void* A, long long lda,
+                      const void* B, long long ldb, void* C, long long ldc, int out_mode, int split_k, float alpha,
+                      int* status, const char** err) {
+  static bool attr_set = false;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) {
+    if (err) *err = "gemm_bf16_tc: operand rows must be 16-byte aligned (leading dimension % 8 == 0)";
+    return 1;
+  }
+  if (split_k < 1) split_k = 1;
+  if (split_k > 1 && out_mode != GEMM_OUT_F32_ATOMIC) {
+    if (err) *err = "gemm_bf16_tc: split_k > 1 needs the f32 atomic output mode";
+    return 1;
+  }
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!a_mn) rc = make_tmap_bf16_2d(&tmA, A, K, M, lda, 64, PM);
+  else       rc = make_tmap_bf16_2d(&tmA, A, M, K, lda, 64, BK);
+  if (rc) { if (err) *err = "gemm_bf16_tc: cuTensorMapEncodeTiled failed for A"; return 2; }
+  if (!b_mn) rc = make_tmap_bf16_2d(&tmB, B, K, N, ldb, 64, PN / 2);
+  else       rc = make_tmap_bf16_2d(&tmB, B, N, K, ldb, 64, BK);
+  if (rc) { if (err) *err = "gemm_bf16_tc: cuTensorMapEncodeTiled failed for B"; return 2; }
+
+  PairParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.a_mn = a_mn; p.b_mn = b_mn;
+  p.C = C; p.ldc = ldc; p.out_mode = out_mode;
+  p.m_tiles = (M + 2 * PM - 1) / (2 * PM);
+  p.n_tiles = (N + PN - 1) / PN;
+  p.kblocks_total = (K + BK - 1) / BK;
+  if (split_k > p.kblocks_total) split_k = p.kblocks_total;
+  p.kblocks_per_split = (p.kblocks_total + split_k - 1) / split_k;
+  split_k = (p.kblocks_total + p.kblocks_per_split - 1) / p.kblocks_per_split;
+  p.split_k = split_k;
+  p.total_tiles = p.m_tiles * p.n_tiles * split_k;
+  p.alpha = alpha;
+  p.status = status;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM);
+    if (e != cudaSuccess) { if (err) *err = cudaGetErrorString(e); return 3; }
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * (gemm_num_sms() / 2), 1, 1);
+  cfg.blockDim = dim3(P_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = P_SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // persistent grid: as many clusters as can be resident at once (SM pairs must share a TPC)
+  static int max_clusters = 0;
+  if (!max_clusters) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_tc2_kernel, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = gemm_num_sms() / 2;
+    }
+    max_clusters = n;
+    if (getenv("EISEN_DEBUG")) fprintf(stderr, "[eisen] paired-CTA GEMM: %d resident clusters on %d SMs\n", n, gemm_num_sms());
+  }
+  const int clusters = p.total_tiles < max_clusters ? p.total_tiles : max_clusters;
+  cfg.gridDim = dim3(2 * clusters, 1, 1);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_tc2_kernel, tmA, tmB, p);
+  if (e != cudaSuccess) { if (err) *err = cudaGetErrorString(e); return 3; }
+  return 0;
+}
+
+int gemm_pair_clusters_hint() { return gemm_num_sms() / 2; }
+
+int gemm_pair_auto_split_k(int M, int N, int K) {
+  const int tiles = ((M + 2 * PM - 1) / (2 * PM)) * ((N + PN - 1) / PN);
+  const int kblocks = (K + BK - 1) / BK;
+  const int clusters = gemm_num_sms() / 2;
+  if (tiles >= clusters) return 1;
+  int s = (2 * clusters + tiles - 1) / tiles;
+  int max_s = kblocks / 8;
+  if (max_s < 1) max_s = 1;
+  if (s > max_s) s = max_s;
+  return s < 1 ? 1 : s;
+}
+
+}  // namespace eisen

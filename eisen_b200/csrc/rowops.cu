@@ -43,10 +43,15 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const float* __restrict__ w, T* __re
     if (rrms_out && lane == 0) rrms_out[row] = rrms;
     if (vec) {
       for (int c = lane * V; c < dim; c += 32 * V) {
-        float v[V];
+        float v[V], wv[V];
         ld16(xr + c, v);
 #pragma unroll
-        for (int k = 0; k < V; ++k) v[k] = v[k] * rrms * w[c + k];
+        for (int k = 0; k < V; k += 4) {
+          const float4 t = *reinterpret_cast<const float4*>(w + c + k);
+          wv[k] = t.x; wv[k + 1] = t.y; wv[k + 2] = t.z; wv[k + 3] = t.w;
+        }
+#pragma unroll
+        for (int k = 0; k < V; ++k) v[k] = v[k] * rrms * wv[k];
         st16(yr + c, v);
       }
     } else {
@@ -71,11 +76,16 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w, const T
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long warp0 = (long long)blockIdx.x * RN_WARPS + warp;
   const long long wstride = (long long)gridDim.x * RN_WARPS;
-  float dwp[NCH][V];
+  float dwp[NCH][V], wv[NCH][V];  // a lane owns the same columns for every row: weights stay in registers
 #pragma unroll
-  for (int j = 0; j < NCH; ++j)
+  for (int j = 0; j < NCH; ++j) {
+    const int c = (j * 32 + lane) * V;
 #pragma unroll
-    for (int k = 0; k < V; ++k) dwp[j][k] = 0.0f;
+    for (int k = 0; k < V; ++k) {
+      dwp[j][k] = 0.0f;
+      wv[j][k] = (c < dim) ? w[c + k] : 0.0f;
+    }
+  }
 
   for (long long row = warp0; row < rows; row += wstride) {
     const T* xr = x + row * dim;
@@ -92,7 +102,7 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w, const T
 #pragma unroll
         for (int k = 0; k < V; ++k) {
           ss += xv[j][k] * xv[j][k];
-          gdxw += gv[j][k] * xv[j][k] * w[c + k];
+          gdxw += gv[j][k] * xv[j][k] * wv[j][k];
         }
       }
     }
@@ -107,7 +117,7 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w, const T
         float o[V];
 #pragma unroll
         for (int k = 0; k < V; ++k) {
-          o[k] = rrms * (gv[j][k] * w[c + k]) - xv[j][k] * rrc_d * gdxw;
+          o[k] = rrms * (gv[j][k] * wv[j][k]) - xv[j][k] * rrc_d * gdxw;
           dwp[j][k] += gv[j][k] * xv[j][k] * rrms;
         }
         if (acc_dx) {

@@ -65,6 +65,11 @@ int eisen_gemm_bf16(void* stream, int a_mn, int b_mn, long long M, long long N, 
                     long long lda, const void* B, long long ldb, void* C, long long ldc, int out_mode,
                     int split_k, float alpha, int* status);
 
+/* Tile shape of eisen_gemm_bf16: 0 = chosen per problem shape, 1 = single-CTA 128x256 tiles,
+ * 2 = paired-CTA 256x256 tiles (tcgen05 cta_group::2, one cluster of two CTAs per tile).
+ * Process-wide; meant for tests and measurements. */
+int eisen_gemm_set_mode(int mode);
+
 /* f32 SIMT GEMM with element strides and a batch dimension (f32 parity path):
  *   C[b,m,n] (+)= sum_k A[b*a_bs + m*a_ms + k*a_ks] * B[b*b_bs + k*b_ks + n*b_ns]
  * Replaces the same reference kernels for f32 tensors plus bmm_f32 and bmm_backward_*

@@ -48,12 +48,42 @@ def test_gemm_bf16_majors(a_mn, b_mn, M, N, K):
     Bd = (B.t().contiguous() if b_mn else B).to(dev())
     C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
     st = status_word()
-    eb.call("eisen_gemm_bf16", stream(), a_mn, b_mn, M, N, K, P(Ad), Ad.stride(0), P(Bd), Bd.stride(0), P(C), N, 0, 1, 1.0, P(st))
-    torch.cuda.synchronize()
+    eb.call("eisen_gemm_set_mode", 1)  # single-CTA 128x256 tiles
+    try:
+        eb.call("eisen_gemm_bf16", stream(), a_mn, b_mn, M, N, K, P(Ad), Ad.stride(0), P(Bd), Bd.stride(0), P(C), N, 0, 1, 1.0, P(st))
+        torch.cuda.synchronize()
+    finally:
+        eb.call("eisen_gemm_set_mode", 0)
     assert int(st.item()) == 0
     out = C.float().cpu()
     assert torch.isfinite(out).all()
     assert rel_l2(out.numpy(), ref.numpy()) < 4e-3  # bf16 output rounding
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 320), (384, 512, 1088), (200, 136, 72), (2048, 1024, 512)])
+def test_gemm_bf16_paired_cta_tiles(a_mn, b_mn, M, N, K):
+    """256x256 tiles computed by two CTAs of a cluster (tcgen05 cta_group::2)."""
+    g = torch.Generator(device="cpu").manual_seed(M + N * 3 + K * 5 + a_mn * 2 + b_mn)
+    A = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    B = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    ref = A.float() @ B.float().t()
+    Ad = (A.t().contiguous() if a_mn else A).to(dev())
+    Bd = (B.t().contiguous() if b_mn else B).to(dev())
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+    C32 = torch.zeros((M, N), dtype=torch.float32, device=dev())
+    st = status_word()
+    eb.call("eisen_gemm_set_mode", 2)
+    try:
+        eb.call("eisen_gemm_bf16", stream(), a_mn, b_mn, M, N, K, P(Ad), Ad.stride(0), P(Bd), Bd.stride(0), P(C), N, 0, 1, 1.0, P(st))
+        eb.call("eisen_gemm_bf16", stream(), a_mn, b_mn, M, N, K, P(Ad), Ad.stride(0), P(Bd), Bd.stride(0), P(C32), N, 4, 2, 1.0, P(st))
+        torch.cuda.synchronize()
+    finally:
+        eb.call("eisen_gemm_set_mode", 0)
+    assert int(st.item()) == 0
+    assert torch.isfinite(C.float()).all()
+    assert rel_l2(C.float().cpu().numpy(), ref.numpy()) < 4e-3
+    assert rel_l2(C32.cpu().numpy(), ref.numpy()) < 1e-5
 
 
 @pytest.mark.parametrize("mode", [2, 3, 4])
