@@ -62,89 +62,135 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const float* __restrict__ w, T* __re
 
 // Backward (src/graph/ops/normalization.rs:155-173):
 //   gdxw = sum_d dy*x*w ; dx (+)= rrms*dy*w - x*rrms^3/dim*gdxw ; dw[d] += dy*x*rrms
-// Each warp walks rows; every lane keeps the dw partial of the columns it owns in registers
-// (NCH chunks of V columns), the CTA folds its warps through shared memory and writes one row of
-// `dw_partial` [gridDim.x, dim]; a second kernel sums the partials in a fixed order (no atomics,
+// A CTA of 256 threads works on ROWS rows at a time; thread t owns the columns of vector
+// t + 256*j (j < NCH) for every row, so its weights and its share of dw stay in registers for the
+// whole kernel and dw needs no reduction inside the CTA.  The two row sums go through one
+// shuffle + shared-memory exchange per group of ROWS rows.  Each CTA writes one row of
+// `dw_partial` [gridDim.x, dim]; a second kernel adds the partials in a fixed order (no atomics,
 // run-to-run deterministic).
+__device__ __forceinline__ void unpack16(const uint4& r, float (&v)[4]) {
+  v[0] = __uint_as_float(r.x); v[1] = __uint_as_float(r.y); v[2] = __uint_as_float(r.z); v[3] = __uint_as_float(r.w);
+}
+__device__ __forceinline__ void unpack16(const uint4& r, float (&v)[8]) {
+  const uint32_t u[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(u[i] << 16);          // low half = even element
+    v[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+  }
+}
+
+constexpr int RB_THREADS = 256;
+constexpr int RB_ROWS = 4;
+
 template <typename T, int NCH>
-__global__ void __launch_bounds__(RN_WARPS * 32)
+__global__ void __launch_bounds__(RB_THREADS, 2)
 rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w, const T* __restrict__ dy,
                    T* __restrict__ dx, float* __restrict__ dw_partial, long long rows, int dim, float eps,
                    int acc_dx) {
   constexpr int V = VecOf<T>::N;
-  extern __shared__ float sh_dw[];  // [RN_WARPS][dim]
+  __shared__ float sh[2][RB_THREADS / 32][2 * RB_ROWS];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const long long warp0 = (long long)blockIdx.x * RN_WARPS + warp;
-  const long long wstride = (long long)gridDim.x * RN_WARPS;
-  float dwp[NCH][V], wv[NCH][V];  // a lane owns the same columns for every row: weights stay in registers
+  float wv[NCH][V], dwp[NCH][V];
 #pragma unroll
   for (int j = 0; j < NCH; ++j) {
-    const int c = (j * 32 + lane) * V;
+    const int c = (threadIdx.x + j * RB_THREADS) * V;
 #pragma unroll
     for (int k = 0; k < V; ++k) {
       dwp[j][k] = 0.0f;
       wv[j][k] = (c < dim) ? w[c + k] : 0.0f;
     }
   }
-
-  for (long long row = warp0; row < rows; row += wstride) {
-    const T* xr = x + row * dim;
-    const T* gr = dy + row * dim;
-    T* dr = dx + row * dim;
-    float xv[NCH][V], gv[NCH][V];
-    float ss = 0.0f, gdxw = 0.0f;
+  int buf = 0;
+  const long long groups = (rows + RB_ROWS - 1) / RB_ROWS;
+  for (long long gi = blockIdx.x; gi < groups; gi += gridDim.x) {
+    const long long r0 = gi * RB_ROWS;
+    // the rows stay packed in registers (16 bytes per vector) and are widened where used
+    uint4 xr[RB_ROWS][NCH], gr[RB_ROWS][NCH];
+    float part[2 * RB_ROWS];
 #pragma unroll
-    for (int j = 0; j < NCH; ++j) {
-      const int c = (j * 32 + lane) * V;
-      if (c < dim) {
-        ld16(xr + c, xv[j]);
-        ld16(gr + c, gv[j]);
+    for (int r = 0; r < RB_ROWS; ++r) {
+      const bool ok = r0 + r < rows;
 #pragma unroll
-        for (int k = 0; k < V; ++k) {
-          ss += xv[j][k] * xv[j][k];
-          gdxw += gv[j][k] * xv[j][k] * wv[j][k];
+      for (int j = 0; j < NCH; ++j) {
+        const int c = (threadIdx.x + j * RB_THREADS) * V;
+        if (ok && c < dim) {
+          xr[r][j] = *reinterpret_cast<const uint4*>(x + (r0 + r) * dim + c);
+          gr[r][j] = *reinterpret_cast<const uint4*>(dy + (r0 + r) * dim + c);
+        } else {
+          xr[r][j] = make_uint4(0, 0, 0, 0);
+          gr[r][j] = make_uint4(0, 0, 0, 0);
         }
       }
     }
-    ss = warp_sum(ss);
-    gdxw = warp_sum(gdxw);
-    const float rrms = 1.0f / sqrtf(ss / (float)dim + eps);
-    const float rrc_d = (rrms * rrms * rrms) / (float)dim;
 #pragma unroll
-    for (int j = 0; j < NCH; ++j) {
-      const int c = (j * 32 + lane) * V;
-      if (c < dim) {
-        float o[V];
+    for (int r = 0; r < RB_ROWS; ++r) {
+      float ss = 0.0f, gd = 0.0f;
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        float xv[V], gv[V];
+        unpack16(xr[r][j], xv);
+        unpack16(gr[r][j], gv);
 #pragma unroll
         for (int k = 0; k < V; ++k) {
-          o[k] = rrms * (gv[j][k] * wv[j][k]) - xv[j][k] * rrc_d * gdxw;
-          dwp[j][k] += gv[j][k] * xv[j][k] * rrms;
+          ss += xv[k] * xv[k];
+          gd += gv[k] * xv[k] * wv[j][k];
         }
-        if (acc_dx) {
-          float old[V];
-          ld16(dr + c, old);
+      }
+      part[2 * r] = warp_sum(ss);
+      part[2 * r + 1] = warp_sum(gd);
+    }
+    if (lane == 0) {
 #pragma unroll
-          for (int k = 0; k < V; ++k) o[k] += old[k];
+      for (int i = 0; i < 2 * RB_ROWS; ++i) sh[buf][warp][i] = part[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 2 * RB_ROWS; ++i) {
+      float t = 0.0f;
+#pragma unroll
+      for (int wq = 0; wq < RB_THREADS / 32; ++wq) t += sh[buf][wq][i];
+      part[i] = t;
+    }
+    buf ^= 1;  // the other buffer is free: everyone passed the barrier of the group before
+#pragma unroll
+    for (int r = 0; r < RB_ROWS; ++r) {
+      if (r0 + r < rows) {
+        const float rrms = 1.0f / sqrtf(part[2 * r] / (float)dim + eps);
+        const float rrc_d = (rrms * rrms * rrms) / (float)dim;
+        const float gdxw = part[2 * r + 1];
+#pragma unroll
+        for (int j = 0; j < NCH; ++j) {
+          const int c = (threadIdx.x + j * RB_THREADS) * V;
+          if (c < dim) {
+            float xv[V], gv[V], o[V];
+            unpack16(xr[r][j], xv);
+            unpack16(gr[r][j], gv);
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+              o[k] = rrms * (gv[k] * wv[j][k]) - xv[k] * rrc_d * gdxw;
+              dwp[j][k] += gv[k] * xv[k] * rrms;
+            }
+            T* dr = dx + (r0 + r) * dim + c;
+            if (acc_dx) {
+              float old[V];
+              ld16(dr, old);
+#pragma unroll
+              for (int k = 0; k < V; ++k) o[k] += old[k];
+            }
+            st16(dr, o);
+          }
         }
-        st16(dr + c, o);
       }
     }
   }
-  // fold the warps of this CTA
 #pragma unroll
   for (int j = 0; j < NCH; ++j) {
-    const int c = (j * 32 + lane) * V;
+    const int c = (threadIdx.x + j * RB_THREADS) * V;
     if (c < dim) {
 #pragma unroll
-      for (int k = 0; k < V; ++k) sh_dw[warp * dim + c + k] = dwp[j][k];
+      for (int k = 0; k < V; ++k) dw_partial[(long long)blockIdx.x * dim + c + k] = dwp[j][k];
     }
-  }
-  __syncthreads();
-  for (int c = threadIdx.x; c < dim; c += blockDim.x) {
-    float s = 0.0f;
-#pragma unroll
-    for (int wq = 0; wq < RN_WARPS; ++wq) s += sh_dw[wq * dim + c];
-    dw_partial[(long long)blockIdx.x * dim + c] = s;
   }
 }
 
@@ -182,13 +228,28 @@ __global__ void rmsnorm_bwd_generic_kernel(const T* __restrict__ x, const float*
   }
 }
 
-__global__ void reduce_partials_kernel(const float* __restrict__ partial, float* __restrict__ out,
-                                       int nparts, int dim) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= dim) return;
+inline int rmsnorm_bwd_grid(long long rows) {
+  return grid_for((rows + RB_ROWS - 1) / RB_ROWS, 1, 2);  // persistent: two resident CTAs per SM
+}
+
+// out[c] += sum_p partial[p][c]: 32 columns per CTA, 8 warps each summing every 8th partial,
+// folded through shared memory in a fixed order
+__global__ void __launch_bounds__(256)
+reduce_partials_kernel(const float* __restrict__ partial, float* __restrict__ out, int nparts, int dim) {
+  __shared__ float sh[8][33];
+  const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
   float s = 0.0f;
-  for (int p = 0; p < nparts; ++p) s += partial[(long long)p * dim + c];
-  out[c] += s;
+  if (c < dim)
+    for (int p = g; p < nparts; p += 8) s += partial[(long long)p * dim + c];
+  sh[g][lane] = s;
+  __syncthreads();
+  if (g == 0 && c < dim) {
+    float t = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += sh[i][lane];
+    out[c] += t;
+  }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -232,6 +293,13 @@ __global__ void __launch_bounds__(256) softmax_bwd_kernel(const T* __restrict__ 
 // ---------------------------------------------------------------------------------------
 constexpr int CE_THREADS = 256;
 
+// f32 logits keep the precise expf (parity with the CPU arm); bf16 logits use the fast one
+template <typename T>
+__device__ __forceinline__ float exp_t(float x) {
+  if constexpr (sizeof(T) == 2) return __expf(x);
+  else return expf(x);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(CE_THREADS)
 ce_fwd_kernel(const T* __restrict__ logits, const int* __restrict__ targets, float* __restrict__ row_loss,
@@ -253,9 +321,9 @@ ce_fwd_kernel(const T* __restrict__ logits, const int* __restrict__ targets, flo
       float cm = v[0];
 #pragma unroll
       for (int k = 1; k < V; ++k) cm = fmaxf(cm, v[k]);
-      if (cm > m) { s *= expf(m - cm); m = cm; }
+      if (cm > m) { s *= exp_t<T>(m - cm); m = cm; }
 #pragma unroll
-      for (int k = 0; k < V; ++k) s += expf(v[k] - m);
+      for (int k = 0; k < V; ++k) s += exp_t<T>(v[k] - m);
     }
   } else {
     for (int c = threadIdx.x; c < V_; c += CE_THREADS) {
@@ -314,7 +382,7 @@ ce_bwd_kernel(const T* __restrict__ logits, const int* __restrict__ targets, con
       ld16(xr + c, v);
 #pragma unroll
       for (int k = 0; k < V; ++k) {
-        float g = expf(v[k] - l);
+        float g = exp_t<T>(v[k] - l);
         if (c + k == t) g -= 1.0f;
         v[k] = g * scale;
       }
@@ -340,16 +408,11 @@ ce_bwd_kernel(const T* __restrict__ logits, const int* __restrict__ targets, con
 template <typename T, int NCH>
 int launch_rmsnorm_bwd(cudaStream_t s, const T* x, const float* w, const T* dy, T* dx, float* dw,
                        float* ws, long long rows, int dim, float eps, int acc_dx) {
-  int grid = grid_for(rows, RN_WARPS, 2);
-  const size_t smem = (size_t)RN_WARPS * dim * 4;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(rmsnorm_bwd_kernel<T, NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return fail(EISEN_ERR_CUDA, cudaGetErrorString(e));
-  }
-  rmsnorm_bwd_kernel<T, NCH><<<grid, RN_WARPS * 32, smem, s>>>(x, w, dy, dx, ws, rows, dim, eps, acc_dx);
+  const int grid = rmsnorm_bwd_grid(rows);
+  rmsnorm_bwd_kernel<T, NCH><<<grid, RB_THREADS, 0, s>>>(x, w, dy, dx, ws, rows, dim, eps, acc_dx);
   int rc = check_launch("rmsnorm_bwd");
   if (rc) return rc;
-  reduce_partials_kernel<<<(dim + 255) / 256, 256, 0, s>>>(ws, dw, grid, dim);
+  reduce_partials_kernel<<<(dim + 31) / 32, 256, 0, s>>>(ws, dw, grid, dim);
   return check_launch("rmsnorm_bwd_reduce");
 }
 
@@ -357,19 +420,16 @@ template <typename T>
 int rmsnorm_bwd_dispatch(cudaStream_t s, const T* x, const float* w, const T* dy, T* dx, float* dw, float* ws,
                          long long rows, int dim, float eps, int acc_dx) {
   constexpr int V = VecOf<T>::N;
-  const bool fast = (dim % V) == 0 && dim <= 16 * 32 * V && ((long long)RN_WARPS * dim * 4) <= 200 * 1024 &&
-                    aligned16(x) && aligned16(dy) && aligned16(dx) && ws != nullptr;
+  const int nch = (dim + RB_THREADS * V - 1) / (RB_THREADS * V);
+  const bool fast = (dim % V) == 0 && nch <= 4 && aligned16(x) && aligned16(dy) && aligned16(dx) && ws != nullptr;
   if (!fast) {
     const int grid = grid_for(rows, 8, 4);
     rmsnorm_bwd_generic_kernel<T><<<grid, 256, 0, s>>>(x, w, dy, dx, dw, rows, dim, eps, acc_dx);
     return check_launch("rmsnorm_bwd_generic");
   }
-  const int nch = (dim + 32 * V - 1) / (32 * V);
   if (nch <= 1) return launch_rmsnorm_bwd<T, 1>(s, x, w, dy, dx, dw, ws, rows, dim, eps, acc_dx);
   if (nch <= 2) return launch_rmsnorm_bwd<T, 2>(s, x, w, dy, dx, dw, ws, rows, dim, eps, acc_dx);
-  if (nch <= 4) return launch_rmsnorm_bwd<T, 4>(s, x, w, dy, dx, dw, ws, rows, dim, eps, acc_dx);
-  if (nch <= 8) return launch_rmsnorm_bwd<T, 8>(s, x, w, dy, dx, dw, ws, rows, dim, eps, acc_dx);
-  return launch_rmsnorm_bwd<T, 16>(s, x, w, dy, dx, dw, ws, rows, dim, eps, acc_dx);
+  return launch_rmsnorm_bwd<T, 4>(s, x, w, dy, dx, dw, ws, rows, dim, eps, acc_dx);
 }
 
 }  // namespace
@@ -392,8 +452,7 @@ int eisen_rmsnorm_fwd(void* stream, const void* x, const float* w, void* y, floa
 }
 
 long long eisen_rmsnorm_bwd_workspace_bytes(long long rows, long long dim) {
-  (void)rows;
-  return (long long)sm_count() * 2 * dim * 4;
+  return (long long)rmsnorm_bwd_grid(rows) * dim * 4 + 256;
 }
 
 
