@@ -358,7 +358,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 // =====================================================================================
-// backward
+// backward: one 128-key tile of one KV head per CTA, looping over the query heads of its group
+// and over query tiles.  Warps 0-15 compute (warp w touches TMEM lanes (w%4)*32.. and the column
+// quarter w/4), warp 16 issues TMA, warp 17 issues MMAs.
+//   S = Q K^T, dP = dO V^T                  -> TMEM
+//   P = exp2(S*c - lse), dS = P*(dP - delta) -> shared memory (bf16); the softmax scale is applied
+//                                              once to dQ (in the conversion kernel) and to dK
+//   dV += P^T dO, dK += dS^T Q              -> TMEM, kept across the whole loop (the GQA reduce)
+//   dQ  = dS K                              -> TMEM -> f32 red.global.add into a workspace
+// With D = 64 the dQ tile has TMEM columns of its own, so the S / dP products of the next query
+// tile are issued right behind dV, dK, dQ and the dQ read-out overlaps them; with D = 128 dQ
+// reuses the S columns (512 columns in total) and the read-out comes first.
 // =====================================================================================
 template <int D>
 struct BwdCfg {
@@ -374,19 +384,22 @@ struct BwdCfg {
   static constexpr int OFF_BAR = OFF_DS + P_TILE;
   static constexpr int SMEM = OFF_BAR + 256 + 1024;
   static constexpr int TMEM_COLS = 512;
-  // TMEM columns: S / dQ at 0 (dQ reuses S once P and dS are in shared memory), dP at 128,
-  // dV at 256, dK at 256 + D
-  static constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + D, COL_DQ = 0;
+  static constexpr bool DQ_OWN = (D == 64);  // dQ has its own TMEM columns
+  static constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + D;
+  static constexpr int COL_DQ = DQ_OWN ? 256 + 2 * D : 0;
+  static constexpr int CWARPS = 16;                 // compute warps
+  static constexpr int THREADS = (CWARPS + 2) * 32;
 };
 
 template <int D>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                 const AttnParams p) {
   using Cfg = BwdCfg<D>;
   constexpr int ATOMS = D / 64;
   constexpr int NS = Cfg::NS;
+  constexpr int NCT = Cfg::CWARPS * 32;  // compute threads
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -395,9 +408,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* qdo_full = bars + 1;   // NS (<= 2)
   uint64_t* qdo_empty = bars + 3;  // NS
   uint64_t* sdp_full = bars + 5;   // 1
-  uint64_t* pds_ready = bars + 6;  // 1 (256 arrivals)
+  uint64_t* pds_ready = bars + 6;  // 1 (NCT arrivals)
   uint64_t* dq_full = bars + 7;    // 1
-  uint64_t* dq_read = bars + 8;    // 1 (256 arrivals)
+  uint64_t* dq_read = bars + 8;    // 1 (NCT arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -414,20 +427,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(kv_full, 1);
     for (int i = 0; i < NS; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
     mbar_init(sdp_full, 1);
-    mbar_init(pds_ready, 256);
+    mbar_init(pds_ready, NCT);
     mbar_init(dq_full, 1);
-    mbar_init(dq_read, 256);
+    mbar_init(dq_read, NCT);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO);
   }
-  if (warp == 9) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
+  if (warp == Cfg::CWARPS + 1) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp == Cfg::CWARPS) {
     // ---------------- TMA ----------------
     if (lane == 0) {
       mbar_arrive_expect_tx(kv_full, 2 * Cfg::TILE);
@@ -450,23 +463,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == Cfg::CWARPS + 1) {
     // ---------------- MMA ----------------
-    if (lane == 0) {
+    if (lane == 0 && iters > 0) {
       const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);   // Q K^T, dO V^T
       const uint32_t idesc_t = make_idesc_bf16(128, D, 1, 1);     // P^T dO, dS^T Q
       const uint32_t idesc_q = make_idesc_bf16(128, D, 0, 1);     // dS K
       const uint32_t sK = smem_u32(smem + Cfg::OFF_K), sV = smem_u32(smem + Cfg::OFF_V);
       const uint32_t sP = smem_u32(smem + Cfg::OFF_P), sDS = smem_u32(smem + Cfg::OFF_DS);
-      mbar_wait(kv_full, 0, abort_flag, p.status, FAULT_WAIT_ATTN);
-      for (int it = 0; it < iters; ++it) {
+      auto issue_sdp = [&](int it) {
         const int st = it % NS;
-        const uint32_t ph = (it / NS) & 1;
-        const uint32_t iph = it & 1;
         const uint32_t sQ = smem_u32(smem + Cfg::OFF_Q + st * Cfg::TILE);
         const uint32_t sDO = smem_u32(smem + Cfg::OFF_DO + st * Cfg::TILE);
-        mbar_wait(&qdo_full[st], ph, abort_flag, p.status, FAULT_WAIT_ATTN);
-        if (it > 0) mbar_wait(dq_read, iph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);  // dQ of it-1 drained
+        mbar_wait(&qdo_full[st], (it / NS) & 1, abort_flag, p.status, FAULT_WAIT_ATTN);
         tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
@@ -481,6 +490,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                        make_smem_desc(sV + off, 16, 1024), idesc_s, k > 0);
         }
         umma_commit(sdp_full);
+      };
+      mbar_wait(kv_full, 0, abort_flag, p.status, FAULT_WAIT_ATTN);
+      issue_sdp(0);
+      for (int it = 0; it < iters; ++it) {
+        const int st = it % NS;
+        const uint32_t iph = it & 1;
+        const uint32_t sQ = smem_u32(smem + Cfg::OFF_Q + st * Cfg::TILE);
+        const uint32_t sDO = smem_u32(smem + Cfg::OFF_DO + st * Cfg::TILE);
         mbar_wait(pds_ready, iph, abort_flag, p.status, FAULT_WAIT_ATTN);
         tc_fence_after_sync();
         // K dimension of the next three products = the 128 query rows (dV, dK) or 128 keys (dQ)
@@ -492,22 +509,69 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int k = 0; k < 8; ++k)  // dK += dS^T Q
           umma_bf16_ss(tmem_base + Cfg::COL_DK, make_smem_desc(sDS + k * 2048u, 16384, 1024),
                        make_smem_desc(sQ + k * 2048u, 16384, 1024), idesc_t, (it > 0 || k > 0));
+        if (Cfg::DQ_OWN && it > 0) {  // the dQ tile of the query tile before has been read out
+          mbar_wait(dq_read, iph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
+          tc_fence_after_sync();
+        }
 #pragma unroll
         for (int k = 0; k < 8; ++k)  // dQ = dS K
           umma_bf16_ss(tmem_base + Cfg::COL_DQ, make_smem_desc(sDS + (k >> 2) * 16384u + (k & 3) * 32u, 16, 1024),
                        make_smem_desc(sK + k * 2048u, 16384, 1024), idesc_q, k > 0);
         umma_commit(dq_full);
         umma_commit(&qdo_empty[st]);
+        if (it + 1 < iters) {
+          if (!Cfg::DQ_OWN) {  // dQ sits in the S columns: wait until it has been read out
+            mbar_wait(dq_read, iph, abort_flag, p.status, FAULT_WAIT_ATTN);
+            tc_fence_after_sync();
+          }
+          issue_sdp(it + 1);
+        }
       }
     }
   } else {
-    // ---------------- compute warps 0-7 ----------------
+    // ---------------- compute warps ----------------
     const int q4 = warp & 3;        // TMEM lane quarter
-    const int ch = warp >> 2;       // column half
+    const int cq = warp >> 2;       // column quarter
     const int row = q4 * 32 + lane;
     const uint32_t lane_off = uint32_t(q4 * 32) << 16;
     const float sl2 = p.scale * LOG2E;
     const uint32_t sP = smem_u32(smem + Cfg::OFF_P), sDS = smem_u32(smem + Cfg::OFF_DS);
+    constexpr int DQC = D / 4;  // dQ / dK / dV columns per thread
+
+    // adds this thread's part of the dQ tile of iteration `it` to the f32 accumulation buffer
+    auto drain_dq = [&](int it) {
+      const int h = kvh * rep + it / per_head;
+      const int qrow = (i0 + it % per_head) * 128 + row;
+      mbar_wait(dq_full, it & 1, abort_flag, p.status, FAULT_WAIT_ATTN);
+      tc_fence_after_sync();
+      float* dq_row = p.dq_acc + (((long long)b * p.S + qrow) * p.Hq + h) * D + cq * DQC;
+      if constexpr (DQC == 16) {
+        uint32_t r[16];
+        tmem_ld_32x32b_x16(tmem_base + Cfg::COL_DQ + cq * DQC + lane_off, r);
+        tmem_ld_wait();
+        if (qrow < p.S) {
+#pragma unroll
+          for (int i = 0; i < 16; i += 4)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + i), "f"(__uint_as_float(r[i])),
+                         "f"(__uint_as_float(r[i + 1])), "f"(__uint_as_float(r[i + 2])), "f"(__uint_as_float(r[i + 3]))
+                         : "memory");
+        }
+      } else {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_base + Cfg::COL_DQ + cq * DQC + lane_off, r);
+        tmem_ld_wait();
+        if (qrow < p.S) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + i), "f"(__uint_as_float(r[i])),
+                         "f"(__uint_as_float(r[i + 1])), "f"(__uint_as_float(r[i + 2])), "f"(__uint_as_float(r[i + 3]))
+                         : "memory");
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(dq_read);
+    };
+
     for (int it = 0; it < iters; ++it) {
       const uint32_t iph = it & 1;
       const int h = kvh * rep + it / per_head;
@@ -520,9 +584,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const bool need_mask = (p.causal && qi == jt) || ((jt + 1) * 128 > p.S);
       mbar_wait(sdp_full, iph, abort_flag, p.status, FAULT_WAIT_ATTN);
       tc_fence_after_sync();
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        const int col0 = ch * 64 + c * 32;
+      {
+        const int col0 = cq * 32;
         uint32_t rs[32], rd[32];
         tmem_ld_32x32b_x32(tmem_base + Cfg::COL_S + col0 + lane_off, rs);
         tmem_ld_32x32b_x32(tmem_base + Cfg::COL_DP + col0 + lane_off, rd);
@@ -530,15 +593,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         uint32_t pk[16], dk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(__uint_as_float(rs[i]) * sl2 - lse2);
-          float p1 = exp2f(__uint_as_float(rs[i + 1]) * sl2 - lse2);
+          float p0 = ex2_approx(fmaf(__uint_as_float(rs[i]), sl2, -lse2));
+          float p1 = ex2_approx(fmaf(__uint_as_float(rs[i + 1]), sl2, -lse2));
           if (need_mask) {
             const int kc = jt * 128 + col0 + i;
             if (kc >= p.S || (p.causal && kc > qrow)) p0 = 0.0f;
             if (kc + 1 >= p.S || (p.causal && kc + 1 > qrow)) p1 = 0.0f;
           }
-          const float d0 = p0 * (__uint_as_float(rd[i]) - dlt) * p.scale;
-          const float d1 = p1 * (__uint_as_float(rd[i + 1]) - dlt) * p.scale;
+          const float d0 = p0 * (__uint_as_float(rd[i]) - dlt);
+          const float d1 = p1 * (__uint_as_float(rd[i + 1]) - dlt);
           pk[i >> 1] = pack_bf16x2(p0, p1);
           dk[i >> 1] = pack_bf16x2(d0, d1);
         }
@@ -548,52 +611,51 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before_sync();
       fence_proxy_async_smem();
       mbar_arrive(pds_ready);
-      // dQ tile -> f32 accumulation buffer
-      mbar_wait(dq_full, iph, abort_flag, p.status, FAULT_WAIT_ATTN);
-      tc_fence_after_sync();
-      float* dq_row = p.dq_acc + (((long long)b * p.S + qrow) * p.Hq + h) * D;
-#pragma unroll 1
-      for (int c = 0; c < D / 64; ++c) {
-        const int col0 = ch * (D / 2) + c * 32;
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_base + Cfg::COL_DQ + col0 + lane_off, r);
-        tmem_ld_wait();
-        if (row_ok) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + col0 + i),
-                         "f"(__uint_as_float(r[i])), "f"(__uint_as_float(r[i + 1])),
-                         "f"(__uint_as_float(r[i + 2])), "f"(__uint_as_float(r[i + 3]))
-                         : "memory");
-        }
+      if (Cfg::DQ_OWN) {
+        if (it > 0) drain_dq(it - 1);  // overlaps the dV / dK products of this query tile
+      } else {
+        drain_dq(it);
       }
-      tc_fence_before_sync();
-      mbar_arrive(dq_read);
     }
+    if (Cfg::DQ_OWN && iters > 0) drain_dq(iters - 1);
     // dK / dV of this key tile: TMEM -> bf16 -> global (the last dq_full wait covers them)
     if (iters > 0) {
       tc_fence_after_sync();
       const int krow = jt * 128 + row;
-      const long long base = (long long)b * p.kv_bs + (long long)krow * p.kv_ss + (long long)kvh * p.kv_hs;
+      const long long base = (long long)b * p.kv_bs + (long long)krow * p.kv_ss + (long long)kvh * p.kv_hs + cq * DQC;
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(which ? p.dk : p.dv) + base;
-        const int colbase = which ? Cfg::COL_DK : Cfg::COL_DV;
-#pragma unroll 1
-        for (int c = 0; c < D / 64; ++c) {
-          const int col0 = ch * (D / 2) + c * 32;
+        const int colbase = (which ? Cfg::COL_DK : Cfg::COL_DV) + cq * DQC;
+        const float mul = which ? p.scale : 1.0f;  // dS was kept unscaled
+        if constexpr (DQC == 16) {
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(tmem_base + colbase + lane_off, r);
+          tmem_ld_wait();
+          if (krow < p.S) {
+#pragma unroll
+            for (int i = 0; i < 16; i += 8) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r[i]) * mul, __uint_as_float(r[i + 1]) * mul);
+              o.y = pack_bf16x2(__uint_as_float(r[i + 2]) * mul, __uint_as_float(r[i + 3]) * mul);
+              o.z = pack_bf16x2(__uint_as_float(r[i + 4]) * mul, __uint_as_float(r[i + 5]) * mul);
+              o.w = pack_bf16x2(__uint_as_float(r[i + 6]) * mul, __uint_as_float(r[i + 7]) * mul);
+              *reinterpret_cast<uint4*>(dst + i) = o;
+            }
+          }
+        } else {
           uint32_t r[32];
-          tmem_ld_32x32b_x32(tmem_base + colbase + col0 + lane_off, r);
+          tmem_ld_32x32b_x32(tmem_base + colbase + lane_off, r);
           tmem_ld_wait();
           if (krow < p.S) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
               uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-              o.y = pack_bf16x2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
-              o.z = pack_bf16x2(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
-              o.w = pack_bf16x2(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
-              *reinterpret_cast<uint4*>(dst + col0 + i) = o;
+              o.x = pack_bf16x2(__uint_as_float(r[i]) * mul, __uint_as_float(r[i + 1]) * mul);
+              o.y = pack_bf16x2(__uint_as_float(r[i + 2]) * mul, __uint_as_float(r[i + 3]) * mul);
+              o.z = pack_bf16x2(__uint_as_float(r[i + 4]) * mul, __uint_as_float(r[i + 5]) * mul);
+              o.w = pack_bf16x2(__uint_as_float(r[i + 6]) * mul, __uint_as_float(r[i + 7]) * mul);
+              *reinterpret_cast<uint4*>(dst + i) = o;
             }
           }
         }
@@ -606,7 +668,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (*abort_flag) {
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
-  if (warp == 9) {
+  if (warp == Cfg::CWARPS + 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
@@ -648,7 +710,7 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
 // dq (bf16, strided [B,S,H,D]) = dq_acc (f32, contiguous [B,S,H,D])
 __global__ void __launch_bounds__(256)
 attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long rows /*B*S*H*/,
-                       int S, int H, int D, long long bs, long long ss, long long hs) {
+                       int S, int H, int D, long long bs, long long ss, long long hs, float scale) {
   const int per_row = D / 8;
   const long long total = rows * per_row;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -661,7 +723,9 @@ attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict_
     float lo[4], hi[4];
     ld16(acc + r * D + c, lo);
     ld16(acc + r * D + c + 4, hi);
-    float v[8] = {lo[0], lo[1], lo[2], lo[3], hi[0], hi[1], hi[2], hi[3]};
+    // the backward kernel accumulates dS K with dS unscaled: the softmax scale is applied here
+    float v[8] = {lo[0] * scale, lo[1] * scale, lo[2] * scale, lo[3] * scale,
+                  hi[0] * scale, hi[1] * scale, hi[2] * scale, hi[3] * scale};
     st16(dq + b * bs + (long long)s * ss + (long long)h * hs + c, v);
   }
 }
@@ -770,16 +834,16 @@ int eisen_attn_bwd(void* stream, const void* q, const void* k, const void* v, co
   if (D == 64) {
     static bool set64 = false;
     if (!set64) { if (cudaFuncSetAttribute(attn_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<64>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_bwd: smem attribute"); set64 = true; }
-    attn_bwd_kernel<64><<<grid, 320, BwdCfg<64>::SMEM, s>>>(tq, tk, tv, tdo, p);
+    attn_bwd_kernel<64><<<grid, BwdCfg<64>::THREADS, BwdCfg<64>::SMEM, s>>>(tq, tk, tv, tdo, p);
   } else {
     static bool set128 = false;
     if (!set128) { if (cudaFuncSetAttribute(attn_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<128>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_bwd: smem attribute"); set128 = true; }
-    attn_bwd_kernel<128><<<grid, 320, BwdCfg<128>::SMEM, s>>>(tq, tk, tv, tdo, p);
+    attn_bwd_kernel<128><<<grid, BwdCfg<128>::THREADS, BwdCfg<128>::SMEM, s>>>(tq, tk, tv, tdo, p);
   }
   rc = check_launch("attn_bwd");
   if (rc) return rc;
   attn_dq_convert_kernel<<<grid_for(B * S * Hq * D / 8, 256, 8), 256, 0, s>>>(dq_acc, (__nv_bfloat16*)dq, B * S * Hq, (int)S,
-                                                                              (int)Hq, (int)D, q_bs, q_ss, q_hs);
+                                                                              (int)Hq, (int)D, q_bs, q_ss, q_hs, scale);
   return check_launch("attn_dq_convert");
 }
 

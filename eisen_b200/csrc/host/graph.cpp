@@ -388,7 +388,8 @@ int64_t Graph::add(int64_t a, int64_t b) {
   const int dt = act_dtype();
   const int64_t n = ta.numel, bn = tb.numel;
   int64_t o = alloc_pooled(ta.shape);
-  ck(eisen_add(stream, operand(tensors[a]), operand(tensors[b]), tensors[o].data, n, bn, dt), "add");
+  if (!skip_forward)
+    ck(eisen_add(stream, operand(tensors[a]), operand(tensors[b]), tensors[o].data, n, bn, dt), "add");
   if (!no_grad) {
     tape.push_back({{a, b}, o, [this, a, b, o, n, bn]() {
       OUT_GRAD_OR_RETURN(o);
@@ -514,7 +515,8 @@ int64_t Graph::matmul(int64_t a, int64_t b) {
   const int64_t k = ta.shape.back(), m = ta.numel / k, n = tb.shape[1];
   if (tb.shape[0] != k) invalid("matmul: lhs last dim must equal rhs first dim");
   int64_t o = alloc_pooled({m, n});
-  gemm(*this, false, true, m, n, k, operand(tensors[a]), operand(tensors[b]), tensors[o].data, act_dtype(), false);
+  if (!skip_forward)
+    gemm(*this, false, true, m, n, k, operand(tensors[a]), operand(tensors[b]), tensors[o].data, act_dtype(), false);
   if (!no_grad) {
     tape.push_back({{a, b}, o, [this, a, b, o, m, n, k]() {
       OUT_GRAD_OR_RETURN(o);

@@ -118,6 +118,10 @@ class Graph {
   std::vector<HTensor> tensors;
   std::vector<HNode> tape;
   bool no_grad = false;
+  // When set, matmul and add record their tape node and allocate their output but do not run the
+  // forward kernel.  Used while a checkpointed block is re-run for its backward pass: the values of
+  // the last projection and of the last residual add are read by no backward node.
+  bool skip_forward = false;
   int64_t num_params = 0;
   Precision precision;
   cudaStream_t stream;
@@ -155,7 +159,8 @@ class TransformerLM {
   TransformerLM(Graph& g, int64_t vocab, int64_t hidden, int64_t heads, int64_t kv_heads, int64_t ffn,
                 int64_t layers, bool tie);
   int64_t forward(Graph& g, int64_t x_ids);                       // :184-196
-  int64_t block_forward(Graph& g, const BlockParams& b, int64_t x);  // :32-49
+  // skip_dead_tail: leave out the forward kernels whose results no backward node reads
+  int64_t block_forward(Graph& g, const BlockParams& b, int64_t x, bool skip_dead_tail = false);  // :32-49
   int64_t gqa_forward(Graph& g, const BlockParams& b, int64_t x, bool causal);  // attention.rs:289-388
   std::vector<int64_t> params() const;                            // :198-210
   // One micro-step: forward, loss (masked cross-entropy over [B*S] targets), backward.

@@ -164,7 +164,7 @@ int64_t TransformerLM::gqa_forward(Graph& g, const BlockParams& b, int64_t x, bo
   return linear_fwd(g, ctx2, b.o);
 }
 
-int64_t TransformerLM::block_forward(Graph& g, const BlockParams& b, int64_t x) {
+int64_t TransformerLM::block_forward(Graph& g, const BlockParams& b, int64_t x, bool skip_dead_tail) {
   int64_t n1 = g.rms_norm(x, b.norm1, 1e-5f);
   int64_t at = gqa_forward(g, b, n1, true);
   int64_t r1 = g.add(x, at);
@@ -179,8 +179,13 @@ int64_t TransformerLM::block_forward(Graph& g, const BlockParams& b, int64_t x) 
     up = linear_fwd(g, n2, b.up);
     gd = g.mul(gt, up);
   }
+  // the down projection's output and the second residual sum feed only the next block: when a
+  // checkpointed block is re-run for its backward pass nothing reads them
+  g.skip_forward = skip_dead_tail;
   int64_t f2 = linear_fwd(g, gd, b.down);
-  return g.add(r1, f2);
+  int64_t out = g.add(r1, f2);
+  g.skip_forward = false;
+  return out;
 }
 
 int64_t TransformerLM::forward(Graph& g, int64_t x) {
@@ -247,7 +252,7 @@ int64_t TransformerLM::train_micro_step_dev(Graph& g, int64_t x, int64_t target_
     for (int64_t l = layers - 1; l >= 0; --l) {
       const int64_t sp = g.mark_save_point();
       const int64_t t0 = (int64_t)g.tape.size();
-      int64_t y = block_forward(g, blocks[l], block_in[l]);
+      int64_t y = block_forward(g, blocks[l], block_in[l], true);
       // hand the output gradient to the recomputed output
       HTensor& ty = g.tensors[y];
       HTensor& to = g.tensors[out];
