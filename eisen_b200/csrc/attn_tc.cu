@@ -6,17 +6,12 @@
 // swizzle and are consumed by tcgen05.mma either K-major or MN-major, so one resident tile serves
 // both A*B^T and A^T*B style products; accumulators live in TMEM.
 //
-// Forward (per CTA: one 128-query tile of one head), warps 0-3 softmax (thread = query row),
-// warp 4 TMA, warp 5 MMA:
-//   S = Q K^T  ->  TMEM (two buffers)         p = exp2((s - m) * scale*log2e), online max / sum
-//   P (bf16)   ->  shared memory (two buffers)
-//   PV         ->  TMEM (two buffers), folded into an f32 register accumulator with the rescale
-// Backward (per CTA: one 128-key tile of one KV head, looping over the query heads of its group
-// and over query tiles), warps 0-7 compute, warp 8 TMA, warp 9 MMA:
-//   S = Q K^T, dP = dO V^T            -> TMEM
-//   P = exp2(S*c - lse), dS = P*(dP - delta)*scale   -> shared memory (bf16)
-//   dV += P^T dO, dK += dS^T Q        -> TMEM, kept across the whole loop (this is the GQA reduce)
-//   dQ  = dS K                        -> TMEM -> f32 red.global.add into a workspace
+// Forward: two 128-query tiles of one head per CTA share the K / V tiles; softmax warps read
+// S = Q K^T from TMEM, write P (bf16) to shared memory, and fold each P V product (a fresh TMEM
+// accumulator) into f32 registers with the online-softmax rescale.
+// Backward: one 128-key tile of one KV head per CTA, looping over the query heads of its group and
+// over query tiles; dV and dK stay in TMEM for the whole loop (the GQA reduce), dQ tiles are added
+// to an f32 workspace.  Details sit above each kernel.
 // It replaces the reference's materialised chain bmm -> mul(scale) -> add(mask) -> softmax -> bmm
 // and its gradient kernels (src/nn/attention.rs:339-375; kernels/ops_f32.cu:342-511, 625-646,
 // 787-840); the reference has no fused backward (src/graph/ops/attention.rs:15-18).
@@ -80,12 +75,19 @@ struct FwdCfg {
   static constexpr int OFF_V = OFF_K + 2 * TILE;  // NSV stages
   static constexpr int OFF_P = OFF_V + NSV * TILE;  // 2 tiles
   static constexpr int OFF_BAR = OFF_P + 2 * P_TILE;
-  static constexpr int SMEM = OFF_BAR + 256 + 1024;
+  // SPLIT threads share a query row (each takes 128 / SPLIT score columns and D / SPLIT output
+  // columns); the row maximum is exchanged through shared memory.  Shared memory leaves room for
+  // the exchange buffer only at D = 64.
+  static constexpr int SPLIT = (D == 64) ? 2 : 1;
+  static constexpr int OFF_XMAX = OFF_BAR + 256;             // float [2 tiles][SPLIT][128]
+  static constexpr int SMEM = OFF_XMAX + (SPLIT > 1 ? 2 * SPLIT * 128 * 4 : 0) + 1024;
   static constexpr int TMEM_COLS = 512;
+  static constexpr int SWARPS = 8 * SPLIT;                   // softmax warps
+  static constexpr int THREADS = (SWARPS + 2) * 32;
 };
 
 template <int D>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(FwdCfg<D>::THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
   using Cfg = FwdCfg<D>;
@@ -123,14 +125,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_ready[i], 128);
+      mbar_init(&p_ready[i], 128 * Cfg::SPLIT);
       mbar_init(&o_full[i], 1);
     }
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
   }
-  if (warp == 9) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
+  if (warp == Cfg::SWARPS + 1) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -138,7 +140,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tm_S = tmem_base;        // S of tile A at +0, of tile B at +128
   const uint32_t tm_O = tmem_base + 256;  // PV of tile A at +0, of tile B at +D
 
-  if (warp == 8) {
+  if (warp == Cfg::SWARPS) {
     // ---------------- TMA ----------------
     if (lane == 0) {
       mbar_arrive_expect_tx(q_full, (b_valid ? 2 : 1) * Cfg::TILE);
@@ -164,7 +166,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tma_load_4d(smem + Cfg::OFF_V + sv * Cfg::TILE + a * 16384, &tmV, &v_full[sv], a * 64, kvh, j * 128, b);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == Cfg::SWARPS + 1) {
     // ---------------- MMA ----------------
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
@@ -229,27 +231,36 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
   } else {
-    // ---------------- softmax + output (warps 0-3: tile A, warps 4-7: tile B; thread = query row) -------------
-    const int t = warp >> 2;
+    // ---------------- softmax + output ----------------
+    // warp w: query tile (w >> 2) & 1, TMEM lane quarter w & 3, column part w >> 3 (of SPLIT).
+    // A thread owns one query row, CW = 128 / SPLIT of its score columns and DW = D / SPLIT of its
+    // output columns; with SPLIT = 2 the two threads of a row agree on the row maximum through
+    // shared memory and add their partial row sums at the end.
+    constexpr int SPLIT = Cfg::SPLIT;
+    constexpr int CW = 128 / SPLIT;
+    constexpr int DW = D / SPLIT;
+    const int t = (warp >> 2) & 1;
+    const int part = warp >> 3;
     const int n_mine = t ? nB : nA;
     const int qt = t ? qtB : qtA;
     const int row = (warp & 3) * 32 + lane;
     const int qrow = qt * 128 + row;
     const uint32_t lane_off = uint32_t((warp & 3) * 32) << 16;
     const float sl2 = p.scale * LOG2E;
-    const uint32_t tS = tm_S + t * 128 + lane_off;
-    const uint32_t tO = tm_O + t * D + lane_off;
+    const uint32_t tS = tm_S + t * 128 + part * CW + lane_off;
+    const uint32_t tO = tm_O + t * D + part * DW + lane_off;
     const uint32_t sP = smem_u32(smem + Cfg::OFF_P + t * Cfg::P_TILE);
+    float* xmax = reinterpret_cast<float*>(smem + Cfg::OFF_XMAX) + t * SPLIT * 128;  // [SPLIT][128]
     float m = -INFINITY, l = 0.0f, alpha_prev = 1.0f;
-    float acc[D];
+    float acc[DW];
 #pragma unroll
-    for (int i = 0; i < D; ++i) acc[i] = 0.0f;
+    for (int i = 0; i < DW; ++i) acc[i] = 0.0f;
 
     auto fold = [&](uint32_t ph, float alpha) {  // acc = acc * alpha + (P V of the finished tile)
       mbar_wait(&o_full[t], ph, abort_flag, p.status, FAULT_WAIT_ATTN);
       tc_fence_after_sync();
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < DW / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(tO + c * 32, r);
         tmem_ld_wait();
@@ -264,17 +275,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const bool need_mask = (p.causal && j == qt) || ((j + 1) * 128 > p.S);
       mbar_wait(&s_full[t], jph, abort_flag, p.status, FAULT_WAIT_ATTN);
       tc_fence_after_sync();
-      // pass 1: row maximum
+      // pass 1: maximum over this thread's columns
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < CW / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(tS + c * 32, r);
         tmem_ld_wait();
         if (need_mask) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const int kc = j * 128 + c * 32 + i;
+            const int kc = j * 128 + part * CW + c * 32 + i;
             if (!(kc >= p.S || (p.causal && kc > qrow))) mx = fmaxf(mx, __uint_as_float(r[i]));
           }
         } else {
@@ -289,16 +300,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
         }
       }
+      if constexpr (SPLIT > 1) {
+        // exchange with the thread that owns the other columns of this row (named barrier per
+        // query tile: 256 threads; two buffers alternate so that one barrier per key tile suffices)
+        float* xb = xmax;  // one buffer, protected by the two barriers of this iteration
+        xb[part * 128 + row] = mx;
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "r"(128 * SPLIT) : "memory");
+        mx = fmaxf(mx, xb[(part ^ 1) * 128 + row]);
+      }
       const float m_new = fmaxf(m, mx);
       const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;  // a fully masked row keeps p = 0
       const float alpha = ex2_approx((m - m_use) * sl2);
       const float msl2 = m_use * sl2;
       // the previous tile's P V is complete by now (the tensor core ran it before this S)
       if (j > 0) fold(jph ^ 1, alpha_prev);
-      // pass 2: probabilities -> shared memory (bf16), row sum
+      // pass 2: probabilities -> shared memory (bf16), partial row sum
       float rs0 = 0.0f, rs1 = 0.0f;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < CW / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(tS + c * 32, r);
         tmem_ld_wait();
@@ -308,7 +327,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), sl2, -msl2));
           float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), sl2, -msl2));
           if (need_mask) {
-            const int kc = j * 128 + c * 32 + i;
+            const int kc = j * 128 + part * CW + c * 32 + i;
             if (kc >= p.S || (p.causal && kc > qrow)) p0 = 0.0f;
             if (kc + 1 >= p.S || (p.causal && kc + 1 > qrow)) p1 = 0.0f;
           }
@@ -316,7 +335,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           rs1 += p1;
           pk[i >> 1] = pack_bf16x2(p0, p1);
         }
-        store_row_chunk32(sP, row, c * 32, pk);
+        store_row_chunk32(sP, row, part * CW + c * 32, pk);
       }
       l = fmaf(l, alpha, rs0 + rs1);
       m = m_new;
@@ -324,17 +343,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before_sync();
       fence_proxy_async_smem();
       mbar_arrive(&p_ready[t]);
+      if constexpr (SPLIT > 1) {
+        // the exchange buffer may be rewritten only after both threads of every row have read it
+        asm volatile("bar.sync %0, %1;" ::"r"(3 + t), "r"(128 * SPLIT) : "memory");
+      }
     }
     if (n_mine > 0) {
-      // the last fold needs no rescale beyond the one already folded into l: acc is scaled to the
-      // running maximum of the tile before, so apply the last alpha
       fold((n_mine - 1) & 1, alpha_prev);
+      if constexpr (SPLIT > 1) {
+        // total row sum = sum of the two partial sums (both were rescaled with the same maxima)
+        xmax[part * 128 + row] = l;
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "r"(128 * SPLIT) : "memory");
+        l += xmax[(part ^ 1) * 128 + row];
+      }
       if (qrow < p.S) {
         const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
         __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + (long long)b * p.o_bs + (long long)qrow * p.o_ss +
-                              (long long)h * p.o_hs;
+                              (long long)h * p.o_hs + part * DW;
 #pragma unroll
-        for (int c = 0; c < D / 8; ++c) {
+        for (int c = 0; c < DW / 8; ++c) {
           uint4 o;
           o.x = pack_bf16x2(acc[c * 8 + 0] * inv, acc[c * 8 + 1] * inv);
           o.y = pack_bf16x2(acc[c * 8 + 2] * inv, acc[c * 8 + 3] * inv);
@@ -342,7 +369,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           o.w = pack_bf16x2(acc[c * 8 + 6] * inv, acc[c * 8 + 7] * inv);
           reinterpret_cast<uint4*>(orow)[c] = o;
         }
-        if (p.lse) p.lse[((long long)b * p.Hq + h) * p.S + qrow] = (l > 0.0f) ? m * p.scale + logf(l) : -INFINITY;
+        if (p.lse && part == 0) p.lse[((long long)b * p.Hq + h) * p.S + qrow] = (l > 0.0f) ? m * p.scale + logf(l) : -INFINITY;
       }
     }
   }
@@ -352,7 +379,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (*abort_flag) {
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
-  if (warp == 9) {
+  if (warp == Cfg::SWARPS + 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
@@ -777,11 +804,11 @@ int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, vo
   if (D == 64) {
     static bool set64 = false;
     if (!set64) { if (cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<64>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute"); set64 = true; }
-    attn_fwd_kernel<64><<<grid, 320, FwdCfg<64>::SMEM, s>>>(tq, tk, tv, p);
+    attn_fwd_kernel<64><<<grid, FwdCfg<64>::THREADS, FwdCfg<64>::SMEM, s>>>(tq, tk, tv, p);
   } else {
     static bool set128 = false;
     if (!set128) { if (cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<128>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute"); set128 = true; }
-    attn_fwd_kernel<128><<<grid, 320, FwdCfg<128>::SMEM, s>>>(tq, tk, tv, p);
+    attn_fwd_kernel<128><<<grid, FwdCfg<128>::THREADS, FwdCfg<128>::SMEM, s>>>(tq, tk, tv, p);
   }
   return check_launch("attn_fwd");
 }
