@@ -34,8 +34,8 @@ CONFIGS = {
 NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # DRAM bytes per algorithmic FLOP of the tcgen05 GEMM, from the ncu capture summarised in
-# profiles/gemm_bf16_tc_M8192_N5632_K2048.md (117.9 MB for 1.890e11 FLOPs)
-GEMM_DRAM_BYTES_PER_FLOP = 117.9e6 / 1.890e11
+# profiles/gemm_bf16_tc2_M8192_N5632_K2048.md (119.5 MB for 1.890e11 FLOPs)
+GEMM_DRAM_BYTES_PER_FLOP = 119.5e6 / 1.890e11
 
 
 def model_flops_per_token(c):
@@ -339,7 +339,7 @@ def run_ours(args, cfg, name):
             "e2e": {"value": tps_e2e, "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * S * 4 * accum,
                     "d2h_bytes_per_step": 4 * accum, "ms_per_step": ms_e2e / args.steps, "last_loss": state["loss"]},
             "gpu_launches": int(launches),
-            "roofline": {"kernel": "gemm_bf16_tc_kernel (all launches of the step)", "bound": "tensor",
+            "roofline": {"kernel": "gemm_bf16_tc2_kernel / gemm_bf16_tc_kernel (all GEMM launches of the step)", "bound": "tensor",
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if peak else None,
                          "peak_source": "bf16_tflops_sustained of %s" % peaks["_source"],
                          "traffic": (gemm_fl / gemm_n) * GEMM_DRAM_BYTES_PER_FLOP if gemm_n else None,
