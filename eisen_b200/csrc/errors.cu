@@ -45,9 +45,9 @@ int eisen_gemm_set_mode(int mode) {
   return 0;
 }
 
-int eisen_gemm_bf16(void* stream, int a_mn, int b_mn, long long M, long long N, long long K, const void* A,
-                    long long lda, const void* B, long long ldb, void* C, long long ldc, int out_mode,
-                    int split_k, float alpha, int* status) {
+static int gemm_dispatch(void* stream, int a_mn, int b_mn, long long M, long long N, long long K, const void* A,
+                         long long lda, const void* B, long long ldb, void* C, long long ldc, const void* R, long long ldr,
+                         int out_mode, int split_k, float alpha, int* status) {
   if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL)
     return eisen::fail(EISEN_ERR_LIMIT, "gemm_bf16: a dimension exceeds 2^31-1");
   if (out_mode < 0 || out_mode > 4) return eisen::fail(EISEN_ERR_INVALID, "gemm_bf16: bad out_mode");
@@ -61,12 +61,25 @@ int eisen_gemm_bf16(void* stream, int a_mn, int b_mn, long long M, long long N, 
   }
   const char* err = nullptr;
   int rc = pair ? eisen::gemm_bf16_tc_pair((cudaStream_t)stream, a_mn, b_mn, (int)M, (int)N, (int)K, A, lda, B, ldb, C, ldc,
-                                           out_mode, split_k, alpha, status, &err)
+                                           R, ldr, out_mode, split_k, alpha, status, &err)
                 : eisen::gemm_bf16_tc((cudaStream_t)stream, a_mn, b_mn, (int)M, (int)N, (int)K, A, lda, B, ldb, C, ldc,
-                                      out_mode, split_k, alpha, status, &err);
+                                      R, ldr, out_mode, split_k, alpha, status, &err);
   if (rc) return eisen::fail(rc == 1 ? EISEN_ERR_INVALID : EISEN_ERR_CUDA, err ? err : "gemm_bf16 failed");
   if (M > 0 && N > 0 && K > 0) eisen::count_launch();
   return 0;
+}
+
+int eisen_gemm_bf16(void* stream, int a_mn, int b_mn, long long M, long long N, long long K, const void* A,
+                    long long lda, const void* B, long long ldb, void* C, long long ldc, int out_mode,
+                    int split_k, float alpha, int* status) {
+  return gemm_dispatch(stream, a_mn, b_mn, M, N, K, A, lda, B, ldb, C, ldc, nullptr, 0, out_mode, split_k, alpha, status);
+}
+
+int eisen_gemm_bf16_residual(void* stream, int a_mn, int b_mn, long long M, long long N, long long K, const void* A,
+                             long long lda, const void* B, long long ldb, const void* R, long long ldr, void* C,
+                             long long ldc, float alpha, int* status) {
+  if (!R) return eisen::fail(EISEN_ERR_INVALID, "gemm_bf16_residual: R is null");
+  return gemm_dispatch(stream, a_mn, b_mn, M, N, K, A, lda, B, ldb, C, ldc, R, ldr, eisen::GEMM_OUT_BF16_ACC, 1, alpha, status);
 }
 
 }  // extern "C"

@@ -7,18 +7,37 @@
 namespace eisen {
 
 // v[0..32) = alpha-scaled accumulator values of row `row`, columns [col0, col0 + 32)
-__device__ __forceinline__ void gemm_store_chunk32(void* C, long long ldc, int out_mode, int row, int col0, int N,
-                                                   float (&v)[32]) {
+// Early load of the bf16 addend of one chunk (32 columns of one row), so that its latency overlaps
+// the TMEM load and the stores of the chunk before.  Returns false when the chunk is ragged or
+// unaligned; the store then reads the addend itself.
+__device__ __forceinline__ bool gemm_prefetch_addend(const void* R, long long ldr, int row, int col0, int N, bool row_ok,
+                                                     uint4 (&pre)[4]) {
+  if (!row_ok || col0 + 32 > N) return false;
+  const __nv_bfloat16* r_row = reinterpret_cast<const __nv_bfloat16*>(R) + (long long)row * ldr + col0;
+  if (reinterpret_cast<uintptr_t>(r_row) & 15) return false;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) pre[j] = reinterpret_cast<const uint4*>(r_row)[j];
+  return true;
+}
+
+// In GEMM_OUT_BF16_ACC mode the addend is read from R (leading dimension ldr): R == C accumulates
+// in place, another R adds a residual tensor while storing.  `pre` holds the addend when
+// `have_pre` is set (see gemm_prefetch_addend).
+__device__ __forceinline__ void gemm_store_chunk32(void* C, long long ldc, const void* R, long long ldr, int out_mode,
+                                                   int row, int col0, int N, float (&v)[32], const uint4 (&pre)[4],
+                                                   bool have_pre) {
   const bool full = (col0 + 32 <= N);
   if (out_mode == GEMM_OUT_BF16 || out_mode == GEMM_OUT_BF16_ACC) {
     __nv_bfloat16* c_row = reinterpret_cast<__nv_bfloat16*>(C) + (long long)row * ldc + col0;
-    const bool vec = full && ((reinterpret_cast<uintptr_t>(c_row) & 15) == 0);
+    const __nv_bfloat16* r_row = reinterpret_cast<const __nv_bfloat16*>(R) + (long long)row * ldr + col0;
+    const bool vec = full && ((reinterpret_cast<uintptr_t>(c_row) & 15) == 0) &&
+                     (out_mode != GEMM_OUT_BF16_ACC || (reinterpret_cast<uintptr_t>(r_row) & 15) == 0);
     if (vec) {
       uint4* dst = reinterpret_cast<uint4*>(c_row);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         if (out_mode == GEMM_OUT_BF16_ACC) {
-          uint4 old = dst[j];
+          uint4 old = have_pre ? pre[j] : reinterpret_cast<const uint4*>(r_row)[j];
           const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&old);
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -37,7 +56,7 @@ __device__ __forceinline__ void gemm_store_chunk32(void* C, long long ldc, int o
     } else {
       for (int i = 0; i < 32 && col0 + i < N; ++i) {
         float x = v[i];
-        if (out_mode == GEMM_OUT_BF16_ACC) x += __bfloat162float(c_row[i]);
+        if (out_mode == GEMM_OUT_BF16_ACC) x += __bfloat162float(r_row[i]);
         c_row[i] = __float2bfloat16(x);
       }
     }

@@ -17,13 +17,13 @@ enum GemmOutMode : int {
 // a_mn / b_mn: 0 = K-major operand ([rows][K]), 1 = MN-major operand ([K][rows]).
 // Returns 0 on success; *err points at a static message otherwise.  Asynchronous on `stream`.
 int gemm_bf16_tc(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int K, const void* A,
-                 long long lda, const void* B, long long ldb, void* C, long long ldc, int out_mode,
-                 int split_k, float alpha, int* status, const char** err);
+                 long long lda, const void* B, long long ldb, void* C, long long ldc, const void* R, long long ldr,
+                 int out_mode, int split_k, float alpha, int* status, const char** err);
 
 // paired-CTA (cta_group::2) variant: 256 x 256 tile per cluster of two CTAs (gemm_tc2.cu)
 int gemm_bf16_tc_pair(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int K, const void* A, long long lda,
-                      const void* B, long long ldb, void* C, long long ldc, int out_mode, int split_k, float alpha,
-                      int* status, const char** err);
+                      const void* B, long long ldb, void* C, long long ldc, const void* R, long long ldr, int out_mode,
+                      int split_k, float alpha, int* status, const char** err);
 int gemm_pair_auto_split_k(int M, int N, int K);
 int gemm_num_sms();
 

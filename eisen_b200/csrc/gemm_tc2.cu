@@ -34,6 +34,8 @@ struct PairParams {
   int a_mn, b_mn;
   void* C;
   long long ldc;
+  const void* R;  // addend of the bf16 accumulate mode (C itself, or a residual tensor)
+  long long ldr;
   int out_mode;
   int split_k, kblocks_per_split, kblocks_total;
   int m_tiles, n_tiles, total_tiles;  // m_tiles counts 256-row pair tiles
@@ -189,17 +191,27 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * P_ACC_COLS + (uint32_t(q * 32) << 16);
       const bool row_ok = row < p.M;
+      const bool acc_bf16 = p.out_mode == GEMM_OUT_BF16_ACC && has_k;
+      uint4 pre_cur[4], pre_next[4];
+      bool have_cur = acc_bf16 && gemm_prefetch_addend(p.R, p.ldr, row, n0, p.N, row_ok, pre_cur);
 #pragma unroll 1
       for (int c = 0; c < PN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        // the addend of the next chunk is requested before this chunk's TMEM load and stores
+        const bool have_next = acc_bf16 && c + 1 < PN / 32 &&
+                               gemm_prefetch_addend(p.R, p.ldr, row, col0 + 32, p.N, row_ok, pre_next);
         uint32_t r[32];
         tmem_ld_32x32b_x32(taddr + c * 32, r);
         tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        if (!row_ok || col0 >= p.N || !has_k) continue;
-        float v[32];
+        if (row_ok && col0 < p.N && has_k) {
+          float v[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-        gemm_store_chunk32(p.C, p.ldc, p.out_mode, row, col0, p.N, v);
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+          gemm_store_chunk32(p.C, p.ldc, p.R, p.ldr, p.out_mode, row, col0, p.N, v, pre_cur, have_cur);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) pre_cur[j] = pre_next[j];
+        have_cur = have_next;
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -225,8 +237,8 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 }  // namespace
 
 int gemm_bf16_tc_pair(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int K, const void* A, long long lda,
-                      const void* B, long long ldb, void* C, long long ldc, int out_mode, int split_k, float alpha,
-                      int* status, const char** err) {
+                      const void* B, long long ldb, void* C, long long ldc, const void* R, long long ldr, int out_mode, int split_k,
+                      float alpha, int* status, const char** err) {
   static bool attr_set = false;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) {
@@ -251,6 +263,7 @@ int gemm_bf16_tc_pair(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int
   p.M = M; p.N = N; p.K = K;
   p.a_mn = a_mn; p.b_mn = b_mn;
   p.C = C; p.ldc = ldc; p.out_mode = out_mode;
+  p.R = R ? R : C; p.ldr = R ? ldr : ldc;
   p.m_tiles = (M + 2 * PM - 1) / (2 * PM);
   p.n_tiles = (N + PN - 1) / PN;
   p.kblocks_total = (K + BK - 1) / BK;

@@ -157,6 +157,9 @@ OP1(transpose_0213, transpose_0213)
 OP2(repeat_kv, repeat_kv)
 OP2(rope, rope)
 
+int eisen_graph_matmul_add(void* g, long long a, long long b, long long r, long long* out) {
+  return guarded([&] { *out = G(g).matmul_add(a, b, r); });
+}
 int eisen_graph_bmm(void* g, long long a, long long b, int trans_b, long long* out) {
   return guarded([&] { *out = G(g).bmm(a, b, trans_b != 0); });
 }

@@ -537,6 +537,56 @@ int64_t Graph::matmul(int64_t a, int64_t b) {
   return o;
 }
 
+// out[m,n] = r[m,n] + a[m,k] b[k,n]: `Linear` followed by the residual `add` of
+// src/nn/transformer.rs:36, 47, with the add folded into the GEMM epilogue (Bf16Mixed only)
+int64_t Graph::matmul_add(int64_t a, int64_t b, int64_t r) {
+  if (precision != Precision::Bf16Mixed) invalid("matmul_add: fused residual epilogue runs in Bf16Mixed mode");
+  const HTensor& ta = tensors.at(a);
+  const HTensor& tb = tensors.at(b);
+  const HTensor& tr = tensors.at(r);
+  if (tb.shape.size() != 2) invalid("matmul_add: rhs must have rank 2 [k, n]");
+  const int64_t k = ta.shape.back(), m = ta.numel / k, n = tb.shape[1];
+  if (tb.shape[0] != k || tr.numel != m * n) invalid("matmul_add: shape mismatch");
+  int64_t o = alloc_pooled(tr.shape);
+  if (!skip_forward) {
+    prof_begin(0, 2.0 * (double)m * (double)n * (double)k);
+    ck(eisen_gemm_bf16_residual(stream, 0, 1, m, n, k, operand(tensors[a]), k, operand(tensors[b]), n, operand(tensors[r]),
+                                n, tensors[o].data, n, 1.0f, status_dev),
+       "matmul_add");
+    prof_end();
+  }
+  if (!no_grad) {
+    tape.push_back({{a, b, r}, o, [this, a, b, r, o, m, n, k]() {
+      OUT_GRAD_OR_RETURN(o);
+      HTensor& ga = tensors[a];
+      HTensor& gb = tensors[b];
+      HTensor& gr = tensors[r];
+      const bool move_to_r = !gr.constant && gr.grad == nullptr && gr.is_pooled && to.is_pooled &&
+                             gr.grad_dtype == to.grad_dtype && gr.numel == to.numel;
+      if (!gr.constant && !move_to_r) {  // dR (+)= dOut
+        ensure_grad(r);
+        ck(eisen_accumulate(stream, gr.grad, gr.grad_dtype, to.grad, to.grad_dtype, m * n, gr.grad_init), "matmul_add.bwd(r)");
+        gr.grad_init = true;
+      }
+      struct MoveGrad {  // dR = dOut without a copy: the output's gradient buffer becomes the residual's
+        HTensor& from; HTensor& dst; bool on;
+        ~MoveGrad() { if (on) { dst.grad = from.grad; dst.grad_init = true; from.grad = nullptr; from.grad_init = false; } }
+      } mover{to, gr, move_to_r};
+      if (!ga.constant) {
+        ensure_grad(a);
+        gemm(*this, false, false, m, k, n, to.grad, operand(gb), ga.grad, ga.grad_dtype, ga.grad_init);
+        ga.grad_init = true;
+      }
+      if (!gb.constant) {
+        ensure_grad(b);
+        gemm(*this, true, true, k, n, m, operand(ga), to.grad, gb.grad, gb.grad_dtype, gb.grad_init);
+        gb.grad_init = true;
+      }
+    }});
+  }
+  return o;
+}
+
 // src/graph/ops/linear.rs:301-523 (tied LM head): C[m,n] = A[m,k] B[n,k]^T
 int64_t Graph::matmul_trans_b(int64_t a, int64_t b) {
   const HTensor& ta = tensors.at(a);

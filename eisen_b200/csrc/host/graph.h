@@ -81,6 +81,8 @@ class Graph {
   int64_t swiglu(int64_t gate, int64_t up);
   int64_t matmul(int64_t a, int64_t b);
   int64_t matmul_trans_b(int64_t a, int64_t b);
+  // r + a b in one launch (Bf16Mixed): the residual add done in the projection's epilogue
+  int64_t matmul_add(int64_t a, int64_t b, int64_t r);
   int64_t bmm(int64_t a, int64_t b, bool trans_b);
   int64_t softmax(int64_t a);
   int64_t cross_entropy(int64_t logits, const int64_t* targets, int64_t n);
@@ -161,7 +163,7 @@ class TransformerLM {
   int64_t forward(Graph& g, int64_t x_ids);                       // :184-196
   // skip_dead_tail: leave out the forward kernels whose results no backward node reads
   int64_t block_forward(Graph& g, const BlockParams& b, int64_t x, bool skip_dead_tail = false);  // :32-49
-  int64_t gqa_forward(Graph& g, const BlockParams& b, int64_t x, bool causal);  // attention.rs:289-388
+  int64_t gqa_forward(Graph& g, const BlockParams& b, int64_t x, bool causal, int64_t residual = -1);  // attention.rs:289-388
   std::vector<int64_t> params() const;                            // :198-210
   // One micro-step: forward, loss (masked cross-entropy over [B*S] targets), backward.
   // checkpoint = true keeps only block inputs in the forward and re-runs each block under a

@@ -113,7 +113,7 @@ std::vector<int64_t> TransformerLM::params() const {
   return p;
 }
 
-int64_t TransformerLM::gqa_forward(Graph& g, const BlockParams& b, int64_t x, bool causal) {
+int64_t TransformerLM::gqa_forward(Graph& g, const BlockParams& b, int64_t x, bool causal, int64_t residual) {
   const std::vector<int64_t> xs = g.tensors.at(x).shape;
   if (xs.size() != 3) throw EisenException(EISEN_ERR_INVALID, "GQA requires [Batch, Seq, Dim]");
   const int64_t B = xs[0], S = xs[1], hd = hidden / heads;
@@ -161,13 +161,24 @@ int64_t TransformerLM::gqa_forward(Graph& g, const BlockParams& b, int64_t x, bo
     int64_t ct = g.transpose_0213(ctx);
     ctx2 = g.reshape(ct, {B, S, hidden});
   }
+  if (residual >= 0) {  // residual + out_proj(ctx) in one launch
+    const std::vector<int64_t> rs = g.tensors.at(residual).shape;
+    int64_t o = g.matmul_add(ctx2, b.o, residual);
+    g.reinterpret_shape(o, rs);
+    return o;
+  }
   return linear_fwd(g, ctx2, b.o);
 }
 
 int64_t TransformerLM::block_forward(Graph& g, const BlockParams& b, int64_t x, bool skip_dead_tail) {
   int64_t n1 = g.rms_norm(x, b.norm1, 1e-5f);
-  int64_t at = gqa_forward(g, b, n1, true);
-  int64_t r1 = g.add(x, at);
+  int64_t r1;
+  if (fused) {
+    r1 = gqa_forward(g, b, n1, true, x);
+  } else {
+    int64_t at = gqa_forward(g, b, n1, true, -1);
+    r1 = g.add(x, at);
+  }
   int64_t n2 = g.rms_norm(r1, b.norm2, 1e-5f);
   int64_t go = linear_fwd(g, n2, b.gate);
   int64_t up, gd;
@@ -182,8 +193,14 @@ int64_t TransformerLM::block_forward(Graph& g, const BlockParams& b, int64_t x, 
   // the down projection's output and the second residual sum feed only the next block: when a
   // checkpointed block is re-run for its backward pass nothing reads them
   g.skip_forward = skip_dead_tail;
-  int64_t f2 = linear_fwd(g, gd, b.down);
-  int64_t out = g.add(r1, f2);
+  int64_t out;
+  if (fused) {
+    out = g.matmul_add(gd, b.down, r1);
+    g.reinterpret_shape(out, g.tensors[r1].shape);
+  } else {
+    int64_t f2 = linear_fwd(g, gd, b.down);
+    out = g.add(r1, f2);
+  }
   g.skip_forward = false;
   return out;
 }

@@ -176,6 +176,10 @@ class Graph:
     def matmul(self, a, b):
         return self._op("matmul", a, b)
 
+    def matmul_add(self, a, b, r):
+        """r + a @ b with the residual add fused into the GEMM epilogue (Bf16Mixed)."""
+        return self._op("matmul_add", a, b, r)
+
     def matmul_trans_b(self, a, b):
         return self._op("matmul_trans_b", a, b)
 

@@ -65,6 +65,13 @@ int eisen_gemm_bf16(void* stream, int a_mn, int b_mn, long long M, long long N, 
                     long long lda, const void* B, long long ldb, void* C, long long ldc, int out_mode,
                     int split_k, float alpha, int* status);
 
+/* C(bf16)[M,N] = alpha * sum_k A(m,k) B(n,k) + R(bf16)[M,N]: the residual add of
+ * src/nn/transformer.rs:36 and :47 (`g.add(x, attn_out)`, `g.add(res1, ffn2_out)`) done in the
+ * epilogue of the projection that produces the second addend.  R may not alias C. */
+int eisen_gemm_bf16_residual(void* stream, int a_mn, int b_mn, long long M, long long N, long long K, const void* A,
+                             long long lda, const void* B, long long ldb, const void* R, long long ldr, void* C,
+                             long long ldc, float alpha, int* status);
+
 /* Tile shape of eisen_gemm_bf16: 0 = chosen per problem shape, 1 = single-CTA 128x256 tiles,
  * 2 = paired-CTA 256x256 tiles (tcgen05 cta_group::2, one cluster of two CTAs per tile).
  * Process-wide; meant for tests and measurements. */
@@ -268,6 +275,7 @@ int eisen_graph_silu(void* g, long long a, long long* out);
 int eisen_graph_swiglu(void* g, long long gate, long long up, long long* out);          /* fused silu(gate)*up */
 int eisen_graph_matmul(void* g, long long a, long long b, long long* out);
 int eisen_graph_matmul_trans_b(void* g, long long a, long long b, long long* out);
+int eisen_graph_matmul_add(void* g, long long a, long long b, long long r, long long* out); /* r + a b, fused epilogue (Bf16Mixed) */
 int eisen_graph_bmm(void* g, long long a, long long b, int trans_b, long long* out);
 int eisen_graph_softmax(void* g, long long a, long long* out);
 int eisen_graph_cross_entropy(void* g, long long logits, const long long* targets, long long n, long long* out);
