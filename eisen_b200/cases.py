@@ -38,7 +38,7 @@ def timed(fn, iters, warmup=1):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "attn", "ce", "rmsnorm", "adamw", "swiglu"])
+    ap.add_argument("case", choices=["gemm", "attn", "ce", "rmsnorm", "adamw", "swiglu", "elementwise"])
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=5632)
@@ -117,6 +117,39 @@ def main():
         mf = timed(lambda: eb.call("eisen_swiglu_fwd", s, P(g_), P(u_), P(h), n, eb.BF16), a.iters)
         mb = timed(lambda: eb.call("eisen_swiglu_bwd", s, P(g_), P(u_), P(dh), P(dg), P(du), n, eb.BF16, 0), a.iters)
         out.update(fwd_ms=mf, fwd_gbs=n * 6 / mf / 1e6, bwd_ms=mb, bwd_gbs=n * 10 / mb / 1e6)
+    elif a.case == "elementwise":
+        # residual add, gradient accumulate, RoPE forward / backward, embedding gather / scatter, squared norm
+        rows, dim = a.rows, a.dim
+        n = rows * dim
+        x, y = (torch.randn(n, device=dev).to(torch.bfloat16) for _ in range(2))
+        o = torch.empty_like(x)
+        ms = timed(lambda: eb.call("eisen_add", s, P(x), P(y), P(o), n, n, eb.BF16), a.iters)
+        out["add_gbs"] = n * 6 / ms / 1e6
+        ms = timed(lambda: eb.call("eisen_accumulate", s, P(o), eb.BF16, P(x), eb.BF16, n, 1), a.iters)
+        out["accumulate_gbs"] = n * 6 / ms / 1e6
+        S, hd = a.seq, a.head_dim
+        tab = torch.empty(S, hd // 2, 2, device=dev)
+        eb.call("eisen_rope_table", s, P(tab), S, hd, 10000.0)
+        ms = timed(lambda: eb.call("eisen_rope", s, P(x), P(o), P(tab), rows // S, S, dim, hd, eb.BF16, 0, 0), a.iters)
+        out["rope_fwd_gbs"] = n * 4 / ms / 1e6
+        ms = timed(lambda: eb.call("eisen_rope", s, P(x), P(o), P(tab), rows // S, S, dim, hd, eb.BF16, 1, 0), a.iters)
+        out["rope_bwd_gbs"] = n * 4 / ms / 1e6
+        V = a.vocab
+        table = torch.randn(V, dim, device=dev).to(torch.bfloat16)
+        ids = torch.randint(0, V, (rows,), device=dev, dtype=torch.int32)
+        ms = timed(lambda: eb.call("eisen_embedding_fwd", s, P(table), eb.BF16, P(ids), P(o), eb.BF16, rows, dim, V, None), a.iters)
+        out["embedding_fwd_gbs"] = (n * 4 + rows * 4) / ms / 1e6
+        dw = torch.zeros(V, dim, device=dev)
+        ws = torch.empty(eb.lib().eisen_embedding_bwd_workspace_bytes(rows, V), dtype=torch.uint8, device=dev)
+        ms = timed(lambda: eb.call("eisen_embedding_bwd", s, P(x), eb.BF16, P(ids), P(dw), P(ws), rows, dim, V), a.iters)
+        touched = len(torch.unique(ids))
+        out["embedding_bwd_gbs"] = (n * 2 + touched * dim * 8 + rows * 4) / ms / 1e6
+        out["embedding_bwd_ms"] = ms
+        g32 = torch.randn(a.nelem, device=dev)
+        ws2 = torch.empty(eb.lib().eisen_sumsq_workspace_bytes(a.nelem), dtype=torch.uint8, device=dev)
+        ss = torch.zeros(1, dtype=torch.float64, device=dev)
+        ms = timed(lambda: eb.call("eisen_sumsq", s, P(g32), a.nelem, P(ws2), P(ss), 0), a.iters)
+        out["sumsq_gbs"] = a.nelem * 4 / ms / 1e6
     else:
         n = a.nelem
         w, g_, m, v = (torch.randn(n, device=dev) * 1e-3 for _ in range(4))

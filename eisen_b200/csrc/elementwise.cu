@@ -189,6 +189,16 @@ int eisen_add(void* stream, const void* a, const void* b, void* out, long long n
     constexpr int V = VecOf<T>::N;
     const T* pa = (const T*)a; const T* pb = (const T*)b; T* po = (T*)out;
     const bool vec_b = (b_numel % V) == 0;
+    if (b_numel == n) {  // plain residual add: no broadcast index arithmetic
+      return launch_vec<V>(s, n, [=] __device__(long long i, int c) {
+        float x[V], y[V];
+        load_n(pa + i, x, c);
+        load_n(pb + i, y, c);
+#pragma unroll
+        for (int k = 0; k < V; ++k) x[k] += y[k];
+        store_n(po + i, x, c);
+      }, "add");
+    }
     return launch_vec<V>(s, n, [=] __device__(long long i, int c) {
       float x[V], y[V];
       load_n(pa + i, x, c);
@@ -403,6 +413,27 @@ int eisen_rope(void* stream, const void* x, void* y, const float* table_cos_sin,
     constexpr int V = VecOf<T>::N;
     const T* px = (const T*)x; T* py = (T*)y;
     // a 16-byte vector never straddles a row when hidden % V == 0; otherwise go pair by pair
+    if (hidden % V == 0 && head_dim % V == 0 && n < 0x7fffffffLL) {
+      // common case: a vector stays inside one head and 32-bit index arithmetic is enough
+      const unsigned hid = (unsigned)hidden, hdm = (unsigned)head_dim, sl = (unsigned)S;
+      return launch_vec<V>((cudaStream_t)stream, n, [=] __device__(long long i, int c) {
+        float v[V], r[V];
+        load_n(px + i, v, c);
+        const unsigned iu = (unsigned)i;
+        const unsigned row = iu / hid;
+        const unsigned pos = row % sl;
+        const unsigned p0 = ((iu - row * hid) % hdm) >> 1;  // first pair of this vector inside its head
+        const float2* trow = tab + pos * half + p0;
+#pragma unroll
+        for (int k = 0; k < V; k += 2) {
+          const float2 cs = trow[k >> 1];
+          const float sn = sgn * cs.y;
+          r[k] = v[k] * cs.x - v[k + 1] * sn;
+          r[k + 1] = v[k] * sn + v[k + 1] * cs.x;
+        }
+        store_acc_n(py + i, r, c, acc);
+      }, "rope");
+    }
     if (hidden % V == 0) {
       return launch_vec<V>((cudaStream_t)stream, n, [=] __device__(long long i, int c) {
         float v[V], r[V];

@@ -3,13 +3,15 @@
 //
 // Token ids are int32 on the device (the reference keeps them as f32 and, in bf16 mode, rounds
 // them through bf16).  The backward is deterministic and free of floating-point atomics:
-//   1. rank[i]   = number of earlier positions j < i with ids[j] == ids[i]   (integer)
-//      count[v]  = occurrences of id v                                       (integer atomics)
-//   2. offset[v] = exclusive prefix sum of count                             (one CTA)
-//   3. perm[offset[ids[i]] + rank[i]] = i      -> positions grouped by id, in position order
-//   4. one warp per vocabulary row sums its positions' gradient rows in that fixed order and
+//   1. count[v]  = occurrences of id v                                       (integer atomics)
+//   2. offset[v] = exclusive prefix sum of count; cursor = offset            (one CTA)
+//   3. slot[cursor[ids[i]]++] = i     -> positions grouped by id, in arrival order
+//   4. perm[offset[id] + #{slots of the same id holding a smaller position}] = position
+//      -> positions grouped by id, in position order: whatever order step 3 ran in, the
+//      result is the stable sort of the ids
+//   5. one warp per vocabulary row sums its positions' gradient rows in that fixed order and
 //      adds the sum to the f32 weight gradient.
-// Steps 1-3 are exact integer bookkeeping (identical to a stable sort of the ids).
+// Steps 1-4 are exact integer bookkeeping; their cost is O(n + vocab + sum of count^2).
 #include "common.cuh"
 #include "errors.h"
 #include "../../include/eisen_b200.h"
@@ -58,40 +60,34 @@ gather_rows_vec_kernel(const T* __restrict__ w, const int* __restrict__ ids, T* 
   }
 }
 
-constexpr int RANK_TILE = 1024;
-
-// rank[i] = #{ j < i : ids[j] == ids[i] }; count[ids[i]] += 1
 __global__ void __launch_bounds__(256)
-rank_kernel(const int* __restrict__ ids, int* __restrict__ rank, int* __restrict__ count, int n, int vocab) {
-  __shared__ int tile[RANK_TILE];
+count_kernel(const int* __restrict__ ids, int* __restrict__ count, int n, int vocab) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  const int my = (i < n) ? ids[i] : -1;
-  const int last = min(n, (int)((blockIdx.x + 1) * blockDim.x));  // ids at or after `last` cannot precede
-  int r = 0;
-  for (int base = 0; base < last; base += RANK_TILE) {
-    __syncthreads();
-    for (int t = threadIdx.x; t < RANK_TILE; t += blockDim.x) tile[t] = (base + t < n) ? ids[base + t] : -2;
-    __syncthreads();
-    const int lim = min(RANK_TILE, i - base);  // only j < i
-    for (int t = 0; t < lim; ++t) r += (tile[t] == my);
-  }
-  if (i < n) {
-    rank[i] = r;
-    if (my >= 0 && my < vocab) atomicAdd(&count[my], 1);
-  }
+  if (i >= n) return;
+  const int id = ids[i];
+  if (id >= 0 && id < vocab) atomicAdd(&count[id], 1);
 }
 
-// exclusive scan of count[0..vocab) by one CTA of 1024 threads
-__global__ void __launch_bounds__(1024) scan_kernel(const int* __restrict__ count, int* __restrict__ offset, int vocab) {
+// exclusive scan of count[0..vocab) by one CTA of 1024 threads, 8 consecutive entries per thread
+// and pass; writes the result to offset and to cursor
+constexpr int SCAN_ITEMS = 8;
+__global__ void __launch_bounds__(1024)
+scan_kernel(const int* __restrict__ count, int* __restrict__ offset, int* __restrict__ cursor, int vocab) {
   __shared__ int warp_tot[32];
   __shared__ int carry_sh;
   if (threadIdx.x == 0) carry_sh = 0;
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int base = 0; base < vocab; base += 1024) {
-    const int idx = base + threadIdx.x;
-    const int v = (idx < vocab) ? count[idx] : 0;
-    int inc = v;
+  for (int base = 0; base < vocab; base += 1024 * SCAN_ITEMS) {
+    const int idx0 = base + threadIdx.x * SCAN_ITEMS;
+    int v[SCAN_ITEMS];
+    int tsum = 0;
+#pragma unroll
+    for (int k = 0; k < SCAN_ITEMS; ++k) {
+      v[k] = (idx0 + k < vocab) ? count[idx0 + k] : 0;
+      tsum += v[k];
+    }
+    int inc = tsum;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       int t = __shfl_up_sync(0xffffffffu, inc, o);
@@ -111,20 +107,47 @@ __global__ void __launch_bounds__(1024) scan_kernel(const int* __restrict__ coun
     }
     __syncthreads();
     const int carry = carry_sh;
-    if (idx < vocab) offset[idx] = carry + warp_tot[warp] + inc - v;
+    int run = carry + warp_tot[warp] + inc - tsum;
+#pragma unroll
+    for (int k = 0; k < SCAN_ITEMS; ++k) {
+      if (idx0 + k < vocab) {
+        offset[idx0 + k] = run;
+        cursor[idx0 + k] = run;
+      }
+      run += v[k];
+    }
     __syncthreads();
-    if (threadIdx.x == 1023) carry_sh = carry + warp_tot[warp] + inc;
+    if (threadIdx.x == 1023) carry_sh = run;
     __syncthreads();
   }
 }
 
-__global__ void place_kernel(const int* __restrict__ ids, const int* __restrict__ rank,
-                             const int* __restrict__ offset, int* __restrict__ perm, int n, int vocab) {
+__global__ void __launch_bounds__(256)
+place_kernel(const int* __restrict__ ids, int* __restrict__ cursor, int* __restrict__ slot, int n, int vocab) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const int id = ids[i];
   if (id < 0 || id >= vocab) return;
-  perm[offset[id] + rank[i]] = i;
+  slot[atomicAdd(&cursor[id], 1)] = i;
+}
+
+// perm = slot with every id's segment put into increasing position order.  One thread per slot
+// counts the smaller positions of its segment (a warp mostly reads the same segment: broadcast).
+__global__ void __launch_bounds__(128)
+order_kernel(const int* __restrict__ ids, const int* __restrict__ slot, const int* __restrict__ offset,
+             const int* __restrict__ count, int* __restrict__ perm, int n_valid_max, int vocab) {
+  const int sidx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (sidx >= n_valid_max) return;
+  // slots past the number of valid ids were never written; offset[vocab-1] + count[vocab-1] bounds them
+  if (sidx >= offset[vocab - 1] + count[vocab - 1]) return;
+  const int pos = slot[sidx];
+  const int id = ids[pos];
+  const int off = offset[id], cnt = count[id];
+  int r = 0;
+  if (cnt > 1) {
+    for (int k = 0; k < cnt; ++k) r += (slot[off + k] < pos);
+  }
+  perm[off + r] = pos;
 }
 
 // one warp per vocabulary row: dW[v,:] += sum over its positions (fixed order) of g[pos,:]
@@ -152,6 +175,60 @@ scatter_rows_kernel(const TG* __restrict__ g, const int* __restrict__ perm, cons
 #pragma unroll
       for (int e = 0; e < 4; ++e)
         if (c + e < dim) drow[c + e] += a[e];
+    }
+  }
+}
+
+// the same for rows of whole 16-byte vectors: a lane owns SW vectors of a sweep of 32*SW vectors,
+// so SW independent 16-byte reads per lane are in flight for every position of the row
+template <typename TG, int SW>
+__global__ void __launch_bounds__(256)
+scatter_rows_vec_kernel(const TG* __restrict__ g, const int* __restrict__ perm, const int* __restrict__ offset,
+                        const int* __restrict__ count, float* __restrict__ dw, int vocab, int dim) {
+  constexpr int V = VecOf<TG>::N;
+  const int lane = threadIdx.x & 31;
+  const int warp0 = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int wstride = gridDim.x * (blockDim.x >> 5);
+  for (int v = warp0; v < vocab; v += wstride) {
+    const int cnt = count[v];
+    if (cnt == 0) continue;
+    const int off = offset[v];
+    float* drow = dw + (long long)v * dim;
+    for (int c0 = 0; c0 < dim; c0 += 32 * SW * V) {
+      float a[SW][V];
+#pragma unroll
+      for (int j = 0; j < SW; ++j)
+#pragma unroll
+        for (int e = 0; e < V; ++e) a[j][e] = 0.0f;
+      for (int k = 0; k < cnt; ++k) {
+        const TG* grow = g + (long long)perm[off + k] * dim;
+        float t[SW][V];
+#pragma unroll
+        for (int j = 0; j < SW; ++j) {
+          const int c = c0 + (j * 32 + lane) * V;
+          if (c < dim) ld16(grow + c, t[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < SW; ++j) {
+          const int c = c0 + (j * 32 + lane) * V;
+          if (c < dim) {
+#pragma unroll
+            for (int e = 0; e < V; ++e) a[j][e] += t[j][e];
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < SW; ++j) {
+        const int c = c0 + (j * 32 + lane) * V;
+        if (c < dim) {
+#pragma unroll
+          for (int e = 0; e < V; e += 4) {
+            float4 o = *reinterpret_cast<float4*>(drow + c + e);
+            o.x += a[j][e]; o.y += a[j][e + 1]; o.z += a[j][e + 2]; o.w += a[j][e + 3];
+            *reinterpret_cast<float4*>(drow + c + e) = o;
+          }
+        }
+      }
     }
   }
 }
@@ -187,9 +264,9 @@ int eisen_embedding_fwd(void* stream, const void* w, int w_dt, const int* ids, v
   return check_launch("embedding_fwd");
 }
 
-// scratch: count[vocab], offset[vocab], rank[n_ids], perm[n_ids] (int32 each)
+// scratch: count[vocab], offset[vocab], cursor[vocab], slot[n_ids], perm[n_ids] (int32 each)
 long long eisen_embedding_bwd_workspace_bytes(long long n_ids, long long vocab) {
-  return (2 * vocab + 2 * n_ids) * 4 + 64;
+  return (3 * vocab + 2 * n_ids) * 4 + 64;
 }
 
 // dW[ids[i],:] += g[i,:] for all i, deterministically.  perm_out (may be null) receives the
@@ -202,18 +279,28 @@ int eisen_embedding_bwd(void* stream, const void* g, int g_dt, const int* ids, f
   cudaStream_t s = (cudaStream_t)stream;
   int* count = (int*)workspace;
   int* offset = count + vocab;
-  int* rank = offset + vocab;
-  int* perm = rank + n_ids;
+  int* cursor = offset + vocab;
+  int* slot = cursor + vocab;
+  int* perm = slot + n_ids;
   if (cudaMemsetAsync(count, 0, (size_t)vocab * 4, s) != cudaSuccess) return fail(EISEN_ERR_CUDA, "embedding_bwd: memset failed");
   const int n = (int)n_ids;
-  rank_kernel<<<(n + 255) / 256, 256, 0, s>>>(ids, rank, count, n, (int)vocab);
-  scan_kernel<<<1, 1024, 0, s>>>(count, offset, (int)vocab);
-  place_kernel<<<(n + 255) / 256, 256, 0, s>>>(ids, rank, offset, perm, n, (int)vocab);
+  count_kernel<<<(n + 255) / 256, 256, 0, s>>>(ids, count, n, (int)vocab);
+  scan_kernel<<<1, 1024, 0, s>>>(count, offset, cursor, (int)vocab);
+  place_kernel<<<(n + 255) / 256, 256, 0, s>>>(ids, cursor, slot, n, (int)vocab);
+  order_kernel<<<(n + 127) / 128, 128, 0, s>>>(ids, slot, offset, count, perm, n, (int)vocab);
   const int grid = grid_for(vocab, 8, 8);
-  if (g_dt == DT_F32)
-    scatter_rows_kernel<float><<<grid, 256, 0, s>>>((const float*)g, perm, offset, count, dw, (int)vocab, (int)dim);
-  else
-    scatter_rows_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)g, perm, offset, count, dw, (int)vocab, (int)dim);
+  const bool vec = aligned16(g) && aligned16(dw) && dim % 8 == 0;
+  if (g_dt == DT_F32) {
+    if (vec)
+      scatter_rows_vec_kernel<float, 4><<<grid, 256, 0, s>>>((const float*)g, perm, offset, count, dw, (int)vocab, (int)dim);
+    else
+      scatter_rows_kernel<float><<<grid, 256, 0, s>>>((const float*)g, perm, offset, count, dw, (int)vocab, (int)dim);
+  } else {
+    if (vec)
+      scatter_rows_vec_kernel<__nv_bfloat16, 4><<<grid, 256, 0, s>>>((const __nv_bfloat16*)g, perm, offset, count, dw, (int)vocab, (int)dim);
+    else
+      scatter_rows_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)g, perm, offset, count, dw, (int)vocab, (int)dim);
+  }
   return check_launch("embedding_bwd");
 }
 
@@ -224,7 +311,7 @@ int eisen_embedding_bwd_bookkeeping(void* stream, const void* workspace, long lo
   cudaStream_t s = (cudaStream_t)stream;
   const int* count = (const int*)workspace;
   const int* offset = count + vocab;
-  const int* perm = offset + vocab + n_ids;
+  const int* perm = offset + 2 * vocab + n_ids;
   if (count_out && cudaMemcpyAsync(count_out, count, (size_t)vocab * 4, cudaMemcpyDeviceToDevice, s) != cudaSuccess) return fail(EISEN_ERR_CUDA, "bookkeeping copy failed");
   if (offset_out && cudaMemcpyAsync(offset_out, offset, (size_t)vocab * 4, cudaMemcpyDeviceToDevice, s) != cudaSuccess) return fail(EISEN_ERR_CUDA, "bookkeeping copy failed");
   if (perm_out && cudaMemcpyAsync(perm_out, perm, (size_t)n_ids * 4, cudaMemcpyDeviceToDevice, s) != cudaSuccess) return fail(EISEN_ERR_CUDA, "bookkeeping copy failed");
@@ -240,16 +327,16 @@ int eisen_embedding_bwd_bookkeeping(void* stream, const void* workspace, long lo
 // workspace on demand: an engine that runs under a fixed VRAM budget and accounts each buffer
 // in its own pool (the way the reference's Graph does with EISEN_VRAM_BUDGET_MB), or a training
 // loop that must not call cudaMalloc in the middle of a step because the call synchronises the
-// device.  For them the integer bookkeeping of the scatter (count, offset, rank, perm) lives in
+// device.  For them the integer bookkeeping of the scatter (count, offset, cursor, slot, perm) lives in
 // a fixed array inside the library image instead of a caller-provided workspace.
 //
 // The array is part of the module: every GPU that loads the library holds
-// (2 * 131072 + 2 * 65536) * 4 bytes = 1.5 MB of it until the process exits.
+// (3 * 131072 + 2 * 65536) * 4 bytes = 2 MB of it until the process exits.
 // ---------------------------------------------------------------------------------------
 namespace {
 constexpr long long kStaticMaxIds = 65536;     // token positions per call
 constexpr long long kStaticMaxVocab = 131072;  // rows of the embedding table
-static __device__ __align__(256) int g_embedding_static_scratch[2 * kStaticMaxVocab + 2 * kStaticMaxIds];
+static __device__ __align__(256) int g_embedding_static_scratch[3 * kStaticMaxVocab + 2 * kStaticMaxIds];
 
 // Device address of the array, looked up once per device.  In host code the array's name is only
 // a handle for the runtime, not an address a kernel could use, so it goes through
@@ -284,6 +371,6 @@ extern "C" int eisen_embedding_bwd_static(void* stream, const void* g, int g_dt,
   int* scratch = static_scratch_for_current_device(&err);
   if (!scratch) return fail(EISEN_ERR_CUDA, err);
   // same kernels as eisen_embedding_bwd; its first step clears count[0..vocab), the only part of
-  // the scratch that has to start at zero (offset, rank and perm are fully rewritten)
+  // the scratch that has to start at zero (offset, cursor, slot and perm are rewritten where read)
   return eisen_embedding_bwd(stream, g, g_dt, ids, dw, scratch, n_ids, dim, vocab);
 }

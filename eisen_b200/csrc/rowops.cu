@@ -15,6 +15,19 @@ namespace {
 // ---------------------------------------------------------------------------------------
 constexpr int RN_WARPS = 8;
 
+__device__ __forceinline__ void unpack16(const uint4& r, float (&v)[4]) {
+  v[0] = __uint_as_float(r.x); v[1] = __uint_as_float(r.y); v[2] = __uint_as_float(r.z); v[3] = __uint_as_float(r.w);
+}
+__device__ __forceinline__ void unpack16(const uint4& r, float (&v)[8]) {
+  const uint32_t u[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(u[i] << 16);          // low half = even element
+    v[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+  }
+}
+
+
 template <typename T>
 __global__ void __launch_bounds__(RN_WARPS * 32)
 rmsnorm_fwd_kernel(const T* __restrict__ x, const float* __restrict__ w, T* __restrict__ y,
@@ -60,6 +73,71 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const float* __restrict__ w, T* __re
   }
 }
 
+// Forward for rows that fit in registers: a warp owns a row, each lane keeps its NCH 16-byte
+// vectors packed, so x is read from memory once.
+template <typename T, int NCH>
+__global__ void __launch_bounds__(RN_WARPS * 32)
+rmsnorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ w, T* __restrict__ y,
+                       float* __restrict__ rrms_out, long long rows, int dim, float eps) {
+  constexpr int V = VecOf<T>::N;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (long long)blockIdx.x * RN_WARPS + (threadIdx.x >> 5);
+  const long long wstride = (long long)gridDim.x * RN_WARPS;
+  for (long long row = warp0; row < rows; row += wstride) {
+    const T* xr = x + row * dim;
+    T* yr = y + row * dim;
+    uint4 raw[NCH];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int c = (j * 32 + lane) * V;
+      raw[j] = (c < dim) ? *reinterpret_cast<const uint4*>(xr + c) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      float v[V];
+      unpack16(raw[j], v);
+#pragma unroll
+      for (int k = 0; k < V; ++k) ss += v[k] * v[k];
+    }
+    ss = warp_sum(ss);
+    const float rrms = 1.0f / sqrtf(ss / (float)dim + eps);
+    if (rrms_out && lane == 0) rrms_out[row] = rrms;
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int c = (j * 32 + lane) * V;
+      if (c < dim) {
+        float v[V], wv[V];
+        unpack16(raw[j], v);
+#pragma unroll
+        for (int k = 0; k < V; k += 4) {
+          const float4 t = *reinterpret_cast<const float4*>(w + c + k);
+          wv[k] = t.x; wv[k + 1] = t.y; wv[k + 2] = t.z; wv[k + 3] = t.w;
+        }
+#pragma unroll
+        for (int k = 0; k < V; ++k) v[k] = v[k] * rrms * wv[k];
+        st16(yr + c, v);
+      }
+    }
+  }
+}
+
+template <typename T>
+static void rmsnorm_fwd_dispatch(const T* x, const float* w, T* y, float* rrms_out, long long rows, int dim, float eps,
+                                 int grid, cudaStream_t s) {
+  constexpr int V = VecOf<T>::N;
+  const int nch = (dim + 32 * V - 1) / (32 * V);
+  if (dim % V == 0 && nch <= 16 && aligned16(w) && aligned16(x) && aligned16(y)) {
+    if (nch <= 1) rmsnorm_fwd_reg_kernel<T, 1><<<grid, RN_WARPS * 32, 0, s>>>(x, w, y, rrms_out, rows, dim, eps);
+    else if (nch <= 2) rmsnorm_fwd_reg_kernel<T, 2><<<grid, RN_WARPS * 32, 0, s>>>(x, w, y, rrms_out, rows, dim, eps);
+    else if (nch <= 4) rmsnorm_fwd_reg_kernel<T, 4><<<grid, RN_WARPS * 32, 0, s>>>(x, w, y, rrms_out, rows, dim, eps);
+    else if (nch <= 8) rmsnorm_fwd_reg_kernel<T, 8><<<grid, RN_WARPS * 32, 0, s>>>(x, w, y, rrms_out, rows, dim, eps);
+    else rmsnorm_fwd_reg_kernel<T, 16><<<grid, RN_WARPS * 32, 0, s>>>(x, w, y, rrms_out, rows, dim, eps);
+  } else {
+    rmsnorm_fwd_kernel<T><<<grid, RN_WARPS * 32, 0, s>>>(x, w, y, rrms_out, rows, dim, eps);
+  }
+}
+
 // Backward (src/graph/ops/normalization.rs:155-173):
 //   gdxw = sum_d dy*x*w ; dx (+)= rrms*dy*w - x*rrms^3/dim*gdxw ; dw[d] += dy*x*rrms
 // A CTA of 256 threads works on ROWS rows at a time; thread t owns the columns of vector
@@ -68,23 +146,21 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const float* __restrict__ w, T* __re
 // shuffle + shared-memory exchange per group of ROWS rows.  Each CTA writes one row of
 // `dw_partial` [gridDim.x, dim]; a second kernel adds the partials in a fixed order (no atomics,
 // run-to-run deterministic).
-__device__ __forceinline__ void unpack16(const uint4& r, float (&v)[4]) {
-  v[0] = __uint_as_float(r.x); v[1] = __uint_as_float(r.y); v[2] = __uint_as_float(r.z); v[3] = __uint_as_float(r.w);
-}
-__device__ __forceinline__ void unpack16(const uint4& r, float (&v)[8]) {
-  const uint32_t u[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    v[2 * i] = __uint_as_float(u[i] << 16);          // low half = even element
-    v[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
-  }
+// 16-byte read of data that is used once: no allocation in L1
+template <typename T>
+__device__ __forceinline__ uint4 ld_stream16(const T* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
 }
 
 constexpr int RB_THREADS = 256;
 constexpr int RB_ROWS = 4;
 
 template <typename T, int NCH>
-__global__ void __launch_bounds__(RB_THREADS, 2)
+__global__ void __launch_bounds__(RB_THREADS, (NCH * VecOf<T>::N <= 8) ? 2 : 1)
 rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w, const T* __restrict__ dy,
                    T* __restrict__ dx, float* __restrict__ dw_partial, long long rows, int dim, float eps,
                    int acc_dx) {
@@ -103,25 +179,44 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w, const T
   }
   int buf = 0;
   const long long groups = (rows + RB_ROWS - 1) / RB_ROWS;
-  for (long long gi = blockIdx.x; gi < groups; gi += gridDim.x) {
+  // the rows stay packed in registers (16 bytes per vector) and are widened where used; with one
+  // vector per thread and row the next group's rows are requested before the current group is reduced,
+  // so that the barrier below does not drain the memory pipeline
+  constexpr bool PREFETCH = NCH == 1;
+  uint4 xr[RB_ROWS][NCH], gr[RB_ROWS][NCH], xn[RB_ROWS][NCH], gn[RB_ROWS][NCH];
+  auto load_group = [&](long long gi, uint4 (&xd)[RB_ROWS][NCH], uint4 (&gd)[RB_ROWS][NCH]) {
     const long long r0 = gi * RB_ROWS;
-    // the rows stay packed in registers (16 bytes per vector) and are widened where used
-    uint4 xr[RB_ROWS][NCH], gr[RB_ROWS][NCH];
-    float part[2 * RB_ROWS];
 #pragma unroll
     for (int r = 0; r < RB_ROWS; ++r) {
-      const bool ok = r0 + r < rows;
+      const bool ok = gi < groups && r0 + r < rows;
 #pragma unroll
       for (int j = 0; j < NCH; ++j) {
         const int c = (threadIdx.x + j * RB_THREADS) * V;
         if (ok && c < dim) {
-          xr[r][j] = *reinterpret_cast<const uint4*>(x + (r0 + r) * dim + c);
-          gr[r][j] = *reinterpret_cast<const uint4*>(dy + (r0 + r) * dim + c);
+          xd[r][j] = ld_stream16(x + (r0 + r) * dim + c);
+          gd[r][j] = ld_stream16(dy + (r0 + r) * dim + c);
         } else {
-          xr[r][j] = make_uint4(0, 0, 0, 0);
-          gr[r][j] = make_uint4(0, 0, 0, 0);
+          xd[r][j] = make_uint4(0, 0, 0, 0);
+          gd[r][j] = make_uint4(0, 0, 0, 0);
         }
       }
+    }
+  };
+  if (PREFETCH) load_group(blockIdx.x, xn, gn);
+  for (long long gi = blockIdx.x; gi < groups; gi += gridDim.x) {
+    const long long r0 = gi * RB_ROWS;
+    float part[2 * RB_ROWS];
+    if (PREFETCH) {
+#pragma unroll
+      for (int r = 0; r < RB_ROWS; ++r)
+#pragma unroll
+        for (int j = 0; j < NCH; ++j) {
+          xr[r][j] = xn[r][j];
+          gr[r][j] = gn[r][j];
+        }
+      load_group(gi + gridDim.x, xn, gn);
+    } else {
+      load_group(gi, xr, gr);
     }
 #pragma unroll
     for (int r = 0; r < RB_ROWS; ++r) {
@@ -137,20 +232,45 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w, const T
           gd += gv[k] * xv[k] * wv[j][k];
         }
       }
-      part[2 * r] = warp_sum(ss);
-      part[2 * r + 1] = warp_sum(gd);
+      part[2 * r] = ss;
+      part[2 * r + 1] = gd;
     }
-    if (lane == 0) {
+    // eight sums over the warp in nine shuffles: each round halves the number of values a lane
+    // carries; afterwards lane l holds the warp total of value ((l>>4)&1)*4 + ((l>>3)&1)*2 + ((l>>2)&1)
+    static_assert(RB_ROWS == 4, "the reduction below is written for 8 values");
+    float w4[4], w2[2], w1;
+    {
+      const bool hi = lane & 16;
 #pragma unroll
-      for (int i = 0; i < 2 * RB_ROWS; ++i) sh[buf][warp][i] = part[i];
+      for (int i = 0; i < 4; ++i) {
+        const float keep = hi ? part[i + 4] : part[i];
+        const float give = hi ? part[i] : part[i + 4];
+        w4[i] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
+      }
+      const bool h8 = lane & 8;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const float keep = h8 ? w4[i + 2] : w4[i];
+        const float give = h8 ? w4[i] : w4[i + 2];
+        w2[i] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
+      }
+      const bool h4 = lane & 4;
+      const float keep = h4 ? w2[1] : w2[0];
+      const float give = h4 ? w2[0] : w2[1];
+      w1 = keep + __shfl_xor_sync(0xffffffffu, give, 4);
+      w1 += __shfl_xor_sync(0xffffffffu, w1, 2);
+      w1 += __shfl_xor_sync(0xffffffffu, w1, 1);
     }
+    const int vidx = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+    if ((lane & 3) == 0) sh[buf][warp][vidx] = w1;
     __syncthreads();
-#pragma unroll
-    for (int i = 0; i < 2 * RB_ROWS; ++i) {
+    {
+      // lane l adds value (l & 7) over the warps of the CTA; the totals go round by shuffle
       float t = 0.0f;
 #pragma unroll
-      for (int wq = 0; wq < RB_THREADS / 32; ++wq) t += sh[buf][wq][i];
-      part[i] = t;
+      for (int wq = 0; wq < RB_THREADS / 32; ++wq) t += sh[buf][wq][lane & 7];
+#pragma unroll
+      for (int i = 0; i < 2 * RB_ROWS; ++i) part[i] = __shfl_sync(0xffffffffu, t, i);
     }
     buf ^= 1;  // the other buffer is free: everyone passed the barrier of the group before
 #pragma unroll
@@ -445,8 +565,7 @@ int eisen_rmsnorm_fwd(void* stream, const void* x, const float* w, void* y, floa
   if (!aligned16(x) || !aligned16(y)) return fail(EISEN_ERR_INVALID, "rmsnorm_fwd: unaligned pointer");
   const int grid = grid_for(rows, RN_WARPS, 8);
   EISEN_DISPATCH_DTYPE(dt, T, {
-    rmsnorm_fwd_kernel<T><<<grid, RN_WARPS * 32, 0, (cudaStream_t)stream>>>((const T*)x, w, (T*)y, rrms_out,
-                                                                          rows, (int)dim, eps);
+    rmsnorm_fwd_dispatch<T>((const T*)x, w, (T*)y, rrms_out, rows, (int)dim, eps, grid, (cudaStream_t)stream);
     return check_launch("rmsnorm_fwd");
   });
 }

@@ -199,8 +199,8 @@ int eisen_embedding_bwd_bookkeeping(void* stream, const void* workspace, long lo
                                     int* count_out, int* offset_out, int* perm_out);
 
 /* Embedding backward for callers that cannot allocate device memory (no counterpart in the
- * reference).  Same result as eisen_embedding_bwd, but the integer scratch (count, offset, rank,
- * perm) is a fixed 1.5 MB array inside the library instead of a caller-provided workspace: meant
+ * reference).  Same result as eisen_embedding_bwd, but the integer scratch (count, offset, cursor, slot,
+ * perm) is a fixed 2 MB array inside the library instead of a caller-provided workspace: meant
  * for hosts that own all device memory under a fixed budget, or that must not call cudaMalloc
  * inside a training step.  Limits: n_ids <= 65536 and vocab <= 131072, larger sizes return
  * EISEN_ERR_LIMIT.  The call allocates nothing.  The first call on each device looks up the
