@@ -145,6 +145,9 @@ def main():
         touched = len(torch.unique(ids))
         out["embedding_bwd_gbs"] = (n * 2 + touched * dim * 8 + rows * 4) / ms / 1e6
         out["embedding_bwd_ms"] = ms
+        ms = timed(lambda: eb.call("eisen_embedding_bwd_apply", s, P(x), eb.BF16, P(dw), P(ws), rows, dim, V), a.iters)
+        out["embedding_bwd_apply_gbs"] = (n * 2 + touched * dim * 8 + rows * 4) / ms / 1e6
+        out["embedding_bwd_apply_ms"] = ms
         g32 = torch.randn(a.nelem, device=dev)
         ws2 = torch.empty(eb.lib().eisen_sumsq_workspace_bytes(a.nelem), dtype=torch.uint8, device=dev)
         ss = torch.zeros(1, dtype=torch.float64, device=dev)

@@ -159,7 +159,8 @@ __device__ __forceinline__ uint4 ld_stream16(const T* p) {
 constexpr int RB_THREADS = 256;
 constexpr int RB_ROWS = 4;
 
-template <typename T, int NCH>
+// FULL: rows is a multiple of RB_ROWS and dim == NCH * RB_THREADS * V, so no element is masked.
+template <typename T, int NCH, bool FULL>
 __global__ void __launch_bounds__(RB_THREADS, (NCH * VecOf<T>::N <= 8) ? 2 : 1)
 rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w, const T* __restrict__ dy,
                    T* __restrict__ dx, float* __restrict__ dw_partial, long long rows, int dim, float eps,
@@ -174,7 +175,7 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w, const T
 #pragma unroll
     for (int k = 0; k < V; ++k) {
       dwp[j][k] = 0.0f;
-      wv[j][k] = (c < dim) ? w[c + k] : 0.0f;
+      wv[j][k] = (FULL || c < dim) ? w[c + k] : 0.0f;
     }
   }
   int buf = 0;
@@ -188,11 +189,11 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w, const T
     const long long r0 = gi * RB_ROWS;
 #pragma unroll
     for (int r = 0; r < RB_ROWS; ++r) {
-      const bool ok = gi < groups && r0 + r < rows;
+      const bool ok = gi < groups && (FULL || r0 + r < rows);
 #pragma unroll
       for (int j = 0; j < NCH; ++j) {
         const int c = (threadIdx.x + j * RB_THREADS) * V;
-        if (ok && c < dim) {
+        if (ok && (FULL || c < dim)) {
           xd[r][j] = ld_stream16(x + (r0 + r) * dim + c);
           gd[r][j] = ld_stream16(dy + (r0 + r) * dim + c);
         } else {
@@ -265,30 +266,37 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w, const T
     if ((lane & 3) == 0) sh[buf][warp][vidx] = w1;
     __syncthreads();
     {
-      // lane l adds value (l & 7) over the warps of the CTA; the totals go round by shuffle
+      // lane l adds value (l & 7) over the warps of the CTA: even values are sums of squares, odd
+      // ones the dy*x*w sums.  The lane pair of a row turns them into that row's two coefficients
+      // (one square root per lane instead of one per row and thread); they go round by shuffle.
       float t = 0.0f;
 #pragma unroll
       for (int wq = 0; wq < RB_THREADS / 32; ++wq) t += sh[buf][wq][lane & 7];
+      const float other = __shfl_xor_sync(0xffffffffu, t, 1);
+      const float ssv = (lane & 1) ? other : t;
+      const float gdv = (lane & 1) ? t : other;
+      const float rr = 1.0f / sqrtf(ssv / (float)dim + eps);
+      const float coef = (rr * rr * rr) / (float)dim * gdv;
+      const float mine = (lane & 1) ? coef : rr;
 #pragma unroll
-      for (int i = 0; i < 2 * RB_ROWS; ++i) part[i] = __shfl_sync(0xffffffffu, t, i);
+      for (int i = 0; i < 2 * RB_ROWS; ++i) part[i] = __shfl_sync(0xffffffffu, mine, i);
     }
     buf ^= 1;  // the other buffer is free: everyone passed the barrier of the group before
 #pragma unroll
     for (int r = 0; r < RB_ROWS; ++r) {
-      if (r0 + r < rows) {
-        const float rrms = 1.0f / sqrtf(part[2 * r] / (float)dim + eps);
-        const float rrc_d = (rrms * rrms * rrms) / (float)dim;
-        const float gdxw = part[2 * r + 1];
+      if (FULL || r0 + r < rows) {
+        const float rrms = part[2 * r];
+        const float coef = part[2 * r + 1];
 #pragma unroll
         for (int j = 0; j < NCH; ++j) {
           const int c = (threadIdx.x + j * RB_THREADS) * V;
-          if (c < dim) {
+          if (FULL || c < dim) {
             float xv[V], gv[V], o[V];
             unpack16(xr[r][j], xv);
             unpack16(gr[r][j], gv);
 #pragma unroll
             for (int k = 0; k < V; ++k) {
-              o[k] = rrms * (gv[k] * wv[j][k]) - xv[k] * rrc_d * gdxw;
+              o[k] = rrms * (gv[k] * wv[j][k]) - xv[k] * coef;
               dwp[j][k] += gv[k] * xv[k] * rrms;
             }
             T* dr = dx + (r0 + r) * dim + c;
@@ -307,7 +315,7 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w, const T
 #pragma unroll
   for (int j = 0; j < NCH; ++j) {
     const int c = (threadIdx.x + j * RB_THREADS) * V;
-    if (c < dim) {
+    if (FULL || c < dim) {
 #pragma unroll
       for (int k = 0; k < V; ++k) dw_partial[(long long)blockIdx.x * dim + c + k] = dwp[j][k];
     }
@@ -529,7 +537,10 @@ template <typename T, int NCH>
 int launch_rmsnorm_bwd(cudaStream_t s, const T* x, const float* w, const T* dy, T* dx, float* dw,
                        float* ws, long long rows, int dim, float eps, int acc_dx) {
   const int grid = rmsnorm_bwd_grid(rows);
-  rmsnorm_bwd_kernel<T, NCH><<<grid, RB_THREADS, 0, s>>>(x, w, dy, dx, ws, rows, dim, eps, acc_dx);
+  if (rows % RB_ROWS == 0 && dim == NCH * RB_THREADS * VecOf<T>::N)
+    rmsnorm_bwd_kernel<T, NCH, true><<<grid, RB_THREADS, 0, s>>>(x, w, dy, dx, ws, rows, dim, eps, acc_dx);
+  else
+    rmsnorm_bwd_kernel<T, NCH, false><<<grid, RB_THREADS, 0, s>>>(x, w, dy, dx, ws, rows, dim, eps, acc_dx);
   int rc = check_launch("rmsnorm_bwd");
   if (rc) return rc;
   reduce_partials_kernel<<<(dim + 31) / 32, 256, 0, s>>>(ws, dw, grid, dim);

@@ -192,6 +192,12 @@ long long eisen_embedding_bwd_workspace_bytes(long long n_ids, long long vocab);
  * (gather_backward_f32, ops_f32.cu:526-537; src/graph/ops/transform.rs:259). */
 int eisen_embedding_bwd(void* stream, const void* g, int g_dtype, const int* ids, float* dw, void* workspace,
                         long long n_ids, long long dim, long long vocab);
+/* The two halves of eisen_embedding_bwd: _plan groups the positions by id (integer work that
+ * depends on the ids only and may run as soon as they are known); _apply adds the gradient rows
+ * with the grouping a _plan call left in `workspace` (16-byte aligned). */
+int eisen_embedding_bwd_plan(void* stream, const int* ids, void* workspace, long long n_ids, long long vocab);
+int eisen_embedding_bwd_apply(void* stream, const void* g, int g_dtype, float* dw, const void* workspace,
+                              long long n_ids, long long dim, long long vocab);
 /* integer bookkeeping of the last eisen_embedding_bwd on `workspace` (device int32 outputs, any
  * may be null): count[vocab], offset[vocab] (exclusive prefix), perm[n_ids] (positions grouped
  * by id in position order) */
@@ -199,8 +205,8 @@ int eisen_embedding_bwd_bookkeeping(void* stream, const void* workspace, long lo
                                     int* count_out, int* offset_out, int* perm_out);
 
 /* Embedding backward for callers that cannot allocate device memory (no counterpart in the
- * reference).  Same result as eisen_embedding_bwd, but the integer scratch (count, offset, cursor, slot,
- * perm) is a fixed 2 MB array inside the library instead of a caller-provided workspace: meant
+ * reference).  Same result as eisen_embedding_bwd, but the integer scratch (count, offset, cursor, slot, active,
+ * perm) is a fixed 2.5 MB array inside the library instead of a caller-provided workspace: meant
  * for hosts that own all device memory under a fixed budget, or that must not call cudaMalloc
  * inside a training step.  Limits: n_ids <= 65536 and vocab <= 131072, larger sizes return
  * EISEN_ERR_LIMIT.  The call allocates nothing.  The first call on each device looks up the
