@@ -27,7 +27,8 @@ constexpr int PB_BYTES = (PN / 2) * BK * 2;  // 16 KB
 constexpr int PSTAGE_BYTES = PA_BYTES + PB_BYTES;
 constexpr int P_THREADS = 192;
 constexpr int P_ACC_COLS = PN;
-constexpr int P_SMEM = PSTAGES * PSTAGE_BYTES + 1024 + 256;
+constexpr int P_EPI_BYTES = 4 * 32 * 128;  // per epilogue warp: 32 rows x 64 bf16 columns
+constexpr int P_SMEM = PSTAGES * PSTAGE_BYTES + 1024 + 256 + P_EPI_BYTES;
 
 struct PairParams {
   int M, N, K;
@@ -39,9 +40,23 @@ struct PairParams {
   int out_mode;
   int split_k, kblocks_per_split, kblocks_total;
   int m_tiles, n_tiles, total_tiles;  // m_tiles counts 256-row pair tiles
+  int band;  // m-tiles per band of the tile order (see pair_tile_coords)
   float alpha;
   int* status;
 };
+
+// Tile order: the m-tiles are cut into bands of `band` tiles; a band is finished (all its n-tiles,
+// m fastest inside the band) before the next one starts.  With band == m_tiles this is plain
+// column-major order.  A small band keeps its rows of A in L2 while the n-tiles sweep over B.
+__device__ __forceinline__ void pair_tile_coords(const PairParams& p, int mn, int& mt, int& nt) {
+  const int per_band = p.band * p.n_tiles;
+  const int b = mn / per_band;
+  const int in = mn - b * per_band;
+  const int m_first = b * p.band;
+  const int rows = min(p.band, p.m_tiles - m_first);
+  nt = in / rows;
+  mt = m_first + (in - nt * rows);
+}
 
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -58,6 +73,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   uint64_t* tmem_empty_bar = bars + 2 * PSTAGES + 2;  // [2]     used in the leader (8 arrivals: 4 warps per CTA)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * PSTAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* epi_stage = smem + PSTAGES * PSTAGE_BYTES + 256;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -101,8 +117,8 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       for (int t = cluster_id; t < p.total_tiles; t += n_clusters) {
         const int ks = t / tiles_mn;
         const int mn = t - ks * tiles_mn;
-        const int mt = mn % p.m_tiles;
-        const int nt = mn / p.m_tiles;
+        int mt, nt;
+        pair_tile_coords(p, mn, mt, nt);
         const int m0 = mt * (2 * PM) + (int)rank * PM;
         const int n0 = nt * PN + (int)rank * (PN / 2);
         const int kb0 = ks * p.kblocks_per_split;
@@ -181,8 +197,8 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     for (int t = cluster_id; t < p.total_tiles; t += n_clusters) {
       const int ks = t / tiles_mn;
       const int mn = t - ks * tiles_mn;
-      const int mt = mn % p.m_tiles;
-      const int nt = mn / p.m_tiles;
+      int mt, nt;
+      pair_tile_coords(p, mn, mt, nt);
       const int row = mt * (2 * PM) + (int)rank * PM + q * 32 + lane;
       const int n0 = nt * PN;
       const int kb0 = ks * p.kblocks_per_split;
@@ -192,6 +208,67 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       const uint32_t taddr = tmem_base + acc * P_ACC_COLS + (uint32_t(q * 32) << 16);
       const bool row_ok = row < p.M;
       const bool acc_bf16 = p.out_mode == GEMM_OUT_BF16_ACC && has_k;
+      const int row0 = row - lane;  // first row of this warp
+      // bf16 outputs of complete 32 x 256 slabs go through shared memory, so that a store (and an
+      // addend load) covers 128 contiguous bytes of four rows instead of 16 bytes of 32 rows
+      const bool staged = has_k && (p.out_mode == GEMM_OUT_BF16 || p.out_mode == GEMM_OUT_BF16_ACC) &&
+                          row0 + 32 <= p.M && n0 + PN <= p.N && (p.ldc % 8) == 0 &&
+                          (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 &&
+                          (!acc_bf16 || ((p.ldr % 8) == 0 && (reinterpret_cast<uintptr_t>(p.R) & 15) == 0));
+      if (staged) {
+        uint8_t* st = epi_stage + q * (32 * 128);
+        const int rr = lane >> 3, seg = lane & 7;
+        __nv_bfloat16* c_base = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)(row0 + rr) * p.ldc + n0 + seg * 8;
+        const __nv_bfloat16* r_base =
+            reinterpret_cast<const __nv_bfloat16*>(p.R) + (long long)(row0 + rr) * p.ldr + n0 + seg * 8;
+#pragma unroll 1
+        for (int c = 0; c < PN / 64; ++c) {
+          uint4 old[8];
+          if (acc_bf16) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) old[i] = *reinterpret_cast<const uint4*>(r_base + (long long)(4 * i) * p.ldr + c * 64);
+          }
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32b_x32(taddr + c * 64, r0);
+          tmem_ld_32x32b_x32(taddr + c * 64 + 32, r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r0[8 * j + 0]) * p.alpha, __uint_as_float(r0[8 * j + 1]) * p.alpha);
+            o.y = pack_bf16x2(__uint_as_float(r0[8 * j + 2]) * p.alpha, __uint_as_float(r0[8 * j + 3]) * p.alpha);
+            o.z = pack_bf16x2(__uint_as_float(r0[8 * j + 4]) * p.alpha, __uint_as_float(r0[8 * j + 5]) * p.alpha);
+            o.w = pack_bf16x2(__uint_as_float(r0[8 * j + 6]) * p.alpha, __uint_as_float(r0[8 * j + 7]) * p.alpha);
+            *reinterpret_cast<uint4*>(st + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
+            o.x = pack_bf16x2(__uint_as_float(r1[8 * j + 0]) * p.alpha, __uint_as_float(r1[8 * j + 1]) * p.alpha);
+            o.y = pack_bf16x2(__uint_as_float(r1[8 * j + 2]) * p.alpha, __uint_as_float(r1[8 * j + 3]) * p.alpha);
+            o.z = pack_bf16x2(__uint_as_float(r1[8 * j + 4]) * p.alpha, __uint_as_float(r1[8 * j + 5]) * p.alpha);
+            o.w = pack_bf16x2(__uint_as_float(r1[8 * j + 6]) * p.alpha, __uint_as_float(r1[8 * j + 7]) * p.alpha);
+            *reinterpret_cast<uint4*>(st + lane * 128 + (((j + 4) ^ (lane & 7)) << 4)) = o;
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rw = 4 * i + rr;
+            uint4 o = *reinterpret_cast<const uint4*>(st + rw * 128 + ((seg ^ (rw & 7)) << 4));
+            if (acc_bf16) {
+              // the product is rounded to bf16 before the addend is added, as a separate matmul
+              // followed by an add would do
+              const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&o);
+              const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&old[i]);
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 fa = __bfloat1622float2(a2[e]), fb = __bfloat1622float2(b2[e]);
+                w[e] = pack_bf16x2(fa.x + fb.x, fa.y + fb.y);
+              }
+              o = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            *reinterpret_cast<uint4*>(c_base + (long long)(4 * i) * p.ldc + c * 64) = o;
+          }
+          __syncwarp();
+        }
+      } else {
       uint4 pre_cur[4], pre_next[4];
       bool have_cur = acc_bf16 && gemm_prefetch_addend(p.R, p.ldr, row, n0, p.N, row_ok, pre_cur);
 #pragma unroll 1
@@ -212,6 +289,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 #pragma unroll
         for (int j = 0; j < 4; ++j) pre_cur[j] = pre_next[j];
         have_cur = have_next;
+      }
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -272,6 +350,24 @@ int gemm_bf16_tc_pair(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int
   split_k = (p.kblocks_total + p.kblocks_per_split - 1) / p.kblocks_per_split;
   p.split_k = split_k;
   p.total_tiles = p.m_tiles * p.n_tiles * split_k;
+  {
+    // DRAM traffic model of the tile order: A's rows of a band are read once if the band fits in
+    // L2 (else once per n-tile); B is read once per band unless all of it fits in L2.
+    const double l2_fit = 75e6;  // bytes of one operand that stay resident next to the streams
+    const double a_total = 2.0 * M * K, b_total = 2.0 * N * K;
+    double best = -1.0;
+    int best_band = p.m_tiles;
+    for (int band = p.m_tiles;; band = (band + 1) / 2) {
+      const int n_bands = (p.m_tiles + band - 1) / band;
+      const double a_band = 2.0 * band * (2 * PM) * K;
+      const double a_tr = a_total * (a_band <= l2_fit ? 1.0 : (double)p.n_tiles);
+      const double b_tr = b_total * (b_total <= l2_fit ? 1.0 : (double)n_bands);
+      const double tr = a_tr + b_tr;
+      if (best < 0.0 || tr < best * 0.95) { best = tr; best_band = band; }
+      if (band <= 4) break;
+    }
+    p.band = best_band;
+  }
   p.alpha = alpha;
   p.status = status;
   if (!attr_set) {
@@ -311,16 +407,26 @@ int gemm_bf16_tc_pair(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int
 
 int gemm_pair_clusters_hint() { return gemm_num_sms() / 2; }
 
+// Split of the k range for the f32 atomic output mode: the persistent grid works in waves of one
+// tile per cluster, so the split is chosen to fill the last wave (176 tiles on 74 clusters are
+// 2.4 waves = 79 % busy; split in two they are 4.8 waves = 95 %).  Every extra split costs one
+// more pass of f32 atomics over C, charged as 1.5 % each.
 int gemm_pair_auto_split_k(int M, int N, int K) {
   const int tiles = ((M + 2 * PM - 1) / (2 * PM)) * ((N + PN - 1) / PN);
   const int kblocks = (K + BK - 1) / BK;
   const int clusters = gemm_num_sms() / 2;
-  if (tiles >= clusters) return 1;
-  int s = (2 * clusters + tiles - 1) / tiles;
-  int max_s = kblocks / 8;
+  int max_s = kblocks / 8;  // at least 8 k-blocks (512 of k) per split
   if (max_s < 1) max_s = 1;
-  if (s > max_s) s = max_s;
-  return s < 1 ? 1 : s;
+  if (max_s > 32) max_s = 32;
+  int best_s = 1;
+  double best = -1.0;
+  for (int s = 1; s <= max_s; ++s) {
+    const long long t = (long long)tiles * s;
+    const long long waves = (t + clusters - 1) / clusters;
+    const double score = (double)t / (double)(waves * clusters) - 0.015 * (s - 1);
+    if (score > best + 1e-9) { best = score; best_s = s; }
+  }
+  return best_s;
 }
 
 }  // namespace eisen
