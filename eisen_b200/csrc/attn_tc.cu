@@ -107,6 +107,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* o_full = bars + 13;     // per query tile
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint64_t* exp_done = bars + 16;   // per query tile: its exponentials of a key tile are issued
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qt = (p.S + 127) / 128;
@@ -127,6 +128,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&s_full[i], 1);
       mbar_init(&p_ready[i], 128 * Cfg::SPLIT);
       mbar_init(&o_full[i], 1);
+      mbar_init(&exp_done[i], 128 * Cfg::SPLIT);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -265,7 +267,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld_32x32b_x32(tO + c * 32, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, __uint_as_float(r[i]));
+        for (int i = 0; i < 32; i += 2)
+          ffma2(acc[c * 32 + i], acc[c * 32 + i + 1], acc[c * 32 + i], acc[c * 32 + i + 1], alpha, alpha,
+                __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
       }
       tc_fence_before_sync();
     };
@@ -291,13 +295,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         } else {
           float m0 = __uint_as_float(r[0]), m1 = __uint_as_float(r[1]), m2 = __uint_as_float(r[2]), m3 = __uint_as_float(r[3]);
 #pragma unroll
-          for (int i = 4; i < 32; i += 4) {
-            m0 = fmaxf(m0, __uint_as_float(r[i]));
-            m1 = fmaxf(m1, __uint_as_float(r[i + 1]));
-            m2 = fmaxf(m2, __uint_as_float(r[i + 2]));
-            m3 = fmaxf(m3, __uint_as_float(r[i + 3]));
+          for (int i = 4; i < 28; i += 8) {
+            m0 = fmax3(m0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+            m1 = fmax3(m1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+            m2 = fmax3(m2, __uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+            m3 = fmax3(m3, __uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
           }
-          mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
+          m0 = fmax3(m0, __uint_as_float(r[28]), __uint_as_float(r[29]));
+          m1 = fmax3(m1, __uint_as_float(r[30]), __uint_as_float(r[31]));
+          mx = fmax3(mx, fmaxf(m0, m1), fmaxf(m2, m3));
         }
       }
       if constexpr (SPLIT > 1) {
@@ -314,29 +320,54 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const float msl2 = m_use * sl2;
       // the previous tile's P V is complete by now (the tensor core ran it before this S)
       if (j > 0) fold(jph ^ 1, alpha_prev);
+      // The two query tiles take turns with the exponentials (A0, B0, A1, B1, ...): the special
+      // function unit is the busiest unit of this kernel, and while one tile keeps it busy the
+      // other tile's barrier round trips, tensor-core products, maxima and folds run beside it
+      // instead of all warps competing for it at once and then all leaving it idle.
+      if (t == 0) {
+        if (j > 0 && b_valid) mbar_wait(&exp_done[1], jph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
+      } else {
+        if (j < nA) mbar_wait(&exp_done[0], jph, abort_flag, p.status, FAULT_WAIT_ATTN);
+      }
       // pass 2: probabilities -> shared memory (bf16), partial row sum
-      float rs0 = 0.0f, rs1 = 0.0f;
+      float rs0 = 0.0f, rs1 = 0.0f, rs2 = 0.0f, rs3 = 0.0f;
+      const float nmsl2 = -msl2;
 #pragma unroll 1
       for (int c = 0; c < CW / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(tS + c * 32, r);
         tmem_ld_wait();
         uint32_t pk[16];
+        if (!need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), sl2, -msl2));
-          float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), sl2, -msl2));
-          if (need_mask) {
+          for (int i = 0; i < 32; i += 4) {
+            float x0, x1, x2, x3;
+            ffma2(x0, x1, __uint_as_float(r[i]), __uint_as_float(r[i + 1]), sl2, sl2, nmsl2, nmsl2);
+            ffma2(x2, x3, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]), sl2, sl2, nmsl2, nmsl2);
+            x0 = ex2_approx(x0); x1 = ex2_approx(x1); x2 = ex2_approx(x2); x3 = ex2_approx(x3);
+            fadd2(rs0, rs1, rs0, rs1, x0, x1);
+            fadd2(rs2, rs3, rs2, rs3, x2, x3);
+            pk[i >> 1] = pack_bf16x2(x0, x1);
+            pk[(i >> 1) + 1] = pack_bf16x2(x2, x3);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), sl2, nmsl2));
+            float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), sl2, nmsl2));
             const int kc = j * 128 + part * CW + c * 32 + i;
             if (kc >= p.S || (p.causal && kc > qrow)) p0 = 0.0f;
             if (kc + 1 >= p.S || (p.causal && kc + 1 > qrow)) p1 = 0.0f;
+            rs0 += p0;
+            rs1 += p1;
+            pk[i >> 1] = pack_bf16x2(p0, p1);
           }
-          rs0 += p0;
-          rs1 += p1;
-          pk[i >> 1] = pack_bf16x2(p0, p1);
         }
         store_row_chunk32(sP, row, part * CW + c * 32, pk);
       }
+      rs0 += rs2;
+      rs1 += rs3;
+      mbar_arrive(&exp_done[t]);
       l = fmaf(l, alpha, rs0 + rs1);
       m = m_new;
       alpha_prev = alpha;
@@ -618,19 +649,32 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld_32x32b_x32(tmem_base + Cfg::COL_DP + col0 + lane_off, rd);
         tmem_ld_wait();
         uint32_t pk[16], dk[16];
+        const float nlse2 = -lse2, ndlt = -dlt;
+        if (!need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = ex2_approx(fmaf(__uint_as_float(rs[i]), sl2, -lse2));
-          float p1 = ex2_approx(fmaf(__uint_as_float(rs[i + 1]), sl2, -lse2));
-          if (need_mask) {
+          for (int i = 0; i < 32; i += 2) {
+            float p0, p1, d0, d1;
+            ffma2(p0, p1, __uint_as_float(rs[i]), __uint_as_float(rs[i + 1]), sl2, sl2, nlse2, nlse2);
+            fadd2(d0, d1, __uint_as_float(rd[i]), __uint_as_float(rd[i + 1]), ndlt, ndlt);
+            p0 = ex2_approx(p0);
+            p1 = ex2_approx(p1);
+            fmul2(d0, d1, d0, d1, p0, p1);
+            pk[i >> 1] = pack_bf16x2(p0, p1);
+            dk[i >> 1] = pack_bf16x2(d0, d1);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = ex2_approx(fmaf(__uint_as_float(rs[i]), sl2, nlse2));
+            float p1 = ex2_approx(fmaf(__uint_as_float(rs[i + 1]), sl2, nlse2));
             const int kc = jt * 128 + col0 + i;
             if (kc >= p.S || (p.causal && kc > qrow)) p0 = 0.0f;
             if (kc + 1 >= p.S || (p.causal && kc + 1 > qrow)) p1 = 0.0f;
+            const float d0 = p0 * (__uint_as_float(rd[i]) + ndlt);
+            const float d1 = p1 * (__uint_as_float(rd[i + 1]) + ndlt);
+            pk[i >> 1] = pack_bf16x2(p0, p1);
+            dk[i >> 1] = pack_bf16x2(d0, d1);
           }
-          const float d0 = p0 * (__uint_as_float(rd[i]) - dlt);
-          const float d1 = p1 * (__uint_as_float(rd[i + 1]) - dlt);
-          pk[i >> 1] = pack_bf16x2(p0, p1);
-          dk[i >> 1] = pack_bf16x2(d0, d1);
         }
         store_row_chunk32(sP, row, col0, pk);
         store_row_chunk32(sDS, row, col0, dk);
