@@ -416,6 +416,333 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 // =====================================================================================
+// forward at head_dim 64.  Same roles as attn_fwd_kernel (two 128-query tiles per CTA, two threads
+// per query row, one TMA and one MMA warp), with a shorter dependency chain per key tile:
+//   * a thread reads its 64 scores from TMEM once and keeps them in registers; as soon as all
+//     threads of a query tile have done so, the tensor core may start the tile's next S = Q K^T,
+//     which then runs beside the exponentials instead of after them;
+//   * O stays in TMEM and P V accumulates into it.  The running maximum used for the exponentials
+//     is only replaced when the true maximum has grown by more than 2^8 (in the exp2 domain); then,
+//     and only then, O is read, scaled and written back.  P <= 2^8 keeps bf16 P and the f32 row sum
+//     exact enough, and the final O / l does not depend on which maximum was used.
+// =====================================================================================
+struct Fwd64Cfg {
+  static constexpr int TILE = 128 * 64 * 2;
+  static constexpr int P_TILE = 128 * 128 * 2;
+  static constexpr int OFF_Q = 0;                 // 2 tiles
+  static constexpr int OFF_K = 2 * TILE;          // 2 stages
+  static constexpr int OFF_V = OFF_K + 2 * TILE;  // 2 stages
+  static constexpr int OFF_P = OFF_V + 2 * TILE;  // 2 tiles
+  static constexpr int OFF_BAR = OFF_P + 2 * P_TILE;
+  static constexpr int OFF_XMAX = OFF_BAR + 256;  // float [2 tiles][2 buffers][2 parts][128]
+  static constexpr int SMEM = OFF_XMAX + 2 * 2 * 2 * 128 * 4 + 1024;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int SWARPS = 16;
+  static constexpr int THREADS = (SWARPS + 2) * 32;
+};
+
+__global__ void __launch_bounds__(Fwd64Cfg::THREADS, 1)
+attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+  using Cfg = Fwd64Cfg;
+  constexpr int D = 64;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+  uint64_t* q_full = bars;          // 1
+  uint64_t* k_full = bars + 1;      // 2
+  uint64_t* k_empty = bars + 3;     // 2
+  uint64_t* v_full = bars + 5;      // 2
+  uint64_t* v_empty = bars + 7;     // 2
+  uint64_t* s_full = bars + 9;      // per query tile: S is in TMEM
+  uint64_t* s_free = bars + 11;     // per query tile (256 arrivals): S has been read into registers
+  uint64_t* p_ready = bars + 13;    // per query tile (256 arrivals): P is in shared memory
+  uint64_t* o_full = bars + 15;     // per query tile: the P V product issued last is complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qt = (p.S + 127) / 128;
+  const int pair = (int)gridDim.x - 1 - (int)blockIdx.x;  // heavy (late) causal tiles first
+  const int qtA = 2 * pair, qtB = 2 * pair + 1;
+  const bool b_valid = qtB < n_qt;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / (p.Hq / p.Hkv);
+  const int nA = p.causal ? min(qtA + 1, n_qt) : n_qt;
+  const int nB = b_valid ? (p.causal ? min(qtB + 1, n_qt) : n_qt) : 0;
+  const int n_kv = max(nA, nB);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_free[i], 256);
+      mbar_init(&p_ready[i], 256);
+      mbar_init(&o_full[i], 1);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+  }
+  if (warp == Cfg::SWARPS + 1) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tm_S = tmem_base;        // S of tile A at +0, of tile B at +128
+  const uint32_t tm_O = tmem_base + 256;  // O of tile A at +0, of tile B at +64
+
+  if (warp == Cfg::SWARPS) {
+    // ---------------- TMA ----------------
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, (b_valid ? 2 : 1) * Cfg::TILE);
+      tma_load_4d(smem + Cfg::OFF_Q, &tmQ, q_full, 0, h, qtA * 128, b);
+      if (b_valid) tma_load_4d(smem + Cfg::OFF_Q + Cfg::TILE, &tmQ, q_full, 0, h, qtB * 128, b);
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
+        mbar_arrive_expect_tx(&k_full[st], Cfg::TILE);
+        tma_load_4d(smem + Cfg::OFF_K + st * Cfg::TILE, &tmK, &k_full[st], 0, kvh, j * 128, b);
+        mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
+        mbar_arrive_expect_tx(&v_full[st], Cfg::TILE);
+        tma_load_4d(smem + Cfg::OFF_V + st * Cfg::TILE, &tmV, &v_full[st], 0, kvh, j * 128, b);
+      }
+    }
+  } else if (warp == Cfg::SWARPS + 1) {
+    // ---------------- MMA ----------------
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_pv = make_idesc_bf16(128, D, 0, 1);
+      const uint32_t sQ = smem_u32(smem + Cfg::OFF_Q);
+      auto issue_s = [&](int t, int j) {  // S_t = Q_t K_j^T
+        const uint32_t sK = smem_u32(smem + Cfg::OFF_K + (j & 1) * Cfg::TILE);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_bf16_ss(tm_S + t * 128, make_smem_desc(sQ + t * Cfg::TILE + k * 32u, 16, 1024),
+                       make_smem_desc(sK + k * 32u, 16, 1024), idesc_s, k > 0);
+        umma_commit(&s_full[t]);
+      };
+      auto issue_pv = [&](int t, int j) {  // O_t (+)= P_t V_j
+        const uint32_t sP = smem_u32(smem + Cfg::OFF_P + t * Cfg::P_TILE);
+        const uint32_t sV = smem_u32(smem + Cfg::OFF_V + (j & 1) * Cfg::TILE);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {  // 128 keys in steps of 16
+          const uint64_t da = make_smem_desc(sP + (k >> 2) * 16384u + (k & 3) * 32u, 16, 1024);
+          const uint64_t db = make_smem_desc(sV + k * 2048u, 16384, 1024);  // V is MN-major: [key][d]
+          umma_bf16_ss(tm_O + t * D, da, db, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&o_full[t]);
+      };
+      mbar_wait(q_full, 0, abort_flag, p.status, FAULT_WAIT_ATTN);
+      mbar_wait(&k_full[0], 0, abort_flag, p.status, FAULT_WAIT_ATTN);
+      tc_fence_after_sync();
+      issue_s(0, 0);
+      if (b_valid) issue_s(1, 0);
+      umma_commit(&k_empty[0]);
+      for (int j = 0; j < n_kv; ++j) {
+        const uint32_t jph = j & 1;
+        const uint32_t phv = (j >> 1) & 1;
+        const uint32_t kph1 = ((j + 1) >> 1) & 1;
+        // the next S of a tile may start once the tile's threads hold the current S in registers
+        if (j + 1 < nA) {
+          mbar_wait(&s_free[0], jph, abort_flag, p.status, FAULT_WAIT_ATTN);
+          mbar_wait(&k_full[(j + 1) & 1], kph1, abort_flag, p.status, FAULT_WAIT_ATTN);
+          tc_fence_after_sync();
+          issue_s(0, j + 1);
+        }
+        if (j + 1 < nB) {
+          mbar_wait(&s_free[1], jph, abort_flag, p.status, FAULT_WAIT_ATTN);
+          mbar_wait(&k_full[(j + 1) & 1], kph1, abort_flag, p.status, FAULT_WAIT_ATTN);
+          tc_fence_after_sync();
+          issue_s(1, j + 1);
+        }
+        if (j + 1 < n_kv) umma_commit(&k_empty[(j + 1) & 1]);
+        if (j < nA) {
+          mbar_wait(&p_ready[0], jph, abort_flag, p.status, FAULT_WAIT_ATTN);
+          mbar_wait(&v_full[j & 1], phv, abort_flag, p.status, FAULT_WAIT_ATTN);
+          tc_fence_after_sync();
+          issue_pv(0, j);
+        }
+        if (j < nB) {
+          mbar_wait(&p_ready[1], jph, abort_flag, p.status, FAULT_WAIT_ATTN);
+          mbar_wait(&v_full[j & 1], phv, abort_flag, p.status, FAULT_WAIT_ATTN);
+          tc_fence_after_sync();
+          issue_pv(1, j);
+        }
+        umma_commit(&v_empty[j & 1]);
+      }
+    }
+  } else {
+    // ---------------- softmax + output ----------------
+    // warp w: query tile (w >> 2) & 1, TMEM lane quarter w & 3, column half w >> 3.  A thread owns
+    // one query row, 64 of its score columns and 32 of its output columns.
+    const int t = (warp >> 2) & 1;
+    const int part = warp >> 3;
+    const int n_mine = t ? nB : nA;
+    const int qt = t ? qtB : qtA;
+    const int row = (warp & 3) * 32 + lane;
+    const int qrow = qt * 128 + row;
+    const uint32_t lane_off = uint32_t((warp & 3) * 32) << 16;
+    const float sl2 = p.scale * LOG2E;
+    const uint32_t tS = tm_S + t * 128 + part * 64 + lane_off;
+    const uint32_t tO = tm_O + t * D + part * 32 + lane_off;
+    const uint32_t sP = smem_u32(smem + Cfg::OFF_P + t * Cfg::P_TILE);
+    float* xbase = reinterpret_cast<float*>(smem + Cfg::OFF_XMAX) + t * 512;  // [2 buffers][2 parts][128]
+    const int bar_id = 1 + t;
+    float m_used = -INFINITY, l = 0.0f;
+
+    for (int j = 0; j < n_mine; ++j) {
+      const uint32_t jph = j & 1;
+      const bool need_mask = (p.causal && j == qt) || ((j + 1) * 128 > p.S);
+      mbar_wait(&s_full[t], jph, abort_flag, p.status, FAULT_WAIT_ATTN);
+      tc_fence_after_sync();
+      uint32_t ra[32], rb[32];
+      tmem_ld_32x32b_x32(tS, ra);
+      tmem_ld_32x32b_x32(tS + 32, rb);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&s_free[t]);
+      if (need_mask) {
+        const int kc0 = j * 128 + part * 64;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (kc0 + i >= p.S || (p.causal && kc0 + i > qrow)) ra[i] = 0xff800000u;
+          if (kc0 + 32 + i >= p.S || (p.causal && kc0 + 32 + i > qrow)) rb[i] = 0xff800000u;
+        }
+      }
+      float mx;
+      {
+        float m0 = __uint_as_float(ra[0]), m1 = __uint_as_float(ra[1]), m2 = __uint_as_float(rb[0]), m3 = __uint_as_float(rb[1]);
+#pragma unroll
+        for (int i = 2; i < 30; i += 4) {
+          m0 = fmax3(m0, __uint_as_float(ra[i]), __uint_as_float(ra[i + 1]));
+          m1 = fmax3(m1, __uint_as_float(ra[i + 2]), __uint_as_float(ra[i + 3]));
+          m2 = fmax3(m2, __uint_as_float(rb[i]), __uint_as_float(rb[i + 1]));
+          m3 = fmax3(m3, __uint_as_float(rb[i + 2]), __uint_as_float(rb[i + 3]));
+        }
+        m0 = fmax3(m0, __uint_as_float(ra[30]), __uint_as_float(ra[31]));
+        m2 = fmax3(m2, __uint_as_float(rb[30]), __uint_as_float(rb[31]));
+        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      }
+      {
+        // the two threads of a row exchange their maxima; the buffers alternate, so the one
+        // barrier of the next key tile also orders this tile's reads before the next reuse
+        float* xb = xbase + (j & 1) * 256;
+        xb[part * 128 + row] = mx;
+        asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(256) : "memory");
+        mx = fmaxf(mx, xb[(part ^ 1) * 128 + row]);
+      }
+      const float m_new = fmaxf(m_used, mx);
+      float alpha = 1.0f;
+      bool resc = false;
+      if (m_used == -INFINITY) {
+        m_used = m_new;  // nothing accumulated under the old value (l == 0, O == 0)
+      } else if ((m_new - m_used) * sl2 > 8.0f) {
+        alpha = ex2_approx((m_used - m_new) * sl2);
+        resc = true;
+        m_used = m_new;
+      }
+      const float nmsl2 = (m_used == -INFINITY) ? 0.0f : -m_used * sl2;  // a fully masked row keeps p = 0
+      // probabilities (bf16, packed) and their row sum
+      uint32_t pk[32];
+      float rs0 = 0.0f, rs1 = 0.0f, rs2 = 0.0f, rs3 = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        float x0, x1, x2, x3;
+        ffma2(x0, x1, __uint_as_float(ra[i]), __uint_as_float(ra[i + 1]), sl2, sl2, nmsl2, nmsl2);
+        ffma2(x2, x3, __uint_as_float(ra[i + 2]), __uint_as_float(ra[i + 3]), sl2, sl2, nmsl2, nmsl2);
+        x0 = ex2_approx(x0); x1 = ex2_approx(x1); x2 = ex2_approx(x2); x3 = ex2_approx(x3);
+        fadd2(rs0, rs1, rs0, rs1, x0, x1);
+        fadd2(rs2, rs3, rs2, rs3, x2, x3);
+        pk[i >> 1] = pack_bf16x2(x0, x1);
+        pk[(i >> 1) + 1] = pack_bf16x2(x2, x3);
+      }
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        float x0, x1, x2, x3;
+        ffma2(x0, x1, __uint_as_float(rb[i]), __uint_as_float(rb[i + 1]), sl2, sl2, nmsl2, nmsl2);
+        ffma2(x2, x3, __uint_as_float(rb[i + 2]), __uint_as_float(rb[i + 3]), sl2, sl2, nmsl2, nmsl2);
+        x0 = ex2_approx(x0); x1 = ex2_approx(x1); x2 = ex2_approx(x2); x3 = ex2_approx(x3);
+        fadd2(rs0, rs1, rs0, rs1, x0, x1);
+        fadd2(rs2, rs3, rs2, rs3, x2, x3);
+        pk[16 + (i >> 1)] = pack_bf16x2(x0, x1);
+        pk[16 + (i >> 1) + 1] = pack_bf16x2(x2, x3);
+      }
+      l = fmaf(l, alpha, (rs0 + rs1) + (rs2 + rs3));
+      if (j > 0) {
+        // the previous P V has read P from shared memory and has been added to O
+        mbar_wait(&o_full[t], jph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
+        tc_fence_after_sync();
+        if (__any_sync(0xffffffffu, resc)) {
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t q8[8];
+            tmem_ld_32x32b_x8(tO + c * 8, q8);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) q8[i] = __float_as_uint(__uint_as_float(q8[i]) * alpha);
+            tmem_st_32x32b_x8(tO + c * 8, q8);
+          }
+          tmem_st_wait();
+        }
+      }
+      {
+        uint32_t lo[16], hi[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { lo[i] = pk[i]; hi[i] = pk[16 + i]; }
+        store_row_chunk32(sP, row, part * 64, lo);
+        store_row_chunk32(sP, row, part * 64 + 32, hi);
+      }
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+      mbar_arrive(&p_ready[t]);
+    }
+    if (n_mine > 0) {
+      mbar_wait(&o_full[t], (n_mine - 1) & 1, abort_flag, p.status, FAULT_WAIT_ATTN);
+      tc_fence_after_sync();
+      uint32_t ro[32];
+      tmem_ld_32x32b_x32(tO, ro);
+      tmem_ld_wait();
+      // total row sum = sum of the two partial sums (both used the same maxima)
+      float* xb = xbase + (n_mine & 1) * 256;
+      xb[part * 128 + row] = l;
+      asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(256) : "memory");
+      l += xb[(part ^ 1) * 128 + row];
+      if (qrow < p.S) {
+        const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
+        __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + (long long)b * p.o_bs + (long long)qrow * p.o_ss +
+                              (long long)h * p.o_hs + part * 32;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4 o;
+          o.x = pack_bf16x2(__uint_as_float(ro[c * 8 + 0]) * inv, __uint_as_float(ro[c * 8 + 1]) * inv);
+          o.y = pack_bf16x2(__uint_as_float(ro[c * 8 + 2]) * inv, __uint_as_float(ro[c * 8 + 3]) * inv);
+          o.z = pack_bf16x2(__uint_as_float(ro[c * 8 + 4]) * inv, __uint_as_float(ro[c * 8 + 5]) * inv);
+          o.w = pack_bf16x2(__uint_as_float(ro[c * 8 + 6]) * inv, __uint_as_float(ro[c * 8 + 7]) * inv);
+          reinterpret_cast<uint4*>(orow)[c] = o;
+        }
+        if (p.lse && part == 0)
+          p.lse[((long long)b * p.Hq + h) * p.S + qrow] = (l > 0.0f) ? m_used * p.scale + logf(l) : -INFINITY;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  if (warp == Cfg::SWARPS + 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// =====================================================================================
 // backward: one 128-key tile of one KV head per CTA, looping over the query heads of its group
 // and over query tiles.  Warps 0-15 compute (warp w touches TMEM lanes (w%4)*32.. and the column
 // quarter w/4), warp 16 issues TMA, warp 17 issues MMAs.
@@ -847,8 +1174,8 @@ int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, vo
   cudaStream_t s = (cudaStream_t)stream;
   if (D == 64) {
     static bool set64 = false;
-    if (!set64) { if (cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<64>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute"); set64 = true; }
-    attn_fwd_kernel<64><<<grid, FwdCfg<64>::THREADS, FwdCfg<64>::SMEM, s>>>(tq, tk, tv, p);
+    if (!set64) { if (cudaFuncSetAttribute(attn_fwd64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd64Cfg::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute"); set64 = true; }
+    attn_fwd64_kernel<<<grid, Fwd64Cfg::THREADS, Fwd64Cfg::SMEM, s>>>(tq, tk, tv, p);
   } else {
     static bool set128 = false;
     if (!set128) { if (cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<128>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute"); set128 = true; }

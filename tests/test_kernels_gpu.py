@@ -209,6 +209,33 @@ def test_flash_attention_fwd_bwd(B, S, Hq, Hkv, D, causal):
     assert rel_l2(dv.float().cpu().numpy(), dv_ref.numpy()) < 2e-2
 
 
+@pytest.mark.parametrize("S,causal", [(512, True), (640, False), (1000, True)])
+def test_flash_attention_fwd_growing_scores(S, causal):
+    """Keys grow along the sequence, so the row maximum jumps by far more than 2^8 between key
+    tiles: the head_dim-64 forward keeps O in tensor memory and must rescale it in these steps
+    (with N(0,1) inputs it never has to)."""
+    B, Hq, Hkv, D = 1, 2, 1, 64
+    g = torch.Generator(device="cpu").manual_seed(S)
+    q = torch.randn(B, S, Hq, D, generator=g).to(torch.bfloat16)
+    ramp = (1.0 + 12.0 * (torch.arange(S) // 96).float() / max(1, S // 96)).view(1, S, 1, 1)
+    k = (torch.randn(B, S, Hkv, D, generator=g) * ramp).to(torch.bfloat16)
+    v = torch.randn(B, S, Hkv, D, generator=g).to(torch.bfloat16)
+    d_o = torch.zeros(B, S, Hq, D).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    o_ref, lse_ref, _, _, _ = _attn_reference(q, k, v, d_o, scale, causal)
+    qd, kd, vd = q.to(dev()), k.to(dev()), v.to(dev())
+    o = torch.full((B, S, Hq, D), float("nan"), dtype=torch.bfloat16, device=dev())
+    lse = torch.empty(B, Hq, S, dtype=torch.float32, device=dev())
+    st = status_word()
+    eb.call("eisen_attn_fwd", stream(), P(qd), P(kd), P(vd), P(o), P(lse), B, S, Hq, Hkv, D,
+            qd.stride(0), qd.stride(1), qd.stride(2), kd.stride(0), kd.stride(1), kd.stride(2),
+            o.stride(0), o.stride(1), o.stride(2), scale, int(causal), P(st))
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert rel_l2(o.float().cpu().numpy(), o_ref.numpy()) < 1e-2
+    assert np.abs(lse.cpu().numpy() - lse_ref.numpy()).max() < 5e-2
+
+
 def test_attention_rejects_bad_head_dim():
     t = torch.zeros(1, 128, 1, 32, dtype=torch.bfloat16, device=dev())
     lse = torch.zeros(1, 1, 128, device=dev())
