@@ -103,7 +103,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* v_full = bars + 5;      // 2
   uint64_t* v_empty = bars + 7;     // 2
   uint64_t* s_full = bars + 9;      // per query tile
-  uint64_t* p_ready = bars + 11;    // per query tile (128 arrivals)
+  uint64_t* p_ready = bars + 11;    // per query tile (one arrival per warp)
   uint64_t* o_full = bars + 13;     // per query tile
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -126,9 +126,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_ready[i], 128 * Cfg::SPLIT);
+      mbar_init(&p_ready[i], 4 * Cfg::SPLIT);  // one arrival per warp
       mbar_init(&o_full[i], 1);
-      mbar_init(&exp_done[i], 128 * Cfg::SPLIT);
+      mbar_init(&exp_done[i], 4 * Cfg::SPLIT);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -367,13 +367,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       rs0 += rs2;
       rs1 += rs3;
-      mbar_arrive(&exp_done[t]);
+      mbar_arrive_warp(&exp_done[t]);
       l = fmaf(l, alpha, rs0 + rs1);
       m = m_new;
       alpha_prev = alpha;
       tc_fence_before_sync();
       fence_proxy_async_smem();
-      mbar_arrive(&p_ready[t]);
+      mbar_arrive_warp(&p_ready[t]);
       if constexpr (SPLIT > 1) {
         // the exchange buffer may be rewritten only after both threads of every row have read it
         asm volatile("bar.sync %0, %1;" ::"r"(3 + t), "r"(128 * SPLIT) : "memory");
@@ -456,8 +456,8 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   uint64_t* v_full = bars + 5;      // 2
   uint64_t* v_empty = bars + 7;     // 2
   uint64_t* s_full = bars + 9;      // per query tile: S is in TMEM
-  uint64_t* s_free = bars + 11;     // per query tile (256 arrivals): S has been read into registers
-  uint64_t* p_ready = bars + 13;    // per query tile (256 arrivals): P is in shared memory
+  uint64_t* s_free = bars + 11;     // per query tile (8 arrivals, one per warp): S has been read into registers
+  uint64_t* p_ready = bars + 13;    // per query tile (8 arrivals, one per warp): P is in shared memory
   uint64_t* o_full = bars + 15;     // per query tile: the P V product issued last is complete
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -479,8 +479,8 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_free[i], 256);
-      mbar_init(&p_ready[i], 256);
+      mbar_init(&s_free[i], 8);   // one arrival per warp
+      mbar_init(&p_ready[i], 8);
       mbar_init(&o_full[i], 1);
     }
     *abort_flag = 0;
@@ -605,7 +605,7 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tmem_ld_32x32b_x32(tS + 32, rb);
       tmem_ld_wait();
       tc_fence_before_sync();
-      mbar_arrive(&s_free[t]);
+      mbar_arrive_warp(&s_free[t]);
       if (need_mask) {
         const int kc0 = j * 128 + part * 64;
 #pragma unroll
@@ -699,7 +699,7 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
       tc_fence_before_sync();
       fence_proxy_async_smem();
-      mbar_arrive(&p_ready[t]);
+      mbar_arrive_warp(&p_ready[t]);
     }
     if (n_mine > 0) {
       mbar_wait(&o_full[t], (n_mine - 1) & 1, abort_flag, p.status, FAULT_WAIT_ATTN);
@@ -751,15 +751,18 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 //                                              once to dQ (in the conversion kernel) and to dK
 //   dV += P^T dO, dK += dS^T Q              -> TMEM, kept across the whole loop (the GQA reduce)
 //   dQ  = dS K                              -> TMEM -> f32 red.global.add into a workspace
-// With D = 64 the dQ tile has TMEM columns of its own, so the S / dP products of the next query
-// tile are issued right behind dV, dK, dQ and the dQ read-out overlaps them; with D = 128 dQ
-// reuses the S columns (512 columns in total) and the read-out comes first.
+// With D = 64 the dQ tile has TMEM columns of its own.  The S / dP products of the next query tile
+// are then issued as soon as the compute warps have read the current S / dP into registers, ahead
+// of the current dV, dK, dQ: the tensor core works on them while the exponentials run, and the
+// compute warps go from one query tile to the next without waiting for a product (only their
+// stores of P / dS wait for the products that still read the tile before).  With D = 128 dQ reuses
+// the S columns (512 columns in total): its read-out comes first and S / dP follow it.
 // =====================================================================================
 template <int D>
 struct BwdCfg {
   static constexpr int TILE = 128 * D * 2;
   static constexpr int P_TILE = 128 * 128 * 2;
-  static constexpr int NS = (D == 64) ? 2 : 1;  // Q / dO stages
+  static constexpr int NS = (D == 64) ? 3 : 1;  // Q / dO stages
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = TILE;
   static constexpr int OFF_Q = 2 * TILE;               // NS stages
@@ -790,13 +793,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
   uint64_t* kv_full = bars;        // 1
-  uint64_t* qdo_full = bars + 1;   // NS (<= 2)
-  uint64_t* qdo_empty = bars + 3;  // NS
-  uint64_t* sdp_full = bars + 5;   // 1
-  uint64_t* pds_ready = bars + 6;  // 1 (NCT arrivals)
-  uint64_t* dq_full = bars + 7;    // 1
-  uint64_t* dq_read = bars + 8;    // 1 (NCT arrivals)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* qdo_full = bars + 1;   // NS (<= 3)
+  uint64_t* qdo_empty = bars + 4;  // NS
+  uint64_t* sdp_full = bars + 7;   // 1
+  uint64_t* pds_ready = bars + 8;  // 1 (one arrival per compute warp)
+  uint64_t* dq_full = bars + 9;    // 1
+  uint64_t* dq_read = bars + 10;   // 1 (one arrival per compute warp)
+  uint64_t* sdp_free = bars + 11;  // 1 (one arrival per compute warp): S / dP are in registers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -812,9 +816,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(kv_full, 1);
     for (int i = 0; i < NS; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
     mbar_init(sdp_full, 1);
-    mbar_init(pds_ready, NCT);
+    mbar_init(pds_ready, Cfg::CWARPS);  // one arrival per warp
     mbar_init(dq_full, 1);
-    mbar_init(dq_read, NCT);
+    mbar_init(dq_read, Cfg::CWARPS);
+    mbar_init(sdp_free, Cfg::CWARPS);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO);
@@ -883,6 +888,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t iph = it & 1;
         const uint32_t sQ = smem_u32(smem + Cfg::OFF_Q + st * Cfg::TILE);
         const uint32_t sDO = smem_u32(smem + Cfg::OFF_DO + st * Cfg::TILE);
+        if (Cfg::DQ_OWN && it + 1 < iters) {
+          // the next S / dP start as soon as the compute warps hold the current ones in registers:
+          // they run beside the exponentials, and the compute warps find them ready afterwards
+          mbar_wait(sdp_free, iph, abort_flag, p.status, FAULT_WAIT_ATTN);
+          tc_fence_after_sync();
+          issue_sdp(it + 1);
+        }
         mbar_wait(pds_ready, iph, abort_flag, p.status, FAULT_WAIT_ATTN);
         tc_fence_after_sync();
         // K dimension of the next three products = the 128 query rows (dV, dK) or 128 keys (dQ)
@@ -904,11 +916,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                        make_smem_desc(sK + k * 2048u, 16384, 1024), idesc_q, k > 0);
         umma_commit(dq_full);
         umma_commit(&qdo_empty[st]);
-        if (it + 1 < iters) {
-          if (!Cfg::DQ_OWN) {  // dQ sits in the S columns: wait until it has been read out
-            mbar_wait(dq_read, iph, abort_flag, p.status, FAULT_WAIT_ATTN);
-            tc_fence_after_sync();
-          }
+        if (!Cfg::DQ_OWN && it + 1 < iters) {  // dQ sits in the S columns: wait until it has been read out
+          mbar_wait(dq_read, iph, abort_flag, p.status, FAULT_WAIT_ATTN);
+          tc_fence_after_sync();
           issue_sdp(it + 1);
         }
       }
@@ -954,7 +964,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
       tc_fence_before_sync();
-      mbar_arrive(dq_read);
+      mbar_arrive_warp(dq_read);
     };
 
     for (int it = 0; it < iters; ++it) {
@@ -975,6 +985,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld_32x32b_x32(tmem_base + Cfg::COL_S + col0 + lane_off, rs);
         tmem_ld_32x32b_x32(tmem_base + Cfg::COL_DP + col0 + lane_off, rd);
         tmem_ld_wait();
+        if (Cfg::DQ_OWN) {
+          tc_fence_before_sync();
+          mbar_arrive_warp(sdp_free);
+        }
         uint32_t pk[16], dk[16];
         const float nlse2 = -lse2, ndlt = -dlt;
         if (!need_mask) {
@@ -1003,17 +1017,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             dk[i >> 1] = pack_bf16x2(d0, d1);
           }
         }
+        // the products of the query tile before read P / dS from shared memory: dq_full, which
+        // the read-out of that tile's dQ waits for, also says that they are done
+        if (Cfg::DQ_OWN && it > 0) drain_dq(it - 1);
         store_row_chunk32(sP, row, col0, pk);
         store_row_chunk32(sDS, row, col0, dk);
       }
       tc_fence_before_sync();
       fence_proxy_async_smem();
-      mbar_arrive(pds_ready);
-      if (Cfg::DQ_OWN) {
-        if (it > 0) drain_dq(it - 1);  // overlaps the dV / dK products of this query tile
-      } else {
-        drain_dq(it);
-      }
+      mbar_arrive_warp(pds_ready);
+      if (!Cfg::DQ_OWN) drain_dq(it);
     }
     if (Cfg::DQ_OWN && iters > 0) drain_dq(iters - 1);
     // dK / dV of this key tile: TMEM -> bf16 -> global (the last dq_full wait covers them)
