@@ -111,10 +111,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qt = (p.S + 127) / 128;
-  const int pair = (int)gridDim.x - 1 - (int)blockIdx.x;  // heavy (late) causal tiles first
+  // blocks are handed out x-fastest, so with the tile index in z every head's heavy (late) causal
+  // tiles start before anybody's light ones
+  const int pair = (int)gridDim.z - 1 - (int)blockIdx.z;
   const int qtA = 2 * pair, qtB = 2 * pair + 1;
   const bool b_valid = qtB < n_qt;
-  const int h = blockIdx.y, b = blockIdx.z;
+  const int h = blockIdx.x, b = blockIdx.y;
   const int kvh = h / (p.Hq / p.Hkv);
   const int nA = p.causal ? min(qtA + 1, n_qt) : n_qt;                 // key tiles of query tile A
   const int nB = b_valid ? (p.causal ? min(qtB + 1, n_qt) : n_qt) : 0;  // key tiles of query tile B
@@ -464,10 +466,12 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qt = (p.S + 127) / 128;
-  const int pair = (int)gridDim.x - 1 - (int)blockIdx.x;  // heavy (late) causal tiles first
+  // blocks are handed out x-fastest, so with the tile index in z every head's heavy (late) causal
+  // tiles start before anybody's light ones
+  const int pair = (int)gridDim.z - 1 - (int)blockIdx.z;
   const int qtA = 2 * pair, qtB = 2 * pair + 1;
   const bool b_valid = qtB < n_qt;
-  const int h = blockIdx.y, b = blockIdx.z;
+  const int h = blockIdx.x, b = blockIdx.y;
   const int kvh = h / (p.Hq / p.Hkv);
   const int nA = p.causal ? min(qtA + 1, n_qt) : n_qt;
   const int nB = b_valid ? (p.causal ? min(qtB + 1, n_qt) : n_qt) : 0;
@@ -769,10 +773,13 @@ struct BwdCfg {
   static constexpr int OFF_DO = OFF_Q + NS * TILE;     // NS stages
   static constexpr int OFF_P = OFF_DO + NS * TILE;
   static constexpr int OFF_DS = OFF_P + P_TILE;
-  static constexpr int OFF_BAR = OFF_DS + P_TILE;
+  static constexpr bool DQ_OWN = (D == 64);  // dQ has its own TMEM columns
+  // with D = 64 a [128 x 64] f32 tile (two 128-byte-swizzled halves of 32 columns) stages dQ for
+  // the TMA unit, which adds it to the f32 accumulation buffer
+  static constexpr int OFF_DQS = OFF_DS + P_TILE;
+  static constexpr int OFF_BAR = OFF_DQS + (DQ_OWN ? 128 * 64 * 4 : 0);
   static constexpr int SMEM = OFF_BAR + 256 + 1024;
   static constexpr int TMEM_COLS = 512;
-  static constexpr bool DQ_OWN = (D == 64);  // dQ has its own TMEM columns
   static constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + D;
   static constexpr int COL_DQ = DQ_OWN ? 256 + 2 * D : 0;
   static constexpr int CWARPS = 16;                 // compute warps
@@ -783,7 +790,7 @@ template <int D>
 __global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                const AttnParams p) {
+                const __grid_constant__ CUtensorMap tmDQ, const AttnParams p) {
   using Cfg = BwdCfg<D>;
   constexpr int ATOMS = D / 64;
   constexpr int NS = Cfg::NS;
@@ -804,8 +811,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int jt = blockIdx.x;  // key tile; tile 0 has the most work under the causal mask
-  const int kvh = blockIdx.y, b = blockIdx.z;
+  // key tile; tile 0 has the most work under the causal mask.  It is the slowest grid index, so
+  // the longest blocks of all heads start first.
+  const int jt = blockIdx.z;
+  const int kvh = blockIdx.x, b = blockIdx.y;
   const int rep = p.Hq / p.Hkv;
   const int n_qt = (p.S + 127) / 128;
   const int i0 = p.causal ? jt : 0;
@@ -823,6 +832,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO);
+    if (Cfg::DQ_OWN) prefetch_tmap(&tmDQ);
   }
   if (warp == Cfg::CWARPS + 1) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
   tc_fence_before_sync();
@@ -941,16 +951,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after_sync();
       float* dq_row = p.dq_acc + (((long long)b * p.S + qrow) * p.Hq + h) * D + cq * DQC;
       if constexpr (DQC == 16) {
+        // TMEM -> registers -> swizzled shared-memory tile -> one TMA reduce-add per half tile.
+        // Adding 16-byte pieces of 32 different rows with one red.global per warp instruction was
+        // the slowest part of this kernel; the TMA unit adds whole 128-byte rows, and rows past
+        // the end of the sequence are clipped by the tensor map.
         uint32_t r[16];
         tmem_ld_32x32b_x16(tmem_base + Cfg::COL_DQ + cq * DQC + lane_off, r);
         tmem_ld_wait();
-        if (qrow < p.S) {
+        tc_fence_before_sync();
+        mbar_arrive_warp(dq_read);
+        if (threadIdx.x == 0) tma_store_wait_read<0>();  // the reduce before has read the staging tile
+        asm volatile("bar.sync 1, %0;" ::"r"(NCT) : "memory");
+        const uint32_t half = smem_u32(smem + Cfg::OFF_DQS) + (cq >> 1) * 16384u;
 #pragma unroll
-          for (int i = 0; i < 16; i += 4)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + i), "f"(__uint_as_float(r[i])),
-                         "f"(__uint_as_float(r[i + 1])), "f"(__uint_as_float(r[i + 2])), "f"(__uint_as_float(r[i + 3]))
-                         : "memory");
+        for (int jv = 0; jv < 4; ++jv)
+          st_shared_v4(half + swz128(row, (cq & 1) * 4 + jv), r[4 * jv], r[4 * jv + 1], r[4 * jv + 2], r[4 * jv + 3]);
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 1, %0;" ::"r"(NCT) : "memory");
+        if (threadIdx.x == 0) {
+          const int qi = i0 + it % per_head;
+          tma_reduce_add_4d(&tmDQ, smem_u32(smem + Cfg::OFF_DQS), 0, h, qi * 128, b);
+          tma_reduce_add_4d(&tmDQ, smem_u32(smem + Cfg::OFF_DQS) + 16384u, 32, h, qi * 128, b);
+          tma_store_commit();
         }
+        return;
       } else {
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_base + Cfg::COL_DQ + cq * DQC + lane_off, r);
@@ -1028,7 +1052,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_arrive_warp(pds_ready);
       if (!Cfg::DQ_OWN) drain_dq(it);
     }
-    if (Cfg::DQ_OWN && iters > 0) drain_dq(iters - 1);
+    if (Cfg::DQ_OWN && iters > 0) {
+      drain_dq(iters - 1);
+      if (threadIdx.x == 0) tma_store_wait<0>();  // the staging tile and the adds outlive nothing
+    }
     // dK / dV of this key tile: TMEM -> bf16 -> global (the last dq_full wait covers them)
     if (iters > 0) {
       tc_fence_after_sync();
@@ -1183,7 +1210,7 @@ int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, vo
   p.causal = causal; p.scale = scale;
   p.o = o; p.o_bs = o_bs; p.o_ss = o_ss; p.o_hs = o_hs;
   p.lse = lse; p.status = status;
-  dim3 grid((unsigned)(((S + 127) / 128 + 1) / 2), (unsigned)Hq, (unsigned)B);  // two query tiles per CTA
+  dim3 grid((unsigned)Hq, (unsigned)B, (unsigned)(((S + 127) / 128 + 1) / 2));  // two query tiles per CTA
   cudaStream_t s = (cudaStream_t)stream;
   if (D == 64) {
     static bool set64 = false;
@@ -1235,21 +1262,28 @@ int eisen_attn_bwd(void* stream, const void* q, const void* k, const void* v, co
       make_qkv_tmap(&tv, v, (int)B, (int)S, (int)Hkv, (int)D, kv_bs, kv_ss, kv_hs) ||
       make_qkv_tmap(&tdo, d_o, (int)B, (int)S, (int)Hq, (int)D, o_bs, o_ss, o_hs))
     return fail(EISEN_ERR_CUDA, "attn_bwd: cuTensorMapEncodeTiled failed");
+  CUtensorMap tdq;
+  {
+    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)Hq, (uint64_t)S, (uint64_t)B};
+    const uint64_t strides[3] = {(uint64_t)D, (uint64_t)(Hq * D), (uint64_t)(S * Hq * D)};
+    const uint32_t box[4] = {32, 1, 128, 1};
+    if (make_tmap_f32_nd(&tdq, dq_acc, 4, dims, strides, box)) return fail(EISEN_ERR_CUDA, "attn_bwd: cuTensorMapEncodeTiled failed for dQ");
+  }
   AttnParams p{};
   p.B = (int)B; p.S = (int)S; p.Hq = (int)Hq; p.Hkv = (int)Hkv; p.D = (int)D;
   p.causal = causal; p.scale = scale;
   p.lse = const_cast<float*>(lse); p.delta = delta; p.dq_acc = dq_acc;
   p.dk = dk; p.dv = dv; p.kv_bs = kv_bs; p.kv_ss = kv_ss; p.kv_hs = kv_hs;
   p.status = status;
-  dim3 grid((unsigned)((S + 127) / 128), (unsigned)Hkv, (unsigned)B);
+  dim3 grid((unsigned)Hkv, (unsigned)B, (unsigned)((S + 127) / 128));
   if (D == 64) {
     static bool set64 = false;
     if (!set64) { if (cudaFuncSetAttribute(attn_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<64>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_bwd: smem attribute"); set64 = true; }
-    attn_bwd_kernel<64><<<grid, BwdCfg<64>::THREADS, BwdCfg<64>::SMEM, s>>>(tq, tk, tv, tdo, p);
+    attn_bwd_kernel<64><<<grid, BwdCfg<64>::THREADS, BwdCfg<64>::SMEM, s>>>(tq, tk, tv, tdo, tdq, p);
   } else {
     static bool set128 = false;
     if (!set128) { if (cudaFuncSetAttribute(attn_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<128>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_bwd: smem attribute"); set128 = true; }
-    attn_bwd_kernel<128><<<grid, BwdCfg<128>::THREADS, BwdCfg<128>::SMEM, s>>>(tq, tk, tv, tdo, p);
+    attn_bwd_kernel<128><<<grid, BwdCfg<128>::THREADS, BwdCfg<128>::SMEM, s>>>(tq, tk, tv, tdo, tdq, p);
   }
   rc = check_launch("attn_bwd");
   if (rc) return rc;

@@ -290,6 +290,23 @@ int make_tmap_bf16_nd(CUtensorMap* out, const void* base, int rank, const uint64
   return r == CUDA_SUCCESS ? 0 : 2;
 }
 
+// f32 tensor, 128-byte swizzle (box rows of 32 floats)
+int make_tmap_f32_nd(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                     const uint64_t* strides_elems /*rank-1, of dims 1..*/, const uint32_t* box) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return 1;
+  cuuint64_t d[5];
+  cuuint64_t s[4];
+  cuuint32_t b[5];
+  cuuint32_t e[5];
+  for (int i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; e[i] = 1; }
+  for (int i = 0; i + 1 < rank; ++i) s[i] = strides_elems[i] * 4;
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, rank, const_cast<void*>(base), d, s, b, e,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 2;
+}
+
 static int g_num_sms = 0;
 static int num_sms() {
   if (!g_num_sms) {

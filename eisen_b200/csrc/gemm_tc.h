@@ -34,5 +34,7 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64
                       uint64_t row_stride_elems, uint32_t box_inner, uint32_t box_outer);
 int make_tmap_bf16_nd(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                       const uint64_t* strides_elems, const uint32_t* box);
+int make_tmap_f32_nd(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                     const uint64_t* strides_elems, const uint32_t* box);
 
 }  // namespace eisen
