@@ -34,8 +34,8 @@ CONFIGS = {
 NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # DRAM bytes per algorithmic FLOP of the tcgen05 GEMM, from the ncu capture summarised in
-# profiles/gemm_bf16_tc2_M8192_N5632_K2048.md (119.5 MB for 1.890e11 FLOPs)
-GEMM_DRAM_BYTES_PER_FLOP = 119.5e6 / 1.890e11
+# profiles/gemm_bf16_tc2_M8192_N5632_K2048.md (128.2 MB for 1.890e11 FLOPs)
+GEMM_DRAM_BYTES_PER_FLOP = 128.2e6 / 1.890e11
 
 
 def model_flops_per_token(c):
