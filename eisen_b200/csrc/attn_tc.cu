@@ -461,7 +461,8 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   uint64_t* s_free = bars + 11;     // per query tile (8 arrivals, one per warp): S has been read into registers
   uint64_t* p_ready = bars + 13;    // per query tile (8 arrivals, one per warp): P is in shared memory
   uint64_t* o_full = bars + 15;     // per query tile: the P V product issued last is complete
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  uint64_t* exp_done = bars + 17;   // per query tile (8 arrivals): its exponentials of a key tile are issued
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -486,6 +487,7 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       mbar_init(&s_free[i], 8);   // one arrival per warp
       mbar_init(&p_ready[i], 8);
       mbar_init(&o_full[i], 1);
+      mbar_init(&exp_done[i], 8);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -651,6 +653,12 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         m_used = m_new;
       }
       const float nmsl2 = (m_used == -INFINITY) ? 0.0f : -m_used * sl2;  // a fully masked row keeps p = 0
+      // the two query tiles take turns with the exponentials (A0, B0, A1, B1, ...)
+      if (t == 0) {
+        if (j > 0 && b_valid) mbar_wait(&exp_done[1], jph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
+      } else {
+        if (j < nA) mbar_wait(&exp_done[0], jph, abort_flag, p.status, FAULT_WAIT_ATTN);
+      }
       // probabilities (bf16, packed) and their row sum
       uint32_t pk[32];
       float rs0 = 0.0f, rs1 = 0.0f, rs2 = 0.0f, rs3 = 0.0f;
@@ -676,6 +684,7 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         pk[16 + (i >> 1)] = pack_bf16x2(x0, x1);
         pk[16 + (i >> 1) + 1] = pack_bf16x2(x2, x3);
       }
+      mbar_arrive_warp(&exp_done[t]);
       l = fmaf(l, alpha, (rs0 + rs1) + (rs2 + rs3));
       if (j > 0) {
         // the previous P V has read P from shared memory and has been added to O
