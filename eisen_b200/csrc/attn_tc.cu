@@ -653,41 +653,9 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         m_used = m_new;
       }
       const float nmsl2 = (m_used == -INFINITY) ? 0.0f : -m_used * sl2;  // a fully masked row keeps p = 0
-      // the two query tiles take turns with the exponentials (A0, B0, A1, B1, ...)
-      if (t == 0) {
-        if (j > 0 && b_valid) mbar_wait(&exp_done[1], jph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
-      } else {
-        if (j < nA) mbar_wait(&exp_done[0], jph, abort_flag, p.status, FAULT_WAIT_ATTN);
-      }
-      // probabilities (bf16, packed) and their row sum
-      uint32_t pk[32];
-      float rs0 = 0.0f, rs1 = 0.0f, rs2 = 0.0f, rs3 = 0.0f;
-#pragma unroll
-      for (int i = 0; i < 32; i += 4) {
-        float x0, x1, x2, x3;
-        ffma2(x0, x1, __uint_as_float(ra[i]), __uint_as_float(ra[i + 1]), sl2, sl2, nmsl2, nmsl2);
-        ffma2(x2, x3, __uint_as_float(ra[i + 2]), __uint_as_float(ra[i + 3]), sl2, sl2, nmsl2, nmsl2);
-        x0 = ex2_approx(x0); x1 = ex2_approx(x1); x2 = ex2_approx(x2); x3 = ex2_approx(x3);
-        fadd2(rs0, rs1, rs0, rs1, x0, x1);
-        fadd2(rs2, rs3, rs2, rs3, x2, x3);
-        pk[i >> 1] = pack_bf16x2(x0, x1);
-        pk[(i >> 1) + 1] = pack_bf16x2(x2, x3);
-      }
-#pragma unroll
-      for (int i = 0; i < 32; i += 4) {
-        float x0, x1, x2, x3;
-        ffma2(x0, x1, __uint_as_float(rb[i]), __uint_as_float(rb[i + 1]), sl2, sl2, nmsl2, nmsl2);
-        ffma2(x2, x3, __uint_as_float(rb[i + 2]), __uint_as_float(rb[i + 3]), sl2, sl2, nmsl2, nmsl2);
-        x0 = ex2_approx(x0); x1 = ex2_approx(x1); x2 = ex2_approx(x2); x3 = ex2_approx(x3);
-        fadd2(rs0, rs1, rs0, rs1, x0, x1);
-        fadd2(rs2, rs3, rs2, rs3, x2, x3);
-        pk[16 + (i >> 1)] = pack_bf16x2(x0, x1);
-        pk[16 + (i >> 1) + 1] = pack_bf16x2(x2, x3);
-      }
-      mbar_arrive_warp(&exp_done[t]);
-      l = fmaf(l, alpha, (rs0 + rs1) + (rs2 + rs3));
       if (j > 0) {
-        // the previous P V has read P from shared memory and has been added to O
+        // the previous P V has read P from shared memory and has been added to O (it was issued
+        // when this tile's last P was ready, a whole softmax ago: the wait is normally over)
         mbar_wait(&o_full[t], jph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
         tc_fence_after_sync();
         if (__any_sync(0xffffffffu, resc)) {
@@ -703,13 +671,50 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           tmem_st_wait();
         }
       }
-      {
-        uint32_t lo[16], hi[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) { lo[i] = pk[i]; hi[i] = pk[16 + i]; }
-        store_row_chunk32(sP, row, part * 64, lo);
-        store_row_chunk32(sP, row, part * 64 + 32, hi);
+      // the two query tiles take turns with the exponentials (A0, B0, A1, B1, ...)
+      if (t == 0) {
+        if (j > 0 && b_valid) mbar_wait(&exp_done[1], jph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
+      } else {
+        if (j < nA) mbar_wait(&exp_done[0], jph, abort_flag, p.status, FAULT_WAIT_ATTN);
       }
+      // probabilities: bf16, stored to the P tile eight at a time as they are produced (the stores
+      // run in the shadow of the exponentials), and their row sum
+      float rs0 = 0.0f, rs1 = 0.0f, rs2 = 0.0f, rs3 = 0.0f;
+      const uint32_t p_half = sP + part * 16384u;  // this thread's 64 columns are one 128-byte row of a half tile
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int u = 0; u < 8; u += 4) {
+          float x0, x1, x2, x3;
+          ffma2(x0, x1, __uint_as_float(ra[i + u]), __uint_as_float(ra[i + u + 1]), sl2, sl2, nmsl2, nmsl2);
+          ffma2(x2, x3, __uint_as_float(ra[i + u + 2]), __uint_as_float(ra[i + u + 3]), sl2, sl2, nmsl2, nmsl2);
+          x0 = ex2_approx(x0); x1 = ex2_approx(x1); x2 = ex2_approx(x2); x3 = ex2_approx(x3);
+          fadd2(rs0, rs1, rs0, rs1, x0, x1);
+          fadd2(rs2, rs3, rs2, rs3, x2, x3);
+          pk[u >> 1] = pack_bf16x2(x0, x1);
+          pk[(u >> 1) + 1] = pack_bf16x2(x2, x3);
+        }
+        st_shared_v4(p_half + swz128(row, i >> 3), pk[0], pk[1], pk[2], pk[3]);
+      }
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int u = 0; u < 8; u += 4) {
+          float x0, x1, x2, x3;
+          ffma2(x0, x1, __uint_as_float(rb[i + u]), __uint_as_float(rb[i + u + 1]), sl2, sl2, nmsl2, nmsl2);
+          ffma2(x2, x3, __uint_as_float(rb[i + u + 2]), __uint_as_float(rb[i + u + 3]), sl2, sl2, nmsl2, nmsl2);
+          x0 = ex2_approx(x0); x1 = ex2_approx(x1); x2 = ex2_approx(x2); x3 = ex2_approx(x3);
+          fadd2(rs0, rs1, rs0, rs1, x0, x1);
+          fadd2(rs2, rs3, rs2, rs3, x2, x3);
+          pk[u >> 1] = pack_bf16x2(x0, x1);
+          pk[(u >> 1) + 1] = pack_bf16x2(x2, x3);
+        }
+        st_shared_v4(p_half + swz128(row, 4 + (i >> 3)), pk[0], pk[1], pk[2], pk[3]);
+      }
+      mbar_arrive_warp(&exp_done[t]);
+      l = fmaf(l, alpha, (rs0 + rs1) + (rs2 + rs3));
       tc_fence_before_sync();
       fence_proxy_async_smem();
       mbar_arrive_warp(&p_ready[t]);
