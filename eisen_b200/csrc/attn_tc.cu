@@ -980,14 +980,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int jv = 0; jv < 4; ++jv)
           st_shared_v4(half + swz128(row, (cq & 1) * 4 + jv), r[4 * jv], r[4 * jv + 1], r[4 * jv + 2], r[4 * jv + 3]);
-        fence_proxy_async_smem();
-        asm volatile("bar.sync 1, %0;" ::"r"(NCT) : "memory");
-        if (threadIdx.x == 0) {
-          const int qi = i0 + it % per_head;
-          tma_reduce_add_4d(&tmDQ, smem_u32(smem + Cfg::OFF_DQS), 0, h, qi * 128, b);
-          tma_reduce_add_4d(&tmDQ, smem_u32(smem + Cfg::OFF_DQS) + 16384u, 32, h, qi * 128, b);
-          tma_store_commit();
-        }
+        // the caller fences these stores together with its own and then calls issue_dq_reduce
         return;
       } else {
         uint32_t r[32];
@@ -1003,6 +996,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       tc_fence_before_sync();
       mbar_arrive_warp(dq_read);
+    };
+
+    // after the staging tile of iteration `it` is complete and fenced in every compute warp: one
+    // thread hands it to the TMA unit (two halves of 32 columns)
+    auto issue_dq_reduce = [&](int it) {
+      asm volatile("bar.sync 1, %0;" ::"r"(NCT) : "memory");
+      if (threadIdx.x == 0) {
+        const int h = kvh * rep + it / per_head;
+        const int qi = i0 + it % per_head;
+        tma_reduce_add_4d(&tmDQ, smem_u32(smem + Cfg::OFF_DQS), 0, h, qi * 128, b);
+        tma_reduce_add_4d(&tmDQ, smem_u32(smem + Cfg::OFF_DQS) + 16384u, 32, h, qi * 128, b);
+        tma_store_commit();
+      }
     };
 
     for (int it = 0; it < iters; ++it) {
@@ -1062,12 +1068,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         store_row_chunk32(sDS, row, col0, dk);
       }
       tc_fence_before_sync();
-      fence_proxy_async_smem();
+      fence_proxy_async_smem();  // covers the P / dS stores and, with D = 64, the dQ staging stores
       mbar_arrive_warp(pds_ready);
-      if (!Cfg::DQ_OWN) drain_dq(it);
+      if (Cfg::DQ_OWN) {
+        if (it > 0) issue_dq_reduce(it - 1);  // off the path to the next products
+      } else {
+        drain_dq(it);
+      }
     }
     if (Cfg::DQ_OWN && iters > 0) {
       drain_dq(iters - 1);
+      fence_proxy_async_smem();
+      issue_dq_reduce(iters - 1);
       if (threadIdx.x == 0) tma_store_wait<0>();  // the staging tile and the adds outlive nothing
     }
     // dK / dV of this key tile: TMEM -> bf16 -> global (the last dq_full wait covers them)
