@@ -1,6 +1,7 @@
 """Single-kernel cases for timing and profiling one entry point of the C ABI at a time.
 
     python -m eisen_b200.cases gemm --m 8192 --n 5632 --k 2048 --a-mn 0 --b-mn 1 --out-mode 0
+    python -m eisen_b200.cases gemm_swiglu --m 16384 --n 5632 --k 2048 --out-mode 1
     python -m eisen_b200.cases attn --batch 2 --seq 2048 --heads 8 --kv-heads 2 --head-dim 64
     python -m eisen_b200.cases ce --rows 4096 --vocab 32000
     python -m eisen_b200.cases rmsnorm --rows 16384 --dim 2048
@@ -38,7 +39,7 @@ def timed(fn, iters, warmup=1):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "attn", "ce", "rmsnorm", "adamw", "swiglu", "elementwise"])
+    ap.add_argument("case", choices=["gemm", "gemm_swiglu", "attn", "ce", "rmsnorm", "adamw", "swiglu", "elementwise"])
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=5632)
@@ -73,6 +74,17 @@ def main():
         ms = timed(lambda: eb.call("eisen_gemm_bf16", s, a.a_mn, a.b_mn, M, N, K, P(A), A.stride(0), P(B), B.stride(0),
                                    P(C), N, a.out_mode, a.split_k, 1.0, P(st)), a.iters)
         out.update(ms=ms, tflops=2.0 * M * N * K / ms / 1e9, shape=[M, N, K])
+    elif a.case == "gemm_swiglu":
+        # gate / up projections + SwiGLU in one launch; --out-mode 1 keeps G and U (a pass that is
+        # followed by a backward pass), 0 writes H only
+        M, N, K = a.m, a.n, a.k
+        A = torch.randn(M, K, device=dev).to(torch.bfloat16)
+        Wg, Wu = ((torch.randn(K, N, device=dev) * 0.05).to(torch.bfloat16) for _ in range(2))
+        G, U, H = (torch.empty(M, N, device=dev, dtype=torch.bfloat16) for _ in range(3))
+        keep = a.out_mode == 1
+        ms = timed(lambda: eb.call("eisen_gemm_bf16_swiglu", s, M, N, K, P(A), K, P(Wg), P(Wu), N,
+                                   P(G) if keep else None, P(U) if keep else None, P(H), N, P(st)), a.iters)
+        out.update(ms=ms, tflops=4.0 * M * N * K / ms / 1e9, shape=[M, N, K], keep_gate_up=keep)
     elif a.case == "attn":
         B_, S, Hq, Hkv, D = a.batch, a.seq, a.heads, a.kv_heads, a.head_dim
         q = torch.randn(B_, S, Hq, D, device=dev).to(torch.bfloat16)

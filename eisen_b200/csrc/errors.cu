@@ -82,4 +82,17 @@ int eisen_gemm_bf16_residual(void* stream, int a_mn, int b_mn, long long M, long
   return gemm_dispatch(stream, a_mn, b_mn, M, N, K, A, lda, B, ldb, C, ldc, R, ldr, eisen::GEMM_OUT_BF16_ACC, 1, alpha, status);
 }
 
+int eisen_gemm_bf16_swiglu(void* stream, long long M, long long N, long long K, const void* A, long long lda,
+                           const void* Bg, const void* Bu, long long ldb, void* G, void* U, void* H, long long ldo,
+                           int* status) {
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL)
+    return eisen::fail(EISEN_ERR_LIMIT, "gemm_bf16_swiglu: a dimension exceeds 2^31-1");
+  const char* err = nullptr;
+  int rc = eisen::gemm_bf16_pair_swiglu((cudaStream_t)stream, (int)M, (int)N, (int)K, A, lda, Bg, Bu, ldb, G, U, H, ldo,
+                                        status, &err);
+  if (rc) return eisen::fail(rc == 1 ? EISEN_ERR_INVALID : EISEN_ERR_CUDA, err ? err : "gemm_bf16_swiglu failed");
+  if (M > 0 && N > 0 && K > 0) eisen::count_launch();
+  return 0;
+}
+
 }  // extern "C"

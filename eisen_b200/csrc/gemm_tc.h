@@ -24,6 +24,10 @@ int gemm_bf16_tc(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int K, c
 int gemm_bf16_tc_pair(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int K, const void* A, long long lda,
                       const void* B, long long ldb, void* C, long long ldc, const void* R, long long ldr, int out_mode,
                       int split_k, float alpha, int* status, const char** err);
+// gate / up projections with the SwiGLU product in the epilogue (dual mode of the paired kernel)
+int gemm_bf16_pair_swiglu(cudaStream_t stream, int M, int N, int K, const void* A, long long lda, const void* Bg,
+                          const void* Bu, long long ldb, void* G, void* U, void* H, long long ldo, int* status,
+                          const char** err);
 int gemm_pair_auto_split_k(int M, int N, int K);
 int gemm_num_sms();
 

@@ -41,6 +41,12 @@ struct PairParams {
   int split_k, kblocks_per_split, kblocks_total;
   int m_tiles, n_tiles, total_tiles;  // m_tiles counts 256-row pair tiles
   int band;  // m-tiles per band of the tile order (see pair_tile_coords)
+  // dual mode (gate / up projections + SwiGLU): CTA 0 of the pair stages 128 columns of B, CTA 1 the
+  // same 128 columns of B2, so the 256-column accumulator holds [x B | x B2]; the epilogue stores
+  // C = bf16(x B), C2 = bf16(x B2) (both optional) and H = silu(C) * C2.  N counts H's columns.
+  int dual;
+  void* C2;
+  void* H;
   float alpha;
   int* status;
 };
@@ -60,7 +66,7 @@ __device__ __forceinline__ void pair_tile_coords(const PairParams& p, int mn, in
 
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                     const PairParams p) {
+                     const __grid_constant__ CUtensorMap tmB2, const PairParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -94,6 +100,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     fence_mbar_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
+    if (p.dual) prefetch_tmap(&tmB2);
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, 2 * P_ACC_COLS);
@@ -120,7 +127,8 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         int mt, nt;
         pair_tile_coords(p, mn, mt, nt);
         const int m0 = mt * (2 * PM) + (int)rank * PM;
-        const int n0 = nt * PN + (int)rank * (PN / 2);
+        const int n0 = p.dual ? nt * (PN / 2) : nt * PN + (int)rank * (PN / 2);
+        const CUtensorMap* tb = (p.dual && rank == 1) ? &tmB2 : &tmB;
         const int kb0 = ks * p.kblocks_per_split;
         const int kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -137,11 +145,11 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             for (int j = 0; j < PM / 64; ++j) tma_load_2d_pair(sa + j * (64 * BK * 2), &tmA, full_leader, m0 + 64 * j, k0);
           }
           if (!p.b_mn) {
-            tma_load_2d_pair(sb, &tmB, full_leader, k0, n0);
+            tma_load_2d_pair(sb, tb, full_leader, k0, n0);
           } else {
 #pragma unroll
             for (int j = 0; j < (PN / 2) / 64; ++j)
-              tma_load_2d_pair(sb + j * (64 * BK * 2), &tmB, full_leader, n0 + 64 * j, k0);
+              tma_load_2d_pair(sb + j * (64 * BK * 2), tb, full_leader, n0 + 64 * j, k0);
           }
           if (++stage == PSTAGES) { stage = 0; phase ^= 1; }
         }
@@ -200,7 +208,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       int mt, nt;
       pair_tile_coords(p, mn, mt, nt);
       const int row = mt * (2 * PM) + (int)rank * PM + q * 32 + lane;
-      const int n0 = nt * PN;
+      const int n0 = p.dual ? nt * (PN / 2) : nt * PN;
       const int kb0 = ks * p.kblocks_per_split;
       const bool has_k = kb0 < p.kblocks_total;
       mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag, p.status, FAULT_WAIT_TMEM_FULL);
@@ -215,7 +223,64 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                           row0 + 32 <= p.M && n0 + PN <= p.N && (p.ldc % 8) == 0 &&
                           (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 &&
                           (!acc_bf16 || ((p.ldr % 8) == 0 && (reinterpret_cast<uintptr_t>(p.R) & 15) == 0));
-      if (staged) {
+      if (p.dual) {
+        // complete slabs only (the host checks M % 256 == 0 and N % 128 == 0).  Per 64 columns:
+        // gate and up are rounded to bf16 first, H is computed from the rounded values (what the
+        // separate SwiGLU kernel reads), then the three 32 x 64 slabs go through the staging tile
+        // one after the other and are stored as 128 contiguous bytes of four rows per instruction.
+        uint8_t* st = epi_stage + q * (32 * 128);
+        const int rr = lane >> 3, seg = lane & 7;
+        const long long out_off = (long long)(row0 + rr) * p.ldc + n0 + seg * 8;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t gq[32], uq[32], hq[32];
+          {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32b_x32(taddr + c * 64, r0);
+            tmem_ld_32x32b_x32(taddr + c * 64 + 32, r1);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              gq[i] = pack_bf16x2(__uint_as_float(r0[2 * i]) * p.alpha, __uint_as_float(r0[2 * i + 1]) * p.alpha);
+              gq[16 + i] = pack_bf16x2(__uint_as_float(r1[2 * i]) * p.alpha, __uint_as_float(r1[2 * i + 1]) * p.alpha);
+            }
+            tmem_ld_32x32b_x32(taddr + PN / 2 + c * 64, r0);
+            tmem_ld_32x32b_x32(taddr + PN / 2 + c * 64 + 32, r1);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              uq[i] = pack_bf16x2(__uint_as_float(r0[2 * i]) * p.alpha, __uint_as_float(r0[2 * i + 1]) * p.alpha);
+              uq[16 + i] = pack_bf16x2(__uint_as_float(r1[2 * i]) * p.alpha, __uint_as_float(r1[2 * i + 1]) * p.alpha);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gq[i]));
+            const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uq[i]));
+            const float h0 = (g.x * __fdividef(1.0f, 1.0f + __expf(-g.x))) * u.x;
+            const float h1 = (g.y * __fdividef(1.0f, 1.0f + __expf(-g.y))) * u.y;
+            hq[i] = pack_bf16x2(h0, h1);
+          }
+          auto store_slab = [&](const uint32_t (&src)[32], void* out) {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<uint4*>(st + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                  make_uint4(src[4 * j], src[4 * j + 1], src[4 * j + 2], src[4 * j + 3]);
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rw = 4 * i + rr;
+              const uint4 o = *reinterpret_cast<const uint4*>(st + rw * 128 + ((seg ^ (rw & 7)) << 4));
+              *reinterpret_cast<uint4*>(dst + out_off + (long long)(4 * i) * p.ldc + c * 64) = o;
+            }
+            __syncwarp();
+          };
+          if (p.C) store_slab(gq, p.C);
+          if (p.C2) store_slab(uq, p.C2);
+          store_slab(hq, p.H);
+        }
+      } else if (staged) {
         uint8_t* st = epi_stage + q * (32 * 128);
         const int rr = lane >> 3, seg = lane & 7;
         __nv_bfloat16* c_base = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)(row0 + rr) * p.ldc + n0 + seg * 8;
@@ -314,10 +379,67 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 
 }  // namespace
 
+// DRAM traffic model of the tile order: A's rows of a band are read once if the band fits in L2
+// (else once per n-tile); B is read once per band unless all of it fits in L2.  Returns the band
+// height (in m-tiles) with the least modelled traffic.
+static int pair_band(int M, int N, int K, int m_tiles, int n_tiles) {
+  const double l2_fit = 75e6;  // bytes of one operand that stay resident next to the streams
+  const double a_total = 2.0 * M * K, b_total = 2.0 * N * K;
+  double best = -1.0;
+  int best_band = m_tiles;
+  for (int band = m_tiles;; band = (band + 1) / 2) {
+    const int n_bands = (m_tiles + band - 1) / band;
+    const double a_band = 2.0 * band * (2 * PM) * K;
+    const double a_tr = a_total * (a_band <= l2_fit ? 1.0 : (double)n_tiles);
+    const double b_tr = b_total * (b_total <= l2_fit ? 1.0 : (double)n_bands);
+    const double tr = a_tr + b_tr;
+    if (best < 0.0 || tr < best * 0.95) { best = tr; best_band = band; }
+    if (band <= 4) break;
+  }
+  return best_band;
+}
+
+static int pair_launch(cudaStream_t stream, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmB2,
+                       const PairParams& p, const char** err) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM);
+    if (e != cudaSuccess) { if (err) *err = cudaGetErrorString(e); return 3; }
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * (gemm_num_sms() / 2), 1, 1);
+  cfg.blockDim = dim3(P_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = P_SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // persistent grid: as many clusters as can be resident at once (SM pairs must share a TPC)
+  static int max_clusters = 0;
+  if (!max_clusters) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_tc2_kernel, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = gemm_num_sms() / 2;
+    }
+    max_clusters = n;
+    if (getenv("EISEN_DEBUG")) fprintf(stderr, "[eisen] paired-CTA GEMM: %d resident clusters on %d SMs\n", n, gemm_num_sms());
+  }
+  const int clusters = p.total_tiles < max_clusters ? p.total_tiles : max_clusters;
+  cfg.gridDim = dim3(2 * clusters, 1, 1);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_tc2_kernel, tmA, tmB, tmB2, p);
+  if (e != cudaSuccess) { if (err) *err = cudaGetErrorString(e); return 3; }
+  return 0;
+}
+
 int gemm_bf16_tc_pair(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int K, const void* A, long long lda,
                       const void* B, long long ldb, void* C, long long ldc, const void* R, long long ldr, int out_mode, int split_k,
                       float alpha, int* status, const char** err) {
-  static bool attr_set = false;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) {
     if (err) *err = "gemm_bf16_tc: operand rows must be 16-byte aligned (leading dimension % 8 == 0)";
@@ -350,59 +472,52 @@ int gemm_bf16_tc_pair(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int
   split_k = (p.kblocks_total + p.kblocks_per_split - 1) / p.kblocks_per_split;
   p.split_k = split_k;
   p.total_tiles = p.m_tiles * p.n_tiles * split_k;
-  {
-    // DRAM traffic model of the tile order: A's rows of a band are read once if the band fits in
-    // L2 (else once per n-tile); B is read once per band unless all of it fits in L2.
-    const double l2_fit = 75e6;  // bytes of one operand that stay resident next to the streams
-    const double a_total = 2.0 * M * K, b_total = 2.0 * N * K;
-    double best = -1.0;
-    int best_band = p.m_tiles;
-    for (int band = p.m_tiles;; band = (band + 1) / 2) {
-      const int n_bands = (p.m_tiles + band - 1) / band;
-      const double a_band = 2.0 * band * (2 * PM) * K;
-      const double a_tr = a_total * (a_band <= l2_fit ? 1.0 : (double)p.n_tiles);
-      const double b_tr = b_total * (b_total <= l2_fit ? 1.0 : (double)n_bands);
-      const double tr = a_tr + b_tr;
-      if (best < 0.0 || tr < best * 0.95) { best = tr; best_band = band; }
-      if (band <= 4) break;
-    }
-    p.band = best_band;
-  }
+  p.band = pair_band(M, N, K, p.m_tiles, p.n_tiles);
   p.alpha = alpha;
   p.status = status;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM);
-    if (e != cudaSuccess) { if (err) *err = cudaGetErrorString(e); return 3; }
-    attr_set = true;
+  p.dual = 0; p.C2 = nullptr; p.H = nullptr;
+  return pair_launch(stream, tmA, tmB, tmB, p, err);
+}
+
+// Gate / up projections with the SwiGLU product in the epilogue (dual mode of the kernel):
+// G = bf16(A Bg), U = bf16(A Bu) (each may be null), H = silu(G) * U.  A is [M,K] K-major, Bg / Bu are
+// [K,N] (MN-major), outputs are [M,N] bf16 with leading dimension ldo.  M % 256 == 0, N % 128 == 0.
+int gemm_bf16_pair_swiglu(cudaStream_t stream, int M, int N, int K, const void* A, long long lda, const void* Bg,
+                          const void* Bu, long long ldb, void* G, void* U, void* H, long long ldo, int* status,
+                          const char** err) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((M % (2 * PM)) || (N % (PN / 2))) {
+    if (err) *err = "gemm_bf16_swiglu: M must be a multiple of 256 and N a multiple of 128";
+    return 1;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * (gemm_num_sms() / 2), 1, 1);
-  cfg.blockDim = dim3(P_THREADS, 1, 1);
-  cfg.dynamicSmemBytes = P_SMEM;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  // persistent grid: as many clusters as can be resident at once (SM pairs must share a TPC)
-  static int max_clusters = 0;
-  if (!max_clusters) {
-    int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_tc2_kernel, &cfg) != cudaSuccess || n <= 0) {
-      cudaGetLastError();
-      n = gemm_num_sms() / 2;
-    }
-    max_clusters = n;
-    if (getenv("EISEN_DEBUG")) fprintf(stderr, "[eisen] paired-CTA GEMM: %d resident clusters on %d SMs\n", n, gemm_num_sms());
+  if ((lda % 8) || (ldb % 8) || (ldo % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(Bg) & 15) ||
+      (reinterpret_cast<uintptr_t>(Bu) & 15) || (reinterpret_cast<uintptr_t>(H) & 15) || (reinterpret_cast<uintptr_t>(G) & 15) ||
+      (reinterpret_cast<uintptr_t>(U) & 15) || !H) {
+    if (err) *err = "gemm_bf16_swiglu: pointers and rows must be 16-byte aligned, H must not be null";
+    return 1;
   }
-  const int clusters = p.total_tiles < max_clusters ? p.total_tiles : max_clusters;
-  cfg.gridDim = dim3(2 * clusters, 1, 1);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_tc2_kernel, tmA, tmB, p);
-  if (e != cudaSuccess) { if (err) *err = cudaGetErrorString(e); return 3; }
-  return 0;
+  CUtensorMap tmA, tmB, tmB2;
+  if (make_tmap_bf16_2d(&tmA, A, K, M, lda, 64, PM) || make_tmap_bf16_2d(&tmB, Bg, N, K, ldb, 64, BK) ||
+      make_tmap_bf16_2d(&tmB2, Bu, N, K, ldb, 64, BK)) {
+    if (err) *err = "gemm_bf16_swiglu: cuTensorMapEncodeTiled failed";
+    return 2;
+  }
+  PairParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.a_mn = 0; p.b_mn = 1;
+  p.C = G; p.ldc = ldo; p.out_mode = GEMM_OUT_BF16;
+  p.R = G; p.ldr = ldo;
+  p.dual = 1; p.C2 = U; p.H = H;
+  p.m_tiles = M / (2 * PM);
+  p.n_tiles = N / (PN / 2);
+  p.kblocks_total = (K + BK - 1) / BK;
+  p.kblocks_per_split = p.kblocks_total;
+  p.split_k = 1;
+  p.total_tiles = p.m_tiles * p.n_tiles;
+  p.band = pair_band(M, 2 * N, K, p.m_tiles, p.n_tiles);
+  p.alpha = 1.0f;
+  p.status = status;
+  return pair_launch(stream, tmA, tmB, tmB2, p, err);
 }
 
 int gemm_pair_clusters_hint() { return gemm_num_sms() / 2; }

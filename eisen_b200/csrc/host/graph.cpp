@@ -465,7 +465,8 @@ int64_t Graph::swiglu(int64_t gate, int64_t up) {
   const int64_t n = tensors.at(gate).numel;
   if (tensors.at(up).numel != n) invalid("swiglu: shapes differ");
   int64_t o = alloc_pooled(tensors[gate].shape);
-  ck(eisen_swiglu_fwd(stream, operand(tensors[gate]), operand(tensors[up]), tensors[o].data, n, dt), "swiglu");
+  if (!skip_forward)
+    ck(eisen_swiglu_fwd(stream, operand(tensors[gate]), operand(tensors[up]), tensors[o].data, n, dt), "swiglu");
   if (!no_grad) {
     tape.push_back({{gate, up}, o, [this, gate, up, o, n, dt]() {
       OUT_GRAD_OR_RETURN(o);
@@ -535,6 +536,46 @@ int64_t Graph::matmul(int64_t a, int64_t b) {
     }});
   }
   return o;
+}
+
+// silu(x Wg) * (x Wu): the gate and up `Linear`s and the SiLU-gated product of
+// src/nn/transformer.rs:41-44 in one launch.  The tape gets the same three entries as
+// matmul, matmul, swiglu (their forward kernels are skipped), so the backward pass is theirs.
+// Shapes the fused kernel does not take (and Fp32 graphs) run the three ops.
+int64_t Graph::gate_up_swiglu(int64_t x, int64_t wg, int64_t wu) {
+  const HTensor& tx = tensors.at(x);
+  const HTensor& tg = tensors.at(wg);
+  const HTensor& tu = tensors.at(wu);
+  if (tg.shape.size() != 2 || tu.shape != tg.shape) invalid("gate_up_swiglu: weights must be two [k, n] matrices");
+  const int64_t k = tx.shape.back(), m = tx.numel / k, n = tg.shape[1];
+  if (tg.shape[0] != k) invalid("gate_up_swiglu: lhs last dim must equal the weights' first dim");
+  const bool fusable = precision == Precision::Bf16Mixed && m % 256 == 0 && n % 128 == 0 && k % 8 == 0 && !skip_forward;
+  if (!fusable) {
+    int64_t go = matmul(x, wg);
+    int64_t up = matmul(x, wu);
+    return swiglu(go, up);
+  }
+  const double flops = 4.0 * (double)m * (double)n * (double)k;
+  if (no_grad) {  // nothing is kept for a backward pass: only the product is written
+    int64_t h = alloc_pooled({m, n});
+    prof_begin(0, flops);
+    ck(eisen_gemm_bf16_swiglu(stream, m, n, k, operand(tensors[x]), k, operand(tensors[wg]), operand(tensors[wu]), n,
+                              nullptr, nullptr, tensors[h].data, n, status_dev),
+       "gate_up_swiglu");
+    prof_end();
+    return h;
+  }
+  skip_forward = true;
+  int64_t go = matmul(x, wg);
+  int64_t up = matmul(x, wu);
+  int64_t h = swiglu(go, up);
+  skip_forward = false;
+  prof_begin(0, flops);
+  ck(eisen_gemm_bf16_swiglu(stream, m, n, k, operand(tensors[x]), k, operand(tensors[wg]), operand(tensors[wu]), n,
+                            tensors[go].data, tensors[up].data, tensors[h].data, n, status_dev),
+     "gate_up_swiglu");
+  prof_end();
+  return h;
 }
 
 // out[m,n] = r[m,n] + a[m,k] b[k,n]: `Linear` followed by the residual `add` of

@@ -180,14 +180,13 @@ int64_t TransformerLM::block_forward(Graph& g, const BlockParams& b, int64_t x, 
     r1 = g.add(x, at);
   }
   int64_t n2 = g.rms_norm(r1, b.norm2, 1e-5f);
-  int64_t go = linear_fwd(g, n2, b.gate);
-  int64_t up, gd;
+  int64_t gd;
   if (fused) {
-    up = linear_fwd(g, n2, b.up);
-    gd = g.swiglu(go, up);
+    gd = g.gate_up_swiglu(n2, b.gate, b.up);  // gate and up projections + SwiGLU in one launch
   } else {
+    int64_t go = linear_fwd(g, n2, b.gate);
     int64_t gt = g.silu(go);
-    up = linear_fwd(g, n2, b.up);
+    int64_t up = linear_fwd(g, n2, b.up);
     gd = g.mul(gt, up);
   }
   // the down projection's output and the second residual sum feed only the next block: when a

@@ -71,6 +71,15 @@ int eisen_gemm_bf16(void* stream, int a_mn, int b_mn, long long M, long long N, 
 int eisen_gemm_bf16_residual(void* stream, int a_mn, int b_mn, long long M, long long N, long long K, const void* A,
                              long long lda, const void* B, long long ldb, const void* R, long long ldr, void* C,
                              long long ldc, float alpha, int* status);
+/* Gate and up projections of the SiLU-gated MLP with the product in the GEMM epilogue
+ * (src/nn/transformer.rs:41-44: Linear, Linear, silu, mul):
+ *   G = bf16(A Bg), U = bf16(A Bu), H = bf16(silu(G) * U)
+ * A is [M,K] row-major, Bg / Bu are the [K,N] weights (leading dimension ldb), G / U / H are
+ * [M,N] bf16 with leading dimension ldo.  G and U may be null (a forward pass that keeps nothing
+ * for a backward pass).  M must be a multiple of 256 and N of 128. */
+int eisen_gemm_bf16_swiglu(void* stream, long long M, long long N, long long K, const void* A, long long lda,
+                           const void* Bg, const void* Bu, long long ldb, void* G, void* U, void* H, long long ldo,
+                           int* status);
 
 /* Tile shape of eisen_gemm_bf16: 0 = chosen per problem shape, 1 = single-CTA 128x256 tiles,
  * 2 = paired-CTA 256x256 tiles (tcgen05 cta_group::2, one cluster of two CTAs per tile).

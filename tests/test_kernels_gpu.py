@@ -86,6 +86,43 @@ def test_gemm_bf16_paired_cta_tiles(a_mn, b_mn, M, N, K):
     assert rel_l2(C32.cpu().numpy(), ref.numpy()) < 1e-5
 
 
+@pytest.mark.parametrize("M,N,K,keep", [(256, 128, 64, True), (512, 384, 320, True), (768, 1024, 1088, False)])
+def test_gemm_bf16_swiglu_epilogue(M, N, K, keep):
+    """Gate and up projections with silu(G) * U computed in the GEMM epilogue (one CTA of the pair
+    stages the gate weight, the other the up weight)."""
+    g = torch.Generator(device="cpu").manual_seed(M + N + K)
+    A = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    Wg = (torch.randn(K, N, generator=g) * 0.1).to(torch.bfloat16)
+    Wu = (torch.randn(K, N, generator=g) * 0.1).to(torch.bfloat16)
+    G_ref = (A.float() @ Wg.float()).to(torch.bfloat16)
+    U_ref = (A.float() @ Wu.float()).to(torch.bfloat16)
+    H_ref = torch.nn.functional.silu(G_ref.float()) * U_ref.float()
+    Ad, Wgd, Wud = A.to(dev()), Wg.to(dev()), Wu.to(dev())
+    G = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+    U = torch.full_like(G, float("nan"))
+    H = torch.full_like(G, float("nan"))
+    st = status_word()
+    eb.call("eisen_gemm_bf16_swiglu", stream(), M, N, K, P(Ad), K, P(Wgd), P(Wud), N,
+            P(G) if keep else None, P(U) if keep else None, P(H), N, P(st))
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert rel_l2(H.float().cpu().numpy(), H_ref.numpy()) < 1e-2
+    if keep:
+        assert rel_l2(G.float().cpu().numpy(), G_ref.float().numpy()) < 5e-3
+        assert rel_l2(U.float().cpu().numpy(), U_ref.float().numpy()) < 5e-3
+        # H is computed from the rounded G and U, as the separate SwiGLU kernel would
+        H2 = torch.nn.functional.silu(G.float()) * U.float()
+        assert rel_l2(H.float().cpu().numpy(), H2.cpu().numpy()) < 4e-3
+    else:
+        assert torch.isnan(G.float()).all() and torch.isnan(U.float()).all()
+
+
+def test_gemm_bf16_swiglu_rejects_ragged_shapes():
+    t = torch.zeros(256, 128, dtype=torch.bfloat16, device=dev())
+    rc = eb.lib().eisen_gemm_bf16_swiglu(stream(), 200, 128, 64, P(t), 64, P(t), P(t), 128, None, None, P(t), 128, None)
+    assert rc == 1
+
+
 @pytest.mark.parametrize("mode", [2, 3, 4])
 def test_gemm_f32_out_modes(mode):
     M, N, K = 256, 384, 2048
