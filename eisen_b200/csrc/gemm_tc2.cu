@@ -111,6 +111,10 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   cluster_sync_all();  // both CTAs' barriers are initialised before anyone signals across the pair
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above ran beside the tail of the kernel before (programmatic dependent launch);
+  // operands, addends and outputs are touched only from here on
+  grid_launch_dependents();
+  grid_dependency_wait();
 
   const int tiles_mn = p.m_tiles * p.n_tiles;
   const int cluster_id = blockIdx.x >> 1;
@@ -412,13 +416,15 @@ static int pair_launch(cudaStream_t stream, const CUtensorMap& tmA, const CUtens
   cfg.blockDim = dim3(P_THREADS, 1, 1);
   cfg.dynamicSmemBytes = P_SMEM;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   // persistent grid: as many clusters as can be resident at once (SM pairs must share a TPC)
   static int max_clusters = 0;
   if (!max_clusters) {

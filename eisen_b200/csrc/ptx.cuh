@@ -62,6 +62,13 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute
+// may start while the kernel before it in the stream is still draining; it must not touch global
+// memory before grid_dependency_wait(), which returns once that kernel has completed and its
+// writes are visible.  grid_launch_dependents() lets the next kernel in the stream start early.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // One arrival for the whole warp: the lanes' earlier writes and fences are ordered before lane 0's
 // arrive by the warp barrier.  Hundreds of threads arriving one by one on the same barrier word
 // serialise in shared memory; a barrier initialised with the number of warps does not.
