@@ -50,7 +50,7 @@ static int gemm_dispatch(void* stream, int a_mn, int b_mn, long long M, long lon
                          int out_mode, int split_k, float alpha, int* status) {
   if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL)
     return eisen::fail(EISEN_ERR_LIMIT, "gemm_bf16: a dimension exceeds 2^31-1");
-  if (out_mode < 0 || out_mode > 4) return eisen::fail(EISEN_ERR_INVALID, "gemm_bf16: bad out_mode");
+  if (out_mode < 0 || out_mode > 4) return eisen::fail(EISEN_ERR_INVALID, "gemm_bf16: bad out_mode");  // mode 5 has its own entry point
   // tile shape: the paired-CTA kernel (256 x 256 per cluster) when the problem has at least one
   // full pair tile in each dimension, else the single-CTA kernel (128 x 256)
   const int mode = eisen::g_gemm_mode.load();
@@ -80,6 +80,19 @@ int eisen_gemm_bf16_residual(void* stream, int a_mn, int b_mn, long long M, long
                              long long ldc, float alpha, int* status) {
   if (!R) return eisen::fail(EISEN_ERR_INVALID, "gemm_bf16_residual: R is null");
   return gemm_dispatch(stream, a_mn, b_mn, M, N, K, A, lda, B, ldb, C, ldc, R, ldr, eisen::GEMM_OUT_BF16_ACC, 1, alpha, status);
+}
+
+int eisen_gemm_bf16_rope(void* stream, long long M, long long N, long long K, const void* A, long long lda, const void* B,
+                         long long ldb, void* C, long long ldc, const float* table_cos_sin, long long seq_len,
+                         long long head_dim, int* status) {
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL || seq_len > 0x7fffffffLL || head_dim > 0x7fffffffLL)
+    return eisen::fail(EISEN_ERR_LIMIT, "gemm_bf16_rope: a dimension exceeds 2^31-1");
+  const char* err = nullptr;
+  int rc = eisen::gemm_bf16_pair_rope((cudaStream_t)stream, (int)M, (int)N, (int)K, A, lda, B, ldb, C, ldc, table_cos_sin,
+                                      (int)seq_len, (int)head_dim, status, &err);
+  if (rc) return eisen::fail(rc == 1 ? EISEN_ERR_INVALID : EISEN_ERR_CUDA, err ? err : "gemm_bf16_rope failed");
+  if (M > 0 && N > 0 && K > 0) eisen::count_launch();
+  return 0;
 }
 
 int eisen_gemm_bf16_swiglu(void* stream, long long M, long long N, long long K, const void* A, long long lda,

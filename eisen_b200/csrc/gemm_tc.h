@@ -12,6 +12,7 @@ enum GemmOutMode : int {
   GEMM_OUT_F32 = 2,         // C(f32)   = alpha * acc
   GEMM_OUT_F32_ACC = 3,     // C(f32)  += alpha * acc   (read-modify-write, one writer per element)
   GEMM_OUT_F32_ATOMIC = 4,  // C(f32)  += alpha * acc   (red.global.add, any number of writers)
+  GEMM_OUT_BF16_ROPE = 5,   // C(bf16)  = rope(bf16(alpha * acc))   (paired kernel, complete tiles only)
 };
 
 // a_mn / b_mn: 0 = K-major operand ([rows][K]), 1 = MN-major operand ([K][rows]).
@@ -28,6 +29,11 @@ int gemm_bf16_tc_pair(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int
 int gemm_bf16_pair_swiglu(cudaStream_t stream, int M, int N, int K, const void* A, long long lda, const void* Bg,
                           const void* Bu, long long ldb, void* G, void* U, void* H, long long ldo, int* status,
                           const char** err);
+// projection followed by interleaved-pair RoPE in the epilogue: rows are tokens of sequences of
+// seq_len positions, columns are heads of head_dim; table is [seq_len][head_dim / 2] (cos, sin)
+int gemm_bf16_pair_rope(cudaStream_t stream, int M, int N, int K, const void* A, long long lda, const void* B,
+                        long long ldb, void* C, long long ldc, const float* table, int seq_len, int head_dim,
+                        int* status, const char** err);
 int gemm_pair_auto_split_k(int M, int N, int K);
 int gemm_num_sms();
 

@@ -47,6 +47,9 @@ struct PairParams {
   int dual;
   void* C2;
   void* H;
+  // GEMM_OUT_BF16_ROPE: rotation table [rope_s][rope_hd / 2] of (cos, sin), row -> position row % rope_s
+  const float2* rope_tab;
+  int rope_s, rope_hd;
   float alpha;
   int* status;
 };
@@ -223,7 +226,8 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       const int row0 = row - lane;  // first row of this warp
       // bf16 outputs of complete 32 x 256 slabs go through shared memory, so that a store (and an
       // addend load) covers 128 contiguous bytes of four rows instead of 16 bytes of 32 rows
-      const bool staged = has_k && (p.out_mode == GEMM_OUT_BF16 || p.out_mode == GEMM_OUT_BF16_ACC) &&
+      const bool rope = p.out_mode == GEMM_OUT_BF16_ROPE;  // the host admits complete tiles only
+      const bool staged = has_k && (p.out_mode == GEMM_OUT_BF16 || p.out_mode == GEMM_OUT_BF16_ACC || rope) &&
                           row0 + 32 <= p.M && n0 + PN <= p.N && (p.ldc % 8) == 0 &&
                           (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 &&
                           (!acc_bf16 || ((p.ldr % 8) == 0 && (reinterpret_cast<uintptr_t>(p.R) & 15) == 0));
@@ -330,6 +334,23 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
               for (int e = 0; e < 4; ++e) {
                 const float2 fa = __bfloat1622float2(a2[e]), fb = __bfloat1622float2(b2[e]);
                 w[e] = pack_bf16x2(fa.x + fb.x, fa.y + fb.y);
+              }
+              o = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            if (rope) {
+              // four (even, odd) column pairs of one head, rotated by the angles of this row's
+              // position; the product was rounded to bf16 first, as a separate RoPE kernel reads it
+              const int pos = (row0 + rw) % p.rope_s;
+              const int pair0 = ((n0 + c * 64 + seg * 8) % p.rope_hd) >> 1;
+              const float4* tp = reinterpret_cast<const float4*>(p.rope_tab + (long long)pos * (p.rope_hd >> 1) + pair0);
+              const float4 t0 = tp[0], t1 = tp[1];
+              const float cs[4] = {t0.x, t0.z, t1.x, t1.z}, sn[4] = {t0.y, t0.w, t1.y, t1.w};
+              const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&o);
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 v = __bfloat1622float2(a2[e]);
+                w[e] = pack_bf16x2(v.x * cs[e] - v.y * sn[e], v.x * sn[e] + v.y * cs[e]);
               }
               o = make_uint4(w[0], w[1], w[2], w[3]);
             }
@@ -482,6 +503,7 @@ int gemm_bf16_tc_pair(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int
   p.alpha = alpha;
   p.status = status;
   p.dual = 0; p.C2 = nullptr; p.H = nullptr;
+  p.rope_tab = nullptr; p.rope_s = 1; p.rope_hd = 2;
   return pair_launch(stream, tmA, tmB, tmB, p, err);
 }
 
@@ -514,6 +536,7 @@ int gemm_bf16_pair_swiglu(cudaStream_t stream, int M, int N, int K, const void* 
   p.C = G; p.ldc = ldo; p.out_mode = GEMM_OUT_BF16;
   p.R = G; p.ldr = ldo;
   p.dual = 1; p.C2 = U; p.H = H;
+  p.rope_tab = nullptr; p.rope_s = 1; p.rope_hd = 2;
   p.m_tiles = M / (2 * PM);
   p.n_tiles = N / (PN / 2);
   p.kblocks_total = (K + BK - 1) / BK;
@@ -524,6 +547,44 @@ int gemm_bf16_pair_swiglu(cudaStream_t stream, int M, int N, int K, const void* 
   p.alpha = 1.0f;
   p.status = status;
   return pair_launch(stream, tmA, tmB, tmB2, p, err);
+}
+
+int gemm_bf16_pair_rope(cudaStream_t stream, int M, int N, int K, const void* A, long long lda, const void* B,
+                        long long ldb, void* C, long long ldc, const float* table, int seq_len, int head_dim,
+                        int* status, const char** err) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((M % (2 * PM)) || (N % PN) || head_dim < 8 || (head_dim % 8) || (N % head_dim) || seq_len <= 0 || !table ||
+      (reinterpret_cast<uintptr_t>(table) & 15)) {
+    if (err) *err = "gemm_bf16_rope: M and N must be multiples of 256, head_dim a multiple of 8 that divides N";
+    return 1;
+  }
+  if ((lda % 8) || (ldb % 8) || (ldc % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
+      (reinterpret_cast<uintptr_t>(C) & 15)) {
+    if (err) *err = "gemm_bf16_rope: pointers and rows must be 16-byte aligned";
+    return 1;
+  }
+  CUtensorMap tmA, tmB;
+  if (make_tmap_bf16_2d(&tmA, A, K, M, lda, 64, PM) || make_tmap_bf16_2d(&tmB, B, N, K, ldb, 64, BK)) {
+    if (err) *err = "gemm_bf16_rope: cuTensorMapEncodeTiled failed";
+    return 2;
+  }
+  PairParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.a_mn = 0; p.b_mn = 1;
+  p.C = C; p.ldc = ldc; p.out_mode = GEMM_OUT_BF16_ROPE;
+  p.R = C; p.ldr = ldc;
+  p.dual = 0; p.C2 = nullptr; p.H = nullptr;
+  p.rope_tab = reinterpret_cast<const float2*>(table); p.rope_s = seq_len; p.rope_hd = head_dim;
+  p.m_tiles = M / (2 * PM);
+  p.n_tiles = N / PN;
+  p.kblocks_total = (K + BK - 1) / BK;
+  p.kblocks_per_split = p.kblocks_total;
+  p.split_k = 1;
+  p.total_tiles = p.m_tiles * p.n_tiles;
+  p.band = pair_band(M, N, K, p.m_tiles, p.n_tiles);
+  p.alpha = 1.0f;
+  p.status = status;
+  return pair_launch(stream, tmA, tmB, tmB, p, err);
 }
 
 int gemm_pair_clusters_hint() { return gemm_num_sms() / 2; }

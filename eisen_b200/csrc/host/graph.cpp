@@ -538,6 +538,54 @@ int64_t Graph::matmul(int64_t a, int64_t b) {
   return o;
 }
 
+// rope(x W): a `Linear` followed by RoPE (src/nn/attention.rs:320-333) with the rotation in the GEMM
+// epilogue.  Backward: the incoming gradient is rotated back in place, then the two products of
+// matmul's backward.  Shapes the fused kernel does not take (and Fp32 graphs) run matmul + rope.
+int64_t Graph::matmul_rope(int64_t a, int64_t b, int64_t head_dim) {
+  const HTensor& ta = tensors.at(a);
+  const HTensor& tb = tensors.at(b);
+  if (ta.shape.size() != 3) invalid("matmul_rope: lhs must be [batch, seq, k]");
+  if (tb.shape.size() != 2) invalid("matmul_rope: rhs must have rank 2 [k, n]");
+  const int64_t B = ta.shape[0], S = ta.shape[1], k = ta.shape[2], m = B * S, n = tb.shape[1];
+  if (tb.shape[0] != k) invalid("matmul_rope: lhs last dim must equal rhs first dim");
+  const bool fusable = precision == Precision::Bf16Mixed && m % 256 == 0 && n % 256 == 0 && k % 8 == 0 &&
+                       head_dim % 8 == 0 && n % head_dim == 0;
+  if (!fusable) {
+    int64_t o = matmul(a, b);
+    reinterpret_shape(o, {B, S, n});
+    return rope(o, head_dim);
+  }
+  const float* tab = rope_table(S, head_dim);
+  const int dt = act_dtype();
+  int64_t o = alloc_pooled({B, S, n});
+  if (!skip_forward) {
+    prof_begin(0, 2.0 * (double)m * (double)n * (double)k);
+    ck(eisen_gemm_bf16_rope(stream, m, n, k, operand(tensors[a]), k, operand(tensors[b]), n, tensors[o].data, n, tab, S,
+                            head_dim, status_dev),
+       "matmul_rope");
+    prof_end();
+  }
+  if (!no_grad) {
+    tape.push_back({{a, b}, o, [this, a, b, o, B, S, m, n, k, head_dim, dt, tab]() {
+      OUT_GRAD_OR_RETURN(o);
+      ck(eisen_rope(stream, to.grad, to.grad, tab, B, S, n, head_dim, dt, 1, 0), "matmul_rope.bwd(rope)");
+      HTensor& ga = tensors[a];
+      HTensor& gb = tensors[b];
+      if (!ga.constant) {
+        ensure_grad(a);
+        gemm(*this, false, false, m, k, n, to.grad, operand(gb), ga.grad, ga.grad_dtype, ga.grad_init);
+        ga.grad_init = true;
+      }
+      if (!gb.constant) {
+        ensure_grad(b);
+        gemm(*this, true, true, k, n, m, operand(ga), to.grad, gb.grad, gb.grad_dtype, gb.grad_init);
+        gb.grad_init = true;
+      }
+    }});
+  }
+  return o;
+}
+
 // silu(x Wg) * (x Wu): the gate and up `Linear`s and the SiLU-gated product of
 // src/nn/transformer.rs:41-44 in one launch.  The tape gets the same three entries as
 // matmul, matmul, swiglu (their forward kernels are skipped), so the backward pass is theirs.

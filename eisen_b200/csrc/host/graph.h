@@ -80,6 +80,7 @@ class Graph {
   int64_t silu(int64_t a);
   int64_t swiglu(int64_t gate, int64_t up);
   int64_t gate_up_swiglu(int64_t x, int64_t wg, int64_t wu);
+  int64_t matmul_rope(int64_t a, int64_t b, int64_t head_dim);
   int64_t matmul(int64_t a, int64_t b);
   int64_t matmul_trans_b(int64_t a, int64_t b);
   // r + a b in one launch (Bf16Mixed): the residual add done in the projection's epilogue

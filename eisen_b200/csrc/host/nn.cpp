@@ -117,8 +117,16 @@ int64_t TransformerLM::gqa_forward(Graph& g, const BlockParams& b, int64_t x, bo
   const std::vector<int64_t> xs = g.tensors.at(x).shape;
   if (xs.size() != 3) throw EisenException(EISEN_ERR_INVALID, "GQA requires [Batch, Seq, Dim]");
   const int64_t B = xs[0], S = xs[1], hd = hidden / heads;
-  int64_t q = linear_fwd(g, x, b.q), k = linear_fwd(g, x, b.k), v = linear_fwd(g, x, b.v);
-  int64_t qr = g.rope(q, hd), kr = g.rope(k, hd);
+  int64_t qr, kr;
+  if (fused) {  // projection + RoPE in one launch each
+    qr = g.matmul_rope(x, b.q, hd);
+    kr = g.matmul_rope(x, b.k, hd);
+  } else {
+    int64_t q = linear_fwd(g, x, b.q), k = linear_fwd(g, x, b.k);
+    qr = g.rope(q, hd);
+    kr = g.rope(k, hd);
+  }
+  int64_t v = linear_fwd(g, x, b.v);
   int64_t ctx2;
   if (fused) {
     ctx2 = g.attention(qr, kr, v, heads, kv_heads, causal);

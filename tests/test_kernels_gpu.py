@@ -117,6 +117,28 @@ def test_gemm_bf16_swiglu_epilogue(M, N, K, keep):
         assert torch.isnan(G.float()).all() and torch.isnan(U.float()).all()
 
 
+@pytest.mark.parametrize("B,S,N,K,hd", [(1, 256, 256, 64, 64), (2, 384, 512, 320, 64), (4, 128, 256, 192, 128)])
+def test_gemm_bf16_rope_epilogue(B, S, N, K, hd):
+    """Projection with interleaved-pair RoPE in the GEMM epilogue == separate GEMM + eisen_rope."""
+    M = B * S
+    g = torch.Generator(device="cpu").manual_seed(M + N + K + hd)
+    A = torch.randn(M, K, generator=g).to(torch.bfloat16).to(dev())
+    W = (torch.randn(K, N, generator=g) * 0.2).to(torch.bfloat16).to(dev())
+    tab = torch.empty(S, hd // 2, 2, device=dev())
+    eb.call("eisen_rope_table", stream(), P(tab), S, hd, 10000.0)
+    st = status_word()
+    plain = torch.empty(M, N, dtype=torch.bfloat16, device=dev())
+    eb.call("eisen_gemm_bf16", stream(), 0, 1, M, N, K, P(A), K, P(W), N, P(plain), N, 0, 1, 1.0, P(st))
+    ref = torch.empty_like(plain)
+    eb.call("eisen_rope", stream(), P(plain), P(ref), P(tab), B, S, N, hd, eb.BF16, 0, 0)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+    eb.call("eisen_gemm_bf16_rope", stream(), M, N, K, P(A), K, P(W), N, P(out), N, P(tab), S, hd, P(st))
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    # same rounding points as the two-kernel path: bit-identical
+    assert torch.equal(out.view(torch.int16), ref.view(torch.int16))
+
+
 def test_gemm_bf16_swiglu_rejects_ragged_shapes():
     t = torch.zeros(256, 128, dtype=torch.bfloat16, device=dev())
     rc = eb.lib().eisen_gemm_bf16_swiglu(stream(), 200, 128, 64, P(t), 64, P(t), P(t), 128, None, None, P(t), 128, None)
