@@ -83,16 +83,23 @@ rmsnorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ w, T* 
   const int lane = threadIdx.x & 31;
   const long long warp0 = (long long)blockIdx.x * RN_WARPS + (threadIdx.x >> 5);
   const long long wstride = (long long)gridDim.x * RN_WARPS;
-  for (long long row = warp0; row < rows; row += wstride) {
+  // the next row of this warp is requested before the current one is reduced and written
+  uint4 raw[NCH], nxt[NCH];
+  auto load_row = [&](long long row, uint4 (&dst)[NCH]) {
     const T* xr = x + row * dim;
-    T* yr = y + row * dim;
-    uint4 raw[NCH];
-    float ss = 0.0f;
 #pragma unroll
     for (int j = 0; j < NCH; ++j) {
       const int c = (j * 32 + lane) * V;
-      raw[j] = (c < dim) ? *reinterpret_cast<const uint4*>(xr + c) : make_uint4(0, 0, 0, 0);
+      dst[j] = (row < rows && c < dim) ? *reinterpret_cast<const uint4*>(xr + c) : make_uint4(0, 0, 0, 0);
     }
+  };
+  load_row(warp0, nxt);
+  for (long long row = warp0; row < rows; row += wstride) {
+    T* yr = y + row * dim;
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) raw[j] = nxt[j];
+    load_row(row + wstride, nxt);
 #pragma unroll
     for (int j = 0; j < NCH; ++j) {
       float v[V];
