@@ -245,7 +245,9 @@ def run_ours(args, cfg, name):
         offs, total = edp.param_offsets(shapes)
         assert total == n_arena, (total, n_arena)
         buckets = edp.plan_buckets(offs, cfg["layers"], total, min_bucket_elems=args.bucket_mb * (1 << 20) // 4)
-        reducer = edp.BucketedAllReduce(flat, buckets)
+        reducer = edp.BucketedAllReduce(flat, buckets, comm_stream=torch.cuda.Stream(device=dev, priority=-1))
+        # the persistent GEMMs leave a few SMs to the all-reduce kernels that run beside the backward
+        eb.call("eisen_gemm_reserve_sms", args.comm_sms)
 
     state = {"loss": None}
 
@@ -366,6 +368,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="llama-0.85b-gqa", choices=sorted(CONFIGS))
     ap.add_argument("--no-checkpoint", action="store_true")
+    ap.add_argument("--comm-sms", type=int, default=4, help="SMs the GEMMs leave free for NCCL when N > 1")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--bucket-mb", type=int, default=256)
     args = ap.parse_args()

@@ -45,6 +45,12 @@ int eisen_gemm_set_mode(int mode) {
   return 0;
 }
 
+int eisen_gemm_reserve_sms(int n) {
+  if (n < 0 || n > 64) return eisen::fail(EISEN_ERR_INVALID, "gemm_reserve_sms: n must be in [0, 64]");
+  eisen::gemm_set_reserved_sms(n);
+  return 0;
+}
+
 static int gemm_dispatch(void* stream, int a_mn, int b_mn, long long M, long long N, long long K, const void* A,
                          long long lda, const void* B, long long ldb, void* C, long long ldc, const void* R, long long ldr,
                          int out_mode, int split_k, float alpha, int* status) {

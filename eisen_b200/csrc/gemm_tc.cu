@@ -307,6 +307,7 @@ int make_tmap_f32_nd(CUtensorMap* out, const void* base, int rank, const uint64_
   return r == CUDA_SUCCESS ? 0 : 2;
 }
 
+static int g_reserved_sms = 0;
 static int g_num_sms = 0;
 static int num_sms() {
   if (!g_num_sms) {
@@ -361,7 +362,9 @@ int gemm_bf16_tc(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int K, c
     if (e != cudaSuccess) { if (err) *err = cudaGetErrorString(e); return 3; }
     attr_set = true;
   }
-  int grid = p.total_tiles < num_sms() ? p.total_tiles : num_sms();
+  int avail = num_sms() - g_reserved_sms;
+  if (avail < 1) avail = 1;
+  int grid = p.total_tiles < avail ? p.total_tiles : avail;
   gemm_bf16_tc_kernel<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { if (err) *err = cudaGetErrorString(e); return 3; }
@@ -369,6 +372,8 @@ int gemm_bf16_tc(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int K, c
 }
 
 int gemm_num_sms() { return num_sms(); }
+int gemm_reserved_sms() { return g_reserved_sms; }
+void gemm_set_reserved_sms(int n) { g_reserved_sms = n < 0 ? 0 : n; }
 
 int gemm_tc_auto_split_k(int M, int N, int K) {
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);

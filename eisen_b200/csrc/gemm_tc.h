@@ -36,6 +36,9 @@ int gemm_bf16_pair_rope(cudaStream_t stream, int M, int N, int K, const void* A,
                         int* status, const char** err);
 int gemm_pair_auto_split_k(int M, int N, int K);
 int gemm_num_sms();
+// SMs the persistent GEMM grids leave free (for a communication kernel that runs beside them)
+int gemm_reserved_sms();
+void gemm_set_reserved_sms(int n);
 
 // split factor that fills the machine when M*N alone gives fewer tiles than SMs
 int gemm_tc_auto_split_k(int M, int N, int K);

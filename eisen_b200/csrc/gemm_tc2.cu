@@ -457,7 +457,9 @@ static int pair_launch(cudaStream_t stream, const CUtensorMap& tmA, const CUtens
     max_clusters = n;
     if (getenv("EISEN_DEBUG")) fprintf(stderr, "[eisen] paired-CTA GEMM: %d resident clusters on %d SMs\n", n, gemm_num_sms());
   }
-  const int clusters = p.total_tiles < max_clusters ? p.total_tiles : max_clusters;
+  int avail = max_clusters - (gemm_reserved_sms() + 1) / 2;
+  if (avail < 1) avail = 1;
+  const int clusters = p.total_tiles < avail ? p.total_tiles : avail;
   cfg.gridDim = dim3(2 * clusters, 1, 1);
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_tc2_kernel, tmA, tmB, tmB2, p);
   if (e != cudaSuccess) { if (err) *err = cudaGetErrorString(e); return 3; }

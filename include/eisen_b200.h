@@ -92,6 +92,11 @@ int eisen_gemm_bf16_swiglu(void* stream, long long M, long long N, long long K, 
  * 2 = paired-CTA 256x256 tiles (tcgen05 cta_group::2, one cluster of two CTAs per tile).
  * Process-wide; meant for tests and measurements. */
 int eisen_gemm_set_mode(int mode);
+/* The tensor-core GEMMs are persistent kernels, one CTA per SM.  A collective that should run
+ * beside them (the gradient all-reduce of a data-parallel step, on its own stream) finds no SM
+ * until they exit; n > 0 makes every later GEMM launch leave n SMs free.  No counterpart in the
+ * reference (single GPU).  Default 0. */
+int eisen_gemm_reserve_sms(int n);
 
 /* f32 SIMT GEMM with element strides and a batch dimension (f32 parity path):
  *   C[b,m,n] (+)= sum_k A[b*a_bs + m*a_ms + k*a_ks] * B[b*b_bs + k*b_ks + n*b_ns]
