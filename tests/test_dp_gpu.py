@@ -1,7 +1,7 @@
 """Two-GPU data-parallel step: bucketed NCCL all-reduce overlapped with the backward pass.
 
 The reduced gradient of two ranks (one micro-batch each) must equal the gradient one rank
-accumulates over both micro-batches (a sum; SURVEY: w-rank result == 1-rank result with accum = w).
+accumulates over both micro-batches (a sum: the w-rank result equals the 1-rank result with accum = w).
 Skipped when fewer than two GPUs are visible.
 """
 import os
