@@ -712,8 +712,11 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           pk[(u >> 1) + 1] = pack_bf16x2(x2, x3);
         }
         st_shared_v4(p_half + swz128(row, 4 + (i >> 3)), pk[0], pk[1], pk[2], pk[3]);
+        // the turn is handed over with 24 of the 64 exponentials still to go: the other tile needs
+        // a few hundred clocks from the barrier to its first exponential (measured: better than
+        // handing over at the end, at 16 or at 32 to go)
+        if (i == 0) mbar_arrive_warp(&exp_done[t]);
       }
-      mbar_arrive_warp(&exp_done[t]);
       l = fmaf(l, alpha, (rs0 + rs1) + (rs2 + rs3));
       tc_fence_before_sync();
       fence_proxy_async_smem();
