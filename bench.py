@@ -352,7 +352,7 @@ def run_ours(args, cfg, name):
         }
         out["config"]["params"] = sum(int(np.prod(g.shape(p))) for p in params)
         if world == 1 and not args.no_cpu_baseline:
-            v, desc, secs = cpu_sample(cfg, 1, tokens=2)
+            v, desc, secs = cpu_sample(cfg, 1, tokens=4)  # about 15 s of single-thread CPU work
             out["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": 1, "kind": "port", "sample": desc,
                                    "seconds": secs}
         print(json.dumps(out), flush=True)
