@@ -228,20 +228,23 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w, const T
     }
 #pragma unroll
     for (int r = 0; r < RB_ROWS; ++r) {
-      float ss = 0.0f, gd = 0.0f;
+      float ss = 0.0f, gd = 0.0f, ss1 = 0.0f, gd1 = 0.0f;
 #pragma unroll
       for (int j = 0; j < NCH; ++j) {
         float xv[V], gv[V];
         unpack16(xr[r][j], xv);
         unpack16(gr[r][j], gv);
+        // packed f32x2 arithmetic: the kernel is bound by instruction issue, not by memory
 #pragma unroll
-        for (int k = 0; k < V; ++k) {
-          ss += xv[k] * xv[k];
-          gd += gv[k] * xv[k] * wv[j][k];
+        for (int k = 0; k < V; k += 2) {
+          float t0, t1;
+          ffma2(ss, ss1, xv[k], xv[k + 1], xv[k], xv[k + 1], ss, ss1);
+          fmul2(t0, t1, gv[k], gv[k + 1], xv[k], xv[k + 1]);
+          ffma2(gd, gd1, t0, t1, wv[j][k], wv[j][k + 1], gd, gd1);
         }
       }
-      part[2 * r] = ss;
-      part[2 * r + 1] = gd;
+      part[2 * r] = ss + ss1;
+      part[2 * r + 1] = gd + gd1;
     }
     // eight sums over the warp in nine shuffles: each round halves the number of values a lane
     // carries; afterwards lane l holds the warp total of value ((l>>4)&1)*4 + ((l>>3)&1)*2 + ((l>>2)&1)
@@ -301,10 +304,15 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w, const T
             float xv[V], gv[V], o[V];
             unpack16(xr[r][j], xv);
             unpack16(gr[r][j], gv);
+            const float ncoef = -coef;
 #pragma unroll
-            for (int k = 0; k < V; ++k) {
-              o[k] = rrms * (gv[k] * wv[j][k]) - xv[k] * coef;
-              dwp[j][k] += gv[k] * xv[k] * rrms;
+            for (int k = 0; k < V; k += 2) {
+              float a0, a1, b0, b1, t0, t1;
+              fmul2(a0, a1, gv[k], gv[k + 1], wv[j][k], wv[j][k + 1]);
+              fmul2(b0, b1, xv[k], xv[k + 1], ncoef, ncoef);
+              ffma2(o[k], o[k + 1], a0, a1, rrms, rrms, b0, b1);
+              fmul2(t0, t1, gv[k], gv[k + 1], xv[k], xv[k + 1]);
+              ffma2(dwp[j][k], dwp[j][k + 1], t0, t1, rrms, rrms, dwp[j][k], dwp[j][k + 1]);
             }
             T* dr = dx + (r0 + r) * dim + c;
             if (acc_dx) {
