@@ -368,7 +368,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="llama-0.85b-gqa", choices=sorted(CONFIGS))
     ap.add_argument("--no-checkpoint", action="store_true")
-    ap.add_argument("--comm-sms", type=int, default=4, help="SMs the GEMMs leave free for NCCL when N > 1")
+    ap.add_argument("--comm-sms", type=int, default=0, help="SMs the GEMMs leave free for NCCL when N > 1 (measured at 8 GPUs: 0 is best)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--bucket-mb", type=int, default=256)
     args = ap.parse_args()
