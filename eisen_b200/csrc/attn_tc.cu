@@ -7,8 +7,9 @@
 // both A*B^T and A^T*B style products; accumulators live in TMEM.
 //
 // Forward: two 128-query tiles of one head per CTA share the K / V tiles; softmax warps read
-// S = Q K^T from TMEM, write P (bf16) to shared memory, and fold each P V product (a fresh TMEM
-// accumulator) into f32 registers with the online-softmax rescale.
+// S = Q K^T from TMEM and write P (bf16) to shared memory.  At D = 64 (attn_fwd64_kernel) O stays in
+// TMEM and is rescaled lazily; at D = 128 (attn_fwd_kernel) each P V product is a fresh TMEM
+// accumulator folded into f32 registers with the online-softmax rescale.
 // Backward: one 128-key tile of one KV head per CTA, looping over the query heads of its group and
 // over query tiles; dV and dK stay in TMEM for the whole loop (the GQA reduce), dQ tiles are added
 // to an f32 workspace.  Details sit above each kernel.
@@ -54,10 +55,11 @@ __device__ __forceinline__ void store_row_chunk32(uint32_t tile_base, int row, i
 }
 
 // =====================================================================================
-// forward: two 128-query tiles of one head per CTA.  Warps 0-3 run the softmax of tile A,
-// warps 4-7 that of tile B (thread = query row), warp 8 issues TMA, warp 9 issues MMAs.  K and V
-// tiles are loaded once and used by both query tiles; while one tile's softmax runs on the SIMT
-// side the tensor core works on the other tile's S = Q K^T and PV products.
+// forward (used at D = 128; D = 64 has attn_fwd64_kernel below): two 128-query tiles of one head
+// per CTA.  Warps 0-3 run the softmax of tile A, warps 4-7 that of tile B (thread = query row), the
+// next two warps issue TMA and MMAs.  K and V tiles are loaded once and used by both query tiles;
+// while one tile's softmax runs on the SIMT side the tensor core works on the other tile's
+// S = Q K^T and PV products.
 // =====================================================================================
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
