@@ -26,6 +26,7 @@ _CTYPES = {
     "const long long*": C.c_void_p,
     "const char*": C.c_char_p,
     "long long": C.c_longlong,
+    "unsigned long long": C.c_ulonglong,
     "int": C.c_int,
     "float": C.c_float,
     "double": C.c_double,

@@ -355,6 +355,23 @@ int eisen_optim_step(void* opt);
 int eisen_optim_step_fused(void* opt, float max_norm, float grad_scale);
 int eisen_optim_is_flat(void* opt, int* flat);
 
+/* ------------------------------------------------------------------------------------------
+ * Input side: pre-tokenised u16 token files (BinaryDataLoader, src/data/dataloader.rs:89-214, with
+ * the fill-in-the-middle transform of src/data/fim.rs:96-180).  Host only: batches are written to
+ * caller-provided buffers (pinned ones for asynchronous copies); ids and targets are int32, the
+ * ignore index is -1.  A batch takes batch * (seq_len + 1) consecutive tokens of the file.
+ * ------------------------------------------------------------------------------------------ */
+int eisen_loader_open(const char* path, long long seq_len, long long batch, void** handle_out);
+int eisen_loader_close(void* loader);
+long long eisen_loader_total_batches(void* loader);
+/* FIM on: control tokens base_vocab .. base_vocab + 3 (prefix, suffix, middle, pad); `rate` of the
+ * sequences are transformed, `spm_rate` of those in suffix-prefix-middle order. */
+int eisen_loader_set_fim(void* loader, long long base_vocab, float rate, float spm_rate);
+int eisen_loader_seed(void* loader, unsigned long long seed);   /* xorshift64 state, default 1337 */
+int eisen_loader_reset(void* loader);                           /* back to the start of the file */
+/* x, targets: [batch * seq_len].  Returns 0, or 1 when no complete batch is left. */
+int eisen_loader_next(void* loader, int* x, int* targets, int* has_masked);
+
 #ifdef __cplusplus
 }
 #endif
