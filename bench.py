@@ -250,11 +250,24 @@ def run_ours(args, cfg, name):
         eb.call("eisen_gemm_reserve_sms", args.comm_sms)
 
     state = {"loss": None}
+    feeder = None
+    if args.data:
+        # e2e leg from a pre-tokenised u16 file (the reference's .bin format) instead of synthetic ids
+        from eisen_b200.data import BinaryDataLoader, PinnedBatchFeeder
+        feeder = PinnedBatchFeeder(BinaryDataLoader(args.data, S, B), g, compute)
 
     def step(e2e, it):
         opt.zero_grad()
         for a in range(accum):
-            if e2e:
+            n_valid = B * S
+            if e2e and feeder is not None:
+                nxt = feeder.next()
+                if nxt is None:  # end of file: start over
+                    feeder.loader.reset()
+                    feeder.ready = feeder._fill(feeder.cur)
+                    nxt = feeder.next()
+                x, t, _, n_valid = nxt
+            elif e2e:
                 j = (it * accum + a) % n_host_batches
                 x = g.alloc_ids([B, S], host_ids[j].data_ptr())
                 t = g.alloc_ids([B * S], host_tgt[j].data_ptr())
@@ -263,7 +276,7 @@ def run_ours(args, cfg, name):
             cb = None
             if reducer is not None and a == accum - 1:
                 cb = lambda layer: reducer.on_block_done(layer, compute)  # noqa: E731
-            loss = lm.train_micro_step_dev(x, t, B * S, checkpoint=checkpoint, after_block=cb)
+            loss = lm.train_micro_step_dev(x, t, n_valid, checkpoint=checkpoint, after_block=cb)
             if e2e:
                 state["loss"] = float(g.data(loss)[0])  # D2H read of the step's loss
             g.clear_activations()
@@ -368,6 +381,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="llama-0.85b-gqa", choices=sorted(CONFIGS))
     ap.add_argument("--no-checkpoint", action="store_true")
+    ap.add_argument("--data", default=None, help="u16 token file for the e2e leg (default: synthetic ids)")
     ap.add_argument("--comm-sms", type=int, default=0, help="SMs the GEMMs leave free for NCCL when N > 1 (measured at 8 GPUs: 0 is best)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--bucket-mb", type=int, default=256)
