@@ -197,6 +197,14 @@ int eisen_lm_set_fused(void* lm, int fused) {
 int eisen_lm_forward(void* lm, void* g, long long x, long long* out) {
   return guarded([&] { *out = static_cast<TransformerLM*>(lm)->forward(G(g), x); });
 }
+int eisen_lm_export_hf(void* lm, void* g, const char* safetensors_path, const char* config_path,
+                       long long max_position_embeddings) {
+  return guarded([&] {
+    if (!lm || !safetensors_path) throw EisenException(EISEN_ERR_INVALID, "lm_export_hf: null argument");
+    export_hf(G(g), *static_cast<TransformerLM*>(lm), safetensors_path, config_path, max_position_embeddings);
+  });
+}
+
 int eisen_lm_params(void* lm, long long* out, int* n) {
   return guarded([&] {
     auto p = static_cast<TransformerLM*>(lm)->params();

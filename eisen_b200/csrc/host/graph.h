@@ -183,6 +183,10 @@ class TransformerLM {
   std::vector<BlockParams> blocks;
 };
 
+// examples/export_hf_pipeline.rs, src/tools/huggingface.rs: model.safetensors + config.json (export_hf.cpp)
+void export_hf(Graph& g, const TransformerLM& lm, const char* safetensors_path, const char* config_path,
+               int64_t max_position_embeddings);
+
 // src/nn/optim.rs
 class AdamW {
  public:

@@ -249,6 +249,11 @@ class TransformerLM:
         call("eisen_lm_params", self._h, buf, C.byref(n))
         return [buf[i] for i in range(n.value)]
 
+    def export_hf(self, safetensors_path, config_path=None, max_position_embeddings=2048):
+        """model.safetensors (+ config.json) loadable as transformers.LlamaForCausalLM."""
+        call("eisen_lm_export_hf", self._h, self.g._h, str(safetensors_path).encode(),
+             str(config_path).encode() if config_path else None, max_position_embeddings)
+
     def train_micro_step(self, x_id, targets, checkpoint=False, after_block=None):
         """targets: sequence of ints or a ctypes long long array.  Returns the loss tensor id."""
         t = targets if isinstance(targets, C.Array) else _ll(targets)

@@ -325,6 +325,11 @@ int eisen_lm_destroy(void* lm);
 int eisen_lm_set_fused(void* lm, int fused);   /* 0: the reference's op-by-op attention / MLP chain */
 int eisen_lm_forward(void* lm, void* g, long long x_ids, long long* logits_out);       /* Module::forward, :184-196 */
 int eisen_lm_params(void* lm, long long* ids_out, int* n_out);                         /* Module::params, :198-210 */
+/* Hugging Face export (examples/export_hf_pipeline.rs:200-300, src/tools/huggingface.rs:88-146): writes the
+ * f32 master weights as LlamaForCausalLM tensors (Linear weights transposed to [out, in], q / k rows
+ * permuted from interleaved-pair to rotate-half RoPE order) and, if config_path is not null, config.json. */
+int eisen_lm_export_hf(void* lm, void* g, const char* safetensors_path, const char* config_path,
+                       long long max_position_embeddings);
 /* one micro-step: forward, masked cross-entropy over n_targets rows, backward; with checkpoint
  * != 0 each block is re-run under a save point during the backward (src/graph/mod.rs:332-365).
  * after_block(l, user) fires when the gradients of block l are final (l == layers: final norm
