@@ -197,6 +197,19 @@ int eisen_lm_set_fused(void* lm, int fused) {
 int eisen_lm_forward(void* lm, void* g, long long x, long long* out) {
   return guarded([&] { *out = static_cast<TransformerLM*>(lm)->forward(G(g), x); });
 }
+int eisen_graph_save_weights(void* g, const char* path) {
+  return guarded([&] {
+    if (!path) throw EisenException(EISEN_ERR_INVALID, "save_weights: null path");
+    save_weights(G(g), path);
+  });
+}
+int eisen_graph_load_weights(void* g, const char* path) {
+  return guarded([&] {
+    if (!path) throw EisenException(EISEN_ERR_INVALID, "load_weights: null path");
+    load_weights(G(g), path);
+  });
+}
+
 int eisen_lm_export_hf(void* lm, void* g, const char* safetensors_path, const char* config_path,
                        long long max_position_embeddings) {
   return guarded([&] {

@@ -131,4 +131,55 @@ void export_hf(Graph& g, const TransformerLM& lm, const char* safetensors_path, 
   }
 }
 
+// Weights-only checkpoint of examples/train_llm.rs:92-105 (`save_weights`): every parameter tensor in id
+// order, f32 little-endian, nothing else; the file the reference's converter
+// (examples/export_hf_pipeline.rs:187-196) reads.  Id tensors that sit below the parameter watermark
+// are not parameters and are skipped.
+void save_weights(Graph& g, const char* path) {
+  g.synchronize();
+  FILE* f = fopen(path, "wb");
+  if (!f) throw EisenException(EISEN_ERR_INVALID, std::string("save_weights: cannot create ") + path);
+  std::vector<float> buf;
+  bool ok = true;
+  for (int64_t i = 0; i < g.num_params && ok; ++i) {
+    const HTensor& t = g.tensors[(size_t)i];
+    if (t.dtype == DT_I32) continue;
+    buf.resize((size_t)t.numel);
+    g.sync_to_cpu(i, buf.data());
+    ok = fwrite(buf.data(), 4, buf.size(), f) == buf.size();
+  }
+  ok = (fclose(f) == 0) && ok;
+  if (!ok) throw EisenException(EISEN_ERR_INVALID, "save_weights: short write");
+}
+
+// The inverse (the reference has none): fills the parameters of an identically built model from such a
+// file; in Bf16Mixed mode the bf16 copies are refreshed too.  The file size must match exactly.
+void load_weights(Graph& g, const char* path) {
+  FILE* f = fopen(path, "rb");
+  if (!f) throw EisenException(EISEN_ERR_INVALID, std::string("load_weights: cannot open ") + path);
+  fseek(f, 0, SEEK_END);
+  const long long bytes = ftell(f);
+  fseek(f, 0, SEEK_SET);
+  long long want = 0;
+  for (int64_t i = 0; i < g.num_params; ++i)
+    if (g.tensors[(size_t)i].dtype != DT_I32) want += g.tensors[(size_t)i].numel * 4;
+  if (bytes != want) {
+    fclose(f);
+    throw EisenException(EISEN_ERR_INVALID, "load_weights: the file does not hold exactly this model's parameters");
+  }
+  std::vector<float> buf;
+  for (int64_t i = 0; i < g.num_params; ++i) {
+    const HTensor& t = g.tensors[(size_t)i];
+    if (t.dtype == DT_I32) continue;
+    buf.resize((size_t)t.numel);
+    if (fread(buf.data(), 4, buf.size(), f) != buf.size()) {
+      fclose(f);
+      throw EisenException(EISEN_ERR_INVALID, "load_weights: short read");
+    }
+    g.load_tensor_data(i, buf.data(), t.numel);
+  }
+  fclose(f);
+  g.synchronize();
+}
+
 }  // namespace eisen

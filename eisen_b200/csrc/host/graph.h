@@ -187,6 +187,10 @@ class TransformerLM {
 void export_hf(Graph& g, const TransformerLM& lm, const char* safetensors_path, const char* config_path,
                int64_t max_position_embeddings);
 
+// examples/train_llm.rs:92-105: weights-only checkpoint (all parameter tensors in id order, f32), and its inverse
+void save_weights(Graph& g, const char* path);
+void load_weights(Graph& g, const char* path);
+
 // src/nn/optim.rs
 class AdamW {
  public:

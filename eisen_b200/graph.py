@@ -103,6 +103,13 @@ class Graph:
         return w.value, s.value, g.value, n.value
 
     # ---- graph state
+    def save_weights(self, path):
+        """All parameter tensors in id order, f32 (examples/train_llm.rs save_weights)."""
+        call("eisen_graph_save_weights", self._h, str(path).encode())
+
+    def load_weights(self, path):
+        call("eisen_graph_load_weights", self._h, str(path).encode())
+
     def set_no_grad(self, flag):
         call("eisen_graph_set_no_grad", self._h, 1 if flag else 0)
 

@@ -325,6 +325,11 @@ int eisen_lm_destroy(void* lm);
 int eisen_lm_set_fused(void* lm, int fused);   /* 0: the reference's op-by-op attention / MLP chain */
 int eisen_lm_forward(void* lm, void* g, long long x_ids, long long* logits_out);       /* Module::forward, :184-196 */
 int eisen_lm_params(void* lm, long long* ids_out, int* n_out);                         /* Module::params, :198-210 */
+/* Weights-only checkpoint (save_weights, examples/train_llm.rs:92-105): every parameter tensor in id
+ * order as f32 little-endian, the `eisen_model.bin` the reference's converter reads.  load_weights is
+ * its inverse for an identically built model (the reference has no loader). */
+int eisen_graph_save_weights(void* g, const char* path);
+int eisen_graph_load_weights(void* g, const char* path);
 /* Hugging Face export (examples/export_hf_pipeline.rs:200-300, src/tools/huggingface.rs:88-146): writes the
  * f32 master weights as LlamaForCausalLM tensors (Linear weights transposed to [out, in], q / k rows
  * permuted from interleaved-pair to rotate-half RoPE order) and, if config_path is not null, config.json. */

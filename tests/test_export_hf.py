@@ -104,3 +104,43 @@ def test_exported_model_reproduces_logits_in_transformers(tmp_path):
         ref = model(torch.from_numpy(ids.astype(np.int64))).logits.numpy()
     assert rel_l2(logits, ref) < 1e-4
     assert math.isfinite(float(ref.sum()))
+
+
+def test_weights_checkpoint_round_trip(tmp_path):
+    """save_weights writes the parameters back to back in id order (the reference's eisen_model.bin);
+    load_weights restores them bit for bit into a second, identically built model (bf16 copies included)."""
+    import torch
+    from eisen_b200.graph import BF16_MIXED, Graph, TransformerLM
+
+    def build(seed):
+        stream = torch.cuda.Stream()
+        g = Graph(BF16_MIXED, stream.cuda_stream)
+        lm = TransformerLM(g, 256, 128, 2, 1, 256, 2, False)
+        g.mark_params()
+        rng = np.random.default_rng(seed)
+        for p in lm.params():
+            shp = g.shape(p)
+            if len(shp) == 2:
+                g.load_tensor_data(p, (rng.standard_normal(int(np.prod(shp))) * 0.02).astype(np.float32))
+        return g, lm, stream
+
+    g1, lm1, _ = build(1)
+    path = tmp_path / "eisen_model.bin"
+    g1.save_weights(path)
+    flat = np.fromfile(path, dtype="<f4")
+    expect = np.concatenate([g1.data(p).reshape(-1) for p in sorted(lm1.params())])
+    assert np.array_equal(flat, expect)
+    g2, lm2, _ = build(2)
+    assert not np.array_equal(g2.data(lm2.params()[1 + 1]), g1.data(lm1.params()[1 + 1]))
+    g2.load_weights(path)
+    for a, b in zip(lm1.params(), lm2.params()):
+        assert np.array_equal(g1.data(a), g2.data(b))
+    ids = np.random.default_rng(3).integers(0, 256, (2, 128)).astype(np.int32)
+    outs = []
+    for g, lm in ((g1, lm1), (g2, lm2)):
+        g.set_no_grad(True)
+        outs.append(g.data(lm.forward(g.alloc_ids([2, 128], ids))))
+    assert np.array_equal(outs[0], outs[1])  # the bf16 shadows were refreshed as well
+    with pytest.raises(Exception):
+        open(tmp_path / "short.bin", "wb").write(b"1234")
+        g2.load_weights(tmp_path / "short.bin")
