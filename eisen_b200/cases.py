@@ -109,7 +109,7 @@ def main():
         t = torch.randint(0, V, (rows,), device=dev, dtype=torch.int32)
         loss, rl, lse = torch.zeros(1, device=dev), torch.empty(rows, device=dev), torch.empty(rows, device=dev)
         dl = torch.empty_like(lg)
-        mf = timed(lambda: eb.call("eisen_ce_fwd", s, P(lg), P(t), P(loss), P(rl), P(lse), rows, V, -1, 1.0 / rows, eb.BF16), a.iters)
+        mf = timed(lambda: eb.call("eisen_ce_fwd", s, P(lg), P(t), P(loss), P(rl), P(lse), rows, V, -1, 1.0 / rows, eb.BF16, None), a.iters)
         mb = timed(lambda: eb.call("eisen_ce_bwd", s, P(lg), P(t), P(lse), P(dl), None, rows, V, -1, 1.0 / rows, eb.BF16, 0), a.iters)
         out.update(fwd_ms=mf, fwd_gbs=(rows * V * 2 + rows * 8) / mf / 1e6, bwd_ms=mb, bwd_gbs=(rows * V * 4 + rows * 8) / mb / 1e6)
     elif a.case == "rmsnorm":

@@ -1244,12 +1244,12 @@ int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, vo
   dim3 grid((unsigned)Hq, (unsigned)B, (unsigned)(((S + 127) / 128 + 1) / 2));  // two query tiles per CTA
   cudaStream_t s = (cudaStream_t)stream;
   if (D == 64) {
-    static bool set64 = false;
-    if (!set64) { if (cudaFuncSetAttribute(attn_fwd64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd64Cfg::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute"); set64 = true; }
+    static bool set64[MAX_DEVICE_SLOTS] = {false};
+    if (!set64[device_slot()]) { if (cudaFuncSetAttribute(attn_fwd64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd64Cfg::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute"); set64[device_slot()] = true; }
     attn_fwd64_kernel<<<grid, Fwd64Cfg::THREADS, Fwd64Cfg::SMEM, s>>>(tq, tk, tv, p);
   } else {
-    static bool set128 = false;
-    if (!set128) { if (cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<128>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute"); set128 = true; }
+    static bool set128[MAX_DEVICE_SLOTS] = {false};
+    if (!set128[device_slot()]) { if (cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<128>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute"); set128[device_slot()] = true; }
     attn_fwd_kernel<128><<<grid, FwdCfg<128>::THREADS, FwdCfg<128>::SMEM, s>>>(tq, tk, tv, p);
   }
   return check_launch("attn_fwd");
@@ -1308,12 +1308,12 @@ int eisen_attn_bwd(void* stream, const void* q, const void* k, const void* v, co
   p.status = status;
   dim3 grid((unsigned)Hkv, (unsigned)B, (unsigned)((S + 127) / 128));
   if (D == 64) {
-    static bool set64 = false;
-    if (!set64) { if (cudaFuncSetAttribute(attn_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<64>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_bwd: smem attribute"); set64 = true; }
+    static bool set64[MAX_DEVICE_SLOTS] = {false};
+    if (!set64[device_slot()]) { if (cudaFuncSetAttribute(attn_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<64>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_bwd: smem attribute"); set64[device_slot()] = true; }
     attn_bwd_kernel<64><<<grid, BwdCfg<64>::THREADS, BwdCfg<64>::SMEM, s>>>(tq, tk, tv, tdo, tdq, p);
   } else {
-    static bool set128 = false;
-    if (!set128) { if (cudaFuncSetAttribute(attn_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<128>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_bwd: smem attribute"); set128 = true; }
+    static bool set128[MAX_DEVICE_SLOTS] = {false};
+    if (!set128[device_slot()]) { if (cudaFuncSetAttribute(attn_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<128>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_bwd: smem attribute"); set128[device_slot()] = true; }
     attn_bwd_kernel<128><<<grid, BwdCfg<128>::THREADS, BwdCfg<128>::SMEM, s>>>(tq, tk, tv, tdo, tdq, p);
   }
   rc = check_launch("attn_bwd");

@@ -257,7 +257,8 @@ inline EmbScratch emb_scratch(void* workspace, long long n_ids, long long vocab)
   e.cursor = e.offset + e.vocab_pad;
   e.slot = e.cursor + e.vocab_pad;
   e.perm = e.slot + n_ids;
-  e.active = reinterpret_cast<int2*>(e.perm + n_ids + (n_ids & 1));
+  // int offset 3 * vocab_pad + 4 + 2 * n_ids is even for every n_ids: int2 stores stay 8-byte aligned
+  e.active = reinterpret_cast<int2*>(e.perm + n_ids);
   return e;
 }
 

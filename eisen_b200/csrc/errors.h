@@ -14,4 +14,13 @@ int fail(int code, const char* msg);
 int check_launch(const char* what);  // also counts the launch
 void count_launch();
 
+// Index of the current device for per-device one-time set-up (kernel attributes and occupancy
+// are properties of a device, not of the process).  Devices beyond 63 share the last slot.
+inline int device_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) dev = 0;
+  return dev < 63 ? dev : 63;
+}
+constexpr int MAX_DEVICE_SLOTS = 64;
+
 }  // namespace eisen

@@ -17,6 +17,7 @@
 #include "ptx.cuh"
 #include "gemm_tc.h"
 #include "gemm_epilogue.cuh"
+#include "errors.h"
 
 #include <cuda.h>
 #include <cstdio>
@@ -322,7 +323,8 @@ static int num_sms() {
 int gemm_bf16_tc(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int K, const void* A,
                  long long lda, const void* B, long long ldb, void* C, long long ldc, const void* R, long long ldr,
                  int out_mode, int split_k, float alpha, int* status, const char** err) {
-  static bool attr_set = false;
+  static bool attr_set[MAX_DEVICE_SLOTS] = {false};
+  const int slot = device_slot();
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) {
     if (err) *err = "gemm_bf16_tc: operand rows must be 16-byte aligned (leading dimension % 8 == 0)";
@@ -357,10 +359,10 @@ int gemm_bf16_tc(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int K, c
   p.total_tiles = p.m_tiles * p.n_tiles * split_k;
   p.alpha = alpha;
   p.status = status;
-  if (!attr_set) {
+  if (!attr_set[slot]) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) { if (err) *err = cudaGetErrorString(e); return 3; }
-    attr_set = true;
+    attr_set[slot] = true;
   }
   int avail = num_sms() - g_reserved_sms;
   if (avail < 1) avail = 1;

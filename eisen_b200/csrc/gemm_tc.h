@@ -35,6 +35,8 @@ int gemm_bf16_pair_rope(cudaStream_t stream, int M, int N, int K, const void* A,
                         long long ldb, void* C, long long ldc, const float* table, int seq_len, int head_dim,
                         int* status, const char** err);
 int gemm_pair_auto_split_k(int M, int N, int K);
+// m-tiles per band of the paired kernel's tile order; 0 = chosen by the DRAM-traffic model
+void gemm_pair_set_band(int band);
 int gemm_num_sms();
 // SMs the persistent GEMM grids leave free (for a communication kernel that runs beside them)
 int gemm_reserved_sms();

@@ -10,10 +10,9 @@
 #include "ptx.cuh"
 #include "gemm_tc.h"
 #include "gemm_epilogue.cuh"
+#include "errors.h"
 
 #include <cuda.h>
-#include <cstdio>
-#include <cstdlib>
 
 namespace eisen {
 namespace {
@@ -407,7 +406,11 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 // DRAM traffic model of the tile order: A's rows of a band are read once if the band fits in L2
 // (else once per n-tile); B is read once per band unless all of it fits in L2.  Returns the band
 // height (in m-tiles) with the least modelled traffic.
+static int g_band_override = 0;
+void gemm_pair_set_band(int band) { g_band_override = band < 0 ? 0 : band; }
+
 static int pair_band(int M, int N, int K, int m_tiles, int n_tiles) {
+  if (g_band_override > 0) return g_band_override < m_tiles ? g_band_override : m_tiles;
   const double l2_fit = 75e6;  // bytes of one operand that stay resident next to the streams
   const double a_total = 2.0 * M * K, b_total = 2.0 * N * K;
   double best = -1.0;
@@ -426,11 +429,12 @@ static int pair_band(int M, int N, int K, int m_tiles, int n_tiles) {
 
 static int pair_launch(cudaStream_t stream, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmB2,
                        const PairParams& p, const char** err) {
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[MAX_DEVICE_SLOTS] = {false};
+  const int slot = device_slot();
+  if (!attr_set[slot]) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM);
     if (e != cudaSuccess) { if (err) *err = cudaGetErrorString(e); return 3; }
-    attr_set = true;
+    attr_set[slot] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * (gemm_num_sms() / 2), 1, 1);
@@ -447,17 +451,16 @@ static int pair_launch(cudaStream_t stream, const CUtensorMap& tmA, const CUtens
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   // persistent grid: as many clusters as can be resident at once (SM pairs must share a TPC)
-  static int max_clusters = 0;
-  if (!max_clusters) {
+  static int max_clusters[MAX_DEVICE_SLOTS] = {0};
+  if (!max_clusters[slot]) {
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_tc2_kernel, &cfg) != cudaSuccess || n <= 0) {
       cudaGetLastError();
       n = gemm_num_sms() / 2;
     }
-    max_clusters = n;
-    if (getenv("EISEN_DEBUG")) fprintf(stderr, "[eisen] paired-CTA GEMM: %d resident clusters on %d SMs\n", n, gemm_num_sms());
+    max_clusters[slot] = n;
   }
-  int avail = max_clusters - (gemm_reserved_sms() + 1) / 2;
+  int avail = max_clusters[slot] - (gemm_reserved_sms() + 1) / 2;
   if (avail < 1) avail = 1;
   const int clusters = p.total_tiles < avail ? p.total_tiles : avail;
   cfg.gridDim = dim3(2 * clusters, 1, 1);

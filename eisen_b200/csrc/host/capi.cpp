@@ -49,6 +49,13 @@ int eisen_graph_create(int precision, void* stream, void** out) {
 int eisen_graph_destroy(void* g) {
   return guarded([&] { delete static_cast<Graph*>(g); });
 }
+int eisen_graph_selftest_bounded_wait(void* g, long long budget_cycles) {
+  return guarded([&] {
+    Graph& gr = G(g);
+    int rc = eisen_selftest_bounded_wait(gr.stream, gr.status_dev, budget_cycles, nullptr);
+    if (rc) throw EisenException(rc, eisen_last_error());
+  });
+}
 int eisen_graph_alloc(void* g, const long long* shape, int ndim, const float* host_data, long long* id_out) {
   return guarded([&] { *id_out = G(g).alloc(shp(shape, ndim), host_data); });
 }

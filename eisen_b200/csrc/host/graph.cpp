@@ -262,6 +262,10 @@ void Graph::check_status() {
     cudaMemset(bad_id_dev, 0, 4);
     throw EisenException(EISEN_ERR_INVALID, "gather: a token id is outside [0, vocab)");
   }
+  if (h[17] != 0) {
+    cudaMemset(bad_id_dev + 1, 0, 4);
+    throw EisenException(EISEN_ERR_INVALID, "cross_entropy: a target is neither the ignore index nor inside [0, vocab)");
+  }
 }
 
 void Graph::restore_save_point(int64_t sp) {
@@ -568,17 +572,22 @@ int64_t Graph::matmul_rope(int64_t a, int64_t b, int64_t head_dim) {
   if (!no_grad) {
     tape.push_back({{a, b}, o, [this, a, b, o, B, S, m, n, k, head_dim, dt, tab]() {
       OUT_GRAD_OR_RETURN(o);
-      ck(eisen_rope(stream, to.grad, to.grad, tab, B, S, n, head_dim, dt, 1, 0), "matmul_rope.bwd(rope)");
+      // the rotated gradient goes to a pooled temporary: the output's own gradient stays as the
+      // consumer wrote it, so a tape that is walked again (the reference keeps its nodes) sees it unchanged
+      const size_t rot_bytes = (size_t)m * n * dsize(dt);
+      void* rot = pool_get(rot_bytes);
+      struct Release { Graph& g; void* p; size_t b; ~Release() { g.pool_put(p, b); } } release{*this, rot, rot_bytes};
+      ck(eisen_rope(stream, to.grad, rot, tab, B, S, n, head_dim, dt, 1, 0), "matmul_rope.bwd(rope)");
       HTensor& ga = tensors[a];
       HTensor& gb = tensors[b];
       if (!ga.constant) {
         ensure_grad(a);
-        gemm(*this, false, false, m, k, n, to.grad, operand(gb), ga.grad, ga.grad_dtype, ga.grad_init);
+        gemm(*this, false, false, m, k, n, rot, operand(gb), ga.grad, ga.grad_dtype, ga.grad_init);
         ga.grad_init = true;
       }
       if (!gb.constant) {
         ensure_grad(b);
-        gemm(*this, true, true, k, n, m, operand(ga), to.grad, gb.grad, gb.grad_dtype, gb.grad_init);
+        gemm(*this, true, true, k, n, m, operand(ga), rot, gb.grad, gb.grad_dtype, gb.grad_init);
         gb.grad_init = true;
       }
     }});
@@ -613,11 +622,13 @@ int64_t Graph::gate_up_swiglu(int64_t x, int64_t wg, int64_t wu) {
     prof_end();
     return h;
   }
-  skip_forward = true;
-  int64_t go = matmul(x, wg);
-  int64_t up = matmul(x, wu);
-  int64_t h = swiglu(go, up);
-  skip_forward = false;
+  int64_t go, up, h;
+  {
+    FlagGuard skip(skip_forward, true);
+    go = matmul(x, wg);
+    up = matmul(x, wu);
+    h = swiglu(go, up);
+  }
   prof_begin(0, flops);
   ck(eisen_gemm_bf16_swiglu(stream, m, n, k, operand(tensors[x]), k, operand(tensors[wg]), operand(tensors[wu]), n,
                             tensors[go].data, tensors[up].data, tensors[h].data, n, status_dev),
@@ -797,7 +808,8 @@ int64_t Graph::ce_device(int64_t logits, int64_t tid, float normalizer) {
   int64_t o = alloc_pooled_dtype({}, 0);
   tensors[lse].constant = tensors[row_loss].constant = true;
   ck(eisen_ce_fwd(stream, operand(tensors[logits]), (const int*)tensors[tid].data, (float*)tensors[o].data,
-                  (float*)tensors[row_loss].data, (float*)tensors[lse].data, rows, vocab, -1, normalizer, dt),
+                  (float*)tensors[row_loss].data, (float*)tensors[lse].data, rows, vocab, -1, normalizer, dt,
+                  bad_id_dev + 1),
      "cross_entropy");
   if (!no_grad) {
     tape.push_back({{logits}, o, [this, logits, tid, lse, o, rows, vocab, normalizer, dt]() {

@@ -150,6 +150,17 @@ class Graph {
   void free_tensor(HTensor& t);
 };
 
+// Sets a graph mode flag (no_grad, skip_forward) for a scope and restores the previous value on
+// every way out, so an exception inside a block forward cannot leave the graph in that mode.
+struct FlagGuard {
+  bool& flag;
+  bool saved;
+  FlagGuard(bool& f, bool value) : flag(f), saved(f) { flag = value; }
+  ~FlagGuard() { flag = saved; }
+  FlagGuard(const FlagGuard&) = delete;
+  FlagGuard& operator=(const FlagGuard&) = delete;
+};
+
 // ---------------------------------------------------------------------------------------
 // modules (src/nn/*.rs)
 // ---------------------------------------------------------------------------------------

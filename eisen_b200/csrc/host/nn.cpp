@@ -199,7 +199,7 @@ int64_t TransformerLM::block_forward(Graph& g, const BlockParams& b, int64_t x, 
   }
   // the down projection's output and the second residual sum feed only the next block: when a
   // checkpointed block is re-run for its backward pass nothing reads them
-  g.skip_forward = skip_dead_tail;
+  FlagGuard skip(g.skip_forward, skip_dead_tail);
   int64_t out;
   if (fused) {
     out = g.matmul_add(gd, b.down, r1);
@@ -208,7 +208,6 @@ int64_t TransformerLM::block_forward(Graph& g, const BlockParams& b, int64_t x, 
     int64_t f2 = linear_fwd(g, gd, b.down);
     out = g.add(r1, f2);
   }
-  g.skip_forward = false;
   return out;
 }
 
@@ -250,9 +249,11 @@ int64_t TransformerLM::train_micro_step_dev(Graph& g, int64_t x, int64_t target_
       // its result into a holder allocated before the save point
       int64_t holder = g.alloc_pooled(g.tensors[h].shape);
       const int64_t sp = g.mark_save_point();
-      g.no_grad = true;
-      int64_t r = block_forward(g, blocks[l], h);
-      g.no_grad = false;
+      int64_t r;
+      {
+        FlagGuard ng(g.no_grad, true);
+        r = block_forward(g, blocks[l], h);
+      }
       std::swap(g.tensors[holder].data, g.tensors[r].data);
       g.restore_save_point(sp);
       h = holder;

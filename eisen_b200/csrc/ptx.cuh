@@ -21,6 +21,7 @@ enum KernelFault : int {
   FAULT_WAIT_TMEM_FULL = 3,
   FAULT_WAIT_TMEM_EMPTY = 4,
   FAULT_WAIT_ATTN = 5,
+  FAULT_WAIT_SELFTEST = 99,  // the wait of eisen_selftest_bounded_wait, which is meant to run out
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -95,8 +96,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait.  `abort_flag` lives in shared memory and is shared by the CTA; once it is
 // raised every later wait returns at once, so a CTA pays the time limit at most once.
+// `budget` is the cycle limit of this wait; the kernels use the default.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+                                          int* status, int code, long long budget = EISEN_WAIT_CYCLES) {
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = clock64();
   uint32_t polls = 0;
@@ -106,7 +108,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     // scheduler with working warps, and every instruction of this loop takes an issue slot
     if ((++polls & 0x3Fu) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > EISEN_WAIT_CYCLES) {
+      if (clock64() - t0 > budget) {
         *abort_flag = 1;
         if (status) atomicCAS(status, 0, code);
         return false;

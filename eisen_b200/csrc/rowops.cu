@@ -446,13 +446,20 @@ __device__ __forceinline__ float exp_t(float x) {
 template <typename T>
 __global__ void __launch_bounds__(CE_THREADS)
 ce_fwd_kernel(const T* __restrict__ logits, const int* __restrict__ targets, float* __restrict__ row_loss,
-              float* __restrict__ lse, int V_, int ignore_index, float normalizer) {
+              float* __restrict__ lse, int V_, int ignore_index, float normalizer, int* __restrict__ bad_target_flag) {
   constexpr int V = VecOf<T>::N;
   __shared__ float sh[32];
   const long long row = blockIdx.x;
   const int t = targets[row];
-  if (t == ignore_index) {
-    if (threadIdx.x == 0) { row_loss[row] = 0.0f; lse[row] = 0.0f; }
+  // a target outside [0, V) that is not the ignore index would index past the row: the row is
+  // skipped like an ignored one and the caller's flag is raised
+  const bool out_of_range = t != ignore_index && (t < 0 || t >= V_);
+  if (t == ignore_index || out_of_range) {
+    if (threadIdx.x == 0) {
+      row_loss[row] = 0.0f;
+      lse[row] = 0.0f;
+      if (out_of_range && bad_target_flag) *bad_target_flag = 1;
+    }
     return;
   }
   const T* xr = logits + row * V_;
@@ -505,7 +512,7 @@ ce_bwd_kernel(const T* __restrict__ logits, const int* __restrict__ targets, con
   const T* xr = logits + row * V_;
   T* dr = dlogits + row * V_;
   const bool vec = (V_ % V) == 0 && aligned_row(xr) && aligned_row(dr);
-  if (t == ignore_index) {
+  if (t == ignore_index || t < 0 || t >= V_) {  // out-of-range targets: no gradient (the forward raised the flag)
     if (acc) return;
     if (vec) {
       float z[V];
@@ -631,13 +638,15 @@ int eisen_softmax_bwd(void* stream, const void* y, const void* dy, void* dx, lon
 }
 
 // row_loss [rows] and lse [rows] are outputs kept for the backward pass; *loss = sum(row_loss).
+// bad_target_flag (device int, may be null) is set to 1 when a target is neither ignore_index nor
+// inside [0, vocab); such rows are skipped like ignored ones, in the forward and in the backward.
 int eisen_ce_fwd(void* stream, const void* logits, const int* targets, float* loss, float* row_loss, float* lse,
-                 long long rows, long long vocab, int ignore_index, float normalizer, int dt) {
+                 long long rows, long long vocab, int ignore_index, float normalizer, int dt, int* bad_target_flag) {
   if (rows <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   EISEN_DISPATCH_DTYPE(dt, T, {
     ce_fwd_kernel<T><<<(unsigned)rows, CE_THREADS, 0, s>>>((const T*)logits, targets, row_loss, lse, (int)vocab,
-                                                          ignore_index, normalizer);
+                                                          ignore_index, normalizer, bad_target_flag);
     int rc = check_launch("ce_fwd");
     if (rc) return rc;
     ce_loss_reduce_kernel<<<1, 1024, 0, s>>>(row_loss, loss, rows);

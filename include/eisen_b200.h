@@ -47,6 +47,13 @@ const char* eisen_version(void);
 /* number of kernels this library has launched in the process so far */
 long long eisen_launch_count(void);
 
+/* Self-test of the bounded waits inside the pipelined kernels (no counterpart in the reference,
+ * whose kernels do not wait on one another): one warp waits budget_cycles on a barrier nobody
+ * signals, gives up, and writes fault code 99 into *status (device int) the way a stuck kernel
+ * would.  report5 (device int[5], may be null): first wait succeeded, second wait succeeded, abort
+ * flag, first wait used its budget, second wait returned at once. */
+int eisen_selftest_bounded_wait(void* stream, int* status, long long budget_cycles, int* report5);
+
 /* ------------------------------------------------------------------------------------------
  * Dense contractions
  * ------------------------------------------------------------------------------------------ */
@@ -92,6 +99,11 @@ int eisen_gemm_bf16_swiglu(void* stream, long long M, long long N, long long K, 
  * 2 = paired-CTA 256x256 tiles (tcgen05 cta_group::2, one cluster of two CTAs per tile).
  * Process-wide; meant for tests and measurements. */
 int eisen_gemm_set_mode(int mode);
+/* Tile order of the paired-CTA kernel: the 256-row tiles are walked in bands of `band` tiles (all
+ * column tiles of a band before the next band).  0 = chosen per problem from a DRAM-traffic model,
+ * which only leaves the plain column-major order for operands beyond the L2 size.  Process-wide;
+ * meant for tests and measurements. */
+int eisen_gemm_set_band(int band);
 /* The tensor-core GEMMs are persistent kernels, one CTA per SM.  A collective that should run
  * beside them (the gradient all-reduce of a data-parallel step, on its own stream) finds no SM
  * until they exit; n > 0 makes every later GEMM launch leave n SMs free.  No counterpart in the
@@ -153,9 +165,13 @@ int eisen_softmax_bwd(void* stream, const void* y, const void* dy, void* dx, lon
 /* Fused softmax-cross-entropy.  Row loss = -ln(softmax(x)[t] + 1e-8) * normalizer; rows whose
  * target equals ignore_index contribute nothing.  Outputs: *loss (device f32), row_loss [rows],
  * lse [rows].  Replaces cross_entropy_f32 / cross_entropy_masked_f32 (kernels/ops_f32.cu:580-598,
- * 5-30; src/graph/ops/reduction.rs:610, 823).  Targets are int32 (the reference passes f32). */
+ * 5-30; src/graph/ops/reduction.rs:610, 823).  Targets are int32 (the reference passes f32).
+ * bad_target_flag (device int, may be null) is set when a target is neither ignore_index nor inside
+ * [0, vocab); such rows are skipped like ignored ones here and in eisen_ce_bwd (the reference does
+ * not check and reads past the row). */
 int eisen_ce_fwd(void* stream, const void* logits, const int* targets, float* loss, float* row_loss, float* lse,
-                 long long rows, long long vocab, int ignore_index, float normalizer, int dtype);
+                 long long rows, long long vocab, int ignore_index, float normalizer, int dtype,
+                 int* bad_target_flag);
 /* dlogits (op)= (softmax(x) - onehot) * normalizer * (*grad_out); dlogits may alias logits.
  * Replaces cross_entropy_backward_f32 / cross_entropy_masked_backward_f32 (600-623, 32-64). */
 int eisen_ce_bwd(void* stream, const void* logits, const int* targets, const float* lse, void* dlogits,
@@ -285,6 +301,9 @@ int eisen_graph_reinterpret_shape(void* g, long long id, const long long* shape,
 int eisen_graph_zero_grad(void* g, long long id);
 int eisen_graph_backward(void* g, long long loss_id);                                  /* :670-796 */
 int eisen_graph_synchronize(void* g);   /* waits for the stream and raises recorded kernel faults */
+/* runs eisen_selftest_bounded_wait on the graph's stream against the graph's own fault word: the
+ * next eisen_graph_synchronize must return EISEN_ERR_KERNEL and clear the word */
+int eisen_graph_selftest_bounded_wait(void* g, long long budget_cycles);
 int eisen_graph_counts(void* g, long long* num_tensors, long long* tape_len, long long* num_params);
 /* out5: pool bytes in use, pool bytes cached, device bytes allocated, pool hits, pool misses */
 int eisen_graph_pool_stats(void* g, long long* out5);

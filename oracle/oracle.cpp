@@ -7,10 +7,11 @@
 //
 // Parity status: the Rust reference cannot be compiled in this environment (no cargo/rustc), so
 // the oracle is pinned against the literal input/output vectors of the reference's own tests
-// (transcribed in tests/golden/reference_vectors.json) and cross-checked against an independent
-// PyTorch-autograd model.  Whole-model gradients, GQA with repeats > 1, masked cross-entropy and
-// AdamW values are not pinned by any reference vector: for those, parity is pinned by restatement
-// only.
+// (transcribed in tests/golden/reference_vectors.json, checked by tests/test_oracle_golden.py).
+// Whole-model gradients, GQA with repeats > 1, masked cross-entropy, the tied head and AdamW
+// values are not pinned by any reference vector: for those, parity is pinned by restatement only,
+// cross-checked against an independent float64 PyTorch-autograd model of the same formulas
+// (tests/test_oracle_vs_torch.py: loss, logits, every parameter gradient, parameters after AdamW).
 //
 // Each function cites the reference file:line it follows (paths relative to the reference root).
 #include <cmath>

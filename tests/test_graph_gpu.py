@@ -360,3 +360,52 @@ def test_adamw_clip_and_fused_step():
         outs.append([g.data(p) for p in ps])
     for a, b in zip(*outs):
         assert rel_l2(a, b) < 1e-6
+
+
+def test_device_targets_out_of_range_raise_and_do_not_poison_the_graph():
+    # targets that arrive on the device (raw file tokens, FIM control tokens) are not seen by the
+    # host checks: the kernel skips such rows and the next synchronize reports them
+    cfg = dict(vocab=128, hidden=64, heads=2, kv=2, ffn=128, layers=1, batch=2, seq=16)
+    g = new_graph(FP32)
+    lm = TransformerLM(g, cfg["vocab"], cfg["hidden"], cfg["heads"], cfg["kv"], cfg["ffn"], cfg["layers"], False)
+    g.mark_params()
+    ids, tg = _tokens(cfg, 6)
+    bad = tg.reshape(-1).astype(np.int32).copy()
+    bad[3], bad[9] = cfg["vocab"], -2
+    x = g.alloc_ids([2, 16], ids.astype(np.int32))
+    t = g.alloc_ids([32], bad)
+    lm.train_micro_step_dev(x, t, 32)
+    with pytest.raises(eb.EisenError, match="target"):
+        g.synchronize()
+    g.clear_activations()
+    # the flag is cleared: a clean step passes
+    x = g.alloc_ids([2, 16], ids.astype(np.int32))
+    t = g.alloc_ids([32], tg.reshape(-1).astype(np.int32))
+    loss = lm.train_micro_step_dev(x, t, 32)
+    g.synchronize()
+    assert np.isfinite(g.data(loss)[0])
+
+
+def test_bounded_wait_gives_up_and_the_graph_reports_it():
+    """A wait on a barrier nobody signals runs out of its cycle budget, returns, and leaves its
+    code in the status word; eisen_graph_synchronize turns that into an error and clears it.
+    Nothing faults: the kernel ends by itself and the context stays usable."""
+    dev = torch.device("cuda:0")
+    st = torch.zeros(1, dtype=torch.int32, device=dev)
+    rep = torch.full((5,), -1, dtype=torch.int32, device=dev)
+    eb.call("eisen_selftest_bounded_wait", torch.cuda.current_stream().cuda_stream, st.data_ptr(), 200000, rep.data_ptr())
+    torch.cuda.synchronize()
+    assert st.item() == 99
+    # first wait failed, second failed, abort flag up, first used its budget, second returned at once
+    assert rep.cpu().tolist() == [0, 0, 1, 1, 1]
+    g = new_graph()
+    w = g.alloc([4, 4], np.eye(4))
+    g.mark_params()
+    call = getattr(eb.lib(), "eisen_graph_selftest_bounded_wait")
+    assert call(g._h, 200000) == 0
+    with pytest.raises(eb.EisenError, match="bounded wait"):
+        g.synchronize()
+    g.synchronize()  # cleared: the graph keeps working
+    x = g.alloc([2, 4], np.ones(8))
+    assert np.allclose(g.data(g.matmul(x, w)), 1.0)
+    assert eb.lib().eisen_selftest_bounded_wait(None, None, 200000, None) == 1  # null status rejected

@@ -86,6 +86,56 @@ def test_gemm_bf16_paired_cta_tiles(a_mn, b_mn, M, N, K):
     assert rel_l2(C32.cpu().numpy(), ref.numpy()) < 1e-5
 
 
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("band", [1, 2, 3])
+def test_gemm_bf16_paired_banded_tile_order(a_mn, b_mn, band):
+    """The banded tile order (used for operands beyond the L2 size) with a last band that is not
+    full: M = 1792 gives 7 row tiles, N = 640 a ragged last column tile; also with the k range split
+    5 and 9 ways into the f32 atomic output."""
+    M, N, K = 1792, 640, 1152
+    g = torch.Generator(device="cpu").manual_seed(band * 11 + a_mn * 2 + b_mn)
+    A = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    B = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    ref = A.float() @ B.float().t()
+    Ad = (A.t().contiguous() if a_mn else A).to(dev())
+    Bd = (B.t().contiguous() if b_mn else B).to(dev())
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+    C5 = torch.zeros((M, N), dtype=torch.float32, device=dev())
+    C9 = torch.zeros((M, N), dtype=torch.float32, device=dev())
+    st = status_word()
+    eb.call("eisen_gemm_set_mode", 2)
+    eb.call("eisen_gemm_set_band", band)
+    try:
+        eb.call("eisen_gemm_bf16", stream(), a_mn, b_mn, M, N, K, P(Ad), Ad.stride(0), P(Bd), Bd.stride(0), P(C), N, 0, 1, 1.0, P(st))
+        eb.call("eisen_gemm_bf16", stream(), a_mn, b_mn, M, N, K, P(Ad), Ad.stride(0), P(Bd), Bd.stride(0), P(C5), N, 4, 5, 1.0, P(st))
+        eb.call("eisen_gemm_bf16", stream(), a_mn, b_mn, M, N, K, P(Ad), Ad.stride(0), P(Bd), Bd.stride(0), P(C9), N, 4, 9, 1.0, P(st))
+        torch.cuda.synchronize()
+    finally:
+        eb.call("eisen_gemm_set_band", 0)
+        eb.call("eisen_gemm_set_mode", 0)
+    assert int(st.item()) == 0
+    assert torch.isfinite(C.float()).all()
+    assert rel_l2(C.float().cpu().numpy(), ref.numpy()) < 4e-3
+    assert rel_l2(C5.cpu().numpy(), ref.numpy()) < 1e-5
+    assert rel_l2(C9.cpu().numpy(), ref.numpy()) < 1e-5
+
+
+def test_gemm_bf16_auto_split_k_large():
+    """dW-shaped product (k = tokens) where the automatic split of the k range is above 4."""
+    M, N, K = 512, 512, 16384
+    g = torch.Generator(device="cpu").manual_seed(77)
+    A = torch.randn(K, M, generator=g).to(torch.bfloat16)
+    B = torch.randn(K, N, generator=g).to(torch.bfloat16)
+    ref = A.float().t() @ B.float()
+    Ad, Bd = A.to(dev()), B.to(dev())
+    C = torch.zeros((M, N), dtype=torch.float32, device=dev())
+    st = status_word()
+    eb.call("eisen_gemm_bf16", stream(), 1, 1, M, N, K, P(Ad), M, P(Bd), N, P(C), N, 4, 0, 1.0, P(st))
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert rel_l2(C.cpu().numpy(), ref.numpy()) < 1e-5
+
+
 @pytest.mark.parametrize("M,N,K,keep", [(256, 128, 64, True), (512, 384, 320, True), (768, 1024, 1088, False)])
 def test_gemm_bf16_swiglu_epilogue(M, N, K, keep):
     """Gate and up projections with silu(G) * U computed in the GEMM epilogue (one CTA of the pair
@@ -233,6 +283,9 @@ def _attn_reference(q, k, v, d_o, scale, causal):
     (1, 200, 2, 2, 64, True),     # ragged sequence (not a multiple of the 128 tile)
     (2, 512, 8, 2, 128, True),
     (1, 320, 2, 2, 128, False),
+    (1, 2048, 8, 2, 128, True),   # the isolated attention-backward benchmark's geometry (16 key tiles per row, 4 query heads per KV head) on one batch element
+    (1, 2048, 8, 2, 64, True),    # the 0.85B model's geometry
+    (2, 1024, 4, 1, 64, False),
 ])
 def test_flash_attention_fwd_bwd(B, S, Hq, Hkv, D, causal):
     g = torch.Generator(device="cpu").manual_seed(B * 1000 + S + Hq * 7 + D)
@@ -374,7 +427,7 @@ def test_cross_entropy_f32_vs_oracle(rows, vocab, masked):
     loss = torch.zeros(1, device=dev())
     row_loss = torch.empty(rows, device=dev())
     lse = torch.empty(rows, device=dev())
-    eb.call("eisen_ce_fwd", stream(), P(l), P(t), P(loss), P(row_loss), P(lse), rows, vocab, IGNORE_INDEX, norm, eb.F32)
+    eb.call("eisen_ce_fwd", stream(), P(l), P(t), P(loss), P(row_loss), P(lse), rows, vocab, IGNORE_INDEX, norm, eb.F32, None)
     assert abs(loss.item() - og.data(oloss)[0]) < 1e-5 * max(1.0, abs(og.data(oloss)[0]))
     dl = torch.full_like(l, float("nan"))
     one = torch.ones(1, device=dev())
@@ -401,10 +454,37 @@ def test_cross_entropy_bf16():
     loss = torch.zeros(1, device=dev())
     row_loss = torch.empty(rows, device=dev())
     lse = torch.empty(rows, device=dev())
-    eb.call("eisen_ce_fwd", stream(), P(ld), P(td), P(loss), P(row_loss), P(lse), rows, vocab, -1, 1.0 / rows, eb.BF16)
+    eb.call("eisen_ce_fwd", stream(), P(ld), P(td), P(loss), P(row_loss), P(lse), rows, vocab, -1, 1.0 / rows, eb.BF16, None)
     assert abs(loss.item() - ref.item()) < 1e-3
     eb.call("eisen_ce_bwd", stream(), P(ld), P(td), P(lse), P(ld), None, rows, vocab, -1, 1.0 / rows, eb.BF16, 0)
     assert rel_l2(ld.float().cpu().numpy(), lf.grad.numpy()) < 1e-2
+
+
+def test_cross_entropy_flags_out_of_range_targets():
+    # targets == vocab and -2 are neither valid nor the ignore index: the rows are skipped (loss and
+    # gradient zero, no read outside the row) and the flag is raised
+    rows, vocab = 6, 40
+    rng = np.random.default_rng(5)
+    L = rng.standard_normal((rows, vocab)).astype(np.float32)
+    T = np.array([3, vocab, -2, IGNORE_INDEX, 7, 2 ** 31 - 1], np.int32)
+    l, t = torch.from_numpy(L).to(dev()), torch.from_numpy(T).to(dev())
+    loss, row_loss, lse = torch.zeros(1, device=dev()), torch.empty(rows, device=dev()), torch.empty(rows, device=dev())
+    bad = torch.zeros(1, dtype=torch.int32, device=dev())
+    eb.call("eisen_ce_fwd", stream(), P(l), P(t), P(loss), P(row_loss), P(lse), rows, vocab, IGNORE_INDEX, 0.5, eb.F32, P(bad))
+    assert bad.item() == 1
+    rl = row_loss.cpu().numpy()
+    assert (rl[[1, 2, 3, 5]] == 0).all() and (rl[[0, 4]] > 0).all()
+    ref = sum(-np.log(np.exp(L[r, T[r]] - L[r].max()) / np.exp(L[r] - L[r].max()).sum() + 1e-8) * 0.5 for r in (0, 4))
+    assert abs(loss.item() - ref) < 1e-5
+    dl = torch.full_like(l, float("nan"))
+    eb.call("eisen_ce_bwd", stream(), P(l), P(t), P(lse), P(dl), None, rows, vocab, IGNORE_INDEX, 0.5, eb.F32, 0)
+    d = dl.cpu().numpy()
+    assert (d[[1, 2, 3, 5]] == 0).all() and np.isfinite(d).all()
+    # valid targets leave the flag alone
+    bad.zero_()
+    t2 = torch.from_numpy(np.array([0, vocab - 1, 5, IGNORE_INDEX, 1, 2], np.int32)).to(dev())
+    eb.call("eisen_ce_fwd", stream(), P(l), P(t2), P(loss), P(row_loss), P(lse), rows, vocab, IGNORE_INDEX, 0.5, eb.F32, P(bad))
+    assert bad.item() == 0
 
 
 def test_softmax_vs_oracle():
@@ -500,7 +580,8 @@ def test_add_broadcast_and_accumulate():
 
 
 # --------------------------------------------------------------------------------- embedding
-@pytest.mark.parametrize("n,vocab,dim,skew", [(4, 3, 2, False), (1000, 64, 48, False), (16384, 32000, 128, False), (4096, 17, 64, True)])
+@pytest.mark.parametrize("n,vocab,dim,skew", [(4, 3, 2, False), (1000, 64, 48, False), (16384, 32000, 128, False), (4096, 17, 64, True),
+                                               (1, 5, 8, False), (4097, 1000, 64, False), (777, 33, 24, True)])
 def test_embedding_gather_scatter_bit_exact(n, vocab, dim, skew):
     rng = np.random.default_rng(n + vocab)
     ids = rng.integers(0, vocab, n).astype(np.int32)

@@ -40,6 +40,12 @@ def test_static_matches_workspace_on_two_calls_in_a_row():
     _run_pair(2, 16384, 257, 64)
 
 
+@pytest.mark.parametrize("n", [1, 4097])
+def test_static_odd_number_of_ids(n):
+    # an odd id count once put the (id, first position) list on a 4-byte boundary
+    _run_pair(3, n, 1000, 64)
+
+
 def test_static_rejects_sizes_beyond_the_built_in_scratch():
     dev = torch.device("cuda:0")
     x = torch.zeros(8, device=dev)
