@@ -100,6 +100,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code, long long budget = EISEN_WAIT_CYCLES) {
   if (mbar_try_wait(bar, parity)) return true;
+  if (*abort_flag) return false;  // the CTA has given up already: do not wait again
   long long t0 = clock64();
   uint32_t polls = 0;
   while (true) {
