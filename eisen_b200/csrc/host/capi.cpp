@@ -176,6 +176,12 @@ int eisen_graph_cross_entropy(void* g, long long logits, const long long* target
 int eisen_graph_cross_entropy_masked(void* g, long long logits, const long long* targets, long long n, long long* out) {
   return guarded([&] { *out = G(g).cross_entropy_masked(logits, (const int64_t*)targets, n); });
 }
+int eisen_graph_lm_head_cross_entropy(void* g, long long h, long long w, long long target_ids, long long n_valid,
+                                      int trans_b, long long chunk_rows, long long* out) {
+  return guarded([&] {
+    *out = G(g).lm_head_cross_entropy(h, w, target_ids, n_valid > 0 ? 1.0f / (float)n_valid : 0.0f, trans_b != 0, chunk_rows);
+  });
+}
 int eisen_graph_rms_norm(void* g, long long x, long long w, float eps, long long* out) {
   return guarded([&] { *out = G(g).rms_norm(x, w, eps); });
 }
@@ -200,6 +206,14 @@ int eisen_lm_destroy(void* lm) {
 }
 int eisen_lm_set_fused(void* lm, int fused) {
   return guarded([&] { static_cast<TransformerLM*>(lm)->fused = fused != 0; });
+}
+int eisen_lm_set_head_fusion(void* lm, int fused, long long chunk_rows) {
+  return guarded([&] {
+    if (chunk_rows < 0) throw EisenException(EISEN_ERR_INVALID, "lm_set_head_fusion: chunk_rows must be >= 0");
+    TransformerLM* m = static_cast<TransformerLM*>(lm);
+    m->fused_head = fused != 0;
+    m->head_chunk_rows = chunk_rows;
+  });
 }
 int eisen_lm_forward(void* lm, void* g, long long x, long long* out) {
   return guarded([&] { *out = static_cast<TransformerLM*>(lm)->forward(G(g), x); });

@@ -312,6 +312,7 @@ void Graph::seed_grad_ones(int64_t id) {
     pool_put(tmp, (size_t)t.numel * 4);  // stream-ordered reuse
   }
   t.grad_init = true;
+  t.grad_is_ones = true;
 }
 
 // src/graph/mod.rs:670-796: seed with ones, walk the tape in reverse, keep the nodes
@@ -820,6 +821,71 @@ int64_t Graph::ce_device(int64_t logits, int64_t tid, float normalizer) {
                       (const float*)to.grad, rows, vocab, -1, normalizer, dt, gl.grad_init),
          "cross_entropy.bwd");
       gl.grad_init = true;
+    }});
+  }
+  return o;
+}
+
+// src/nn/transformer.rs:189-195 (`Linear` head, or `matmul_trans_b` with the tied table) followed by
+// src/graph/ops/reduction.rs:529-944 (cross_entropy[_masked]) and their backward kernels, as one op
+// that never holds more than a [chunk_rows, vocab] slab of logits.
+int64_t Graph::lm_head_cross_entropy(int64_t h, int64_t w, int64_t tid, float normalizer, bool trans_b,
+                                     int64_t chunk_rows) {
+  const HTensor& th = tensors.at(h);
+  const HTensor& tw = tensors.at(w);
+  if (tw.shape.size() != 2) invalid("lm_head_cross_entropy: the head weight must have rank 2");
+  const int64_t k = th.shape.back(), rows = th.numel / k;
+  const int64_t vocab = trans_b ? tw.shape[0] : tw.shape[1];
+  if ((trans_b ? tw.shape[1] : tw.shape[0]) != k) invalid("lm_head_cross_entropy: inner dims differ");
+  if (tensors.at(tid).dtype != DT_I32 || tensors[tid].numel != rows) invalid("lm_head_cross_entropy: one int32 target per row expected");
+  if (chunk_rows <= 0 || chunk_rows > rows) chunk_rows = rows;
+  const int dt = act_dtype();
+  const bool grads = !no_grad;
+  int64_t row_loss = alloc_pooled_dtype({rows}, 0);
+  int64_t o = alloc_pooled_dtype({}, 0);
+  tensors[row_loss].constant = true;
+  if (grads) {
+    ensure_grad(h);
+    if (!tensors[w].constant) ensure_grad(w);
+    if (tensors[h].grad_dtype != dt) invalid("lm_head_cross_entropy: the hidden-state gradient must have the activation dtype");
+  }
+  const size_t slab_bytes = (size_t)chunk_rows * vocab * dsize(dt);
+  void* slab = pool_get(slab_bytes);
+  struct Release { Graph& g; void* p; size_t b; ~Release() { g.pool_put(p, b); } } release{*this, slab, slab_bytes};
+  const int* targets = (const int*)tensors[tid].data;
+  float* rl = (float*)tensors[row_loss].data;
+  for (int64_t r0 = 0; r0 < rows; r0 += chunk_rows) {
+    const int64_t m = std::min(chunk_rows, rows - r0);
+    const char* hrows = (const char*)operand(tensors[h]) + (size_t)r0 * k * dsize(dt);
+    // logits of these rows: [m, vocab] = H[m, k] W[k, vocab]  (tied: W^T with W [vocab, k])
+    gemm(*this, false, !trans_b, m, vocab, k, hrows, operand(tensors[w]), slab, dt, false);
+    if (!grads) {
+      ck(eisen_ce_fwd(stream, slab, targets + r0, nullptr, rl + r0, nullptr, m, vocab, -1, normalizer, dt, bad_id_dev + 1),
+         "lm_head_cross_entropy(loss)");
+      continue;
+    }
+    ck(eisen_ce_fused(stream, slab, targets + r0, nullptr, rl + r0, nullptr, m, vocab, -1, normalizer, 1.0f, dt, bad_id_dev + 1),
+       "lm_head_cross_entropy(ce)");
+    HTensor& gh = tensors[h];
+    HTensor& gw = tensors[w];
+    // dH rows (op)= dlogits W^T
+    char* dh = (char*)gh.grad + (size_t)r0 * k * dsize(gh.grad_dtype);
+    gemm(*this, false, trans_b, m, k, vocab, slab, operand(gw), dh, gh.grad_dtype, gh.grad_init);
+    if (!gw.constant) {
+      // dW (op)= H^T dlogits  (tied: dW[vocab, k] (op)= dlogits^T H)
+      if (!trans_b) gemm(*this, true, true, k, vocab, m, hrows, slab, gw.grad, gw.grad_dtype, gw.grad_init);
+      else gemm(*this, true, true, vocab, k, m, slab, hrows, gw.grad, gw.grad_dtype, gw.grad_init);
+      gw.grad_init = true;
+    }
+  }
+  if (grads) tensors[h].grad_init = true;
+  ck(eisen_ce_loss_reduce(stream, rl, (float*)tensors[o].data, rows), "lm_head_cross_entropy(reduce)");
+  if (grads) {
+    tape.push_back({{h, w}, o, [this, o]() {
+      OUT_GRAD_OR_RETURN(o);
+      if (!to.grad_is_ones)
+        invalid("lm_head_cross_entropy: its gradients are formed in the forward with a loss gradient of 1; "
+                "the loss must be the tensor backward() starts from");
     }});
   }
   return o;

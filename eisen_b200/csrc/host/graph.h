@@ -35,6 +35,7 @@ struct HTensor {
   bool owns_data = false;  // free with cudaFree on destruction (non-pooled, non-arena)
   bool owns_grad = false;
   bool is_param = false;
+  bool grad_is_ones = false;  // the gradient was seeded with ones by backward() and not written since
   bool constant = false;   // no gradient is ever formed (masks, scale tensors, ids)
   std::string name;
 };
@@ -108,6 +109,14 @@ class Graph {
   const float* rope_table(int64_t seq_len, int64_t head_dim);
   int64_t ce_impl(int64_t logits, const int64_t* targets, int64_t n, bool masked, float normalizer);
   int64_t ce_device(int64_t logits, int64_t target_ids, float normalizer);  // targets already on the device
+  // LM head and cross-entropy as one op: loss = CE(h W, targets) with W [k, vocab] (or, trans_b,
+  // the tied table [vocab, k]).  The token rows are worked through in chunks of chunk_rows (0 =
+  // all at once): logits of a chunk -> loss and dlogits in place (one read, one write) -> dH rows
+  // and dW, so only a [chunk_rows, vocab] slab of logits ever exists.  The gradients are formed
+  // during the forward with the loss gradient taken as 1: the result must be the tensor that
+  // backward() starts from (checked there).  Under no_grad only the loss is computed.
+  int64_t lm_head_cross_entropy(int64_t h, int64_t w, int64_t target_ids, float normalizer, bool trans_b,
+                                int64_t chunk_rows);
 
   // event-based timing of the tensor-core kernels (class 0 GEMM, 1 attention fwd, 2 attention bwd)
   bool prof_on = false;
@@ -190,6 +199,10 @@ class TransformerLM {
   int64_t vocab, hidden, heads, kv_heads, ffn, layers;
   bool tie;
   bool fused = true;  // fused attention / SwiGLU ops (always the reference chain in Fp32 mode when false)
+  // train_micro_step: head projection and cross-entropy as one op (Graph::lm_head_cross_entropy)
+  // working through head_chunk_rows token rows at a time (0 = all rows at once)
+  bool fused_head = true;
+  int64_t head_chunk_rows = 0;
   int64_t emb, norm_f, head;
   std::vector<BlockParams> blocks;
 };

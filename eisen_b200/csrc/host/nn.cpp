@@ -263,10 +263,16 @@ int64_t TransformerLM::train_micro_step_dev(Graph& g, int64_t x, int64_t target_
   }
   block_tape[layers] = (int64_t)g.tape.size();
   int64_t hn = g.rms_norm(h, norm_f, 1e-5f);
-  int64_t logits = tie ? g.matmul_trans_b(hn, emb) : linear_fwd(g, hn, head);
-  g.reinterpret_shape(logits, {n_targets, vocab});
   // src/graph/ops/reduction.rs:724-737: mean over the valid rows; all rows masked -> loss 0, no gradient
-  int64_t loss = g.ce_device(logits, target_ids, n_valid > 0 ? 1.0f / (float)n_valid : 0.0f);
+  const float normalizer = n_valid > 0 ? 1.0f / (float)n_valid : 0.0f;
+  int64_t loss;
+  if (fused_head) {
+    loss = g.lm_head_cross_entropy(hn, tie ? emb : head, target_ids, normalizer, tie, head_chunk_rows);
+  } else {
+    int64_t logits = tie ? g.matmul_trans_b(hn, emb) : linear_fwd(g, hn, head);
+    g.reinterpret_shape(logits, {n_targets, vocab});
+    loss = g.ce_device(logits, target_ids, normalizer);
+  }
 
   // ---- backward
   g.seed_grad_ones(loss);

@@ -457,7 +457,7 @@ ce_fwd_kernel(const T* __restrict__ logits, const int* __restrict__ targets, flo
   if (t == ignore_index || out_of_range) {
     if (threadIdx.x == 0) {
       row_loss[row] = 0.0f;
-      lse[row] = 0.0f;
+      if (lse) lse[row] = 0.0f;
       if (out_of_range && bad_target_flag) *bad_target_flag = 1;
     }
     return;
@@ -488,7 +488,7 @@ ce_fwd_kernel(const T* __restrict__ logits, const int* __restrict__ targets, flo
   if (threadIdx.x == 0) {
     const float p = expf(to_f32(xr[t]) - gm) / s;
     row_loss[row] = -logf(p + 1e-8f) * normalizer;
-    lse[row] = gm + logf(s);
+    if (lse) lse[row] = gm + logf(s);
   }
 }
 
@@ -551,6 +551,98 @@ ce_bwd_kernel(const T* __restrict__ logits, const int* __restrict__ targets, con
       g *= scale;
       if (acc) g += to_f32(dr[c]);
       dr[c] = from_f32<T>(g);
+    }
+  }
+}
+
+// Cross-entropy forward and backward in one pass over a row: the row is read from global memory
+// once into shared memory, the online max / sum runs while it arrives, and dlogits =
+// (softmax - onehot) * scale is written back over the logits.  One read and one write of the row
+// instead of a forward read plus a backward read and write.  The loss gradient is a launch
+// argument (`scale` includes it), so the op that uses this kernel must be the last one before the
+// loss.  Rows that do not fit `smem_elems` are read from global memory a second time.
+template <typename T>
+__global__ void __launch_bounds__(CE_THREADS)
+ce_fused_kernel(T* __restrict__ logits, const int* __restrict__ targets, float* __restrict__ row_loss,
+                float* __restrict__ lse_out, int V_, int ignore_index, float normalizer, float scale, int smem_elems,
+                int* __restrict__ bad_target_flag) {
+  constexpr int V = VecOf<T>::N;
+  extern __shared__ uint4 ce_row_raw[];
+  T* srow = reinterpret_cast<T*>(ce_row_raw);
+  __shared__ float sh[32];
+  const long long row = blockIdx.x;
+  const int t = targets[row];
+  T* xr = logits + row * V_;
+  const bool vec = (V_ % V) == 0 && aligned_row(xr);
+  const bool out_of_range = t != ignore_index && (t < 0 || t >= V_);
+  if (t == ignore_index || out_of_range) {
+    if (vec) {
+      float z[V];
+#pragma unroll
+      for (int k = 0; k < V; ++k) z[k] = 0.0f;
+      for (int c = threadIdx.x * V; c < V_; c += CE_THREADS * V) st16(xr + c, z);
+    } else {
+      for (int c = threadIdx.x; c < V_; c += CE_THREADS) xr[c] = from_f32<T>(0.0f);
+    }
+    if (threadIdx.x == 0) {
+      row_loss[row] = 0.0f;
+      if (lse_out) lse_out[row] = 0.0f;
+      if (out_of_range && bad_target_flag) *bad_target_flag = 1;
+    }
+    return;
+  }
+  const bool staged = V_ <= smem_elems;
+  float m = -INFINITY, s = 0.0f;
+  if (vec) {
+    for (int c = threadIdx.x * V; c < V_; c += CE_THREADS * V) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
+      if (staged) *reinterpret_cast<uint4*>(srow + c) = raw;
+      float v[V];
+      unpack16(raw, v);
+      float cm = v[0];
+#pragma unroll
+      for (int k = 1; k < V; ++k) cm = fmaxf(cm, v[k]);
+      if (cm > m) { s *= exp_t<T>(m - cm); m = cm; }
+#pragma unroll
+      for (int k = 0; k < V; ++k) s += exp_t<T>(v[k] - m);
+    }
+  } else {
+    for (int c = threadIdx.x; c < V_; c += CE_THREADS) {
+      const T raw = xr[c];
+      if (staged) srow[c] = raw;
+      const float v = to_f32(raw);
+      if (v > m) { s *= expf(m - v); m = v; }
+      s += expf(v - m);
+    }
+  }
+  const float gm = block_max(m, sh);
+  s = (m == -INFINITY) ? 0.0f : s * expf(m - gm);
+  s = block_sum(s, sh);  // the barriers inside also publish the staged row to the whole CTA
+  const float l = gm + logf(s);
+  if (threadIdx.x == 0) {
+    const float xt = to_f32(staged ? srow[t] : xr[t]);
+    row_loss[row] = -logf(expf(xt - gm) / s + 1e-8f) * normalizer;
+    if (lse_out) lse_out[row] = l;
+  }
+  __syncthreads();  // the target logit is read before anyone overwrites it
+  const T* src = staged ? srow : xr;
+  if (vec) {
+    for (int c = threadIdx.x * V; c < V_; c += CE_THREADS * V) {
+      float v[V];
+      ld16(src + c, v);
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        float g = exp_t<T>(v[k] - l);
+        if (c + k == t) g -= 1.0f;
+        v[k] = g * scale;
+      }
+      st16(xr + c, v);
+    }
+  } else {
+    for (int c = threadIdx.x; c < V_; c += CE_THREADS) {
+      float g = expf(to_f32(src[c]) - l);
+      if (c == t) g -= 1.0f;
+      xr[c] = from_f32<T>(g * scale);
     }
   }
 }
@@ -648,10 +740,58 @@ int eisen_ce_fwd(void* stream, const void* logits, const int* targets, float* lo
     ce_fwd_kernel<T><<<(unsigned)rows, CE_THREADS, 0, s>>>((const T*)logits, targets, row_loss, lse, (int)vocab,
                                                           ignore_index, normalizer, bad_target_flag);
     int rc = check_launch("ce_fwd");
-    if (rc) return rc;
+    if (rc || !loss) return rc;
     ce_loss_reduce_kernel<<<1, 1024, 0, s>>>(row_loss, loss, rows);
     return check_launch("ce_loss_reduce");
   });
+}
+
+// Forward and backward of the cross-entropy in one launch, in place: on return `logits` holds
+// dlogits = (softmax - onehot) * normalizer * grad_scale (zero for ignored rows), *loss the summed
+// row losses, row_loss [rows] each row's share and lse (may be null) the log-sum-exp.
+int eisen_ce_fused(void* stream, void* logits, const int* targets, float* loss, float* row_loss, float* lse,
+                   long long rows, long long vocab, int ignore_index, float normalizer, float grad_scale, int dt,
+                   int* bad_target_flag) {
+  if (rows <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  static int max_smem[MAX_DEVICE_SLOTS] = {0};
+  static bool attr_f32[MAX_DEVICE_SLOTS] = {false}, attr_bf16[MAX_DEVICE_SLOTS] = {false};
+  const int slot = device_slot();
+  if (!max_smem[slot]) {
+    int dev = 0, v = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess || v <= 0) v = 48 * 1024;
+    max_smem[slot] = v;
+  }
+  EISEN_DISPATCH_DTYPE(dt, T, {
+    // three CTAs per SM when the row allows it (a 32000-entry bf16 row is 62.5 KB)
+    size_t row_bytes = ((size_t)vocab * sizeof(T) + 15) & ~size_t(15);
+    size_t smem = row_bytes;
+    const size_t cap = (size_t)max_smem[slot] - 1024;
+    if (smem > cap) smem = 0;  // row too long for shared memory: second pass reads global memory
+    bool& attr = sizeof(T) == 2 ? attr_bf16[slot] : attr_f32[slot];
+    if (!attr) {
+      if (cudaFuncSetAttribute(ce_fused_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cap) != cudaSuccess)
+        return fail(EISEN_ERR_CUDA, "ce_fused: shared-memory attribute");
+      attr = true;
+    }
+    ce_fused_kernel<T><<<(unsigned)rows, CE_THREADS, smem, s>>>((T*)logits, targets, row_loss, lse, (int)vocab, ignore_index,
+                                                                normalizer, normalizer * grad_scale,
+                                                                smem ? (int)(smem / sizeof(T)) : 0, bad_target_flag);
+    int rc = check_launch("ce_fused");
+    if (rc) return rc;
+    if (loss) {
+      ce_loss_reduce_kernel<<<1, 1024, 0, s>>>(row_loss, loss, rows);
+      return check_launch("ce_loss_reduce");
+    }
+    return 0;
+  });
+}
+
+int eisen_ce_loss_reduce(void* stream, const float* row_loss, float* loss, long long rows) {
+  if (rows <= 0) return 0;
+  ce_loss_reduce_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(row_loss, loss, rows);
+  return check_launch("ce_loss_reduce");
 }
 
 // dlogits may alias logits (in place).  grad_out: device scalar (the loss gradient) or null for 1.

@@ -223,6 +223,9 @@ class Graph:
     def flash_attention(self, q, k, v, scale, causal):
         return self._op("flash_attention", q, k, v, scale, 1 if causal else 0)
 
+    def lm_head_cross_entropy(self, h, w, target_ids, n_valid, trans_b=False, chunk_rows=0):
+        return self._op("lm_head_cross_entropy", h, w, target_ids, n_valid, 1 if trans_b else 0, chunk_rows)
+
     def attention(self, q, k, v, num_heads, num_kv_heads, causal=True):
         return self._op("attention", q, k, v, num_heads, num_kv_heads, 1 if causal else 0)
 
@@ -244,6 +247,10 @@ class TransformerLM:
 
     def set_fused(self, flag):
         call("eisen_lm_set_fused", self._h, 1 if flag else 0)
+
+    def set_head_fusion(self, fused=True, chunk_rows=0):
+        """Head projection + cross-entropy as one chunked op in train_micro_step (default on)."""
+        call("eisen_lm_set_head_fusion", self._h, 1 if fused else 0, chunk_rows)
 
     def forward(self, x_id):
         out = C.c_longlong()

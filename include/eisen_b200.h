@@ -178,6 +178,19 @@ int eisen_ce_bwd(void* stream, const void* logits, const int* targets, const flo
                  const float* grad_out, long long rows, long long vocab, int ignore_index, float normalizer,
                  int dtype, int accumulate);
 
+/* Cross-entropy forward and backward in one launch, in place: each row is read once (staged in
+ * shared memory), its loss is formed, and dlogits = (softmax - onehot) * normalizer * grad_scale
+ * is written over the logits (zero for ignored and out-of-range rows).  For an op that ends in
+ * the loss, where the loss gradient is known when the logits are: one read and one write of
+ * [rows, vocab] instead of the two reads and one write of eisen_ce_fwd + eisen_ce_bwd
+ * (cross_entropy_f32 + cross_entropy_backward_f32, kernels/ops_f32.cu:580-623).  loss and lse may
+ * be null (a caller that works through the rows in chunks adds row_loss itself). */
+int eisen_ce_fused(void* stream, void* logits, const int* targets, float* loss, float* row_loss, float* lse,
+                   long long rows, long long vocab, int ignore_index, float normalizer, float grad_scale, int dtype,
+                   int* bad_target_flag);
+/* *loss = sum(row_loss[0..rows)) in a fixed order (the second half of eisen_ce_fwd) */
+int eisen_ce_loss_reduce(void* stream, const float* row_loss, float* loss, long long rows);
+
 /* ------------------------------------------------------------------------------------------
  * Elementwise / layout ops
  * ------------------------------------------------------------------------------------------ */
@@ -326,6 +339,16 @@ int eisen_graph_bmm(void* g, long long a, long long b, int trans_b, long long* o
 int eisen_graph_softmax(void* g, long long a, long long* out);
 int eisen_graph_cross_entropy(void* g, long long logits, const long long* targets, long long n, long long* out);
 int eisen_graph_cross_entropy_masked(void* g, long long logits, const long long* targets, long long n, long long* out);
+/* LM head and cross-entropy as one op (src/nn/transformer.rs:189-195 followed by
+ * src/graph/ops/reduction.rs:529-944): loss = mean over the n_valid rows whose target is >= 0 of
+ * -ln(softmax(h W)[t] + 1e-8).  h [rows, k]; w [k, vocab], or with trans_b the tied table
+ * [vocab, k]; target_ids an id tensor of eisen_graph_alloc_ids (-1 = ignored).  The rows are worked
+ * through in chunks of chunk_rows (0 = all at once), so only a [chunk_rows, vocab] slab of logits
+ * exists at any time and each slab is read once and overwritten with its gradient.  The gradients
+ * of h and w are formed during this call with a loss gradient of 1: the result must be the tensor
+ * eisen_graph_backward is called on (checked there).  With no_grad set only the loss is computed. */
+int eisen_graph_lm_head_cross_entropy(void* g, long long h, long long w, long long target_ids, long long n_valid,
+                                      int trans_b, long long chunk_rows, long long* out);
 int eisen_graph_rms_norm(void* g, long long x, long long w, float eps, long long* out);
 int eisen_graph_rope(void* g, long long a, long long head_dim, long long* out);
 int eisen_graph_gather(void* g, long long weights, long long indices, long long* out);
@@ -342,6 +365,10 @@ int eisen_lm_create(void* g, long long vocab, long long hidden, long long heads,
                     long long layers, int tie_weights, void** out);
 int eisen_lm_destroy(void* lm);
 int eisen_lm_set_fused(void* lm, int fused);   /* 0: the reference's op-by-op attention / MLP chain */
+/* eisen_lm_train_micro_step[_dev]: fused != 0 (default) runs head projection and cross-entropy as
+ * eisen_graph_lm_head_cross_entropy in chunks of chunk_rows token rows (0 = all rows at once);
+ * fused == 0 runs matmul + cross_entropy_masked as the reference does. */
+int eisen_lm_set_head_fusion(void* lm, int fused, long long chunk_rows);
 int eisen_lm_forward(void* lm, void* g, long long x_ids, long long* logits_out);       /* Module::forward, :184-196 */
 int eisen_lm_params(void* lm, long long* ids_out, int* n_out);                         /* Module::params, :198-210 */
 /* Weights-only checkpoint (save_weights, examples/train_llm.rs:92-105): every parameter tensor in id

@@ -409,3 +409,122 @@ def test_bounded_wait_gives_up_and_the_graph_reports_it():
     x = g.alloc([2, 4], np.ones(8))
     assert np.allclose(g.data(g.matmul(x, w)), 1.0)
     assert eb.lib().eisen_selftest_bounded_wait(None, None, 200000, None) == 1  # null status rejected
+
+
+# ------------------------------------------------------------------ LM head x cross-entropy
+def _head_ce_oracle(H, W, T, tied, threads=1):
+    from oracle_binding import lib as olib
+    olib().orc_set_threads(threads)
+    og = OracleGraph()
+    oh = og.alloc(list(H.shape), H)
+    ow = og.alloc(list(W.shape), W)
+    ol = og.matmul_trans_b(oh, ow) if tied else og.matmul(oh, ow)
+    oloss = og.cross_entropy_masked(ol, T.tolist())
+    og.backward(oloss)
+    olib().orc_set_threads(1)
+    return float(og.data(oloss)[0]), og.grad(oh), og.grad(ow)
+
+
+@pytest.mark.parametrize("tied", [False, True])
+@pytest.mark.parametrize("chunk", [0, 7, 16])
+def test_lm_head_cross_entropy_f32_matches_oracle(tied, chunk):
+    rows, k, vocab = 37, 24, 101
+    rng = np.random.default_rng(rows + chunk + tied)
+    H = rng.standard_normal((rows, k)).astype(np.float32)
+    W = (rng.standard_normal((vocab, k) if tied else (k, vocab)) * 0.3).astype(np.float32)
+    T = rng.integers(0, vocab, rows)
+    T[rng.random(rows) < 0.2] = -1
+    T[0] = 5
+    oloss, odh, odw = _head_ce_oracle(H, W, T, tied)
+    g = new_graph(FP32)
+    w = g.alloc(list(W.shape), W)
+    g.mark_params()
+    h = g.alloc([rows, k], H)
+    t = g.alloc_ids([rows], T.astype(np.int32))
+    loss = g.lm_head_cross_entropy(h, w, t, int((T >= 0).sum()), trans_b=tied, chunk_rows=chunk)
+    g.backward(loss)
+    assert abs(g.data(loss)[0] - oloss) < 1e-5 * max(1.0, abs(oloss))
+    assert rel_l2(g.grad(h), odh) < 1e-4
+    assert rel_l2(g.grad(w), odw) < 1e-4
+    # a second micro-batch accumulates into the weight gradient (sum, not mean)
+    g.clear_activations()
+    h = g.alloc([rows, k], H)
+    t = g.alloc_ids([rows], T.astype(np.int32))
+    g.backward(g.lm_head_cross_entropy(h, w, t, int((T >= 0).sum()), trans_b=tied, chunk_rows=chunk))
+    assert rel_l2(g.grad(w), 2.0 * odw) < 1e-4
+
+
+def test_lm_head_cross_entropy_must_end_the_graph():
+    g = new_graph(FP32)
+    rng = np.random.default_rng(0)
+    w = g.alloc([8, 16], rng.standard_normal((8, 16)))
+    g.mark_params()
+    h = g.alloc([4, 8], rng.standard_normal((4, 8)))
+    t = g.alloc_ids([4], np.array([1, 2, 3, 4], np.int32))
+    loss = g.lm_head_cross_entropy(h, w, t, 4)
+    two = g.alloc([1], np.array([2.0]))
+    g.reinterpret_shape(loss, [1])
+    scaled = g.mul(loss, two)
+    with pytest.raises(eb.EisenError, match="backward"):
+        g.backward(scaled)  # the loss gradient would be 2, not the 1 the op assumed
+    # no_grad: loss only, no gradient written
+    g2 = new_graph(FP32)
+    w2 = g2.alloc([8, 16], rng.standard_normal((8, 16)))
+    g2.mark_params()
+    g2.set_no_grad(True)
+    h2 = g2.alloc([4, 8], rng.standard_normal((4, 8)))
+    t2 = g2.alloc_ids([4], np.array([1, 2, 3, 4], np.int32))
+    l2 = g2.lm_head_cross_entropy(h2, w2, t2, 4)
+    assert np.isfinite(g2.data(l2)[0]) and not g2.grad(w2).any()
+
+
+_BIG_HEAD = {}
+
+
+def _big_head_case():
+    """[256, 2048] x [2048, 32000], 5 % ignored rows; the oracle runs once (about 25 s on 8 cores)."""
+    if not _BIG_HEAD:
+        rows, k, vocab = 256, 2048, 32000
+        rng = np.random.default_rng(32000)
+        H = torch.from_numpy(rng.standard_normal((rows, k)).astype(np.float32)).to(torch.bfloat16).float().numpy()
+        W = torch.from_numpy((rng.standard_normal((k, vocab)) * 0.02).astype(np.float32)).to(torch.bfloat16).float().numpy()
+        T = rng.integers(0, vocab, rows)
+        T[rng.random(rows) < 0.05] = -1
+        _BIG_HEAD.update(H=H, W=W, T=T, oracle=_head_ce_oracle(H, W, T, False, threads=os.cpu_count() or 1))
+    return _BIG_HEAD
+
+
+@pytest.mark.parametrize("chunk", [0, 96])
+def test_lm_head_cross_entropy_bf16_vocab_32000(chunk):
+    """Hidden states x a [2048, 32000] head with 5 % ignored rows, against the oracle's matmul +
+    cross_entropy_masked on the same bf16-rounded inputs; chunk 96 leaves a ragged last chunk."""
+    c = _big_head_case()
+    H, W, T = c["H"], c["W"], c["T"]
+    oloss, odh, odw = c["oracle"]
+    rows, k = H.shape
+    vocab = W.shape[1]
+    g = new_graph(BF16_MIXED)
+    w = g.alloc([k, vocab], W)
+    hw = g.alloc([k, k], np.eye(k, dtype=np.float32))  # identity projection: gives h a producer on the tape
+    g.mark_params()
+    hp = g.alloc([rows, k], H)
+    t = g.alloc_ids([rows], T.astype(np.int32))
+    h = g.matmul(hp, hw)
+    loss = g.lm_head_cross_entropy(h, w, t, int((T >= 0).sum()), chunk_rows=chunk)
+    g.backward(loss)
+    assert abs(g.data(loss)[0] - oloss) < 1e-3 * max(1.0, abs(oloss))
+    assert rel_l2(g.grad(h), odh) < 2e-2
+    assert rel_l2(g.grad(hp), odh) < 2e-2  # and it flows on through the tape
+    assert rel_l2(g.grad(w), odw) < 2e-2
+    assert not np.asarray(g.grad(h)).reshape(rows, k)[T < 0].any()
+
+
+@pytest.mark.parametrize("fused_head,chunk", [(False, 0), (True, 96)])
+def test_bf16_step_head_paths_match_oracle(fused_head, chunk):
+    og, olm, g, lm = build_pair(CFG_BF16, BF16_MIXED, seed=7)
+    lm.set_head_fusion(fused_head, chunk)
+    ids, tg = _tokens(CFG_BF16, 7)
+    tg = tg.copy()
+    tg[:, ::9] = -1
+    res = run_step(og, olm, g, lm, CFG_BF16, ids, tg, masked=True, checkpoint=True, use_micro_step=True)
+    _check(res, 2e-2, 1e-3)

@@ -460,6 +460,35 @@ def test_cross_entropy_bf16():
     assert rel_l2(ld.float().cpu().numpy(), lf.grad.numpy()) < 1e-2
 
 
+@pytest.mark.parametrize("rows,vocab,dt", [(33, 1000, "f32"), (5, 7, "f32"), (64, 32000, "bf16"), (9, 70001, "f32"), (16, 4100, "bf16")])
+def test_cross_entropy_fused_matches_the_two_pass_kernels(rows, vocab, dt):
+    """eisen_ce_fused (row staged in shared memory, dlogits written over the logits) against
+    eisen_ce_fwd + eisen_ce_bwd; 70001 f32 entries do not fit shared memory (second pass from
+    global memory), 7 and 4100 are not multiples of the vector width of their type."""
+    rng = np.random.default_rng(rows + vocab)
+    tdt = torch.float32 if dt == "f32" else torch.bfloat16
+    edt = eb.F32 if dt == "f32" else eb.BF16
+    l0 = torch.from_numpy((2.0 * rng.standard_normal((rows, vocab))).astype(np.float32)).to(tdt).to(dev())
+    T = rng.integers(0, vocab, rows).astype(np.int32)
+    T[rng.random(rows) < 0.2] = IGNORE_INDEX
+    T[0] = vocab - 1
+    t = torch.from_numpy(T).to(dev())
+    norm, gs = 1.0 / max(1, int((T >= 0).sum())), 0.75
+    loss, row_loss, lse = torch.zeros(1, device=dev()), torch.empty(rows, device=dev()), torch.empty(rows, device=dev())
+    go = torch.full((1,), gs, device=dev())
+    eb.call("eisen_ce_fwd", stream(), P(l0), P(t), P(loss), P(row_loss), P(lse), rows, vocab, IGNORE_INDEX, norm, edt, None)
+    ref = torch.full_like(l0, float("nan"))
+    eb.call("eisen_ce_bwd", stream(), P(l0), P(t), P(lse), P(ref), P(go), rows, vocab, IGNORE_INDEX, norm, edt, 0)
+    l1 = l0.clone()
+    loss2, row_loss2, lse2 = torch.zeros(1, device=dev()), torch.empty(rows, device=dev()), torch.empty(rows, device=dev())
+    eb.call("eisen_ce_fused", stream(), P(l1), P(t), P(loss2), P(row_loss2), P(lse2), rows, vocab, IGNORE_INDEX, norm, gs, edt, None)
+    torch.cuda.synchronize()
+    assert abs(loss.item() - loss2.item()) < 1e-6 * max(1.0, abs(loss.item()))
+    assert np.abs(lse.cpu().numpy() - lse2.cpu().numpy()).max() < 1e-5
+    assert rel_l2(l1.float().cpu().numpy(), ref.float().cpu().numpy()) < (1e-6 if dt == "f32" else 4e-3)
+    assert (l1.float().cpu().numpy()[T == IGNORE_INDEX] == 0).all()
+
+
 def test_cross_entropy_flags_out_of_range_targets():
     # targets == vocab and -2 are neither valid nor the ignore index: the rows are skipped (loss and
     # gradient zero, no read outside the row) and the flag is raised
