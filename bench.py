@@ -256,14 +256,41 @@ class Runner:
         self.opt.config(3e-4, 0.9, 0.95, 1e-8, 0.1)
         self.n_params = sum(int(np.prod(g.shape(p))) for p in self.params)
         self.reducer = None
+        self.sharded = False
         if world > 1:
-            _, _, gptr, n_arena = g.param_arena()
+            import torch.distributed as dist
+            wptr, sptr, gptr, n_arena = g.param_arena()
             flat = edp.device_view(gptr, n_arena, dev)
             shapes = [g.shape(p) for p in sorted(self.params)]  # creation order == arena order
             offs, total = edp.param_offsets(shapes)
             assert total == n_arena, (total, n_arena)
             buckets = edp.plan_buckets(offs, cfg["layers"], total, min_bucket_elems=args.bucket_mb * (1 << 20) // 4)
-            self.reducer = edp.BucketedAllReduce(flat, buckets, comm_stream=torch.cuda.Stream(device=dev, priority=-1))
+            comm = torch.cuda.Stream(device=dev, priority=-1)
+            if args.backend == "abi":
+                # the library's own NCCL layer (eisen_dp_*); the 128-byte id travels over the process group
+                def exchange_id(raw):
+                    t = torch.zeros(128, dtype=torch.uint8, device=dev)
+                    if raw is not None:
+                        t.copy_(torch.frombuffer(bytearray(raw), dtype=torch.uint8))
+                    dist.broadcast(t, src=0)
+                    return bytes(t.cpu().numpy().tobytes())
+                backend = edp.NcclAbiBackend(rank, world, comm, exchange_id)
+            else:
+                backend = edp.TorchBackend(None, comm)
+            hs = None
+            if not args.no_handshake:
+                hs = edp.StepHandshake(dist.distributed_c10d._get_default_store(), rank, world, timeout_s=120.0)
+            if args.exchange == "zero1":
+                exact = [(o, o + s[0]) for o, s in zip(offs, shapes) if len(s) == 1]  # norm weights are read in f32
+                self.reducer = edp.ShardedExchange(flat, buckets, gather=edp.device_view(sptr, n_arena, dev, torch.bfloat16),
+                                                   flat_w=edp.device_view(wptr, n_arena, dev), exact_ranges=exact,
+                                                   backend=backend, handshake=hs)
+                from eisen_b200.graph import ShardedAdamW
+                self.opt = ShardedAdamW(g, self.params, 3e-4, self.reducer.pieces())
+                self.opt.config(3e-4, 0.9, 0.95, 1e-8, 0.1)
+                self.sharded = True
+            else:
+                self.reducer = edp.BucketedAllReduce(flat, buckets, backend=backend, handshake=hs)
             eb.call("eisen_gemm_reserve_sms", args.comm_sms)
         self.last_loss = None
         self.feeder = None
@@ -293,11 +320,17 @@ class Runner:
                 x, t = self.res_ids[a], self.res_tgt[a]
             cb = None
             if self.reducer is not None and a == accum - 1:
-                cb = lambda layer: self.reducer.on_block_done(layer, self.compute)  # noqa: E731
+                if self.sharded:
+                    cb = lambda layer: self.reducer.on_block_done(layer, self.compute, optimizer=self.opt)  # noqa: E731
+                else:
+                    cb = lambda layer: self.reducer.on_block_done(layer, self.compute)  # noqa: E731
             loss = self.lm.train_micro_step_dev(x, t, n_valid, checkpoint=self.checkpoint, after_block=cb)
             if e2e:
                 self.last_loss = float(g.data(loss)[0])  # D2H read of the step's loss
             g.clear_activations()
+        if self.sharded:
+            self.reducer.finish_and_step(self.opt, self.clip, self.compute)
+            return
         if self.reducer is not None:
             self.reducer.finish(self.compute)
         self.opt.step_fused(self.clip, 1.0 / self.world)
@@ -478,7 +511,8 @@ def run_ours(args, cfg, name):
                        "micro_batch_per_gpu": B, "grad_accum": accum, "parallelism": "dp%d" % world,
                        "gradient_checkpointing": "per-block" if r.checkpoint else "off", "grad_clip_norm": r.clip,
                        "l2": "inputs larger than L2 (weights, activations and logits far exceed 126 MB)",
-                       "bucket_mb": args.bucket_mb if world > 1 else None},
+                       "bucket_mb": args.bucket_mb if world > 1 else None,
+                       "exchange": (args.exchange + " via " + ("eisen_dp_* (NCCL)" if args.backend == "abi" else "torch.distributed")) if world > 1 else None},
             "mfu": {"model_flops_per_token": fpt,
                     "of_nominal_2250_tflops": tps / world * fpt / (NOMINAL_BF16_TFLOPS * 1e12),
                     "of_measured_burst": tps / world * fpt / (float(peaks.get("bf16_tflops", 1590.0)) * 1e12),
@@ -534,6 +568,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cases", action="store_true", help="skip the other benchmark configurations (N = 1 only)")
     ap.add_argument("--bucket-mb", type=int, default=256)
+    ap.add_argument("--exchange", default="allreduce", choices=["allreduce", "zero1"],
+                    help="N > 1: all-reduce of gradient buckets with replicated AdamW, or reduce-scatter + sharded AdamW + all-gather")
+    ap.add_argument("--backend", default="abi", choices=["abi", "torch"],
+                    help="N > 1: collectives through the library's eisen_dp_* C ABI over NCCL, or through torch.distributed")
+    ap.add_argument("--no-handshake", action="store_true", help="N > 1: skip the per-step host-side step handshake")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
     if args.impl == "reference":

@@ -301,6 +301,29 @@ int eisen_optim_step(void* opt) {
 int eisen_optim_step_fused(void* opt, float max_norm, float grad_scale) {
   return guarded([&] { static_cast<AdamW*>(opt)->step_fused(max_norm, grad_scale); });
 }
+int eisen_optim_create_sharded(void* g, const long long* params, int n, float lr, const long long* piece_lo,
+                               const long long* piece_hi, int n_pieces, void** out) {
+  return guarded([&] {
+    std::vector<std::pair<int64_t, int64_t>> pieces;
+    for (int i = 0; i < n_pieces; ++i) pieces.emplace_back(piece_lo[i], piece_hi[i]);
+    *out = new AdamW(G(g), std::vector<int64_t>(params, params + n), lr, std::move(pieces));
+  });
+}
+int eisen_optim_begin_step(void* opt) {
+  return guarded([&] { static_cast<AdamW*>(opt)->begin_step(); });
+}
+int eisen_optim_sumsq_piece(void* opt, int piece, int accumulate, void* stream) {
+  return guarded([&] {
+    AdamW* o = static_cast<AdamW*>(opt);
+    o->sumsq_piece((size_t)piece, accumulate != 0, stream ? (cudaStream_t)stream : o->g.stream);
+  });
+}
+int eisen_optim_step_piece(void* opt, int piece, float max_norm, float grad_scale) {
+  return guarded([&] { static_cast<AdamW*>(opt)->step_piece((size_t)piece, max_norm, grad_scale); });
+}
+int eisen_optim_sumsq_ptr(void* opt, void** out) {
+  return guarded([&] { *out = static_cast<AdamW*>(opt)->sumsq_dev; });
+}
 int eisen_optim_is_flat(void* opt, int* flat) {
   return guarded([&] { *flat = static_cast<AdamW*>(opt)->flat ? 1 : 0; });
 }

@@ -10,6 +10,7 @@
 #include <stdexcept>
 #include <string>
 #include <unordered_map>
+#include <utility>
 #include <vector>
 
 namespace eisen {
@@ -226,6 +227,14 @@ class AdamW {
   // no host synchronisation: norm and clip coefficient stay on the device; grad_scale folds the
   // data-parallel 1/world factor
   void step_fused(float max_norm, float grad_scale);
+  // Sharded state (ZeRO-1): this rank keeps moments only for `pieces` (element ranges of the flat
+  // arena) and updates only those; the other ranks' pieces arrive through the exchange.
+  AdamW(Graph& g, std::vector<int64_t> params, float lr, std::vector<std::pair<int64_t, int64_t>> pieces);
+  void begin_step() { t += 1; }                       // once per optimizer step, before step_piece
+  void sumsq_piece(size_t i, bool accumulate, cudaStream_t s);   // sumsq_dev (op)= sum g^2 over piece i
+  void step_piece(size_t i, float max_norm, float grad_scale);   // clip coefficient from sumsq_dev when max_norm > 0
+  std::vector<std::pair<int64_t, int64_t>> pieces;
+  std::vector<int64_t> piece_state_off;  // offset of each piece's moments in m / v
   float lr, beta1 = 0.9f, beta2 = 0.999f, eps = 1e-8f, weight_decay = 0.01f;
   int64_t t = 0;
   Graph& g;

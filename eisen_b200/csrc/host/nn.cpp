@@ -339,6 +339,56 @@ AdamW::AdamW(Graph& g_, std::vector<int64_t> params_, float lr_) : lr(lr_), g(g_
   g.device_bytes_allocated += 2 * bytes;
 }
 
+AdamW::AdamW(Graph& g_, std::vector<int64_t> params_, float lr_, std::vector<std::pair<int64_t, int64_t>> pieces_)
+    : lr(lr_), g(g_), params(std::move(params_)), pieces(std::move(pieces_)) {
+  if (!g.arena_w) throw EisenException(EISEN_ERR_INVALID, "sharded AdamW needs the flat parameter arena");
+  for (int64_t p : params) {
+    const HTensor& t = g.tensors.at(p);
+    if (!(t.data >= (void*)g.arena_w && t.data < (void*)(g.arena_w + g.arena_cap)))
+      throw EisenException(EISEN_ERR_INVALID, "sharded AdamW: every parameter must live in the arena");
+  }
+  flat = true;
+  total = g.arena_used;
+  int64_t mine = 0;
+  for (auto& pc : pieces) {
+    if (pc.first < 0 || pc.second < pc.first || pc.second > total || (pc.first % 4) || (pc.second % 4))
+      throw EisenException(EISEN_ERR_INVALID, "sharded AdamW: a piece must be a 4-element-aligned range inside the arena");
+    piece_state_off.push_back(mine);
+    mine += pc.second - pc.first;
+  }
+  const size_t bytes = (size_t)std::max<int64_t>(mine, 64) * 4;
+  cuck(cudaMalloc(&m, bytes), "cudaMalloc(adam m)");
+  cuck(cudaMalloc(&v, bytes), "cudaMalloc(adam v)");
+  cuck(cudaMemsetAsync(m, 0, bytes, g.stream), "memset");
+  cuck(cudaMemsetAsync(v, 0, bytes, g.stream), "memset");
+  cuck(cudaMalloc(&sumsq_dev, 64), "cudaMalloc(sumsq)");
+  cuck(cudaMemsetAsync(sumsq_dev, 0, 64, g.stream), "memset");
+  cuck(cudaMalloc(&sumsq_ws, (size_t)eisen_sumsq_workspace_bytes(std::max<int64_t>(total, 64))), "cudaMalloc(sumsq ws)");
+  g.device_bytes_allocated += 2 * bytes;
+}
+
+void AdamW::sumsq_piece(size_t i, bool accumulate, cudaStream_t s) {
+  const auto& pc = pieces.at(i);
+  if (pc.second == pc.first) {
+    if (!accumulate) cuck(cudaMemsetAsync(sumsq_dev, 0, 8, s), "memset(sumsq)");
+    return;
+  }
+  ck(eisen_sumsq(s, g.arena_g + pc.first, pc.second - pc.first, sumsq_ws, sumsq_dev, accumulate ? 1 : 0), "sumsq(piece)");
+}
+
+void AdamW::step_piece(size_t i, float max_norm, float grad_scale) {
+  const auto& pc = pieces.at(i);
+  if (pc.second == pc.first) return;
+  float p1 = 1.0f, p2 = 1.0f;
+  for (int64_t k = 0; k < t; ++k) { p1 *= beta1; p2 *= beta2; }
+  const float bc1 = 1.0f / (1.0f - p1), bc2 = 1.0f / (1.0f - p2);
+  const int64_t so = piece_state_off[i];
+  void* shadow = g.arena_shadow ? (void*)((uint16_t*)g.arena_shadow + pc.first) : nullptr;
+  ck(eisen_adamw_step(g.stream, g.arena_w + pc.first, shadow, g.arena_g + pc.first, m + so, v + so, pc.second - pc.first, lr,
+                      beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale, max_norm > 0.0f ? sumsq_dev : nullptr, max_norm),
+     "adamw_step(piece)");
+}
+
 AdamW::~AdamW() {
   cudaStreamSynchronize(g.stream);
   cudaFree(m);

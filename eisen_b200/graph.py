@@ -321,3 +321,40 @@ class AdamW:
         f = C.c_int()
         call("eisen_optim_is_flat", self._h, C.byref(f))
         return bool(f.value)
+
+
+class ShardedAdamW(AdamW):
+    """AdamW that keeps moments for, and updates, only `pieces` (element ranges of the flat
+    parameter arena): the optimizer of a ZeRO-1 data-parallel step (eisen_b200.dp.ShardedExchange)."""
+
+    def __init__(self, g, params, lr, pieces):
+        self.g = g
+        self._h = C.c_void_p()
+        lo, hi = _ll([a for a, _ in pieces]), _ll([b for _, b in pieces])
+        call("eisen_optim_create_sharded", g._h, _ll(params), len(params), lr, lo, hi, len(pieces), C.byref(self._h))
+        self.pieces = list(pieces)
+        self._sumsq = None
+
+    @property
+    def sumsq(self):
+        """One-element float64 device tensor: the squared gradient norm the clip uses."""
+        if self._sumsq is None:
+            import torch
+
+            p = C.c_void_p()
+            call("eisen_optim_sumsq_ptr", self._h, C.byref(p))
+
+            class _V:
+                __cuda_array_interface__ = {"shape": (1,), "typestr": "<f8", "data": (p.value, False), "version": 2}
+
+            self._sumsq = torch.as_tensor(_V(), device=torch.device("cuda", torch.cuda.current_device()))
+        return self._sumsq
+
+    def begin_step(self):
+        call("eisen_optim_begin_step", self._h)
+
+    def sumsq_piece(self, i, accumulate, stream=None):
+        call("eisen_optim_sumsq_piece", self._h, i, 1 if accumulate else 0, stream.cuda_stream if stream is not None else None)
+
+    def step_piece(self, i, max_norm=0.0, grad_scale=1.0):
+        call("eisen_optim_step_piece", self._h, i, max_norm, grad_scale)

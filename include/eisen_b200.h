@@ -32,6 +32,8 @@ extern "C" {
 
 #define EISEN_F32 0
 #define EISEN_BF16 1
+#define EISEN_F64 3 /* eisen_dp_* only: the squared gradient norm */
+#define EISEN_I64 4 /* eisen_dp_* only: counters of a host-side handshake */
 
 #define EISEN_OK 0
 #define EISEN_ERR_INVALID 1
@@ -39,6 +41,8 @@ extern "C" {
 #define EISEN_ERR_KERNEL 3
 #define EISEN_ERR_OOM 4
 #define EISEN_ERR_LIMIT 5
+#define EISEN_ERR_COMM 6    /* NCCL missing, reported an error, or the communicator was aborted */
+#define EISEN_ERR_TIMEOUT 7 /* eisen_dp_wait ran past its deadline (the communicator is aborted) */
 
 /* message of the last failed call on this thread ("" if none) */
 const char* eisen_last_error(void);
@@ -410,6 +414,55 @@ int eisen_optim_step(void* opt);
 /* clip (max_norm > 0) and step without a host round trip; the gradient is read as g * grad_scale */
 int eisen_optim_step_fused(void* opt, float max_norm, float grad_scale);
 int eisen_optim_is_flat(void* opt, int* flat);
+/* Sharded optimizer state (ZeRO-1; no counterpart in the reference): this rank keeps AdamW moments
+ * only for n_pieces element ranges [piece_lo[i], piece_hi[i]) of the flat parameter arena and
+ * updates only those (master weights and their bf16 copies); the exchange layer brings in the
+ * other ranks' updated ranges.  One optimizer step is: eisen_optim_begin_step (t += 1), for the
+ * clip eisen_optim_sumsq_piece over all pieces (accumulating into the 8-byte device value at
+ * eisen_optim_sumsq_ptr, which the caller sums across ranks), then eisen_optim_step_piece for
+ * every piece (the update of src/nn/optim.rs:334-481 on that range, clip coefficient
+ * min(1, max_norm / (sqrt(sumsq) * grad_scale + 1e-6)) when max_norm > 0). */
+int eisen_optim_create_sharded(void* g, const long long* params, int n, float lr, const long long* piece_lo,
+                               const long long* piece_hi, int n_pieces, void** out);
+int eisen_optim_begin_step(void* opt);
+int eisen_optim_sumsq_piece(void* opt, int piece, int accumulate, void* stream); /* stream null: the graph's */
+int eisen_optim_step_piece(void* opt, int piece, float max_norm, float grad_scale);
+int eisen_optim_sumsq_ptr(void* opt, void** out);
+
+/* ------------------------------------------------------------------------------------------
+ * Data-parallel exchange (no counterpart in the reference, which is single-GPU): one process per
+ * GPU, every rank runs the whole step on its own micro-batch, the flat f32 gradient buffer
+ * (eisen_graph_param_arena) is summed across ranks bucket by bucket while the backward pass is
+ * still running (eisen_lm_train_micro_step's after_block callback says when a bucket is final).
+ * Thin checked layer over NCCL, bound at run time (dlopen of libnccl.so.2).  All collectives are
+ * in place or caller-buffered, asynchronous on the given stream, and allocate nothing.
+ *   unique id: rank 0 calls eisen_dp_unique_id and hands the 128 bytes to every rank by its own
+ *   means (a file, a socket, an environment variable); every rank then calls eisen_dp_init with
+ *   its CUDA device current.
+ * Failure handling: no call waits without a limit.  eisen_dp_poll_error reads the communicator's
+ * asynchronous error state (ncclCommGetAsyncError); eisen_dp_wait polls the stream and that state
+ * until the stream is idle or deadline_ms have passed, and on an error or a missed deadline aborts
+ * the communicator (ncclCommAbort) and returns EISEN_ERR_COMM / EISEN_ERR_TIMEOUT; afterwards
+ * every call on the handle fails with EISEN_ERR_COMM until it is destroyed and a new one made.
+ * ------------------------------------------------------------------------------------------ */
+int eisen_dp_available(void);                      /* 1 if NCCL could be bound in this process */
+int eisen_dp_unique_id(void* out128);
+int eisen_dp_init(int rank, int world, const void* unique_id128, void** comm_out);
+int eisen_dp_destroy(void* comm);
+/* rank, world and the number of collectives enqueued on this handle so far (each may be null) */
+int eisen_dp_rank_world(void* comm, int* rank, int* world, long long* launched);
+/* ptr[0..n) = sum over ranks, in place */
+int eisen_dp_allreduce_bucket(void* comm, void* ptr, long long n, int dtype, void* stream);
+/* recv[0..recv_n) = sum over ranks of their send[rank * recv_n ..]; recv may be send + rank * recv_n */
+int eisen_dp_reduce_scatter(void* comm, const void* send, void* recv, long long recv_n, int dtype, void* stream);
+/* recv[r * send_n ..] = rank r's send[0..send_n); send may be recv + rank * send_n */
+int eisen_dp_all_gather(void* comm, const void* send, void* recv, long long send_n, int dtype, void* stream);
+int eisen_dp_broadcast(void* comm, void* ptr, long long n, int dtype, int root, void* stream);
+int eisen_dp_group_begin(void);                    /* ncclGroupStart: the calls up to group_end become one launch */
+int eisen_dp_group_end(void);
+int eisen_dp_poll_error(void* comm);
+int eisen_dp_wait(void* comm, void* stream, long long deadline_ms);
+int eisen_dp_abort(void* comm);
 
 /* ------------------------------------------------------------------------------------------
  * Input side: pre-tokenised u16 token files (BinaryDataLoader, src/data/dataloader.rs:89-214, with
