@@ -218,6 +218,13 @@ int eisen_lm_set_head_fusion(void* lm, int fused, long long chunk_rows) {
 int eisen_lm_forward(void* lm, void* g, long long x, long long* out) {
   return guarded([&] { *out = static_cast<TransformerLM*>(lm)->forward(G(g), x); });
 }
+int eisen_lm_generate(void* lm, void* g, const int* prompt, long long n_prompt, long long max_new_tokens, long long max_context,
+                      int kv_cache, int* out_tokens, float* last_logits) {
+  return guarded([&] {
+    if (!prompt || !out_tokens) throw EisenException(EISEN_ERR_INVALID, "lm_generate: null prompt or output");
+    static_cast<TransformerLM*>(lm)->generate(G(g), prompt, n_prompt, max_new_tokens, max_context, kv_cache != 0, out_tokens, last_logits);
+  });
+}
 int eisen_graph_save_weights(void* g, const char* path) {
   return guarded([&] {
     if (!path) throw EisenException(EISEN_ERR_INVALID, "save_weights: null path");
@@ -300,6 +307,12 @@ int eisen_optim_step(void* opt) {
 }
 int eisen_optim_step_fused(void* opt, float max_norm, float grad_scale) {
   return guarded([&] { static_cast<AdamW*>(opt)->step_fused(max_norm, grad_scale); });
+}
+int eisen_optim_save_state(void* opt, const char* path) {
+  return guarded([&] { static_cast<AdamW*>(opt)->save_state(path); });
+}
+int eisen_optim_load_state(void* opt, const char* path) {
+  return guarded([&] { static_cast<AdamW*>(opt)->load_state(path); });
 }
 int eisen_optim_create_sharded(void* g, const long long* params, int n, float lr, const long long* piece_lo,
                                const long long* piece_hi, int n_pieces, void** out) {

@@ -185,8 +185,21 @@ class TransformerLM {
                 int64_t layers, bool tie);
   int64_t forward(Graph& g, int64_t x_ids);                       // :184-196
   // skip_dead_tail: leave out the forward kernels whose results no backward node reads
-  int64_t block_forward(Graph& g, const BlockParams& b, int64_t x, bool skip_dead_tail = false);  // :32-49
-  int64_t gqa_forward(Graph& g, const BlockParams& b, int64_t x, bool causal, int64_t residual = -1);  // attention.rs:289-388
+  // kv_out (optional): receives the ids of the rotated key projection and of the value projection,
+  // [B, S, kv_heads * head_dim] each (what a KV cache keeps)
+  int64_t block_forward(Graph& g, const BlockParams& b, int64_t x, bool skip_dead_tail = false,
+                        std::pair<int64_t, int64_t>* kv_out = nullptr);  // :32-49
+  int64_t gqa_forward(Graph& g, const BlockParams& b, int64_t x, bool causal, int64_t residual = -1,
+                      std::pair<int64_t, int64_t>* kv_out = nullptr);  // attention.rs:289-388
+  // Greedy generation as in examples/train_llm.rs:560-584 (argmax of the last position's logits,
+  // context window max_context).  kv_cache = false runs that loop as the reference does, the
+  // whole context through forward() for every token.  kv_cache = true keeps every layer's rotated
+  // keys and values: the prompt is run once, each further token is one row through the
+  // projections plus eisen_attn_decode over the cache (README.md:94 lists this as future work);
+  // it needs n_prompt + max_new <= max_context, because a sliding window re-positions every token.
+  // out_tokens receives max_new tokens; last_logits (may be null) the [vocab] logits behind the last one.
+  void generate(Graph& g, const int32_t* prompt, int64_t n_prompt, int64_t max_new, int64_t max_context, bool kv_cache,
+                int32_t* out_tokens, float* last_logits);
   std::vector<int64_t> params() const;                            // :198-210
   // One micro-step: forward, loss (masked cross-entropy over [B*S] targets), backward.
   // checkpoint = true keeps only block inputs in the forward and re-runs each block under a
@@ -233,6 +246,11 @@ class AdamW {
   void begin_step() { t += 1; }                       // once per optimizer step, before step_piece
   void sumsq_piece(size_t i, bool accumulate, cudaStream_t s);   // sumsq_dev (op)= sum g^2 over piece i
   void step_piece(size_t i, float max_norm, float grad_scale);   // clip coefficient from sumsq_dev when max_norm > 0
+  // Optimizer state of a checkpoint (the reference saves weights only and lists this as future
+  // work, README.md:88): step count t, hyper-parameters and the moments of the ranges this object owns.
+  void save_state(const char* path);
+  void load_state(const char* path);
+  int64_t state_elems() const;
   std::vector<std::pair<int64_t, int64_t>> pieces;
   std::vector<int64_t> piece_state_off;  // offset of each piece's moments in m / v
   float lr, beta1 = 0.9f, beta2 = 0.999f, eps = 1e-8f, weight_decay = 0.01f;

@@ -2,7 +2,9 @@
 // GroupedQueryAttention (src/nn/attention.rs:251-404), Linear / Embedding / RMSNorm
 // (src/nn/linear.rs, embedding.rs, rmsnorm.rs) and AdamW (src/nn/optim.rs), on the Graph of
 // graph.h.  Parameter ids, creation order and params() order follow the reference.
+#include <algorithm>
 #include <cmath>
+#include <cstdio>
 #include <cstring>
 
 #include "../../../include/eisen_b200.h"
@@ -113,7 +115,8 @@ std::vector<int64_t> TransformerLM::params() const {
   return p;
 }
 
-int64_t TransformerLM::gqa_forward(Graph& g, const BlockParams& b, int64_t x, bool causal, int64_t residual) {
+int64_t TransformerLM::gqa_forward(Graph& g, const BlockParams& b, int64_t x, bool causal, int64_t residual,
+                                   std::pair<int64_t, int64_t>* kv_out) {
   const std::vector<int64_t> xs = g.tensors.at(x).shape;
   if (xs.size() != 3) throw EisenException(EISEN_ERR_INVALID, "GQA requires [Batch, Seq, Dim]");
   const int64_t B = xs[0], S = xs[1], hd = hidden / heads;
@@ -127,6 +130,7 @@ int64_t TransformerLM::gqa_forward(Graph& g, const BlockParams& b, int64_t x, bo
     kr = g.rope(k, hd);
   }
   int64_t v = linear_fwd(g, x, b.v);
+  if (kv_out) *kv_out = {kr, v};
   int64_t ctx2;
   if (fused) {
     ctx2 = g.attention(qr, kr, v, heads, kv_heads, causal);
@@ -178,13 +182,14 @@ int64_t TransformerLM::gqa_forward(Graph& g, const BlockParams& b, int64_t x, bo
   return linear_fwd(g, ctx2, b.o);
 }
 
-int64_t TransformerLM::block_forward(Graph& g, const BlockParams& b, int64_t x, bool skip_dead_tail) {
+int64_t TransformerLM::block_forward(Graph& g, const BlockParams& b, int64_t x, bool skip_dead_tail,
+                                     std::pair<int64_t, int64_t>* kv_out) {
   int64_t n1 = g.rms_norm(x, b.norm1, 1e-5f);
   int64_t r1;
   if (fused) {
-    r1 = gqa_forward(g, b, n1, true, x);
+    r1 = gqa_forward(g, b, n1, true, x, kv_out);
   } else {
-    int64_t at = gqa_forward(g, b, n1, true, -1);
+    int64_t at = gqa_forward(g, b, n1, true, -1, kv_out);
     r1 = g.add(x, at);
   }
   int64_t n2 = g.rms_norm(r1, b.norm2, 1e-5f);
@@ -309,6 +314,126 @@ int64_t TransformerLM::train_micro_step_dev(Graph& g, int64_t x, int64_t target_
   return loss;
 }
 
+// ------------------------------------------------------------------------------------- generation
+namespace {
+// logits row `row` of a [rows, vocab] tensor as f32 on the host
+void read_logits_row(Graph& g, int64_t logits, int64_t row, int64_t vocab, std::vector<float>& out) {
+  const HTensor& t = g.tensors.at(logits);
+  out.resize((size_t)vocab);
+  if (t.dtype == 0) {
+    cuck(cudaMemcpyAsync(out.data(), (const float*)t.data + row * vocab, (size_t)vocab * 4, cudaMemcpyDeviceToHost, g.stream), "D2H(logits)");
+  } else {
+    float* tmp = static_cast<float*>(g.pool_get((size_t)vocab * 4));
+    ck(eisen_cast(g.stream, (const uint16_t*)t.data + row * vocab, 1, tmp, 0, vocab), "cast(logits)");
+    cuck(cudaMemcpyAsync(out.data(), tmp, (size_t)vocab * 4, cudaMemcpyDeviceToHost, g.stream), "D2H(logits)");
+    g.pool_put(tmp, (size_t)vocab * 4);
+  }
+  cuck(cudaStreamSynchronize(g.stream), "sync");
+  g.check_status();
+}
+// examples/train_llm.rs:573-578: max_by over partial_cmp keeps the LAST of equal maxima
+int32_t argmax_last(const std::vector<float>& v) {
+  size_t best = 0;
+  for (size_t i = 1; i < v.size(); ++i)
+    if (v[i] >= v[best]) best = i;
+  return (int32_t)best;
+}
+}  // namespace
+
+void TransformerLM::generate(Graph& g, const int32_t* prompt, int64_t n_prompt, int64_t max_new, int64_t max_context,
+                             bool kv_cache, int32_t* out_tokens, float* last_logits) {
+  if (n_prompt <= 0 || max_new <= 0 || max_context <= 0) throw EisenException(EISEN_ERR_INVALID, "generate: needs a prompt, max_new > 0 and max_context > 0");
+  for (int64_t i = 0; i < n_prompt; ++i)
+    if (prompt[i] < 0 || prompt[i] >= vocab) throw EisenException(EISEN_ERR_INVALID, "generate: prompt token outside [0, vocab)");
+  FlagGuard ng(g.no_grad, true);
+  std::vector<float> row;
+  if (!kv_cache) {
+    // the reference's loop: the whole (windowed) context goes through forward() for every token
+    std::vector<int32_t> tokens(prompt, prompt + n_prompt);
+    for (int64_t i = 0; i < max_new; ++i) {
+      const int64_t start = std::max<int64_t>(0, (int64_t)tokens.size() - max_context);
+      const int64_t csl = (int64_t)tokens.size() - start;
+      int64_t x = g.alloc_ids({1, csl}, tokens.data() + start, false);
+      int64_t logits = forward(g, x);
+      read_logits_row(g, logits, csl - 1, vocab, row);
+      const int32_t next = argmax_last(row);
+      out_tokens[i] = next;
+      tokens.push_back(next);
+      g.clear_activations();
+    }
+    if (last_logits) std::memcpy(last_logits, row.data(), (size_t)vocab * 4);
+    return;
+  }
+  const int64_t max_len = n_prompt + max_new;
+  if (max_len > max_context)
+    throw EisenException(EISEN_ERR_LIMIT, "generate: with a KV cache prompt + new tokens must fit max_context "
+                                          "(a sliding window re-positions every cached key); use kv_cache = 0");
+  const int64_t hd = hidden / heads, kvd = kv_heads * hd;
+  const int dt = g.act_dtype();
+  const size_t esz = dt == 1 ? 2 : 4;
+  const size_t cache_bytes = (size_t)max_len * kvd * esz;
+  std::vector<char*> kc((size_t)layers), vc((size_t)layers);
+  struct Release {
+    Graph& g; std::vector<char*>&a, &b; size_t bytes;
+    ~Release() { for (char* p : a) g.pool_put(p, bytes); for (char* p : b) g.pool_put(p, bytes); }
+  } release{g, kc, vc, cache_bytes};
+  for (int64_t l = 0; l < layers; ++l) { kc[l] = nullptr; vc[l] = nullptr; }
+  for (int64_t l = 0; l < layers; ++l) {
+    kc[l] = static_cast<char*>(g.pool_get(cache_bytes));
+    vc[l] = static_cast<char*>(g.pool_get(cache_bytes));
+  }
+  const float* tab = g.rope_table(max_len, hd);
+  const float scale = 1.0f / std::sqrt((float)hd);
+  // ---- the prompt in one pass; every layer's rotated keys and its values go to the cache
+  {
+    int64_t x = g.alloc_ids({1, n_prompt}, prompt, false);
+    int64_t h = g.gather(emb, x);
+    for (int64_t l = 0; l < layers; ++l) {
+      std::pair<int64_t, int64_t> kv;
+      h = block_forward(g, blocks[l], h, false, &kv);
+      cuck(cudaMemcpyAsync(kc[l], g.tensors[kv.first].data, (size_t)n_prompt * kvd * esz, cudaMemcpyDeviceToDevice, g.stream), "copy(k cache)");
+      cuck(cudaMemcpyAsync(vc[l], g.tensors[kv.second].data, (size_t)n_prompt * kvd * esz, cudaMemcpyDeviceToDevice, g.stream), "copy(v cache)");
+    }
+    h = g.rms_norm(h, norm_f, 1e-5f);
+    int64_t logits = tie ? g.matmul_trans_b(h, emb) : linear_fwd(g, h, head);
+    read_logits_row(g, logits, n_prompt - 1, vocab, row);
+    out_tokens[0] = argmax_last(row);
+    g.clear_activations();
+  }
+  // ---- one row per further token
+  for (int64_t i = 1; i < max_new; ++i) {
+    const int64_t pos = n_prompt + i - 1;  // position of the token fed in
+    const int32_t tok = out_tokens[i - 1];
+    int64_t x = g.alloc_ids({1, 1}, &tok, false);
+    int64_t h = g.gather(emb, x);
+    const float* tab_pos = tab + pos * (hd / 2) * 2;
+    for (int64_t l = 0; l < layers; ++l) {
+      const BlockParams& b = blocks[l];
+      int64_t n1 = g.rms_norm(h, b.norm1, 1e-5f);
+      int64_t q = g.matmul(n1, b.q), k = g.matmul(n1, b.k), v = g.matmul(n1, b.v);
+      int64_t qr = g.alloc_pooled({1, hidden});
+      ck(eisen_rope(g.stream, g.tensors[q].data, g.tensors[qr].data, tab_pos, 1, 1, hidden, hd, dt, 0, 0), "rope(q)");
+      ck(eisen_rope(g.stream, g.tensors[k].data, kc[l] + (size_t)pos * kvd * esz, tab_pos, 1, 1, kvd, hd, dt, 0, 0), "rope(k)");
+      ck(eisen_cast(g.stream, g.tensors[v].data, dt, vc[l] + (size_t)pos * kvd * esz, dt, kvd), "copy(v)");
+      int64_t ctx = g.alloc_pooled({1, hidden});
+      ck(eisen_attn_decode(g.stream, g.tensors[qr].data, kc[l], vc[l], g.tensors[ctx].data, pos + 1, heads, kv_heads, hd, kvd,
+                           scale, dt),
+         "attn_decode");
+      int64_t r1 = g.add(h, g.matmul(ctx, b.o));
+      int64_t n2 = g.rms_norm(r1, b.norm2, 1e-5f);
+      int64_t go = g.matmul(n2, b.gate), up = g.matmul(n2, b.up);
+      int64_t gd = fused ? g.swiglu(go, up) : g.mul(g.silu(go), up);
+      h = g.add(r1, g.matmul(gd, b.down));
+    }
+    h = g.rms_norm(h, norm_f, 1e-5f);
+    int64_t logits = tie ? g.matmul_trans_b(h, emb) : g.matmul(h, head);
+    read_logits_row(g, logits, 0, vocab, row);
+    out_tokens[i] = argmax_last(row);
+    g.clear_activations();
+  }
+  if (last_logits) std::memcpy(last_logits, row.data(), (size_t)vocab * 4);
+}
+
 // ------------------------------------------------------------------------------------- AdamW
 AdamW::AdamW(Graph& g_, std::vector<int64_t> params_, float lr_) : lr(lr_), g(g_), params(std::move(params_)) {
   // one launch over the arena when the parameter list is exactly the arena's content
@@ -387,6 +512,78 @@ void AdamW::step_piece(size_t i, float max_norm, float grad_scale) {
   ck(eisen_adamw_step(g.stream, g.arena_w + pc.first, shadow, g.arena_g + pc.first, m + so, v + so, pc.second - pc.first, lr,
                       beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale, max_norm > 0.0f ? sumsq_dev : nullptr, max_norm),
      "adamw_step(piece)");
+}
+
+int64_t AdamW::state_elems() const {
+  if (pieces.empty()) return total;
+  int64_t n = 0;
+  for (const auto& pc : pieces) n += pc.second - pc.first;
+  return n;
+}
+
+namespace {
+struct OptStateHeader {
+  char magic[8];          // "EISENOPT"
+  int64_t version;        // 1
+  int64_t t;              // optimizer steps taken
+  int64_t elems;          // f32 elements of m (and of v) that follow
+  int64_t total;          // elements the optimizer covers across all ranks
+  int64_t n_pieces;       // 0: one contiguous state; else the [lo, hi) ranges follow the header
+  float lr, beta1, beta2, eps, weight_decay;
+  float reserved[3];
+};
+}  // namespace
+
+void AdamW::save_state(const char* path) {
+  cuck(cudaStreamSynchronize(g.stream), "sync");
+  FILE* f = fopen(path, "wb");
+  if (!f) throw EisenException(EISEN_ERR_INVALID, std::string("optimizer save_state: cannot create ") + path);
+  OptStateHeader h{};
+  std::memcpy(h.magic, "EISENOPT", 8);
+  h.version = 1; h.t = t; h.elems = state_elems(); h.total = total; h.n_pieces = (int64_t)pieces.size();
+  h.lr = lr; h.beta1 = beta1; h.beta2 = beta2; h.eps = eps; h.weight_decay = weight_decay;
+  bool ok = fwrite(&h, sizeof(h), 1, f) == 1;
+  for (const auto& pc : pieces) {
+    const int64_t r[2] = {pc.first, pc.second};
+    ok = ok && fwrite(r, sizeof(r), 1, f) == 1;
+  }
+  std::vector<float> buf((size_t)std::min<int64_t>(h.elems, 1 << 24));
+  for (float* src : {m, v}) {
+    for (int64_t off = 0; off < h.elems && ok; off += (int64_t)buf.size()) {
+      const size_t n = (size_t)std::min<int64_t>((int64_t)buf.size(), h.elems - off);
+      cuck(cudaMemcpy(buf.data(), src + off, n * 4, cudaMemcpyDeviceToHost), "D2H(optimizer state)");
+      ok = fwrite(buf.data(), 4, n, f) == n;
+    }
+  }
+  ok = (fclose(f) == 0) && ok;
+  if (!ok) throw EisenException(EISEN_ERR_INVALID, "optimizer save_state: short write");
+}
+
+void AdamW::load_state(const char* path) {
+  FILE* f = fopen(path, "rb");
+  if (!f) throw EisenException(EISEN_ERR_INVALID, std::string("optimizer load_state: cannot open ") + path);
+  struct Closer { FILE* f; ~Closer() { fclose(f); } } closer{f};
+  OptStateHeader h{};
+  if (fread(&h, sizeof(h), 1, f) != 1 || std::memcmp(h.magic, "EISENOPT", 8) != 0 || h.version != 1)
+    throw EisenException(EISEN_ERR_INVALID, "optimizer load_state: not an optimizer state file of this library");
+  if (h.elems != state_elems() || h.total != total || h.n_pieces != (int64_t)pieces.size())
+    throw EisenException(EISEN_ERR_INVALID, "optimizer load_state: the file was written for another model or another sharding");
+  for (const auto& pc : pieces) {
+    int64_t r[2];
+    if (fread(r, sizeof(r), 1, f) != 1 || r[0] != pc.first || r[1] != pc.second)
+      throw EisenException(EISEN_ERR_INVALID, "optimizer load_state: the file's ranges differ from this rank's");
+  }
+  cuck(cudaStreamSynchronize(g.stream), "sync");
+  std::vector<float> buf((size_t)std::min<int64_t>(h.elems, 1 << 24));
+  for (float* dst : {m, v}) {
+    for (int64_t off = 0; off < h.elems; off += (int64_t)buf.size()) {
+      const size_t n = (size_t)std::min<int64_t>((int64_t)buf.size(), h.elems - off);
+      if (fread(buf.data(), 4, n, f) != n) throw EisenException(EISEN_ERR_INVALID, "optimizer load_state: short read");
+      cuck(cudaMemcpy(dst + off, buf.data(), n * 4, cudaMemcpyHostToDevice), "H2D(optimizer state)");
+    }
+  }
+  t = h.t;
+  lr = h.lr; beta1 = h.beta1; beta2 = h.beta2; eps = h.eps; weight_decay = h.weight_decay;
 }
 
 AdamW::~AdamW() {

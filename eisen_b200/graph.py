@@ -263,6 +263,15 @@ class TransformerLM:
         call("eisen_lm_params", self._h, buf, C.byref(n))
         return [buf[i] for i in range(n.value)]
 
+    def generate(self, prompt, max_new_tokens, max_context, kv_cache=True, return_logits=False):
+        """Greedy generation (examples/train_llm.rs:560-584); kv_cache=False is the reference's loop."""
+        p = np.ascontiguousarray(np.asarray(prompt, dtype=np.int32).reshape(-1))
+        out = np.empty(max_new_tokens, dtype=np.int32)
+        logits = np.empty(self.vocab, dtype=np.float32) if return_logits else None
+        call("eisen_lm_generate", self._h, self.g._h, p.ctypes.data, p.size, max_new_tokens, max_context,
+             1 if kv_cache else 0, out.ctypes.data, logits.ctypes.data if return_logits else None)
+        return (out, logits) if return_logits else out
+
     def export_hf(self, safetensors_path, config_path=None, max_position_embeddings=2048):
         """model.safetensors (+ config.json) loadable as transformers.LlamaForCausalLM."""
         call("eisen_lm_export_hf", self._h, self.g._h, str(safetensors_path).encode(),
@@ -316,6 +325,13 @@ class AdamW:
 
     def step_fused(self, max_norm=0.0, grad_scale=1.0):
         call("eisen_optim_step_fused", self._h, max_norm, grad_scale)
+
+    def save_state(self, path):
+        """Step count, hyper-parameters and moments: with the weights file this resumes a run bit for bit."""
+        call("eisen_optim_save_state", self._h, str(path).encode())
+
+    def load_state(self, path):
+        call("eisen_optim_load_state", self._h, str(path).encode())
 
     def is_flat(self):
         f = C.c_int()

@@ -146,6 +146,12 @@ int eisen_attn_bwd(void* stream, const void* q, const void* k, const void* v, co
                    long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs, long long o_ss,
                    long long o_hs, float scale, int causal, int* status);
 
+/* One new query position against a KV cache (generation; no counterpart in the reference, which
+ * re-runs the whole context per token): o[h,:] = softmax(scale * q[h,:] K[0..n_keys, h/(Hq/Hkv), :]^T) V[...].
+ * q, o: [Hq, D]; k_cache, v_cache: rows of cache_row_stride elements holding [Hkv, D]; D <= 256. */
+int eisen_attn_decode(void* stream, const void* q, const void* k_cache, const void* v_cache, void* o, long long n_keys,
+                      long long Hq, long long Hkv, long long D, long long cache_row_stride, float scale, int dtype);
+
 /* ------------------------------------------------------------------------------------------
  * Row-wise ops
  * ------------------------------------------------------------------------------------------ */
@@ -375,6 +381,18 @@ int eisen_lm_set_fused(void* lm, int fused);   /* 0: the reference's op-by-op at
 int eisen_lm_set_head_fusion(void* lm, int fused, long long chunk_rows);
 int eisen_lm_forward(void* lm, void* g, long long x_ids, long long* logits_out);       /* Module::forward, :184-196 */
 int eisen_lm_params(void* lm, long long* ids_out, int* n_out);                         /* Module::params, :198-210 */
+/* Greedy generation, the loop of examples/train_llm.rs:560-584: max_new_tokens times the argmax of
+ * the last position's logits (the last of equal maxima, as Rust's max_by), context window
+ * max_context.  kv_cache = 0 runs it as the reference does, the whole context through the forward
+ * pass for every token.  kv_cache = 1 keeps every layer's rotated keys and its values on the device:
+ * the prompt runs once, every further token is one row through the projections plus
+ * eisen_attn_decode over the cache (the reference lists KV caching as future work, README.md:94);
+ * it needs n_prompt + max_new_tokens <= max_context (EISEN_ERR_LIMIT otherwise), because a sliding
+ * window re-positions every cached key.  last_logits (host f32 [vocab], may be null) receives the
+ * logits behind the last token.  Synchronises the graph's stream once per token (the argmax is
+ * taken on the host, as in the reference). */
+int eisen_lm_generate(void* lm, void* g, const int* prompt, long long n_prompt, long long max_new_tokens, long long max_context,
+                      int kv_cache, int* out_tokens, float* last_logits);
 /* Weights-only checkpoint (save_weights, examples/train_llm.rs:92-105): every parameter tensor in id
  * order as f32 little-endian, the `eisen_model.bin` the reference's converter reads.  load_weights is
  * its inverse for an identically built model (the reference has no loader). */
@@ -414,6 +432,12 @@ int eisen_optim_step(void* opt);
 /* clip (max_norm > 0) and step without a host round trip; the gradient is read as g * grad_scale */
 int eisen_optim_step_fused(void* opt, float max_norm, float grad_scale);
 int eisen_optim_is_flat(void* opt, int* flat);
+/* Optimizer state of a checkpoint: step count, hyper-parameters and the AdamW moments (of this
+ * rank's ranges for a sharded optimizer), so that weights file + state file resume a run bit for
+ * bit.  The reference saves weights only (examples/train_llm.rs:93-105) and lists optimizer state
+ * as future work (README.md:88).  load_state rejects a file written for another model or sharding. */
+int eisen_optim_save_state(void* opt, const char* path);
+int eisen_optim_load_state(void* opt, const char* path);
 /* Sharded optimizer state (ZeRO-1; no counterpart in the reference): this rank keeps AdamW moments
  * only for n_pieces element ranges [piece_lo[i], piece_hi[i]) of the flat parameter arena and
  * updates only those (master weights and their bf16 copies); the exchange layer brings in the

@@ -144,3 +144,59 @@ def test_weights_checkpoint_round_trip(tmp_path):
     with pytest.raises(Exception):
         open(tmp_path / "short.bin", "wb").write(b"1234")
         g2.load_weights(tmp_path / "short.bin")
+
+
+def test_resume_from_weights_and_optimizer_state_is_bit_exact(tmp_path):
+    """Two optimizer steps == one step, save (weights + optimizer state), load into a freshly built
+    model and optimizer, one more step: bit for bit in the f32 graph (whose kernels use no atomics)."""
+    import torch
+    from eisen_b200.graph import AdamW, FP32, Graph, TransformerLM
+
+    cfg = dict(vocab=128, hidden=64, heads=2, kv=1, ffn=128, layers=2)
+    rng = np.random.default_rng(9)
+    batches = [(rng.integers(0, cfg["vocab"], (2, 16)).astype(np.int32), rng.integers(0, cfg["vocab"], 32)) for _ in range(2)]
+
+    def build(seed):
+        g = Graph(FP32, torch.cuda.current_stream().cuda_stream)
+        lm = TransformerLM(g, cfg["vocab"], cfg["hidden"], cfg["heads"], cfg["kv"], cfg["ffn"], cfg["layers"], False)
+        g.mark_params()
+        r = np.random.default_rng(seed)
+        for p in lm.params():
+            shp = g.shape(p)
+            if len(shp) == 2:
+                g.load_tensor_data(p, (r.standard_normal(int(np.prod(shp))) * 0.02).astype(np.float32))
+        opt = AdamW(g, lm.params(), 1e-2)
+        opt.config(1e-2, 0.9, 0.95, 1e-8, 0.1)
+        return g, lm, opt
+
+    def step(g, lm, opt, b):
+        opt.zero_grad()
+        lm.train_micro_step(g.alloc_ids([2, 16], b[0]), b[1].tolist())
+        g.clear_activations()
+        opt.step_fused(1.0, 1.0)
+        g.synchronize()
+
+    g1, lm1, o1 = build(1)
+    step(g1, lm1, o1, batches[0])
+    g1.save_weights(tmp_path / "w.bin")
+    o1.save_state(tmp_path / "opt.bin")
+    step(g1, lm1, o1, batches[1])
+
+    g2, lm2, o2 = build(2)  # other initial weights, fresh moments, t = 0
+    g2.load_weights(tmp_path / "w.bin")
+    o2.load_state(tmp_path / "opt.bin")
+    step(g2, lm2, o2, batches[1])
+    for a, b in zip(lm1.params(), lm2.params()):
+        assert np.array_equal(g1.data(a), g2.data(b))
+
+    # without the optimizer state the resumed step differs (moments and bias correction restart)
+    g3, lm3, o3 = build(2)
+    g3.load_weights(tmp_path / "w.bin")
+    step(g3, lm3, o3, batches[1])
+    assert not np.array_equal(g1.data(lm1.params()[1]), g3.data(lm3.params()[1]))
+    # a state file of another model is rejected
+    gs = Graph(FP32, torch.cuda.current_stream().cuda_stream)
+    lms = TransformerLM(gs, 64, 32, 2, 1, 64, 1, False)
+    gs.mark_params()
+    with pytest.raises(Exception, match="another model"):
+        AdamW(gs, lms.params(), 1e-2).load_state(tmp_path / "opt.bin")
