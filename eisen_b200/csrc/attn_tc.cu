@@ -16,6 +16,8 @@
 // It replaces the reference's materialised chain bmm -> mul(scale) -> add(mask) -> softmax -> bmm
 // and its gradient kernels (src/nn/attention.rs:339-375; kernels/ops_f32.cu:342-511, 625-646,
 // 787-840); the reference has no fused backward (src/graph/ops/attention.rs:15-18).
+#include <atomic>
+
 #include "ptx.cuh"
 #include "common.cuh"
 #include "errors.h"
@@ -26,6 +28,9 @@ namespace eisen {
 namespace {
 
 constexpr float LOG2E = 1.4426950408889634f;
+
+// share of the forward's exponentials taken by the FMA-pipe polynomial, in eighths (0..4)
+std::atomic<int> g_attn_poly_level{0};
 
 struct AttnParams {
   int B, S, Hq, Hkv, D;
@@ -65,6 +70,25 @@ __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// 2^x for two values on the FMA pipe instead of the special-function unit: x = n + f with n the
+// nearest integer and f in [-0.5, 0.5]; 2^f by a degree-3 polynomial (maximum relative error
+// 7.5e-5, far below the bf16 rounding of the probabilities), n added into the exponent field.
+// Inputs must be <= 127; values below -126 give 2^-126 (the callers use it for unmasked scores).
+__device__ __forceinline__ void ex2_poly2(float& x0, float& x1) {
+  constexpr float MAGIC = 12582912.0f;  // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
+  x0 = fmaxf(x0, -126.0f);
+  x1 = fmaxf(x1, -126.0f);
+  float t0, t1, n0, n1, f0, f1, p0, p1;
+  fadd2(t0, t1, x0, x1, MAGIC, MAGIC);
+  fadd2(n0, n1, t0, t1, -MAGIC, -MAGIC);
+  ffma2(f0, f1, n0, n1, -1.0f, -1.0f, x0, x1);
+  ffma2(p0, p1, f0, f1, 0.05517167f, 0.05517167f, 0.24261114f, 0.24261114f);
+  ffma2(p0, p1, p0, p1, f0, f1, 0.69326099f, 0.69326099f);
+  ffma2(p0, p1, p0, p1, f0, f1, 0.99992807f, 0.99992807f);
+  x0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
+  x1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
 }
 
 template <int D>
@@ -445,6 +469,10 @@ struct Fwd64Cfg {
   static constexpr int THREADS = (SWARPS + 2) * 32;
 };
 
+// POLY_MASK: bit g set = the second pair of score group g (four consecutive scores; a thread has
+// 16 groups per key tile) takes ex2_poly2 instead of two ex2.approx; tiles that need masking
+// always use ex2.approx (a masked score is -inf).
+template <int POLY_MASK>
 __global__ void __launch_bounds__(Fwd64Cfg::THREADS, 1)
 attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
@@ -691,7 +719,9 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           float x0, x1, x2, x3;
           ffma2(x0, x1, __uint_as_float(ra[i + u]), __uint_as_float(ra[i + u + 1]), sl2, sl2, nmsl2, nmsl2);
           ffma2(x2, x3, __uint_as_float(ra[i + u + 2]), __uint_as_float(ra[i + u + 3]), sl2, sl2, nmsl2, nmsl2);
-          x0 = ex2_approx(x0); x1 = ex2_approx(x1); x2 = ex2_approx(x2); x3 = ex2_approx(x3);
+          x0 = ex2_approx(x0); x1 = ex2_approx(x1);
+          if (((POLY_MASK >> ((i + u) >> 2)) & 1) && !need_mask) ex2_poly2(x2, x3);
+          else { x2 = ex2_approx(x2); x3 = ex2_approx(x3); }
           fadd2(rs0, rs1, rs0, rs1, x0, x1);
           fadd2(rs2, rs3, rs2, rs3, x2, x3);
           pk[u >> 1] = pack_bf16x2(x0, x1);
@@ -707,7 +737,9 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           float x0, x1, x2, x3;
           ffma2(x0, x1, __uint_as_float(rb[i + u]), __uint_as_float(rb[i + u + 1]), sl2, sl2, nmsl2, nmsl2);
           ffma2(x2, x3, __uint_as_float(rb[i + u + 2]), __uint_as_float(rb[i + u + 3]), sl2, sl2, nmsl2, nmsl2);
-          x0 = ex2_approx(x0); x1 = ex2_approx(x1); x2 = ex2_approx(x2); x3 = ex2_approx(x3);
+          x0 = ex2_approx(x0); x1 = ex2_approx(x1);
+          if (((POLY_MASK >> (8 + ((i + u) >> 2))) & 1) && !need_mask) ex2_poly2(x2, x3);
+          else { x2 = ex2_approx(x2); x3 = ex2_approx(x3); }
           fadd2(rs0, rs1, rs0, rs1, x0, x1);
           fadd2(rs2, rs3, rs2, rs3, x2, x3);
           pk[u >> 1] = pack_bf16x2(x0, x1);
@@ -1223,6 +1255,12 @@ using namespace eisen;
 
 extern "C" {
 
+int eisen_attn_set_poly_exp(int level) {
+  if (level < 0 || level > 4) return fail(EISEN_ERR_INVALID, "attn_set_poly_exp: level must be in [0, 4]");
+  g_attn_poly_level.store(level);
+  return 0;
+}
+
 int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, void* o, float* lse, long long B,
                    long long S, long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss,
                    long long q_hs, long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs,
@@ -1244,9 +1282,26 @@ int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, vo
   dim3 grid((unsigned)Hq, (unsigned)B, (unsigned)(((S + 127) / 128 + 1) / 2));  // two query tiles per CTA
   cudaStream_t s = (cudaStream_t)stream;
   if (D == 64) {
-    static bool set64[MAX_DEVICE_SLOTS] = {false};
-    if (!set64[device_slot()]) { if (cudaFuncSetAttribute(attn_fwd64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd64Cfg::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute"); set64[device_slot()] = true; }
-    attn_fwd64_kernel<<<grid, Fwd64Cfg::THREADS, Fwd64Cfg::SMEM, s>>>(tq, tk, tv, p);
+    // share of the exponentials computed by polynomial on the FMA pipe: 0, 1/8, 1/4, 3/8 or 1/2
+    auto launch64 = [&](auto kern, bool& attr_done) -> int {
+      if (!attr_done) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd64Cfg::SMEM) != cudaSuccess) return 1;
+        attr_done = true;
+      }
+      kern<<<grid, Fwd64Cfg::THREADS, Fwd64Cfg::SMEM, s>>>(tq, tk, tv, p);
+      return 0;
+    };
+    static bool set64[5][MAX_DEVICE_SLOTS] = {{false}};
+    const int slot = device_slot();
+    int bad = 0;
+    switch (g_attn_poly_level.load()) {
+      case 0: bad = launch64(attn_fwd64_kernel<0x0000>, set64[0][slot]); break;
+      case 1: bad = launch64(attn_fwd64_kernel<0x1111>, set64[1][slot]); break;
+      case 2: bad = launch64(attn_fwd64_kernel<0x5555>, set64[2][slot]); break;
+      case 3: bad = launch64(attn_fwd64_kernel<0x7777>, set64[3][slot]); break;
+      default: bad = launch64(attn_fwd64_kernel<0xFFFF>, set64[4][slot]); break;
+    }
+    if (bad) return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute");
   } else {
     static bool set128[MAX_DEVICE_SLOTS] = {false};
     if (!set128[device_slot()]) { if (cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<128>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute"); set128[device_slot()] = true; }

@@ -56,6 +56,36 @@ int eisen_graph_selftest_bounded_wait(void* g, long long budget_cycles) {
     if (rc) throw EisenException(rc, eisen_last_error());
   });
 }
+int eisen_graph_set_vram_budget(void* g, long long budget_bytes, long long activation_reserve_bytes) {
+  return guarded([&] {
+    if (budget_bytes < 0 || activation_reserve_bytes < 0) throw EisenException(EISEN_ERR_INVALID, "set_vram_budget: negative size");
+    G(g).vram_budget_bytes = (size_t)budget_bytes;
+    G(g).activation_reserve_bytes = (size_t)activation_reserve_bytes;
+  });
+}
+int eisen_graph_vram_usage(void* g, long long* used, long long* budget) {
+  return guarded([&] {
+    if (used) *used = (long long)G(g).current_vram_usage();
+    if (budget) *budget = (long long)G(g).vram_budget_bytes;
+  });
+}
+int eisen_graph_plan_streaming(void* g, long long budget_bytes, long long activation_reserve_bytes, const long long* pinned,
+                               int n_pinned, int apply, long long* resident_ids, int* n_resident, long long* streamed_ids,
+                               int* n_streamed, long long* bytes4) {
+  return guarded([&] {
+    std::vector<int64_t> pin(pinned, pinned + n_pinned);
+    StreamingReport r = apply ? G(g).plan_streaming((size_t)budget_bytes, (size_t)activation_reserve_bytes, pin)
+                              : G(g).plan_streaming_layout((size_t)budget_bytes, (size_t)activation_reserve_bytes, pin);
+    if (resident_ids) for (size_t i = 0; i < r.resident_param_ids.size(); ++i) resident_ids[i] = r.resident_param_ids[i];
+    if (streamed_ids) for (size_t i = 0; i < r.streamed_param_ids.size(); ++i) streamed_ids[i] = r.streamed_param_ids[i];
+    if (n_resident) *n_resident = (int)r.resident_param_ids.size();
+    if (n_streamed) *n_streamed = (int)r.streamed_param_ids.size();
+    if (bytes4) {
+      bytes4[0] = r.resident_bytes; bytes4[1] = r.resident_headroom_bytes;
+      bytes4[2] = r.streamed_bytes; bytes4[3] = r.streaming_headroom_bytes;
+    }
+  });
+}
 int eisen_graph_alloc(void* g, const long long* shape, int ndim, const float* host_data, long long* id_out) {
   return guarded([&] { *id_out = G(g).alloc(shp(shape, ndim), host_data); });
 }
@@ -206,6 +236,9 @@ int eisen_lm_destroy(void* lm) {
 }
 int eisen_lm_set_fused(void* lm, int fused) {
   return guarded([&] { static_cast<TransformerLM*>(lm)->fused = fused != 0; });
+}
+int eisen_lm_set_keep_attention(void* lm, int keep) {
+  return guarded([&] { static_cast<TransformerLM*>(lm)->keep_attention = keep != 0; });
 }
 int eisen_lm_set_head_fusion(void* lm, int fused, long long chunk_rows) {
   return guarded([&] {

@@ -5,6 +5,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 #include "../../../include/eisen_b200.h"
@@ -32,7 +33,31 @@ void cuck(cudaError_t e, const char* what) {
 }  // namespace
 
 // ------------------------------------------------------------------------------------- storage
+namespace {
+size_t env_mb(const char* name, size_t fallback_mb) {
+  const char* v = std::getenv(name);
+  if (!v || !*v) return fallback_mb;
+  char* end = nullptr;
+  const unsigned long long mb = std::strtoull(v, &end, 10);
+  return (end && *end == 0) ? (size_t)mb : fallback_mb;
+}
+void* host_alloc(size_t bytes) {
+  void* p = nullptr;
+  cuck(cudaHostAlloc(&p, std::max<size_t>(bytes, 16), cudaHostAllocMapped | cudaHostAllocPortable), "cudaHostAlloc");
+  void* d = nullptr;
+  cuck(cudaHostGetDevicePointer(&d, p, 0), "cudaHostGetDevicePointer");
+  if (d != p) {
+    cudaFreeHost(p);
+    throw EisenException(EISEN_ERR_CUDA, "host-homed parameters need unified addressing (host and device pointer differ)");
+  }
+  return p;
+}
+}  // namespace
+
 Graph::Graph(Precision prec, cudaStream_t s) : precision(prec), stream(s) {
+  // src/graph/mod.rs:283-288
+  vram_budget_bytes = env_mb("EISEN_VRAM_BUDGET_MB", 0) << 20;
+  activation_reserve_bytes = env_mb("EISEN_ACTIVATION_RESERVE_MB", 64) << 20;
   cuck(cudaMalloc(&status_dev, 256), "cudaMalloc(status)");
   cuck(cudaMemsetAsync(status_dev, 0, 256, stream), "memset(status)");
   bad_id_dev = status_dev + 16;
@@ -49,6 +74,12 @@ Graph::~Graph() {
   if (arena_shadow) cudaFree(arena_shadow);
   if (arena_g) cudaFree(arena_g);
   if (status_dev) cudaFree(status_dev);
+  for (StageSlot& sl : stage_) {
+    if (sl.buf) cudaFree(sl.buf);
+    if (sl.ready) cudaEventDestroy(sl.ready);
+  }
+  if (compute_mark_) cudaEventDestroy(compute_mark_);
+  if (copy_stream_) cudaStreamDestroy(copy_stream_);
 }
 
 // exact-size free lists, as the reference's vram_pool keyed by element count
@@ -64,10 +95,12 @@ void* Graph::pool_get(size_t bytes) {
     ++pool_hits;
     return p;
   }
+  // src/graph/memory.rs:189-266 (safe_alloc_zeros): allocate if the budget allows; else drop the
+  // cached pool buffers and try again; else fail (with a status, where the reference panics)
+  auto within_budget = [&]() { return vram_budget_bytes == 0 || current_vram_usage() + bytes <= vram_budget_bytes; };
   void* p = nullptr;
-  cudaError_t e = cudaMalloc(&p, bytes);
+  cudaError_t e = within_budget() ? cudaMalloc(&p, bytes) : cudaErrorMemoryAllocation;
   if (e != cudaSuccess) {
-    // drop the cache and retry once (src/graph/memory.rs:189-266: alloc -> drop pool -> retry)
     cudaGetLastError();
     cudaStreamSynchronize(stream);
     for (auto& kv : pool_) {
@@ -76,6 +109,10 @@ void* Graph::pool_get(size_t bytes) {
     }
     device_bytes_allocated -= pool_bytes_cached;
     pool_bytes_cached = 0;
+    if (!within_budget())
+      throw EisenException(EISEN_ERR_OOM, "VRAM budget exhausted: " + std::to_string(current_vram_usage() >> 20) + " MB in use, " +
+                                              std::to_string(bytes >> 20) + " MB requested, budget " +
+                                              std::to_string(vram_budget_bytes >> 20) + " MB");
     e = cudaMalloc(&p, bytes);
     if (e != cudaSuccess) throw EisenException(EISEN_ERR_OOM, "out of device memory in the activation pool");
   }
@@ -111,8 +148,12 @@ int64_t Graph::new_tensor(HTensor&& t) {
 
 void Graph::free_tensor(HTensor& t) {
   if (t.is_pooled) {
-    pool_put(t.data, (size_t)t.numel * dsize(t.dtype == DT_I32 ? 0 : t.dtype));
+    if (!t.data_kept) pool_put(t.data, (size_t)t.numel * dsize(t.dtype == DT_I32 ? 0 : t.dtype));
     pool_put(t.grad, (size_t)t.numel * dsize(t.grad_dtype));
+  } else if (t.host_homed) {
+    if (t.data) cudaFreeHost(t.data);
+    if (t.shadow) cudaFreeHost(t.shadow);
+    if (t.grad) cudaFreeHost(t.grad);
   } else {
     if (t.owns_data && t.data) cudaFree(t.data);
     if (t.owns_data && t.shadow) cudaFree(t.shadow);
@@ -147,8 +188,15 @@ int64_t Graph::alloc(const std::vector<int64_t>& shape, const float* host) {
   t.is_param = param;
   const size_t n = (size_t)std::max<int64_t>(t.numel, 1);
   const int64_t padded = (t.numel + 63) / 64 * 64;
-  const bool in_arena = param && arena_w && arena_used + padded <= arena_cap;
-  if (in_arena) {
+  const bool in_arena = param && !home_params_on_host && arena_w && arena_used + padded <= arena_cap;
+  if (param && home_params_on_host) {
+    t.data = host_alloc(n * 4);
+    t.grad = host_alloc(n * 4);
+    t.grad_dtype = 0;
+    std::memset(t.grad, 0, n * 4);
+    if (precision == Precision::Bf16Mixed) t.shadow = host_alloc(n * 2);
+    t.host_homed = true;
+  } else if (in_arena) {
     t.data = arena_w + arena_used;
     t.grad = arena_g + arena_used;
     t.grad_dtype = 0;
@@ -204,8 +252,9 @@ void Graph::load_tensor_data(int64_t id, const float* host, int64_t n) {
   HTensor& t = tensors.at(id);
   if (n != t.numel) invalid("load_tensor_data: element count does not match the tensor shape");
   if (t.dtype == 0) {
-    cuck(cudaMemcpyAsync(t.data, host, (size_t)n * 4, cudaMemcpyHostToDevice, stream), "H2D");
+    cuck(cudaMemcpyAsync(t.data, host, (size_t)n * 4, cudaMemcpyDefault, stream), "H2D");
     if (t.shadow) ck(eisen_cast(stream, t.data, 0, t.shadow, 1, n), "cast(shadow)");
+    if (t.host_homed) invalidate_staged_weights();
     cuck(cudaStreamSynchronize(stream), "sync");
   } else if (t.dtype == 1) {
     float* tmp = static_cast<float*>(pool_get((size_t)n * 4));
@@ -220,7 +269,7 @@ void Graph::load_tensor_data(int64_t id, const float* host, int64_t n) {
 
 static void read_back(Graph& g, const void* dev, int dt, int64_t n, float* out) {
   if (dt == 0) {
-    cuck(cudaMemcpyAsync(out, dev, (size_t)n * 4, cudaMemcpyDeviceToHost, g.stream), "D2H");
+    cuck(cudaMemcpyAsync(out, dev, (size_t)n * 4, cudaMemcpyDefault, g.stream), "D2H");
     cuck(cudaStreamSynchronize(g.stream), "sync");
   } else {
     float* tmp = static_cast<float*>(g.pool_get((size_t)n * 4));
@@ -265,6 +314,15 @@ void Graph::check_status() {
   if (h[17] != 0) {
     cudaMemset(bad_id_dev + 1, 0, 4);
     throw EisenException(EISEN_ERR_INVALID, "cross_entropy: a target is neither the ignore index nor inside [0, vocab)");
+  }
+}
+
+void Graph::release_attn_stash() {
+  for (AttnStash& st : attn_stash) {
+    // a stashed buffer was never returned to the pool, so it still counts as live: pool_put settles that
+    if (st.o) pool_put(st.o, st.o_bytes);
+    if (st.lse) pool_put(st.lse, st.lse_bytes);
+    st = AttnStash();
   }
 }
 
@@ -342,6 +400,170 @@ const float* Graph::rope_table(int64_t S, int64_t hd) {
   ck(eisen_rope_table(stream, tab, S, hd, 10000.0f), "rope_table");
   rope_tables_[key] = tab;
   return tab;
+}
+
+// ------------------------------------------------------------------------------------- streaming
+// src/graph/memory.rs:64-125: the residency plan.  Sixteen bytes per element (f32 weight, gradient
+// and two AdamW moments) for everything that stays on the device, the largest streamed tensor's
+// f32 size as transfer headroom.
+StreamingReport Graph::plan_streaming_layout(size_t budget, size_t reserve, const std::vector<int64_t>& pinned) const {
+  if (num_params <= 0) invalid("plan_streaming: call mark_params() first");
+  auto sat_sub = [](size_t a, size_t b) { return a > b ? a - b : (size_t)0; };
+  auto is_param_tensor = [&](int64_t id) { return tensors[(size_t)id].dtype != DT_I32; };
+  std::vector<char> is_pinned((size_t)num_params, 0);
+  size_t pinned_vram = 0;
+  for (int64_t pid : pinned) {
+    if (pid < 0 || pid >= num_params || !is_param_tensor(pid)) invalid("plan_streaming: pinned id is not a parameter");
+    is_pinned[(size_t)pid] = 1;
+    pinned_vram += (size_t)tensors[(size_t)pid].numel * 16;
+  }
+  const size_t budget_after_fixed = sat_sub(sat_sub(budget, reserve), pinned_vram);
+  StreamingReport rep;
+  std::vector<int64_t> resident;
+  size_t used = 0;
+  for (int64_t pid = 0; pid < num_params; ++pid) {
+    if (is_pinned[(size_t)pid] || !is_param_tensor(pid)) continue;
+    const size_t cost = (size_t)tensors[(size_t)pid].numel * 16;
+    if (used + cost <= budget_after_fixed) { used += cost; resident.push_back(pid); }
+    else rep.streamed_param_ids.push_back(pid);
+  }
+  size_t max_stream_bytes = 0;
+  for (int64_t pid : rep.streamed_param_ids) max_stream_bytes = std::max(max_stream_bytes, (size_t)tensors[(size_t)pid].numel * 4);
+  // make room for one streamed tensor: the largest resident tensor goes first (of equals the last)
+  while (max_stream_bytes > sat_sub(budget_after_fixed, used) && !resident.empty()) {
+    size_t best = 0;
+    for (size_t i = 1; i < resident.size(); ++i)
+      if (tensors[(size_t)resident[i]].numel >= tensors[(size_t)resident[best]].numel) best = i;
+    const int64_t pid = resident[best];
+    resident.erase(resident.begin() + (long)best);
+    used -= (size_t)tensors[(size_t)pid].numel * 16;
+    rep.streamed_param_ids.push_back(pid);
+  }
+  for (int64_t pid : rep.streamed_param_ids) rep.streamed_bytes += tensors[(size_t)pid].numel * 4;
+  rep.resident_param_ids = pinned;
+  rep.resident_param_ids.insert(rep.resident_param_ids.end(), resident.begin(), resident.end());
+  for (int64_t pid : rep.resident_param_ids) rep.resident_bytes += tensors[(size_t)pid].numel * 16;
+  rep.streaming_headroom_bytes = (int64_t)max_stream_bytes;
+  rep.resident_headroom_bytes = 0;  // the reference reports the bytes in use before planning, which is 0
+  return rep;
+}
+
+StreamingReport Graph::plan_streaming(size_t budget, size_t reserve, const std::vector<int64_t>& pinned) {
+  StreamingReport rep = plan_streaming_layout(budget, reserve, pinned);
+  cuck(cudaStreamSynchronize(stream), "sync");
+  for (int64_t pid : rep.streamed_param_ids) move_param_to_host(pid);
+  for (int64_t pid : rep.resident_param_ids) move_param_to_device(pid);
+  vram_budget_bytes = budget;
+  activation_reserve_bytes = reserve;
+  invalidate_staged_weights();
+  return rep;
+}
+
+// src/graph/memory.rs:323-373 (demote_tensor_to_cpu) for a parameter: data, bf16 copy and gradient
+// move to page-locked host memory.  A tensor inside the flat arena keeps its arena range unused.
+void Graph::move_param_to_host(int64_t id) {
+  HTensor& t = tensors.at(id);
+  if (t.host_homed) return;
+  if (!t.is_param || t.dtype != 0) invalid("move_param_to_host: not an f32 parameter");
+  const size_t n = (size_t)std::max<int64_t>(t.numel, 1);
+  void* hd = host_alloc(n * 4);
+  void* hg = host_alloc(n * 4);
+  void* hs = t.shadow ? host_alloc(n * 2) : nullptr;
+  cuck(cudaMemcpy(hd, t.data, n * 4, cudaMemcpyDefault), "D2H(param)");
+  cuck(cudaMemcpy(hg, t.grad, n * 4, cudaMemcpyDefault), "D2H(param grad)");
+  if (hs) cuck(cudaMemcpy(hs, t.shadow, n * 2, cudaMemcpyDefault), "D2H(param shadow)");
+  if (t.owns_data) {
+    cudaFree(t.data);
+    if (t.shadow) cudaFree(t.shadow);
+    device_bytes_allocated -= round256(n * 4) + (t.shadow ? round256(n * 2) : 0);
+  }
+  if (t.owns_grad) { cudaFree(t.grad); device_bytes_allocated -= round256(n * 4); }
+  t.data = hd; t.grad = hg; t.shadow = hs;
+  t.owns_data = t.owns_grad = false;
+  t.host_homed = true;
+}
+
+// src/graph/memory.rs:268-321 (ensure_on_gpu)
+void Graph::move_param_to_device(int64_t id) {
+  HTensor& t = tensors.at(id);
+  if (!t.host_homed) return;
+  const size_t n = (size_t)std::max<int64_t>(t.numel, 1);
+  void *dd = nullptr, *dg = nullptr, *ds = nullptr;
+  cuck(cudaMalloc(&dd, round256(n * 4)), "cudaMalloc(param)");
+  cuck(cudaMalloc(&dg, round256(n * 4)), "cudaMalloc(param grad)");
+  if (t.shadow) cuck(cudaMalloc(&ds, round256(n * 2)), "cudaMalloc(param shadow)");
+  cuck(cudaMemcpy(dd, t.data, n * 4, cudaMemcpyDefault), "H2D(param)");
+  cuck(cudaMemcpy(dg, t.grad, n * 4, cudaMemcpyDefault), "H2D(param grad)");
+  if (ds) cuck(cudaMemcpy(ds, t.shadow, n * 2, cudaMemcpyDefault), "H2D(param shadow)");
+  cudaFreeHost(t.data);
+  cudaFreeHost(t.grad);
+  if (t.shadow) cudaFreeHost(t.shadow);
+  t.data = dd; t.grad = dg; t.shadow = ds;
+  t.owns_data = t.owns_grad = true;
+  t.host_homed = false;
+  device_bytes_allocated += 2 * round256(n * 4) + (ds ? round256(n * 2) : 0);
+}
+
+// Staging ring for host-homed GEMM operands.  The reference uploads a streamed weight with a
+// blocking copy inside every matmul, forward and backward (src/graph/ops/linear.rs:804-807,
+// 893-897); here the copy runs on its own stream into one of a ring of device buffers, early
+// when prefetch_weight is called ahead of use, and the compute stream only waits on its event.
+constexpr size_t kStageSlots = 16;
+
+void Graph::ensure_stage(size_t bytes) {
+  if (!copy_stream_) {
+    cuck(cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking), "cudaStreamCreate(copy)");
+    cuck(cudaEventCreateWithFlags(&compute_mark_, cudaEventDisableTiming), "cudaEventCreate");
+  }
+  if (bytes <= stage_slot_bytes_ && !stage_.empty()) return;
+  // (re)build the ring with slots large enough for this operand
+  cuck(cudaStreamSynchronize(stream), "sync");
+  cuck(cudaStreamSynchronize(copy_stream_), "sync");
+  for (StageSlot& sl : stage_) {
+    if (sl.buf) { cudaFree(sl.buf); device_bytes_allocated -= stage_slot_bytes_; }
+    sl.buf = nullptr;
+    sl.id = -1;
+  }
+  stage_.resize(kStageSlots);
+  stage_slot_bytes_ = round256(bytes);
+  for (StageSlot& sl : stage_) {
+    cuck(cudaMalloc(&sl.buf, stage_slot_bytes_), "cudaMalloc(weight staging)");
+    device_bytes_allocated += stage_slot_bytes_;
+    if (!sl.ready) cuck(cudaEventCreateWithFlags(&sl.ready, cudaEventDisableTiming), "cudaEventCreate");
+  }
+}
+
+Graph::StageSlot* Graph::stage_weight(int64_t id) {
+  const HTensor& t = tensors.at(id);
+  const bool bf16 = precision == Precision::Bf16Mixed;
+  const void* src = bf16 ? t.shadow : t.data;
+  if (!src) invalid("weight_operand: host-homed parameter without data");
+  const size_t bytes = (size_t)t.numel * (bf16 ? 2 : 4);
+  ensure_stage(bytes);
+  for (StageSlot& sl : stage_)
+    if (sl.id == id && sl.generation == weight_generation_) return &sl;
+  StageSlot& sl = stage_[stage_next_];
+  stage_next_ = (stage_next_ + 1) % stage_.size();
+  // whatever the compute stream has queued so far may still read this slot
+  cuck(cudaEventRecord(compute_mark_, stream), "cudaEventRecord");
+  cuck(cudaStreamWaitEvent(copy_stream_, compute_mark_, 0), "cudaStreamWaitEvent");
+  cuck(cudaMemcpyAsync(sl.buf, src, bytes, cudaMemcpyDefault, copy_stream_), "H2D(weight staging)");
+  cuck(cudaEventRecord(sl.ready, copy_stream_), "cudaEventRecord");
+  sl.id = id;
+  sl.generation = weight_generation_;
+  return &sl;
+}
+
+void Graph::prefetch_weight(int64_t id) {
+  if (tensors.at(id).host_homed) stage_weight(id);
+}
+
+const void* Graph::weight_operand(int64_t id) {
+  const HTensor& t = tensors.at(id);
+  if (!t.host_homed) return operand(t);
+  StageSlot* sl = stage_weight(id);
+  cuck(cudaStreamWaitEvent(stream, sl->ready, 0), "cudaStreamWaitEvent");
+  return sl->buf;
 }
 
 void Graph::prof_begin(int cls, double flops) {
@@ -510,6 +732,24 @@ void gemm(Graph& g, bool a_mn, bool b_mn, int64_t M, int64_t N, int64_t K, const
      "gemm_bf16");
   g.prof_end();
 }
+
+// Weight gradient dW[M,N] (+)= A(m,k) B(n,k) into parameter (or activation) `w`.  A host-homed
+// parameter keeps its gradient in host memory: the product goes to a pooled device buffer and is
+// then added to the host gradient by a plain element kernel (the reference downloads the product
+// and adds it on the CPU, src/graph/ops/linear.rs:937-947).
+void dw_gemm(Graph& g, bool a_mn, bool b_mn, int64_t M, int64_t N, int64_t K, const void* A, const void* B, int64_t w) {
+  HTensor& gw = g.tensors[w];
+  if (!gw.host_homed) {
+    gemm(g, a_mn, b_mn, M, N, K, A, B, gw.grad, gw.grad_dtype, gw.grad_init);
+  } else {
+    const size_t bytes = (size_t)M * N * 4;
+    void* tmp = g.pool_get(bytes);
+    struct Release { Graph& g; void* p; size_t b; ~Release() { g.pool_put(p, b); } } release{g, tmp, bytes};
+    gemm(g, a_mn, b_mn, M, N, K, A, B, tmp, 0, false);
+    ck(eisen_accumulate(g.stream, gw.grad, 0, tmp, 0, M * N, gw.grad_init), "dW(host-homed)");
+  }
+  gw.grad_init = true;
+}
 }  // namespace
 
 // src/graph/ops/linear.rs:35-299 (f32) and 526-770 (bf16 operands): C[m,n] = A[m,k] B[k,n]
@@ -522,7 +762,7 @@ int64_t Graph::matmul(int64_t a, int64_t b) {
   if (tb.shape[0] != k) invalid("matmul: lhs last dim must equal rhs first dim");
   int64_t o = alloc_pooled({m, n});
   if (!skip_forward)
-    gemm(*this, false, true, m, n, k, operand(tensors[a]), operand(tensors[b]), tensors[o].data, act_dtype(), false);
+    gemm(*this, false, true, m, n, k, operand(tensors[a]), weight_operand(b), tensors[o].data, act_dtype(), false);
   if (!no_grad) {
     tape.push_back({{a, b}, o, [this, a, b, o, m, n, k]() {
       OUT_GRAD_OR_RETURN(o);
@@ -530,13 +770,12 @@ int64_t Graph::matmul(int64_t a, int64_t b) {
       HTensor& gb = tensors[b];
       if (!ga.constant) {  // dA[m,k] (+)= dC[m,n] B[k,n]^T
         ensure_grad(a);
-        gemm(*this, false, false, m, k, n, to.grad, operand(gb), ga.grad, ga.grad_dtype, ga.grad_init);
+        gemm(*this, false, false, m, k, n, to.grad, weight_operand(b), ga.grad, ga.grad_dtype, ga.grad_init);
         ga.grad_init = true;
       }
       if (!gb.constant) {  // dB[k,n] (+)= A[m,k]^T dC[m,n]
         ensure_grad(b);
-        gemm(*this, true, true, k, n, m, operand(ga), to.grad, gb.grad, gb.grad_dtype, gb.grad_init);
-        gb.grad_init = true;
+        dw_gemm(*this, true, true, k, n, m, operand(ga), to.grad, b);
       }
     }});
   }
@@ -565,7 +804,7 @@ int64_t Graph::matmul_rope(int64_t a, int64_t b, int64_t head_dim) {
   int64_t o = alloc_pooled({B, S, n});
   if (!skip_forward) {
     prof_begin(0, 2.0 * (double)m * (double)n * (double)k);
-    ck(eisen_gemm_bf16_rope(stream, m, n, k, operand(tensors[a]), k, operand(tensors[b]), n, tensors[o].data, n, tab, S,
+    ck(eisen_gemm_bf16_rope(stream, m, n, k, operand(tensors[a]), k, weight_operand(b), n, tensors[o].data, n, tab, S,
                             head_dim, status_dev),
        "matmul_rope");
     prof_end();
@@ -583,13 +822,12 @@ int64_t Graph::matmul_rope(int64_t a, int64_t b, int64_t head_dim) {
       HTensor& gb = tensors[b];
       if (!ga.constant) {
         ensure_grad(a);
-        gemm(*this, false, false, m, k, n, rot, operand(gb), ga.grad, ga.grad_dtype, ga.grad_init);
+        gemm(*this, false, false, m, k, n, rot, weight_operand(b), ga.grad, ga.grad_dtype, ga.grad_init);
         ga.grad_init = true;
       }
       if (!gb.constant) {
         ensure_grad(b);
-        gemm(*this, true, true, k, n, m, operand(ga), rot, gb.grad, gb.grad_dtype, gb.grad_init);
-        gb.grad_init = true;
+        dw_gemm(*this, true, true, k, n, m, operand(ga), rot, b);
       }
     }});
   }
@@ -617,7 +855,7 @@ int64_t Graph::gate_up_swiglu(int64_t x, int64_t wg, int64_t wu) {
   if (no_grad) {  // nothing is kept for a backward pass: only the product is written
     int64_t h = alloc_pooled({m, n});
     prof_begin(0, flops);
-    ck(eisen_gemm_bf16_swiglu(stream, m, n, k, operand(tensors[x]), k, operand(tensors[wg]), operand(tensors[wu]), n,
+    ck(eisen_gemm_bf16_swiglu(stream, m, n, k, operand(tensors[x]), k, weight_operand(wg), weight_operand(wu), n,
                               nullptr, nullptr, tensors[h].data, n, status_dev),
        "gate_up_swiglu");
     prof_end();
@@ -631,7 +869,7 @@ int64_t Graph::gate_up_swiglu(int64_t x, int64_t wg, int64_t wu) {
     h = swiglu(go, up);
   }
   prof_begin(0, flops);
-  ck(eisen_gemm_bf16_swiglu(stream, m, n, k, operand(tensors[x]), k, operand(tensors[wg]), operand(tensors[wu]), n,
+  ck(eisen_gemm_bf16_swiglu(stream, m, n, k, operand(tensors[x]), k, weight_operand(wg), weight_operand(wu), n,
                             tensors[go].data, tensors[up].data, tensors[h].data, n, status_dev),
      "gate_up_swiglu");
   prof_end();
@@ -651,7 +889,7 @@ int64_t Graph::matmul_add(int64_t a, int64_t b, int64_t r) {
   int64_t o = alloc_pooled(tr.shape);
   if (!skip_forward) {
     prof_begin(0, 2.0 * (double)m * (double)n * (double)k);
-    ck(eisen_gemm_bf16_residual(stream, 0, 1, m, n, k, operand(tensors[a]), k, operand(tensors[b]), n, operand(tensors[r]),
+    ck(eisen_gemm_bf16_residual(stream, 0, 1, m, n, k, operand(tensors[a]), k, weight_operand(b), n, operand(tensors[r]),
                                 n, tensors[o].data, n, 1.0f, status_dev),
        "matmul_add");
     prof_end();
@@ -675,13 +913,12 @@ int64_t Graph::matmul_add(int64_t a, int64_t b, int64_t r) {
       } mover{to, gr, move_to_r};
       if (!ga.constant) {
         ensure_grad(a);
-        gemm(*this, false, false, m, k, n, to.grad, operand(gb), ga.grad, ga.grad_dtype, ga.grad_init);
+        gemm(*this, false, false, m, k, n, to.grad, weight_operand(b), ga.grad, ga.grad_dtype, ga.grad_init);
         ga.grad_init = true;
       }
       if (!gb.constant) {
         ensure_grad(b);
-        gemm(*this, true, true, k, n, m, operand(ga), to.grad, gb.grad, gb.grad_dtype, gb.grad_init);
-        gb.grad_init = true;
+        dw_gemm(*this, true, true, k, n, m, operand(ga), to.grad, b);
       }
     }});
   }
@@ -696,7 +933,7 @@ int64_t Graph::matmul_trans_b(int64_t a, int64_t b) {
   const int64_t k = ta.shape.back(), m = ta.numel / k, n = tb.shape[0];
   if (tb.shape[1] != k) invalid("matmul_trans_b: inner dims differ");
   int64_t o = alloc_pooled({m, n});
-  gemm(*this, false, false, m, n, k, operand(tensors[a]), operand(tensors[b]), tensors[o].data, act_dtype(), false);
+  gemm(*this, false, false, m, n, k, operand(tensors[a]), weight_operand(b), tensors[o].data, act_dtype(), false);
   if (!no_grad) {
     tape.push_back({{a, b}, o, [this, a, b, o, m, n, k]() {
       OUT_GRAD_OR_RETURN(o);
@@ -704,13 +941,12 @@ int64_t Graph::matmul_trans_b(int64_t a, int64_t b) {
       HTensor& gb = tensors[b];
       if (!ga.constant) {  // dA[m,k] (+)= dC[m,n] B[n,k]
         ensure_grad(a);
-        gemm(*this, false, true, m, k, n, to.grad, operand(gb), ga.grad, ga.grad_dtype, ga.grad_init);
+        gemm(*this, false, true, m, k, n, to.grad, weight_operand(b), ga.grad, ga.grad_dtype, ga.grad_init);
         ga.grad_init = true;
       }
       if (!gb.constant) {  // dB[n,k] (+)= dC[m,n]^T A[m,k]
         ensure_grad(b);
-        gemm(*this, true, true, n, k, m, to.grad, operand(ga), gb.grad, gb.grad_dtype, gb.grad_init);
-        gb.grad_init = true;
+        dw_gemm(*this, true, true, n, k, m, to.grad, operand(ga), b);
       }
     }});
   }
@@ -858,7 +1094,7 @@ int64_t Graph::lm_head_cross_entropy(int64_t h, int64_t w, int64_t tid, float no
     const int64_t m = std::min(chunk_rows, rows - r0);
     const char* hrows = (const char*)operand(tensors[h]) + (size_t)r0 * k * dsize(dt);
     // logits of these rows: [m, vocab] = H[m, k] W[k, vocab]  (tied: W^T with W [vocab, k])
-    gemm(*this, false, !trans_b, m, vocab, k, hrows, operand(tensors[w]), slab, dt, false);
+    gemm(*this, false, !trans_b, m, vocab, k, hrows, weight_operand(w), slab, dt, false);
     if (!grads) {
       ck(eisen_ce_fwd(stream, slab, targets + r0, nullptr, rl + r0, nullptr, m, vocab, -1, normalizer, dt, bad_id_dev + 1),
          "lm_head_cross_entropy(loss)");
@@ -870,12 +1106,11 @@ int64_t Graph::lm_head_cross_entropy(int64_t h, int64_t w, int64_t tid, float no
     HTensor& gw = tensors[w];
     // dH rows (op)= dlogits W^T
     char* dh = (char*)gh.grad + (size_t)r0 * k * dsize(gh.grad_dtype);
-    gemm(*this, false, trans_b, m, k, vocab, slab, operand(gw), dh, gh.grad_dtype, gh.grad_init);
+    gemm(*this, false, trans_b, m, k, vocab, slab, weight_operand(w), dh, gh.grad_dtype, gh.grad_init);
     if (!gw.constant) {
       // dW (op)= H^T dlogits  (tied: dW[vocab, k] (op)= dlogits^T H)
-      if (!trans_b) gemm(*this, true, true, k, vocab, m, hrows, slab, gw.grad, gw.grad_dtype, gw.grad_init);
-      else gemm(*this, true, true, vocab, k, m, slab, hrows, gw.grad, gw.grad_dtype, gw.grad_init);
-      gw.grad_init = true;
+      if (!trans_b) dw_gemm(*this, true, true, k, vocab, m, hrows, slab, w);
+      else dw_gemm(*this, true, true, vocab, k, m, slab, hrows, w);
     }
   }
   if (grads) tensors[h].grad_init = true;
@@ -1115,17 +1350,43 @@ int64_t Graph::attention(int64_t q, int64_t k, int64_t v, int64_t Hq, int64_t Hk
   const int64_t B = tq.shape[0], S = tq.shape[1], D = tq.shape[2] / Hq;
   if (tk.shape[2] != Hkv * D) invalid("attention: k/v width must be kv_heads*head_dim");
   const float scale = 1.0f / std::sqrt((float)D);
-  int64_t o = alloc_pooled(tq.shape);
-  int64_t lse = alloc_pooled_dtype({B, Hq, S}, 0);
+  const size_t o_bytes = (size_t)tq.numel * 2, lse_bytes = (size_t)B * Hq * S * 4;
+  const bool slot_ok = attn_stash_slot >= 0 && attn_stash_slot < (int64_t)attn_stash.size();
+  const bool replay = attn_stash_mode == 2 && slot_ok && attn_stash[(size_t)attn_stash_slot].o &&
+                      attn_stash[(size_t)attn_stash_slot].o_bytes == o_bytes &&
+                      attn_stash[(size_t)attn_stash_slot].lse_bytes == lse_bytes;
+  int64_t o, lse;
+  if (replay) {
+    // the output and log-sum-exp of the first forward pass were kept: adopt them, no kernel
+    AttnStash& st = attn_stash[(size_t)attn_stash_slot];
+    HTensor to_, tl_;
+    to_.shape = tq.shape; to_.numel = tq.numel; to_.dtype = to_.grad_dtype = 1; to_.is_pooled = true; to_.data = st.o;
+    tl_.shape = {B, Hq, S}; tl_.numel = B * Hq * S; tl_.dtype = tl_.grad_dtype = 0; tl_.is_pooled = true; tl_.data = st.lse;
+    st = AttnStash();
+    o = new_tensor(std::move(to_));
+    lse = new_tensor(std::move(tl_));
+  } else {
+    o = alloc_pooled(tq.shape);
+    lse = alloc_pooled_dtype({B, Hq, S}, 0);
+  }
   tensors[lse].constant = true;
   const int64_t qb = S * Hq * D, qs = Hq * D, kb = S * Hkv * D, ks = Hkv * D;
   // flash convention: 4*B*H*S^2*D forward FLOPs, halved under the causal mask; backward 2.5x
   const double attn_flops = 4.0 * (double)B * (double)Hq * (double)S * (double)S * (double)D * (causal ? 0.5 : 1.0);
-  prof_begin(1, attn_flops);
-  ck(eisen_attn_fwd(stream, operand(tensors[q]), operand(tensors[k]), operand(tensors[v]), tensors[o].data,
-                    (float*)tensors[lse].data, B, S, Hq, Hkv, D, qb, qs, D, kb, ks, D, qb, qs, D, scale, causal, status_dev),
-     "attention");
-  prof_end();
+  if (!replay) {
+    prof_begin(1, attn_flops);
+    ck(eisen_attn_fwd(stream, operand(tensors[q]), operand(tensors[k]), operand(tensors[v]), tensors[o].data,
+                      (float*)tensors[lse].data, B, S, Hq, Hkv, D, qb, qs, D, kb, ks, D, qb, qs, D, scale, causal, status_dev),
+       "attention");
+    prof_end();
+    if (attn_stash_mode == 1 && slot_ok) {
+      AttnStash& st = attn_stash[(size_t)attn_stash_slot];
+      if (st.o) pool_put(st.o, st.o_bytes);
+      if (st.lse) pool_put(st.lse, st.lse_bytes);
+      st.o = tensors[o].data; st.lse = tensors[lse].data; st.o_bytes = o_bytes; st.lse_bytes = lse_bytes;
+      tensors[o].data_kept = tensors[lse].data_kept = true;  // popped without returning the buffers
+    }
+  }
   if (!no_grad) {
     tape.push_back({{q, k, v}, o, [this, q, k, v, o, lse, B, S, Hq, Hkv, D, qb, qs, kb, ks, scale, causal, attn_flops]() {
       OUT_GRAD_OR_RETURN(o);

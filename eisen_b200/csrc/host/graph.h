@@ -33,12 +33,23 @@ struct HTensor {
   int grad_dtype = 0;
   bool grad_init = false;  // false: grad holds garbage and stands for zero; first writer overwrites
   bool is_pooled = false;  // activation: buffers return to the pool on restore_save_point
+  bool data_kept = false;  // pooled tensor whose data buffer was handed to Graph::attn_stash: not returned to the pool
   bool owns_data = false;  // free with cudaFree on destruction (non-pooled, non-arena)
   bool owns_grad = false;
   bool is_param = false;
+  // Parameter homed in page-locked host memory that the GPU can address (a "streamed" parameter of
+  // the reference, src/graph/memory.rs:125-170): data, shadow and grad are host pointers; kernels
+  // that read rows or elements use them in place over PCIe, GEMM operands are staged on the device.
+  bool host_homed = false;
   bool grad_is_ones = false;  // the gradient was seeded with ones by backward() and not written since
   bool constant = false;   // no gradient is ever formed (masks, scale tensors, ids)
   std::string name;
+};
+
+// src/graph/memory.rs:7-14
+struct StreamingReport {
+  std::vector<int64_t> resident_param_ids, streamed_param_ids;
+  int64_t resident_bytes = 0, resident_headroom_bytes = 0, streamed_bytes = 0, streaming_headroom_bytes = 0;
 };
 
 struct HNode {
@@ -101,6 +112,40 @@ class Graph {
   // fused GQA attention on the projections' [B,S,H*D] outputs, with backward
   int64_t attention(int64_t q, int64_t k, int64_t v, int64_t num_heads, int64_t num_kv_heads, bool causal);
 
+  // ---- VRAM budget and parameter streaming (src/graph/mod.rs:283-288, src/graph/memory.rs:64-266)
+  // Budget in bytes for everything this graph allocates on the device (0 = none).  Read from
+  // EISEN_VRAM_BUDGET_MB when the graph is created, like the reference.  Activation allocations that
+  // would exceed it first drop the cached pool buffers and then fail with EISEN_ERR_OOM.
+  size_t vram_budget_bytes = 0;
+  size_t activation_reserve_bytes = 64u << 20;  // EISEN_ACTIVATION_RESERVE_MB, default 64
+  size_t current_vram_usage() const { return device_bytes_allocated; }
+  // While set, parameters created by alloc() are homed in host memory (TransformerLM sets it around
+  // the 2-D block weights when a budget is in force, src/nn/transformer.rs:92-101).
+  bool home_params_on_host = false;
+  // The planning arithmetic of plan_streaming only (no tensor is moved): which parameters fit the
+  // budget at 16 bytes per element (weight, gradient, two moments), the rest is streamed.
+  StreamingReport plan_streaming_layout(size_t vram_budget, size_t activation_reserve, const std::vector<int64_t>& pinned) const;
+  // Plans and then re-homes: resident parameters are moved to device memory, streamed ones to host memory.
+  StreamingReport plan_streaming(size_t vram_budget, size_t activation_reserve, const std::vector<int64_t>& pinned);
+  void move_param_to_host(int64_t id);
+  void move_param_to_device(int64_t id);
+  // Device copy of a weight for use as a GEMM operand: the tensor's own buffer, or for a host-homed
+  // parameter a slot of the staging ring filled on the copy stream (prefetch_weight starts that copy
+  // early, at the latest it is started here).  The compute stream is made to wait for the copy.
+  const void* weight_operand(int64_t id);
+  void prefetch_weight(int64_t id);
+  void invalidate_staged_weights() { ++weight_generation_; }
+
+  // Selective recompute for per-block checkpointing: with attn_stash_mode == 1 the fused attention
+  // op hands its output and log-sum-exp buffers to attn_stash[attn_stash_slot] instead of the pool
+  // when its tensors are popped; with mode 2 it adopts the stashed buffers and skips its forward
+  // kernel (the block re-run for the backward pass then recomputes everything except attention).
+  struct AttnStash { void* o = nullptr; void* lse = nullptr; size_t o_bytes = 0, lse_bytes = 0; };
+  std::vector<AttnStash> attn_stash;
+  int attn_stash_mode = 0;
+  int64_t attn_stash_slot = -1;
+  void release_attn_stash();  // returns every stashed buffer to the pool
+
   // ---- helpers used by modules / optimizer
   int act_dtype() const { return precision == Precision::Bf16Mixed ? 1 : 0; }
   void* pool_get(size_t bytes);
@@ -156,6 +201,16 @@ class Graph {
   void* scratch_ = nullptr;
   size_t scratch_bytes_ = 0;
   std::unordered_map<int64_t, float*> rope_tables_;
+  // staging ring for host-homed GEMM operands
+  struct StageSlot { void* buf = nullptr; int64_t id = -1; uint64_t generation = 0; cudaEvent_t ready = nullptr; };
+  std::vector<StageSlot> stage_;
+  size_t stage_slot_bytes_ = 0;
+  size_t stage_next_ = 0;
+  uint64_t weight_generation_ = 1;
+  cudaStream_t copy_stream_ = nullptr;
+  cudaEvent_t compute_mark_ = nullptr;
+  void ensure_stage(size_t bytes);
+  StageSlot* stage_weight(int64_t id);
   int64_t new_tensor(HTensor&& t);
   void free_tensor(HTensor& t);
 };
@@ -201,6 +256,8 @@ class TransformerLM {
   void generate(Graph& g, const int32_t* prompt, int64_t n_prompt, int64_t max_new, int64_t max_context, bool kv_cache,
                 int32_t* out_tokens, float* last_logits);
   std::vector<int64_t> params() const;                            // :198-210
+  // starts the host-to-device copies of block l's host-homed weights (no-op for resident ones)
+  void prefetch_block(Graph& g, int64_t l) const;
   // One micro-step: forward, loss (masked cross-entropy over [B*S] targets), backward.
   // checkpoint = true keeps only block inputs in the forward and re-runs each block under a
   // save point during the backward (the primitives of src/graph/mod.rs:332-365).
@@ -215,6 +272,9 @@ class TransformerLM {
   bool fused = true;  // fused attention / SwiGLU ops (always the reference chain in Fp32 mode when false)
   // train_micro_step: head projection and cross-entropy as one op (Graph::lm_head_cross_entropy)
   // working through head_chunk_rows token rows at a time (0 = all rows at once)
+  // per-block checkpointing keeps the attention output and log-sum-exp of every block (66 MB per
+  // block at 8 x 2048 tokens, d 2048) and does not run the attention forward again in the backward pass
+  bool keep_attention = false;
   bool fused_head = true;
   int64_t head_chunk_rows = 0;
   int64_t emb, norm_f, head;
@@ -261,6 +321,10 @@ class AdamW {
   float* m = nullptr;
   float* v = nullptr;
   std::vector<int64_t> offsets;  // per-parameter offsets into m / v when not flat
+  // not flat: where each parameter's moments live; a host-homed parameter keeps them in host memory
+  // (the reference's streamed parameters are updated by its CPU arm, src/nn/optim.rs:523-543)
+  std::vector<float*> m_ptr, v_ptr;
+  std::vector<float*> host_moments;  // page-locked buffers owned by this optimizer
   int64_t total = 0;
   double* sumsq_dev = nullptr;
   void* sumsq_ws = nullptr;

@@ -76,11 +76,20 @@ TransformerLM::TransformerLM(Graph& g, int64_t vocab_, int64_t hidden_, int64_t 
   if (hidden % heads) throw EisenException(EISEN_ERR_INVALID, "hidden_dim must be cleanly divisible by num_heads");
   if (heads % kv_heads) throw EisenException(EISEN_ERR_INVALID, "num_heads must be divisible by num_kv_heads");
   const int64_t hd = hidden / heads, kvd = kv_heads * hd;
+  // With a VRAM budget in force the 2-D block weights start out in host memory, as the reference
+  // demotes them while it builds the model (src/nn/transformer.rs:92-101); Graph::plan_streaming
+  // decides afterwards which of them move to the device.  Only embedding, norms and head share the arena.
+  const bool budgeted = g.vram_budget_bytes > 0;
   if (!g.arena_w && g.num_params == 0) {
     int64_t total = pad64(vocab * hidden) + pad64(hidden) + (tie ? 0 : pad64(hidden * vocab));
-    total += layers * (2 * pad64(hidden) + 2 * pad64(hidden * hidden) + 2 * pad64(hidden * kvd) + 3 * pad64(hidden * ffn));
+    total += layers * 2 * pad64(hidden);
+    if (!budgeted) total += layers * (2 * pad64(hidden * hidden) + 2 * pad64(hidden * kvd) + 3 * pad64(hidden * ffn));
     g.reserve_param_arena(total);
   }
+  auto block_linear = [&](int64_t in, int64_t out, std::vector<float>& c) {
+    FlagGuard host(g.home_params_on_host, budgeted);
+    return linear_new(g, in, out, c);
+  };
   std::vector<float> cache;
   {
     std::vector<float> e = embedding_init((size_t)vocab * hidden);
@@ -90,14 +99,14 @@ TransformerLM::TransformerLM(Graph& g, int64_t vocab_, int64_t hidden_, int64_t 
   for (int64_t l = 0; l < layers; ++l) {
     BlockParams b;
     b.norm1 = norm_new(g, hidden);
-    b.q = linear_new(g, hidden, hidden, cache);
-    b.k = linear_new(g, hidden, kvd, cache);
-    b.v = linear_new(g, hidden, kvd, cache);
-    b.o = linear_new(g, hidden, hidden, cache);
+    b.q = block_linear(hidden, hidden, cache);
+    b.k = block_linear(hidden, kvd, cache);
+    b.v = block_linear(hidden, kvd, cache);
+    b.o = block_linear(hidden, hidden, cache);
     b.norm2 = norm_new(g, hidden);
-    b.gate = linear_new(g, hidden, ffn, cache);
-    b.up = linear_new(g, hidden, ffn, cache);
-    b.down = linear_new(g, ffn, hidden, cache);
+    b.gate = block_linear(hidden, ffn, cache);
+    b.up = block_linear(hidden, ffn, cache);
+    b.down = block_linear(ffn, hidden, cache);
     blocks.push_back(b);
   }
   norm_f = norm_new(g, hidden);
@@ -113,6 +122,12 @@ std::vector<int64_t> TransformerLM::params() const {
   p.push_back(norm_f);
   if (!tie) p.push_back(head);
   return p;
+}
+
+void TransformerLM::prefetch_block(Graph& g, int64_t l) const {
+  if (l < 0 || l >= layers) return;
+  const BlockParams& b = blocks[(size_t)l];
+  for (int64_t id : {b.q, b.k, b.v, b.o, b.gate, b.up, b.down}) g.prefetch_weight(id);
 }
 
 int64_t TransformerLM::gqa_forward(Graph& g, const BlockParams& b, int64_t x, bool causal, int64_t residual,
@@ -218,7 +233,10 @@ int64_t TransformerLM::block_forward(Graph& g, const BlockParams& b, int64_t x, 
 
 int64_t TransformerLM::forward(Graph& g, int64_t x) {
   int64_t h = g.gather(emb, x);
-  for (const BlockParams& b : blocks) h = block_forward(g, b, h);
+  for (int64_t l = 0; l < layers; ++l) {
+    prefetch_block(g, l + 1);
+    h = block_forward(g, blocks[(size_t)l], h);
+  }
   h = g.rms_norm(h, norm_f, 1e-5f);
   if (tie) return g.matmul_trans_b(h, emb);
   return linear_fwd(g, h, head);
@@ -242,6 +260,12 @@ int64_t TransformerLM::train_micro_step_dev(Graph& g, int64_t x, int64_t target_
   if (g.no_grad) throw EisenException(EISEN_ERR_INVALID, "train_micro_step: graph is in no_grad mode");
   const int64_t n_targets = g.tensors.at(target_ids).numel;
   const int64_t tape0 = (int64_t)g.tape.size();
+  const bool stash = checkpoint && keep_attention && fused;
+  struct StashScope {  // whatever happens, no stashed buffer outlives the step and the mode is off again
+    Graph& g;
+    ~StashScope() { g.attn_stash_mode = 0; g.attn_stash_slot = -1; g.release_attn_stash(); }
+  } stash_scope{g};
+  if (stash) g.attn_stash.resize((size_t)layers);
   int64_t h = g.gather(emb, x);
   const int64_t tape_after_emb = (int64_t)g.tape.size();
   std::vector<int64_t> block_in((size_t)layers);
@@ -249,6 +273,7 @@ int64_t TransformerLM::train_micro_step_dev(Graph& g, int64_t x, int64_t target_
   for (int64_t l = 0; l < layers; ++l) {
     block_in[l] = h;
     block_tape[l] = (int64_t)g.tape.size();
+    prefetch_block(g, l + 1);  // the next block's streamed weights travel while this block computes
     if (checkpoint) {
       // keep only the block output: run the block without a tape under a save point and move
       // its result into a holder allocated before the save point
@@ -257,7 +282,10 @@ int64_t TransformerLM::train_micro_step_dev(Graph& g, int64_t x, int64_t target_
       int64_t r;
       {
         FlagGuard ng(g.no_grad, true);
+        g.attn_stash_mode = stash ? 1 : 0;
+        g.attn_stash_slot = l;
         r = block_forward(g, blocks[l], h);
+        g.attn_stash_mode = 0;
       }
       std::swap(g.tensors[holder].data, g.tensors[r].data);
       g.restore_save_point(sp);
@@ -286,9 +314,13 @@ int64_t TransformerLM::train_micro_step_dev(Graph& g, int64_t x, int64_t target_
   if (checkpoint) {
     int64_t out = h;  // holder of the last block's output; its grad is complete now
     for (int64_t l = layers - 1; l >= 0; --l) {
+      prefetch_block(g, l - 1);
       const int64_t sp = g.mark_save_point();
       const int64_t t0 = (int64_t)g.tape.size();
+      g.attn_stash_mode = stash ? 2 : 0;
+      g.attn_stash_slot = l;
       int64_t y = block_forward(g, blocks[l], block_in[l], true);
+      g.attn_stash_mode = 0;
       // hand the output gradient to the recomputed output
       HTensor& ty = g.tensors[y];
       HTensor& to = g.tensors[out];
@@ -451,7 +483,7 @@ AdamW::AdamW(Graph& g_, std::vector<int64_t> params_, float lr_) : lr(lr_), g(g_
   } else {
     for (int64_t p : params) {
       offsets.push_back(total);
-      total += (g.tensors.at(p).numel + 63) / 64 * 64;
+      if (!g.tensors.at(p).host_homed) total += (g.tensors.at(p).numel + 63) / 64 * 64;
     }
   }
   const size_t bytes = (size_t)std::max<int64_t>(total, 64) * 4;
@@ -459,8 +491,28 @@ AdamW::AdamW(Graph& g_, std::vector<int64_t> params_, float lr_) : lr(lr_), g(g_
   cuck(cudaMalloc(&v, bytes), "cudaMalloc(adam v)");
   cuck(cudaMemsetAsync(m, 0, bytes, g.stream), "memset");
   cuck(cudaMemsetAsync(v, 0, bytes, g.stream), "memset");
+  if (!flat) {
+    for (size_t i = 0; i < params.size(); ++i) {
+      const HTensor& tt = g.tensors[params[i]];
+      if (!tt.host_homed) {
+        m_ptr.push_back(m + offsets[i]);
+        v_ptr.push_back(v + offsets[i]);
+        continue;
+      }
+      for (std::vector<float*>* dst : {&m_ptr, &v_ptr}) {
+        void* hp = nullptr;
+        const size_t hb = (size_t)std::max<int64_t>(tt.numel, 4) * 4;
+        cuck(cudaHostAlloc(&hp, hb, cudaHostAllocMapped | cudaHostAllocPortable), "cudaHostAlloc(adam moments)");
+        std::memset(hp, 0, hb);
+        host_moments.push_back((float*)hp);
+        dst->push_back((float*)hp);
+      }
+    }
+  }
+  int64_t longest = 64;
+  for (int64_t p : params) longest = std::max(longest, g.tensors[p].numel);
   cuck(cudaMalloc(&sumsq_dev, 64), "cudaMalloc(sumsq)");
-  cuck(cudaMalloc(&sumsq_ws, (size_t)eisen_sumsq_workspace_bytes(std::max<int64_t>(total, 64))), "cudaMalloc(sumsq ws)");
+  cuck(cudaMalloc(&sumsq_ws, (size_t)eisen_sumsq_workspace_bytes(std::max<int64_t>(std::max(total, longest), 64))), "cudaMalloc(sumsq ws)");
   g.device_bytes_allocated += 2 * bytes;
 }
 
@@ -515,10 +567,27 @@ void AdamW::step_piece(size_t i, float max_norm, float grad_scale) {
 }
 
 int64_t AdamW::state_elems() const {
-  if (pieces.empty()) return total;
   int64_t n = 0;
-  for (const auto& pc : pieces) n += pc.second - pc.first;
+  if (!pieces.empty()) {
+    for (const auto& pc : pieces) n += pc.second - pc.first;
+    return n;
+  }
+  if (flat) return total;
+  for (int64_t p : params) n += g.tensors[p].numel;
   return n;
+}
+
+namespace {
+struct MomentSegment { float* m; float* v; int64_t n; };
+}
+static std::vector<MomentSegment> moment_segments(const AdamW& o) {
+  std::vector<MomentSegment> segs;
+  if (!o.pieces.empty() || o.flat) {
+    segs.push_back({o.m, o.v, o.state_elems()});
+  } else {
+    for (size_t i = 0; i < o.params.size(); ++i) segs.push_back({o.m_ptr[i], o.v_ptr[i], o.g.tensors[o.params[i]].numel});
+  }
+  return segs;
 }
 
 namespace {
@@ -547,12 +616,16 @@ void AdamW::save_state(const char* path) {
     const int64_t r[2] = {pc.first, pc.second};
     ok = ok && fwrite(r, sizeof(r), 1, f) == 1;
   }
-  std::vector<float> buf((size_t)std::min<int64_t>(h.elems, 1 << 24));
-  for (float* src : {m, v}) {
-    for (int64_t off = 0; off < h.elems && ok; off += (int64_t)buf.size()) {
-      const size_t n = (size_t)std::min<int64_t>((int64_t)buf.size(), h.elems - off);
-      cuck(cudaMemcpy(buf.data(), src + off, n * 4, cudaMemcpyDeviceToHost), "D2H(optimizer state)");
-      ok = fwrite(buf.data(), 4, n, f) == n;
+  std::vector<float> buf((size_t)std::max<int64_t>(std::min<int64_t>(h.elems, 1 << 24), 1));
+  const std::vector<MomentSegment> segs = moment_segments(*this);
+  for (int which = 0; which < 2; ++which) {
+    for (const MomentSegment& sg : segs) {
+      const float* src = which ? sg.v : sg.m;
+      for (int64_t off = 0; off < sg.n && ok; off += (int64_t)buf.size()) {
+        const size_t n = (size_t)std::min<int64_t>((int64_t)buf.size(), sg.n - off);
+        cuck(cudaMemcpy(buf.data(), src + off, n * 4, cudaMemcpyDefault), "D2H(optimizer state)");
+        ok = fwrite(buf.data(), 4, n, f) == n;
+      }
     }
   }
   ok = (fclose(f) == 0) && ok;
@@ -574,12 +647,16 @@ void AdamW::load_state(const char* path) {
       throw EisenException(EISEN_ERR_INVALID, "optimizer load_state: the file's ranges differ from this rank's");
   }
   cuck(cudaStreamSynchronize(g.stream), "sync");
-  std::vector<float> buf((size_t)std::min<int64_t>(h.elems, 1 << 24));
-  for (float* dst : {m, v}) {
-    for (int64_t off = 0; off < h.elems; off += (int64_t)buf.size()) {
-      const size_t n = (size_t)std::min<int64_t>((int64_t)buf.size(), h.elems - off);
-      if (fread(buf.data(), 4, n, f) != n) throw EisenException(EISEN_ERR_INVALID, "optimizer load_state: short read");
-      cuck(cudaMemcpy(dst + off, buf.data(), n * 4, cudaMemcpyHostToDevice), "H2D(optimizer state)");
+  std::vector<float> buf((size_t)std::max<int64_t>(std::min<int64_t>(h.elems, 1 << 24), 1));
+  const std::vector<MomentSegment> segs = moment_segments(*this);
+  for (int which = 0; which < 2; ++which) {
+    for (const MomentSegment& sg : segs) {
+      float* dst = which ? sg.v : sg.m;
+      for (int64_t off = 0; off < sg.n; off += (int64_t)buf.size()) {
+        const size_t n = (size_t)std::min<int64_t>((int64_t)buf.size(), sg.n - off);
+        if (fread(buf.data(), 4, n, f) != n) throw EisenException(EISEN_ERR_INVALID, "optimizer load_state: short read");
+        cuck(cudaMemcpy(dst + off, buf.data(), n * 4, cudaMemcpyDefault), "H2D(optimizer state)");
+      }
     }
   }
   t = h.t;
@@ -592,6 +669,7 @@ AdamW::~AdamW() {
   cudaFree(v);
   cudaFree(sumsq_dev);
   cudaFree(sumsq_ws);
+  for (float* p : host_moments) cudaFreeHost(p);
 }
 
 void AdamW::zero_grad() {
@@ -649,10 +727,11 @@ void AdamW::launch(float grad_scale, const double* sumsq, float max_norm) {
   }
   for (size_t i = 0; i < params.size(); ++i) {
     HTensor& tt = g.tensors[params[i]];
-    ck(eisen_adamw_step(g.stream, (float*)tt.data, tt.shadow, (const float*)tt.grad, m + offsets[i], v + offsets[i],
+    ck(eisen_adamw_step(g.stream, (float*)tt.data, tt.shadow, (const float*)tt.grad, m_ptr[i], v_ptr[i],
                         tt.numel, lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale, sumsq, max_norm),
        "adamw_step");
   }
+  g.invalidate_staged_weights();  // staged copies of host-homed weights are stale now
 }
 
 void AdamW::step() { launch(1.0f, nullptr, 0.0f); }

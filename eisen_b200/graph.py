@@ -40,6 +40,27 @@ class Graph:
         except Exception:
             pass
 
+    def set_vram_budget(self, budget_bytes, activation_reserve_bytes=64 << 20):
+        """Budget for everything the graph allocates on the device; set it before building the model."""
+        call("eisen_graph_set_vram_budget", self._h, int(budget_bytes), int(activation_reserve_bytes))
+
+    def vram_usage(self):
+        u, b = C.c_longlong(), C.c_longlong()
+        call("eisen_graph_vram_usage", self._h, C.byref(u), C.byref(b))
+        return u.value, b.value
+
+    def plan_streaming(self, budget_bytes, activation_reserve_bytes, pinned_ids, apply=True):
+        """Graph::plan_streaming (src/graph/memory.rs:64-187); returns the report as a dict."""
+        n = self.counts()[2]
+        res, stm = (C.c_longlong * max(1, n))(), (C.c_longlong * max(1, n))()
+        nr, ns = C.c_int(), C.c_int()
+        b4 = (C.c_longlong * 4)()
+        call("eisen_graph_plan_streaming", self._h, int(budget_bytes), int(activation_reserve_bytes), _ll(pinned_ids),
+             len(pinned_ids), 1 if apply else 0, res, C.byref(nr), stm, C.byref(ns), b4)
+        return {"resident_param_ids": [res[i] for i in range(nr.value)], "streamed_param_ids": [stm[i] for i in range(ns.value)],
+                "resident_bytes": b4[0], "resident_headroom_bytes": b4[1], "streamed_bytes": b4[2],
+                "streaming_headroom_bytes": b4[3]}
+
     def _op(self, name, *args):
         out = C.c_longlong(-1)
         call("eisen_graph_" + name, self._h, *args, C.byref(out))
@@ -247,6 +268,10 @@ class TransformerLM:
 
     def set_fused(self, flag):
         call("eisen_lm_set_fused", self._h, 1 if flag else 0)
+
+    def set_keep_attention(self, keep=True):
+        """Checkpointed steps keep each block's attention output + log-sum-exp instead of recomputing them."""
+        call("eisen_lm_set_keep_attention", self._h, 1 if keep else 0)
 
     def set_head_fusion(self, fused=True, chunk_rows=0):
         """Head projection + cross-entropy as one chunked op in train_micro_step (default on)."""

@@ -138,6 +138,11 @@ int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, vo
                    long long S, long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss,
                    long long q_hs, long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs,
                    long long o_ss, long long o_hs, float scale, int causal, int* status);
+/* Share of the head_dim-64 forward's exponentials that run as a degree-3 polynomial on the FMA pipe
+ * instead of on the special-function unit, in eighths: 0 (none) .. 4 (half).  The polynomial's
+ * relative error (7.5e-5) is far below the bf16 rounding of the probabilities.  Process-wide; meant
+ * for tests and measurements. */
+int eisen_attn_set_poly_exp(int level);
 long long eisen_attn_bwd_workspace_bytes(long long B, long long S, long long Hq, long long Hkv, long long D);
 /* dq, dk, dv are written (not accumulated); they use the strides of q and k/v respectively. */
 int eisen_attn_bwd(void* stream, const void* q, const void* k, const void* v, const void* o, const float* lse,
@@ -306,6 +311,27 @@ typedef void (*eisen_block_cb)(long long layer, void* user);
 
 int eisen_graph_create(int precision, void* stream, void** out);                       /* Graph::new, src/graph/mod.rs:152-307 */
 int eisen_graph_destroy(void* g);
+/* VRAM budget and parameter streaming (src/graph/mod.rs:283-288, src/graph/memory.rs:64-266).
+ * A graph created while EISEN_VRAM_BUDGET_MB is set (or given a budget here before the model is
+ * built) counts every device byte it allocates against the budget: an activation allocation that
+ * would exceed it first drops the cached pool buffers and then fails with EISEN_ERR_OOM (the
+ * reference panics).  A TransformerLM built under a budget homes its 2-D block weights in
+ * page-locked host memory (src/nn/transformer.rs:92-101).
+ * eisen_graph_plan_streaming is Graph::plan_streaming: parameters cost 16 bytes per element
+ * (weight, gradient, two moments); pinned ones stay on the device, the others are taken in id order
+ * while they fit budget - reserve - pinned, then the largest resident ones give way until the
+ * largest streamed tensor has room to pass through.  apply = 0 only reports; apply = 1 also moves
+ * resident parameters to device memory and streamed ones to host memory.  Streamed weights are GEMM
+ * operands through a ring of device staging buffers filled on a copy stream (started a block ahead
+ * by the model) instead of the reference's blocking upload inside every matmul
+ * (src/graph/ops/linear.rs:804-807); their gradients and AdamW moments stay in host memory.
+ * Outputs (any may be null): resident ids (pinned first), streamed ids, bytes4 = resident bytes,
+ * resident headroom, streamed f32 bytes, streaming headroom (the largest streamed tensor). */
+int eisen_graph_set_vram_budget(void* g, long long budget_bytes, long long activation_reserve_bytes);
+int eisen_graph_vram_usage(void* g, long long* used_bytes, long long* budget_bytes);
+int eisen_graph_plan_streaming(void* g, long long budget_bytes, long long activation_reserve_bytes, const long long* pinned,
+                               int n_pinned, int apply, long long* resident_ids, int* n_resident, long long* streamed_ids,
+                               int* n_streamed, long long* bytes4);
 int eisen_graph_alloc(void* g, const long long* shape, int ndim, const float* host_data, long long* id_out); /* Graph::alloc */
 int eisen_graph_alloc_ids(void* g, const long long* shape, int ndim, const int* host_ids, long long* id_out); /* int32 token ids */
 int eisen_graph_alloc_pooled(void* g, const long long* shape, int ndim, long long* id_out);  /* Graph::alloc_pooled, :437-556 */
@@ -375,6 +401,12 @@ int eisen_lm_create(void* g, long long vocab, long long hidden, long long heads,
                     long long layers, int tie_weights, void** out);
 int eisen_lm_destroy(void* lm);
 int eisen_lm_set_fused(void* lm, int fused);   /* 0: the reference's op-by-op attention / MLP chain */
+/* eisen_lm_train_micro_step[_dev] with checkpoint != 0: keep != 0 keeps every block's attention
+ * output and log-sum-exp from the first forward pass (2 bytes per activation element plus 4 bytes
+ * per head and token) and leaves the attention forward out of the block's re-run; everything else
+ * of the block is recomputed.  Default 0: the whole block is recomputed, as the reference's
+ * mark_save_point / restore_save_point loop does. */
+int eisen_lm_set_keep_attention(void* lm, int keep);
 /* eisen_lm_train_micro_step[_dev]: fused != 0 (default) runs head projection and cross-entropy as
  * eisen_graph_lm_head_cross_entropy in chunks of chunk_rows token rows (0 = all rows at once);
  * fused == 0 runs matmul + cross_entropy_masked as the reference does. */

@@ -528,3 +528,21 @@ def test_bf16_step_head_paths_match_oracle(fused_head, chunk):
     tg[:, ::9] = -1
     res = run_step(og, olm, g, lm, CFG_BF16, ids, tg, masked=True, checkpoint=True, use_micro_step=True)
     _check(res, 2e-2, 1e-3)
+
+
+def test_bf16_checkpointed_step_with_kept_attention_output():
+    """Per-block checkpointing that keeps each block's attention output and log-sum-exp instead of
+    running the attention forward again: same gradients as the full re-run (up to the order of the
+    f32 atomic adds of the split-k weight gradients), same parity with the oracle, no buffer leaked."""
+    ids, tg = _tokens(CFG_BF16, 11)
+    grads, live = [], []
+    for keep in (False, True):
+        og, olm, g, lm = build_pair(CFG_BF16, BF16_MIXED, seed=11)
+        lm.set_keep_attention(keep)
+        res = run_step(og, olm, g, lm, CFG_BF16, ids, tg, checkpoint=True, use_micro_step=True)
+        _check(res, 2e-2, 1e-3)
+        grads.append(res["grads"])
+        live.append(g.pool_stats()["live_bytes"])
+    for a, b in zip(*grads):
+        assert rel_l2(b, a) < 1e-3
+    assert live[0] == live[1]  # every pooled buffer, the stashed ones included, went back to the pool
