@@ -289,6 +289,9 @@ class Runner:
                 self.opt = ShardedAdamW(g, self.params, 3e-4, self.reducer.pieces())
                 self.opt.config(3e-4, 0.9, 0.95, 1e-8, 0.1)
                 self.sharded = True
+                if not args.no_gather_overlap:
+                    # the forward pass waits per block for the all-gather of the weights it is about to read
+                    lm.set_forward_hook(lambda l: self.reducer.wait_for_block(l, self.compute))
             else:
                 self.reducer = edp.BucketedAllReduce(flat, buckets, backend=backend, handshake=hs)
             eb.call("eisen_gemm_reserve_sms", args.comm_sms)
@@ -329,7 +332,7 @@ class Runner:
                 self.last_loss = float(g.data(loss)[0])  # D2H read of the step's loss
             g.clear_activations()
         if self.sharded:
-            self.reducer.finish_and_step(self.opt, self.clip, self.compute)
+            self.reducer.finish_and_step(self.opt, self.clip, self.compute, overlap=not self.args.no_gather_overlap)
             return
         if self.reducer is not None:
             self.reducer.finish(self.compute)
@@ -355,6 +358,9 @@ class Runner:
         return float(ms.item())
 
     def close(self):
+        if self.sharded:
+            self.reducer.wait_all(self.compute)
+            self.lm.set_forward_hook(None)
         self.g.synchronize()
         self.feeder = None
         self.reducer = None
@@ -486,6 +492,17 @@ def run_ours(args, cfg, name):
     g.prof_enable(False)
     g.synchronize()
 
+    # ---- variant: per-block checkpointing that keeps each block's attention output and log-sum-exp
+    # (66 MB per block here) instead of running the attention forward again in the backward pass
+    ms_keep = None
+    if r.checkpoint and not args.no_variants:
+        r.lm.set_keep_attention(True)
+        for it in range(2):
+            r.step(False, it)
+        ms_keep = r.timed(False, args.steps)
+        r.lm.set_keep_attention(False)
+        g.synchronize()
+
     step_tokens = B * S * accum * world
     tps = step_tokens * args.steps / (ms_total / 1e3)
     tps_e2e = step_tokens * args.steps / (ms_e2e / 1e3)
@@ -529,6 +546,12 @@ def run_ours(args, cfg, name):
             "kernels": kernels,
             "clocks": clocks,
         }
+        if ms_keep is not None:
+            out["variants"] = {"keep_attention_output": {
+                "what": "per-block checkpointing that keeps every block's attention output and log-sum-exp from the first "
+                        "forward pass and recomputes the rest of the block (`value` recomputes the whole block)",
+                "ms_per_step": ms_keep / args.steps, "tokens_per_s": step_tokens * args.steps / (ms_keep / 1e3),
+                "mfu_of_nominal_2250_tflops": step_tokens * args.steps / (ms_keep / 1e3) / world * fpt / (NOMINAL_BF16_TFLOPS * 1e12)}}
     r.close()
     del r, g
     if rank == 0 and world == 1 and not args.no_cases:
@@ -566,9 +589,12 @@ def main():
     ap.add_argument("--data", default=None, help="u16 token file for the e2e leg (default: synthetic ids)")
     ap.add_argument("--comm-sms", type=int, default=0, help="SMs the GEMMs leave free for NCCL when N > 1 (measured at 8 GPUs: 0 is best)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-variants", action="store_true", help="skip the kept-attention-output variant")
     ap.add_argument("--no-cases", action="store_true", help="skip the other benchmark configurations (N = 1 only)")
     ap.add_argument("--bucket-mb", type=int, default=256)
-    ap.add_argument("--exchange", default="allreduce", choices=["allreduce", "zero1"],
+    ap.add_argument("--no-gather-overlap", action="store_true",
+                    help="zero1: wait for the whole weight all-gather after the optimizer instead of per block in the next forward")
+    ap.add_argument("--exchange", default="zero1", choices=["allreduce", "zero1"],
                     help="N > 1: all-reduce of gradient buckets with replicated AdamW, or reduce-scatter + sharded AdamW + all-gather")
     ap.add_argument("--backend", default="abi", choices=["abi", "torch"],
                     help="N > 1: collectives through the library's eisen_dp_* C ABI over NCCL, or through torch.distributed")

@@ -237,6 +237,13 @@ int eisen_lm_destroy(void* lm) {
 int eisen_lm_set_fused(void* lm, int fused) {
   return guarded([&] { static_cast<TransformerLM*>(lm)->fused = fused != 0; });
 }
+int eisen_lm_set_forward_hook(void* lm, eisen_block_cb before_block, void* user) {
+  return guarded([&] {
+    TransformerLM* m = static_cast<TransformerLM*>(lm);
+    if (before_block) m->before_block = [before_block, user](int64_t l) { before_block((long long)l, user); };
+    else m->before_block = nullptr;
+  });
+}
 int eisen_lm_set_keep_attention(void* lm, int keep) {
   return guarded([&] { static_cast<TransformerLM*>(lm)->keep_attention = keep != 0; });
 }

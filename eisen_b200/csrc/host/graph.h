@@ -275,6 +275,10 @@ class TransformerLM {
   // per-block checkpointing keeps the attention output and log-sum-exp of every block (66 MB per
   // block at 8 x 2048 tokens, d 2048) and does not run the attention forward again in the backward pass
   bool keep_attention = false;
+  // called in train_micro_step before the forward pass first touches the parameters of block l
+  // (l == -1: embedding, l == layers: final norm and head); a sharded data-parallel step uses it to
+  // wait for the all-gather of exactly those weights instead of for all of them up front
+  std::function<void(int64_t)> before_block;
   bool fused_head = true;
   int64_t head_chunk_rows = 0;
   int64_t emb, norm_f, head;

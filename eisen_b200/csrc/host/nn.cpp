@@ -266,6 +266,7 @@ int64_t TransformerLM::train_micro_step_dev(Graph& g, int64_t x, int64_t target_
     ~StashScope() { g.attn_stash_mode = 0; g.attn_stash_slot = -1; g.release_attn_stash(); }
   } stash_scope{g};
   if (stash) g.attn_stash.resize((size_t)layers);
+  if (before_block) before_block(-1);
   int64_t h = g.gather(emb, x);
   const int64_t tape_after_emb = (int64_t)g.tape.size();
   std::vector<int64_t> block_in((size_t)layers);
@@ -273,6 +274,7 @@ int64_t TransformerLM::train_micro_step_dev(Graph& g, int64_t x, int64_t target_
   for (int64_t l = 0; l < layers; ++l) {
     block_in[l] = h;
     block_tape[l] = (int64_t)g.tape.size();
+    if (before_block) before_block(l);
     prefetch_block(g, l + 1);  // the next block's streamed weights travel while this block computes
     if (checkpoint) {
       // keep only the block output: run the block without a tape under a save point and move
@@ -295,6 +297,7 @@ int64_t TransformerLM::train_micro_step_dev(Graph& g, int64_t x, int64_t target_
     }
   }
   block_tape[layers] = (int64_t)g.tape.size();
+  if (before_block) before_block(layers);
   int64_t hn = g.rms_norm(h, norm_f, 1e-5f);
   // src/graph/ops/reduction.rs:724-737: mean over the valid rows; all rows masked -> loss 0, no gradient
   const float normalizer = n_valid > 0 ? 1.0f / (float)n_valid : 0.0f;

@@ -172,6 +172,8 @@ class NcclAbiBackend:
     The 128-byte unique id travels through `exchange_id`, a callable that takes rank 0's bytes (or
     None on the other ranks) and returns rank 0's bytes on every rank."""
 
+    stream_ordered = True  # every collective runs on comm_stream itself: an event recorded there covers it
+
     def __init__(self, rank, world, comm_stream, exchange_id):
         self.rank, self.world, self.comm_stream = rank, world, comm_stream
         buf = (C.c_char * 128)()
@@ -383,10 +385,13 @@ class ShardedExchange(_Exchange):
             optimizer.sumsq_piece(self.order.index(key), not self._first, self.comm_stream)
             self._first = False
 
-    def finish_and_step(self, optimizer, max_norm, compute_stream=None, deadline_s=None):
-        """Squared-norm all-reduce, the optimizer on this rank's pieces (in forward order, so the
-        first weights the next forward needs are gathered first), all-gather of the updated
-        weights behind each piece's update, broadcast of the exact (f32) ranges."""
+    def finish_and_step(self, optimizer, max_norm, compute_stream=None, deadline_s=None, overlap=False):
+        """Squared-norm all-reduce, the optimizer on this rank's pieces, broadcast of the exact (f32)
+        ranges, then the all-gather of the updated weights bucket by bucket in forward order.
+        overlap=False: the compute stream waits for all of it.  overlap=True (stream-ordered
+        backends): it waits for nothing here; wait_for_block(l), called from the model's forward
+        hook, makes it wait for exactly the bucket block l reads, so the gathers of later blocks run
+        beside the next step's forward pass."""
         self._first = True
         if self.world > 1:
             if max_norm > 0.0:
@@ -395,29 +400,65 @@ class ShardedExchange(_Exchange):
             self._handshake()
         self.backend.wait(compute_stream, deadline_s)
         optimizer.begin_step()
-        for key in reversed(self.order):
-            i = self.order.index(key)
+        for i in range(len(self.order)):
             optimizer.step_piece(i, max_norm, self.grad_scale())
-            if self.world > 1:
-                a, b = self.buckets[key]
-                lo, hi = self.piece(key)
-                self._comm_waits_for_compute(compute_stream)
-                self.backend.all_gather(self.gather[a:b], self.gather[lo:hi])
-        if self.world > 1 and self.exact and self.flat_w is not None:
-            self._comm_waits_for_compute(compute_stream)
+        if self.world == 1:
+            return
+        overlap = overlap and self.cuda and getattr(self.backend, "stream_ordered", False)
+        self._comm_waits_for_compute(compute_stream)
+        self._gather_events = {}
+        if self.exact and self.flat_w is not None:
             self.backend.group_begin()
             for x, y, r in self.exact:
                 self.backend.broadcast(self.flat_w[x:y], r)
             self.backend.group_end()
-        if self.world > 1:
+        for key in reversed(self.order):  # forward order: embedding, blocks from first to last, final norm + head
+            a, b = self.buckets[key]
+            lo, hi = self.piece(key)
+            self.backend.all_gather(self.gather[a:b], self.gather[lo:hi])
+            if overlap:
+                ev = torch.cuda.Event()
+                ev.record(self.comm_stream)
+                self._gather_events[key] = ev
+        if not overlap:
             self.backend.wait(compute_stream, deadline_s)
-            self._launched0 = self.backend.launched
+        self._launched0 = self.backend.launched
+
+    def wait_for_block(self, l, compute_stream):
+        """Forward hook of an overlapped step: block l (-1 embedding, `layers` final norm + head) is
+        about to read its weights; wait for the gather of the bucket that holds them."""
+        evs = getattr(self, "_gather_events", None)
+        if not evs:
+            return
+        block_keys = sorted(k for k in self.order if 0 <= k < max(self.order))
+        if l < 0:
+            key = -1
+        elif l >= max(self.order):
+            key = max(self.order)
+        else:
+            key = max([k for k in block_keys if k <= l], default=block_keys[0])
+        # buckets were gathered in forward order on one stream: waiting for this one covers the earlier ones
+        ev = evs.pop(key, None)
+        if ev is not None:
+            compute_stream.wait_event(ev)
+            for k in [k for k in evs if k < key]:
+                evs.pop(k)
+
+    def wait_all(self, compute_stream):
+        """Makes the compute stream wait for every outstanding gather (end of training, checkpoints)."""
+        evs = getattr(self, "_gather_events", None)
+        if evs:
+            for ev in evs.values():
+                compute_stream.wait_event(ev)
+            evs.clear()
 
     def gather_master(self, compute_stream=None):
         """All-gathers the f32 master weights (for a checkpoint: under ZeRO-1 a rank's master copy
         is current only inside its own pieces)."""
         if self.world == 1 or self.flat_w is None:
             return
+        if compute_stream is not None:
+            self.wait_all(compute_stream)
         self._comm_waits_for_compute(compute_stream)
         for key in self.order:
             a, b = self.buckets[key]

@@ -269,6 +269,12 @@ class TransformerLM:
     def set_fused(self, flag):
         call("eisen_lm_set_fused", self._h, 1 if flag else 0)
 
+    def set_forward_hook(self, before_block):
+        """before_block(l) runs before the forward pass first reads block l's parameters (-1: embedding,
+        layers: final norm and head)."""
+        self._fwd_cb = BLOCK_CB(lambda layer, user: before_block(layer)) if before_block else None
+        call("eisen_lm_set_forward_hook", self._h, C.cast(self._fwd_cb, C.c_void_p) if self._fwd_cb else None, None)
+
     def set_keep_attention(self, keep=True):
         """Checkpointed steps keep each block's attention output + log-sum-exp instead of recomputing them."""
         call("eisen_lm_set_keep_attention", self._h, 1 if keep else 0)

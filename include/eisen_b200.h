@@ -401,6 +401,11 @@ int eisen_lm_create(void* g, long long vocab, long long hidden, long long heads,
                     long long layers, int tie_weights, void** out);
 int eisen_lm_destroy(void* lm);
 int eisen_lm_set_fused(void* lm, int fused);   /* 0: the reference's op-by-op attention / MLP chain */
+/* before_block(l, user) is called inside eisen_lm_train_micro_step[_dev] just before the forward
+ * pass first reads the parameters of block l (l == -1: embedding, l == layers: final norm and
+ * head); it may make the graph's stream wait for work on other streams (a sharded data-parallel
+ * step waits here for the all-gather of those weights).  Null removes the hook. */
+int eisen_lm_set_forward_hook(void* lm, eisen_block_cb before_block, void* user);
 /* eisen_lm_train_micro_step[_dev] with checkpoint != 0: keep != 0 keeps every block's attention
  * output and log-sum-exp from the first forward pass (2 bytes per activation element plus 4 bytes
  * per head and token) and leaves the attention forward out of the block's re-run; everything else

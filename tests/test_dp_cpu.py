@@ -254,7 +254,9 @@ def _failing_worker(rank, world, port, out, mode):
                 # the rank leaves between steps, with nothing of its own in flight
                 _put_and_exit(out, (rank, "left"))
             if mode == "skip" and rank == 1 and step == 1:
-                red.skip_keys = {1}  # host-side fault: this rank forgets block 1's bucket
+                # host-side fault: this rank forgets its last bucket (the embedding's), so the peer is
+                # left with one all-reduce that nobody answers
+                red.skip_keys = {-1}
             for key in BACKWARD_ORDER:
                 red.on_block_done(key)
             t0 = __import__("time").monotonic()
