@@ -357,6 +357,58 @@ int eisen_swiglu_fwd(void* stream, const void* gate, const void* up, void* out, 
   });
 }
 
+}  // extern "C"
+
+namespace eisen {
+namespace {
+// Five streams (three read, two written).  With one 16-byte vector per thread and iteration the
+// kernel waits on memory most of the time (long-scoreboard stalls, 36 % issue utilisation): here a
+// thread requests two vectors of each input before it touches the first.
+template <typename T, bool ACC>
+__global__ void __launch_bounds__(EW_THREADS)
+swiglu_bwd_kernel(const T* __restrict__ pg, const T* __restrict__ pu, const T* __restrict__ ph, T* __restrict__ pdg,
+                  T* __restrict__ pdu, long long nvec) {
+  constexpr int V = VecOf<T>::N;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long v0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; v0 < nvec; v0 += 2 * stride) {
+    const long long v1 = v0 + stride;
+    const bool two = v1 < nvec;
+    const long long i0 = v0 * V, i1 = (two ? v1 : v0) * V;
+    float g0[V], u0[V], h0[V], g1[V], u1[V], h1[V];
+    ld16(pg + i0, g0); ld16(pu + i0, u0); ld16(ph + i0, h0);
+    ld16(pg + i1, g1); ld16(pu + i1, u1); ld16(ph + i1, h1);
+    float a0[V], b0[V], a1[V], b1[V];
+    if (ACC) { ld16(pdg + i0, a0); ld16(pdu + i0, b0); ld16(pdg + i1, a1); ld16(pdu + i1, b1); }
+    float dg[V], du[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const float sig = sigmoid_t<T>(g0[k]);
+      const float silu = g0[k] * sig;
+      du[k] = h0[k] * silu;
+      dg[k] = (h0[k] * u0[k]) * (silu + sig * (1.0f - silu));
+      if (ACC) { dg[k] += a0[k]; du[k] += b0[k]; }
+    }
+    st16(pdg + i0, dg);
+    st16(pdu + i0, du);
+    if (two) {
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        const float sig = sigmoid_t<T>(g1[k]);
+        const float silu = g1[k] * sig;
+        du[k] = h1[k] * silu;
+        dg[k] = (h1[k] * u1[k]) * (silu + sig * (1.0f - silu));
+        if (ACC) { dg[k] += a1[k]; du[k] += b1[k]; }
+      }
+      st16(pdg + i1, dg);
+      st16(pdu + i1, du);
+    }
+  }
+}
+}  // namespace
+}  // namespace eisen
+
+extern "C" {
+
 // dgate (+)= dh*up*silu'(gate) ; dup (+)= dh*silu(gate): one pass instead of mul_bwd + silu_bwd
 int eisen_swiglu_bwd(void* stream, const void* gate, const void* up, const void* dh, void* dgate, void* dup,
                      long long n, int dt, int accumulate) {
@@ -366,6 +418,13 @@ int eisen_swiglu_bwd(void* stream, const void* gate, const void* up, const void*
     const T* pg = (const T*)gate; const T* pu = (const T*)up; const T* ph = (const T*)dh;
     T* pdg = (T*)dgate; T* pdu = (T*)dup;
     const bool acc = accumulate != 0;
+    if (n % V == 0) {
+      const long long nvec = n / V;
+      const int grid = grid_for((nvec + 1) / 2, EW_THREADS, 4);
+      if (acc) swiglu_bwd_kernel<T, true><<<grid, EW_THREADS, 0, (cudaStream_t)stream>>>(pg, pu, ph, pdg, pdu, nvec);
+      else swiglu_bwd_kernel<T, false><<<grid, EW_THREADS, 0, (cudaStream_t)stream>>>(pg, pu, ph, pdg, pdu, nvec);
+      return check_launch("swiglu_bwd");
+    }
     return launch_vec<V>((cudaStream_t)stream, n, [=] __device__(long long i, int c) {
       float g[V], u[V], h[V], dg[V], du[V];
       load_n(pg + i, g, c);

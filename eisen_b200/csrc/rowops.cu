@@ -163,6 +163,10 @@ __device__ __forceinline__ uint4 ld_stream16(const T* p) {
   return r;
 }
 
+#ifndef EISEN_RMS_BWD_PACKED
+#define EISEN_RMS_BWD_PACKED 1
+#endif
+constexpr bool RMS_BWD_PACKED = EISEN_RMS_BWD_PACKED != 0;
 constexpr int RB_THREADS = 256;
 constexpr int RB_ROWS = 4;
 
@@ -234,13 +238,23 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w, const T
         float xv[V], gv[V];
         unpack16(xr[r][j], xv);
         unpack16(gr[r][j], gv);
-        // packed f32x2 arithmetic: the kernel is bound by instruction issue, not by memory
+        if (RMS_BWD_PACKED) {
+          // packed f32x2 arithmetic
 #pragma unroll
-        for (int k = 0; k < V; k += 2) {
-          float t0, t1;
-          ffma2(ss, ss1, xv[k], xv[k + 1], xv[k], xv[k + 1], ss, ss1);
-          fmul2(t0, t1, gv[k], gv[k + 1], xv[k], xv[k + 1]);
-          ffma2(gd, gd1, t0, t1, wv[j][k], wv[j][k + 1], gd, gd1);
+          for (int k = 0; k < V; k += 2) {
+            float t0, t1;
+            ffma2(ss, ss1, xv[k], xv[k + 1], xv[k], xv[k + 1], ss, ss1);
+            fmul2(t0, t1, gv[k], gv[k + 1], xv[k], xv[k + 1]);
+            ffma2(gd, gd1, t0, t1, wv[j][k], wv[j][k + 1], gd, gd1);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < V; k += 2) {
+            ss = fmaf(xv[k], xv[k], ss);
+            ss1 = fmaf(xv[k + 1], xv[k + 1], ss1);
+            gd = fmaf(gv[k] * wv[j][k], xv[k], gd);
+            gd1 = fmaf(gv[k + 1] * wv[j][k + 1], xv[k + 1], gd1);
+          }
         }
       }
       part[2 * r] = ss + ss1;
@@ -305,14 +319,22 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w, const T
             unpack16(xr[r][j], xv);
             unpack16(gr[r][j], gv);
             const float ncoef = -coef;
+            if (RMS_BWD_PACKED) {
 #pragma unroll
-            for (int k = 0; k < V; k += 2) {
-              float a0, a1, b0, b1, t0, t1;
-              fmul2(a0, a1, gv[k], gv[k + 1], wv[j][k], wv[j][k + 1]);
-              fmul2(b0, b1, xv[k], xv[k + 1], ncoef, ncoef);
-              ffma2(o[k], o[k + 1], a0, a1, rrms, rrms, b0, b1);
-              fmul2(t0, t1, gv[k], gv[k + 1], xv[k], xv[k + 1]);
-              ffma2(dwp[j][k], dwp[j][k + 1], t0, t1, rrms, rrms, dwp[j][k], dwp[j][k + 1]);
+              for (int k = 0; k < V; k += 2) {
+                float a0, a1, b0, b1, t0, t1;
+                fmul2(a0, a1, gv[k], gv[k + 1], wv[j][k], wv[j][k + 1]);
+                fmul2(b0, b1, xv[k], xv[k + 1], ncoef, ncoef);
+                ffma2(o[k], o[k + 1], a0, a1, rrms, rrms, b0, b1);
+                fmul2(t0, t1, gv[k], gv[k + 1], xv[k], xv[k + 1]);
+                ffma2(dwp[j][k], dwp[j][k + 1], t0, t1, rrms, rrms, dwp[j][k], dwp[j][k + 1]);
+              }
+            } else {
+#pragma unroll
+              for (int k = 0; k < V; ++k) {
+                o[k] = fmaf(gv[k] * wv[j][k], rrms, xv[k] * ncoef);
+                dwp[j][k] = fmaf(gv[k] * xv[k], rrms, dwp[j][k]);
+              }
             }
             T* dr = dx + (r0 + r) * dim + c;
             if (acc_dx) {
