@@ -29,8 +29,8 @@ namespace {
 
 constexpr float LOG2E = 1.4426950408889634f;
 
-// share of the forward's exponentials taken by the FMA-pipe polynomial, in eighths (0..4)
-std::atomic<int> g_attn_poly_level{0};
+// query tiles per CTA of the head_dim-64 forward: 1 (two CTAs per SM) or 2 (one CTA per SM)
+std::atomic<int> g_attn_fwd_tiles{1};
 
 struct AttnParams {
   int B, S, Hq, Hkv, D;
@@ -70,25 +70,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-}
-
-// 2^x for two values on the FMA pipe instead of the special-function unit: x = n + f with n the
-// nearest integer and f in [-0.5, 0.5]; 2^f by a degree-3 polynomial (maximum relative error
-// 7.5e-5, far below the bf16 rounding of the probabilities), n added into the exponent field.
-// Inputs must be <= 127; values below -126 give 2^-126 (the callers use it for unmasked scores).
-__device__ __forceinline__ void ex2_poly2(float& x0, float& x1) {
-  constexpr float MAGIC = 12582912.0f;  // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
-  x0 = fmaxf(x0, -126.0f);
-  x1 = fmaxf(x1, -126.0f);
-  float t0, t1, n0, n1, f0, f1, p0, p1;
-  fadd2(t0, t1, x0, x1, MAGIC, MAGIC);
-  fadd2(n0, n1, t0, t1, -MAGIC, -MAGIC);
-  ffma2(f0, f1, n0, n1, -1.0f, -1.0f, x0, x1);
-  ffma2(p0, p1, f0, f1, 0.05517167f, 0.05517167f, 0.24261114f, 0.24261114f);
-  ffma2(p0, p1, p0, p1, f0, f1, 0.69326099f, 0.69326099f);
-  ffma2(p0, p1, p0, p1, f0, f1, 0.99992807f, 0.99992807f);
-  x0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
-  x1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
 }
 
 template <int D>
@@ -454,29 +435,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 //     and only then, O is read, scaled and written back.  P <= 2^8 keeps bf16 P and the f32 row sum
 //     exact enough, and the final O / l does not depend on which maximum was used.
 // =====================================================================================
+// NT = query tiles per CTA.  NT = 2: the two tiles share every K / V tile and take turns with the
+// exponentials (one CTA per SM).  NT = 1: half the shared memory, tensor memory and threads, so
+// that two CTAs are resident per SM and the hardware interleaves their phases; K and V are then
+// fetched once per query tile (from L2), and V has a single stage.
+template <int NT>
 struct Fwd64Cfg {
   static constexpr int TILE = 128 * 64 * 2;
   static constexpr int P_TILE = 128 * 128 * 2;
-  static constexpr int OFF_Q = 0;                 // 2 tiles
-  static constexpr int OFF_K = 2 * TILE;          // 2 stages
-  static constexpr int OFF_V = OFF_K + 2 * TILE;  // 2 stages
-  static constexpr int OFF_P = OFF_V + 2 * TILE;  // 2 tiles
-  static constexpr int OFF_BAR = OFF_P + 2 * P_TILE;
-  static constexpr int OFF_XMAX = OFF_BAR + 256;  // float [2 tiles][2 buffers][2 parts][128]
-  static constexpr int SMEM = OFF_XMAX + 2 * 2 * 2 * 128 * 4 + 1024;
-  static constexpr int TMEM_COLS = 512;
-  static constexpr int SWARPS = 16;
+  static constexpr int NSV = NT == 2 ? 2 : 1;     // V stages
+  static constexpr int OFF_Q = 0;                 // NT tiles
+  static constexpr int OFF_K = NT * TILE;         // 2 stages
+  static constexpr int OFF_V = OFF_K + 2 * TILE;  // NSV stages
+  static constexpr int OFF_P = OFF_V + NSV * TILE;  // NT tiles
+  static constexpr int OFF_BAR = OFF_P + NT * P_TILE;
+  static constexpr int OFF_XMAX = OFF_BAR + 256;  // float [NT tiles][2 buffers][2 parts][128]
+  static constexpr int SMEM = OFF_XMAX + NT * 2 * 2 * 128 * 4 + 1024;
+  static constexpr int TMEM_COLS = NT == 2 ? 512 : 256;
+  static constexpr int SWARPS = 8 * NT;
   static constexpr int THREADS = (SWARPS + 2) * 32;
+  static constexpr int CTAS_PER_SM = NT == 2 ? 1 : 2;
 };
 
-// POLY_MASK: bit g set = the second pair of score group g (four consecutive scores; a thread has
-// 16 groups per key tile) takes ex2_poly2 instead of two ex2.approx; tiles that need masking
-// always use ex2.approx (a masked score is -inf).
-template <int POLY_MASK>
-__global__ void __launch_bounds__(Fwd64Cfg::THREADS, 1)
+template <int NT>
+__global__ void __launch_bounds__(Fwd64Cfg<NT>::THREADS, Fwd64Cfg<NT>::CTAS_PER_SM)
 attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
-  using Cfg = Fwd64Cfg;
+  using Cfg = Fwd64Cfg<NT>;
+  constexpr int NSV = Cfg::NSV;
   constexpr int D = 64;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -500,8 +486,8 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   // blocks are handed out x-fastest, so with the tile index in z every head's heavy (late) causal
   // tiles start before anybody's light ones
   const int pair = (int)gridDim.z - 1 - (int)blockIdx.z;
-  const int qtA = 2 * pair, qtB = 2 * pair + 1;
-  const bool b_valid = qtB < n_qt;
+  const int qtA = NT * pair, qtB = NT * pair + 1;
+  const bool b_valid = NT == 2 && qtB < n_qt;
   const int h = blockIdx.x, b = blockIdx.y;
   const int kvh = h / (p.Hq / p.Hkv);
   const int nA = p.causal ? min(qtA + 1, n_qt) : n_qt;
@@ -514,7 +500,7 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_free[i], 8);   // one arrival per warp
+      mbar_init(&s_free[i], 8);   // one arrival per warp (eight warps per query tile)
       mbar_init(&p_ready[i], 8);
       mbar_init(&o_full[i], 1);
       mbar_init(&exp_done[i], 8);
@@ -529,7 +515,7 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tm_S = tmem_base;        // S of tile A at +0, of tile B at +128
-  const uint32_t tm_O = tmem_base + 256;  // O of tile A at +0, of tile B at +64
+  const uint32_t tm_O = tmem_base + NT * 128;  // O of tile A at +0, of tile B at +64
 
   if (warp == Cfg::SWARPS) {
     // ---------------- TMA ----------------
@@ -543,9 +529,11 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
         mbar_arrive_expect_tx(&k_full[st], Cfg::TILE);
         tma_load_4d(smem + Cfg::OFF_K + st * Cfg::TILE, &tmK, &k_full[st], 0, kvh, j * 128, b);
-        mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
-        mbar_arrive_expect_tx(&v_full[st], Cfg::TILE);
-        tma_load_4d(smem + Cfg::OFF_V + st * Cfg::TILE, &tmV, &v_full[st], 0, kvh, j * 128, b);
+        const int sv = j % NSV;
+        const uint32_t phv = (j / NSV) & 1;
+        mbar_wait(&v_empty[sv], phv ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
+        mbar_arrive_expect_tx(&v_full[sv], Cfg::TILE);
+        tma_load_4d(smem + Cfg::OFF_V + sv * Cfg::TILE, &tmV, &v_full[sv], 0, kvh, j * 128, b);
       }
     }
   } else if (warp == Cfg::SWARPS + 1) {
@@ -564,7 +552,7 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       };
       auto issue_pv = [&](int t, int j) {  // O_t (+)= P_t V_j
         const uint32_t sP = smem_u32(smem + Cfg::OFF_P + t * Cfg::P_TILE);
-        const uint32_t sV = smem_u32(smem + Cfg::OFF_V + (j & 1) * Cfg::TILE);
+        const uint32_t sV = smem_u32(smem + Cfg::OFF_V + (j % NSV) * Cfg::TILE);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {  // 128 keys in steps of 16
           const uint64_t da = make_smem_desc(sP + (k >> 2) * 16384u + (k & 3) * 32u, 16, 1024);
@@ -581,7 +569,7 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       umma_commit(&k_empty[0]);
       for (int j = 0; j < n_kv; ++j) {
         const uint32_t jph = j & 1;
-        const uint32_t phv = (j >> 1) & 1;
+        const uint32_t phv = (j / NSV) & 1;
         const uint32_t kph1 = ((j + 1) >> 1) & 1;
         // the next S of a tile may start once the tile's threads hold the current S in registers
         if (j + 1 < nA) {
@@ -599,25 +587,25 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (j + 1 < n_kv) umma_commit(&k_empty[(j + 1) & 1]);
         if (j < nA) {
           mbar_wait(&p_ready[0], jph, abort_flag, p.status, FAULT_WAIT_ATTN);
-          mbar_wait(&v_full[j & 1], phv, abort_flag, p.status, FAULT_WAIT_ATTN);
+          mbar_wait(&v_full[j % NSV], phv, abort_flag, p.status, FAULT_WAIT_ATTN);
           tc_fence_after_sync();
           issue_pv(0, j);
         }
         if (j < nB) {
           mbar_wait(&p_ready[1], jph, abort_flag, p.status, FAULT_WAIT_ATTN);
-          mbar_wait(&v_full[j & 1], phv, abort_flag, p.status, FAULT_WAIT_ATTN);
+          mbar_wait(&v_full[j % NSV], phv, abort_flag, p.status, FAULT_WAIT_ATTN);
           tc_fence_after_sync();
           issue_pv(1, j);
         }
-        umma_commit(&v_empty[j & 1]);
+        umma_commit(&v_empty[j % NSV]);
       }
     }
   } else {
     // ---------------- softmax + output ----------------
     // warp w: query tile (w >> 2) & 1, TMEM lane quarter w & 3, column half w >> 3.  A thread owns
     // one query row, 64 of its score columns and 32 of its output columns.
-    const int t = (warp >> 2) & 1;
-    const int part = warp >> 3;
+    const int t = NT == 2 ? (warp >> 2) & 1 : 0;
+    const int part = NT == 2 ? warp >> 3 : warp >> 2;
     const int n_mine = t ? nB : nA;
     const int qt = t ? qtB : qtA;
     const int row = (warp & 3) * 32 + lane;
@@ -702,10 +690,12 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
       }
       // the two query tiles take turns with the exponentials (A0, B0, A1, B1, ...)
-      if (t == 0) {
-        if (j > 0 && b_valid) mbar_wait(&exp_done[1], jph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
-      } else {
-        if (j < nA) mbar_wait(&exp_done[0], jph, abort_flag, p.status, FAULT_WAIT_ATTN);
+      if (NT == 2) {
+        if (t == 0) {
+          if (j > 0 && b_valid) mbar_wait(&exp_done[1], jph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
+        } else {
+          if (j < nA) mbar_wait(&exp_done[0], jph, abort_flag, p.status, FAULT_WAIT_ATTN);
+        }
       }
       // probabilities: bf16, stored to the P tile eight at a time as they are produced (the stores
       // run in the shadow of the exponentials), and their row sum
@@ -719,9 +709,7 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           float x0, x1, x2, x3;
           ffma2(x0, x1, __uint_as_float(ra[i + u]), __uint_as_float(ra[i + u + 1]), sl2, sl2, nmsl2, nmsl2);
           ffma2(x2, x3, __uint_as_float(ra[i + u + 2]), __uint_as_float(ra[i + u + 3]), sl2, sl2, nmsl2, nmsl2);
-          x0 = ex2_approx(x0); x1 = ex2_approx(x1);
-          if (((POLY_MASK >> ((i + u) >> 2)) & 1) && !need_mask) ex2_poly2(x2, x3);
-          else { x2 = ex2_approx(x2); x3 = ex2_approx(x3); }
+          x0 = ex2_approx(x0); x1 = ex2_approx(x1); x2 = ex2_approx(x2); x3 = ex2_approx(x3);
           fadd2(rs0, rs1, rs0, rs1, x0, x1);
           fadd2(rs2, rs3, rs2, rs3, x2, x3);
           pk[u >> 1] = pack_bf16x2(x0, x1);
@@ -737,9 +725,7 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           float x0, x1, x2, x3;
           ffma2(x0, x1, __uint_as_float(rb[i + u]), __uint_as_float(rb[i + u + 1]), sl2, sl2, nmsl2, nmsl2);
           ffma2(x2, x3, __uint_as_float(rb[i + u + 2]), __uint_as_float(rb[i + u + 3]), sl2, sl2, nmsl2, nmsl2);
-          x0 = ex2_approx(x0); x1 = ex2_approx(x1);
-          if (((POLY_MASK >> (8 + ((i + u) >> 2))) & 1) && !need_mask) ex2_poly2(x2, x3);
-          else { x2 = ex2_approx(x2); x3 = ex2_approx(x3); }
+          x0 = ex2_approx(x0); x1 = ex2_approx(x1); x2 = ex2_approx(x2); x3 = ex2_approx(x3);
           fadd2(rs0, rs1, rs0, rs1, x0, x1);
           fadd2(rs2, rs3, rs2, rs3, x2, x3);
           pk[u >> 1] = pack_bf16x2(x0, x1);
@@ -749,7 +735,7 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         // the turn is handed over with 24 of the 64 exponentials still to go: the other tile needs
         // a few hundred clocks from the barrier to its first exponential (measured: better than
         // handing over at the end, at 16 or at 32 to go)
-        if (i == 0) mbar_arrive_warp(&exp_done[t]);
+        if (NT == 2 && i == 0) mbar_arrive_warp(&exp_done[t]);
       }
       l = fmaf(l, alpha, (rs0 + rs1) + (rs2 + rs3));
       tc_fence_before_sync();
@@ -1255,9 +1241,9 @@ using namespace eisen;
 
 extern "C" {
 
-int eisen_attn_set_poly_exp(int level) {
-  if (level < 0 || level > 4) return fail(EISEN_ERR_INVALID, "attn_set_poly_exp: level must be in [0, 4]");
-  g_attn_poly_level.store(level);
+int eisen_attn_set_fwd_tiles(int tiles) {
+  if (tiles != 1 && tiles != 2) return fail(EISEN_ERR_INVALID, "attn_set_fwd_tiles: 1 or 2 query tiles per CTA");
+  g_attn_fwd_tiles.store(tiles);
   return 0;
 }
 
@@ -1282,26 +1268,26 @@ int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, vo
   dim3 grid((unsigned)Hq, (unsigned)B, (unsigned)(((S + 127) / 128 + 1) / 2));  // two query tiles per CTA
   cudaStream_t s = (cudaStream_t)stream;
   if (D == 64) {
-    // share of the exponentials computed by polynomial on the FMA pipe: 0, 1/8, 1/4, 3/8 or 1/2
-    auto launch64 = [&](auto kern, bool& attr_done) -> int {
-      if (!attr_done) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd64Cfg::SMEM) != cudaSuccess) return 1;
-        attr_done = true;
-      }
-      kern<<<grid, Fwd64Cfg::THREADS, Fwd64Cfg::SMEM, s>>>(tq, tk, tv, p);
-      return 0;
-    };
-    static bool set64[5][MAX_DEVICE_SLOTS] = {{false}};
+    // one query tile per CTA and two CTAs per SM, or two query tiles per CTA (see Fwd64Cfg)
+    static bool set64[2][MAX_DEVICE_SLOTS] = {{false}};
     const int slot = device_slot();
-    int bad = 0;
-    switch (g_attn_poly_level.load()) {
-      case 0: bad = launch64(attn_fwd64_kernel<0x0000>, set64[0][slot]); break;
-      case 1: bad = launch64(attn_fwd64_kernel<0x1111>, set64[1][slot]); break;
-      case 2: bad = launch64(attn_fwd64_kernel<0x5555>, set64[2][slot]); break;
-      case 3: bad = launch64(attn_fwd64_kernel<0x7777>, set64[3][slot]); break;
-      default: bad = launch64(attn_fwd64_kernel<0xFFFF>, set64[4][slot]); break;
+    const int nt = g_attn_fwd_tiles.load() == 2 ? 2 : 1;
+    if (nt == 2) {
+      if (!set64[1][slot]) {
+        if (cudaFuncSetAttribute(attn_fwd64_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd64Cfg<2>::SMEM) != cudaSuccess)
+          return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute");
+        set64[1][slot] = true;
+      }
+      attn_fwd64_kernel<2><<<grid, Fwd64Cfg<2>::THREADS, Fwd64Cfg<2>::SMEM, s>>>(tq, tk, tv, p);
+    } else {
+      if (!set64[0][slot]) {
+        if (cudaFuncSetAttribute(attn_fwd64_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd64Cfg<1>::SMEM) != cudaSuccess)
+          return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute");
+        set64[0][slot] = true;
+      }
+      dim3 grid1((unsigned)Hq, (unsigned)B, (unsigned)((S + 127) / 128));
+      attn_fwd64_kernel<1><<<grid1, Fwd64Cfg<1>::THREADS, Fwd64Cfg<1>::SMEM, s>>>(tq, tk, tv, p);
     }
-    if (bad) return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute");
   } else {
     static bool set128[MAX_DEVICE_SLOTS] = {false};
     if (!set128[device_slot()]) { if (cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<128>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute"); set128[device_slot()] = true; }

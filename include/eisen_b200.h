@@ -138,11 +138,10 @@ int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, vo
                    long long S, long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss,
                    long long q_hs, long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs,
                    long long o_ss, long long o_hs, float scale, int causal, int* status);
-/* Share of the head_dim-64 forward's exponentials that run as a degree-3 polynomial on the FMA pipe
- * instead of on the special-function unit, in eighths: 0 (none) .. 4 (half).  The polynomial's
- * relative error (7.5e-5) is far below the bf16 rounding of the probabilities.  Process-wide; meant
- * for tests and measurements. */
-int eisen_attn_set_poly_exp(int level);
+/* Query tiles (128 rows) per CTA of the head_dim-64 forward: 1 = one tile per CTA, two CTAs resident
+ * per SM whose phases the hardware interleaves (default); 2 = two tiles per CTA sharing every K / V
+ * tile and taking turns with the exponentials.  Process-wide; meant for tests and measurements. */
+int eisen_attn_set_fwd_tiles(int tiles);
 long long eisen_attn_bwd_workspace_bytes(long long B, long long S, long long Hq, long long Hkv, long long D);
 /* dq, dk, dv are written (not accumulated); they use the strides of q and k/v respectively. */
 int eisen_attn_bwd(void* stream, const void* q, const void* k, const void* v, const void* o, const float* lse,
