@@ -397,7 +397,9 @@ def side_cases(args, peaks, dev, compute):
         # RMSNorm backward on [16384, 2048], AdamW over 1.1e9 f32 parameters
         c = bc.case_ce(16384, 32000, iters=5, ignore_frac=0.05)
         c4 = {"ce_fwd": {"gbs": c["fwd_gbs"], "ms": c["fwd_ms"], "bytes": c["fwd_bytes"], "frac_of_hbm": c["fwd_gbs"] / hbm},
-              "ce_bwd": {"gbs": c["bwd_gbs"], "ms": c["bwd_ms"], "bytes": c["bwd_bytes"], "frac_of_hbm": c["bwd_gbs"] / hbm}}
+              "ce_bwd": {"gbs": c["bwd_gbs"], "ms": c["bwd_ms"], "bytes": c["bwd_bytes"], "frac_of_hbm": c["bwd_gbs"] / hbm},
+              "ce_fused_fwd_bwd": {"gbs": c["fused_gbs"], "ms": c["fused_ms"], "bytes": c["fused_bytes"],
+                                   "frac_of_hbm": c["fused_gbs"] / hbm}}
         del c
         torch.cuda.empty_cache()
         d = bc.case_gemm(2048, 32000, 16384, a_mn=1, b_mn=1, out_mode=4, split_k=0, iters=5)

@@ -460,11 +460,13 @@ def test_cross_entropy_bf16():
     assert rel_l2(ld.float().cpu().numpy(), lf.grad.numpy()) < 1e-2
 
 
-@pytest.mark.parametrize("rows,vocab,dt", [(33, 1000, "f32"), (5, 7, "f32"), (64, 32000, "bf16"), (9, 70001, "f32"), (16, 4100, "bf16")])
+@pytest.mark.parametrize("rows,vocab,dt", [(33, 1000, "f32"), (5, 7, "f32"), (64, 32000, "bf16"), (9, 70001, "f32"), (16, 4100, "bf16"),
+                                            (8, 8192, "f32"), (4, 65536, "bf16"), (6, 2048, "bf16"), (3, 32768, "f32")])
 def test_cross_entropy_fused_matches_the_two_pass_kernels(rows, vocab, dt):
     """eisen_ce_fused (row staged in shared memory, dlogits written over the logits) against
     eisen_ce_fwd + eisen_ce_bwd; 70001 f32 entries do not fit shared memory (second pass from
-    global memory), 7 and 4100 are not multiples of the vector width of their type."""
+    global memory), 7 and 4100 are not multiples of the vector width of their type; rows of 2048 to
+    8192 vectors take the register-resident kernel with 1, 2, 4 or 8 vectors per thread."""
     rng = np.random.default_rng(rows + vocab)
     tdt = torch.float32 if dt == "f32" else torch.bfloat16
     edt = eb.F32 if dt == "f32" else eb.BF16
