@@ -3,7 +3,10 @@
 // One warp (RMSNorm) or one CTA (softmax, cross-entropy) per row, 16-byte accesses, shuffle
 // reductions; the reference runs one THREAD per row (kernels/ops_f32.cu:539-578 rmsnorm,
 // 580-646 cross-entropy and softmax, 5-64 masked cross-entropy).
+#include <algorithm>
+
 #include "common.cuh"
+#include "ptx.cuh"
 #include "errors.h"
 #include "../../include/eisen_b200.h"
 
@@ -359,6 +362,148 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w, const T
   }
 }
 
+
+// Backward with the rows staged in shared memory by bulk asynchronous copies (one 1-D copy per
+// tensor and group of ROWS rows, completion on an mbarrier): S stages per CTA are in flight instead
+// of what fits the registers, and without row buffers in registers three or four CTAs fit an SM.
+// Column ownership, the reduction of the two row sums and the dw partials are those of
+// rmsnorm_bwd_kernel.  A stage is refilled right after the barrier of the iteration that follows its
+// last use, when every thread is known to be done with it.  Needs dim == 256 vectors and rows % ROWS == 0.
+template <typename T, int ROWS, int S, int CTAS>
+__global__ void __launch_bounds__(RB_THREADS, CTAS)
+rmsnorm_bwd_staged_kernel(const T* __restrict__ x, const float* __restrict__ w, const T* __restrict__ dy,
+                          T* __restrict__ dx, float* __restrict__ dw_partial, long long groups, float eps,
+                          int acc_dx) {
+  constexpr int V = VecOf<T>::N;
+  constexpr int DIM = RB_THREADS * V;
+  constexpr int NVAL = 2 * ROWS;
+  constexpr uint32_t TENSOR_BYTES = ROWS * DIM * sizeof(T);
+  static_assert(ROWS == 2 || ROWS == 4, "two or four rows per group");
+  extern __shared__ __align__(128) uint8_t rs_smem[];
+  __shared__ uint64_t full_bar[S];
+  __shared__ float sh[2][RB_THREADS / 32][NVAL];
+  __shared__ int abort_flag;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) mbar_init(&full_bar[i], 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  float wv[V], dwp[V];
+#pragma unroll
+  for (int k = 0; k < V; ++k) { wv[k] = w[threadIdx.x * V + k]; dwp[k] = 0.0f; }
+  const long long g0 = blockIdx.x, gstride = gridDim.x;
+  const long long n_mine = g0 < groups ? (groups - g0 + gstride - 1) / gstride : 0;
+  auto issue = [&](long long k) {
+    if (threadIdx.x == 0 && k < n_mine) {
+      const int st = (int)(k % S);
+      const long long r0 = (g0 + k * gstride) * ROWS;
+      uint8_t* dst = rs_smem + (size_t)st * 2 * TENSOR_BYTES;
+      mbar_arrive_expect_tx(&full_bar[st], 2 * TENSOR_BYTES);
+      const uint32_t bar = smem_u32(&full_bar[st]);
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(smem_u32(dst)), "l"(x + r0 * DIM), "r"(TENSOR_BYTES), "r"(bar) : "memory");
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(smem_u32(dst + TENSOR_BYTES)), "l"(dy + r0 * DIM), "r"(TENSOR_BYTES), "r"(bar) : "memory");
+    }
+  };
+  for (int k = 0; k < S - 1; ++k) issue(k);
+  int buf = 0;
+  for (long long k = 0; k < n_mine; ++k) {
+    const int st = (int)(k % S);
+    const uint32_t ph = (uint32_t)((k / S) & 1);
+    const long long r0 = (g0 + k * gstride) * ROWS;
+    mbar_wait(&full_bar[st], ph, &abort_flag, nullptr, FAULT_WAIT_FULL);
+    const T* sx = reinterpret_cast<const T*>(rs_smem + (size_t)st * 2 * TENSOR_BYTES) + threadIdx.x * V;
+    const T* sg = sx + ROWS * DIM;
+    float part[NVAL];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      float xv[V], gv[V];
+      ld16(sx + r * DIM, xv);
+      ld16(sg + r * DIM, gv);
+      float ss = 0.0f, gd = 0.0f, ss1 = 0.0f, gd1 = 0.0f;
+#pragma unroll
+      for (int e = 0; e < V; e += 2) {
+        ss = fmaf(xv[e], xv[e], ss);
+        ss1 = fmaf(xv[e + 1], xv[e + 1], ss1);
+        gd = fmaf(gv[e] * wv[e], xv[e], gd);
+        gd1 = fmaf(gv[e + 1] * wv[e + 1], xv[e + 1], gd1);
+      }
+      part[2 * r] = ss + ss1;
+      part[2 * r + 1] = gd + gd1;
+    }
+    // NVAL sums over the warp by recursive halving; lane l ends with the total of value vidx(l)
+    float w1;
+    int vidx;
+    if constexpr (ROWS == 4) {
+      float w4[4], w2[2];
+      const bool hi = lane & 16;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) w4[i] = (hi ? part[i + 4] : part[i]) + __shfl_xor_sync(0xffffffffu, hi ? part[i] : part[i + 4], 16);
+      const bool h8 = lane & 8;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) w2[i] = (h8 ? w4[i + 2] : w4[i]) + __shfl_xor_sync(0xffffffffu, h8 ? w4[i] : w4[i + 2], 8);
+      const bool h4 = lane & 4;
+      w1 = (h4 ? w2[1] : w2[0]) + __shfl_xor_sync(0xffffffffu, h4 ? w2[0] : w2[1], 4);
+      w1 += __shfl_xor_sync(0xffffffffu, w1, 2);
+      w1 += __shfl_xor_sync(0xffffffffu, w1, 1);
+      vidx = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+    } else {
+      float w2[2];
+      const bool hi = lane & 16;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) w2[i] = (hi ? part[i + 2] : part[i]) + __shfl_xor_sync(0xffffffffu, hi ? part[i] : part[i + 2], 16);
+      const bool h8 = lane & 8;
+      w1 = (h8 ? w2[1] : w2[0]) + __shfl_xor_sync(0xffffffffu, h8 ? w2[0] : w2[1], 8);
+      w1 += __shfl_xor_sync(0xffffffffu, w1, 4);
+      w1 += __shfl_xor_sync(0xffffffffu, w1, 2);
+      w1 += __shfl_xor_sync(0xffffffffu, w1, 1);
+      vidx = ((lane >> 4) & 1) * 2 + ((lane >> 3) & 1);
+    }
+    if ((lane & (ROWS == 4 ? 3 : 7)) == 0) sh[buf][warp][vidx] = w1;
+    __syncthreads();
+    issue(k + S - 1);  // its stage was last read in the iteration before this one
+    {
+      float t = 0.0f;
+#pragma unroll
+      for (int wq = 0; wq < RB_THREADS / 32; ++wq) t += sh[buf][wq][lane & (NVAL - 1)];
+      const float other = __shfl_xor_sync(0xffffffffu, t, 1);
+      const float ssv = (lane & 1) ? other : t;
+      const float gdv = (lane & 1) ? t : other;
+      const float rr = 1.0f / sqrtf(ssv / (float)DIM + eps);
+      const float coef = (rr * rr * rr) / (float)DIM * gdv;
+      const float mine = (lane & 1) ? coef : rr;
+#pragma unroll
+      for (int i = 0; i < NVAL; ++i) part[i] = __shfl_sync(0xffffffffu, mine, i);
+    }
+    buf ^= 1;
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const float rrms = part[2 * r], ncoef = -part[2 * r + 1];
+      float xv[V], gv[V], o[V];
+      ld16(sx + r * DIM, xv);
+      ld16(sg + r * DIM, gv);
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        o[e] = fmaf(gv[e] * wv[e], rrms, xv[e] * ncoef);
+        dwp[e] = fmaf(gv[e] * xv[e], rrms, dwp[e]);
+      }
+      T* dr = dx + (r0 + r) * DIM + threadIdx.x * V;
+      if (acc_dx) {
+        float old[V];
+        ld16(dr, old);
+#pragma unroll
+        for (int e = 0; e < V; ++e) o[e] += old[e];
+      }
+      st16(dr, o);
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < V; ++e) dw_partial[(long long)blockIdx.x * DIM + threadIdx.x * V + e] = dwp[e];
+}
+
 // generic fallback for dims that are not a multiple of the vector width or exceed the register
 // budget: one warp per row, dw through f32 atomics
 template <typename T>
@@ -391,6 +536,125 @@ __global__ void rmsnorm_bwd_generic_kernel(const T* __restrict__ x, const float*
       atomicAdd(dw + c, gv * xv * rrms);
     }
   }
+}
+
+
+// Warp-per-row form of the backward for rows of 32 * NV 16-byte vectors (NV <= 8: 2048 bf16 or 1024
+// f32 columns).  A warp owns whole rows, so the two row sums are ten shuffles and the kernel has no
+// barrier inside its loop; lane l owns the columns of vectors l + 32 j for every row it sees and
+// keeps their dw partial in registers; the weights sit in shared memory.  Rows are requested one
+// iteration ahead (two register buffers, the loop is unrolled by two so that no copy is needed).
+// At the end the warps of a CTA add their dw partials in a fixed order through shared memory and
+// the CTA writes one row of dw_partial, which reduce_partials_kernel adds up (no atomics).
+constexpr int RW_WARPS = 8;
+int g_rms_bwd_mode = 2;  // eisen_rmsnorm_bwd_set_mode
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(RW_WARPS * 32, 1)
+rmsnorm_bwd_warp_kernel(const T* __restrict__ x, const float* __restrict__ w, const T* __restrict__ dy,
+                        T* __restrict__ dx, float* __restrict__ dw_partial, long long rows, int dim, float eps,
+                        int acc_dx) {
+  constexpr int V = VecOf<T>::N;
+  extern __shared__ float rw_smem[];
+  float* sw = rw_smem;         // [dim] weights
+  float* sacc = rw_smem + dim;  // [dim] dw of this CTA
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int c = threadIdx.x; c < dim; c += RW_WARPS * 32) { sw[c] = w[c]; sacc[c] = 0.0f; }
+  __syncthreads();
+  float dwp[NV][V];
+#pragma unroll
+  for (int j = 0; j < NV; ++j)
+#pragma unroll
+    for (int k = 0; k < V; ++k) dwp[j][k] = 0.0f;
+  const long long w0 = (long long)blockIdx.x * RW_WARPS + warp;
+  const long long nw = (long long)gridDim.x * RW_WARPS;
+  const float inv_dim = 1.0f / (float)dim;
+
+  auto load_row = [&](long long row, uint4 (&xd)[NV], uint4 (&gd)[NV]) {
+    if (row < rows) {
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        const long long off = row * dim + (lane + 32 * j) * V;
+        xd[j] = ld_stream16(x + off);
+        gd[j] = ld_stream16(dy + off);
+      }
+    }
+  };
+  auto do_row = [&](long long row, const uint4 (&xd)[NV], const uint4 (&gdv)[NV]) {
+    float ss = 0.0f, gsum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      float xv[V], gv[V];
+      unpack16(xd[j], xv);
+      unpack16(gdv[j], gv);
+      const float* wp = sw + (lane + 32 * j) * V;
+#pragma unroll
+      for (int k = 0; k < V; k += 4) {
+        const float4 w4 = *reinterpret_cast<const float4*>(wp + k);
+        ss = fmaf(xv[k], xv[k], ss);             gsum = fmaf(gv[k] * w4.x, xv[k], gsum);
+        ss = fmaf(xv[k + 1], xv[k + 1], ss);     gsum = fmaf(gv[k + 1] * w4.y, xv[k + 1], gsum);
+        ss = fmaf(xv[k + 2], xv[k + 2], ss);     gsum = fmaf(gv[k + 2] * w4.z, xv[k + 2], gsum);
+        ss = fmaf(xv[k + 3], xv[k + 3], ss);     gsum = fmaf(gv[k + 3] * w4.w, xv[k + 3], gsum);
+      }
+    }
+    ss = warp_sum(ss);
+    gsum = warp_sum(gsum);
+    const float rrms = 1.0f / sqrtf(ss * inv_dim + eps);
+    const float ncoef = -(rrms * rrms * rrms) * inv_dim * gsum;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      float xv[V], gv[V], o[V];
+      unpack16(xd[j], xv);
+      unpack16(gdv[j], gv);
+      const float* wp = sw + (lane + 32 * j) * V;
+#pragma unroll
+      for (int k = 0; k < V; k += 4) {
+        const float4 w4 = *reinterpret_cast<const float4*>(wp + k);
+        const float ww[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          o[k + e] = fmaf(gv[k + e] * ww[e], rrms, xv[k + e] * ncoef);
+          dwp[j][k + e] = fmaf(gv[k + e] * xv[k + e], rrms, dwp[j][k + e]);
+        }
+      }
+      T* dr = dx + row * dim + (lane + 32 * j) * V;
+      if (acc_dx) {
+        float old[V];
+        ld16(dr, old);
+#pragma unroll
+        for (int k = 0; k < V; ++k) o[k] += old[k];
+      }
+      st16(dr, o);
+    }
+  };
+
+  uint4 xa[NV], ga[NV], xb[NV], gb[NV];
+  load_row(w0, xa, ga);
+  for (long long row = w0; row < rows; row += 2 * nw) {
+    load_row(row + nw, xb, gb);
+    do_row(row, xa, ga);
+    load_row(row + 2 * nw, xa, ga);
+    if (row + nw < rows) do_row(row + nw, xb, gb);
+  }
+  // dw of this CTA: the warps add their partials one after the other (fixed order)
+  for (int wq = 0; wq < RW_WARPS; ++wq) {
+    if (warp == wq) {
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        float* ap = sacc + (lane + 32 * j) * V;
+#pragma unroll
+        for (int k = 0; k < V; ++k) ap[k] += dwp[j][k];
+      }
+    }
+    __syncthreads();
+  }
+  for (int c = threadIdx.x; c < dim; c += RW_WARPS * 32) dw_partial[(long long)blockIdx.x * dim + c] = sacc[c];
+}
+
+inline int rmsnorm_bwd_warp_grid(long long rows) {
+  const long long need = (rows + RW_WARPS - 1) / RW_WARPS;
+  const long long cap = sm_count();
+  return (int)(need < cap ? (need < 1 ? 1 : need) : cap);
 }
 
 inline int rmsnorm_bwd_grid(long long rows) {
@@ -783,6 +1047,54 @@ int rmsnorm_bwd_dispatch(cudaStream_t s, const T* x, const float* w, const T* dy
     rmsnorm_bwd_generic_kernel<T><<<grid, 256, 0, s>>>(x, w, dy, dx, dw, rows, dim, eps, acc_dx);
     return check_launch("rmsnorm_bwd_generic");
   }
+  if (g_rms_bwd_mode >= 2 && dim == RB_THREADS * V && rows % 4 == 0 && rows >= 4 && aligned16(w)) {
+    // staged kernel: mode 2 = 4 rows x 3 stages, 2 CTAs per SM; 3 = 2 rows x 4 stages, 3 CTAs; 4 = 2 rows x 3 stages, 4 CTAs
+    const int mode = g_rms_bwd_mode;
+    const int rows_per = (mode == 2 || mode == 5) ? 4 : 2, stages = mode == 3 ? 4 : (mode == 5 ? 2 : 3),
+              ctas = mode == 2 ? 2 : (mode == 3 || mode == 5 ? 3 : 4);
+    const long long groups = rows / rows_per;
+    const long long cap = (long long)sm_count() * ctas;
+    const int grid = (int)(groups < cap ? groups : cap);
+    const size_t smem = (size_t)stages * 2 * rows_per * dim * sizeof(T);
+    static bool attr[4][2][MAX_DEVICE_SLOTS] = {{{false}}};
+    auto go = [&](auto kern) -> int {
+      bool& done = attr[mode - 2][sizeof(T) == 2][device_slot()];
+      if (!done) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 1;
+        done = true;
+      }
+      kern<<<grid, RB_THREADS, smem, s>>>(x, w, dy, dx, ws, groups, eps, acc_dx);
+      return 0;
+    };
+    int bad = mode == 2 ? go(rmsnorm_bwd_staged_kernel<T, 4, 3, 2>)
+            : mode == 3 ? go(rmsnorm_bwd_staged_kernel<T, 2, 4, 3>)
+            : mode == 4 ? go(rmsnorm_bwd_staged_kernel<T, 2, 3, 4>) : go(rmsnorm_bwd_staged_kernel<T, 4, 2, 3>);
+    if (bad) return fail(EISEN_ERR_CUDA, "rmsnorm_bwd: shared-memory attribute");
+    int rc = check_launch("rmsnorm_bwd_staged");
+    if (rc) return rc;
+    reduce_partials_kernel<<<(dim + 31) / 32, 256, 0, s>>>(ws, dw, grid, dim);
+    return check_launch("rmsnorm_bwd_reduce");
+  }
+  if (g_rms_bwd_mode == 1 && dim % (32 * V) == 0 && dim / (32 * V) <= 8 && aligned16(w)) {
+    const int nv = dim / (32 * V);
+    const int grid = rmsnorm_bwd_warp_grid(rows);
+    const size_t smem = (size_t)dim * 8;
+    auto go = [&](auto kern) { kern<<<grid, RW_WARPS * 32, smem, s>>>(x, w, dy, dx, ws, rows, dim, eps, acc_dx); };
+    switch (nv) {
+      case 1: go(rmsnorm_bwd_warp_kernel<T, 1>); break;
+      case 2: go(rmsnorm_bwd_warp_kernel<T, 2>); break;
+      case 3: go(rmsnorm_bwd_warp_kernel<T, 3>); break;
+      case 4: go(rmsnorm_bwd_warp_kernel<T, 4>); break;
+      case 5: go(rmsnorm_bwd_warp_kernel<T, 5>); break;
+      case 6: go(rmsnorm_bwd_warp_kernel<T, 6>); break;
+      case 7: go(rmsnorm_bwd_warp_kernel<T, 7>); break;
+      default: go(rmsnorm_bwd_warp_kernel<T, 8>); break;
+    }
+    int rc = check_launch("rmsnorm_bwd_warp");
+    if (rc) return rc;
+    reduce_partials_kernel<<<(dim + 31) / 32, 256, 0, s>>>(ws, dw, grid, dim);
+    return check_launch("rmsnorm_bwd_reduce");
+  }
   if (nch <= 1) return launch_rmsnorm_bwd<T, 1>(s, x, w, dy, dx, dw, ws, rows, dim, eps, acc_dx);
   if (nch <= 2) return launch_rmsnorm_bwd<T, 2>(s, x, w, dy, dx, dw, ws, rows, dim, eps, acc_dx);
   return launch_rmsnorm_bwd<T, 4>(s, x, w, dy, dx, dw, ws, rows, dim, eps, acc_dx);
@@ -806,8 +1118,15 @@ int eisen_rmsnorm_fwd(void* stream, const void* x, const float* w, void* y, floa
   });
 }
 
+int eisen_rmsnorm_bwd_set_mode(int mode) {
+  if (mode < 0 || mode > 5) return fail(EISEN_ERR_INVALID, "rmsnorm_bwd_set_mode: mode must be in [0, 5]");
+  g_rms_bwd_mode = mode;
+  return 0;
+}
+
 long long eisen_rmsnorm_bwd_workspace_bytes(long long rows, long long dim) {
-  return (long long)rmsnorm_bwd_grid(rows) * dim * 4 + 256;
+  const long long g = std::max<long long>(std::max<long long>(rmsnorm_bwd_grid(rows), rmsnorm_bwd_warp_grid(rows)), 4LL * sm_count());
+  return g * dim * 4 + 256;
 }
 
 

@@ -385,8 +385,12 @@ def test_rmsnorm_f32_vs_oracle(rows, dim):
     assert rel_l2(dw.cpu().numpy(), 2 * og.grad(ow)) < 1e-5
 
 
-def test_rmsnorm_bf16():
-    rows, dim = 300, 2048
+@pytest.mark.parametrize("mode,rows", [(2, 300), (0, 300), (1, 300), (2, 5), (2, 2052), (3, 304), (4, 304), (5, 304)])
+def test_rmsnorm_bf16(mode, rows):
+    """Forward and every backward kernel (0: rows in registers, 1: warp per row, 2-5: rows staged in
+    shared memory by bulk copies; 5 rows fall back to the register kernel) against f32 autograd."""
+    dim = 2048
+    eb.call("eisen_rmsnorm_bwd_set_mode", mode)
     g = torch.Generator(device="cpu").manual_seed(9)
     x = torch.randn(rows, dim, generator=g).to(torch.bfloat16)
     dy = torch.randn(rows, dim, generator=g).to(torch.bfloat16)
@@ -402,9 +406,19 @@ def test_rmsnorm_bf16():
     dx = torch.empty_like(xd)
     dw = torch.zeros(dim, device=dev())
     ws = torch.empty(eb.lib().eisen_rmsnorm_bwd_workspace_bytes(rows, dim), dtype=torch.uint8, device=dev())
-    eb.call("eisen_rmsnorm_bwd", stream(), P(xd), P(wd), P(dyd), P(dx), P(dw), P(ws), rows, dim, 1e-5, eb.BF16, 0)
+    try:
+        eb.call("eisen_rmsnorm_bwd", stream(), P(xd), P(wd), P(dyd), P(dx), P(dw), P(ws), rows, dim, 1e-5, eb.BF16, 0)
+        # accumulate into an existing gradient (the residual stream's)
+        dx2 = torch.ones_like(xd)
+        dw2 = torch.zeros(dim, device=dev())
+        eb.call("eisen_rmsnorm_bwd", stream(), P(xd), P(wd), P(dyd), P(dx2), P(dw2), P(ws), rows, dim, 1e-5, eb.BF16, 1)
+        torch.cuda.synchronize()
+    finally:
+        eb.call("eisen_rmsnorm_bwd_set_mode", 2)
     assert rel_l2(dx.float().cpu().numpy(), xf.grad.numpy()) < 5e-3
     assert rel_l2(dw.cpu().numpy(), wf.grad.numpy()) < 1e-4
+    assert rel_l2(dx2.float().cpu().numpy(), xf.grad.numpy() + 1.0) < 5e-3
+    assert rel_l2(dw2.cpu().numpy(), wf.grad.numpy()) < 1e-4
 
 
 @pytest.mark.parametrize("rows,vocab,masked", [(2, 3, False), (64, 512, False), (40, 1000, True), (16, 32000, True)])
