@@ -357,7 +357,7 @@ def test_attention_rejects_bad_head_dim():
 
 
 # --------------------------------------------------------------------------------- row ops
-@pytest.mark.parametrize("rows,dim", [(2, 4), (33, 128), (64, 2048), (7, 100)])
+@pytest.mark.parametrize("rows,dim", [(2, 4), (33, 128), (64, 2048), (7, 100), (64, 1024)])  # 1024 f32 columns: the staged backward
 def test_rmsnorm_f32_vs_oracle(rows, dim):
     rng = np.random.default_rng(rows + dim)
     X = rng.standard_normal((rows, dim)).astype(np.float32)
