@@ -441,6 +441,27 @@ def side_models(args, dev, compute):
         n = cfg["batch"] * cfg["seq"] * cfg["accum"]
         out[key] = {"ms_per_step": ms, "tokens_per_s": n / (ms * 1e-3), "tokens_per_step": n, "params": r.n_params,
                     "dtype": "f32" if cfg.get("f32") else "bf16"}
+        if not cfg.get("f32"):
+            # the same step recorded once into a CUDA graph and replayed (the eager step of this small
+            # model is bound by its ~1500 launches); the Fp32 graph's reference attention chain uploads
+            # its mask from the host and cannot be captured
+            import torch
+            r.opt.advance()
+            captured = r.g.capture(lambda: r.step(False, 0))
+            for _ in range(3):
+                r.opt.advance()
+                captured.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(compute)
+            for _ in range(steps):
+                r.opt.advance()
+                captured.replay()
+            e1.record(compute)
+            torch.cuda.synchronize()
+            gms = e0.elapsed_time(e1) / steps
+            out[key]["cuda_graph"] = {"ms_per_step": gms, "tokens_per_s": n / (gms * 1e-3)}
+            captured.close()
         r.close()
     return out
 

@@ -49,6 +49,41 @@ int eisen_graph_create(int precision, void* stream, void** out) {
 int eisen_graph_destroy(void* g) {
   return guarded([&] { delete static_cast<Graph*>(g); });
 }
+int eisen_graph_capture_begin(void* g) {
+  return guarded([&] { G(g).capture_begin(); });
+}
+int eisen_graph_capture_end(void* g, void** exec_out) {
+  Graph& gr = G(g);
+  int rc = guarded([&] { *exec_out = gr.capture_end(); });
+  return rc;
+}
+int eisen_graph_capture_abort(void* g) {
+  return guarded([&] {
+    Graph& gr = G(g);
+    if (!gr.capturing) return;
+    gr.capturing = false;
+    cudaGraph_t tmp = nullptr;
+    cudaStreamEndCapture(gr.stream, &tmp);
+    if (tmp) cudaGraphDestroy(tmp);
+    cudaGetLastError();
+  });
+}
+int eisen_graph_replay(void* exec, void* stream) {
+  struct CS { cudaGraph_t graph; cudaGraphExec_t exec; };
+  if (!exec) return eisen::fail(EISEN_ERR_INVALID, "graph_replay: null handle");
+  cudaError_t e = cudaGraphLaunch(static_cast<CS*>(exec)->exec, (cudaStream_t)stream);
+  if (e != cudaSuccess) return eisen::fail(EISEN_ERR_CUDA, cudaGetErrorString(e));
+  return 0;
+}
+int eisen_graph_exec_destroy(void* exec) {
+  struct CS { cudaGraph_t graph; cudaGraphExec_t exec; };
+  if (!exec) return 0;
+  CS* cs = static_cast<CS*>(exec);
+  if (cs->exec) cudaGraphExecDestroy(cs->exec);
+  if (cs->graph) cudaGraphDestroy(cs->graph);
+  delete cs;
+  return 0;
+}
 int eisen_graph_selftest_bounded_wait(void* g, long long budget_cycles) {
   return guarded([&] {
     Graph& gr = G(g);
@@ -347,6 +382,9 @@ int eisen_optim_step(void* opt) {
 }
 int eisen_optim_step_fused(void* opt, float max_norm, float grad_scale) {
   return guarded([&] { static_cast<AdamW*>(opt)->step_fused(max_norm, grad_scale); });
+}
+int eisen_optim_advance(void* opt) {
+  return guarded([&] { static_cast<AdamW*>(opt)->advance(); });
 }
 int eisen_optim_save_state(void* opt, const char* path) {
   return guarded([&] { static_cast<AdamW*>(opt)->save_state(path); });

@@ -97,6 +97,9 @@ void* Graph::pool_get(size_t bytes) {
   }
   // src/graph/memory.rs:189-266 (safe_alloc_zeros): allocate if the budget allows; else drop the
   // cached pool buffers and try again; else fail (with a status, where the reference panics)
+  if (capturing)
+    throw EisenException(EISEN_ERR_INVALID, "a pooled buffer of " + std::to_string(bytes) + " bytes is not cached: run the step "
+                                                "once before capturing it, so that the capture allocates nothing");
   auto within_budget = [&]() { return vram_budget_bytes == 0 || current_vram_usage() + bytes <= vram_budget_bytes; };
   void* p = nullptr;
   cudaError_t e = within_budget() ? cudaMalloc(&p, bytes) : cudaErrorMemoryAllocation;
@@ -298,6 +301,41 @@ void Graph::sync_grad_to_cpu(int64_t id, float* out) {
 void Graph::synchronize() {
   cuck(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
   check_status();
+}
+
+namespace {
+struct CapturedStep {
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+};
+}  // namespace
+
+void Graph::capture_begin() {
+  if (capturing) invalid("capture_begin: a capture is already running on this graph");
+  cuck(cudaStreamSynchronize(stream), "sync");
+  check_status();
+  cuck(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+  capturing = true;
+}
+
+void* Graph::capture_end() {
+  if (!capturing) invalid("capture_end: no capture is running");
+  capturing = false;
+  CapturedStep* cs = new CapturedStep();
+  cudaError_t e = cudaStreamEndCapture(stream, &cs->graph);
+  if (e != cudaSuccess || !cs->graph) {
+    delete cs;
+    cudaGetLastError();
+    throw EisenException(EISEN_ERR_CUDA, std::string("cudaStreamEndCapture: ") + cudaGetErrorString(e) +
+                                             " (the captured step allocated, synchronised or waited on the host?)");
+  }
+  e = cudaGraphInstantiate(&cs->exec, cs->graph, 0);
+  if (e != cudaSuccess) {
+    cudaGraphDestroy(cs->graph);
+    delete cs;
+    throw EisenException(EISEN_ERR_CUDA, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e));
+  }
+  return cs;
 }
 
 void Graph::check_status() {

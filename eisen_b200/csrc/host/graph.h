@@ -86,6 +86,14 @@ class Graph {
   void seed_grad_ones(int64_t id);
   void synchronize();
   void check_status();                      // raises if a kernel recorded a fault
+  // CUDA-graph capture of everything enqueued on the graph's stream between the two calls (a whole
+  // training step of a small model is hundreds of launches of a few microseconds: launch-bound).
+  // The captured work must allocate nothing and never wait on the host: run the same step eagerly
+  // first so that the pool, the scratch buffers and the RoPE tables are warm.  The executable
+  // graph replays the captured launches with the captured pointers.
+  void capture_begin();
+  void* capture_end();                      // -> handle for graph_replay / graph_exec_destroy
+  bool capturing = false;
 
   // ---- ops (src/graph/ops/*.rs)
   int64_t add(int64_t a, int64_t b);
@@ -329,6 +337,11 @@ class AdamW {
   // (the reference's streamed parameters are updated by its CPU arm, src/nn/optim.rs:523-543)
   std::vector<float*> m_ptr, v_ptr;
   std::vector<float*> host_moments;  // page-locked buffers owned by this optimizer
+  // step-dependent scalars of a captured step: {lr, bc1, bc2, -} in page-locked host memory, copied to
+  // the device by a node of the captured graph
+  float* hyper_host = nullptr;
+  float* hyper_dev = nullptr;
+  void advance();
   int64_t total = 0;
   double* sumsq_dev = nullptr;
   void* sumsq_ws = nullptr;

@@ -673,6 +673,8 @@ AdamW::~AdamW() {
   cudaFree(sumsq_dev);
   cudaFree(sumsq_ws);
   for (float* p : host_moments) cudaFreeHost(p);
+  if (hyper_host) cudaFreeHost(hyper_host);
+  if (hyper_dev) cudaFree(hyper_dev);
 }
 
 void AdamW::zero_grad() {
@@ -716,22 +718,45 @@ float AdamW::clip_grad_norm(float max_norm, float* coef_out) {
   return norm;
 }
 
-void AdamW::launch(float grad_scale, const double* sumsq, float max_norm) {
+// t += 1 and the step's scalars into the page-locked record a captured step copies from
+void AdamW::advance() {
+  if (!hyper_host) {
+    cuck(cudaHostAlloc((void**)&hyper_host, 16, cudaHostAllocDefault), "cudaHostAlloc(adam scalars)");
+    cuck(cudaMalloc((void**)&hyper_dev, 16), "cudaMalloc(adam scalars)");
+  }
   t += 1;
+  float p1 = 1.0f, p2 = 1.0f;
+  for (int64_t i = 0; i < t; ++i) { p1 *= beta1; p2 *= beta2; }
+  hyper_host[0] = lr;
+  hyper_host[1] = 1.0f / (1.0f - p1);
+  hyper_host[2] = 1.0f / (1.0f - p2);
+  hyper_host[3] = 0.0f;
+}
+
+void AdamW::launch(float grad_scale, const double* sumsq, float max_norm) {
+  const float* hyper = nullptr;
+  if (g.capturing) {
+    // recorded once, replayed every step: the scalars come from device memory (see advance())
+    if (!hyper_host) throw EisenException(EISEN_ERR_INVALID, "optimizer step inside a capture: call eisen_optim_advance first");
+    cuck(cudaMemcpyAsync(hyper_dev, hyper_host, 16, cudaMemcpyHostToDevice, g.stream), "H2D(adam scalars)");
+    hyper = hyper_dev;
+  } else {
+    t += 1;
+  }
   // src/nn/optim.rs:336-338: reciprocal bias corrections from powi
   float p1 = 1.0f, p2 = 1.0f;
   for (int64_t i = 0; i < t; ++i) { p1 *= beta1; p2 *= beta2; }
   const float bc1 = 1.0f / (1.0f - p1), bc2 = 1.0f / (1.0f - p2);
   if (flat) {
-    ck(eisen_adamw_step(g.stream, g.arena_w, g.arena_shadow, g.arena_g, m, v, total, lr, beta1, beta2, eps, weight_decay,
-                        bc1, bc2, grad_scale, sumsq, max_norm),
+    ck(eisen_adamw_step_dev(g.stream, g.arena_w, g.arena_shadow, g.arena_g, m, v, total, lr, beta1, beta2, eps, weight_decay,
+                            bc1, bc2, grad_scale, sumsq, max_norm, hyper),
        "adamw_step");
     return;
   }
   for (size_t i = 0; i < params.size(); ++i) {
     HTensor& tt = g.tensors[params[i]];
-    ck(eisen_adamw_step(g.stream, (float*)tt.data, tt.shadow, (const float*)tt.grad, m_ptr[i], v_ptr[i],
-                        tt.numel, lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale, sumsq, max_norm),
+    ck(eisen_adamw_step_dev(g.stream, (float*)tt.data, tt.shadow, (const float*)tt.grad, m_ptr[i], v_ptr[i],
+                            tt.numel, lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale, sumsq, max_norm, hyper),
        "adamw_step");
   }
   g.invalidate_staged_weights();  // staged copies of host-homed weights are stale now

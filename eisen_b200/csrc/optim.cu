@@ -33,7 +33,9 @@ __global__ void __launch_bounds__(OPT_THREADS)
 adamw_kernel(float* __restrict__ w, __nv_bfloat16* __restrict__ w_bf16, const float* __restrict__ g,
              float* __restrict__ m, float* __restrict__ v, long long n, float lr, float b1, float b2, float eps,
              float wd, float bc1, float bc2, float grad_scale, const double* __restrict__ sumsq,
-             float max_norm) {
+             float max_norm, const float* __restrict__ hyper) {
+  // step-dependent scalars from device memory (a launch recorded once and replayed every step)
+  if (hyper != nullptr) { lr = hyper[0]; bc1 = hyper[1]; bc2 = hyper[2]; }
   float gs = grad_scale;
   if (sumsq != nullptr && max_norm > 0.0f) {
     // clip coefficient of src/nn/optim.rs:283-287 applied to the scaled gradient
@@ -123,13 +125,22 @@ extern "C" {
 int eisen_adamw_step(void* stream, float* w, void* w_bf16, const float* g, float* m, float* v, long long n,
                      float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2,
                      float grad_scale, const double* sumsq, float max_norm) {
+  return eisen_adamw_step_dev(stream, w, w_bf16, g, m, v, n, lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale,
+                              sumsq, max_norm, nullptr);
+}
+
+// As eisen_adamw_step; when hyper (device float[3]) is not null the kernel takes lr, bc1 and bc2 from
+// it instead of from the arguments.
+int eisen_adamw_step_dev(void* stream, float* w, void* w_bf16, const float* g, float* m, float* v, long long n,
+                         float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2,
+                         float grad_scale, const double* sumsq, float max_norm, const float* hyper) {
   if (n <= 0) return 0;
   if (!aligned16(w) || !aligned16(g) || !aligned16(m) || !aligned16(v) || (w_bf16 && (reinterpret_cast<uintptr_t>(w_bf16) & 7)))
     return fail(EISEN_ERR_INVALID, "adamw_step: buffers must be 16-byte aligned");
   const int grid = grid_for(n >> 2, OPT_THREADS, 8);
   adamw_kernel<<<grid, OPT_THREADS, 0, (cudaStream_t)stream>>>(w, (__nv_bfloat16*)w_bf16, g, m, v, n, lr, beta1,
                                                               beta2, eps, weight_decay, bc1, bc2, grad_scale,
-                                                              sumsq, max_norm);
+                                                              sumsq, max_norm, hyper);
   return check_launch("adamw_step");
 }
 

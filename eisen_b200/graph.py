@@ -21,6 +21,27 @@ def _ll(seq):
     return (C.c_longlong * max(1, len(seq)))(*[int(x) for x in seq])
 
 
+class CapturedStep:
+    """An executable CUDA graph of a captured step (Graph.capture)."""
+
+    def __init__(self, handle, stream):
+        self._h, self.stream = handle, stream
+
+    def replay(self):
+        call("eisen_graph_replay", self._h, self.stream)
+
+    def close(self):
+        if self._h:
+            lib().eisen_graph_exec_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class Graph:
     def __init__(self, precision=FP32, stream=0):
         """stream: a cudaStream_t as an integer (e.g. torch.cuda.current_stream().cuda_stream)."""
@@ -39,6 +60,19 @@ class Graph:
             self.close()
         except Exception:
             pass
+
+    def capture(self, fn):
+        """Records everything fn() enqueues on the graph's stream into a CUDA graph and returns a
+        CapturedStep.  Run fn() once eagerly beforehand so that the capture allocates nothing."""
+        call("eisen_graph_capture_begin", self._h)
+        try:
+            fn()
+        except Exception:
+            lib().eisen_graph_capture_abort(self._h)
+            raise
+        h = C.c_void_p()
+        call("eisen_graph_capture_end", self._h, C.byref(h))
+        return CapturedStep(h, self.stream)
 
     def set_vram_budget(self, budget_bytes, activation_reserve_bytes=64 << 20):
         """Budget for everything the graph allocates on the device; set it before building the model."""
@@ -356,6 +390,11 @@ class AdamW:
 
     def step_fused(self, max_norm=0.0, grad_scale=1.0):
         call("eisen_optim_step_fused", self._h, max_norm, grad_scale)
+
+    def advance(self):
+        """For steps replayed from a CUDA graph: t += 1 and this step's lr / bias corrections into
+        the record the captured optimizer launch reads; call before the capture and before every replay."""
+        call("eisen_optim_advance", self._h)
 
     def save_state(self, path):
         """Step count, hyper-parameters and moments: with the weights file this resumes a run bit for bit."""

@@ -294,6 +294,11 @@ int eisen_embedding_bwd_static(void* stream, const void* g, int g_dtype, const i
 int eisen_adamw_step(void* stream, float* w, void* w_bf16, const float* g, float* m, float* v, long long n,
                      float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2,
                      float grad_scale, const double* sumsq, float max_norm);
+/* The same update with the step-dependent scalars (lr, bc1, bc2) read from device memory when
+ * hyper is not null: for a launch that is recorded once in a CUDA graph and replayed every step. */
+int eisen_adamw_step_dev(void* stream, float* w, void* w_bf16, const float* g, float* m, float* v, long long n,
+                         float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2,
+                         float grad_scale, const double* sumsq, float max_norm, const float* hyper);
 long long eisen_sumsq_workspace_bytes(long long n);
 /* *out (device f64) (op)= sum x^2 — the device-side half of AdamW::clip_grad_norm
  * (src/nn/optim.rs:250-281 copies every gradient to the host instead). */
@@ -354,6 +359,19 @@ int eisen_graph_reinterpret_shape(void* g, long long id, const long long* shape,
 int eisen_graph_zero_grad(void* g, long long id);
 int eisen_graph_backward(void* g, long long loss_id);                                  /* :670-796 */
 int eisen_graph_synchronize(void* g);   /* waits for the stream and raises recorded kernel faults */
+/* CUDA-graph capture of a whole step (no counterpart in the reference, which synchronises after almost
+ * every launch): everything the graph-level calls enqueue between capture_begin and capture_end is
+ * recorded instead of run, and eisen_graph_replay launches it as one executable graph.  For steps
+ * that are launch-bound (a 14M-parameter model: about 1500 launches of a few microseconds).  Rules:
+ * run the identical step eagerly first (the capture may not allocate: a pool miss fails with
+ * EISEN_ERR_INVALID), feed token ids through tensors that live below the parameter watermark and
+ * refresh their contents between replays, read the loss from the device pointer the loss tensor had
+ * during capture.  capture_abort ends a capture after a failed call. */
+int eisen_graph_capture_begin(void* g);
+int eisen_graph_capture_end(void* g, void** exec_out);
+int eisen_graph_capture_abort(void* g);
+int eisen_graph_replay(void* exec, void* stream);
+int eisen_graph_exec_destroy(void* exec);
 /* runs eisen_selftest_bounded_wait on the graph's stream against the graph's own fault word: the
  * next eisen_graph_synchronize must return EISEN_ERR_KERNEL and clear the word */
 int eisen_graph_selftest_bounded_wait(void* g, long long budget_cycles);
@@ -473,6 +491,11 @@ int eisen_optim_step(void* opt);
 /* clip (max_norm > 0) and step without a host round trip; the gradient is read as g * grad_scale */
 int eisen_optim_step_fused(void* opt, float max_norm, float grad_scale);
 int eisen_optim_is_flat(void* opt, int* flat);
+/* For a step replayed from a CUDA graph (eisen_graph_capture_*): an optimizer step enqueued during
+ * capture takes lr and the bias corrections from device memory, refreshed by a copy node from a
+ * page-locked host record; eisen_optim_advance (t += 1, new bias corrections, current lr into that
+ * record) must be called before every replay, and once before the capture itself. */
+int eisen_optim_advance(void* opt);
 /* Optimizer state of a checkpoint: step count, hyper-parameters and the AdamW moments (of this
  * rank's ranges for a sharded optimizer), so that weights file + state file resume a run bit for
  * bit.  The reference saves weights only (examples/train_llm.rs:93-105) and lists optimizer state

@@ -546,3 +546,84 @@ def test_bf16_checkpointed_step_with_kept_attention_output():
     for a, b in zip(*grads):
         assert rel_l2(b, a) < 1e-3
     assert live[0] == live[1]  # every pooled buffer, the stashed ones included, went back to the pool
+
+
+def test_captured_step_replays_like_eager_steps():
+    """A whole bf16 training step (zero_grad, forward, loss, backward, clip, AdamW) recorded into a CUDA
+    graph and replayed three times equals three eager steps (up to the order of the f32 atomic adds of
+    the split-k weight gradients); the optimizer's step count and bias corrections advance through
+    device memory, the token ids through the resident id tensors.  (The Fp32 graph's reference
+    attention chain uploads its mask from the host and cannot be captured.)"""
+    cfg = dict(vocab=256, hidden=128, heads=2, kv=1, ffn=256, layers=2, batch=2, seq=128)
+    rng = np.random.default_rng(21)
+    batches = [(rng.integers(0, cfg["vocab"], (2, 128)).astype(np.int32), rng.integers(0, cfg["vocab"], 256).astype(np.int32))
+               for _ in range(4)]
+
+    def build():
+        stream = torch.cuda.Stream()
+        g = Graph(BF16_MIXED, stream.cuda_stream)
+        lm = TransformerLM(g, cfg["vocab"], cfg["hidden"], cfg["heads"], cfg["kv"], cfg["ffn"], cfg["layers"], False)
+        x = g.alloc_ids([2, 128], batches[0][0])   # below the parameter watermark: they survive clear_activations
+        t = g.alloc_ids([256], batches[0][1])
+        g.mark_params()
+        r = np.random.default_rng(3)
+        for p in lm.params():
+            shp = g.shape(p)
+            if len(shp) == 2:
+                g.load_tensor_data(p, (r.standard_normal(int(np.prod(shp))) * 0.02).astype(np.float32))
+        opt = AdamW(g, lm.params(), 1e-3)
+        opt.config(1e-3, 0.9, 0.95, 1e-8, 0.1)
+        return stream, g, lm, opt, x, t
+
+    def feed(g, x, t, b):
+        from eisen_b200.dp import _CudaView
+        dev = torch.device("cuda", torch.cuda.current_device())
+        for tid, src in ((x, b[0].reshape(-1)), (t, b[1])):
+            view = torch.as_tensor(_CudaView(g.tensor_ptrs(tid)[0], src.size, "<i4"), device=dev)
+            g.synchronize()
+            view.copy_(torch.from_numpy(src.copy()))
+        torch.cuda.synchronize()
+
+    def one_step(g, lm, opt, x, t):
+        opt.zero_grad()
+        lm.train_micro_step_dev(x, t, 256, checkpoint=True)
+        g.clear_activations()
+        opt.step_fused(1.0, 1.0)
+
+    # eager: four steps
+    s1, g1, lm1, o1, x1, t1 = build()
+    for b in batches:
+        feed(g1, x1, t1, b)
+        one_step(g1, lm1, o1, x1, t1)
+    g1.synchronize()
+    # captured: first step eager (warms the pool), then capture once and replay for the other three
+    s2, g2, lm2, o2, x2, t2 = build()
+    feed(g2, x2, t2, batches[0])
+    one_step(g2, lm2, o2, x2, t2)
+    g2.synchronize()
+    o2.advance()
+    step = g2.capture(lambda: one_step(g2, lm2, o2, x2, t2))
+    for i, b in enumerate(batches[1:]):
+        if i > 0:
+            o2.advance()
+        feed(g2, x2, t2, b)
+        step.replay()
+        g2.synchronize()
+    for a, b in zip(lm1.params(), lm2.params()):
+        assert rel_l2(g2.data(b), g1.data(a)) < 1e-4
+    # the step counter advanced: a fifth eager step on both still agrees (moments and t are in step)
+    for g, lm, o, x, t in ((g1, lm1, o1, x1, t1), (g2, lm2, o2, x2, t2)):
+        feed(g, x, t, batches[0])
+        one_step(g, lm, o, x, t)
+        g.synchronize()
+    for a, b in zip(lm1.params(), lm2.params()):
+        assert rel_l2(g2.data(b), g1.data(a)) < 1e-4
+    # a capture that would have to allocate is refused, and the graph stays usable
+    s3 = torch.cuda.Stream()  # the legacy default stream cannot be captured
+    g3 = Graph(FP32, s3.cuda_stream)
+    w = g3.alloc([8, 8], np.eye(8))
+    g3.mark_params()
+    xin = g3.alloc([4, 8], np.ones(32))
+    with pytest.raises(eb.EisenError, match="not cached"):
+        g3.capture(lambda: g3.matmul(xin, w))
+    assert np.allclose(g3.data(g3.matmul(xin, w)), 1.0)
