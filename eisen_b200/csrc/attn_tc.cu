@@ -1194,6 +1194,60 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
   }
 }
 
+// The two preparations of the backward in one pass: delta[b,h,s] = sum_d o*do (as attn_delta_kernel)
+// and dq_acc = 0 (the f32 buffer the key-tile CTAs add their dQ tiles to; contiguous [B,S,H,D], so the
+// thread that reads vector i of O / dO clears the 32 bytes of vector i).  32-bit index arithmetic
+// (the caller checks B*S*H*D < 2^31), two vectors per thread requested before the first use.  A row's
+// LPR lanes always sit in one warp and are valid together (LPR divides 32 and the row count is whole).
+template <int D>
+__global__ void __launch_bounds__(256)
+attn_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
+                 float* __restrict__ dq_acc, unsigned nvec, unsigned S, unsigned H, long long bs, long long ss, long long hs) {
+  constexpr unsigned LPR = D / 8;  // lanes per (b,s,h) row
+  const unsigned stride = gridDim.x * blockDim.x;
+  const unsigned lane = threadIdx.x & 31;
+  const float4 z = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  // the loop runs on warp bases so that every lane of a warp takes part in each shuffle
+  for (unsigned base = blockIdx.x * blockDim.x + (threadIdx.x - lane); base < nvec; base += 2 * stride) {
+    const bool warp_two = base + stride < nvec;  // uniform over the warp
+    const unsigned tt[2] = {base + lane, base + stride + lane};
+    const bool valid[2] = {tt[0] < nvec, warp_two && tt[1] < nvec};
+    long long off[2];
+    unsigned bq[2], hq[2], sq[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const unsigned t = valid[u] ? tt[u] : 0u;
+      const unsigned w = t / LPR, c = (t % LPR) * 8;
+      hq[u] = w % H;
+      const unsigned ws = w / H;
+      sq[u] = ws % S;
+      bq[u] = ws / S;
+      off[u] = (long long)bq[u] * bs + (long long)sq[u] * ss + (long long)hq[u] * hs + c;
+    }
+    float x0[8], y0[8], x1[8], y1[8];
+    ld16(o + off[0], x0); ld16(d_o + off[0], y0);
+    ld16(o + off[1], x1); ld16(d_o + off[1], y1);
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (valid[u]) {
+        float4* zp = reinterpret_cast<float4*>(dq_acc + (size_t)tt[u] * 8);
+        zp[0] = z;
+        zp[1] = z;
+      }
+    }
+    float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { a0 = fmaf(x0[k], y0[k], a0); a1 = fmaf(x1[k], y1[k], a1); }
+#pragma unroll
+    for (unsigned m = LPR / 2; m > 0; m >>= 1) {
+      a0 += __shfl_xor_sync(0xffffffffu, a0, m);
+      a1 += __shfl_xor_sync(0xffffffffu, a1, m);
+    }
+    if (valid[0] && (tt[0] % LPR) == 0) delta[((size_t)bq[0] * H + hq[0]) * S + sq[0]] = a0;
+    if (valid[1] && (tt[1] % LPR) == 0) delta[((size_t)bq[1] * H + hq[1]) * S + sq[1]] = a1;
+  }
+}
+
 // dq (bf16, strided [B,S,H,D]) = dq_acc (f32, contiguous [B,S,H,D])
 __global__ void __launch_bounds__(256)
 attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long rows /*B*S*H*/,
@@ -1317,14 +1371,27 @@ int eisen_attn_bwd(void* stream, const void* q, const void* k, const void* v, co
   cudaStream_t s = (cudaStream_t)stream;
   float* dq_acc = (float*)workspace;
   float* delta = dq_acc + B * S * Hq * D;
-  if (cudaMemsetAsync(dq_acc, 0, (size_t)(B * S * Hq * D) * 4, s) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_bwd: memset failed");
-  // total threads is a multiple of 32 (S*H*D/8 with D/8 in {8,16}), so every shuffle group is complete
-  if (D == 64)
-    attn_delta_kernel<64><<<grid_for(B * S * Hq * 8, 256, 8), 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o,
-                                                                          delta, (int)B, (int)S, (int)Hq, o_bs, o_ss, o_hs);
-  else
-    attn_delta_kernel<128><<<grid_for(B * S * Hq * 16, 256, 8), 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o,
+  const long long n_elems = B * S * Hq * D;
+  if (n_elems < 0x7fffffffLL) {
+    // delta and the clearing of the dQ accumulation buffer in one pass
+    const unsigned nvec = (unsigned)(n_elems / 8);
+    const int grid = grid_for((nvec + 1) / 2, 256, 8);
+    if (D == 64)
+      attn_prep_kernel<64><<<grid, 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, dq_acc, nvec,
+                                                (unsigned)S, (unsigned)Hq, o_bs, o_ss, o_hs);
+    else
+      attn_prep_kernel<128><<<grid, 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, dq_acc, nvec,
+                                                 (unsigned)S, (unsigned)Hq, o_bs, o_ss, o_hs);
+  } else {
+    if (cudaMemsetAsync(dq_acc, 0, (size_t)n_elems * 4, s) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_bwd: memset failed");
+    // total threads is a multiple of 32 (S*H*D/8 with D/8 in {8,16}), so every shuffle group is complete
+    if (D == 64)
+      attn_delta_kernel<64><<<grid_for(B * S * Hq * 8, 256, 8), 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o,
                                                                             delta, (int)B, (int)S, (int)Hq, o_bs, o_ss, o_hs);
+    else
+      attn_delta_kernel<128><<<grid_for(B * S * Hq * 16, 256, 8), 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o,
+                                                                              delta, (int)B, (int)S, (int)Hq, o_bs, o_ss, o_hs);
+  }
   rc = check_launch("attn_delta");
   if (rc) return rc;
   CUtensorMap tq, tk, tv, tdo;
