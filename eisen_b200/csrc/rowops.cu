@@ -363,6 +363,91 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ w, const T
 }
 
 
+// Forward with the rows staged in shared memory by bulk asynchronous copies, the forward twin of
+// rmsnorm_bwd_staged_kernel: a CTA of 256 threads takes ROWS rows per stage, thread t owns vector t
+// of every row and keeps its weights in registers; the row sums of squares go through one
+// shuffle reduction and one barrier per stage.  Needs dim == 256 vectors and rows % ROWS == 0.
+template <typename T, int S, int CTAS>
+__global__ void __launch_bounds__(RB_THREADS, CTAS)
+rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const float* __restrict__ w, T* __restrict__ y,
+                          float* __restrict__ rrms_out, long long groups, float eps) {
+  constexpr int V = VecOf<T>::N;
+  constexpr int DIM = RB_THREADS * V;
+  constexpr int ROWS = 4;
+  constexpr uint32_t STAGE_BYTES = ROWS * DIM * sizeof(T);
+  extern __shared__ __align__(128) uint8_t rs_smem[];
+  __shared__ uint64_t full_bar[S];
+  __shared__ float sh[2][RB_THREADS / 32][ROWS];
+  __shared__ int abort_flag;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) mbar_init(&full_bar[i], 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  float wv[V];
+#pragma unroll
+  for (int k = 0; k < V; ++k) wv[k] = w[threadIdx.x * V + k];
+  const long long g0 = blockIdx.x, gstride = gridDim.x;
+  const long long n_mine = g0 < groups ? (groups - g0 + gstride - 1) / gstride : 0;
+  auto issue = [&](long long k) {
+    if (threadIdx.x == 0 && k < n_mine) {
+      const int st = (int)(k % S);
+      const long long r0 = (g0 + k * gstride) * ROWS;
+      mbar_arrive_expect_tx(&full_bar[st], STAGE_BYTES);
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(smem_u32(rs_smem + (size_t)st * STAGE_BYTES)), "l"(x + r0 * DIM), "r"(STAGE_BYTES),
+                   "r"(smem_u32(&full_bar[st])) : "memory");
+    }
+  };
+  for (int k = 0; k < S - 1; ++k) issue(k);
+  int buf = 0;
+  for (long long k = 0; k < n_mine; ++k) {
+    const int st = (int)(k % S);
+    const uint32_t ph = (uint32_t)((k / S) & 1);
+    const long long r0 = (g0 + k * gstride) * ROWS;
+    mbar_wait(&full_bar[st], ph, &abort_flag, nullptr, FAULT_WAIT_FULL);
+    const T* sx = reinterpret_cast<const T*>(rs_smem + (size_t)st * STAGE_BYTES) + threadIdx.x * V;
+    float xv[ROWS][V], part[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      ld16(sx + r * DIM, xv[r]);
+      float a = 0.0f, b = 0.0f;
+#pragma unroll
+      for (int e = 0; e < V; e += 2) { a = fmaf(xv[r][e], xv[r][e], a); b = fmaf(xv[r][e + 1], xv[r][e + 1], b); }
+      part[r] = a + b;
+    }
+    // four sums over the warp by recursive halving: lane l ends with the total of row ((l>>4)&1)*2 + ((l>>3)&1)
+    float w2[2];
+    const bool hi = lane & 16;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) w2[i] = (hi ? part[i + 2] : part[i]) + __shfl_xor_sync(0xffffffffu, hi ? part[i] : part[i + 2], 16);
+    const bool h8 = lane & 8;
+    float w1 = (h8 ? w2[1] : w2[0]) + __shfl_xor_sync(0xffffffffu, h8 ? w2[0] : w2[1], 8);
+    w1 += __shfl_xor_sync(0xffffffffu, w1, 4);
+    w1 += __shfl_xor_sync(0xffffffffu, w1, 2);
+    w1 += __shfl_xor_sync(0xffffffffu, w1, 1);
+    if ((lane & 7) == 0) sh[buf][warp][((lane >> 4) & 1) * 2 + ((lane >> 3) & 1)] = w1;
+    __syncthreads();
+    issue(k + S - 1);  // its stage was last read before this barrier (the rows now sit in registers)
+    float t = 0.0f;
+#pragma unroll
+    for (int wq = 0; wq < RB_THREADS / 32; ++wq) t += sh[buf][wq][lane & 3];
+    const float rr = 1.0f / sqrtf(t / (float)DIM + eps);
+    buf ^= 1;
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const float rrms = __shfl_sync(0xffffffffu, rr, r);
+      if (rrms_out && threadIdx.x == 0) rrms_out[r0 + r] = rrms;
+      float o[V];
+#pragma unroll
+      for (int e = 0; e < V; ++e) o[e] = xv[r][e] * rrms * wv[e];
+      st16(y + (r0 + r) * DIM + threadIdx.x * V, o);
+    }
+  }
+}
+
 // Backward with the rows staged in shared memory by bulk asynchronous copies (one 1-D copy per
 // tensor and group of ROWS rows, completion on an mbarrier): S stages per CTA are in flight instead
 // of what fits the registers, and without row buffers in registers three or four CTAs fit an SM.
@@ -548,6 +633,7 @@ __global__ void rmsnorm_bwd_generic_kernel(const T* __restrict__ x, const float*
 // the CTA writes one row of dw_partial, which reduce_partials_kernel adds up (no atomics).
 constexpr int RW_WARPS = 8;
 int g_rms_bwd_mode = 2;  // eisen_rmsnorm_bwd_set_mode
+bool g_rms_fwd_staged = true;  // eisen_rmsnorm_fwd_set_mode
 
 template <typename T, int NV>
 __global__ void __launch_bounds__(RW_WARPS * 32, 1)
@@ -1113,9 +1199,31 @@ int eisen_rmsnorm_fwd(void* stream, const void* x, const float* w, void* y, floa
   if (!aligned16(x) || !aligned16(y)) return fail(EISEN_ERR_INVALID, "rmsnorm_fwd: unaligned pointer");
   const int grid = grid_for(rows, RN_WARPS, 8);
   EISEN_DISPATCH_DTYPE(dt, T, {
+    if (g_rms_fwd_staged && dim == RB_THREADS * VecOf<T>::N && rows % 4 == 0 && rows >= 4 && aligned16(w)) {
+      // rows staged in shared memory: 3 stages of 4 rows, four CTAs per SM
+      constexpr int ST = 3, CT = 4;
+      const long long groups = rows / 4;
+      const long long cap = (long long)sm_count() * CT;
+      const size_t smem = (size_t)ST * 4 * dim * sizeof(T);
+      static bool attr[2][MAX_DEVICE_SLOTS] = {{false}};
+      bool& done = attr[sizeof(T) == 2][device_slot()];
+      if (!done) {
+        if (cudaFuncSetAttribute(rmsnorm_fwd_staged_kernel<T, ST, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+          return fail(EISEN_ERR_CUDA, "rmsnorm_fwd: shared-memory attribute");
+        done = true;
+      }
+      rmsnorm_fwd_staged_kernel<T, ST, CT><<<(int)(groups < cap ? groups : cap), RB_THREADS, smem, (cudaStream_t)stream>>>(
+          (const T*)x, w, (T*)y, rrms_out, groups, eps);
+      return check_launch("rmsnorm_fwd_staged");
+    }
     rmsnorm_fwd_dispatch<T>((const T*)x, w, (T*)y, rrms_out, rows, (int)dim, eps, grid, (cudaStream_t)stream);
     return check_launch("rmsnorm_fwd");
   });
+}
+
+int eisen_rmsnorm_fwd_set_mode(int staged) {
+  g_rms_fwd_staged = staged != 0;
+  return 0;
 }
 
 int eisen_rmsnorm_bwd_set_mode(int mode) {

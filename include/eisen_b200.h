@@ -165,6 +165,9 @@ int eisen_attn_decode(void* stream, const void* q, const void* k_cache, const vo
  * src/graph/ops/normalization.rs:88). */
 int eisen_rmsnorm_fwd(void* stream, const void* x, const float* w, void* y, float* rrms_out, long long rows,
                       long long dim, float eps, int dtype);
+/* 1 (default): rows of exactly 256 16-byte vectors are staged in shared memory by bulk asynchronous
+ * copies; 0: always the warp-per-row kernel.  Process-wide; meant for tests and measurements. */
+int eisen_rmsnorm_fwd_set_mode(int staged);
 long long eisen_rmsnorm_bwd_workspace_bytes(long long rows, long long dim);
 /* Kernel of eisen_rmsnorm_bwd where several apply: 0 = CTA-wide kernel with the rows in registers,
  * 1 = warp per row, 2 / 3 / 4 = rows staged in shared memory by bulk asynchronous copies (4 rows x 3
