@@ -92,6 +92,28 @@ def case_gemm_swiglu(M, N, K, keep_gate_up=True, iters=3):
     return dict(ms=ms, tflops=4.0 * M * N * K / ms / 1e9, shape=[M, N, K], keep_gate_up=keep_gate_up, status=int(st.item()))
 
 
+def case_gemm_rope(M, N, K, seq, head_dim, iters=3, sets=0):
+    # q / k projection with the RoPE rotation in the epilogue, beside the plain projection of the same shape
+    dev, s, st = _ctx()
+    ns = n_sets_for(2 * (M * K + N * K + M * N), sets)
+    tab = torch.empty(seq * (head_dim // 2) * 2, device=dev)
+    eb.call("eisen_rope_table", s, P(tab), seq, head_dim, 10000.0)
+    fr, fp, keep = [], [], []
+    for _ in range(ns):
+        A = torch.randn(M, K, device=dev).to(torch.bfloat16)
+        B = (torch.randn(K, N, device=dev) * 0.05).to(torch.bfloat16)
+        C = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        keep.append((A, B, C))
+        fr.append(lambda A=A, B=B, C=C: eb.call("eisen_gemm_bf16_rope", s, M, N, K, P(A), K, P(B), N, P(C), N, P(tab), seq,
+                                                head_dim, P(st)))
+        fp.append(lambda A=A, B=B, C=C: eb.call("eisen_gemm_bf16", s, 0, 1, M, N, K, P(A), K, P(B), N, P(C), N, 0, 0, 1.0, P(st)))
+    mr = timed(fr, iters)
+    mp = timed(fp, iters)
+    fl = 2.0 * M * N * K
+    return dict(rope_ms=mr, rope_tflops=fl / mr / 1e9, plain_ms=mp, plain_tflops=fl / mp / 1e9, shape=[M, N, K], sets=ns,
+                status=int(st.item()))
+
+
 def case_attn(B_, S, Hq, Hkv, D, iters=3, sets=0):
     dev, s, st = _ctx()
     per_set = 2 * B_ * S * D * (4 * Hq + 4 * Hkv)
@@ -232,7 +254,7 @@ def case_elementwise(rows, dim, seq, head_dim, vocab, nelem, iters=3, sets=0):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "gemm_swiglu", "attn", "ce", "rmsnorm", "adamw", "swiglu", "elementwise"])
+    ap.add_argument("case", choices=["gemm", "gemm_swiglu", "gemm_rope", "attn", "ce", "rmsnorm", "adamw", "swiglu", "elementwise"])
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--sets", type=int, default=0, help="buffer sets to rotate through (0: enough to cover 3 x L2)")
     ap.add_argument("--m", type=int, default=8192)
@@ -261,6 +283,8 @@ def main():
         out = case_gemm(a.m, a.n, a.k, a.a_mn, a.b_mn, a.out_mode, a.split_k, a.iters, a.sets)
     elif a.case == "gemm_swiglu":
         out = case_gemm_swiglu(a.m, a.n, a.k, a.out_mode == 1, a.iters)
+    elif a.case == "gemm_rope":
+        out = case_gemm_rope(a.m, a.n, a.k, a.seq, a.head_dim, a.iters, a.sets)
     elif a.case == "attn":
         out = case_attn(a.batch, a.seq, a.heads, a.kv_heads, a.head_dim, a.iters, a.sets)
     elif a.case == "ce":

@@ -295,10 +295,11 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             reinterpret_cast<const __nv_bfloat16*>(p.R) + (long long)(row0 + rr) * p.ldr + n0 + seg * 8;
 #pragma unroll 1
         for (int c = 0; c < PN / 64; ++c) {
-          uint4 old[8];
+          // addend rows: requested before the TMEM load so that their latency runs beside it
+          uint4 pre[8];  // the addend's eight rows, or the angles of four rows (the modes exclude each other)
           if (acc_bf16) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) old[i] = *reinterpret_cast<const uint4*>(r_base + (long long)(4 * i) * p.ldr + c * 64);
+            for (int i = 0; i < 8; ++i) pre[i] = *reinterpret_cast<const uint4*>(r_base + (long long)(4 * i) * p.ldr + c * 64);
           }
           uint32_t r0[32], r1[32];
           tmem_ld_32x32b_x32(taddr + c * 64, r0);
@@ -320,40 +321,54 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           }
           __syncwarp();
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int rw = 4 * i + rr;
-            uint4 o = *reinterpret_cast<const uint4*>(st + rw * 128 + ((seg ^ (rw & 7)) << 4));
-            if (acc_bf16) {
-              // the product is rounded to bf16 before the addend is added, as a separate matmul
-              // followed by an add would do
-              const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&o);
-              const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&old[i]);
-              uint32_t w[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 fa = __bfloat1622float2(a2[e]), fb = __bfloat1622float2(b2[e]);
-                w[e] = pack_bf16x2(fa.x + fb.x, fa.y + fb.y);
-              }
-              o = make_uint4(w[0], w[1], w[2], w[3]);
-            }
+          for (int h = 0; h < 2; ++h) {
             if (rope) {
-              // four (even, odd) column pairs of one head, rotated by the angles of this row's
-              // position; the product was rounded to bf16 first, as a separate RoPE kernel reads it
-              const int pos = (row0 + rw) % p.rope_s;
+              // the angles of four rows are requested together (inside the store loop each request
+              // would wait for the one before it, since loads stay behind the stores to C)
               const int pair0 = ((n0 + c * 64 + seg * 8) % p.rope_hd) >> 1;
-              const float4* tp = reinterpret_cast<const float4*>(p.rope_tab + (long long)pos * (p.rope_hd >> 1) + pair0);
-              const float4 t0 = tp[0], t1 = tp[1];
-              const float cs[4] = {t0.x, t0.z, t1.x, t1.z}, sn[4] = {t0.y, t0.w, t1.y, t1.w};
-              const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&o);
-              uint32_t w[4];
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 v = __bfloat1622float2(a2[e]);
-                w[e] = pack_bf16x2(v.x * cs[e] - v.y * sn[e], v.x * sn[e] + v.y * cs[e]);
+              for (int ii = 0; ii < 4; ++ii) {
+                const int pos = (row0 + 4 * (4 * h + ii) + rr) % p.rope_s;
+                const uint4* tp = reinterpret_cast<const uint4*>(p.rope_tab + (long long)pos * (p.rope_hd >> 1) + pair0);
+                pre[2 * ii] = __ldg(tp);
+                pre[2 * ii + 1] = __ldg(tp + 1);
               }
-              o = make_uint4(w[0], w[1], w[2], w[3]);
             }
-            *reinterpret_cast<uint4*>(c_base + (long long)(4 * i) * p.ldc + c * 64) = o;
+#pragma unroll
+            for (int ii = 0; ii < 4; ++ii) {
+              const int i = 4 * h + ii;
+              const int rw = 4 * i + rr;
+              uint4 o = *reinterpret_cast<const uint4*>(st + rw * 128 + ((seg ^ (rw & 7)) << 4));
+              if (acc_bf16) {
+                // the product is rounded to bf16 before the addend is added, as a separate matmul
+                // followed by an add would do
+                const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&o);
+                const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&pre[i]);
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 fa = __bfloat1622float2(a2[e]), fb = __bfloat1622float2(b2[e]);
+                  w[e] = pack_bf16x2(fa.x + fb.x, fa.y + fb.y);
+                }
+                o = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+              if (rope) {
+                // four (even, odd) column pairs of one head, rotated by the angles of this row's
+                // position; the product was rounded to bf16 first, as a separate RoPE kernel reads it
+                const uint4 t0 = pre[2 * ii], t1 = pre[2 * ii + 1];
+                const float cs[4] = {__uint_as_float(t0.x), __uint_as_float(t0.z), __uint_as_float(t1.x), __uint_as_float(t1.z)};
+                const float sn[4] = {__uint_as_float(t0.y), __uint_as_float(t0.w), __uint_as_float(t1.y), __uint_as_float(t1.w)};
+                const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&o);
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 v = __bfloat1622float2(a2[e]);
+                  w[e] = pack_bf16x2(v.x * cs[e] - v.y * sn[e], v.x * sn[e] + v.y * cs[e]);
+                }
+                o = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+              *reinterpret_cast<uint4*>(c_base + (long long)(4 * i) * p.ldc + c * 64) = o;
+            }
           }
           __syncwarp();
         }

@@ -327,6 +327,22 @@ def test_bf16_head_dim_128_and_tied_head():
     _check(res, 2e-2, 1e-3)
 
 
+def test_bf16_config2_architecture_step():
+    """Benchmark config 2's architecture (vocab 8192, d 384, 6 blocks, 6 heads of 64, ffn 1024, seq 256,
+    gradient accumulation 2) at a batch the CPU oracle finishes in seconds (2 x 256 tokens per micro-batch)."""
+    from oracle_binding import lib as olib
+    cfg = dict(vocab=8192, hidden=384, heads=6, kv=6, ffn=1024, layers=6, batch=2, seq=256)
+    olib().orc_set_threads(max(1, min(16, os.cpu_count() or 1)))
+    try:
+        og, olm, g, lm = build_pair(cfg, BF16_MIXED, seed=5)
+        ids, tg = _tokens(cfg, 5, n_batches=2)
+        res = run_step(og, olm, g, lm, cfg, ids, tg, checkpoint=True, accum=2, use_micro_step=True)
+    finally:
+        olib().orc_set_threads(1)
+    worst = _check(res, 2e-2, 1e-3)
+    print("config 2 architecture, bf16 worst grad rel-L2", worst)
+
+
 def test_adamw_clip_and_fused_step():
     cfg = dict(vocab=128, hidden=64, heads=2, kv=2, ffn=128, layers=1, batch=2, seq=16)
     ids, tg = _tokens(cfg, 5)
