@@ -114,6 +114,48 @@ def case_gemm_rope(M, N, K, seq, head_dim, iters=3, sets=0):
                 status=int(st.item()))
 
 
+def case_qkv_bwd(M, d, nq, nkv, iters=3):
+    # backward of the q / k / v projections of one input: three launches per product against the
+    # K-segmented (dX) and N-segmented (dW) single launches
+    import ctypes
+    dev, s, st = _ctx()
+    Ns = [nq, nkv, nkv]
+    X = torch.randn(M, d, device=dev).to(torch.bfloat16)
+    dYs = [torch.randn(M, n, device=dev).to(torch.bfloat16) for n in Ns]
+    Ws = [(torch.randn(d, n, device=dev) * 0.05).to(torch.bfloat16) for n in Ns]
+    dX = torch.empty(M, d, device=dev, dtype=torch.bfloat16)
+    dWs = [torch.zeros(d, n, device=dev) for n in Ns]
+    pa = lambda ts: (ctypes.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+    la = lambda vs: (ctypes.c_longlong * len(vs))(*vs)
+
+    def dx_separate():
+        # dV first (store), then dK and dQ accumulate, as the tape walks them
+        for i, mode in ((2, 0), (1, 1), (0, 1)):
+            eb.call("eisen_gemm_bf16", s, 0, 0, M, d, Ns[i], P(dYs[i]), Ns[i], P(Ws[i]), Ns[i], P(dX), d, mode, 1, 1.0, P(st))
+
+    def dx_fused():
+        eb.call("eisen_gemm_bf16_concat_k", s, 0, 0, M, d, 3, pa(dYs), la(Ns), pa(Ws), la(Ns), la(Ns), P(dX), d, 0, 1, 1.0, P(st))
+
+    def dw_separate():
+        for i in range(3):
+            eb.call("eisen_gemm_bf16", s, 1, 1, d, Ns[i], M, P(X), d, P(dYs[i]), Ns[i], P(dWs[i]), Ns[i], 4, 0, 1.0, P(st))
+
+    modes = (ctypes.c_int * 3)(4, 4, 4)
+
+    def dw_fused():
+        eb.call("eisen_gemm_bf16_multi_n", s, 1, 1, d, M, P(X), d, 3, pa(dYs), la(Ns), la(Ns), pa(dWs), la(Ns), modes, 0, 1.0,
+                None, 0, 0, P(st))
+
+    fl = 2.0 * M * d * sum(Ns)
+    out = {}
+    for name, fn in (("dx_separate", dx_separate), ("dx_fused", dx_fused), ("dw_separate", dw_separate), ("dw_fused", dw_fused)):
+        ms = timed(fn, iters)
+        out[name] = dict(ms=ms, tflops=fl / ms / 1e9)
+    out["status"] = int(st.item())
+    out["shape"] = dict(tokens=M, d=d, nq=nq, nkv=nkv)
+    return out
+
+
 def case_attn(B_, S, Hq, Hkv, D, iters=3, sets=0):
     dev, s, st = _ctx()
     per_set = 2 * B_ * S * D * (4 * Hq + 4 * Hkv)
@@ -254,7 +296,7 @@ def case_elementwise(rows, dim, seq, head_dim, vocab, nelem, iters=3, sets=0):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "gemm_swiglu", "gemm_rope", "attn", "ce", "rmsnorm", "adamw", "swiglu", "elementwise"])
+    ap.add_argument("case", choices=["gemm", "gemm_swiglu", "gemm_rope", "qkv_bwd", "attn", "ce", "rmsnorm", "adamw", "swiglu", "elementwise"])
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--sets", type=int, default=0, help="buffer sets to rotate through (0: enough to cover 3 x L2)")
     ap.add_argument("--m", type=int, default=8192)
@@ -285,6 +327,8 @@ def main():
         out = case_gemm_swiglu(a.m, a.n, a.k, a.out_mode == 1, a.iters)
     elif a.case == "gemm_rope":
         out = case_gemm_rope(a.m, a.n, a.k, a.seq, a.head_dim, a.iters, a.sets)
+    elif a.case == "qkv_bwd":
+        out = case_qkv_bwd(a.rows, a.dim, a.n, a.k, a.iters)
     elif a.case == "attn":
         out = case_attn(a.batch, a.seq, a.heads, a.kv_heads, a.head_dim, a.iters, a.sets)
     elif a.case == "ce":

@@ -31,6 +31,8 @@ _CTYPES = {
     "float": C.c_float,
     "double": C.c_double,
     "void**": C.c_void_p,
+    "const void* const*": C.c_void_p,
+    "void* const*": C.c_void_p,
     "eisen_block_cb": C.c_void_p,
 }
 

@@ -93,4 +93,54 @@ int eisen_gemm_bf16_swiglu(void* stream, long long M, long long N, long long K, 
   return 0;
 }
 
+int eisen_gemm_bf16_concat_k(void* stream, int a_mn, int b_mn, long long M, long long N, int n_seg, const void* const* A,
+                             const long long* lda, const void* const* B, const long long* ldb, const long long* K,
+                             void* C, long long ldc, int out_mode, int split_k, float alpha, int* status) {
+  if (n_seg < 1 || n_seg > 3 || !A || !B || !lda || !ldb || !K)
+    return eisen::fail(EISEN_ERR_INVALID, "gemm_bf16_concat_k: 1 to 3 segments, no null arrays");
+  if (out_mode < 0 || out_mode > 4) return eisen::fail(EISEN_ERR_INVALID, "gemm_bf16_concat_k: bad out_mode");
+  int k32[3];
+  long long ktotal = 0;
+  for (int i = 0; i < n_seg; ++i) {
+    if (K[i] > 0x7fffffffLL) return eisen::fail(EISEN_ERR_LIMIT, "gemm_bf16_concat_k: a dimension exceeds 2^31-1");
+    k32[i] = (int)K[i];
+    ktotal += K[i];
+  }
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || ktotal > 0x7fffffffLL)
+    return eisen::fail(EISEN_ERR_LIMIT, "gemm_bf16_concat_k: a dimension exceeds 2^31-1");
+  if (split_k == 0)
+    split_k = out_mode == eisen::GEMM_OUT_F32_ATOMIC ? eisen::gemm_pair_auto_split_k((int)M, (int)N, (int)ktotal) : 1;
+  const char* err = nullptr;
+  int rc = eisen::gemm_bf16_pair_concat_k((cudaStream_t)stream, a_mn, b_mn, (int)M, (int)N, n_seg, A, lda, B, ldb, k32, C, ldc,
+                                          nullptr, 0, out_mode, split_k, alpha, status, &err);
+  if (rc) return eisen::fail(rc == 1 ? EISEN_ERR_INVALID : EISEN_ERR_CUDA, err ? err : "gemm_bf16_concat_k failed");
+  if (M > 0 && N > 0) eisen::count_launch();
+  return 0;
+}
+
+int eisen_gemm_bf16_multi_n(void* stream, int a_mn, int b_mn, long long M, long long K, const void* A, long long lda,
+                            int n_seg, const void* const* B, const long long* ldb, const long long* N, void* const* C,
+                            const long long* ldc, const int* out_mode, int split_k, float alpha,
+                            const float* table_cos_sin, long long seq_len, long long head_dim, int* status) {
+  if (n_seg < 1 || n_seg > 3 || !B || !ldb || !N || !C || !ldc || !out_mode)
+    return eisen::fail(EISEN_ERR_INVALID, "gemm_bf16_multi_n: 1 to 3 segments, no null arrays");
+  int n32[3];
+  long long ntotal = 0;
+  for (int i = 0; i < n_seg; ++i) {
+    if (N[i] > 0x7fffffffLL) return eisen::fail(EISEN_ERR_LIMIT, "gemm_bf16_multi_n: a dimension exceeds 2^31-1");
+    if (out_mode[i] < 0 || out_mode[i] > 5 || out_mode[i] == eisen::GEMM_OUT_BF16_ACC)
+      return eisen::fail(EISEN_ERR_INVALID, "gemm_bf16_multi_n: output modes 0 (bf16), 2 (f32), 4 (f32 add) and 5 (bf16 + RoPE)");
+    n32[i] = (int)N[i];
+    ntotal += N[i];
+  }
+  if (M > 0x7fffffffLL || K > 0x7fffffffLL || ntotal > 0x7fffffffLL || seq_len > 0x7fffffffLL || head_dim > 0x7fffffffLL)
+    return eisen::fail(EISEN_ERR_LIMIT, "gemm_bf16_multi_n: a dimension exceeds 2^31-1");
+  const char* err = nullptr;
+  int rc = eisen::gemm_bf16_pair_multi_n((cudaStream_t)stream, a_mn, b_mn, (int)M, (int)K, A, lda, n_seg, B, ldb, n32, C, ldc,
+                                         out_mode, split_k, alpha, table_cos_sin, (int)seq_len, (int)head_dim, status, &err);
+  if (rc) return eisen::fail(rc == 1 ? EISEN_ERR_INVALID : EISEN_ERR_CUDA, err ? err : "gemm_bf16_multi_n failed");
+  if (M > 0 && K > 0) eisen::count_launch();
+  return 0;
+}
+
 }  // extern "C"

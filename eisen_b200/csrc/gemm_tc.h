@@ -34,6 +34,16 @@ int gemm_bf16_pair_swiglu(cudaStream_t stream, int M, int N, int K, const void* 
 int gemm_bf16_pair_rope(cudaStream_t stream, int M, int N, int K, const void* A, long long lda, const void* B,
                         long long ldb, void* C, long long ldc, const float* table, int seq_len, int head_dim,
                         int* status, const char** err);
+// C (op)= A1 B1^T + A2 B2^T + A3 B3^T in one pass over up to three operand pairs (K segments)
+int gemm_bf16_pair_concat_k(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int n_seg, const void* const* A,
+                            const long long* lda, const void* const* B, const long long* ldb, const int* K, void* C,
+                            long long ldc, const void* R, long long ldr, int out_mode, int split_k, float alpha,
+                            int* status, const char** err);
+// C_i (op)= A B_i^T for up to three B operands that share A, each with its own output (N segments)
+int gemm_bf16_pair_multi_n(cudaStream_t stream, int a_mn, int b_mn, int M, int K, const void* A, long long lda, int n_seg,
+                           const void* const* B, const long long* ldb, const int* N, void* const* C, const long long* ldc,
+                           const int* out_mode, int split_k, float alpha, const float* rope_table, int seq_len,
+                           int head_dim, int* status, const char** err);
 int gemm_pair_auto_split_k(int M, int N, int K);
 // m-tiles per band of the paired kernel's tile order; 0 = chosen by the DRAM-traffic model
 void gemm_pair_set_band(int band);

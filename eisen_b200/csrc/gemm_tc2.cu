@@ -14,6 +14,8 @@
 
 #include <cuda.h>
 
+#include <climits>
+
 namespace eisen {
 namespace {
 
@@ -51,6 +53,16 @@ struct PairParams {
   int rope_s, rope_hd;
   float alpha;
   int* status;
+  // segmented launches (the SEG instantiation of the kernel only).
+  // K segments: the k-blocks from kseg[1] on come from the operand pair (A2, B2), those from kseg[2]
+  // on from (A3, B3): C = A1 B1^T + A2 B2^T + A3 B3^T without intermediate roundings.
+  // N segments: the n-tiles from nseg[1] / nseg[2] on read the B operand B2 / B3 and write their own
+  // output matrix: three products that share A in one launch.  A launch uses one kind or the other.
+  int kseg[3], nseg[3];
+  void* Cs[3];
+  long long ldcs[3];
+  int Ns[3];
+  int out_modes[3];
 };
 
 // Tile order: the m-tiles are cut into bands of `band` tiles; a band is finished (all its n-tiles,
@@ -66,9 +78,16 @@ __device__ __forceinline__ void pair_tile_coords(const PairParams& p, int mn, in
   mt = m_first + (in - nt * rows);
 }
 
+struct SegMaps {
+  CUtensorMap a[2];  // A2, A3 (K segments)
+  CUtensorMap b;     // B3 (B2 travels in the dual mode's slot)
+};
+
+template <bool SEG>
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                     const __grid_constant__ CUtensorMap tmB2, const PairParams p) {
+                     const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ SegMaps seg_maps,
+                     const PairParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -133,8 +152,12 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         int mt, nt;
         pair_tile_coords(p, mn, mt, nt);
         const int m0 = mt * (2 * PM) + (int)rank * PM;
-        const int n0 = p.dual ? nt * (PN / 2) : nt * PN + (int)rank * (PN / 2);
+        int n0 = p.dual ? nt * (PN / 2) : nt * PN + (int)rank * (PN / 2);
         const CUtensorMap* tb = (p.dual && rank == 1) ? &tmB2 : &tmB;
+        if (SEG) {
+          if (nt >= p.nseg[2]) { tb = &seg_maps.b; n0 -= p.nseg[2] * PN; }
+          else if (nt >= p.nseg[1]) { tb = &tmB2; n0 -= p.nseg[1] * PN; }
+        }
         const int kb0 = ks * p.kblocks_per_split;
         const int kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -143,12 +166,17 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           mbar_arrive_expect_tx_cluster(full_leader, PSTAGE_BYTES);
           uint8_t* sa = smem_a + stage * PA_BYTES;
           uint8_t* sb = smem_b + stage * PB_BYTES;
-          const int k0 = kb * BK;
+          int k0 = kb * BK;
+          const CUtensorMap* ta = &tmA;
+          if (SEG) {
+            if (kb >= p.kseg[2]) { ta = &seg_maps.a[1]; tb = &seg_maps.b; k0 -= p.kseg[2] * BK; }
+            else if (kb >= p.kseg[1]) { ta = &seg_maps.a[0]; tb = &tmB2; k0 -= p.kseg[1] * BK; }
+          }
           if (!p.a_mn) {
-            tma_load_2d_pair(sa, &tmA, full_leader, k0, m0);
+            tma_load_2d_pair(sa, ta, full_leader, k0, m0);
           } else {
 #pragma unroll
-            for (int j = 0; j < PM / 64; ++j) tma_load_2d_pair(sa + j * (64 * BK * 2), &tmA, full_leader, m0 + 64 * j, k0);
+            for (int j = 0; j < PM / 64; ++j) tma_load_2d_pair(sa + j * (64 * BK * 2), ta, full_leader, m0 + 64 * j, k0);
           }
           if (!p.b_mn) {
             tma_load_2d_pair(sb, tb, full_leader, k0, n0);
@@ -214,22 +242,34 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       int mt, nt;
       pair_tile_coords(p, mn, mt, nt);
       const int row = mt * (2 * PM) + (int)rank * PM + q * 32 + lane;
-      const int n0 = p.dual ? nt * (PN / 2) : nt * PN;
+      int n0 = p.dual ? nt * (PN / 2) : nt * PN;
+      // output matrix of this tile (one per N segment)
+      void* Cp = p.C;
+      long long ldc = p.ldc;
+      const void* Rp = p.R;
+      long long ldr = p.ldr;
+      int Nn = p.N, out_mode = p.out_mode;
+      if (SEG) {
+        const int sg = nt >= p.nseg[2] ? 2 : (nt >= p.nseg[1] ? 1 : 0);
+        n0 -= p.nseg[sg] * PN;
+        Cp = p.Cs[sg]; ldc = p.ldcs[sg]; Nn = p.Ns[sg]; out_mode = p.out_modes[sg];
+        if (sg > 0) { Rp = Cp; ldr = ldc; }
+      }
       const int kb0 = ks * p.kblocks_per_split;
       const bool has_k = kb0 < p.kblocks_total;
       mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag, p.status, FAULT_WAIT_TMEM_FULL);
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * P_ACC_COLS + (uint32_t(q * 32) << 16);
       const bool row_ok = row < p.M;
-      const bool acc_bf16 = p.out_mode == GEMM_OUT_BF16_ACC && has_k;
+      const bool acc_bf16 = out_mode == GEMM_OUT_BF16_ACC && has_k;
       const int row0 = row - lane;  // first row of this warp
       // bf16 outputs of complete 32 x 256 slabs go through shared memory, so that a store (and an
       // addend load) covers 128 contiguous bytes of four rows instead of 16 bytes of 32 rows
-      const bool rope = p.out_mode == GEMM_OUT_BF16_ROPE;  // the host admits complete tiles only
-      const bool staged = has_k && (p.out_mode == GEMM_OUT_BF16 || p.out_mode == GEMM_OUT_BF16_ACC || rope) &&
-                          row0 + 32 <= p.M && n0 + PN <= p.N && (p.ldc % 8) == 0 &&
-                          (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 &&
-                          (!acc_bf16 || ((p.ldr % 8) == 0 && (reinterpret_cast<uintptr_t>(p.R) & 15) == 0));
+      const bool rope = out_mode == GEMM_OUT_BF16_ROPE;  // the host admits complete tiles only
+      const bool staged = has_k && (out_mode == GEMM_OUT_BF16 || out_mode == GEMM_OUT_BF16_ACC || rope) &&
+                          row0 + 32 <= p.M && n0 + PN <= Nn && (ldc % 8) == 0 &&
+                          (reinterpret_cast<uintptr_t>(Cp) & 15) == 0 &&
+                          (!acc_bf16 || ((ldr % 8) == 0 && (reinterpret_cast<uintptr_t>(Rp) & 15) == 0));
       if (p.dual) {
         // complete slabs only (the host checks M % 256 == 0 and N % 128 == 0).  Per 64 columns:
         // gate and up are rounded to bf16 first, H is computed from the rounded values (what the
@@ -290,16 +330,16 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       } else if (staged) {
         uint8_t* st = epi_stage + q * (32 * 128);
         const int rr = lane >> 3, seg = lane & 7;
-        __nv_bfloat16* c_base = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)(row0 + rr) * p.ldc + n0 + seg * 8;
+        __nv_bfloat16* c_base = reinterpret_cast<__nv_bfloat16*>(Cp) + (long long)(row0 + rr) * ldc + n0 + seg * 8;
         const __nv_bfloat16* r_base =
-            reinterpret_cast<const __nv_bfloat16*>(p.R) + (long long)(row0 + rr) * p.ldr + n0 + seg * 8;
+            reinterpret_cast<const __nv_bfloat16*>(Rp) + (long long)(row0 + rr) * ldr + n0 + seg * 8;
 #pragma unroll 1
         for (int c = 0; c < PN / 64; ++c) {
           // addend rows: requested before the TMEM load so that their latency runs beside it
           uint4 pre[8];  // the addend's eight rows, or the angles of four rows (the modes exclude each other)
           if (acc_bf16) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) pre[i] = *reinterpret_cast<const uint4*>(r_base + (long long)(4 * i) * p.ldr + c * 64);
+            for (int i = 0; i < 8; ++i) pre[i] = *reinterpret_cast<const uint4*>(r_base + (long long)(4 * i) * ldr + c * 64);
           }
           uint32_t r0[32], r1[32];
           tmem_ld_32x32b_x32(taddr + c * 64, r0);
@@ -367,28 +407,28 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                 }
                 o = make_uint4(w[0], w[1], w[2], w[3]);
               }
-              *reinterpret_cast<uint4*>(c_base + (long long)(4 * i) * p.ldc + c * 64) = o;
+              *reinterpret_cast<uint4*>(c_base + (long long)(4 * i) * ldc + c * 64) = o;
             }
           }
           __syncwarp();
         }
       } else {
       uint4 pre_cur[4], pre_next[4];
-      bool have_cur = acc_bf16 && gemm_prefetch_addend(p.R, p.ldr, row, n0, p.N, row_ok, pre_cur);
+      bool have_cur = acc_bf16 && gemm_prefetch_addend(Rp, ldr, row, n0, Nn, row_ok, pre_cur);
 #pragma unroll 1
       for (int c = 0; c < PN / 32; ++c) {
         const int col0 = n0 + c * 32;
         // the addend of the next chunk is requested before this chunk's TMEM load and stores
         const bool have_next = acc_bf16 && c + 1 < PN / 32 &&
-                               gemm_prefetch_addend(p.R, p.ldr, row, col0 + 32, p.N, row_ok, pre_next);
+                               gemm_prefetch_addend(Rp, ldr, row, col0 + 32, Nn, row_ok, pre_next);
         uint32_t r[32];
         tmem_ld_32x32b_x32(taddr + c * 32, r);
         tmem_ld_wait();
-        if (row_ok && col0 < p.N && has_k) {
+        if (row_ok && col0 < Nn && has_k) {
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-          gemm_store_chunk32(p.C, p.ldc, p.R, p.ldr, p.out_mode, row, col0, p.N, v, pre_cur, have_cur);
+          gemm_store_chunk32(Cp, ldc, Rp, ldr, out_mode, row, col0, Nn, v, pre_cur, have_cur);
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) pre_cur[j] = pre_next[j];
@@ -443,11 +483,14 @@ static int pair_band(int M, int N, int K, int m_tiles, int n_tiles) {
 }
 
 static int pair_launch(cudaStream_t stream, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmB2,
-                       const PairParams& p, const char** err) {
+                       const PairParams& p, const char** err, const SegMaps* seg = nullptr) {
   static bool attr_set[MAX_DEVICE_SLOTS] = {false};
+  static const SegMaps no_seg = {};
   const int slot = device_slot();
   if (!attr_set[slot]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_bf16_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM);
     if (e != cudaSuccess) { if (err) *err = cudaGetErrorString(e); return 3; }
     attr_set[slot] = true;
   }
@@ -469,7 +512,7 @@ static int pair_launch(cudaStream_t stream, const CUtensorMap& tmA, const CUtens
   static int max_clusters[MAX_DEVICE_SLOTS] = {0};
   if (!max_clusters[slot]) {
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_tc2_kernel, &cfg) != cudaSuccess || n <= 0) {
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_tc2_kernel<false>, &cfg) != cudaSuccess || n <= 0) {
       cudaGetLastError();
       n = gemm_num_sms() / 2;
     }
@@ -479,9 +522,170 @@ static int pair_launch(cudaStream_t stream, const CUtensorMap& tmA, const CUtens
   if (avail < 1) avail = 1;
   const int clusters = p.total_tiles < avail ? p.total_tiles : avail;
   cfg.gridDim = dim3(2 * clusters, 1, 1);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_tc2_kernel, tmA, tmB, tmB2, p);
+  cudaError_t e = seg ? cudaLaunchKernelEx(&cfg, gemm_bf16_tc2_kernel<true>, tmA, tmB, tmB2, *seg, p)
+                      : cudaLaunchKernelEx(&cfg, gemm_bf16_tc2_kernel<false>, tmA, tmB, tmB2, no_seg, p);
   if (e != cudaSuccess) { if (err) *err = cudaGetErrorString(e); return 3; }
   return 0;
+}
+
+static void pair_no_segments(PairParams& p) {
+  for (int i = 0; i < 3; ++i) {
+    p.kseg[i] = p.nseg[i] = i == 0 ? 0 : INT_MAX;
+    p.Cs[i] = p.C; p.ldcs[i] = p.ldc; p.Ns[i] = p.N; p.out_modes[i] = p.out_mode;
+  }
+}
+
+static void pair_set_split(PairParams& p, int split_k) {
+  if (split_k < 1) split_k = 1;
+  if (split_k > p.kblocks_total) split_k = p.kblocks_total;
+  p.kblocks_per_split = (p.kblocks_total + split_k - 1) / split_k;
+  p.split_k = (p.kblocks_total + p.kblocks_per_split - 1) / p.kblocks_per_split;
+  p.total_tiles = p.m_tiles * p.n_tiles * p.split_k;
+}
+
+static int pair_auto_split(int tiles, int kblocks) {
+  const int clusters = gemm_num_sms() / 2;
+  int max_s = kblocks / 8;  // at least 8 k-blocks (512 of k) per split
+  if (max_s < 1) max_s = 1;
+  if (max_s > 32) max_s = 32;
+  int best_s = 1;
+  double best = -1.0;
+  for (int s = 1; s <= max_s; ++s) {
+    const long long t = (long long)tiles * s;
+    const long long waves = (t + clusters - 1) / clusters;
+    const double score = (double)t / (double)(waves * clusters) - 0.015 * (s - 1);
+    if (score > best + 1e-9) { best = score; best_s = s; }
+  }
+  return best_s;
+}
+
+// C (op)= sum over up to three operand pairs of A_i B_i^T, accumulated in one pass (K segments).
+// All pairs share the majors; every K_i but the last must be a multiple of 64.
+int gemm_bf16_pair_concat_k(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int n_seg, const void* const* A,
+                            const long long* lda, const void* const* B, const long long* ldb, const int* K, void* C,
+                            long long ldc, const void* R, long long ldr, int out_mode, int split_k, float alpha,
+                            int* status, const char** err) {
+  if (M <= 0 || N <= 0) return 0;
+  if (n_seg < 1 || n_seg > 3) { if (err) *err = "gemm_bf16_concat_k: 1 to 3 segments"; return 1; }
+  CUtensorMap ma[3], mb[3];
+  int kb_start[3] = {0, INT_MAX, INT_MAX}, kblocks = 0, ktotal = 0;
+  for (int i = 0; i < n_seg; ++i) {
+    if (K[i] <= 0 || (i + 1 < n_seg && K[i] % BK)) {
+      if (err) *err = "gemm_bf16_concat_k: every K but the last must be a positive multiple of 64";
+      return 1;
+    }
+    if ((lda[i] % 8) || (ldb[i] % 8) || (reinterpret_cast<uintptr_t>(A[i]) & 15) || (reinterpret_cast<uintptr_t>(B[i]) & 15)) {
+      if (err) *err = "gemm_bf16_concat_k: operand rows must be 16-byte aligned (leading dimension % 8 == 0)";
+      return 1;
+    }
+    int rc = a_mn ? make_tmap_bf16_2d(&ma[i], A[i], M, K[i], lda[i], 64, BK) : make_tmap_bf16_2d(&ma[i], A[i], K[i], M, lda[i], 64, PM);
+    if (!rc) rc = b_mn ? make_tmap_bf16_2d(&mb[i], B[i], N, K[i], ldb[i], 64, BK) : make_tmap_bf16_2d(&mb[i], B[i], K[i], N, ldb[i], 64, PN / 2);
+    if (rc) { if (err) *err = "gemm_bf16_concat_k: cuTensorMapEncodeTiled failed"; return 2; }
+    kb_start[i] = kblocks;
+    kblocks += (K[i] + BK - 1) / BK;
+    ktotal += K[i];
+  }
+  if (split_k > 1 && out_mode != GEMM_OUT_F32_ATOMIC) {
+    if (err) *err = "gemm_bf16_concat_k: split_k > 1 needs the f32 atomic output mode";
+    return 1;
+  }
+  PairParams p;
+  p.M = M; p.N = N; p.K = ktotal;
+  p.a_mn = a_mn; p.b_mn = b_mn;
+  p.C = C; p.ldc = ldc; p.out_mode = out_mode;
+  p.R = R ? R : C; p.ldr = R ? ldr : ldc;
+  p.m_tiles = (M + 2 * PM - 1) / (2 * PM);
+  p.n_tiles = (N + PN - 1) / PN;
+  p.kblocks_total = kblocks;
+  pair_set_split(p, split_k);
+  p.band = pair_band(M, N, ktotal, p.m_tiles, p.n_tiles);
+  p.alpha = alpha;
+  p.status = status;
+  p.dual = 0; p.C2 = nullptr; p.H = nullptr;
+  p.rope_tab = nullptr; p.rope_s = 1; p.rope_hd = 2;
+  pair_no_segments(p);
+  for (int i = 1; i < n_seg; ++i) p.kseg[i] = kb_start[i];
+  SegMaps sm;
+  sm.a[0] = ma[n_seg > 1 ? 1 : 0];
+  sm.a[1] = ma[n_seg > 2 ? 2 : 0];
+  sm.b = mb[n_seg > 2 ? 2 : 0];
+  return pair_launch(stream, ma[0], mb[0], mb[n_seg > 1 ? 1 : 0], p, err, &sm);
+}
+
+// Up to three products that share A in one launch (N segments): C_i (op)= A B_i^T, each with its own
+// output matrix and output mode.  Every N_i but the last must be a multiple of 256.  The RoPE output
+// mode (complete tiles only: M % 256 == 0, N_i % 256 == 0) uses one table for all segments that ask for it.
+int gemm_bf16_pair_multi_n(cudaStream_t stream, int a_mn, int b_mn, int M, int K, const void* A, long long lda, int n_seg,
+                           const void* const* B, const long long* ldb, const int* N, void* const* C, const long long* ldc,
+                           const int* out_mode, int split_k, float alpha, const float* rope_table, int seq_len,
+                           int head_dim, int* status, const char** err) {
+  if (M <= 0 || K <= 0) return 0;
+  if (n_seg < 1 || n_seg > 3) { if (err) *err = "gemm_bf16_multi_n: 1 to 3 segments"; return 1; }
+  if ((lda % 8) || (reinterpret_cast<uintptr_t>(A) & 15)) {
+    if (err) *err = "gemm_bf16_multi_n: operand rows must be 16-byte aligned (leading dimension % 8 == 0)";
+    return 1;
+  }
+  CUtensorMap ma, mb[3];
+  if (a_mn ? make_tmap_bf16_2d(&ma, A, M, K, lda, 64, BK) : make_tmap_bf16_2d(&ma, A, K, M, lda, 64, PM)) {
+    if (err) *err = "gemm_bf16_multi_n: cuTensorMapEncodeTiled failed for A";
+    return 2;
+  }
+  PairParams p;
+  int nt_start[3] = {0, INT_MAX, INT_MAX}, n_tiles = 0, n_total = 0;
+  bool all_atomic = true;
+  for (int i = 0; i < n_seg; ++i) {
+    if (N[i] <= 0 || (i + 1 < n_seg && N[i] % PN)) {
+      if (err) *err = "gemm_bf16_multi_n: every N but the last must be a positive multiple of 256";
+      return 1;
+    }
+    if ((ldb[i] % 8) || (reinterpret_cast<uintptr_t>(B[i]) & 15) || !C[i]) {
+      if (err) *err = "gemm_bf16_multi_n: operand rows must be 16-byte aligned, outputs must not be null";
+      return 1;
+    }
+    if (out_mode[i] == GEMM_OUT_BF16_ROPE &&
+        ((M % (2 * PM)) || (N[i] % PN) || head_dim < 8 || (head_dim % 8) || (N[i] % head_dim) || seq_len <= 0 || !rope_table ||
+         (reinterpret_cast<uintptr_t>(rope_table) & 15) || (ldc[i] % 8) || (reinterpret_cast<uintptr_t>(C[i]) & 15))) {
+      if (err) *err = "gemm_bf16_multi_n: the RoPE output mode needs complete 256 x 256 tiles, a table and 16-byte aligned rows";
+      return 1;
+    }
+    if (b_mn ? make_tmap_bf16_2d(&mb[i], B[i], N[i], K, ldb[i], 64, BK) : make_tmap_bf16_2d(&mb[i], B[i], K, N[i], ldb[i], 64, PN / 2)) {
+      if (err) *err = "gemm_bf16_multi_n: cuTensorMapEncodeTiled failed for B";
+      return 2;
+    }
+    all_atomic = all_atomic && out_mode[i] == GEMM_OUT_F32_ATOMIC;
+    nt_start[i] = n_tiles;
+    n_tiles += (N[i] + PN - 1) / PN;
+    n_total += N[i];
+  }
+  p.M = M; p.N = n_total; p.K = K;
+  p.a_mn = a_mn; p.b_mn = b_mn;
+  p.C = C[0]; p.ldc = ldc[0]; p.out_mode = out_mode[0];
+  p.R = C[0]; p.ldr = ldc[0];
+  p.m_tiles = (M + 2 * PM - 1) / (2 * PM);
+  p.n_tiles = n_tiles;
+  p.kblocks_total = (K + BK - 1) / BK;
+  if (split_k == 0) split_k = all_atomic ? pair_auto_split(p.m_tiles * n_tiles, p.kblocks_total) : 1;
+  if (split_k > 1 && !all_atomic) {
+    if (err) *err = "gemm_bf16_multi_n: split_k > 1 needs the f32 atomic output mode in every segment";
+    return 1;
+  }
+  pair_set_split(p, split_k);
+  p.band = pair_band(M, n_total, K, p.m_tiles, p.n_tiles);
+  p.alpha = alpha;
+  p.status = status;
+  p.dual = 0; p.C2 = nullptr; p.H = nullptr;
+  p.rope_tab = reinterpret_cast<const float2*>(rope_table);
+  p.rope_s = seq_len > 0 ? seq_len : 1;
+  p.rope_hd = head_dim >= 2 ? head_dim : 2;
+  pair_no_segments(p);
+  for (int i = 0; i < n_seg; ++i) {
+    p.nseg[i] = nt_start[i];
+    p.Cs[i] = C[i]; p.ldcs[i] = ldc[i]; p.Ns[i] = N[i]; p.out_modes[i] = out_mode[i];
+  }
+  SegMaps sm;
+  sm.a[0] = ma; sm.a[1] = ma;
+  sm.b = mb[n_seg > 2 ? 2 : 0];
+  return pair_launch(stream, ma, mb[0], mb[n_seg > 1 ? 1 : 0], p, err, &sm);
 }
 
 int gemm_bf16_tc_pair(cudaStream_t stream, int a_mn, int b_mn, int M, int N, int K, const void* A, long long lda,
@@ -615,20 +819,7 @@ int gemm_pair_clusters_hint() { return gemm_num_sms() / 2; }
 // more pass of f32 atomics over C, charged as 1.5 % each.
 int gemm_pair_auto_split_k(int M, int N, int K) {
   const int tiles = ((M + 2 * PM - 1) / (2 * PM)) * ((N + PN - 1) / PN);
-  const int kblocks = (K + BK - 1) / BK;
-  const int clusters = gemm_num_sms() / 2;
-  int max_s = kblocks / 8;  // at least 8 k-blocks (512 of k) per split
-  if (max_s < 1) max_s = 1;
-  if (max_s > 32) max_s = 32;
-  int best_s = 1;
-  double best = -1.0;
-  for (int s = 1; s <= max_s; ++s) {
-    const long long t = (long long)tiles * s;
-    const long long waves = (t + clusters - 1) / clusters;
-    const double score = (double)t / (double)(waves * clusters) - 0.015 * (s - 1);
-    if (score > best + 1e-9) { best = score; best_s = s; }
-  }
-  return best_s;
+  return pair_auto_split(tiles, (K + BK - 1) / BK);
 }
 
 }  // namespace eisen

@@ -872,6 +872,116 @@ int64_t Graph::matmul_rope(int64_t a, int64_t b, int64_t head_dim) {
   return o;
 }
 
+// The three projections of GroupedQueryAttention::forward_with_mask (src/nn/attention.rs:316-333:
+// q_proj, k_proj, v_proj on one input, RoPE on q and k) as one tape entry.  Forward: one launch
+// whose n-tiles are spread over the three weights (RoPE in the epilogue of the q and k tiles).
+// Backward: dX = dQ' Wq^T + dK' Wk^T + dV Wv^T in one pass over the three operand pairs (dQ', dK' =
+// the gradients rotated back), and the three dW = X^T dY in one launch.  Shapes the fused kernels do
+// not take, Fp32 graphs and host-homed weights run matmul_rope, matmul_rope, matmul.
+void Graph::qkv_proj_rope(int64_t x, int64_t wq, int64_t wk, int64_t wv, int64_t head_dim, int64_t out3[3]) {
+  const HTensor& tx = tensors.at(x);
+  const int64_t ws[3] = {wq, wk, wv};
+  bool fusable = precision == Precision::Bf16Mixed && tx.shape.size() == 3 && head_dim % 8 == 0 && head_dim >= 8;
+  int64_t B = 0, S = 0, k = 0, m = 0;
+  long long ns[3] = {0, 0, 0};
+  if (fusable) {
+    B = tx.shape[0]; S = tx.shape[1]; k = tx.shape[2]; m = B * S;
+    fusable = m % 256 == 0 && k % 8 == 0;
+    for (int i = 0; i < 3 && fusable; ++i) {
+      const HTensor& tw = tensors.at(ws[i]);
+      fusable = tw.shape.size() == 2 && tw.shape[0] == k && tw.shape[1] % 256 == 0 && tw.shape[1] % head_dim == 0 &&
+                !tw.host_homed && !tw.constant && tw.grad_dtype == 0;
+      ns[i] = fusable ? tw.shape[1] : 0;
+    }
+    fusable = fusable && !tx.constant;
+  }
+  if (!fusable) {
+    out3[0] = matmul_rope(x, wq, head_dim);
+    out3[1] = matmul_rope(x, wk, head_dim);
+    out3[2] = matmul(x, wv);
+    if (tensors.at(x).shape.size() == 3)
+      reinterpret_shape(out3[2], {tensors[x].shape[0], tensors[x].shape[1], tensors.at(wv).shape[1]});
+    return;
+  }
+  const float* tab = rope_table(S, head_dim);
+  const int dt = act_dtype();
+  for (int i = 0; i < 3; ++i) out3[i] = alloc_pooled({B, S, ns[i]});
+  const int64_t oq = out3[0], ok = out3[1], ov = out3[2];
+  if (!skip_forward) {
+    const void* bs[3] = {weight_operand(wq), weight_operand(wk), weight_operand(wv)};
+    void* cs[3] = {tensors[oq].data, tensors[ok].data, tensors[ov].data};
+    const int modes[3] = {5, 5, 0};
+    prof_begin(0, 2.0 * (double)m * (double)(ns[0] + ns[1] + ns[2]) * (double)k);
+    ck(eisen_gemm_bf16_multi_n(stream, 0, 1, m, k, operand(tensors[x]), k, 3, bs, ns, ns, cs, ns, modes, 1, 1.0f, tab, S,
+                               head_dim, status_dev),
+       "qkv_proj_rope");
+    prof_end();
+  }
+  if (no_grad) return;
+  const long long n0 = ns[0], n1 = ns[1], n2 = ns[2];
+  tape.push_back({{x, wq, wk, wv}, ov, [this, x, wq, wk, wv, oq, ok, ov, B, S, m, k, n0, n1, n2, head_dim, dt, tab]() {
+    const int64_t outs[3] = {oq, ok, ov}, ws[3] = {wq, wk, wv};
+    const long long ns[3] = {n0, n1, n2};
+    bool have[3];
+    int n_have = 0;
+    for (int i = 0; i < 3; ++i) {
+      const HTensor& to = tensors[outs[i]];
+      have[i] = to.grad && to.grad_init;
+      n_have += have[i];
+    }
+    if (!n_have) return;
+    // the gradients of q and k are rotated back into pooled temporaries (the outputs' own gradients
+    // stay as their consumer wrote them, so the tape can be walked again)
+    struct Temp { Graph& g; void* p; size_t b; ~Temp() { if (p) g.pool_put(p, b); } };
+    Temp rq{*this, nullptr, 0}, rk{*this, nullptr, 0};
+    const void* dy[3] = {nullptr, nullptr, nullptr};
+    for (int i = 0; i < 2; ++i) {
+      if (!have[i]) continue;
+      Temp& t = i == 0 ? rq : rk;
+      t.b = (size_t)m * ns[i] * dsize(dt);
+      t.p = pool_get(t.b);
+      ck(eisen_rope(stream, tensors[outs[i]].grad, t.p, tab, B, S, ns[i], head_dim, dt, 1, 0), "qkv_proj_rope.bwd(rope)");
+      dy[i] = t.p;
+    }
+    if (have[2]) dy[2] = tensors[ov].grad;
+    HTensor& gx = tensors[x];
+    ensure_grad(x);
+    for (int i = 0; i < 3; ++i) ensure_grad(ws[i]);
+    if (n_have == 3 && gx.grad_dtype == 1) {
+      // dX (op)= sum_i dY_i W_i^T, one pass over the three operand pairs
+      const void* as[3] = {dy[0], dy[1], dy[2]};
+      const void* bs[3] = {weight_operand(wq), weight_operand(wk), weight_operand(wv)};
+      prof_begin(0, 2.0 * (double)m * (double)(n0 + n1 + n2) * (double)k);
+      ck(eisen_gemm_bf16_concat_k(stream, 0, 0, m, k, 3, as, ns, bs, ns, ns, gx.grad, k, gx.grad_init ? 1 : 0, 1, 1.0f,
+                                  status_dev),
+         "qkv_proj_rope.bwd(dX)");
+      prof_end();
+      gx.grad_init = true;
+      // dW_i (+)= X^T dY_i, one launch over the n-tiles of the three gradients
+      bool fresh = false;
+      for (int i = 0; i < 3; ++i) fresh = fresh || !tensors[ws[i]].grad_init;
+      if (!fresh) {
+        void* cs[3] = {tensors[wq].grad, tensors[wk].grad, tensors[wv].grad};
+        const int modes[3] = {4, 4, 4};
+        prof_begin(0, 2.0 * (double)m * (double)(n0 + n1 + n2) * (double)k);
+        ck(eisen_gemm_bf16_multi_n(stream, 1, 1, k, m, operand(gx), k, 3, dy, ns, ns, cs, ns, modes, 0, 1.0f, nullptr, 0, 0,
+                                   status_dev),
+           "qkv_proj_rope.bwd(dW)");
+        prof_end();
+        return;
+      }
+      for (int i = 0; i < 3; ++i) dw_gemm(*this, true, true, k, ns[i], m, operand(gx), dy[i], ws[i]);
+      return;
+    }
+    for (int i = 2; i >= 0; --i) {  // the order in which the separate tape entries would run
+      if (!have[i]) continue;
+      gemm(*this, false, false, m, k, ns[i], dy[i], weight_operand(ws[i]), gx.grad, gx.grad_dtype, gx.grad_init);
+      gx.grad_init = true;
+      dw_gemm(*this, true, true, k, ns[i], m, operand(gx), dy[i], ws[i]);
+    }
+  }});
+}
+
 // silu(x Wg) * (x Wu): the gate and up `Linear`s and the SiLU-gated product of
 // src/nn/transformer.rs:41-44 in one launch.  The tape gets the same three entries as
 // matmul, matmul, swiglu (their forward kernels are skipped), so the backward pass is theirs.

@@ -102,6 +102,8 @@ class Graph {
   int64_t swiglu(int64_t gate, int64_t up);
   int64_t gate_up_swiglu(int64_t x, int64_t wg, int64_t wu);
   int64_t matmul_rope(int64_t a, int64_t b, int64_t head_dim);
+  // q = rope(x Wq), k = rope(x Wk), v = x Wv as one tape entry (out3 = {q, k, v})
+  void qkv_proj_rope(int64_t x, int64_t wq, int64_t wk, int64_t wv, int64_t head_dim, int64_t out3[3]);
   int64_t matmul(int64_t a, int64_t b);
   int64_t matmul_trans_b(int64_t a, int64_t b);
   // r + a b in one launch (Bf16Mixed): the residual add done in the projection's epilogue

@@ -135,16 +135,17 @@ int64_t TransformerLM::gqa_forward(Graph& g, const BlockParams& b, int64_t x, bo
   const std::vector<int64_t> xs = g.tensors.at(x).shape;
   if (xs.size() != 3) throw EisenException(EISEN_ERR_INVALID, "GQA requires [Batch, Seq, Dim]");
   const int64_t B = xs[0], S = xs[1], hd = hidden / heads;
-  int64_t qr, kr;
-  if (fused) {  // projection + RoPE in one launch each
-    qr = g.matmul_rope(x, b.q, hd);
-    kr = g.matmul_rope(x, b.k, hd);
+  int64_t qr, kr, v;
+  if (fused) {  // the three projections, RoPE on q and k, as one tape entry
+    int64_t out3[3];
+    g.qkv_proj_rope(x, b.q, b.k, b.v, hd, out3);
+    qr = out3[0]; kr = out3[1]; v = out3[2];
   } else {
     int64_t q = linear_fwd(g, x, b.q), k = linear_fwd(g, x, b.k);
     qr = g.rope(q, hd);
     kr = g.rope(k, hd);
+    v = linear_fwd(g, x, b.v);
   }
-  int64_t v = linear_fwd(g, x, b.v);
   if (kv_out) *kv_out = {kr, v};
   int64_t ctx2;
   if (fused) {

@@ -89,6 +89,28 @@ int eisen_gemm_bf16_residual(void* stream, int a_mn, int b_mn, long long M, long
 int eisen_gemm_bf16_rope(void* stream, long long M, long long N, long long K, const void* A, long long lda, const void* B,
                          long long ldb, void* C, long long ldc, const float* table_cos_sin, long long seq_len,
                          long long head_dim, int* status);
+/* Backward of the three projections of GroupedQueryAttention::forward_with_mask
+ * (src/nn/attention.rs:316-318: q_proj, k_proj, v_proj on the same input) as two launches instead
+ * of six.  The reference runs matmul's backward closure three times (src/graph/ops/linear.rs:
+ * 615-730), each adding its `dC W^T` into the input's gradient and writing its own dW.
+ *
+ * eisen_gemm_bf16_concat_k: C[M,N] (op)= alpha * sum_i sum_k A_i(m,k) B_i(n,k) over n_seg <= 3 operand
+ * pairs with their own K_i (every K_i but the last a multiple of 64): the three `dC W^T` products
+ * summed in the f32 accumulator in one pass, no bf16 rounding or read-modify-write in between.
+ * Operand conventions, out_mode and split_k as in eisen_gemm_bf16; all pairs share a_mn / b_mn.
+ *
+ * eisen_gemm_bf16_multi_n: C_i[M,N_i] (op)= alpha * sum_k A(m,k) B_i(n,k) for n_seg <= 3 B operands that
+ * share A, each with its own output matrix, leading dimension and out_mode (0, 2, 4 or 5; every N_i but
+ * the last a multiple of 256): the three `A^T dC` weight gradients in one launch (out_mode 4, split_k 0
+ * = chosen for the whole tile set), or the three forward projections with RoPE on some of them
+ * (out_mode 5 uses table_cos_sin / seq_len / head_dim as eisen_gemm_bf16_rope does). */
+int eisen_gemm_bf16_concat_k(void* stream, int a_mn, int b_mn, long long M, long long N, int n_seg, const void* const* A,
+                             const long long* lda, const void* const* B, const long long* ldb, const long long* K,
+                             void* C, long long ldc, int out_mode, int split_k, float alpha, int* status);
+int eisen_gemm_bf16_multi_n(void* stream, int a_mn, int b_mn, long long M, long long K, const void* A, long long lda,
+                            int n_seg, const void* const* B, const long long* ldb, const long long* N, void* const* C,
+                            const long long* ldc, const int* out_mode, int split_k, float alpha,
+                            const float* table_cos_sin, long long seq_len, long long head_dim, int* status);
 /* Gate and up projections of the SiLU-gated MLP with the product in the GEMM epilogue
  * (src/nn/transformer.rs:41-44: Linear, Linear, silu, mul):
  *   G = bf16(A Bg), U = bf16(A Bu), H = bf16(silu(G) * U)

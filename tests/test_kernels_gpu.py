@@ -189,6 +189,104 @@ def test_gemm_bf16_rope_epilogue(B, S, N, K, hd):
     assert torch.equal(out.view(torch.int16), ref.view(torch.int16))
 
 
+def _ptr_array(ts):
+    import ctypes
+    return (ctypes.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+
+
+def _ll_array(vs):
+    import ctypes
+    return (ctypes.c_longlong * len(vs))(*vs)
+
+
+@pytest.mark.parametrize("M,N,Ks", [(512, 256, [128, 64, 64]), (1024, 2048, [2048, 512, 512]), (300, 200, [64, 192]),
+                                    (256, 384, [320])])
+@pytest.mark.parametrize("out_mode", [0, 1, 4])
+def test_gemm_bf16_concat_k(M, N, Ks, out_mode):
+    """sum_i A_i B_i^T over up to three operand pairs in one launch == the sum of the separate products
+    (the shape of dX = dQ Wq^T + dK Wk^T + dV Wv^T: A_i K-major activations, B_i [N, K_i] weights)."""
+    g = torch.Generator(device="cpu").manual_seed(M + N + sum(Ks) + out_mode)
+    As = [torch.randn(M, k, generator=g).to(torch.bfloat16).to(dev()) for k in Ks]
+    Bs = [(torch.randn(N, k, generator=g) * 0.1).to(torch.bfloat16).to(dev()) for k in Ks]
+    ref = sum(a.float() @ b.float().t() for a, b in zip(As, Bs))
+    init = torch.randn(M, N, generator=g).to(dev())
+    if out_mode == 4:
+        C = init.clone()
+        ref = ref + init
+    elif out_mode == 1:
+        C = init.to(torch.bfloat16)
+        ref = ref + C.float()
+    else:
+        C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+    st = status_word()
+    eb.call("eisen_gemm_bf16_concat_k", stream(), 0, 0, M, N, len(Ks), _ptr_array(As), _ll_array(Ks), _ptr_array(Bs),
+            _ll_array(Ks), _ll_array(Ks), P(C), N, out_mode, 0 if out_mode == 4 else 1, 1.0, P(st))
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert torch.isfinite(C.float()).all()
+    assert rel_l2(C.float().cpu().numpy(), ref.cpu().numpy()) < (1e-5 if out_mode == 4 else 5e-3)
+
+
+def test_gemm_bf16_concat_k_rejects_bad_segments():
+    t = torch.zeros(256, 256, dtype=torch.bfloat16, device=dev())
+    ptrs = _ptr_array([t, t])
+    # the first K is not a multiple of 64
+    rc = eb.lib().eisen_gemm_bf16_concat_k(stream(), 0, 0, 256, 256, 2, ptrs, _ll_array([256, 256]), ptrs,
+                                           _ll_array([256, 256]), _ll_array([72, 64]), P(t), 256, 0, 1, 1.0, None)
+    assert rc == 1
+    rc = eb.lib().eisen_gemm_bf16_concat_k(stream(), 0, 0, 256, 256, 4, ptrs, _ll_array([256, 256]), ptrs,
+                                           _ll_array([256, 256]), _ll_array([64, 64]), P(t), 256, 0, 1, 1.0, None)
+    assert rc == 1
+
+
+@pytest.mark.parametrize("M,K,Ns,split_k", [(256, 512, [512, 256, 256], 0), (2048, 4096, [2048, 512, 512], 0),
+                                            (384, 1024, [256, 200], 3), (512, 2048, [256], 1)])
+def test_gemm_bf16_multi_n_weight_gradients(M, K, Ns, split_k):
+    """dW_i += X^T dY_i for up to three dY_i that share X, in one launch with split-K (f32 red.add):
+    A = X stored [K, M] (tokens x in-features), B_i = dY_i stored [K, N_i]."""
+    g = torch.Generator(device="cpu").manual_seed(M + K + sum(Ns))
+    X = torch.randn(K, M, generator=g).to(torch.bfloat16).to(dev())
+    dYs = [torch.randn(K, n, generator=g).to(torch.bfloat16).to(dev()) for n in Ns]
+    inits = [torch.randn(M, n, generator=g).to(dev()) for n in Ns]
+    Cs = [t.clone() for t in inits]
+    st = status_word()
+    import ctypes
+    modes = (ctypes.c_int * len(Ns))(*([4] * len(Ns)))
+    eb.call("eisen_gemm_bf16_multi_n", stream(), 1, 1, M, K, P(X), M, len(Ns), _ptr_array(dYs), _ll_array(Ns), _ll_array(Ns),
+            _ptr_array(Cs), _ll_array(Ns), modes, split_k, 1.0, None, 0, 0, P(st))
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    for C, dY, init in zip(Cs, dYs, inits):
+        ref = X.float().t() @ dY.float() + init
+        assert rel_l2(C.cpu().numpy(), ref.cpu().numpy()) < 1e-5
+
+
+def test_gemm_bf16_multi_n_projections_with_rope():
+    """q, k and v projections of one input in one launch, RoPE on q and k: bit-identical to the three launches."""
+    B, S, K, hd = 2, 256, 320, 64
+    Ns = [512, 256, 256]
+    M = B * S
+    g = torch.Generator(device="cpu").manual_seed(11)
+    A = torch.randn(M, K, generator=g).to(torch.bfloat16).to(dev())
+    Ws = [(torch.randn(K, n, generator=g) * 0.2).to(torch.bfloat16).to(dev()) for n in Ns]
+    tab = torch.empty(S, hd // 2, 2, device=dev())
+    eb.call("eisen_rope_table", stream(), P(tab), S, hd, 10000.0)
+    st = status_word()
+    refs = [torch.empty(M, n, dtype=torch.bfloat16, device=dev()) for n in Ns]
+    eb.call("eisen_gemm_bf16_rope", stream(), M, Ns[0], K, P(A), K, P(Ws[0]), Ns[0], P(refs[0]), Ns[0], P(tab), S, hd, P(st))
+    eb.call("eisen_gemm_bf16_rope", stream(), M, Ns[1], K, P(A), K, P(Ws[1]), Ns[1], P(refs[1]), Ns[1], P(tab), S, hd, P(st))
+    eb.call("eisen_gemm_bf16", stream(), 0, 1, M, Ns[2], K, P(A), K, P(Ws[2]), Ns[2], P(refs[2]), Ns[2], 0, 1, 1.0, P(st))
+    outs = [torch.full((M, n), float("nan"), dtype=torch.bfloat16, device=dev()) for n in Ns]
+    import ctypes
+    modes = (ctypes.c_int * 3)(5, 5, 0)
+    eb.call("eisen_gemm_bf16_multi_n", stream(), 0, 1, M, K, P(A), K, 3, _ptr_array(Ws), _ll_array(Ns), _ll_array(Ns),
+            _ptr_array(outs), _ll_array(Ns), modes, 1, 1.0, P(tab), S, hd, P(st))
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    for o, r in zip(outs, refs):
+        assert torch.equal(o.view(torch.int16), r.view(torch.int16))
+
+
 def test_gemm_bf16_swiglu_rejects_ragged_shapes():
     t = torch.zeros(256, 128, dtype=torch.bfloat16, device=dev())
     rc = eb.lib().eisen_gemm_bf16_swiglu(stream(), 200, 128, 64, P(t), 64, P(t), P(t), 128, None, None, P(t), 128, None)
