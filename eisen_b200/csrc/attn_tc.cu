@@ -6,10 +6,12 @@
 // swizzle and are consumed by tcgen05.mma either K-major or MN-major, so one resident tile serves
 // both A*B^T and A^T*B style products; accumulators live in TMEM.
 //
-// Forward: two 128-query tiles of one head per CTA share the K / V tiles; softmax warps read
-// S = Q K^T from TMEM and write P (bf16) to shared memory.  At D = 64 (attn_fwd64_kernel) O stays in
-// TMEM and is rescaled lazily; at D = 128 (attn_fwd_kernel) each P V product is a fresh TMEM
-// accumulator folded into f32 registers with the online-softmax rescale.
+// Forward: softmax warps read S = Q K^T from TMEM and hand P (bf16) to the P V product.  At D = 64
+// (attn_fwd64_kernel) a CTA owns one 128-query tile (two CTAs per SM), P goes back to TMEM and is
+// read from there as the product's A operand, O stays in TMEM and is rescaled lazily; variants with
+// P staged in shared memory and with two query tiles per CTA stay selectable.  At D = 128
+// (attn_fwd_kernel) two query tiles per CTA share the K / V tiles, P goes through shared memory and
+// each P V product is a fresh TMEM accumulator folded into f32 registers with the online-softmax rescale.
 // Backward: one 128-key tile of one KV head per CTA, looping over the query heads of its group and
 // over query tiles; dV and dK stay in TMEM for the whole loop (the GQA reduce), dQ tiles are added
 // to an f32 workspace.  Details sit above each kernel.
@@ -29,8 +31,9 @@ namespace {
 
 constexpr float LOG2E = 1.4426950408889634f;
 
-// query tiles per CTA of the head_dim-64 forward: 1 (two CTAs per SM) or 2 (one CTA per SM)
-std::atomic<int> g_attn_fwd_tiles{1};
+// variant of the head_dim-64 forward: 3 = one query tile per CTA with P through TMEM, 1 = the same
+// with P through shared memory, 2 = two query tiles per CTA (one CTA per SM)
+std::atomic<int> g_attn_fwd_tiles{3};
 
 struct AttnParams {
   int B, S, Hq, Hkv, D;
@@ -439,11 +442,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 // exponentials (one CTA per SM).  NT = 1: half the shared memory, tensor memory and threads, so
 // that two CTAs are resident per SM and the hardware interleaves their phases; K and V are then
 // fetched once per query tile (from L2), and V has a single stage.
-template <int NT>
+template <int NT, bool PTM = false>
 struct Fwd64Cfg {
+  static_assert(!PTM || NT == 1, "P through TMEM is built for one query tile per CTA");
   static constexpr int TILE = 128 * 64 * 2;
-  static constexpr int P_TILE = 128 * 128 * 2;
-  static constexpr int NSV = NT == 2 ? 2 : 1;     // V stages
+  static constexpr int P_TILE = PTM ? 0 : 128 * 128 * 2;  // PTM: P goes to TMEM, no shared-memory tile
+  static constexpr int NSV = (NT == 2 || PTM) ? 2 : 1;  // V stages
   static constexpr int OFF_Q = 0;                 // NT tiles
   static constexpr int OFF_K = NT * TILE;         // 2 stages
   static constexpr int OFF_V = OFF_K + 2 * TILE;  // NSV stages
@@ -457,11 +461,11 @@ struct Fwd64Cfg {
   static constexpr int CTAS_PER_SM = NT == 2 ? 1 : 2;
 };
 
-template <int NT>
-__global__ void __launch_bounds__(Fwd64Cfg<NT>::THREADS, Fwd64Cfg<NT>::CTAS_PER_SM)
+template <int NT, bool PTM = false>
+__global__ void __launch_bounds__(Fwd64Cfg<NT, PTM>::THREADS, Fwd64Cfg<NT, PTM>::CTAS_PER_SM)
 attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
-  using Cfg = Fwd64Cfg<NT>;
+  using Cfg = Fwd64Cfg<NT, PTM>;
   constexpr int NSV = Cfg::NSV;
   constexpr int D = 64;
   extern __shared__ uint8_t smem_raw[];
@@ -516,6 +520,7 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tm_S = tmem_base;        // S of tile A at +0, of tile B at +128
   const uint32_t tm_O = tmem_base + NT * 128;  // O of tile A at +0, of tile B at +64
+  const uint32_t tm_P = tmem_base + 192;       // PTM: P as bf16 pairs, 64 columns (A operand of P V)
 
   if (warp == Cfg::SWARPS) {
     // ---------------- TMA ----------------
@@ -555,9 +560,14 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const uint32_t sV = smem_u32(smem + Cfg::OFF_V + (j % NSV) * Cfg::TILE);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {  // 128 keys in steps of 16
-          const uint64_t da = make_smem_desc(sP + (k >> 2) * 16384u + (k & 3) * 32u, 16, 1024);
           const uint64_t db = make_smem_desc(sV + k * 2048u, 16384, 1024);  // V is MN-major: [key][d]
-          umma_bf16_ss(tm_O + t * D, da, db, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+          if (PTM) {
+            // A from TMEM: lane = query row, 16 keys of a step = 8 columns of bf16 pairs
+            umma_bf16_ts(tm_O + t * D, tm_P + k * 8u, db, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+          } else {
+            const uint64_t da = make_smem_desc(sP + (k >> 2) * 16384u + (k & 3) * 32u, 16, 1024);
+            umma_bf16_ss(tm_O + t * D, da, db, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+          }
         }
         umma_commit(&o_full[t]);
       };
@@ -615,6 +625,7 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const uint32_t tS = tm_S + t * 128 + part * 64 + lane_off;
     const uint32_t tO = tm_O + t * D + part * 32 + lane_off;
     const uint32_t sP = smem_u32(smem + Cfg::OFF_P + t * Cfg::P_TILE);
+    const uint32_t tP = tm_P + part * 32 + lane_off;  // PTM: this thread's 64 probabilities = 32 columns of its lane
     float* xbase = reinterpret_cast<float*>(smem + Cfg::OFF_XMAX) + t * 512;  // [2 buffers][2 parts][128]
     const int bar_id = 1 + t;
     float m_used = -INFINITY, l = 0.0f;
@@ -715,7 +726,8 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           pk[u >> 1] = pack_bf16x2(x0, x1);
           pk[(u >> 1) + 1] = pack_bf16x2(x2, x3);
         }
-        st_shared_v4(p_half + swz128(row, i >> 3), pk[0], pk[1], pk[2], pk[3]);
+        if (PTM) tmem_st_32x32b_x4(tP + (i >> 1), pk);
+        else st_shared_v4(p_half + swz128(row, i >> 3), pk[0], pk[1], pk[2], pk[3]);
       }
 #pragma unroll
       for (int i = 0; i < 32; i += 8) {
@@ -731,15 +743,21 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           pk[u >> 1] = pack_bf16x2(x0, x1);
           pk[(u >> 1) + 1] = pack_bf16x2(x2, x3);
         }
-        st_shared_v4(p_half + swz128(row, 4 + (i >> 3)), pk[0], pk[1], pk[2], pk[3]);
+        if (PTM) tmem_st_32x32b_x4(tP + 16 + (i >> 1), pk);
+        else st_shared_v4(p_half + swz128(row, 4 + (i >> 3)), pk[0], pk[1], pk[2], pk[3]);
         // the turn is handed over with 24 of the 64 exponentials still to go: the other tile needs
         // a few hundred clocks from the barrier to its first exponential (measured: better than
         // handing over at the end, at 16 or at 32 to go)
         if (NT == 2 && i == 0) mbar_arrive_warp(&exp_done[t]);
       }
       l = fmaf(l, alpha, (rs0 + rs1) + (rs2 + rs3));
-      tc_fence_before_sync();
-      fence_proxy_async_smem();
+      if (PTM) {
+        tmem_st_wait();
+        tc_fence_before_sync();
+      } else {
+        tc_fence_before_sync();
+        fence_proxy_async_smem();
+      }
       mbar_arrive_warp(&p_ready[t]);
     }
     if (n_mine > 0) {
@@ -1296,7 +1314,8 @@ using namespace eisen;
 extern "C" {
 
 int eisen_attn_set_fwd_tiles(int tiles) {
-  if (tiles != 1 && tiles != 2) return fail(EISEN_ERR_INVALID, "attn_set_fwd_tiles: 1 or 2 query tiles per CTA");
+  if (tiles < 1 || tiles > 3)
+    return fail(EISEN_ERR_INVALID, "attn_set_fwd_tiles: 1 or 2 query tiles per CTA, or 3 = one tile with P through TMEM");
   g_attn_fwd_tiles.store(tiles);
   return 0;
 }
@@ -1325,8 +1344,18 @@ int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, vo
     // one query tile per CTA and two CTAs per SM, or two query tiles per CTA (see Fwd64Cfg)
     static bool set64[2][MAX_DEVICE_SLOTS] = {{false}};
     const int slot = device_slot();
-    const int nt = g_attn_fwd_tiles.load() == 2 ? 2 : 1;
-    if (nt == 2) {
+    const int nt = g_attn_fwd_tiles.load();
+    if (nt == 3) {
+      static bool set3[MAX_DEVICE_SLOTS] = {false};
+      if (!set3[slot]) {
+        if (cudaFuncSetAttribute(attn_fwd64_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Fwd64Cfg<1, true>::SMEM) != cudaSuccess)
+          return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute");
+        set3[slot] = true;
+      }
+      dim3 grid1((unsigned)Hq, (unsigned)B, (unsigned)((S + 127) / 128));
+      attn_fwd64_kernel<1, true><<<grid1, Fwd64Cfg<1, true>::THREADS, Fwd64Cfg<1, true>::SMEM, s>>>(tq, tk, tv, p);
+    } else if (nt == 2) {
       if (!set64[1][slot]) {
         if (cudaFuncSetAttribute(attn_fwd64_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd64Cfg<2>::SMEM) != cudaSuccess)
           return fail(EISEN_ERR_CUDA, "attn_fwd: smem attribute");

@@ -160,9 +160,11 @@ int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, vo
                    long long S, long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss,
                    long long q_hs, long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs,
                    long long o_ss, long long o_hs, float scale, int causal, int* status);
-/* Query tiles (128 rows) per CTA of the head_dim-64 forward: 1 = one tile per CTA, two CTAs resident
- * per SM whose phases the hardware interleaves (default); 2 = two tiles per CTA sharing every K / V
- * tile and taking turns with the exponentials.  Process-wide; meant for tests and measurements. */
+/* Variant of the head_dim-64 forward: 3 (default) = one 128-row query tile per CTA, two CTAs resident
+ * per SM whose phases the hardware interleaves, the probabilities handed to the P V product through
+ * tensor memory (tcgen05.st; the product reads its A operand from TMEM); 1 = the same with P staged in
+ * shared memory; 2 = two tiles per CTA sharing every K / V tile and taking turns with the
+ * exponentials.  Process-wide; meant for tests and measurements. */
 int eisen_attn_set_fwd_tiles(int tiles);
 long long eisen_attn_bwd_workspace_bytes(long long B, long long S, long long Hq, long long Hkv, long long D);
 /* dq, dk, dv are written (not accumulated); they use the strides of q and k/v respectively. */

@@ -446,6 +446,42 @@ def test_flash_attention_fwd_growing_scores(S, causal):
     assert np.abs(lse.cpu().numpy() - lse_ref.numpy()).max() < 5e-2
 
 
+@pytest.mark.parametrize("tiles", [1, 2])
+@pytest.mark.parametrize("B,S,Hq,Hkv,causal,ramp", [(2, 256, 4, 2, True, False), (1, 200, 2, 2, True, False),
+                                                   (1, 2048, 8, 2, True, False), (2, 1024, 4, 1, False, False),
+                                                   (1, 1000, 2, 1, True, True)])
+def test_flash_attention_fwd64_variants(tiles, B, S, Hq, Hkv, causal, ramp):
+    """The selectable head_dim-64 forward kernels (eisen_attn_set_fwd_tiles: 1 = one query tile per CTA with
+    P staged in shared memory, 2 = two query tiles per CTA; the default, 3, hands P to the P V product
+    through tensor memory) against the same reference as the default kernel, including the case whose
+    row maxima jump between key tiles."""
+    D = 64
+    g = torch.Generator(device="cpu").manual_seed(tiles * 100 + S + Hq)
+    q = torch.randn(B, S, Hq, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, Hkv, D, generator=g)
+    if ramp:
+        k = k * (1.0 + 12.0 * (torch.arange(S) // 96).float() / max(1, S // 96)).view(1, S, 1, 1)
+    k = k.to(torch.bfloat16)
+    v = torch.randn(B, S, Hkv, D, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    o_ref, lse_ref, _, _, _ = _attn_reference(q, k, v, torch.zeros(B, S, Hq, D).to(torch.bfloat16), scale, causal)
+    qd, kd, vd = q.to(dev()), k.to(dev()), v.to(dev())
+    o = torch.full((B, S, Hq, D), float("nan"), dtype=torch.bfloat16, device=dev())
+    lse = torch.empty(B, Hq, S, dtype=torch.float32, device=dev())
+    st = status_word()
+    eb.call("eisen_attn_set_fwd_tiles", tiles)
+    try:
+        eb.call("eisen_attn_fwd", stream(), P(qd), P(kd), P(vd), P(o), P(lse), B, S, Hq, Hkv, D,
+                qd.stride(0), qd.stride(1), qd.stride(2), kd.stride(0), kd.stride(1), kd.stride(2),
+                o.stride(0), o.stride(1), o.stride(2), scale, int(causal), P(st))
+        torch.cuda.synchronize()
+    finally:
+        eb.call("eisen_attn_set_fwd_tiles", 3)
+    assert int(st.item()) == 0
+    assert rel_l2(o.float().cpu().numpy(), o_ref.numpy()) < 1e-2
+    assert np.abs(lse.cpu().numpy() - lse_ref.numpy()).max() < 5e-2
+
+
 def test_attention_rejects_bad_head_dim():
     t = torch.zeros(1, 128, 1, 32, dtype=torch.bfloat16, device=dev())
     lse = torch.zeros(1, 1, 128, device=dev())
