@@ -34,6 +34,8 @@ constexpr float LOG2E = 1.4426950408889634f;
 // variant of the head_dim-64 forward: 3 = one query tile per CTA with P through TMEM, 1 = the same
 // with P through shared memory, 2 = two query tiles per CTA (one CTA per SM)
 std::atomic<int> g_attn_fwd_tiles{3};
+// head_dim-64 backward: 1 = transposed score tiles with P^T handed to the dV product through TMEM
+std::atomic<int> g_attn_bwd_transposed{1};
 
 struct AttnParams {
   int B, S, Hq, Hkv, D;
@@ -810,6 +812,11 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 //                                              once to dQ (in the conversion kernel) and to dK
 //   dV += P^T dO, dK += dS^T Q              -> TMEM, kept across the whole loop (the GQA reduce)
 //   dQ  = dS K                              -> TMEM -> f32 red.global.add into a workspace
+// Transposed form (TS, D = 64, the default there): the score tiles are formed as S^T = K Q^T and
+// dP^T = V dO^T, so a compute thread owns a key and 32 queries; P^T goes back to TMEM as bf16 pairs and
+// the dV product reads its A operand from there; dS^T goes to one shared-memory tile that serves dK
+// (K-major A) and dQ (MN-major A).  lse and delta now belong to the columns: -lse*log2(e) and -delta
+// of the query tile sit in shared memory (two buffers) and every thread reads its 32 of each.
 // With D = 64 the dQ tile has TMEM columns of its own.  The S / dP products of the next query tile
 // are then issued as soon as the compute warps have read the current S / dP into registers, ahead
 // of the current dV, dK, dQ: the tensor core works on them while the exponentials run, and the
@@ -817,8 +824,9 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 // stores of P / dS wait for the products that still read the tile before).  With D = 128 dQ reuses
 // the S columns (512 columns in total): its read-out comes first and S / dP follow it.
 // =====================================================================================
-template <int D>
+template <int D, bool TS = false>
 struct BwdCfg {
+  static_assert(!TS || D == 64, "the transposed form is built for head_dim 64");
   static constexpr int TILE = 128 * D * 2;
   static constexpr int P_TILE = 128 * 128 * 2;
   static constexpr int NS = (D == 64) ? 3 : 1;  // Q / dO stages
@@ -826,8 +834,8 @@ struct BwdCfg {
   static constexpr int OFF_V = TILE;
   static constexpr int OFF_Q = 2 * TILE;               // NS stages
   static constexpr int OFF_DO = OFF_Q + NS * TILE;     // NS stages
-  static constexpr int OFF_P = OFF_DO + NS * TILE;
-  static constexpr int OFF_DS = OFF_P + P_TILE;
+  static constexpr int OFF_P = OFF_DO + NS * TILE;     // TS: no P tile; [2 buffers][-lse2, -delta][128] floats instead
+  static constexpr int OFF_DS = OFF_P + (TS ? 2048 : P_TILE);
   static constexpr bool DQ_OWN = (D == 64);  // dQ has its own TMEM columns
   // with D = 64 a [128 x 64] f32 tile (two 128-byte-swizzled halves of 32 columns) stages dQ for
   // the TMA unit, which adds it to the f32 accumulation buffer
@@ -837,16 +845,17 @@ struct BwdCfg {
   static constexpr int TMEM_COLS = 512;
   static constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + D;
   static constexpr int COL_DQ = DQ_OWN ? 256 + 2 * D : 0;
+  static constexpr int COL_PT = 448;                // TS: P^T as bf16 pairs (64 columns), A operand of dV
   static constexpr int CWARPS = 16;                 // compute warps
   static constexpr int THREADS = (CWARPS + 2) * 32;
 };
 
-template <int D>
-__global__ void __launch_bounds__(BwdCfg<D>::THREADS, 1)
+template <int D, bool TS = false>
+__global__ void __launch_bounds__(BwdCfg<D, TS>::THREADS, 1)  // 18 warps: five on one scheduler, hence 96 registers
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                 const __grid_constant__ CUtensorMap tmDQ, const AttnParams p) {
-  using Cfg = BwdCfg<D>;
+  using Cfg = BwdCfg<D, TS>;
   constexpr int ATOMS = D / 64;
   constexpr int NS = Cfg::NS;
   constexpr int NCT = Cfg::CWARPS * 32;  // compute threads
@@ -932,17 +941,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t sDO = smem_u32(smem + Cfg::OFF_DO + st * Cfg::TILE);
         mbar_wait(&qdo_full[st], (it / NS) & 1, abort_flag, p.status, FAULT_WAIT_ATTN);
         tc_fence_after_sync();
+        // TS: the transposed products S^T = K Q^T and dP^T = V dO^T (TMEM lane = key, column = query)
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * 16384u + (k & 3) * 32u;
-          umma_bf16_ss(tmem_base + Cfg::COL_S, make_smem_desc(sQ + off, 16, 1024), make_smem_desc(sK + off, 16, 1024),
-                       idesc_s, k > 0);
+          const uint64_t dq_ = make_smem_desc(sQ + off, 16, 1024), dk_ = make_smem_desc(sK + off, 16, 1024);
+          umma_bf16_ss(tmem_base + Cfg::COL_S, TS ? dk_ : dq_, TS ? dq_ : dk_, idesc_s, k > 0);
         }
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * 16384u + (k & 3) * 32u;
-          umma_bf16_ss(tmem_base + Cfg::COL_DP, make_smem_desc(sDO + off, 16, 1024),
-                       make_smem_desc(sV + off, 16, 1024), idesc_s, k > 0);
+          const uint64_t do_ = make_smem_desc(sDO + off, 16, 1024), dv_ = make_smem_desc(sV + off, 16, 1024);
+          umma_bf16_ss(tmem_base + Cfg::COL_DP, TS ? dv_ : do_, TS ? do_ : dv_, idesc_s, k > 0);
         }
         umma_commit(sdp_full);
       };
@@ -964,21 +974,36 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_after_sync();
         // K dimension of the next three products = the 128 query rows (dV, dK) or 128 keys (dQ)
 #pragma unroll
-        for (int k = 0; k < 8; ++k)  // dV += P^T dO
-          umma_bf16_ss(tmem_base + Cfg::COL_DV, make_smem_desc(sP + k * 2048u, 16384, 1024),
-                       make_smem_desc(sDO + k * 2048u, 16384, 1024), idesc_t, (it > 0 || k > 0));
+        for (int k = 0; k < 8; ++k) {  // dV += P^T dO
+          if (TS)  // A = P^T from TMEM: lane = key, 16 queries of a step = 8 columns of bf16 pairs
+            umma_bf16_ts(tmem_base + Cfg::COL_DV, tmem_base + Cfg::COL_PT + k * 8u,
+                         make_smem_desc(sDO + k * 2048u, 16384, 1024), idesc_q, (it > 0 || k > 0));
+          else
+            umma_bf16_ss(tmem_base + Cfg::COL_DV, make_smem_desc(sP + k * 2048u, 16384, 1024),
+                         make_smem_desc(sDO + k * 2048u, 16384, 1024), idesc_t, (it > 0 || k > 0));
+        }
 #pragma unroll
-        for (int k = 0; k < 8; ++k)  // dK += dS^T Q
-          umma_bf16_ss(tmem_base + Cfg::COL_DK, make_smem_desc(sDS + k * 2048u, 16384, 1024),
-                       make_smem_desc(sQ + k * 2048u, 16384, 1024), idesc_t, (it > 0 || k > 0));
+        for (int k = 0; k < 8; ++k) {  // dK += dS^T Q  (TS: the dS tile holds dS^T, rows = keys: K-major A)
+          if (TS)
+            umma_bf16_ss(tmem_base + Cfg::COL_DK, make_smem_desc(sDS + (k >> 2) * 16384u + (k & 3) * 32u, 16, 1024),
+                         make_smem_desc(sQ + k * 2048u, 16384, 1024), idesc_q, (it > 0 || k > 0));
+          else
+            umma_bf16_ss(tmem_base + Cfg::COL_DK, make_smem_desc(sDS + k * 2048u, 16384, 1024),
+                         make_smem_desc(sQ + k * 2048u, 16384, 1024), idesc_t, (it > 0 || k > 0));
+        }
         if (Cfg::DQ_OWN && it > 0) {  // the dQ tile of the query tile before has been read out
           mbar_wait(dq_read, iph ^ 1, abort_flag, p.status, FAULT_WAIT_ATTN);
           tc_fence_after_sync();
         }
 #pragma unroll
-        for (int k = 0; k < 8; ++k)  // dQ = dS K
-          umma_bf16_ss(tmem_base + Cfg::COL_DQ, make_smem_desc(sDS + (k >> 2) * 16384u + (k & 3) * 32u, 16, 1024),
-                       make_smem_desc(sK + k * 2048u, 16384, 1024), idesc_q, k > 0);
+        for (int k = 0; k < 8; ++k) {  // dQ = dS K  (TS: dS^T read MN-major, its rows are the keys of the contraction)
+          if (TS)
+            umma_bf16_ss(tmem_base + Cfg::COL_DQ, make_smem_desc(sDS + k * 2048u, 16384, 1024),
+                         make_smem_desc(sK + k * 2048u, 16384, 1024), idesc_t, k > 0);
+          else
+            umma_bf16_ss(tmem_base + Cfg::COL_DQ, make_smem_desc(sDS + (k >> 2) * 16384u + (k & 3) * 32u, 16, 1024),
+                         make_smem_desc(sK + k * 2048u, 16384, 1024), idesc_q, k > 0);
+        }
         umma_commit(dq_full);
         umma_commit(&qdo_empty[st]);
         if (!Cfg::DQ_OWN && it + 1 < iters) {  // dQ sits in the S columns: wait until it has been read out
@@ -1052,6 +1077,29 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     };
 
+    // TS: the statistics belong to the columns (queries) of the transposed tiles, so every thread needs
+    // all 128 of them: -lse * log2(e) and -delta of a query tile sit in shared memory, two buffers.
+    // Threads 0..255 fetch one value each; the value for iteration it + 1 is requested at the top of
+    // iteration it and stored behind that iteration's first barrier (the buffer's readers of
+    // iteration it - 1 are past it), ahead of its second one (which the readers of it + 1 follow).
+    float* stat = reinterpret_cast<float*>(smem + Cfg::OFF_P);
+    auto stat_load = [&](int it) -> float {
+      if (threadIdx.x >= 256 || it >= iters) return 0.0f;
+      const int sh = kvh * rep + it / per_head;
+      const int sq = (i0 + it % per_head) * 128 + (int)(threadIdx.x & 127);
+      if (sq >= p.S) return threadIdx.x < 128 ? -INFINITY : 0.0f;  // -inf -> p = 0
+      const long long idx = ((long long)b * p.Hq + sh) * p.S + sq;
+      return threadIdx.x < 128 ? -p.lse[idx] * LOG2E : -p.delta[idx];
+    };
+    auto stat_store = [&](int it, float v) {
+      if (threadIdx.x < 256 && it < iters) stat[(it & 1) * 256 + threadIdx.x] = v;
+    };
+    if (TS) {
+      stat_store(0, stat_load(0));
+      stat_store(1, stat_load(1));
+      asm volatile("bar.sync 1, %0;" ::"r"(NCT) : "memory");
+    }
+
     for (int it = 0; it < iters; ++it) {
       const uint32_t iph = it & 1;
       const int h = kvh * rep + it / per_head;
@@ -1059,12 +1107,71 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int qrow = qi * 128 + row;
       const bool row_ok = qrow < p.S;
       const long long stat_idx = ((long long)b * p.Hq + h) * p.S + qrow;
-      const float lse2 = row_ok ? p.lse[stat_idx] * LOG2E : INFINITY;  // +inf -> p = 0
-      const float dlt = row_ok ? p.delta[stat_idx] : 0.0f;
+      float lse2 = 0.0f, dlt = 0.0f, stat_next = 0.0f;
+      if (TS) {
+        if (it >= 1) stat_next = stat_load(it + 1);
+      } else {
+        lse2 = row_ok ? p.lse[stat_idx] * LOG2E : INFINITY;  // +inf -> p = 0
+        dlt = row_ok ? p.delta[stat_idx] : 0.0f;
+      }
       const bool need_mask = (p.causal && qi == jt) || ((jt + 1) * 128 > p.S);
       mbar_wait(sdp_full, iph, abort_flag, p.status, FAULT_WAIT_ATTN);
       tc_fence_after_sync();
-      {
+      if (TS) {
+        // lane = key row of this CTA's key tile, columns = the 32 queries of this thread's quarter
+        const int col0 = cq * 32;
+        const int krow = jt * 128 + row;
+        uint32_t rs[32], rd[32];
+        tmem_ld_32x32b_x32(tmem_base + Cfg::COL_S + col0 + lane_off, rs);
+        tmem_ld_32x32b_x32(tmem_base + Cfg::COL_DP + col0 + lane_off, rd);
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        mbar_arrive_warp(sdp_free);
+        uint32_t pk[16], dk[16];
+        const float* sb = stat + (it & 1) * 256 + col0;
+        if (!need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float4 nl = *reinterpret_cast<const float4*>(sb + i);
+            const float4 nd = *reinterpret_cast<const float4*>(sb + 128 + i);
+            float p0, p1, p2, p3, d0, d1, d2, d3;
+            ffma2(p0, p1, __uint_as_float(rs[i]), __uint_as_float(rs[i + 1]), sl2, sl2, nl.x, nl.y);
+            ffma2(p2, p3, __uint_as_float(rs[i + 2]), __uint_as_float(rs[i + 3]), sl2, sl2, nl.z, nl.w);
+            fadd2(d0, d1, __uint_as_float(rd[i]), __uint_as_float(rd[i + 1]), nd.x, nd.y);
+            fadd2(d2, d3, __uint_as_float(rd[i + 2]), __uint_as_float(rd[i + 3]), nd.z, nd.w);
+            p0 = ex2_approx(p0); p1 = ex2_approx(p1); p2 = ex2_approx(p2); p3 = ex2_approx(p3);
+            fmul2(d0, d1, d0, d1, p0, p1);
+            fmul2(d2, d3, d2, d3, p2, p3);
+            pk[i >> 1] = pack_bf16x2(p0, p1);
+            pk[(i >> 1) + 1] = pack_bf16x2(p2, p3);
+            dk[i >> 1] = pack_bf16x2(d0, d1);
+            dk[(i >> 1) + 1] = pack_bf16x2(d2, d3);
+          }
+        } else {
+          const bool key_ok = krow < p.S;
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = ex2_approx(fmaf(__uint_as_float(rs[i]), sl2, sb[i]));
+            float p1 = ex2_approx(fmaf(__uint_as_float(rs[i + 1]), sl2, sb[i + 1]));
+            const int qr = qi * 128 + col0 + i;
+            if (!key_ok || (p.causal && krow > qr)) p0 = 0.0f;
+            if (!key_ok || (p.causal && krow > qr + 1)) p1 = 0.0f;
+            const float d0 = p0 * (__uint_as_float(rd[i]) + sb[128 + i]);
+            const float d1 = p1 * (__uint_as_float(rd[i + 1]) + sb[128 + i + 1]);
+            pk[i >> 1] = pack_bf16x2(p0, p1);
+            dk[i >> 1] = pack_bf16x2(d0, d1);
+          }
+        }
+        // the products of the query tile before read P^T from TMEM and dS^T from shared memory:
+        // dq_full, which the read-out of that tile's dQ waits for, also says that they are done
+        if (it > 0) {
+          drain_dq(it - 1);
+          stat_store(it + 1, stat_next);
+        }
+        tmem_st_32x32b_x16(tmem_base + Cfg::COL_PT + cq * 16 + lane_off, pk);
+        store_row_chunk32(sDS, row, col0, dk);
+        tmem_st_wait();
+      } else {
         const int col0 = cq * 32;
         uint32_t rs[32], rd[32];
         tmem_ld_32x32b_x32(tmem_base + Cfg::COL_S + col0 + lane_off, rs);
@@ -1313,6 +1420,12 @@ using namespace eisen;
 
 extern "C" {
 
+int eisen_attn_set_bwd_mode(int transposed) {
+  if (transposed != 0 && transposed != 1) return fail(EISEN_ERR_INVALID, "attn_set_bwd_mode: 0 or 1");
+  g_attn_bwd_transposed.store(transposed);
+  return 0;
+}
+
 int eisen_attn_set_fwd_tiles(int tiles) {
   if (tiles < 1 || tiles > 3)
     return fail(EISEN_ERR_INVALID, "attn_set_fwd_tiles: 1 or 2 query tiles per CTA, or 3 = one tile with P through TMEM");
@@ -1444,7 +1557,16 @@ int eisen_attn_bwd(void* stream, const void* q, const void* k, const void* v, co
   p.dk = dk; p.dv = dv; p.kv_bs = kv_bs; p.kv_ss = kv_ss; p.kv_hs = kv_hs;
   p.status = status;
   dim3 grid((unsigned)Hkv, (unsigned)B, (unsigned)((S + 127) / 128));
-  if (D == 64) {
+  if (D == 64 && g_attn_bwd_transposed.load()) {
+    static bool set64t[MAX_DEVICE_SLOTS] = {false};
+    if (!set64t[device_slot()]) {
+      if (cudaFuncSetAttribute(attn_bwd_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<64, true>::SMEM) !=
+          cudaSuccess)
+        return fail(EISEN_ERR_CUDA, "attn_bwd: smem attribute");
+      set64t[device_slot()] = true;
+    }
+    attn_bwd_kernel<64, true><<<grid, BwdCfg<64, true>::THREADS, BwdCfg<64, true>::SMEM, s>>>(tq, tk, tv, tdo, tdq, p);
+  } else if (D == 64) {
     static bool set64[MAX_DEVICE_SLOTS] = {false};
     if (!set64[device_slot()]) { if (cudaFuncSetAttribute(attn_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<64>::SMEM) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_bwd: smem attribute"); set64[device_slot()] = true; }
     attn_bwd_kernel<64><<<grid, BwdCfg<64>::THREADS, BwdCfg<64>::SMEM, s>>>(tq, tk, tv, tdo, tdq, p);

@@ -166,6 +166,11 @@ int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, vo
  * shared memory; 2 = two tiles per CTA sharing every K / V tile and taking turns with the
  * exponentials.  Process-wide; meant for tests and measurements. */
 int eisen_attn_set_fwd_tiles(int tiles);
+/* Variant of the head_dim-64 backward: 1 = the score tiles are formed transposed (S^T = K Q^T,
+ * dP^T = V dO^T: TMEM lane = key), so P^T goes back to TMEM and the dV product reads it from there,
+ * and one shared-memory tile (dS^T) serves both dK and dQ; 0 = P and dS through shared memory.
+ * Process-wide; meant for tests and measurements. */
+int eisen_attn_set_bwd_mode(int transposed);
 long long eisen_attn_bwd_workspace_bytes(long long B, long long S, long long Hq, long long Hkv, long long D);
 /* dq, dk, dv are written (not accumulated); they use the strides of q and k/v respectively. */
 int eisen_attn_bwd(void* stream, const void* q, const void* k, const void* v, const void* o, const float* lse,

@@ -384,6 +384,7 @@ def _attn_reference(q, k, v, d_o, scale, causal):
     (1, 2048, 8, 2, 128, True),   # the isolated attention-backward benchmark's geometry (16 key tiles per row, 4 query heads per KV head) on one batch element
     (1, 2048, 8, 2, 64, True),    # the 0.85B model's geometry
     (2, 1024, 4, 1, 64, False),
+    (1, 333, 4, 1, 64, False),    # ragged, four query heads per KV head
 ])
 def test_flash_attention_fwd_bwd(B, S, Hq, Hkv, D, causal):
     g = torch.Generator(device="cpu").manual_seed(B * 1000 + S + Hq * 7 + D)
@@ -444,6 +445,19 @@ def test_flash_attention_fwd_growing_scores(S, causal):
     assert int(st.item()) == 0
     assert rel_l2(o.float().cpu().numpy(), o_ref.numpy()) < 1e-2
     assert np.abs(lse.cpu().numpy() - lse_ref.numpy()).max() < 5e-2
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv,causal", [(1, 128, 1, 1, False), (2, 256, 4, 2, True), (1, 200, 2, 2, True),
+                                                (1, 2048, 8, 2, True), (2, 1024, 4, 1, False), (1, 333, 4, 1, False)])
+def test_flash_attention_bwd64_untransposed(B, S, Hq, Hkv, causal):
+    """The selectable head_dim-64 backward with P and dS through shared memory (eisen_attn_set_bwd_mode(0);
+    the default forms the score tiles transposed and hands P^T to the dV product through tensor memory)
+    against the same reference as the default kernel."""
+    eb.call("eisen_attn_set_bwd_mode", 0)
+    try:
+        test_flash_attention_fwd_bwd(B, S, Hq, Hkv, 64, causal)
+    finally:
+        eb.call("eisen_attn_set_bwd_mode", 1)
 
 
 @pytest.mark.parametrize("tiles", [1, 2])
