@@ -416,7 +416,11 @@ def side_cases(args, peaks, dev, compute):
         torch.cuda.empty_cache()
         e = bc.case_elementwise(16384, 2048, 2048, 64, 32000, 100_000_000, iters=12)
         c4["rope_bwd"] = {"gbs": e["rope_bwd_gbs"], "frac_of_hbm": e["rope_bwd_gbs"] / hbm}
-        c4["embedding_bwd"] = {"gbs": e["embedding_bwd_gbs"], "ms": e["embedding_bwd_ms"], "frac_of_hbm": e["embedding_bwd_gbs"] / hbm}
+        c4["embedding_bwd"] = {"gbs": e["embedding_bwd_gbs"], "ms": e["embedding_bwd_ms"], "frac_of_hbm": e["embedding_bwd_gbs"] / hbm,
+                               "what": "whole call: grouping of the positions by id (five small launches on the ids alone) + row sums"}
+        c4["embedding_bwd_row_sums"] = {"gbs": e["embedding_bwd_apply_gbs"], "ms": e["embedding_bwd_apply_ms"],
+                                        "frac_of_hbm": e["embedding_bwd_apply_gbs"] / hbm,
+                                        "what": "eisen_embedding_bwd_apply, the part on the backward path: the model runs the grouping on a side stream during the forward pass"}
         c4["sumsq"] = {"gbs": e["sumsq_gbs"], "frac_of_hbm": e["sumsq_gbs"] / hbm}
         del e
         torch.cuda.empty_cache()

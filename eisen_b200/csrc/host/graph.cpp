@@ -80,6 +80,9 @@ Graph::~Graph() {
   }
   if (compute_mark_) cudaEventDestroy(compute_mark_);
   if (copy_stream_) cudaStreamDestroy(copy_stream_);
+  if (aux_stream_) cudaStreamDestroy(aux_stream_);
+  if (aux_fork_) cudaEventDestroy(aux_fork_);
+  if (aux_join_) cudaEventDestroy(aux_join_);
 }
 
 // exact-size free lists, as the reference's vram_pool keyed by element count
@@ -372,6 +375,11 @@ void Graph::restore_save_point(int64_t sp) {
 }
 void Graph::clear_activations() {
   tape.clear();
+  if (aux_pending_ && !capturing) {
+    // a forward pass whose backward never ran: its side-stream work still owns a pooled buffer
+    cuck(cudaStreamWaitEvent(stream, aux_join_, 0), "cudaStreamWaitEvent");
+    aux_pending_ = false;
+  }
   restore_save_point(num_params);
 }
 void Graph::reinterpret_shape(int64_t id, const std::vector<int64_t>& shape) {
@@ -1369,15 +1377,40 @@ int64_t Graph::gather(int64_t w, int64_t idx) {
                          vocab, bad_id_dev),
      "gather");
   if (!no_grad) {
-    tape.push_back({{w, idx}, o, [this, w, ids, o, n, dim, vocab]() {
+    // The grouping of the positions by id (count, scan, place, order: integer work on the ids alone)
+    // runs now, on a side stream beside the first blocks, into a buffer that lives as long as the
+    // activations; the backward pass then only adds the gradient rows.  While a step is being
+    // captured the grouping stays on the graph's own stream.
+    const size_t ws_bytes = (size_t)eisen_embedding_bwd_workspace_bytes(n, vocab);
+    const int64_t ws_id = alloc_pooled({(int64_t)((ws_bytes + dsize(dt) - 1) / dsize(dt))});
+    tensors[ws_id].constant = true;
+    void* ws = tensors[ws_id].data;
+    const bool side = !capturing;
+    if (side) {
+      if (!aux_stream_) {
+        cuck(cudaStreamCreateWithFlags(&aux_stream_, cudaStreamNonBlocking), "cudaStreamCreate(aux)");
+        cuck(cudaEventCreateWithFlags(&aux_fork_, cudaEventDisableTiming), "cudaEventCreate");
+        cuck(cudaEventCreateWithFlags(&aux_join_, cudaEventDisableTiming), "cudaEventCreate");
+      }
+      cuck(cudaEventRecord(aux_fork_, stream), "cudaEventRecord");
+      cuck(cudaStreamWaitEvent(aux_stream_, aux_fork_, 0), "cudaStreamWaitEvent");
+      ck(eisen_embedding_bwd_plan(aux_stream_, (const int*)tensors[ids].data, ws, n, vocab), "gather(plan)");
+      cuck(cudaEventRecord(aux_join_, aux_stream_), "cudaEventRecord");
+      aux_pending_ = true;
+    } else {
+      ck(eisen_embedding_bwd_plan(stream, (const int*)tensors[ids].data, ws, n, vocab), "gather(plan)");
+    }
+    tape.push_back({{w, idx}, o, [this, w, o, n, dim, vocab, ws, side]() {
       OUT_GRAD_OR_RETURN(o);
       HTensor& gw = tensors[w];
       ensure_grad(w);
       if (gw.grad_dtype != 0) invalid("gather: the table gradient must be f32");
       if (!gw.grad_init) { cuck(cudaMemsetAsync(gw.grad, 0, (size_t)gw.numel * 4, stream), "memset"); gw.grad_init = true; }
-      void* ws = scratch((size_t)eisen_embedding_bwd_workspace_bytes(n, vocab));
-      ck(eisen_embedding_bwd(stream, to.grad, to.grad_dtype, (const int*)tensors[ids].data, (float*)gw.grad, ws, n, dim, vocab),
-         "gather.bwd");
+      if (side) {
+        cuck(cudaStreamWaitEvent(stream, aux_join_, 0), "cudaStreamWaitEvent");
+        aux_pending_ = false;
+      }
+      ck(eisen_embedding_bwd_apply(stream, to.grad, to.grad_dtype, (float*)gw.grad, ws, n, dim, vocab), "gather.bwd");
     }});
   }
   return o;

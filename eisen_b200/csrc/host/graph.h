@@ -218,6 +218,10 @@ class Graph {
   size_t stage_next_ = 0;
   uint64_t weight_generation_ = 1;
   cudaStream_t copy_stream_ = nullptr;
+  // side stream for work that depends on the token ids only (the grouping of the embedding backward)
+  cudaStream_t aux_stream_ = nullptr;
+  cudaEvent_t aux_fork_ = nullptr, aux_join_ = nullptr;
+  bool aux_pending_ = false;  // side-stream work the graph's stream has not waited for yet
   cudaEvent_t compute_mark_ = nullptr;
   void ensure_stage(size_t bytes);
   StageSlot* stage_weight(int64_t id);
