@@ -47,6 +47,9 @@ struct AttnParams {
   const float* delta;  // [B, Hq, S]
   float* dq_acc;     // [B, S, Hq, D] f32
   void* dk; void* dv; long long kv_bs, kv_ss, kv_hs;
+  // backward only, may be null: (cos, sin) table [S][D / 2]; dK (and dQ, in the conversion kernel) are
+  // then written rotated back by the RoPE angles of their positions
+  const float2* unrope_tab;
   int* status;
 };
 
@@ -1240,10 +1243,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(which ? p.dk : p.dv) + base;
         const int colbase = (which ? Cfg::COL_DK : Cfg::COL_DV) + cq * DQC;
         const float mul = which ? p.scale : 1.0f;  // dS was kept unscaled
+        // dK of a rotated k: the pairs (2i, 2i + 1) of this thread's columns turn back by the angles of the key's position
+        const bool unrope = which && p.unrope_tab != nullptr && krow < p.S;
+        auto rotate_back = [&](auto& r) {
+          constexpr int n = (int)(sizeof(r) / sizeof(uint32_t));
+          const float4* tp = reinterpret_cast<const float4*>(p.unrope_tab + (long long)krow * (D / 2) + (cq * DQC) / 2);
+#pragma unroll
+          for (int i = 0; i < n; i += 4) {
+            const float4 t = __ldg(tp + (i >> 2));  // (cos, sin) of two pairs
+            const float x0 = __uint_as_float(r[i]), y0 = __uint_as_float(r[i + 1]);
+            const float x1 = __uint_as_float(r[i + 2]), y1 = __uint_as_float(r[i + 3]);
+            r[i] = __float_as_uint(x0 * t.x + y0 * t.y);
+            r[i + 1] = __float_as_uint(y0 * t.x - x0 * t.y);
+            r[i + 2] = __float_as_uint(x1 * t.z + y1 * t.w);
+            r[i + 3] = __float_as_uint(y1 * t.z - x1 * t.w);
+          }
+        };
         if constexpr (DQC == 16) {
           uint32_t r[16];
           tmem_ld_32x32b_x16(tmem_base + colbase + lane_off, r);
           tmem_ld_wait();
+          if (unrope) rotate_back(r);
           if (krow < p.S) {
 #pragma unroll
             for (int i = 0; i < 16; i += 8) {
@@ -1259,6 +1279,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           uint32_t r[32];
           tmem_ld_32x32b_x32(tmem_base + colbase + lane_off, r);
           tmem_ld_wait();
+          if (unrope) rotate_back(r);
           if (krow < p.S) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
@@ -1373,10 +1394,13 @@ attn_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __res
   }
 }
 
-// dq (bf16, strided [B,S,H,D]) = dq_acc (f32, contiguous [B,S,H,D])
+// dq (bf16, strided [B,S,H,D]) = dq_acc (f32, contiguous [B,S,H,D]); UNROPE: rotated back by the RoPE
+// angles of the row's position (table [S][D / 2] of (cos, sin)) before the rounding
+template <bool UNROPE>
 __global__ void __launch_bounds__(256)
 attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long rows /*B*S*H*/,
-                       int S, int H, int D, long long bs, long long ss, long long hs, float scale) {
+                       int S, int H, int D, long long bs, long long ss, long long hs, float scale,
+                       const float2* __restrict__ unrope_tab) {
   const int per_row = D / 8;
   const long long total = rows * per_row;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -1387,11 +1411,27 @@ attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict_
     const int s = (int)((r / H) % S);
     const long long b = r / ((long long)H * S);
     float lo[4], hi[4];
+    float4 t0 = make_float4(1.0f, 0.0f, 1.0f, 0.0f), t1 = t0;
+    if (UNROPE) {  // requested together with the accumulator's two vectors
+      const float4* tp = reinterpret_cast<const float4*>(unrope_tab + (long long)s * (D / 2) + (c >> 1));
+      t0 = __ldg(tp);
+      t1 = __ldg(tp + 1);
+    }
     ld16(acc + r * D + c, lo);
     ld16(acc + r * D + c + 4, hi);
     // the backward kernel accumulates dS K with dS unscaled: the softmax scale is applied here
     float v[8] = {lo[0] * scale, lo[1] * scale, lo[2] * scale, lo[3] * scale,
                   hi[0] * scale, hi[1] * scale, hi[2] * scale, hi[3] * scale};
+    if (UNROPE) {
+      // dQ of a rotated q: the four (even, odd) pairs turn back by the angles of the query's position
+      const float cs[4] = {t0.x, t0.z, t1.x, t1.z}, sn[4] = {t0.y, t0.w, t1.y, t1.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float x = v[2 * e], y = v[2 * e + 1];
+        v[2 * e] = x * cs[e] + y * sn[e];
+        v[2 * e + 1] = y * cs[e] - x * sn[e];
+      }
+    }
     st16(dq + b * bs + (long long)s * ss + (long long)h * hs + c, v);
   }
 }
@@ -1498,12 +1538,14 @@ long long eisen_attn_bwd_workspace_bytes(long long B, long long S, long long Hq,
   return B * S * Hq * D * 4 + B * Hq * S * 4 + 256;
 }
 
-int eisen_attn_bwd(void* stream, const void* q, const void* k, const void* v, const void* o, const float* lse,
-                   const void* d_o, void* dq, void* dk, void* dv, void* workspace, long long B, long long S,
-                   long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss, long long q_hs,
-                   long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs, long long o_ss,
-                   long long o_hs, float scale, int causal, int* status) {
+static int attn_bwd_impl(void* stream, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                         const void* d_o, void* dq, void* dk, void* dv, void* workspace, long long B, long long S,
+                         long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss, long long q_hs,
+                         long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs, long long o_ss,
+                         long long o_hs, float scale, int causal, const float* unrope_table, int* status) {
   const long long st[9] = {q_bs, q_ss, q_hs, kv_bs, kv_ss, kv_hs, o_bs, o_ss, o_hs};
+  if (unrope_table && (reinterpret_cast<uintptr_t>(unrope_table) & 15))
+    return fail(EISEN_ERR_INVALID, "attn_bwd: the rotation table must be 16-byte aligned");
   int rc = check_args(B, S, Hq, Hkv, D, st, 9);
   if (rc) return rc;
   if (!workspace) return fail(EISEN_ERR_INVALID, "attn_bwd: workspace is null");
@@ -1555,6 +1597,7 @@ int eisen_attn_bwd(void* stream, const void* q, const void* k, const void* v, co
   p.causal = causal; p.scale = scale;
   p.lse = const_cast<float*>(lse); p.delta = delta; p.dq_acc = dq_acc;
   p.dk = dk; p.dv = dv; p.kv_bs = kv_bs; p.kv_ss = kv_ss; p.kv_hs = kv_hs;
+  p.unrope_tab = reinterpret_cast<const float2*>(unrope_table);
   p.status = status;
   dim3 grid((unsigned)Hkv, (unsigned)B, (unsigned)((S + 127) / 128));
   if (D == 64 && g_attn_bwd_transposed.load()) {
@@ -1577,9 +1620,33 @@ int eisen_attn_bwd(void* stream, const void* q, const void* k, const void* v, co
   }
   rc = check_launch("attn_bwd");
   if (rc) return rc;
-  attn_dq_convert_kernel<<<grid_for(B * S * Hq * D / 8, 256, 8), 256, 0, s>>>(dq_acc, (__nv_bfloat16*)dq, B * S * Hq, (int)S,
-                                                                              (int)Hq, (int)D, q_bs, q_ss, q_hs, scale);
+  if (unrope_table)
+    attn_dq_convert_kernel<true><<<grid_for(B * S * Hq * D / 8, 256, 8), 256, 0, s>>>(
+        dq_acc, (__nv_bfloat16*)dq, B * S * Hq, (int)S, (int)Hq, (int)D, q_bs, q_ss, q_hs, scale,
+        reinterpret_cast<const float2*>(unrope_table));
+  else
+    attn_dq_convert_kernel<false><<<grid_for(B * S * Hq * D / 8, 256, 8), 256, 0, s>>>(
+        dq_acc, (__nv_bfloat16*)dq, B * S * Hq, (int)S, (int)Hq, (int)D, q_bs, q_ss, q_hs, scale, nullptr);
   return check_launch("attn_dq_convert");
+}
+
+int eisen_attn_bwd(void* stream, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                   const void* d_o, void* dq, void* dk, void* dv, void* workspace, long long B, long long S,
+                   long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss, long long q_hs,
+                   long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs, long long o_ss,
+                   long long o_hs, float scale, int causal, int* status) {
+  return attn_bwd_impl(stream, q, k, v, o, lse, d_o, dq, dk, dv, workspace, B, S, Hq, Hkv, D, q_bs, q_ss, q_hs, kv_bs, kv_ss,
+                       kv_hs, o_bs, o_ss, o_hs, scale, causal, nullptr, status);
+}
+
+int eisen_attn_bwd_unrope(void* stream, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                          const void* d_o, void* dq, void* dk, void* dv, void* workspace, long long B, long long S,
+                          long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss, long long q_hs,
+                          long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs, long long o_ss,
+                          long long o_hs, float scale, int causal, const float* table_cos_sin, int* status) {
+  if (!table_cos_sin) return fail(EISEN_ERR_INVALID, "attn_bwd_unrope: the rotation table is null");
+  return attn_bwd_impl(stream, q, k, v, o, lse, d_o, dq, dk, dv, workspace, B, S, Hq, Hkv, D, q_bs, q_ss, q_hs, kv_bs, kv_ss,
+                       kv_hs, o_bs, o_ss, o_hs, scale, causal, table_cos_sin, status);
 }
 
 }  // extern "C"

@@ -886,6 +886,9 @@ int64_t Graph::matmul_rope(int64_t a, int64_t b, int64_t head_dim) {
 // Backward: dX = dQ' Wq^T + dK' Wk^T + dV Wv^T in one pass over the three operand pairs (dQ', dK' =
 // the gradients rotated back), and the three dW = X^T dY in one launch.  Shapes the fused kernels do
 // not take, Fp32 graphs and host-homed weights run matmul_rope, matmul_rope, matmul.
+// The q and k it returns are meant for Graph::attention alone: that op's backward hands their
+// gradients over rotated back already (HTensor::unrope_hd / grad_unrotated), which a second consumer
+// adding a gradient in the rotated form would not match.
 void Graph::qkv_proj_rope(int64_t x, int64_t wq, int64_t wk, int64_t wv, int64_t head_dim, int64_t out3[3]) {
   const HTensor& tx = tensors.at(x);
   const int64_t ws[3] = {wq, wk, wv};
@@ -915,6 +918,7 @@ void Graph::qkv_proj_rope(int64_t x, int64_t wq, int64_t wk, int64_t wv, int64_t
   const int dt = act_dtype();
   for (int i = 0; i < 3; ++i) out3[i] = alloc_pooled({B, S, ns[i]});
   const int64_t oq = out3[0], ok = out3[1], ov = out3[2];
+  tensors[oq].unrope_hd = tensors[ok].unrope_hd = head_dim;
   if (!skip_forward) {
     const void* bs[3] = {weight_operand(wq), weight_operand(wk), weight_operand(wv)};
     void* cs[3] = {tensors[oq].data, tensors[ok].data, tensors[ov].data};
@@ -945,6 +949,10 @@ void Graph::qkv_proj_rope(int64_t x, int64_t wq, int64_t wk, int64_t wv, int64_t
     const void* dy[3] = {nullptr, nullptr, nullptr};
     for (int i = 0; i < 2; ++i) {
       if (!have[i]) continue;
+      if (tensors[outs[i]].grad_unrotated) {  // the attention backward delivered it rotated back already
+        dy[i] = tensors[outs[i]].grad;
+        continue;
+      }
       Temp& t = i == 0 ? rq : rk;
       t.b = (size_t)m * ns[i] * dsize(dt);
       t.p = pool_get(t.b);
@@ -1582,11 +1590,25 @@ int64_t Graph::attention(int64_t q, int64_t k, int64_t v, int64_t Hq, int64_t Hk
         else dst[i] = gt[i]->grad;
       }
       void* ws = scratch((size_t)eisen_attn_bwd_workspace_bytes(B, S, Hq, Hkv, D));
+      // q and k that come from a projection + RoPE op take their gradients rotated back: no separate
+      // RoPE backward launch.  Both must be in that form (fresh, or accumulated in it before).
+      auto takes_unrotated = [&](const HTensor& t) { return t.unrope_hd == D && (!t.grad_init || t.grad_unrotated); };
+      const bool unrope = takes_unrotated(*gt[0]) && takes_unrotated(*gt[1]);
+      if (!unrope && (gt[0]->grad_unrotated || gt[1]->grad_unrotated))
+        invalid("attention: the gradients of q and k are kept in different forms");
       prof_begin(2, 2.5 * attn_flops);
-      ck(eisen_attn_bwd(stream, operand(*gt[0]), operand(*gt[1]), operand(*gt[2]), to.data, (const float*)tensors[lse].data,
-                        to.grad, dst[0], dst[1], dst[2], ws, B, S, Hq, Hkv, D, qb, qs, D, kb, ks, D, qb, qs, D, scale,
-                        causal, status_dev),
-         "attention.bwd");
+      if (unrope) {
+        ck(eisen_attn_bwd_unrope(stream, operand(*gt[0]), operand(*gt[1]), operand(*gt[2]), to.data,
+                                 (const float*)tensors[lse].data, to.grad, dst[0], dst[1], dst[2], ws, B, S, Hq, Hkv, D, qb, qs,
+                                 D, kb, ks, D, qb, qs, D, scale, causal, rope_table(S, D), status_dev),
+           "attention.bwd");
+        gt[0]->grad_unrotated = gt[1]->grad_unrotated = true;
+      } else {
+        ck(eisen_attn_bwd(stream, operand(*gt[0]), operand(*gt[1]), operand(*gt[2]), to.data, (const float*)tensors[lse].data,
+                          to.grad, dst[0], dst[1], dst[2], ws, B, S, Hq, Hkv, D, qb, qs, D, kb, ks, D, qb, qs, D, scale,
+                          causal, status_dev),
+           "attention.bwd");
+      }
       prof_end();
       for (int i = 0; i < 3; ++i) {
         if (tmp[i]) {

@@ -42,6 +42,10 @@ struct HTensor {
   // that read rows or elements use them in place over PCIe, GEMM operands are staged on the device.
   bool host_homed = false;
   bool grad_is_ones = false;  // the gradient was seeded with ones by backward() and not written since
+  // Output of a projection + RoPE op that can take its gradient already rotated back (head_dim; 0 = no):
+  // the fused attention backward then writes dq / dk in that form and sets grad_unrotated.
+  int64_t unrope_hd = 0;
+  bool grad_unrotated = false;
   bool constant = false;   // no gradient is ever formed (masks, scale tensors, ids)
   std::string name;
 };

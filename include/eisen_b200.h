@@ -160,6 +160,16 @@ int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, vo
                    long long S, long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss,
                    long long q_hs, long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs,
                    long long o_ss, long long o_hs, float scale, int causal, int* status);
+/* eisen_attn_bwd for q and k that were rotated by RoPE right before the attention
+ * (src/nn/attention.rs:320-333): dq and dk come out rotated back by the angles of their positions
+ * (table_cos_sin of eisen_rope_table for (S, D)), i.e. as the gradients of the un-rotated projections,
+ * so the backward closure of `rope` has nothing left to launch.  The rotation is applied in f32
+ * before the one rounding to bf16. */
+int eisen_attn_bwd_unrope(void* stream, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                          const void* d_o, void* dq, void* dk, void* dv, void* workspace, long long B, long long S,
+                          long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss, long long q_hs,
+                          long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs, long long o_ss,
+                          long long o_hs, float scale, int causal, const float* table_cos_sin, int* status);
 /* Variant of the head_dim-64 forward: 3 (default) = one 128-row query tile per CTA, two CTAs resident
  * per SM whose phases the hardware interleaves, the probabilities handed to the P V product through
  * tensor memory (tcgen05.st; the product reads its A operand from TMEM); 1 = the same with P staged in
