@@ -158,6 +158,12 @@ int eisen_graph_tensor_ptrs(void* g, long long id, void** data, void** grad, int
 int eisen_graph_set_no_grad(void* g, int flag) {
   return guarded([&] { G(g).no_grad = flag != 0; });
 }
+int eisen_graph_get_flags(void* g, int* no_grad, int* skip_forward) {
+  return guarded([&] {
+    if (no_grad) *no_grad = G(g).no_grad ? 1 : 0;
+    if (skip_forward) *skip_forward = G(g).skip_forward ? 1 : 0;
+  });
+}
 int eisen_graph_mark_params(void* g) {
   return guarded([&] { G(g).mark_params(); });
 }

@@ -168,6 +168,12 @@ class Graph:
     def set_no_grad(self, flag):
         call("eisen_graph_set_no_grad", self._h, 1 if flag else 0)
 
+    def flags(self):
+        """(no_grad, skip_forward) as the graph holds them now."""
+        a, b = C.c_int(), C.c_int()
+        call("eisen_graph_get_flags", self._h, C.byref(a), C.byref(b))
+        return bool(a.value), bool(b.value)
+
     def mark_params(self):
         call("eisen_graph_mark_params", self._h)
 

@@ -392,6 +392,10 @@ int eisen_graph_sync_grad_to_cpu(void* g, long long id, float* out);            
 int eisen_graph_shape(void* g, long long id, long long* shape_out, int* ndim_out);
 int eisen_graph_tensor_ptrs(void* g, long long id, void** data, void** grad, int* dtype, int* grad_dtype);
 int eisen_graph_set_no_grad(void* g, int flag);                                        /* Graph.no_grad */
+/* The graph's mode flags (no_grad: ops record no tape entry; skip_forward: ops allocate their output but
+ * launch no forward kernel, used while a checkpointed block is re-recorded).  Both are set for a scope
+ * by the model code and restored when the scope ends, also when an op inside it fails. */
+int eisen_graph_get_flags(void* g, int* no_grad, int* skip_forward);
 int eisen_graph_mark_params(void* g);                                                  /* :328-330 */
 int eisen_graph_mark_save_point(void* g, long long* out);                              /* :332-334 */
 int eisen_graph_restore_save_point(void* g, long long save_point);                     /* :336-365 */

@@ -343,6 +343,49 @@ def test_bf16_config2_architecture_step():
     print("config 2 architecture, bf16 worst grad rel-L2", worst)
 
 
+def test_mode_flags_are_restored_when_a_step_fails_midway():
+    """A host-side failure (an activation allocation over the VRAM budget) at every depth of a checkpointed
+    bf16 step: the call reports out-of-memory, no_grad / skip_forward are back to false, and the same graph
+    then runs the step under a sufficient budget with the result of an undisturbed graph."""
+    cfg = dict(vocab=512, hidden=256, heads=4, kv=2, ffn=512, layers=2, batch=2, seq=256)
+    ids, tg = _tokens(cfg, 9)
+    tl = tg.reshape(-1).tolist()
+
+    def build():
+        g = new_graph(BF16_MIXED)
+        lm = TransformerLM(g, cfg["vocab"], cfg["hidden"], cfg["heads"], cfg["kv"], cfg["ffn"], cfg["layers"], False)
+        g.mark_params()
+        return g, lm
+
+    g0, lm0 = build()
+    x0 = g0.alloc_ids([cfg["batch"], cfg["seq"]], ids.astype(np.int32))
+    ref_loss = float(g0.data(lm0.train_micro_step(x0, tl, checkpoint=True))[0])
+    ref_grad = g0.grad(lm0.params()[1])
+    g, lm = build()
+    used, _ = g.vram_usage()
+    failures = 0
+    for extra_kb in (64, 600, 1400, 2200, 3000, 4000, 5200, 6500, 8000, 12000, 1 << 20):
+        g.set_vram_budget(used + extra_kb * 1024, 0)
+        x = g.alloc_ids([cfg["batch"], cfg["seq"]], ids.astype(np.int32))
+        for p in lm.params():
+            g.zero_grad_tensor(p)
+        try:
+            loss = lm.train_micro_step(x, tl, checkpoint=True)
+        except eb.EisenError as e:
+            failures += 1
+            assert "budget" in str(e).lower() or "memory" in str(e).lower(), str(e)
+            assert g.flags() == (False, False)
+            g.clear_activations()
+            continue
+        assert g.flags() == (False, False)
+        assert abs(float(g.data(loss)[0]) - ref_loss) < 1e-6 * max(1.0, abs(ref_loss))
+        assert rel_l2(g.grad(lm.params()[1]), ref_grad) < 1e-4
+        break
+    else:
+        raise AssertionError("the step never fit the budget")
+    assert failures >= 3  # the budgets above fail at several different depths
+
+
 def test_adamw_clip_and_fused_step():
     cfg = dict(vocab=128, hidden=64, heads=2, kv=2, ffn=128, layers=1, batch=2, seq=16)
     ids, tg = _tokens(cfg, 5)
