@@ -529,6 +529,18 @@ def run_ours(args, cfg, name):
         ms_keep = r.timed(False, args.steps)
         r.lm.set_keep_attention(False)
         g.synchronize()
+    # ---- variant: fixed-order arithmetic (one slice per weight-gradient tile, dQ summed in key order):
+    # gradients are bit-identical from run to run
+    ms_det = None
+    if world == 1 and not args.no_variants:
+        eb.call("eisen_set_deterministic", 1)
+        try:
+            for it in range(2):
+                r.step(False, it)
+            ms_det = r.timed(False, min(args.steps, 3)) / min(args.steps, 3)
+        finally:
+            eb.call("eisen_set_deterministic", 0)
+        g.synchronize()
 
     step_tokens = B * S * accum * world
     tps = step_tokens * args.steps / (ms_total / 1e3)
@@ -579,6 +591,12 @@ def run_ours(args, cfg, name):
                         "forward pass and recomputes the rest of the block (`value` recomputes the whole block)",
                 "ms_per_step": ms_keep / args.steps, "tokens_per_s": step_tokens * args.steps / (ms_keep / 1e3),
                 "mfu_of_nominal_2250_tflops": step_tokens * args.steps / (ms_keep / 1e3) / world * fpt / (NOMINAL_BF16_TFLOPS * 1e12)}}
+        if ms_det is not None:
+            out.setdefault("variants", {})["fixed_order_arithmetic"] = {
+                "what": "eisen_set_deterministic(1): weight-gradient GEMMs with one slice per tile, attention dQ written per key "
+                        "tile and summed in key order; gradients are bit-identical from run to run (`value` uses split-K and "
+                        "atomic adds)",
+                "ms_per_step": ms_det, "tokens_per_s": step_tokens / (ms_det / 1e3)}
     r.close()
     del r, g
     if rank == 0 and world == 1 and not args.no_cases:

@@ -50,6 +50,10 @@ struct AttnParams {
   // backward only, may be null: (cos, sin) table [S][D / 2]; dK (and dQ, in the conversion kernel) are
   // then written rotated back by the RoPE angles of their positions
   const float2* unrope_tab;
+  // backward, fixed-order mode: key tile jt writes its dQ tiles to slice jt of dq_acc (dq_slice elements
+  // apart) instead of adding them to one buffer; the conversion kernel sums the slices in key order
+  int det;
+  long long dq_slice;
   int* status;
 };
 
@@ -1034,7 +1038,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int qrow = (i0 + it % per_head) * 128 + row;
       mbar_wait(dq_full, it & 1, abort_flag, p.status, FAULT_WAIT_ATTN);
       tc_fence_after_sync();
-      float* dq_row = p.dq_acc + (((long long)b * p.S + qrow) * p.Hq + h) * D + cq * DQC;
+      float* dq_row = p.dq_acc + (p.det ? (long long)jt * p.dq_slice : 0LL) + (((long long)b * p.S + qrow) * p.Hq + h) * D + cq * DQC;
       if constexpr (DQC == 16) {
         // TMEM -> registers -> swizzled shared-memory tile -> one TMA reduce-add per half tile.
         // Adding 16-byte pieces of 32 different rows with one red.global per warp instruction was
@@ -1068,11 +1072,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld_32x32b_x32(tmem_base + Cfg::COL_DQ + cq * DQC + lane_off, r);
         tmem_ld_wait();
         if (qrow < p.S) {
+          if (p.det) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + i), "f"(__uint_as_float(r[i])),
-                         "f"(__uint_as_float(r[i + 1])), "f"(__uint_as_float(r[i + 2])), "f"(__uint_as_float(r[i + 3]))
-                         : "memory");
+            for (int i = 0; i < 32; i += 4)
+              *reinterpret_cast<uint4*>(dq_row + i) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + i), "f"(__uint_as_float(r[i])),
+                           "f"(__uint_as_float(r[i + 1])), "f"(__uint_as_float(r[i + 2])), "f"(__uint_as_float(r[i + 3]))
+                           : "memory");
+          }
         }
       }
       tc_fence_before_sync();
@@ -1087,8 +1097,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (threadIdx.x == 0) {
         const int h = kvh * rep + it / per_head;
         const int qi = i0 + it % per_head;
-        tma_reduce_add_4d(&tmDQ, smem_u32(smem + Cfg::OFF_DQS), 0, h, qi * 128, b);
-        tma_reduce_add_4d(&tmDQ, smem_u32(smem + Cfg::OFF_DQS) + 16384u, 32, h, qi * 128, b);
+        if (p.det) {  // the map's last dimension runs over (key tile, batch element)
+          tma_store_4d(&tmDQ, smem_u32(smem + Cfg::OFF_DQS), 0, h, qi * 128, jt * p.B + b);
+          tma_store_4d(&tmDQ, smem_u32(smem + Cfg::OFF_DQS) + 16384u, 32, h, qi * 128, jt * p.B + b);
+        } else {
+          tma_reduce_add_4d(&tmDQ, smem_u32(smem + Cfg::OFF_DQS), 0, h, qi * 128, b);
+          tma_reduce_add_4d(&tmDQ, smem_u32(smem + Cfg::OFF_DQS) + 16384u, 32, h, qi * 128, b);
+        }
         tma_store_commit();
       }
     };
@@ -1409,11 +1424,13 @@ attn_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __res
 
 // dq (bf16, strided [B,S,H,D]) = dq_acc (f32, contiguous [B,S,H,D]); UNROPE: rotated back by the RoPE
 // angles of the row's position (table [S][D / 2] of (cos, sin)) before the rounding
+// n_slices > 1 (fixed-order mode): acc holds one [B,S,H,D] slice per key tile, `slice` elements apart; row s
+// sums slices 0 .. s / 128 under the causal mask (later key tiles wrote nothing there), all of them otherwise
 template <bool UNROPE>
 __global__ void __launch_bounds__(256)
 attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long rows /*B*S*H*/,
                        int S, int H, int D, long long bs, long long ss, long long hs, float scale,
-                       const float2* __restrict__ unrope_tab) {
+                       const float2* __restrict__ unrope_tab, int n_slices, long long slice, int causal) {
   const int per_row = D / 8;
   const long long total = rows * per_row;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -1432,6 +1449,16 @@ attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict_
     }
     ld16(acc + r * D + c, lo);
     ld16(acc + r * D + c + 4, hi);
+    if (n_slices > 1) {
+      const int last = causal ? min(s >> 7, n_slices - 1) : n_slices - 1;
+      for (int j = 1; j <= last; ++j) {
+        float lo2[4], hi2[4];
+        ld16(acc + j * slice + r * D + c, lo2);
+        ld16(acc + j * slice + r * D + c + 4, hi2);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { lo[e] += lo2[e]; hi[e] += hi2[e]; }
+      }
+    }
     // the backward kernel accumulates dS K with dS unscaled: the softmax scale is applied here
     float v[8] = {lo[0] * scale, lo[1] * scale, lo[2] * scale, lo[3] * scale,
                   hi[0] * scale, hi[1] * scale, hi[2] * scale, hi[3] * scale};
@@ -1545,10 +1572,11 @@ int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, vo
   return check_launch("attn_fwd");
 }
 
-// workspace layout: dq_acc f32 [B,S,Hq,D] | delta f32 [B,Hq,S]
+// workspace layout: dq_acc f32 [B,S,Hq,D] (in the fixed-order mode one such slice per 128-key tile) | delta f32 [B,Hq,S]
 long long eisen_attn_bwd_workspace_bytes(long long B, long long S, long long Hq, long long Hkv, long long D) {
   (void)Hkv;
-  return B * S * Hq * D * 4 + B * Hq * S * 4 + 256;
+  const long long slices = deterministic() ? (S + 127) / 128 : 1;
+  return slices * B * S * Hq * D * 4 + B * Hq * S * 4 + 256;
 }
 
 static int attn_bwd_impl(void* stream, const void* q, const void* k, const void* v, const void* o, const float* lse,
@@ -1567,9 +1595,12 @@ static int attn_bwd_impl(void* stream, const void* q, const void* k, const void*
     return fail(EISEN_ERR_INVALID, "attn_bwd: unaligned pointer");
   cudaStream_t s = (cudaStream_t)stream;
   float* dq_acc = (float*)workspace;
-  float* delta = dq_acc + B * S * Hq * D;
   const long long n_elems = B * S * Hq * D;
-  if (n_elems < 0x7fffffffLL) {
+  const bool det = deterministic();
+  const long long n_kt = (S + 127) / 128;
+  if (det && n_kt * B > 0x7fffffffLL) return fail(EISEN_ERR_LIMIT, "attn_bwd: too many (key tile, batch) slices");
+  float* delta = dq_acc + (det ? n_kt : 1) * n_elems;
+  if (n_elems < 0x7fffffffLL && !det) {
     // delta and the clearing of the dQ accumulation buffer in one pass
     const unsigned nvec = (unsigned)(n_elems / 8);
     const int grid = grid_for((nvec + 1) / 2, 256, 8);
@@ -1580,7 +1611,9 @@ static int attn_bwd_impl(void* stream, const void* q, const void* k, const void*
       attn_prep_kernel<128><<<grid, 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, dq_acc, nvec,
                                                  (unsigned)S, (unsigned)Hq, o_bs, o_ss, o_hs);
   } else {
-    if (cudaMemsetAsync(dq_acc, 0, (size_t)n_elems * 4, s) != cudaSuccess) return fail(EISEN_ERR_CUDA, "attn_bwd: memset failed");
+    // fixed-order mode: every slice element that the conversion reads is written by its key tile, nothing to clear
+    if (!det && cudaMemsetAsync(dq_acc, 0, (size_t)n_elems * 4, s) != cudaSuccess)
+      return fail(EISEN_ERR_CUDA, "attn_bwd: memset failed");
     // total threads is a multiple of 32 (S*H*D/8 with D/8 in {8,16}), so every shuffle group is complete
     if (D == 64)
       attn_delta_kernel<64><<<grid_for(B * S * Hq * 8, 256, 8), 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o,
@@ -1600,7 +1633,7 @@ static int attn_bwd_impl(void* stream, const void* q, const void* k, const void*
     return fail(EISEN_ERR_CUDA, "attn_bwd: cuTensorMapEncodeTiled failed");
   CUtensorMap tdq;
   {
-    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)Hq, (uint64_t)S, (uint64_t)B};
+    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)Hq, (uint64_t)S, (uint64_t)(det ? n_kt * B : B)};  // slices are contiguous
     const uint64_t strides[3] = {(uint64_t)D, (uint64_t)(Hq * D), (uint64_t)(S * Hq * D)};
     const uint32_t box[4] = {32, 1, 128, 1};
     if (make_tmap_f32_nd(&tdq, dq_acc, 4, dims, strides, box)) return fail(EISEN_ERR_CUDA, "attn_bwd: cuTensorMapEncodeTiled failed for dQ");
@@ -1611,6 +1644,8 @@ static int attn_bwd_impl(void* stream, const void* q, const void* k, const void*
   p.lse = const_cast<float*>(lse); p.delta = delta; p.dq_acc = dq_acc;
   p.dk = dk; p.dv = dv; p.kv_bs = kv_bs; p.kv_ss = kv_ss; p.kv_hs = kv_hs;
   p.unrope_tab = reinterpret_cast<const float2*>(unrope_table);
+  p.det = det ? 1 : 0;
+  p.dq_slice = n_elems;
   p.status = status;
   dim3 grid((unsigned)Hkv, (unsigned)B, (unsigned)((S + 127) / 128));
   if (D == 64 && g_attn_bwd_transposed.load()) {
@@ -1636,10 +1671,11 @@ static int attn_bwd_impl(void* stream, const void* q, const void* k, const void*
   if (unrope_table)
     attn_dq_convert_kernel<true><<<grid_for(B * S * Hq * D / 8, 256, 8), 256, 0, s>>>(
         dq_acc, (__nv_bfloat16*)dq, B * S * Hq, (int)S, (int)Hq, (int)D, q_bs, q_ss, q_hs, scale,
-        reinterpret_cast<const float2*>(unrope_table));
+        reinterpret_cast<const float2*>(unrope_table), det ? (int)n_kt : 1, n_elems, causal);
   else
     attn_dq_convert_kernel<false><<<grid_for(B * S * Hq * D / 8, 256, 8), 256, 0, s>>>(
-        dq_acc, (__nv_bfloat16*)dq, B * S * Hq, (int)S, (int)Hq, (int)D, q_bs, q_ss, q_hs, scale, nullptr);
+        dq_acc, (__nv_bfloat16*)dq, B * S * Hq, (int)S, (int)Hq, (int)D, q_bs, q_ss, q_hs, scale, nullptr,
+        det ? (int)n_kt : 1, n_elems, causal);
   return check_launch("attn_dq_convert");
 }
 

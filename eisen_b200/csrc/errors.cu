@@ -10,6 +10,9 @@ namespace eisen {
 
 static thread_local char g_err[512] = "";
 static std::atomic<long long> g_launches{0};
+static std::atomic<int> g_deterministic{0};
+
+bool deterministic() { return g_deterministic.load(std::memory_order_relaxed) != 0; }
 
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
@@ -37,4 +40,9 @@ extern "C" {
 const char* eisen_last_error(void) { return eisen::g_err; }
 const char* eisen_version(void) { return "eisen_b200 0.1 (sm_100a)"; }
 long long eisen_launch_count(void) { return eisen::g_launches.load(); }
+int eisen_set_deterministic(int on) {
+  eisen::g_deterministic.store(on ? 1 : 0);
+  return 0;
+}
+int eisen_get_deterministic(void) { return eisen::g_deterministic.load(); }
 }  // extern "C"

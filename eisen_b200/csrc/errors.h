@@ -23,4 +23,8 @@ inline int device_slot() {
 }
 constexpr int MAX_DEVICE_SLOTS = 64;
 
+// eisen_set_deterministic: kernels whose result depends on the order of floating-point adds (split-K
+// weight gradients, the dQ accumulation of the attention backward) switch to fixed-order forms
+bool deterministic();
+
 }  // namespace eisen

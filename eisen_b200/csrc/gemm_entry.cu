@@ -41,7 +41,7 @@ static int gemm_dispatch(void* stream, int a_mn, int b_mn, long long M, long lon
   const int mode = eisen::g_gemm_mode.load();
   const bool pair = mode == 2 || (mode == 0 && M >= 256 && N >= 128);
   if (split_k == 0) {
-    if (out_mode != eisen::GEMM_OUT_F32_ATOMIC) split_k = 1;
+    if (out_mode != eisen::GEMM_OUT_F32_ATOMIC || eisen::deterministic()) split_k = 1;  // one writer per element
     else split_k = pair ? eisen::gemm_pair_auto_split_k((int)M, (int)N, (int)K) : eisen::gemm_tc_auto_split_k((int)M, (int)N, (int)K);
   }
   const char* err = nullptr;
@@ -109,7 +109,8 @@ int eisen_gemm_bf16_concat_k(void* stream, int a_mn, int b_mn, long long M, long
   if (M > 0x7fffffffLL || N > 0x7fffffffLL || ktotal > 0x7fffffffLL)
     return eisen::fail(EISEN_ERR_LIMIT, "gemm_bf16_concat_k: a dimension exceeds 2^31-1");
   if (split_k == 0)
-    split_k = out_mode == eisen::GEMM_OUT_F32_ATOMIC ? eisen::gemm_pair_auto_split_k((int)M, (int)N, (int)ktotal) : 1;
+    split_k = (out_mode == eisen::GEMM_OUT_F32_ATOMIC && !eisen::deterministic())
+                  ? eisen::gemm_pair_auto_split_k((int)M, (int)N, (int)ktotal) : 1;
   const char* err = nullptr;
   int rc = eisen::gemm_bf16_pair_concat_k((cudaStream_t)stream, a_mn, b_mn, (int)M, (int)N, n_seg, A, lda, B, ldb, k32, C, ldc,
                                           nullptr, 0, out_mode, split_k, alpha, status, &err);

@@ -664,7 +664,7 @@ int gemm_bf16_pair_multi_n(cudaStream_t stream, int a_mn, int b_mn, int M, int K
   p.m_tiles = (M + 2 * PM - 1) / (2 * PM);
   p.n_tiles = n_tiles;
   p.kblocks_total = (K + BK - 1) / BK;
-  if (split_k == 0) split_k = all_atomic ? pair_auto_split(p.m_tiles * n_tiles, p.kblocks_total) : 1;
+  if (split_k == 0) split_k = (all_atomic && !deterministic()) ? pair_auto_split(p.m_tiles * n_tiles, p.kblocks_total) : 1;
   if (split_k > 1 && !all_atomic) {
     if (err) *err = "gemm_bf16_multi_n: split_k > 1 needs the f32 atomic output mode in every segment";
     return 1;

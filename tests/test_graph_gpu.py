@@ -386,6 +386,29 @@ def test_mode_flags_are_restored_when_a_step_fails_midway():
     assert failures >= 3  # the budgets above fail at several different depths
 
 
+def test_bf16_step_is_bit_reproducible_in_fixed_order_mode():
+    """eisen_set_deterministic(1): two fresh graphs running the same checkpointed bf16 step (split weight
+    gradients, fused attention backward, LM head x cross-entropy) produce identical gradient bits."""
+    cfg = dict(vocab=1024, hidden=512, heads=8, kv=2, ffn=1024, layers=2, batch=2, seq=512)
+    ids, tg = _tokens(cfg, 21)
+    tl = tg.reshape(-1).tolist()
+    eb.call("eisen_set_deterministic", 1)
+    try:
+        grads = []
+        for _ in range(2):
+            g = new_graph(BF16_MIXED)
+            lm = TransformerLM(g, cfg["vocab"], cfg["hidden"], cfg["heads"], cfg["kv"], cfg["ffn"], cfg["layers"], False)
+            g.mark_params()
+            x = g.alloc_ids([cfg["batch"], cfg["seq"]], ids.astype(np.int32))
+            loss = lm.train_micro_step(x, tl, checkpoint=True)
+            grads.append([float(g.data(loss)[0])] + [g.grad(p) for p in lm.params()])
+        assert grads[0][0] == grads[1][0]
+        for a, b in zip(grads[0][1:], grads[1][1:]):
+            assert (a.view(np.uint32) == b.view(np.uint32)).all()
+    finally:
+        eb.call("eisen_set_deterministic", 0)
+
+
 def test_adamw_clip_and_fused_step():
     cfg = dict(vocab=128, hidden=64, heads=2, kv=2, ffn=128, layers=1, batch=2, seq=16)
     ids, tg = _tokens(cfg, 5)
