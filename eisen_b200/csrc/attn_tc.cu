@@ -905,7 +905,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO);
-    if (Cfg::DQ_OWN) prefetch_tmap(&tmDQ);
+    prefetch_tmap(&tmDQ);
   }
   if (warp == Cfg::CWARPS + 1) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
   tc_fence_before_sync();
@@ -1071,22 +1071,37 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_base + Cfg::COL_DQ + cq * DQC + lane_off, r);
         tmem_ld_wait();
-        if (qrow < p.S) {
-          if (p.det) {
+        // dQ shares the S columns: they are free for the next S / dP from here on
+        tc_fence_before_sync();
+        mbar_arrive_warp(dq_read);
+        if (p.det) {
+          if (qrow < p.S) {
 #pragma unroll
             for (int i = 0; i < 32; i += 4)
               *reinterpret_cast<uint4*>(dq_row + i) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; i += 4)
-              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + i), "f"(__uint_as_float(r[i])),
-                           "f"(__uint_as_float(r[i + 1])), "f"(__uint_as_float(r[i + 2])), "f"(__uint_as_float(r[i + 3]))
-                           : "memory");
           }
+          return;
         }
+        // The [128 x 128] f32 tile is staged where P and dS lie (64 KB in a row; the products that read
+        // them are complete, dq_full says so, and the next probabilities are a whole S / dP product and
+        // their exponentials away) as four 128-byte-swizzled quarters of 32 columns, and the TMA unit adds
+        // the quarters to the f32 buffer: whole 128-byte rows, clipped at the end of the sequence.  One
+        // red.global of 16-byte pieces of 32 different rows per warp instruction stood here before.
+        const uint32_t quarter = smem_u32(smem + Cfg::OFF_P) + cq * 16384u;
+#pragma unroll
+        for (int jv = 0; jv < 8; ++jv)
+          st_shared_v4(quarter + swz128(row, jv), r[4 * jv], r[4 * jv + 1], r[4 * jv + 2], r[4 * jv + 3]);
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 1, %0;" ::"r"(NCT) : "memory");
+        if (threadIdx.x == 0) {
+          const int qi = i0 + it % per_head;
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            tma_reduce_add_4d(&tmDQ, smem_u32(smem + Cfg::OFF_P) + c * 16384u, c * 32, h, qi * 128, b);
+          tma_store_commit();
+        }
+        return;
       }
-      tc_fence_before_sync();
-      mbar_arrive_warp(dq_read);
     };
 
 
@@ -1243,6 +1258,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         // the products of the query tile before read P / dS from shared memory: dq_full, which
         // the read-out of that tile's dQ waits for, also says that they are done
         if (Cfg::DQ_OWN && it > 0) drain_dq(it - 1);
+        if (!Cfg::DQ_OWN && it > 0 && !p.det) {
+          // D = 128: the TMA unit still may be reading the dQ tile staged over P and dS a query tile ago
+          if (threadIdx.x == 0) {
+            tma_store_wait_read<0>();
+            mbar_arrive(stage_free);
+          }
+          mbar_wait(stage_free, (it - 1) & 1, abort_flag, p.status, FAULT_WAIT_ATTN);
+        }
         store_row_chunk32(sP, row, col0, pk);
         store_row_chunk32(sDS, row, col0, dk);
       }
@@ -1261,6 +1284,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       issue_dq_reduce(iters - 1);
       if (threadIdx.x == 0) tma_store_wait<0>();  // the staging tile and the adds outlive nothing
     }
+    if (!Cfg::DQ_OWN && iters > 0 && !p.det && threadIdx.x == 0) tma_store_wait<0>();  // the staged tile outlives nothing
     // dK / dV of this key tile: TMEM -> bf16 -> global (the last dq_full wait covers them)
     if (iters > 0) {
       tc_fence_after_sync();
