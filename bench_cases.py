@@ -309,6 +309,7 @@ def main():
     ap.add_argument("--gemm-mode", type=int, default=-1, help="eisen_gemm_set_mode value (default: leave as is)")
     ap.add_argument("--fwd-tiles", type=int, default=0, help="eisen_attn_set_fwd_tiles value (default: leave as is)")
     ap.add_argument("--bwd-mode", type=int, default=-1, help="eisen_attn_set_bwd_mode value (default: leave as is)")
+    ap.add_argument("--rms-bwd-mode", type=int, default=-1, help="eisen_rmsnorm_bwd_set_mode value (default: leave as is)")
     ap.add_argument("--batch", type=int, default=2)
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=8)
@@ -327,6 +328,8 @@ def main():
         eb.call("eisen_attn_set_fwd_tiles", a.fwd_tiles)
     if a.bwd_mode >= 0:
         eb.call("eisen_attn_set_bwd_mode", a.bwd_mode)
+    if a.rms_bwd_mode >= 0:
+        eb.call("eisen_rmsnorm_bwd_set_mode", a.rms_bwd_mode)
     if a.case == "gemm":
         out = case_gemm(a.m, a.n, a.k, a.a_mn, a.b_mn, a.out_mode, a.split_k, a.iters, a.sets)
     elif a.case == "gemm_swiglu":

@@ -219,9 +219,9 @@ int eisen_rmsnorm_fwd(void* stream, const void* x, const float* w, void* y, floa
 int eisen_rmsnorm_fwd_set_mode(int staged);
 long long eisen_rmsnorm_bwd_workspace_bytes(long long rows, long long dim);
 /* Kernel of eisen_rmsnorm_bwd where several apply: 0 = CTA-wide kernel with the rows in registers,
- * 1 = warp per row, 2 / 3 / 4 = rows staged in shared memory by bulk asynchronous copies (4 rows x 3
- * stages, 2 rows x 4 stages, 2 rows x 3 stages per CTA; rows of exactly 256 16-byte vectors).
- * Process-wide; meant for tests and measurements. */
+ * 1 = warp per row, 2 (default) / 3 / 4 / 5 = rows staged in shared memory by bulk asynchronous copies
+ * (4 rows x 3 stages, 2 x 4, 2 x 3, 4 x 2 per CTA; rows of exactly 256 16-byte vectors), 6 = as 2 with
+ * two columns per arithmetic instruction (packed f32x2; measured slower).  Process-wide; meant for tests and measurements. */
 int eisen_rmsnorm_bwd_set_mode(int mode);
 /* dx (op)= ..., dw (f32) += ...  Replaces rmsnorm_backward_f32 and its bf16 variants
  * (kernels/ops_f32.cu:553-578; src/graph/ops/normalization.rs:122). */

@@ -609,7 +609,7 @@ def test_rmsnorm_f32_vs_oracle(rows, dim):
     assert rel_l2(dw.cpu().numpy(), 2 * og.grad(ow)) < 1e-5
 
 
-@pytest.mark.parametrize("mode,rows", [(2, 300), (0, 300), (1, 300), (2, 5), (2, 2052), (3, 304), (4, 304), (5, 304)])
+@pytest.mark.parametrize("mode,rows", [(2, 300), (0, 300), (1, 300), (2, 5), (2, 2052), (3, 304), (4, 304), (5, 304), (6, 304)])
 def test_rmsnorm_bf16(mode, rows):
     """Forward and every backward kernel (0: rows in registers, 1: warp per row, 2-5: rows staged in
     shared memory by bulk copies; 5 rows fall back to the register kernel) against f32 autograd."""
