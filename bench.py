@@ -34,7 +34,7 @@ CONFIGS = {
                             accum=1, checkpoint=True, tie=False),
     # BASELINE.json configs[1]: ~14M-parameter model, batch 32 x 256, gradient accumulation 2
     "llama-14m": dict(vocab=8192, hidden=384, layers=6, heads=6, kv=6, ffn=1024, batch=32, seq=256, accum=2,
-                      checkpoint=False, tie=False),
+                      checkpoint=False, tie=False, overlap_optimizer=False),  # its step is also replayed from a CUDA graph
     # BASELINE.json configs[0]: the CPU-runnable tiny f32 model, one step of batch 4 x 64
     "tiny-f32": dict(vocab=512, hidden=128, layers=2, heads=4, kv=4, ffn=384, batch=4, seq=64, accum=1,
                      checkpoint=False, tie=False, f32=True),
@@ -257,6 +257,13 @@ class Runner:
         self.n_params = sum(int(np.prod(g.shape(p))) for p in self.params)
         self.reducer = None
         self.sharded = False
+        self.overlapped = False
+        if world == 1 and not cfg.get("f32") and getattr(args, "optimizer_overlap", False) and cfg.get("overlap_optimizer", True):
+            # the update of step t runs on a side stream beside the forward pass of step t + 1
+            from eisen_b200.overlap import OverlappedAdamW
+            self.opt = OverlappedAdamW(g, lm, self.params, 3e-4, cfg["layers"], compute)
+            self.opt.config(3e-4, 0.9, 0.95, 1e-8, 0.1)
+            self.overlapped = True
         if world > 1:
             import torch.distributed as dist
             wptr, sptr, gptr, n_arena = g.param_arena()
@@ -348,6 +355,8 @@ class Runner:
         e0.record(self.compute)
         for it in range(steps):
             self.step(e2e, it)
+        if self.overlapped:
+            self.opt.finish()  # the last step's update runs on the side stream: it belongs to the timed region
         e1.record(self.compute)
         torch.cuda.synchronize()
         if self.world > 1:
@@ -358,6 +367,8 @@ class Runner:
         return float(ms.item())
 
     def close(self):
+        if self.overlapped:
+            self.opt.close()
         if self.sharded:
             self.reducer.wait_all(self.compute)
             self.lm.set_forward_hook(None)
@@ -568,7 +579,9 @@ def run_ours(args, cfg, name):
                        "gradient_checkpointing": "per-block" if r.checkpoint else "off", "grad_clip_norm": r.clip,
                        "l2": "inputs larger than L2 (weights, activations and logits far exceed 126 MB)",
                        "bucket_mb": args.bucket_mb if world > 1 else None,
-                       "exchange": (args.exchange + " via " + ("eisen_dp_* (NCCL)" if args.backend == "abi" else "torch.distributed")) if world > 1 else None},
+                       "exchange": (args.exchange + " via " + ("eisen_dp_* (NCCL)" if args.backend == "abi" else "torch.distributed")) if world > 1 else None,
+                       "optimizer": ("AdamW pieces on a side stream beside the next step's forward pass; every timed step "
+                                     "contains one full update" if r.overlapped else "AdamW on the compute stream")},
             "mfu": {"model_flops_per_token": fpt,
                     "of_nominal_2250_tflops": tps / world * fpt / (NOMINAL_BF16_TFLOPS * 1e12),
                     "of_measured_burst": tps / world * fpt / (float(peaks.get("bf16_tflops", 1590.0)) * 1e12),
@@ -637,6 +650,9 @@ def main():
     ap.add_argument("--no-variants", action="store_true", help="skip the kept-attention-output variant")
     ap.add_argument("--no-cases", action="store_true", help="skip the other benchmark configurations (N = 1 only)")
     ap.add_argument("--bucket-mb", type=int, default=256)
+    ap.add_argument("--optimizer-overlap", action="store_true",
+                    help="1 GPU: run AdamW block by block on a side stream beside the next step's forward pass "
+                         "(eisen_b200.overlap.OverlappedAdamW; measured no faster: the step is power-limited)")
     ap.add_argument("--no-gather-overlap", action="store_true",
                     help="zero1: wait for the whole weight all-gather after the optimizer instead of per block in the next forward")
     ap.add_argument("--exchange", default="zero1", choices=["allreduce", "zero1"],

@@ -418,6 +418,11 @@ int eisen_optim_sumsq_piece(void* opt, int piece, int accumulate, void* stream) 
 int eisen_optim_step_piece(void* opt, int piece, float max_norm, float grad_scale) {
   return guarded([&] { static_cast<AdamW*>(opt)->step_piece((size_t)piece, max_norm, grad_scale); });
 }
+int eisen_optim_step_piece_on(void* opt, int piece, float max_norm, float grad_scale, void* stream, int zero_grads) {
+  return guarded([&] {
+    static_cast<AdamW*>(opt)->step_piece((size_t)piece, max_norm, grad_scale, (cudaStream_t)stream, zero_grads != 0);
+  });
+}
 int eisen_optim_sumsq_ptr(void* opt, void** out) {
   return guarded([&] { *out = static_cast<AdamW*>(opt)->sumsq_dev; });
 }

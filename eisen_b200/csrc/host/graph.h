@@ -327,7 +327,7 @@ class AdamW {
   AdamW(Graph& g, std::vector<int64_t> params, float lr, std::vector<std::pair<int64_t, int64_t>> pieces);
   void begin_step() { t += 1; }                       // once per optimizer step, before step_piece
   void sumsq_piece(size_t i, bool accumulate, cudaStream_t s);   // sumsq_dev (op)= sum g^2 over piece i
-  void step_piece(size_t i, float max_norm, float grad_scale);   // clip coefficient from sumsq_dev when max_norm > 0
+  void step_piece(size_t i, float max_norm, float grad_scale, cudaStream_t s = nullptr, bool zero_grads = false);   // clip coefficient from sumsq_dev when max_norm > 0
   // Optimizer state of a checkpoint (the reference saves weights only and lists this as future
   // work, README.md:88): step count t, hyper-parameters and the moments of the ranges this object owns.
   void save_state(const char* path);

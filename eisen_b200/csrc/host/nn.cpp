@@ -557,7 +557,7 @@ void AdamW::sumsq_piece(size_t i, bool accumulate, cudaStream_t s) {
   ck(eisen_sumsq(s, g.arena_g + pc.first, pc.second - pc.first, sumsq_ws, sumsq_dev, accumulate ? 1 : 0), "sumsq(piece)");
 }
 
-void AdamW::step_piece(size_t i, float max_norm, float grad_scale) {
+void AdamW::step_piece(size_t i, float max_norm, float grad_scale, cudaStream_t s, bool zero_grads) {
   const auto& pc = pieces.at(i);
   if (pc.second == pc.first) return;
   float p1 = 1.0f, p2 = 1.0f;
@@ -565,8 +565,9 @@ void AdamW::step_piece(size_t i, float max_norm, float grad_scale) {
   const float bc1 = 1.0f / (1.0f - p1), bc2 = 1.0f / (1.0f - p2);
   const int64_t so = piece_state_off[i];
   void* shadow = g.arena_shadow ? (void*)((uint16_t*)g.arena_shadow + pc.first) : nullptr;
-  ck(eisen_adamw_step(g.stream, g.arena_w + pc.first, shadow, g.arena_g + pc.first, m + so, v + so, pc.second - pc.first, lr,
-                      beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale, max_norm > 0.0f ? sumsq_dev : nullptr, max_norm),
+  ck(eisen_adamw_step_ex(s ? s : g.stream, g.arena_w + pc.first, shadow, g.arena_g + pc.first, m + so, v + so,
+                         pc.second - pc.first, lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale,
+                         max_norm > 0.0f ? sumsq_dev : nullptr, max_norm, nullptr, zero_grads ? 1 : 0),
      "adamw_step(piece)");
 }
 

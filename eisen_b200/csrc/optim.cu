@@ -29,8 +29,11 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// ZERO_G: the gradient is cleared as it is read, so that no separate memset stands between this step and
+// the next backward pass
+template <bool ZERO_G>
 __global__ void __launch_bounds__(OPT_THREADS)
-adamw_kernel(float* __restrict__ w, __nv_bfloat16* __restrict__ w_bf16, const float* __restrict__ g,
+adamw_kernel(float* __restrict__ w, __nv_bfloat16* __restrict__ w_bf16, float* __restrict__ g,
              float* __restrict__ m, float* __restrict__ v, long long n, float lr, float b1, float b2, float eps,
              float wd, float bc1, float bc2, float grad_scale, const double* __restrict__ sumsq,
              float max_norm, const float* __restrict__ hyper) {
@@ -56,6 +59,7 @@ adamw_kernel(float* __restrict__ w, __nv_bfloat16* __restrict__ w_bf16, const fl
     reinterpret_cast<float4*>(w)[i] = w4;
     reinterpret_cast<float4*>(m)[i] = m4;
     reinterpret_cast<float4*>(v)[i] = v4;
+    if (ZERO_G) reinterpret_cast<float4*>(g)[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     if (w_bf16) {
       uint2 o;
       o.x = pack2(w4.x, w4.y);
@@ -69,6 +73,7 @@ adamw_kernel(float* __restrict__ w, __nv_bfloat16* __restrict__ w_bf16, const fl
     float ww = w[i], mm = m[i], vv = v[i];
     adamw_one(ww, g[i] * gs, mm, vv, lr, b1, b2, eps, wd, bc1, bc2);
     w[i] = ww; m[i] = mm; v[i] = vv;
+    if (ZERO_G) g[i] = 0.0f;
     if (w_bf16) w_bf16[i] = __float2bfloat16(ww);
   }
 }
@@ -134,13 +139,24 @@ int eisen_adamw_step(void* stream, float* w, void* w_bf16, const float* g, float
 int eisen_adamw_step_dev(void* stream, float* w, void* w_bf16, const float* g, float* m, float* v, long long n,
                          float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2,
                          float grad_scale, const double* sumsq, float max_norm, const float* hyper) {
+  return eisen_adamw_step_ex(stream, w, w_bf16, const_cast<float*>(g), m, v, n, lr, beta1, beta2, eps, weight_decay, bc1, bc2,
+                             grad_scale, sumsq, max_norm, hyper, 0);
+}
+
+// As eisen_adamw_step_dev; zero_grad != 0 clears g while it is read.
+int eisen_adamw_step_ex(void* stream, float* w, void* w_bf16, float* g, float* m, float* v, long long n, float lr,
+                        float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2, float grad_scale,
+                        const double* sumsq, float max_norm, const float* hyper, int zero_grad) {
   if (n <= 0) return 0;
   if (!aligned16(w) || !aligned16(g) || !aligned16(m) || !aligned16(v) || (w_bf16 && (reinterpret_cast<uintptr_t>(w_bf16) & 7)))
     return fail(EISEN_ERR_INVALID, "adamw_step: buffers must be 16-byte aligned");
   const int grid = grid_for(n >> 2, OPT_THREADS, 8);
-  adamw_kernel<<<grid, OPT_THREADS, 0, (cudaStream_t)stream>>>(w, (__nv_bfloat16*)w_bf16, g, m, v, n, lr, beta1,
-                                                              beta2, eps, weight_decay, bc1, bc2, grad_scale,
-                                                              sumsq, max_norm, hyper);
+  if (zero_grad)
+    adamw_kernel<true><<<grid, OPT_THREADS, 0, (cudaStream_t)stream>>>(w, (__nv_bfloat16*)w_bf16, g, m, v, n, lr, beta1, beta2, eps,
+                                                                      weight_decay, bc1, bc2, grad_scale, sumsq, max_norm, hyper);
+  else
+    adamw_kernel<false><<<grid, OPT_THREADS, 0, (cudaStream_t)stream>>>(w, (__nv_bfloat16*)w_bf16, g, m, v, n, lr, beta1, beta2, eps,
+                                                                       weight_decay, bc1, bc2, grad_scale, sumsq, max_norm, hyper);
   return check_launch("adamw_step");
 }
 

@@ -450,3 +450,8 @@ class ShardedAdamW(AdamW):
 
     def step_piece(self, i, max_norm=0.0, grad_scale=1.0):
         call("eisen_optim_step_piece", self._h, i, max_norm, grad_scale)
+
+    def step_piece_on(self, i, max_norm=0.0, grad_scale=1.0, stream=None, zero_grads=False):
+        """step_piece on `stream` (a torch stream; None: the graph's), optionally clearing the piece's gradients."""
+        call("eisen_optim_step_piece_on", self._h, i, max_norm, grad_scale, stream.cuda_stream if stream is not None else None,
+             1 if zero_grads else 0)

@@ -351,6 +351,11 @@ int eisen_adamw_step(void* stream, float* w, void* w_bf16, const float* g, float
 int eisen_adamw_step_dev(void* stream, float* w, void* w_bf16, const float* g, float* m, float* v, long long n,
                          float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2,
                          float grad_scale, const double* sumsq, float max_norm, const float* hyper);
+/* eisen_adamw_step_dev that also clears the gradient as it reads it (zero_grad != 0), which stands for the
+ * `zero_grad` memset of the next step (src/nn/optim.rs zero_grad) at no extra pass over memory. */
+int eisen_adamw_step_ex(void* stream, float* w, void* w_bf16, float* g, float* m, float* v, long long n, float lr,
+                        float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2, float grad_scale,
+                        const double* sumsq, float max_norm, const float* hyper, int zero_grad);
 long long eisen_sumsq_workspace_bytes(long long n);
 /* *out (device f64) (op)= sum x^2 — the device-side half of AdamW::clip_grad_norm
  * (src/nn/optim.rs:250-281 copies every gradient to the host instead). */
@@ -571,6 +576,11 @@ int eisen_optim_create_sharded(void* g, const long long* params, int n, float lr
 int eisen_optim_begin_step(void* opt);
 int eisen_optim_sumsq_piece(void* opt, int piece, int accumulate, void* stream); /* stream null: the graph's */
 int eisen_optim_step_piece(void* opt, int piece, float max_norm, float grad_scale);
+/* eisen_optim_step_piece on a stream of the caller's choice (null: the graph's), optionally clearing the
+ * piece's gradients as they are read.  With the pieces cut at block boundaries and launched in forward order
+ * on a side stream, the update of step t runs beside the forward pass of step t + 1, which waits (an event
+ * per piece, from the model's forward hook) only for the block it is about to read. */
+int eisen_optim_step_piece_on(void* opt, int piece, float max_norm, float grad_scale, void* stream, int zero_grads);
 int eisen_optim_sumsq_ptr(void* opt, void** out);
 
 /* ------------------------------------------------------------------------------------------

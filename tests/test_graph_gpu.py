@@ -409,6 +409,53 @@ def test_bf16_step_is_bit_reproducible_in_fixed_order_mode():
         eb.call("eisen_set_deterministic", 0)
 
 
+def test_overlapped_adamw_equals_adamw():
+    """eisen_b200.overlap.OverlappedAdamW (update on a side stream, block by block, beside the next forward
+    pass; gradients cleared by the update itself) against the plain fused AdamW over three checkpointed bf16
+    steps with gradient clipping: identical weights (fixed-order mode, so that the gradients are identical)."""
+    from eisen_b200.overlap import OverlappedAdamW
+    cfg = dict(vocab=1024, hidden=256, heads=4, kv=2, ffn=512, layers=3, batch=2, seq=256)
+    rng = np.random.default_rng(31)
+    batches = [(rng.integers(0, cfg["vocab"], (cfg["batch"], cfg["seq"])).astype(np.int32),
+                rng.integers(0, cfg["vocab"], cfg["batch"] * cfg["seq"]).tolist()) for _ in range(3)]
+    eb.call("eisen_set_deterministic", 1)
+    try:
+        finals = []
+        for overlapped in (False, True):
+            compute = torch.cuda.Stream()
+            with torch.cuda.stream(compute):
+                g = Graph(BF16_MIXED, compute.cuda_stream)
+                lm = TransformerLM(g, cfg["vocab"], cfg["hidden"], cfg["heads"], cfg["kv"], cfg["ffn"], cfg["layers"], False)
+                g.mark_params()
+                ps = lm.params()
+                if overlapped:
+                    opt = OverlappedAdamW(g, lm, ps, 1e-3, cfg["layers"], compute)
+                else:
+                    opt = AdamW(g, ps, 1e-3)
+                opt.config(1e-3, 0.9, 0.95, 1e-8, 0.1)
+                losses = []
+                for ids, tg in batches:
+                    opt.zero_grad()
+                    x = g.alloc_ids([cfg["batch"], cfg["seq"]], ids)
+                    loss = lm.train_micro_step(x, tg, checkpoint=True)
+                    losses.append(float(g.data(loss)[0]))
+                    g.clear_activations()
+                    opt.step_fused(0.5, 1.0)
+                if overlapped:
+                    opt.close()
+                g.synchronize()
+                finals.append((losses, [g.data(p) for p in ps], [g.grad(p) for p in ps]))
+        assert finals[0][0] == finals[1][0]
+        assert finals[0][0][2] < finals[0][0][0] + 1.0
+        for a, b in zip(finals[0][1], finals[1][1]):
+            assert (a.view(np.uint32) == b.view(np.uint32)).all()
+        # the overlapped update leaves the gradients cleared; the plain one leaves them as the backward pass wrote them
+        assert all((gr == 0).all() for gr in finals[1][2])
+        assert any((gr != 0).any() for gr in finals[0][2])
+    finally:
+        eb.call("eisen_set_deterministic", 0)
+
+
 def test_adamw_clip_and_fused_step():
     cfg = dict(vocab=128, hidden=64, heads=2, kv=2, ffn=128, layers=1, batch=2, seq=16)
     ids, tg = _tokens(cfg, 5)
