@@ -540,6 +540,17 @@ def run_ours(args, cfg, name):
         ms_keep = r.timed(False, args.steps)
         r.lm.set_keep_attention(False)
         g.synchronize()
+    # ---- variant: no recomputation at all (every block's activations are kept: about 1 GB per block here)
+    ms_plain = None
+    if r.checkpoint and world == 1 and not args.no_variants:
+        r.checkpoint = False
+        try:
+            for it in range(2):
+                r.step(False, it)
+            ms_plain = r.timed(False, min(args.steps, 3)) / min(args.steps, 3)
+        finally:
+            r.checkpoint = True
+        g.synchronize()
     # ---- variant: fixed-order arithmetic (one slice per weight-gradient tile, dQ summed in key order):
     # gradients are bit-identical from run to run
     ms_det = None
@@ -604,6 +615,12 @@ def run_ours(args, cfg, name):
                         "forward pass and recomputes the rest of the block (`value` recomputes the whole block)",
                 "ms_per_step": ms_keep / args.steps, "tokens_per_s": step_tokens * args.steps / (ms_keep / 1e3),
                 "mfu_of_nominal_2250_tflops": step_tokens * args.steps / (ms_keep / 1e3) / world * fpt / (NOMINAL_BF16_TFLOPS * 1e12)}}
+        if ms_plain is not None:
+            out.setdefault("variants", {})["no_checkpointing"] = {
+                "what": "the same step without recomputation (activations of all blocks kept, about 16 GB at this batch): what the "
+                        "step costs when memory, not the benchmark's configuration, decides; `value` recomputes every block",
+                "ms_per_step": ms_plain, "tokens_per_s": step_tokens / (ms_plain / 1e3),
+                "mfu_of_nominal_2250_tflops": step_tokens / (ms_plain / 1e3) / world * fpt / (NOMINAL_BF16_TFLOPS * 1e12)}
         if ms_det is not None:
             out.setdefault("variants", {})["fixed_order_arithmetic"] = {
                 "what": "eisen_set_deterministic(1): weight-gradient GEMMs with one slice per tile, attention dQ written per key "
