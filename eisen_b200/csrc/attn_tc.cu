@@ -43,6 +43,13 @@ struct AttnParams {
   float scale;
   // outputs / side inputs (element strides)
   void* o; long long o_bs, o_ss, o_hs;
+  // forward, may be null: bf16 tensor with O's strides that receives the part of the f32 output that the
+  // rounding of O drops (o_lo = bf16(o_f32 - float(bf16(o_f32)))); the backward forms delta = dO . (O + O_lo)
+  void* o_lo;
+  // forward, may be null: f32 [B, Hkv, D] vector that was subtracted from every value row before the call
+  // (eisen_attn_center_values).  The output gets it added back, and o_lo then receives the output
+  // before the addition, bf16(sum_j P_ij (V_j - mean)), the tensor the backward pass forms delta from.
+  const float* v_mean;
   float* lse;        // [B, Hq, S]
   const float* delta;  // [B, Hq, S]
   float* dq_acc;     // [B, S, Hq, D] f32
@@ -59,6 +66,40 @@ struct AttnParams {
 
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// the bf16 pair that the rounding of (a, b) to bf16 drops
+__device__ __forceinline__ uint32_t pack_bf16x2_lo(float a, float b) {
+  const float ha = __bfloat162float(__float2bfloat16_rn(a)), hb = __bfloat162float(__float2bfloat16_rn(b));
+  return pack_bf16x2(a - ha, b - hb);
+}
+
+// Eight output columns of one row.  Plain: out = bf16(x).  With `aux`: the part the rounding drops goes
+// there as well.  With `mean` (the vector the values were centred by): out = bf16(x + mean) and aux, if
+// given, receives bf16(x), the centred output.
+__device__ __forceinline__ void store_out8(__nv_bfloat16* out, __nv_bfloat16* aux, const float* mean, const float (&x)[8]) {
+  float y[8];
+  if (mean) {
+    const float4 m0 = *reinterpret_cast<const float4*>(mean), m1 = *reinterpret_cast<const float4*>(mean + 4);
+    const float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = x[e] + mm[e];
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = x[e];
+  }
+  uint4 o;
+  o.x = pack_bf16x2(y[0], y[1]); o.y = pack_bf16x2(y[2], y[3]); o.z = pack_bf16x2(y[4], y[5]); o.w = pack_bf16x2(y[6], y[7]);
+  *reinterpret_cast<uint4*>(out) = o;
+  if (aux) {
+    uint4 a;
+    if (mean) {
+      a.x = pack_bf16x2(x[0], x[1]); a.y = pack_bf16x2(x[2], x[3]); a.z = pack_bf16x2(x[4], x[5]); a.w = pack_bf16x2(x[6], x[7]);
+    } else {
+      a.x = pack_bf16x2_lo(x[0], x[1]); a.y = pack_bf16x2_lo(x[2], x[3]); a.z = pack_bf16x2_lo(x[4], x[5]); a.w = pack_bf16x2_lo(x[6], x[7]);
+    }
+    *reinterpret_cast<uint4*>(aux) = a;
+  }
 }
 
 // writes 32 consecutive bf16 of row `row` starting at column `col0` (multiple of 32) into a
@@ -412,14 +453,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
         __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + (long long)b * p.o_bs + (long long)qrow * p.o_ss +
                               (long long)h * p.o_hs + part * DW;
+        __nv_bfloat16* lrow = p.o_lo ? reinterpret_cast<__nv_bfloat16*>(p.o_lo) + (orow - reinterpret_cast<__nv_bfloat16*>(p.o)) : nullptr;
+        const float* mrow = (p.v_mean && l > 0.0f) ? p.v_mean + ((long long)b * p.Hkv + kvh) * D + part * DW : nullptr;
 #pragma unroll
         for (int c = 0; c < DW / 8; ++c) {
-          uint4 o;
-          o.x = pack_bf16x2(acc[c * 8 + 0] * inv, acc[c * 8 + 1] * inv);
-          o.y = pack_bf16x2(acc[c * 8 + 2] * inv, acc[c * 8 + 3] * inv);
-          o.z = pack_bf16x2(acc[c * 8 + 4] * inv, acc[c * 8 + 5] * inv);
-          o.w = pack_bf16x2(acc[c * 8 + 6] * inv, acc[c * 8 + 7] * inv);
-          reinterpret_cast<uint4*>(orow)[c] = o;
+          float x[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) x[e] = acc[c * 8 + e] * inv;
+          store_out8(orow + c * 8, lrow ? lrow + c * 8 : nullptr, mrow ? mrow + c * 8 : nullptr, x);
         }
         if (p.lse && part == 0) p.lse[((long long)b * p.Hq + h) * p.S + qrow] = (l > 0.0f) ? m * p.scale + logf(l) : -INFINITY;
       }
@@ -784,14 +825,14 @@ attn_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
         __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + (long long)b * p.o_bs + (long long)qrow * p.o_ss +
                               (long long)h * p.o_hs + part * 32;
+        __nv_bfloat16* lrow = p.o_lo ? reinterpret_cast<__nv_bfloat16*>(p.o_lo) + (orow - reinterpret_cast<__nv_bfloat16*>(p.o)) : nullptr;
+        const float* mrow = (p.v_mean && l > 0.0f) ? p.v_mean + ((long long)b * p.Hkv + kvh) * D + part * 32 : nullptr;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          uint4 o;
-          o.x = pack_bf16x2(__uint_as_float(ro[c * 8 + 0]) * inv, __uint_as_float(ro[c * 8 + 1]) * inv);
-          o.y = pack_bf16x2(__uint_as_float(ro[c * 8 + 2]) * inv, __uint_as_float(ro[c * 8 + 3]) * inv);
-          o.z = pack_bf16x2(__uint_as_float(ro[c * 8 + 4]) * inv, __uint_as_float(ro[c * 8 + 5]) * inv);
-          o.w = pack_bf16x2(__uint_as_float(ro[c * 8 + 6]) * inv, __uint_as_float(ro[c * 8 + 7]) * inv);
-          reinterpret_cast<uint4*>(orow)[c] = o;
+          float x[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(ro[c * 8 + e]) * inv;
+          store_out8(orow + c * 8, lrow ? lrow + c * 8 : nullptr, mrow ? mrow + c * 8 : nullptr, x);
         }
         if (p.lse && part == 0)
           p.lse[((long long)b * p.Hq + h) * p.S + qrow] = (l > 0.0f) ? m_used * p.scale + logf(l) : -INFINITY;
@@ -1362,7 +1403,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 // delta[b,h,s] = sum_d o[b,s,h,d] * do[b,s,h,d]; D/8 lanes per (b,s,h) row, 16 bytes per lane
 template <int D>
 __global__ void __launch_bounds__(256)
-attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
+attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ o_lo,
+                  const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
                   int B, int S, int H, long long bs, long long ss, long long hs) {
   constexpr int LPR = D / 8;  // lanes per row (8 or 16)
   const long long total = (long long)B * S * H;
@@ -1383,6 +1425,12 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
       float x[8], y[8];
       ld16(o + off, x);
       ld16(d_o + off, y);
+      if (o_lo) {
+        float xl[8];
+        ld16(o_lo + off, xl);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) x[k] += xl[k];
+      }
 #pragma unroll
       for (int k = 0; k < 8; ++k) acc += x[k] * y[k];
     }
@@ -1399,7 +1447,8 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
 // LPR lanes always sit in one warp and are valid together (LPR divides 32 and the row count is whole).
 template <int D>
 __global__ void __launch_bounds__(256)
-attn_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
+attn_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ o_lo,
+                 const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
                  float* __restrict__ dq_acc, unsigned nvec, unsigned S, unsigned H, long long bs, long long ss, long long hs) {
   constexpr unsigned LPR = D / 8;  // lanes per (b,s,h) row
   const unsigned stride = gridDim.x * blockDim.x;
@@ -1425,6 +1474,13 @@ attn_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __res
     float x0[8], y0[8], x1[8], y1[8];
     ld16(o + off[0], x0); ld16(d_o + off[0], y0);
     ld16(o + off[1], x1); ld16(d_o + off[1], y1);
+    if (o_lo) {  // the part of the forward's f32 output that its rounding to bf16 dropped
+      float l0[8], l1[8];
+      ld16(o_lo + off[0], l0);
+      ld16(o_lo + off[1], l1);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { x0[k] += l0[k]; x1[k] += l1[k]; }
+    }
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       if (valid[u]) {
@@ -1500,6 +1556,58 @@ attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict_
   }
 }
 
+// mean[b, h, :] = mean over s of v[b, s, h, :]; one CTA per (b, h), f32 sums in a fixed order
+__global__ void __launch_bounds__(256)
+attn_value_mean_kernel(const __nv_bfloat16* __restrict__ v, float* __restrict__ mean, int S, int H, int D, long long bs,
+                       long long ss, long long hs) {
+  __shared__ float sh[8][128];
+  const int b = blockIdx.x / H, h = blockIdx.x % H;
+  const int per_row = D / 8;                 // 16-byte vectors per row: 8 or 16
+  const int rows_per_pass = 256 / per_row;   // 32 or 16 rows at a time
+  const int c = (threadIdx.x % per_row) * 8, r0 = threadIdx.x / per_row;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const __nv_bfloat16* base = v + (long long)b * bs + (long long)h * hs + c;
+  for (int s = r0; s < S; s += rows_per_pass) {
+    float x[8];
+    ld16(base + (long long)s * ss, x);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] += x[e];
+  }
+  // threads with the same column chunk sit per_row apart: reduce them through shared memory in a fixed order
+  float* slot = &sh[0][0];
+  for (int e = 0; e < 8; ++e) {
+    __syncthreads();
+    slot[threadIdx.x] = acc[e];
+    __syncthreads();
+    if (threadIdx.x < per_row) {
+      float t = 0.0f;
+      for (int r = 0; r < rows_per_pass; ++r) t += slot[r * per_row + threadIdx.x];
+      mean[((long long)b * H + h) * D + threadIdx.x * 8 + e] = t / (float)S;
+    }
+  }
+}
+
+// vc[b, s, h, :] = bf16(v[b, s, h, :] - mean[b, h, :]) (vc contiguous [B, S, H, D])
+__global__ void __launch_bounds__(256)
+attn_value_center_kernel(const __nv_bfloat16* __restrict__ v, const float* __restrict__ mean, __nv_bfloat16* __restrict__ vc,
+                         long long rows /*B*S*H*/, int S, int H, int D, long long bs, long long ss, long long hs) {
+  const int per_row = D / 8;
+  const long long total = rows * per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / per_row;
+    const int c = (int)(i % per_row) * 8;
+    const int h = (int)(r % H);
+    const int s = (int)((r / H) % S);
+    const long long b = r / ((long long)H * S);
+    float x[8];
+    ld16(v + b * bs + (long long)s * ss + (long long)h * hs + c, x);
+    const float* m = mean + (b * H + h) * D + c;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] -= m[e];
+    st16(vc + r * D + c, x);
+  }
+}
+
 int make_qkv_tmap(CUtensorMap* tm, const void* base, int B, int S, int H, int D, long long bs, long long ss,
                   long long hs) {
   const uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)S, (uint64_t)B};
@@ -1537,14 +1645,15 @@ int eisen_attn_set_fwd_tiles(int tiles) {
   return 0;
 }
 
-int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, void* o, float* lse, long long B,
-                   long long S, long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss,
-                   long long q_hs, long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs,
-                   long long o_ss, long long o_hs, float scale, int causal, int* status) {
+static int attn_fwd_impl(void* stream, const void* q, const void* k, const void* v, void* o, void* o_lo,
+                         const float* v_mean, float* lse, long long B, long long S, long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss,
+                         long long q_hs, long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs,
+                         long long o_ss, long long o_hs, float scale, int causal, int* status) {
   const long long st[9] = {q_bs, q_ss, q_hs, kv_bs, kv_ss, kv_hs, o_bs, o_ss, o_hs};
   int rc = check_args(B, S, Hq, Hkv, D, st, 9);
   if (rc) return rc;
-  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return fail(EISEN_ERR_INVALID, "attn_fwd: unaligned pointer");
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(o_lo))
+    return fail(EISEN_ERR_INVALID, "attn_fwd: unaligned pointer");
   CUtensorMap tq, tk, tv;
   if (make_qkv_tmap(&tq, q, (int)B, (int)S, (int)Hq, (int)D, q_bs, q_ss, q_hs) ||
       make_qkv_tmap(&tk, k, (int)B, (int)S, (int)Hkv, (int)D, kv_bs, kv_ss, kv_hs) ||
@@ -1554,6 +1663,8 @@ int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, vo
   p.B = (int)B; p.S = (int)S; p.Hq = (int)Hq; p.Hkv = (int)Hkv; p.D = (int)D;
   p.causal = causal; p.scale = scale;
   p.o = o; p.o_bs = o_bs; p.o_ss = o_ss; p.o_hs = o_hs;
+  p.o_lo = o_lo;
+  p.v_mean = v_mean;
   p.lse = lse; p.status = status;
   dim3 grid((unsigned)Hq, (unsigned)B, (unsigned)(((S + 127) / 128 + 1) / 2));  // two query tiles per CTA
   cudaStream_t s = (cudaStream_t)stream;
@@ -1596,6 +1707,40 @@ int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, vo
   return check_launch("attn_fwd");
 }
 
+int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, void* o, float* lse, long long B,
+                   long long S, long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss,
+                   long long q_hs, long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs,
+                   long long o_ss, long long o_hs, float scale, int causal, int* status) {
+  return attn_fwd_impl(stream, q, k, v, o, nullptr, nullptr, lse, B, S, Hq, Hkv, D, q_bs, q_ss, q_hs, kv_bs, kv_ss, kv_hs, o_bs,
+                       o_ss, o_hs, scale, causal, status);
+}
+
+int eisen_attn_fwd_ex(void* stream, const void* q, const void* k, const void* v, void* o, void* o_aux, const float* v_mean,
+                      float* lse, long long B, long long S, long long Hq, long long Hkv, long long D, long long q_bs,
+                      long long q_ss, long long q_hs, long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs,
+                      long long o_ss, long long o_hs, float scale, int causal, int* status) {
+  if (v_mean && (reinterpret_cast<uintptr_t>(v_mean) & 15)) return fail(EISEN_ERR_INVALID, "attn_fwd: unaligned pointer");
+  return attn_fwd_impl(stream, q, k, v, o, o_aux, v_mean, lse, B, S, Hq, Hkv, D, q_bs, q_ss, q_hs, kv_bs, kv_ss, kv_hs, o_bs,
+                       o_ss, o_hs, scale, causal, status);
+}
+
+int eisen_attn_center_values(void* stream, const void* v, void* v_centered, float* mean, long long B, long long S,
+                             long long Hkv, long long D, long long kv_bs, long long kv_ss, long long kv_hs) {
+  if (D != 64 && D != 128) return fail(EISEN_ERR_INVALID, "attention: head_dim must be 64 or 128");
+  if (B <= 0 || S <= 0 || Hkv <= 0 || B * Hkv > 0x7fffffffLL || S > 0x7fffffffLL)
+    return fail(EISEN_ERR_INVALID, "attn_center_values: bad B/S/H");
+  if (!v || !v_centered || !mean || !aligned16(v) || !aligned16(v_centered) || !aligned16(mean) || (kv_bs % 8) || (kv_ss % 8) || (kv_hs % 8))
+    return fail(EISEN_ERR_INVALID, "attn_center_values: null or unaligned pointer, or strides that are not multiples of 8");
+  cudaStream_t s = (cudaStream_t)stream;
+  attn_value_mean_kernel<<<(unsigned)(B * Hkv), 256, 0, s>>>((const __nv_bfloat16*)v, mean, (int)S, (int)Hkv, (int)D, kv_bs, kv_ss, kv_hs);
+  int rc = check_launch("attn_value_mean");
+  if (rc) return rc;
+  attn_value_center_kernel<<<grid_for(B * S * Hkv * D / 8, 256, 8), 256, 0, s>>>((const __nv_bfloat16*)v, mean, (__nv_bfloat16*)v_centered,
+                                                                                B * S * Hkv, (int)S, (int)Hkv, (int)D, kv_bs, kv_ss,
+                                                                                kv_hs);
+  return check_launch("attn_value_center");
+}
+
 // workspace layout: dq_acc f32 [B,S,Hq,D] (in the fixed-order mode one such slice per 128-key tile) | delta f32 [B,Hq,S]
 long long eisen_attn_bwd_workspace_bytes(long long B, long long S, long long Hq, long long Hkv, long long D) {
   (void)Hkv;
@@ -1603,8 +1748,8 @@ long long eisen_attn_bwd_workspace_bytes(long long B, long long S, long long Hq,
   return slices * B * S * Hq * D * 4 + B * Hq * S * 4 + 256;
 }
 
-static int attn_bwd_impl(void* stream, const void* q, const void* k, const void* v, const void* o, const float* lse,
-                         const void* d_o, void* dq, void* dk, void* dv, void* workspace, long long B, long long S,
+static int attn_bwd_impl(void* stream, const void* q, const void* k, const void* v, const void* o, const void* o_lo,
+                         const float* lse, const void* d_o, void* dq, void* dk, void* dv, void* workspace, long long B, long long S,
                          long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss, long long q_hs,
                          long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs, long long o_ss,
                          long long o_hs, float scale, int causal, const float* unrope_table, int* status) {
@@ -1614,7 +1759,7 @@ static int attn_bwd_impl(void* stream, const void* q, const void* k, const void*
   int rc = check_args(B, S, Hq, Hkv, D, st, 9);
   if (rc) return rc;
   if (!workspace) return fail(EISEN_ERR_INVALID, "attn_bwd: workspace is null");
-  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(d_o) || !aligned16(dq) ||
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(o_lo) || !aligned16(d_o) || !aligned16(dq) ||
       !aligned16(dk) || !aligned16(dv) || !aligned16(workspace))
     return fail(EISEN_ERR_INVALID, "attn_bwd: unaligned pointer");
   cudaStream_t s = (cudaStream_t)stream;
@@ -1629,22 +1774,24 @@ static int attn_bwd_impl(void* stream, const void* q, const void* k, const void*
     const unsigned nvec = (unsigned)(n_elems / 8);
     const int grid = grid_for((nvec + 1) / 2, 256, 8);
     if (D == 64)
-      attn_prep_kernel<64><<<grid, 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, dq_acc, nvec,
-                                                (unsigned)S, (unsigned)Hq, o_bs, o_ss, o_hs);
+      attn_prep_kernel<64><<<grid, 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)o_lo, (const __nv_bfloat16*)d_o,
+                                                delta, dq_acc, nvec, (unsigned)S, (unsigned)Hq, o_bs, o_ss, o_hs);
     else
-      attn_prep_kernel<128><<<grid, 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, dq_acc, nvec,
-                                                 (unsigned)S, (unsigned)Hq, o_bs, o_ss, o_hs);
+      attn_prep_kernel<128><<<grid, 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)o_lo, (const __nv_bfloat16*)d_o,
+                                                 delta, dq_acc, nvec, (unsigned)S, (unsigned)Hq, o_bs, o_ss, o_hs);
   } else {
     // fixed-order mode: every slice element that the conversion reads is written by its key tile, nothing to clear
     if (!det && cudaMemsetAsync(dq_acc, 0, (size_t)n_elems * 4, s) != cudaSuccess)
       return fail(EISEN_ERR_CUDA, "attn_bwd: memset failed");
     // total threads is a multiple of 32 (S*H*D/8 with D/8 in {8,16}), so every shuffle group is complete
     if (D == 64)
-      attn_delta_kernel<64><<<grid_for(B * S * Hq * 8, 256, 8), 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o,
-                                                                            delta, (int)B, (int)S, (int)Hq, o_bs, o_ss, o_hs);
+      attn_delta_kernel<64><<<grid_for(B * S * Hq * 8, 256, 8), 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)o_lo,
+                                                                            (const __nv_bfloat16*)d_o, delta, (int)B, (int)S,
+                                                                            (int)Hq, o_bs, o_ss, o_hs);
     else
-      attn_delta_kernel<128><<<grid_for(B * S * Hq * 16, 256, 8), 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o,
-                                                                              delta, (int)B, (int)S, (int)Hq, o_bs, o_ss, o_hs);
+      attn_delta_kernel<128><<<grid_for(B * S * Hq * 16, 256, 8), 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)o_lo,
+                                                                              (const __nv_bfloat16*)d_o, delta, (int)B, (int)S,
+                                                                              (int)Hq, o_bs, o_ss, o_hs);
   }
   rc = check_launch("attn_delta");
   if (rc) return rc;
@@ -1708,8 +1855,8 @@ int eisen_attn_bwd(void* stream, const void* q, const void* k, const void* v, co
                    long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss, long long q_hs,
                    long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs, long long o_ss,
                    long long o_hs, float scale, int causal, int* status) {
-  return attn_bwd_impl(stream, q, k, v, o, lse, d_o, dq, dk, dv, workspace, B, S, Hq, Hkv, D, q_bs, q_ss, q_hs, kv_bs, kv_ss,
-                       kv_hs, o_bs, o_ss, o_hs, scale, causal, nullptr, status);
+  return attn_bwd_impl(stream, q, k, v, o, nullptr, lse, d_o, dq, dk, dv, workspace, B, S, Hq, Hkv, D, q_bs, q_ss, q_hs, kv_bs,
+                       kv_ss, kv_hs, o_bs, o_ss, o_hs, scale, causal, nullptr, status);
 }
 
 int eisen_attn_bwd_unrope(void* stream, const void* q, const void* k, const void* v, const void* o, const float* lse,
@@ -1718,8 +1865,17 @@ int eisen_attn_bwd_unrope(void* stream, const void* q, const void* k, const void
                           long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs, long long o_ss,
                           long long o_hs, float scale, int causal, const float* table_cos_sin, int* status) {
   if (!table_cos_sin) return fail(EISEN_ERR_INVALID, "attn_bwd_unrope: the rotation table is null");
-  return attn_bwd_impl(stream, q, k, v, o, lse, d_o, dq, dk, dv, workspace, B, S, Hq, Hkv, D, q_bs, q_ss, q_hs, kv_bs, kv_ss,
-                       kv_hs, o_bs, o_ss, o_hs, scale, causal, table_cos_sin, status);
+  return attn_bwd_impl(stream, q, k, v, o, nullptr, lse, d_o, dq, dk, dv, workspace, B, S, Hq, Hkv, D, q_bs, q_ss, q_hs, kv_bs,
+                       kv_ss, kv_hs, o_bs, o_ss, o_hs, scale, causal, table_cos_sin, status);
+}
+
+int eisen_attn_bwd_ex(void* stream, const void* q, const void* k, const void* v, const void* o, const void* o_lo,
+                      const float* lse, const void* d_o, void* dq, void* dk, void* dv, void* workspace, long long B,
+                      long long S, long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss, long long q_hs,
+                      long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs, long long o_ss, long long o_hs,
+                      float scale, int causal, const float* table_cos_sin, int* status) {
+  return attn_bwd_impl(stream, q, k, v, o, o_lo, lse, d_o, dq, dk, dv, workspace, B, S, Hq, Hkv, D, q_bs, q_ss, q_hs, kv_bs,
+                       kv_ss, kv_hs, o_bs, o_ss, o_hs, scale, causal, table_cos_sin, status);
 }
 
 }  // extern "C"

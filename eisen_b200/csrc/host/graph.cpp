@@ -362,6 +362,7 @@ void Graph::release_attn_stash() {
   for (AttnStash& st : attn_stash) {
     // a stashed buffer was never returned to the pool, so it still counts as live: pool_put settles that
     if (st.o) pool_put(st.o, st.o_bytes);
+    if (st.o_lo) pool_put(st.o_lo, st.o_bytes);
     if (st.lse) pool_put(st.lse, st.lse_bytes);
     st = AttnStash();
   }
@@ -1539,24 +1540,45 @@ int64_t Graph::attention(int64_t q, int64_t k, int64_t v, int64_t Hq, int64_t Hk
   const int64_t B = tq.shape[0], S = tq.shape[1], D = tq.shape[2] / Hq;
   if (tk.shape[2] != Hkv * D) invalid("attention: k/v width must be kv_heads*head_dim");
   const float scale = 1.0f / std::sqrt((float)D);
-  const size_t o_bytes = (size_t)tq.numel * 2, lse_bytes = (size_t)B * Hq * S * 4;
+  // copies: the allocations below grow `tensors`, which invalidates tq / tk
+  const std::vector<int64_t> q_shape = tq.shape;
+  const int64_t q_numel = tq.numel;
+  const size_t o_bytes = (size_t)q_numel * 2, lse_bytes = (size_t)B * Hq * S * 4;
   const bool slot_ok = attn_stash_slot >= 0 && attn_stash_slot < (int64_t)attn_stash.size();
   const bool replay = attn_stash_mode == 2 && slot_ok && attn_stash[(size_t)attn_stash_slot].o &&
                       attn_stash[(size_t)attn_stash_slot].o_bytes == o_bytes &&
                       attn_stash[(size_t)attn_stash_slot].lse_bytes == lse_bytes;
-  int64_t o, lse;
+  // Whenever a backward pass will read this forward's result, the forward also writes o_lo, the part of its
+  // f32 output that the rounding to bf16 drops, and the backward pass forms delta = dO . (O + O_lo): the
+  // rounding error of a bf16 O scales with the common component of the value vectors, which is large in deep
+  // models, while dP - delta does not (see eisen_attn_fwd_ex in the header; the gradients of the q / k weights of
+  // a 16-block model were off by 3.0e-2 against the f32 path without it, 2.2e-2 with it, the rest being the
+  // bf16 storage of q, k and v themselves.  Centring the values, eisen_attn_center_values, is more accurate
+  // still for one attention call but no better for the model, and costs two more launches).
+  const bool want_c = !no_grad || (attn_stash_mode == 1 && slot_ok);
+  int64_t o, lse, o_lo = -1;
   if (replay) {
-    // the output and log-sum-exp of the first forward pass were kept: adopt them, no kernel
+    // the output, its low part and the log-sum-exp of the first forward pass were kept: adopt them, no kernel
     AttnStash& st = attn_stash[(size_t)attn_stash_slot];
-    HTensor to_, tl_;
-    to_.shape = tq.shape; to_.numel = tq.numel; to_.dtype = to_.grad_dtype = 1; to_.is_pooled = true; to_.data = st.o;
+    HTensor to_, tl_, tlo_;
+    to_.shape = q_shape; to_.numel = q_numel; to_.dtype = to_.grad_dtype = 1; to_.is_pooled = true; to_.data = st.o;
     tl_.shape = {B, Hq, S}; tl_.numel = B * Hq * S; tl_.dtype = tl_.grad_dtype = 0; tl_.is_pooled = true; tl_.data = st.lse;
+    tlo_ = to_; tlo_.data = st.o_lo;
+    const bool have_lo = st.o_lo != nullptr;
     st = AttnStash();
     o = new_tensor(std::move(to_));
     lse = new_tensor(std::move(tl_));
+    if (have_lo) {
+      o_lo = new_tensor(std::move(tlo_));
+      tensors[o_lo].constant = true;
+    }
   } else {
-    o = alloc_pooled(tq.shape);
+    o = alloc_pooled(q_shape);
     lse = alloc_pooled_dtype({B, Hq, S}, 0);
+    if (want_c) {
+      o_lo = alloc_pooled(q_shape);
+      tensors[o_lo].constant = true;
+    }
   }
   tensors[lse].constant = true;
   const int64_t qb = S * Hq * D, qs = Hq * D, kb = S * Hkv * D, ks = Hkv * D;
@@ -1564,20 +1586,24 @@ int64_t Graph::attention(int64_t q, int64_t k, int64_t v, int64_t Hq, int64_t Hk
   const double attn_flops = 4.0 * (double)B * (double)Hq * (double)S * (double)S * (double)D * (causal ? 0.5 : 1.0);
   if (!replay) {
     prof_begin(1, attn_flops);
-    ck(eisen_attn_fwd(stream, operand(tensors[q]), operand(tensors[k]), operand(tensors[v]), tensors[o].data,
-                      (float*)tensors[lse].data, B, S, Hq, Hkv, D, qb, qs, D, kb, ks, D, qb, qs, D, scale, causal, status_dev),
+    ck(eisen_attn_fwd_ex(stream, operand(tensors[q]), operand(tensors[k]), operand(tensors[v]), tensors[o].data,
+                         o_lo >= 0 ? tensors[o_lo].data : nullptr, nullptr, (float*)tensors[lse].data, B, S, Hq, Hkv, D, qb, qs, D,
+                         kb, ks, D, qb, qs, D, scale, causal, status_dev),
        "attention");
     prof_end();
     if (attn_stash_mode == 1 && slot_ok) {
       AttnStash& st = attn_stash[(size_t)attn_stash_slot];
       if (st.o) pool_put(st.o, st.o_bytes);
+      if (st.o_lo) pool_put(st.o_lo, st.o_bytes);
       if (st.lse) pool_put(st.lse, st.lse_bytes);
       st.o = tensors[o].data; st.lse = tensors[lse].data; st.o_bytes = o_bytes; st.lse_bytes = lse_bytes;
+      st.o_lo = o_lo >= 0 ? tensors[o_lo].data : nullptr;
       tensors[o].data_kept = tensors[lse].data_kept = true;  // popped without returning the buffers
+      if (o_lo >= 0) tensors[o_lo].data_kept = true;
     }
   }
   if (!no_grad) {
-    tape.push_back({{q, k, v}, o, [this, q, k, v, o, lse, B, S, Hq, Hkv, D, qb, qs, kb, ks, scale, causal, attn_flops]() {
+    tape.push_back({{q, k, v}, o, [this, q, k, v, o, o_lo, lse, B, S, Hq, Hkv, D, qb, qs, kb, ks, scale, causal, attn_flops]() {
       OUT_GRAD_OR_RETURN(o);
       HTensor* gt[3] = {&tensors[q], &tensors[k], &tensors[v]};
       void* dst[3];
@@ -1597,18 +1623,12 @@ int64_t Graph::attention(int64_t q, int64_t k, int64_t v, int64_t Hq, int64_t Hk
       if (!unrope && (gt[0]->grad_unrotated || gt[1]->grad_unrotated))
         invalid("attention: the gradients of q and k are kept in different forms");
       prof_begin(2, 2.5 * attn_flops);
-      if (unrope) {
-        ck(eisen_attn_bwd_unrope(stream, operand(*gt[0]), operand(*gt[1]), operand(*gt[2]), to.data,
-                                 (const float*)tensors[lse].data, to.grad, dst[0], dst[1], dst[2], ws, B, S, Hq, Hkv, D, qb, qs,
-                                 D, kb, ks, D, qb, qs, D, scale, causal, rope_table(S, D), status_dev),
-           "attention.bwd");
-        gt[0]->grad_unrotated = gt[1]->grad_unrotated = true;
-      } else {
-        ck(eisen_attn_bwd(stream, operand(*gt[0]), operand(*gt[1]), operand(*gt[2]), to.data, (const float*)tensors[lse].data,
-                          to.grad, dst[0], dst[1], dst[2], ws, B, S, Hq, Hkv, D, qb, qs, D, kb, ks, D, qb, qs, D, scale,
-                          causal, status_dev),
-           "attention.bwd");
-      }
+      ck(eisen_attn_bwd_ex(stream, operand(*gt[0]), operand(*gt[1]), operand(*gt[2]), to.data,
+                           o_lo >= 0 ? tensors[o_lo].data : nullptr, (const float*)tensors[lse].data, to.grad, dst[0], dst[1],
+                           dst[2], ws, B, S, Hq, Hkv, D, qb, qs, D, kb, ks, D, qb, qs, D, scale, causal,
+                           unrope ? rope_table(S, D) : nullptr, status_dev),
+         "attention.bwd");
+      if (unrope) gt[0]->grad_unrotated = gt[1]->grad_unrotated = true;
       prof_end();
       for (int i = 0; i < 3; ++i) {
         if (tmp[i]) {

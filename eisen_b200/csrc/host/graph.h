@@ -154,7 +154,7 @@ class Graph {
   // op hands its output and log-sum-exp buffers to attn_stash[attn_stash_slot] instead of the pool
   // when its tensors are popped; with mode 2 it adopts the stashed buffers and skips its forward
   // kernel (the block re-run for the backward pass then recomputes everything except attention).
-  struct AttnStash { void* o = nullptr; void* lse = nullptr; size_t o_bytes = 0, lse_bytes = 0; };
+  struct AttnStash { void* o = nullptr; void* o_lo = nullptr; void* lse = nullptr; size_t o_bytes = 0, lse_bytes = 0; };
   std::vector<AttnStash> attn_stash;
   int attn_stash_mode = 0;
   int64_t attn_stash_slot = -1;

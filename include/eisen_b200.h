@@ -170,6 +170,32 @@ int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, vo
                    long long S, long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss,
                    long long q_hs, long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs,
                    long long o_ss, long long o_hs, float scale, int causal, int* status);
+/* The extended pair, for the accuracy of dq and dk in deep models.  dS = P * (dP - delta) subtracts two
+ * numbers that both carry the common component of the value vectors (dP = dO . V_j, delta = dO . O); rounding
+ * errors of O (bf16) and of P (bf16 inside P V) scale with that component while the difference does not, and
+ * the value vectors of a deep model share a large mean: against the f32 path the gradients of the q and k
+ * weights were off by 3e-2 (relative L2) at 16 blocks where all other gradients were within 1.6e-2.
+ *   eisen_attn_center_values: mean[B, Hkv, D] (f32) = mean of v over the sequence, v_centered (bf16,
+ *     contiguous [B, S, Hkv, D]) = v - mean.
+ *   eisen_attn_fwd_ex with v = v_centered and v_mean = mean: o = bf16(P V_c + mean) (the same output) and
+ *     o_aux (bf16, O's strides, may be null) = bf16(P V_c), the centred output.
+ *   eisen_attn_bwd_ex with v = v_centered, o = that centred output: delta = dO . O_c and dP = dO . V_c differ
+ *     by the same constant from the uncentred ones, so dS, dq, dk are the same numbers computed without the
+ *     cancellation, and dv = P^T dO does not see the shift at all.
+ * Without v_mean (null) the forward is eisen_attn_fwd and o_aux, if given, receives what the rounding of O
+ * drops (o_f32 - float(bf16(o_f32))); eisen_attn_bwd_ex then takes it as o_lo and forms delta from O + O_lo,
+ * which removes the rounding error of O but not that of P.  table_cos_sin as in eisen_attn_bwd_unrope. */
+int eisen_attn_center_values(void* stream, const void* v, void* v_centered, float* mean, long long B, long long S,
+                             long long Hkv, long long D, long long kv_bs, long long kv_ss, long long kv_hs);
+int eisen_attn_fwd_ex(void* stream, const void* q, const void* k, const void* v, void* o, void* o_aux, const float* v_mean,
+                      float* lse, long long B, long long S, long long Hq, long long Hkv, long long D, long long q_bs,
+                      long long q_ss, long long q_hs, long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs,
+                      long long o_ss, long long o_hs, float scale, int causal, int* status);
+int eisen_attn_bwd_ex(void* stream, const void* q, const void* k, const void* v, const void* o, const void* o_lo,
+                      const float* lse, const void* d_o, void* dq, void* dk, void* dv, void* workspace, long long B,
+                      long long S, long long Hq, long long Hkv, long long D, long long q_bs, long long q_ss, long long q_hs,
+                      long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs, long long o_ss, long long o_hs,
+                      float scale, int causal, const float* table_cos_sin, int* status);
 /* eisen_attn_bwd for q and k that were rotated by RoPE right before the attention
  * (src/nn/attention.rs:320-333): dq and dk come out rotated back by the angles of their positions
  * (table_cos_sin of eisen_rope_table for (S, D)), i.e. as the gradients of the un-rotated projections,

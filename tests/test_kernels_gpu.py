@@ -536,6 +536,66 @@ def test_flash_attention_bwd_fixed_order(B, S, Hq, Hkv, D, causal):
         eb.call("eisen_set_deterministic", 0)
 
 
+@pytest.mark.parametrize("D", [64, 128])
+def test_flash_attention_values_with_a_common_component(D):
+    """Values that share a large mean (as the value vectors of a deep model do): dS = P (dP - delta) subtracts
+    two numbers that both carry it, and the rounding errors of O and P scale with that mean.  Three ways to run
+    the backward pass: plain (delta from the bf16 output), with the low part of the f32 output handed over,
+    and on centred values (eisen_attn_center_values / eisen_attn_fwd_ex / eisen_attn_bwd_ex).  The centred form
+    keeps the accuracy the kernel has on centred data; the plain form loses most of it for dq and dk."""
+    B, S, Hq, Hkv = 1, 512, 4, 2
+    g = torch.Generator(device="cpu").manual_seed(D + 7)
+    q = (0.3 * torch.randn(B, S, Hq, D, generator=g)).to(torch.bfloat16)
+    k = (0.3 * torch.randn(B, S, Hkv, D, generator=g)).to(torch.bfloat16)
+    v = (torch.randn(B, S, Hkv, D, generator=g) + 12.0 * torch.randn(1, 1, Hkv, D, generator=g)).to(torch.bfloat16)
+    d_o = torch.randn(B, S, Hq, D, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    o_ref, _, dq_ref, dk_ref, dv_ref = _attn_reference(q, k, v, d_o, scale, True)
+    qd, kd, vd, dod = (t.to(dev()) for t in (q, k, v, d_o))
+    lse = torch.empty(B, Hq, S, dtype=torch.float32, device=dev())
+    st = status_word()
+    sq, sk = qd.stride()[:3], kd.stride()[:3]
+    ws = torch.empty(eb.lib().eisen_attn_bwd_workspace_bytes(B, S, Hq, Hkv, D), dtype=torch.uint8, device=dev())
+
+    def backward(vv, oo, lo):
+        dq, dk, dv = torch.empty_like(qd), torch.empty_like(kd), torch.empty_like(vd)
+        eb.call("eisen_attn_bwd_ex", stream(), P(qd), P(kd), P(vv), P(oo), P(lo), P(lse), P(dod), P(dq), P(dk), P(dv), P(ws),
+                B, S, Hq, Hkv, D, *sq, *sk, *sq, scale, 1, None, P(st))
+        torch.cuda.synchronize()
+        assert rel_l2(dv.float().cpu().numpy(), dv_ref.numpy()) < 2e-2
+        return max(rel_l2(dq.float().cpu().numpy(), dq_ref.numpy()), rel_l2(dk.float().cpu().numpy(), dk_ref.numpy()))
+
+    # plain forward with the low part of the output
+    o, o_lo = torch.empty_like(qd), torch.full_like(qd, float("nan"))
+    eb.call("eisen_attn_fwd_ex", stream(), P(qd), P(kd), P(vd), P(o), P(o_lo), None, P(lse), B, S, Hq, Hkv, D, *sq, *sk, *sq,
+            scale, 1, P(st))
+    torch.cuda.synchronize()
+    assert rel_l2(o.float().cpu().numpy(), o_ref.numpy()) < 1e-2
+    assert rel_l2((o.float() + o_lo.float()).cpu().numpy(), o_ref.numpy()) < 3e-3  # P is rounded to bf16 before P V
+    err_plain = backward(vd, o, None)
+    err_lo = backward(vd, o, o_lo)
+    # centred values
+    vc = torch.full_like(vd, float("nan"))
+    mean = torch.empty(B, Hkv, D, dtype=torch.float32, device=dev())
+    eb.call("eisen_attn_center_values", stream(), P(vd), P(vc), P(mean), B, S, Hkv, D, *sk)
+    torch.cuda.synchronize()
+    assert rel_l2(mean.cpu().numpy(), v.float().mean(dim=1).numpy()) < 1e-6
+    assert rel_l2(vc.float().cpu().numpy(), (v.float() - v.float().mean(dim=1, keepdim=True)).numpy()) < 4e-3
+    o2, oc = torch.empty_like(qd), torch.full_like(qd, float("nan"))
+    eb.call("eisen_attn_fwd_ex", stream(), P(qd), P(kd), P(vc), P(o2), P(oc), P(mean), P(lse), B, S, Hq, Hkv, D, *sq, *sk, *sq,
+            scale, 1, P(st))
+    torch.cuda.synchronize()
+    assert rel_l2(o2.float().cpu().numpy(), o_ref.numpy()) < 1e-2
+    rep = Hq // Hkv
+    assert rel_l2(oc.float().cpu().numpy(), (o_ref - v.float().mean(dim=1, keepdim=True).repeat_interleave(rep, 2)).numpy()) < 1e-2
+    err_c = backward(vc, oc, None)
+    assert int(st.item()) == 0
+    print("dq / dk error: plain %.4f, with the low part %.4f, centred %.4f" % (err_plain, err_lo, err_c))
+    assert err_c < 6e-3
+    assert err_lo < 1e-2
+    assert err_plain > 2.0 * err_lo and err_plain > 3.0 * err_c
+
+
 @pytest.mark.parametrize("tiles", [1, 2])
 @pytest.mark.parametrize("B,S,Hq,Hkv,causal,ramp", [(2, 256, 4, 2, True, False), (1, 200, 2, 2, True, False),
                                                    (1, 2048, 8, 2, True, False), (2, 1024, 4, 1, False, False),
