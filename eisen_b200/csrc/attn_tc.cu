@@ -1557,8 +1557,19 @@ attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict_
 }
 
 // mean[b, h, :] = mean over s of v[b, s, h, :]; one CTA per (b, h), f32 sums in a fixed order
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&x)[8]);
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&x)[8]) { ld16(p, x); }
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&x)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+
+template <typename T>
 __global__ void __launch_bounds__(256)
-attn_value_mean_kernel(const __nv_bfloat16* __restrict__ v, float* __restrict__ mean, int S, int H, int D, long long bs,
+attn_value_mean_kernel(const T* __restrict__ v, float* __restrict__ mean, int S, int H, int D, long long bs,
                        long long ss, long long hs) {
   __shared__ float sh[8][128];
   const int b = blockIdx.x / H, h = blockIdx.x % H;
@@ -1566,10 +1577,10 @@ attn_value_mean_kernel(const __nv_bfloat16* __restrict__ v, float* __restrict__ 
   const int rows_per_pass = 256 / per_row;   // 32 or 16 rows at a time
   const int c = (threadIdx.x % per_row) * 8, r0 = threadIdx.x / per_row;
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  const __nv_bfloat16* base = v + (long long)b * bs + (long long)h * hs + c;
+  const T* base = v + (long long)b * bs + (long long)h * hs + c;
   for (int s = r0; s < S; s += rows_per_pass) {
     float x[8];
-    ld16(base + (long long)s * ss, x);
+    load8<T>(base + (long long)s * ss, x);
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[e] += x[e];
   }
@@ -1588,8 +1599,9 @@ attn_value_mean_kernel(const __nv_bfloat16* __restrict__ v, float* __restrict__ 
 }
 
 // vc[b, s, h, :] = bf16(v[b, s, h, :] - mean[b, h, :]) (vc contiguous [B, S, H, D])
+template <typename T>
 __global__ void __launch_bounds__(256)
-attn_value_center_kernel(const __nv_bfloat16* __restrict__ v, const float* __restrict__ mean, __nv_bfloat16* __restrict__ vc,
+attn_value_center_kernel(const T* __restrict__ v, const float* __restrict__ mean, __nv_bfloat16* __restrict__ vc,
                          long long rows /*B*S*H*/, int S, int H, int D, long long bs, long long ss, long long hs) {
   const int per_row = D / 8;
   const long long total = rows * per_row;
@@ -1600,7 +1612,7 @@ attn_value_center_kernel(const __nv_bfloat16* __restrict__ v, const float* __res
     const int s = (int)((r / H) % S);
     const long long b = r / ((long long)H * S);
     float x[8];
-    ld16(v + b * bs + (long long)s * ss + (long long)h * hs + c, x);
+    load8<T>(v + b * bs + (long long)s * ss + (long long)h * hs + c, x);
     const float* m = mean + (b * H + h) * D + c;
 #pragma unroll
     for (int e = 0; e < 8; ++e) x[e] -= m[e];
@@ -1724,20 +1736,30 @@ int eisen_attn_fwd_ex(void* stream, const void* q, const void* k, const void* v,
                        o_ss, o_hs, scale, causal, status);
 }
 
-int eisen_attn_center_values(void* stream, const void* v, void* v_centered, float* mean, long long B, long long S,
-                             long long Hkv, long long D, long long kv_bs, long long kv_ss, long long kv_hs) {
+int eisen_attn_center_values(void* stream, const void* v, int v_dtype, void* v_centered, float* mean, long long B,
+                             long long S, long long Hkv, long long D, long long kv_bs, long long kv_ss, long long kv_hs) {
   if (D != 64 && D != 128) return fail(EISEN_ERR_INVALID, "attention: head_dim must be 64 or 128");
+  if (v_dtype != EISEN_F32 && v_dtype != EISEN_BF16) return fail(EISEN_ERR_INVALID, "attn_center_values: v must be f32 or bf16");
   if (B <= 0 || S <= 0 || Hkv <= 0 || B * Hkv > 0x7fffffffLL || S > 0x7fffffffLL)
     return fail(EISEN_ERR_INVALID, "attn_center_values: bad B/S/H");
   if (!v || !v_centered || !mean || !aligned16(v) || !aligned16(v_centered) || !aligned16(mean) || (kv_bs % 8) || (kv_ss % 8) || (kv_hs % 8))
     return fail(EISEN_ERR_INVALID, "attn_center_values: null or unaligned pointer, or strides that are not multiples of 8");
   cudaStream_t s = (cudaStream_t)stream;
-  attn_value_mean_kernel<<<(unsigned)(B * Hkv), 256, 0, s>>>((const __nv_bfloat16*)v, mean, (int)S, (int)Hkv, (int)D, kv_bs, kv_ss, kv_hs);
-  int rc = check_launch("attn_value_mean");
-  if (rc) return rc;
-  attn_value_center_kernel<<<grid_for(B * S * Hkv * D / 8, 256, 8), 256, 0, s>>>((const __nv_bfloat16*)v, mean, (__nv_bfloat16*)v_centered,
-                                                                                B * S * Hkv, (int)S, (int)Hkv, (int)D, kv_bs, kv_ss,
-                                                                                kv_hs);
+  const int grid2 = grid_for(B * S * Hkv * D / 8, 256, 8);
+  if (v_dtype == EISEN_F32) {
+    attn_value_mean_kernel<float><<<(unsigned)(B * Hkv), 256, 0, s>>>((const float*)v, mean, (int)S, (int)Hkv, (int)D, kv_bs, kv_ss, kv_hs);
+    int rc = check_launch("attn_value_mean");
+    if (rc) return rc;
+    attn_value_center_kernel<float><<<grid2, 256, 0, s>>>((const float*)v, mean, (__nv_bfloat16*)v_centered, B * S * Hkv, (int)S,
+                                                          (int)Hkv, (int)D, kv_bs, kv_ss, kv_hs);
+  } else {
+    attn_value_mean_kernel<__nv_bfloat16><<<(unsigned)(B * Hkv), 256, 0, s>>>((const __nv_bfloat16*)v, mean, (int)S, (int)Hkv, (int)D,
+                                                                             kv_bs, kv_ss, kv_hs);
+    int rc = check_launch("attn_value_mean");
+    if (rc) return rc;
+    attn_value_center_kernel<__nv_bfloat16><<<grid2, 256, 0, s>>>((const __nv_bfloat16*)v, mean, (__nv_bfloat16*)v_centered,
+                                                                  B * S * Hkv, (int)S, (int)Hkv, (int)D, kv_bs, kv_ss, kv_hs);
+  }
   return check_launch("attn_value_center");
 }
 

@@ -917,13 +917,18 @@ void Graph::qkv_proj_rope(int64_t x, int64_t wq, int64_t wk, int64_t wv, int64_t
   }
   const float* tab = rope_table(S, head_dim);
   const int dt = act_dtype();
-  for (int i = 0; i < 3; ++i) out3[i] = alloc_pooled({B, S, ns[i]});
+  // With Graph::center_values the value projection is written in f32: Graph::attention then subtracts the
+  // values' mean before rounding them to bf16, which keeps their token-specific part to bf16 precision.
+  const bool v_f32 = center_values;
+  for (int i = 0; i < 2; ++i) out3[i] = alloc_pooled({B, S, ns[i]});
+  out3[2] = v_f32 ? alloc_pooled_dtype({B, S, ns[2]}, 0) : alloc_pooled({B, S, ns[2]});
   const int64_t oq = out3[0], ok = out3[1], ov = out3[2];
+  tensors[ov].grad_dtype = dt;  // the attention backward writes dv in the activation type
   tensors[oq].unrope_hd = tensors[ok].unrope_hd = head_dim;
   if (!skip_forward) {
     const void* bs[3] = {weight_operand(wq), weight_operand(wk), weight_operand(wv)};
     void* cs[3] = {tensors[oq].data, tensors[ok].data, tensors[ov].data};
-    const int modes[3] = {5, 5, 0};
+    const int modes[3] = {5, 5, v_f32 ? 2 : 0};
     prof_begin(0, 2.0 * (double)m * (double)(ns[0] + ns[1] + ns[2]) * (double)k);
     ck(eisen_gemm_bf16_multi_n(stream, 0, 1, m, k, operand(tensors[x]), k, 3, bs, ns, ns, cs, ns, modes, 1, 1.0f, tab, S,
                                head_dim, status_dev),
@@ -1548,15 +1553,25 @@ int64_t Graph::attention(int64_t q, int64_t k, int64_t v, int64_t Hq, int64_t Hk
   const bool replay = attn_stash_mode == 2 && slot_ok && attn_stash[(size_t)attn_stash_slot].o &&
                       attn_stash[(size_t)attn_stash_slot].o_bytes == o_bytes &&
                       attn_stash[(size_t)attn_stash_slot].lse_bytes == lse_bytes;
-  // Whenever a backward pass will read this forward's result, the forward also writes o_lo, the part of its
-  // f32 output that the rounding to bf16 drops, and the backward pass forms delta = dO . (O + O_lo): the
-  // rounding error of a bf16 O scales with the common component of the value vectors, which is large in deep
-  // models, while dP - delta does not (see eisen_attn_fwd_ex in the header; the gradients of the q / k weights of
-  // a 16-block model were off by 3.0e-2 against the f32 path without it, 2.2e-2 with it, the rest being the
-  // bf16 storage of q, k and v themselves.  Centring the values, eisen_attn_center_values, is more accurate
-  // still for one attention call but no better for the model, and costs two more launches).
+  // Accuracy of dq / dk in deep models (see eisen_attn_fwd_ex in the header): dS = P (dP - delta) subtracts two
+  // numbers that both carry the common component of the value vectors, which is large in deep models.
+  //  * v in f32 (Graph::qkv_proj_rope writes it so): the values are centred (v_c = bf16(v - mean over the
+  //    sequence)) and forward and backward work on v_c; the second output slot holds the centred output P v_c.
+  //  * v in bf16: the second output slot holds the part of the f32 output that the rounding to bf16 drops, and
+  //    the backward pass forms delta = dO . (O + O_lo).
+  // Against the f32 path the q / k weight gradients of a 16-block model were off by 3.0e-2 with neither and by
+  // 2.2e-2 with either; the second form is what runs (v is bf16 unless Graph::center_values is set).
   const bool want_c = !no_grad || (attn_stash_mode == 1 && slot_ok);
-  int64_t o, lse, o_lo = -1;
+  const bool centred = tensors[v].dtype == 0 && precision == Precision::Bf16Mixed;
+  int64_t o, lse, o_lo = -1, vc = -1, vmean = -1;
+  if (centred) {
+    vc = alloc_pooled({B, S, Hkv * D});
+    vmean = alloc_pooled_dtype({B, Hkv, D}, 0);
+    tensors[vc].constant = tensors[vmean].constant = true;
+    ck(eisen_attn_center_values(stream, tensors[v].data, EISEN_F32, tensors[vc].data, (float*)tensors[vmean].data, B, S, Hkv, D,
+                                S * Hkv * D, Hkv * D, D),
+       "attention(center)");
+  }
   if (replay) {
     // the output, its low part and the log-sum-exp of the first forward pass were kept: adopt them, no kernel
     AttnStash& st = attn_stash[(size_t)attn_stash_slot];
@@ -1586,9 +1601,10 @@ int64_t Graph::attention(int64_t q, int64_t k, int64_t v, int64_t Hq, int64_t Hk
   const double attn_flops = 4.0 * (double)B * (double)Hq * (double)S * (double)S * (double)D * (causal ? 0.5 : 1.0);
   if (!replay) {
     prof_begin(1, attn_flops);
-    ck(eisen_attn_fwd_ex(stream, operand(tensors[q]), operand(tensors[k]), operand(tensors[v]), tensors[o].data,
-                         o_lo >= 0 ? tensors[o_lo].data : nullptr, nullptr, (float*)tensors[lse].data, B, S, Hq, Hkv, D, qb, qs, D,
-                         kb, ks, D, qb, qs, D, scale, causal, status_dev),
+    ck(eisen_attn_fwd_ex(stream, operand(tensors[q]), operand(tensors[k]), centred ? tensors[vc].data : operand(tensors[v]),
+                         tensors[o].data, o_lo >= 0 ? tensors[o_lo].data : nullptr,
+                         centred ? (const float*)tensors[vmean].data : nullptr, (float*)tensors[lse].data, B, S, Hq, Hkv, D, qb, qs,
+                         D, kb, ks, D, qb, qs, D, scale, causal, status_dev),
        "attention");
     prof_end();
     if (attn_stash_mode == 1 && slot_ok) {
@@ -1603,7 +1619,7 @@ int64_t Graph::attention(int64_t q, int64_t k, int64_t v, int64_t Hq, int64_t Hk
     }
   }
   if (!no_grad) {
-    tape.push_back({{q, k, v}, o, [this, q, k, v, o, o_lo, lse, B, S, Hq, Hkv, D, qb, qs, kb, ks, scale, causal, attn_flops]() {
+    tape.push_back({{q, k, v}, o, [this, q, k, v, o, o_lo, vc, lse, B, S, Hq, Hkv, D, qb, qs, kb, ks, scale, causal, attn_flops]() {
       OUT_GRAD_OR_RETURN(o);
       HTensor* gt[3] = {&tensors[q], &tensors[k], &tensors[v]};
       void* dst[3];
@@ -1623,11 +1639,19 @@ int64_t Graph::attention(int64_t q, int64_t k, int64_t v, int64_t Hq, int64_t Hk
       if (!unrope && (gt[0]->grad_unrotated || gt[1]->grad_unrotated))
         invalid("attention: the gradients of q and k are kept in different forms");
       prof_begin(2, 2.5 * attn_flops);
-      ck(eisen_attn_bwd_ex(stream, operand(*gt[0]), operand(*gt[1]), operand(*gt[2]), to.data,
-                           o_lo >= 0 ? tensors[o_lo].data : nullptr, (const float*)tensors[lse].data, to.grad, dst[0], dst[1],
-                           dst[2], ws, B, S, Hq, Hkv, D, qb, qs, D, kb, ks, D, qb, qs, D, scale, causal,
-                           unrope ? rope_table(S, D) : nullptr, status_dev),
-         "attention.bwd");
+      if (vc >= 0) {  // centred values: delta from the centred output (held in the second output slot)
+        if (o_lo < 0) invalid("attention: the centred output of the forward pass is missing");
+        ck(eisen_attn_bwd_ex(stream, operand(*gt[0]), operand(*gt[1]), tensors[vc].data, tensors[o_lo].data, nullptr,
+                             (const float*)tensors[lse].data, to.grad, dst[0], dst[1], dst[2], ws, B, S, Hq, Hkv, D, qb, qs, D, kb,
+                             ks, D, qb, qs, D, scale, causal, unrope ? rope_table(S, D) : nullptr, status_dev),
+           "attention.bwd");
+      } else {
+        ck(eisen_attn_bwd_ex(stream, operand(*gt[0]), operand(*gt[1]), operand(*gt[2]), to.data,
+                             o_lo >= 0 ? tensors[o_lo].data : nullptr, (const float*)tensors[lse].data, to.grad, dst[0], dst[1],
+                             dst[2], ws, B, S, Hq, Hkv, D, qb, qs, D, kb, ks, D, qb, qs, D, scale, causal,
+                             unrope ? rope_table(S, D) : nullptr, status_dev),
+           "attention.bwd");
+      }
       if (unrope) gt[0]->grad_unrotated = gt[1]->grad_unrotated = true;
       prof_end();
       for (int i = 0; i < 3; ++i) {

@@ -195,6 +195,10 @@ class Graph {
   // forward kernel.  Used while a checkpointed block is re-run for its backward pass: the values of
   // the last projection and of the last residual add are read by no backward node.
   bool skip_forward = false;
+  // Off by default and set by nobody in this library: qkv_proj_rope then writes the value projection in f32 and
+  // attention centres it before rounding (see Graph::attention).  Measured on a 16-block model: no better than
+  // the default (the low part of the attention output handed to the backward pass), at 1 ms more per step.
+  bool center_values = false;
   int64_t num_params = 0;
   Precision precision;
   cudaStream_t stream;

@@ -176,7 +176,9 @@ int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, vo
  * the value vectors of a deep model share a large mean: against the f32 path the gradients of the q and k
  * weights were off by 3e-2 (relative L2) at 16 blocks where all other gradients were within 1.6e-2.
  *   eisen_attn_center_values: mean[B, Hkv, D] (f32) = mean of v over the sequence, v_centered (bf16,
- *     contiguous [B, S, Hkv, D]) = v - mean.
+ *     contiguous [B, S, Hkv, D]) = v - mean.  v may be f32 (v_dtype = EISEN_F32; strides in elements): a value
+ *     projection that writes f32 and is rounded only after the subtraction keeps the token-specific part of v
+ *     to bf16 precision, where rounding v itself loses it to the common component.
  *   eisen_attn_fwd_ex with v = v_centered and v_mean = mean: o = bf16(P V_c + mean) (the same output) and
  *     o_aux (bf16, O's strides, may be null) = bf16(P V_c), the centred output.
  *   eisen_attn_bwd_ex with v = v_centered, o = that centred output: delta = dO . O_c and dP = dO . V_c differ
@@ -185,8 +187,8 @@ int eisen_attn_fwd(void* stream, const void* q, const void* k, const void* v, vo
  * Without v_mean (null) the forward is eisen_attn_fwd and o_aux, if given, receives what the rounding of O
  * drops (o_f32 - float(bf16(o_f32))); eisen_attn_bwd_ex then takes it as o_lo and forms delta from O + O_lo,
  * which removes the rounding error of O but not that of P.  table_cos_sin as in eisen_attn_bwd_unrope. */
-int eisen_attn_center_values(void* stream, const void* v, void* v_centered, float* mean, long long B, long long S,
-                             long long Hkv, long long D, long long kv_bs, long long kv_ss, long long kv_hs);
+int eisen_attn_center_values(void* stream, const void* v, int v_dtype, void* v_centered, float* mean, long long B,
+                             long long S, long long Hkv, long long D, long long kv_bs, long long kv_ss, long long kv_hs);
 int eisen_attn_fwd_ex(void* stream, const void* q, const void* k, const void* v, void* o, void* o_aux, const float* v_mean,
                       float* lse, long long B, long long S, long long Hq, long long Hkv, long long D, long long q_bs,
                       long long q_ss, long long q_hs, long long kv_bs, long long kv_ss, long long kv_hs, long long o_bs,

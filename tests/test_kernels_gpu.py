@@ -577,10 +577,16 @@ def test_flash_attention_values_with_a_common_component(D):
     # centred values
     vc = torch.full_like(vd, float("nan"))
     mean = torch.empty(B, Hkv, D, dtype=torch.float32, device=dev())
-    eb.call("eisen_attn_center_values", stream(), P(vd), P(vc), P(mean), B, S, Hkv, D, *sk)
+    eb.call("eisen_attn_center_values", stream(), P(vd), eb.BF16, P(vc), P(mean), B, S, Hkv, D, *sk)
     torch.cuda.synchronize()
     assert rel_l2(mean.cpu().numpy(), v.float().mean(dim=1).numpy()) < 1e-6
     assert rel_l2(vc.float().cpu().numpy(), (v.float() - v.float().mean(dim=1, keepdim=True)).numpy()) < 4e-3
+    # f32 values (a projection that is rounded only after the subtraction): same mean, same centred values
+    vc32, mean32 = torch.full_like(vd, float("nan")), torch.empty_like(mean)
+    v32 = vd.float().contiguous()
+    eb.call("eisen_attn_center_values", stream(), P(v32), eb.F32, P(vc32), P(mean32), B, S, Hkv, D, *v32.stride()[:3])
+    torch.cuda.synchronize()
+    assert torch.equal(mean32, mean) and torch.equal(vc32.view(torch.int16), vc.view(torch.int16))
     o2, oc = torch.empty_like(qd), torch.full_like(qd, float("nan"))
     eb.call("eisen_attn_fwd_ex", stream(), P(qd), P(kd), P(vc), P(o2), P(oc), P(mean), P(lse), B, S, Hq, Hkv, D, *sq, *sk, *sq,
             scale, 1, P(st))
