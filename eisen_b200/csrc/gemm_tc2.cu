@@ -336,7 +336,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 #pragma unroll 1
         for (int c = 0; c < PN / 64; ++c) {
           // addend rows: requested before the TMEM load so that their latency runs beside it
-          uint4 pre[8];  // the addend's eight rows, or the angles of four rows (the modes exclude each other)
+          uint4 pre[8];  // the addend's eight rows
           if (acc_bf16) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) pre[i] = *reinterpret_cast<const uint4*>(r_base + (long long)(4 * i) * ldr + c * 64);
@@ -345,6 +345,43 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           tmem_ld_32x32b_x32(taddr + c * 64, r0);
           tmem_ld_32x32b_x32(taddr + c * 64 + 32, r1);
           tmem_ld_wait();
+          if (rope) {
+            // RoPE on the f32 accumulators, one rounding to bf16 afterwards (a projection followed by a separate
+            // RoPE kernel rounds twice).  The chunk goes through the staging tile in two halves of 32 f32 columns
+            // (the same 32 x 128 bytes); a thread then holds four columns (two pairs) of eight rows.
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const uint32_t* rr32 = h ? r1 : r0;
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<uint4*>(st + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                    make_uint4(rr32[4 * j], rr32[4 * j + 1], rr32[4 * j + 2], rr32[4 * j + 3]);
+              __syncwarp();
+              const int col = n0 + c * 64 + h * 32 + seg * 4;
+              const int pair0 = (col % p.rope_hd) >> 1;
+              uint4 ang[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int pos = (row0 + 4 * i + rr) % p.rope_s;
+                ang[i] = __ldg(reinterpret_cast<const uint4*>(p.rope_tab + (long long)pos * (p.rope_hd >> 1) + pair0));
+              }
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int rw = 4 * i + rr;
+                const uint4 x = *reinterpret_cast<const uint4*>(st + rw * 128 + ((seg ^ (rw & 7)) << 4));
+                const float x0 = __uint_as_float(x.x) * p.alpha, y0 = __uint_as_float(x.y) * p.alpha;
+                const float x1 = __uint_as_float(x.z) * p.alpha, y1 = __uint_as_float(x.w) * p.alpha;
+                const float c0 = __uint_as_float(ang[i].x), s0 = __uint_as_float(ang[i].y);
+                const float c1 = __uint_as_float(ang[i].z), s1 = __uint_as_float(ang[i].w);
+                uint2 o;
+                o.x = pack_bf16x2(x0 * c0 - y0 * s0, x0 * s0 + y0 * c0);
+                o.y = pack_bf16x2(x1 * c1 - y1 * s1, x1 * s1 + y1 * c1);
+                *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(Cp) + (long long)(row0 + rw) * ldc + col) = o;
+              }
+              __syncwarp();
+            }
+            continue;
+          }
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             uint4 o;
@@ -362,18 +399,6 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           __syncwarp();
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            if (rope) {
-              // the angles of four rows are requested together (inside the store loop each request
-              // would wait for the one before it, since loads stay behind the stores to C)
-              const int pair0 = ((n0 + c * 64 + seg * 8) % p.rope_hd) >> 1;
-#pragma unroll
-              for (int ii = 0; ii < 4; ++ii) {
-                const int pos = (row0 + 4 * (4 * h + ii) + rr) % p.rope_s;
-                const uint4* tp = reinterpret_cast<const uint4*>(p.rope_tab + (long long)pos * (p.rope_hd >> 1) + pair0);
-                pre[2 * ii] = __ldg(tp);
-                pre[2 * ii + 1] = __ldg(tp + 1);
-              }
-            }
 #pragma unroll
             for (int ii = 0; ii < 4; ++ii) {
               const int i = 4 * h + ii;
@@ -389,21 +414,6 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                 for (int e = 0; e < 4; ++e) {
                   const float2 fa = __bfloat1622float2(a2[e]), fb = __bfloat1622float2(b2[e]);
                   w[e] = pack_bf16x2(fa.x + fb.x, fa.y + fb.y);
-                }
-                o = make_uint4(w[0], w[1], w[2], w[3]);
-              }
-              if (rope) {
-                // four (even, odd) column pairs of one head, rotated by the angles of this row's
-                // position; the product was rounded to bf16 first, as a separate RoPE kernel reads it
-                const uint4 t0 = pre[2 * ii], t1 = pre[2 * ii + 1];
-                const float cs[4] = {__uint_as_float(t0.x), __uint_as_float(t0.z), __uint_as_float(t1.x), __uint_as_float(t1.z)};
-                const float sn[4] = {__uint_as_float(t0.y), __uint_as_float(t0.w), __uint_as_float(t1.y), __uint_as_float(t1.w)};
-                const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&o);
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const float2 v = __bfloat1622float2(a2[e]);
-                  w[e] = pack_bf16x2(v.x * cs[e] - v.y * sn[e], v.x * sn[e] + v.y * cs[e]);
                 }
                 o = make_uint4(w[0], w[1], w[2], w[3]);
               }

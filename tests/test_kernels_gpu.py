@@ -169,7 +169,9 @@ def test_gemm_bf16_swiglu_epilogue(M, N, K, keep):
 
 @pytest.mark.parametrize("B,S,N,K,hd", [(1, 256, 256, 64, 64), (2, 384, 512, 320, 64), (4, 128, 256, 192, 128)])
 def test_gemm_bf16_rope_epilogue(B, S, N, K, hd):
-    """Projection with interleaved-pair RoPE in the GEMM epilogue == separate GEMM + eisen_rope."""
+    """Projection with interleaved-pair RoPE in the GEMM epilogue: the rotation is applied to the f32
+    accumulators and the result rounded once, so it is closer to the f32 rotation of the f32 product than
+    a separate GEMM + eisen_rope (two roundings) and within one bf16 step of it."""
     M = B * S
     g = torch.Generator(device="cpu").manual_seed(M + N + K + hd)
     A = torch.randn(M, K, generator=g).to(torch.bfloat16).to(dev())
@@ -179,14 +181,24 @@ def test_gemm_bf16_rope_epilogue(B, S, N, K, hd):
     st = status_word()
     plain = torch.empty(M, N, dtype=torch.bfloat16, device=dev())
     eb.call("eisen_gemm_bf16", stream(), 0, 1, M, N, K, P(A), K, P(W), N, P(plain), N, 0, 1, 1.0, P(st))
-    ref = torch.empty_like(plain)
-    eb.call("eisen_rope", stream(), P(plain), P(ref), P(tab), B, S, N, hd, eb.BF16, 0, 0)
+    two = torch.empty_like(plain)
+    eb.call("eisen_rope", stream(), P(plain), P(two), P(tab), B, S, N, hd, eb.BF16, 0, 0)
     out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
     eb.call("eisen_gemm_bf16_rope", stream(), M, N, K, P(A), K, P(W), N, P(out), N, P(tab), S, hd, P(st))
     torch.cuda.synchronize()
     assert int(st.item()) == 0
-    # same rounding points as the two-kernel path: bit-identical
-    assert torch.equal(out.view(torch.int16), ref.view(torch.int16))
+    ref = _rope_f32(A.float() @ W.float(), tab, B, S, N, hd)
+    e_one, e_two = rel_l2(out.float().cpu().numpy(), ref.cpu().numpy()), rel_l2(two.float().cpu().numpy(), ref.cpu().numpy())
+    assert e_one < 2.5e-3 and e_one < e_two
+    assert rel_l2(out.float().cpu().numpy(), two.float().cpu().numpy()) < 6e-3
+
+
+def _rope_f32(y, tab, B, S, N, hd):
+    """Interleaved-pair RoPE of y [B*S, N] in f32 with the library's (cos, sin) table."""
+    y = y.view(B, S, N // hd, hd // 2, 2)
+    c, s_ = tab[..., 0].view(1, S, 1, hd // 2), tab[..., 1].view(1, S, 1, hd // 2)
+    out = torch.stack((y[..., 0] * c - y[..., 1] * s_, y[..., 0] * s_ + y[..., 1] * c), dim=-1)
+    return out.reshape(B * S, N)
 
 
 def _ptr_array(ts):
