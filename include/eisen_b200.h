@@ -93,7 +93,7 @@ int eisen_gemm_bf16_residual(void* stream, int a_mn, int b_mn, long long M, long
                              long long lda, const void* B, long long ldb, const void* R, long long ldr, void* C,
                              long long ldc, float alpha, int* status);
 /* A projection followed by RoPE (src/nn/attention.rs:320-333: Linear, then rope on q and k), with
- * the rotation in the GEMM epilogue: C = rope(bf16(A B)).  A is [M,K] row-major with M = batch *
+ * the rotation in the GEMM epilogue: C = bf16(rope(A B)), rotated in f32 and rounded once.  A is [M,K] row-major with M = batch *
  * seq_len token rows, B the [K,N] weight, table_cos_sin the table of eisen_rope_table for
  * (seq_len, head_dim).  M and N must be multiples of 256, head_dim a multiple of 8 dividing N. */
 int eisen_gemm_bf16_rope(void* stream, long long M, long long N, long long K, const void* A, long long lda, const void* B,
