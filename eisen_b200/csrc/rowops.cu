@@ -29,7 +29,18 @@ __device__ __forceinline__ void unpack16(const uint4& r, float (&v)[8]) {
     v[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
   }
 }
-
+__device__ __forceinline__ uint4 pack16(const float (&v)[4]) {
+  return make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
+}
+__device__ __forceinline__ uint4 pack16(const float (&v)[8]) {
+  uint32_t u[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);  // .x = low half = even element
+    u[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return make_uint4(u[0], u[1], u[2], u[3]);
+}
 
 template <typename T>
 __global__ void __launch_bounds__(RN_WARPS * 32)
@@ -827,6 +838,11 @@ __global__ void __launch_bounds__(256) softmax_bwd_kernel(const T* __restrict__ 
 constexpr int CE_THREADS = 256;
 
 // f32 logits keep the precise expf (parity with the CPU arm); bf16 logits use the fast one
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 template <typename T>
 __device__ __forceinline__ float exp_t(float x) {
   if constexpr (sizeof(T) == 2) return __expf(x);
@@ -1040,16 +1056,17 @@ ce_fused_kernel(T* __restrict__ logits, const int* __restrict__ targets, float* 
 // Register-resident form of ce_fused_kernel for rows of up to 1024 * NV 16-byte vectors: a CTA of
 // 1024 threads holds the whole row in registers (NV vectors per thread), so there is no staging
 // copy, every load of the row is in flight at once and two CTAs per SM keep 2048 threads busy.
-// The exponentials are computed twice (for the sum and for the gradient): keeping them in
-// registers (KEEP) halves the special-function work but needs 64 registers, i.e. one CTA per SM,
-// and measured slower (0.67 against 0.51 ms at 16384 x 32000 bf16), so it is off.
+// Each exponential is computed once: after the sum it replaces its logit in the same registers (in
+// T, so a bf16 row keeps bf16 exponentials; the row sum and the target's own gradient are formed
+// from the f32 values), and the gradient is e * scale / sum.  Keeping the exponentials in f32 beside
+// the row needs 64 registers, i.e. one CTA per SM, and measured slower (0.67 against 0.51 ms at
+// 16384 x 32000 bf16).
 template <typename T, int NV>
 __global__ void __launch_bounds__(1024, 2)
 ce_fused_reg_kernel(T* __restrict__ logits, const int* __restrict__ targets, float* __restrict__ row_loss,
                     float* __restrict__ lse_out, int V_, int ignore_index, float normalizer, float scale,
                     int* __restrict__ bad_target_flag) {
   constexpr int V = VecOf<T>::N;
-  constexpr bool KEEP = false;
   __shared__ float sh[32];
   const long long row = blockIdx.x;
   const int t = targets[row];
@@ -1070,16 +1087,45 @@ ce_fused_reg_kernel(T* __restrict__ logits, const int* __restrict__ targets, flo
     }
     return;
   }
+  // vectors past the end of the row read as -inf: they drop out of the maximum and add 0 to the sum
+  constexpr uint32_t NEG_INF = sizeof(T) == 2 ? 0xff80ff80u : 0xff800000u;
   uint4 raw[NV];
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
     const int v = threadIdx.x + j * 1024;
-    raw[j] = (v < nvec) ? ld_stream16(xr + (long long)v * V) : make_uint4(0, 0, 0, 0);
+    raw[j] = (v < nvec) ? ld_stream16(xr + (long long)v * V) : make_uint4(NEG_INF, NEG_INF, NEG_INF, NEG_INF);
   }
-  float m = -INFINITY;
+  // the thread that holds the target's vector keeps the target's logit in f32
+  const bool holder = (t / V) % 1024 == (int)threadIdx.x;
+  float xt = 0.0f;
+  if (holder) {
+    const int jt = (t / V) / 1024, kt = t % V;
+    uint4 r = raw[0];
 #pragma unroll
-  for (int j = 0; j < NV; ++j) {
-    if (threadIdx.x + j * 1024 < nvec) {
+    for (int j = 1; j < NV; ++j)
+      if (j == jt) r = raw[j];
+    float x[V];
+    unpack16(r, x);
+#pragma unroll
+    for (int k = 0; k < V; ++k)
+      if (k == kt) xt = x[k];
+  }
+  float m;
+  if constexpr (sizeof(T) == 2) {  // the maximum on packed pairs
+    auto pair = [](uint32_t w) { return *reinterpret_cast<const __nv_bfloat162*>(&w); };
+    __nv_bfloat162 m2 = pair(raw[0].x);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      m2 = __hmax2(m2, pair(raw[j].x));
+      m2 = __hmax2(m2, pair(raw[j].y));
+      m2 = __hmax2(m2, pair(raw[j].z));
+      m2 = __hmax2(m2, pair(raw[j].w));
+    }
+    m = fmaxf(__low2float(m2), __high2float(m2));
+  } else {
+    m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
       float x[V];
       unpack16(raw[j], x);
 #pragma unroll
@@ -1087,42 +1133,39 @@ ce_fused_reg_kernel(T* __restrict__ logits, const int* __restrict__ targets, flo
     }
   }
   const float gm = block_max(m, sh);
-  float e[KEEP ? NV * V : 1];
-  float s = 0.0f, xt = 0.0f;
+  float s = 0.0f;
+  const float ngm2 = -gm * 1.4426950408889634f;
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
-    const int v = threadIdx.x + j * 1024;
     float x[V];
     unpack16(raw[j], x);
 #pragma unroll
     for (int k = 0; k < V; ++k) {
-      const float ev = (v < nvec) ? exp_t<T>(x[k] - gm) : 0.0f;
-      if (KEEP) e[j * V + k] = ev;
-      s += ev;
-      if (v * V + k == t) xt = x[k];
+      if constexpr (sizeof(T) == 2) x[k] = ex2_approx(fmaf(x[k], 1.4426950408889634f, ngm2));
+      else x[k] = expf(x[k] - gm);
+      s += x[k];
     }
+    raw[j] = pack16(x);  // the exponentials take the place of the logits
   }
   s = block_sum(s, sh);
   const float l = gm + logf(s);
-  if (t / V % 1024 == (int)threadIdx.x) {  // the thread that holds the target's vector
-    row_loss[row] = -logf(expf(xt - gm) / s + 1e-8f) * normalizer;
-    if (lse_out) lse_out[row] = l;
-  }
   const float pscale = scale / s;  // softmax = e / s
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
     const int v = threadIdx.x + j * 1024;
     if (v < nvec) {
       float x[V];
-      if (!KEEP) unpack16(raw[j], x);
+      unpack16(raw[j], x);
 #pragma unroll
-      for (int k = 0; k < V; ++k) {
-        float g = KEEP ? e[j * V + k] * pscale : exp_t<T>(x[k] - l) * scale;
-        if (v * V + k == t) g -= scale;
-        x[k] = g;
-      }
+      for (int k = 0; k < V; ++k) x[k] *= pscale;
       st16(xr + (long long)v * V, x);
     }
+  }
+  if (holder) {
+    const float pt = expf(xt - gm) / s;
+    row_loss[row] = -logf(pt + 1e-8f) * normalizer;
+    if (lse_out) lse_out[row] = l;
+    xr[t] = from_f32<T>((pt - 1.0f) * scale);  // after this thread's own vector store to the same address
   }
 }
 
