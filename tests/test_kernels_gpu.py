@@ -807,6 +807,43 @@ def test_cross_entropy_fused_matches_the_two_pass_kernels(rows, vocab, dt):
     assert (l1.float().cpu().numpy()[T == IGNORE_INDEX] == 0).all()
 
 
+@pytest.mark.parametrize("vocab", [2048, 32000, 65536])
+def test_cross_entropy_fused_confident_and_negative_rows(vocab):
+    """Register-resident fused kernel on bf16 rows: a row whose target holds almost all the mass (its
+    gradient entry p_t - 1 is a small difference, formed from the f32 logit), a row of large negative
+    logits only (the padding vectors of a row that does not fill the CTA must not win the maximum)
+    and a row whose target is the last column."""
+    rng = np.random.default_rng(vocab)
+    rows = 6
+    L = rng.standard_normal((rows, vocab)).astype(np.float32)
+    T = rng.integers(0, vocab, rows).astype(np.int32)
+    L[0, T[0]] = 14.0
+    L[1] -= 300.0
+    T[2] = vocab - 1
+    L[3, T[3]] = 9.0
+    l = torch.from_numpy(L).to(torch.bfloat16).to(dev())
+    Lb = l.float().cpu().numpy().astype(np.float64)
+    t = torch.from_numpy(T).to(dev())
+    loss, row_loss, lse = torch.zeros(1, device=dev()), torch.empty(rows, device=dev()), torch.empty(rows, device=dev())
+    norm, gs = 1.0 / rows, 1.0
+    eb.call("eisen_ce_fused", stream(), P(l), P(t), P(loss), P(row_loss), P(lse), rows, vocab, IGNORE_INDEX, norm, gs, eb.BF16, None)
+    torch.cuda.synchronize()
+    m = Lb.max(axis=1, keepdims=True)
+    e = np.exp(Lb - m)
+    p = e / e.sum(axis=1, keepdims=True)
+    ref_lse = (m[:, 0] + np.log(e.sum(axis=1)))
+    g = p.copy()
+    g[np.arange(rows), T] -= 1.0
+    g *= norm * gs
+    out = l.float().cpu().numpy().astype(np.float64)
+    assert np.abs(lse.cpu().numpy() - ref_lse).max() < 2e-4 * np.abs(ref_lse).max()
+    assert rel_l2(out, g) < 6e-3
+    tgt = out[np.arange(rows), T]
+    assert np.all(np.abs(tgt - g[np.arange(rows), T]) <= 5e-3 * np.abs(g[np.arange(rows), T]) + 1e-12)
+    ref_loss = -(np.log(p[np.arange(rows), T] + 1e-8)).sum() * norm
+    assert abs(loss.item() - ref_loss) < 1e-3 * max(1.0, abs(ref_loss))
+
+
 def test_cross_entropy_flags_out_of_range_targets():
     # targets == vocab and -2 are neither valid nor the ignore index: the rows are skipped (loss and
     # gradient zero, no read outside the row) and the flag is raised
