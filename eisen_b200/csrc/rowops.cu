@@ -462,8 +462,9 @@ rmsnorm_fwd_staged_kernel(const T* __restrict__ x, const float* __restrict__ w, 
 // Backward with the rows staged in shared memory by bulk asynchronous copies (one 1-D copy per
 // tensor and group of ROWS rows, completion on an mbarrier): S stages per CTA are in flight instead
 // of what fits the registers, and without row buffers in registers three or four CTAs fit an SM.
-// Column ownership, the reduction of the two row sums and the dw partials are those of
-// rmsnorm_bwd_kernel.  A stage is refilled right after the barrier of the iteration that follows its
+// Column ownership and the reduction of the two row sums are those of rmsnorm_bwd_kernel; the CTA's
+// column sums of dw go to dw itself by vector reductions (dw_direct) or, for a fixed order, to
+// dw_partial for reduce_partials_kernel.  A stage is refilled right after the barrier of the iteration that follows its
 // last use, when every thread is known to be done with it.  Needs dim == 256 vectors and rows % ROWS == 0.
 template <typename T, int ROWS, int S, int CTAS, bool PK = false>
 __global__ void __launch_bounds__(RB_THREADS, CTAS)

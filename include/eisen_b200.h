@@ -50,13 +50,15 @@ const char* eisen_last_error(void);
 const char* eisen_version(void);
 /* number of kernels this library has launched in the process so far */
 long long eisen_launch_count(void);
-/* Fixed-order arithmetic (process-wide, default off).  Two kernels of the Bf16Mixed path add f32 values in
+/* Fixed-order arithmetic (process-wide, default off).  Three kernels of the Bf16Mixed path add f32 values in
  * an order that varies from run to run: weight-gradient GEMMs that split the token dimension over several
- * SM clusters (red.global.add), and the attention backward, whose key-tile CTAs add their dQ tiles to one
- * buffer.  With the switch on, a weight-gradient GEMM whose split is left to the library uses one slice per
- * tile, and the attention backward writes every key tile's dQ to its own slice of the workspace
- * (eisen_attn_bwd_workspace_bytes grows by the number of key tiles) and sums the slices in key order:
- * gradients are then bit-identical from run to run, at a few percent of step time.  The reference's
+ * SM clusters (red.global.add), the attention backward, whose key-tile CTAs add their dQ tiles to one
+ * buffer, and the staged RMSNorm backward, whose CTAs add their column sums of dw to one vector.  With the
+ * switch on, a weight-gradient GEMM whose split is left to the library uses one slice per tile, the
+ * attention backward writes every key tile's dQ to its own slice of the workspace
+ * (eisen_attn_bwd_workspace_bytes grows by the number of key tiles) and sums the slices in key order, and
+ * the RMSNorm backward writes per-CTA partials that a second launch adds in CTA order: gradients are then
+ * bit-identical from run to run, at a few percent of step time.  The reference's
  * kernels have no atomics on this path (one thread per output element), so they are run-to-run exact too. */
 int eisen_set_deterministic(int on);
 int eisen_get_deterministic(void);
