@@ -1214,7 +1214,7 @@ int rmsnorm_bwd_dispatch(cudaStream_t s, const T* x, const float* w, const T* dy
     const size_t smem = (size_t)stages * 2 * rows_per * dim * sizeof(T);
     // Outside the fixed-order mode the CTAs add their column sums into dw themselves: no second launch (7 us of a
     // 42 us call at 16384 x 2048).  In the fixed-order mode a second kernel adds the partials in CTA order.
-    const bool direct = !deterministic() && aligned16(dw);
+    const bool direct = !deterministic() && sizeof(T) == 2 && aligned16(dw);  // the f32 path keeps one order always
     static bool attr[5][2][MAX_DEVICE_SLOTS] = {{{false}}};
     auto go = [&](auto kern) -> int {
       bool& done = attr[mode - 2][sizeof(T) == 2][device_slot()];

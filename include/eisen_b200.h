@@ -53,7 +53,7 @@ long long eisen_launch_count(void);
 /* Fixed-order arithmetic (process-wide, default off).  Three kernels of the Bf16Mixed path add f32 values in
  * an order that varies from run to run: weight-gradient GEMMs that split the token dimension over several
  * SM clusters (red.global.add), the attention backward, whose key-tile CTAs add their dQ tiles to one
- * buffer, and the staged RMSNorm backward, whose CTAs add their column sums of dw to one vector.  With the
+ * buffer, and the staged RMSNorm backward on bf16 rows, whose CTAs add their column sums of dw to one vector.  With the
  * switch on, a weight-gradient GEMM whose split is left to the library uses one slice per tile, the
  * attention backward writes every key tile's dQ to its own slice of the workspace
  * (eisen_attn_bwd_workspace_bytes grows by the number of key tiles) and sums the slices in key order, and
